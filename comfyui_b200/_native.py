@@ -1,0 +1,152 @@
+"""ctypes binding of libcomfy_b200_moe.so (declared in include/comfy_b200_moe.h).
+
+There is no CPU or PyTorch fallback here: if the shared library is missing the import of the
+kernels fails with an error that tells how to build it.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from ctypes import POINTER, Structure, c_char_p, c_float, c_int, c_int32, c_int64, c_uint8, c_void_p
+
+from . import build as _build
+
+ABI_VERSION = 1
+
+OK, EINVAL, EUNSUPPORTED, ECUDA, ETIMEOUT, EDEVICE = range(6)
+BF16, FP32, FP8_E4M3 = 0, 1, 2
+ROW_ALIGN = 128
+TOKENS_PER_BLOCK = 32
+MAX_EXPERTS = 8
+
+EXPORTS = (
+    "comfy_moe_abi_version",
+    "comfy_moe_error_string",
+    "comfy_moe_plan_sizes",
+    "comfy_moe_gate_topk",
+    "comfy_moe_route_plan",
+    "comfy_moe_permute",
+    "comfy_moe_grouped_swiglu",
+    "comfy_moe_combine",
+    "comfy_moe_forward",
+    "comfy_moe_read_status",
+)
+
+
+class FfnWeights(Structure):
+    """struct ComfyMoeFfnWeights"""
+
+    _fields_ = [
+        ("w1", c_void_p),
+        ("w3", c_void_p),
+        ("w2", c_void_p),
+        ("ld13", c_int64),
+        ("ld2", c_int64),
+        ("hidden", c_int32),
+        ("reserved", c_int32),
+        ("scale_w1", c_void_p),
+        ("scale_w3", c_void_p),
+        ("scale_w2", c_void_p),
+        ("scale_in13", c_void_p),
+        ("scale_in2", c_void_p),
+    ]
+
+
+class Layer(Structure):
+    """struct ComfyMoeLayer"""
+
+    _fields_ = [
+        ("dim", c_int32),
+        ("n_experts", c_int32),
+        ("top_k", c_int32),
+        ("w_dtype", c_int32),
+        ("gate_dtype", c_int32),
+        ("reserved", c_int32),
+        ("w_gate", c_void_p),
+        ("experts", FfnWeights * MAX_EXPERTS),
+        ("shared", FfnWeights),
+    ]
+
+
+class Workspace(Structure):
+    """struct ComfyMoeWorkspace"""
+
+    _fields_ = [
+        ("topk_idx", c_void_p),
+        ("topk_weight", c_void_p),
+        ("block_counts", c_void_p),
+        ("block_offsets", c_void_p),
+        ("expert_counts", c_void_p),
+        ("expert_offsets", c_void_p),
+        ("row_map", c_void_p),
+        ("status", c_void_p),
+        ("x_perm", c_void_p),
+        ("x_q", c_void_p),
+        ("h_perm", c_void_p),
+        ("y_perm", c_void_p),
+        ("h_shared", c_void_p),
+        ("y_shared", c_void_p),
+        ("rows_cap", c_int64),
+    ]
+
+
+class MoeError(RuntimeError):
+    def __init__(self, fn: str, code: int, text: str):
+        super().__init__(f"{fn} failed with code {code}: {text}")
+        self.code = code
+
+
+_lib = None
+
+
+def lib_path() -> str:
+    return _build.LIB_PATH
+
+
+def load(build_if_missing: bool = False) -> ctypes.CDLL:
+    """Load the shared library (once).  Raises if it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    path = lib_path()
+    if not os.path.exists(path):
+        if build_if_missing:
+            _build.build()
+        else:
+            raise ImportError(
+                f"{path} is missing: the sm_100a kernels are not built. "
+                "Run `python -m comfyui_b200.build` (needs nvcc); there is no fallback path."
+            )
+    lib = ctypes.CDLL(path)
+    lib.comfy_moe_abi_version.restype = c_int
+    lib.comfy_moe_error_string.restype = c_char_p
+    lib.comfy_moe_error_string.argtypes = [c_int]
+    lib.comfy_moe_plan_sizes.argtypes = [c_int, c_int, c_int, POINTER(c_int64), POINTER(c_int)]
+    lib.comfy_moe_gate_topk.argtypes = [
+        c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+        c_float, c_void_p,
+    ]
+    lib.comfy_moe_route_plan.argtypes = [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]
+    lib.comfy_moe_permute.argtypes = [
+        c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+        c_void_p, c_void_p,
+    ]
+    lib.comfy_moe_grouped_swiglu.argtypes = [
+        c_int, c_int, POINTER(FfnWeights), POINTER(FfnWeights), c_void_p, c_int64, c_int, c_int, c_void_p,
+        c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+    ]
+    lib.comfy_moe_combine.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]
+    lib.comfy_moe_forward.argtypes = [POINTER(Layer), POINTER(Workspace), c_void_p, c_int, c_void_p, c_void_p]
+    lib.comfy_moe_read_status.argtypes = [c_void_p, c_void_p, POINTER(c_int32)]
+    for name in EXPORTS:
+        if name not in ("comfy_moe_error_string",):
+            getattr(lib, name).restype = c_int
+    if lib.comfy_moe_abi_version() != ABI_VERSION:
+        raise ImportError(f"{path}: ABI version {lib.comfy_moe_abi_version()} != expected {ABI_VERSION}; rebuild it")
+    _lib = lib
+    return lib
+
+
+def check(fn: str, code: int) -> None:
+    if code != OK:
+        raise MoeError(fn, code, load().comfy_moe_error_string(code).decode())

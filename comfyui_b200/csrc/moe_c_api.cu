@@ -1,0 +1,65 @@
+// Fused entry point and small utilities of the C ABI.
+#include "moe_common.cuh"
+
+extern "C" int comfy_moe_abi_version(void) { return COMFY_MOE_ABI_VERSION; }
+
+extern "C" const char* comfy_moe_error_string(int code) {
+  switch (code) {
+    case COMFY_MOE_OK: return "ok";
+    case COMFY_MOE_EINVAL: return "invalid argument (null pointer, negative size or misaligned pointer)";
+    case COMFY_MOE_EUNSUPPORTED: return "shape, dtype or expert count not covered by the sm_100a kernels";
+    case COMFY_MOE_ECUDA: return "a CUDA runtime or driver call failed";
+    case COMFY_MOE_ETIMEOUT: return "a bounded device-side wait ran out";
+    case COMFY_MOE_EDEVICE: return "device is not sm_100 or the driver lacks tensor-map support";
+    default: return "unknown error code";
+  }
+}
+
+extern "C" int comfy_moe_read_status(const int32_t* status, void* stream, int32_t* h_status) {
+  if (!status || !h_status) return COMFY_MOE_EINVAL;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (cudaMemcpyAsync(h_status, status, sizeof(int32_t), cudaMemcpyDeviceToHost, s) != cudaSuccess)
+    return COMFY_MOE_ECUDA;
+  if (cudaStreamSynchronize(s) != cudaSuccess) return COMFY_MOE_ECUDA;
+  return *h_status == 0 ? COMFY_MOE_OK : COMFY_MOE_ETIMEOUT;
+}
+
+// MOEFeedForwardSwiGLU.forward (comfy/ldm/hidream/model.py:307-325) as six launches on one stream:
+// gate, routing plan, permutation, two passes of the grouped GEMM, combine.
+extern "C" int comfy_moe_forward(const ComfyMoeLayer* L, const ComfyMoeWorkspace* ws, const void* x, int n_tokens,
+                                 void* out, void* stream) {
+  if (!L || !ws || n_tokens < 0) return COMFY_MOE_EINVAL;
+  if (n_tokens == 0) return COMFY_MOE_OK;
+  if (!x || !out) return COMFY_MOE_EINVAL;
+  if (L->top_k != 2 || L->n_experts < 2 || L->n_experts > COMFY_MOE_MAX_EXPERTS) return COMFY_MOE_EUNSUPPORTED;
+  if (!ws->topk_idx || !ws->topk_weight || !ws->block_counts || !ws->block_offsets || !ws->expert_counts ||
+      !ws->expert_offsets || !ws->row_map || !ws->status || !ws->x_perm || !ws->h_perm || !ws->y_perm ||
+      !ws->h_shared || !ws->y_shared)
+    return COMFY_MOE_EINVAL;
+  int64_t rows_need = 0;
+  int rc = comfy_moe_plan_sizes(n_tokens, L->n_experts, L->top_k, &rows_need, nullptr);
+  if (rc != COMFY_MOE_OK) return rc;
+  if (ws->rows_cap < rows_need) return COMFY_MOE_EINVAL;
+  const bool fp8 = L->w_dtype == COMFY_MOE_FP8_E4M3;
+  if (fp8 && !ws->x_q) return COMFY_MOE_EINVAL;
+
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (cudaMemsetAsync(ws->status, 0, 2 * sizeof(int32_t), s) != cudaSuccess) return COMFY_MOE_ECUDA;
+
+  rc = comfy_moe_gate_topk(x, L->w_gate, L->gate_dtype, n_tokens, L->dim, L->n_experts, L->top_k, ws->topk_idx,
+                           ws->topk_weight, ws->block_counts, ws->status + 1, nullptr, 1e-6f, stream);
+  if (rc != COMFY_MOE_OK) return rc;
+  rc = comfy_moe_route_plan(ws->block_counts, n_tokens, L->n_experts, ws->block_offsets, ws->expert_counts,
+                            ws->expert_offsets, stream);
+  if (rc != COMFY_MOE_OK) return rc;
+  rc = comfy_moe_permute(x, ws->topk_idx, ws->block_offsets, ws->expert_offsets, n_tokens, L->dim, L->n_experts,
+                         fp8 ? COMFY_MOE_FP8_E4M3 : COMFY_MOE_BF16, fp8 ? L->experts[0].scale_in13 : nullptr,
+                         ws->x_perm, fp8 ? ws->x_q : nullptr, fp8 ? L->shared.scale_in13 : nullptr, ws->row_map,
+                         stream);
+  if (rc != COMFY_MOE_OK) return rc;
+  rc = comfy_moe_grouped_swiglu(L->w_dtype, L->n_experts, L->experts, &L->shared, ws->expert_offsets, ws->rows_cap,
+                                n_tokens, L->dim, ws->x_perm, ws->h_perm, ws->y_perm, fp8 ? ws->x_q : x,
+                                ws->h_shared, ws->y_shared, ws->status, stream);
+  if (rc != COMFY_MOE_OK) return rc;
+  return comfy_moe_combine(ws->y_perm, ws->row_map, ws->topk_weight, ws->y_shared, n_tokens, L->dim, out, stream);
+}

@@ -1,0 +1,502 @@
+// Grouped SwiGLU expert GEMM for sm_100a: TMA-fed tcgen05.mma with fp32 accumulators in TMEM.
+//
+// One persistent kernel, launched twice per layer call:
+//   pass 1 (kSwiglu):  h[m, j]  = silu(a[m,:] . w1[j,:]) * (a[m,:] . w3[j,:])
+//   pass 2 (plain):    y[m, n]  = h[m,:] . w2[n,:]
+// over "groups" = the routed experts (rows expert_offsets[e] .. expert_offsets[e+1] of the permuted
+// activations, every block a multiple of 128 rows) plus, optionally, the shared expert over the
+// un-permuted rows.  It replaces the three F.linear calls, F.silu and the product of
+// FeedForwardSwiGLU.forward (comfy/ldm/hidream/model.py:238) for all experts at once, and in the
+// fp8 variant the clamp / cast / torch._scaled_mm sequence of comfy/ops.py:338-348.
+//
+// CTA layout (192 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer,
+// warps 2-5 = epilogue (TMEM -> registers -> global).  A tile is 128 rows x 256 accumulator
+// columns; in pass 1 the 256 columns are 128 of w1 next to the matching 128 of w3, so one MMA
+// stream yields both halves of the SwiGLU and the epilogue emits 128 columns of h.
+// Shared memory: 4 stages x (A 16 KB + B 32 KB), 128-byte swizzle.  TMEM: 2 x 256 columns, so the
+// epilogue of tile i overlaps the MMAs of tile i+1.
+#include <cuda.h>
+
+#include "moe_common.cuh"
+#include "ptx_sm100.cuh"
+
+namespace comfy_b200 {
+
+constexpr int kBlockM = 128;
+constexpr int kBlockN = 256;
+constexpr int kRowBytes = 128;                    // bytes of K per operand row per stage
+constexpr int kStages = 4;
+constexpr int kAccStages = 2;
+constexpr int kABytes = kBlockM * kRowBytes;      // 16 KB
+constexpr int kBHalfBytes = 128 * kRowBytes;      // 16 KB: one 128-row B box
+constexpr int kBBytes = 2 * kBHalfBytes;          // 32 KB
+constexpr int kStageBytes = kABytes + kBBytes;    // 48 KB
+constexpr int kGemmThreads = 192;
+constexpr int kTmemCols = kAccStages * kBlockN;   // 512
+constexpr int kMaxGroups = kMaxExperts + 1;
+constexpr int kMaxMaps = 2 + 2 * kMaxGroups;
+constexpr size_t kGemmSmemBytes = static_cast<size_t>(kStages) * kStageBytes + 1024;  // + alignment slack
+
+// Device-side status codes written to *status when a bounded wait gives up.
+constexpr int kStatusProducerTimeout = 1;
+constexpr int kStatusMmaTimeout = 2;
+constexpr int kStatusEpilogueTimeout = 3;
+
+struct GemmGroup {
+  int a_map;          // index of the A tensor map
+  int b0_map;         // first 128-row B box
+  int b1_map;         // second 128-row B box
+  int b1_row_off;     // its row offset relative to the first box (0 in pass 1, 128 in pass 2)
+  int k_blocks;       // K / (kRowBytes / element size)
+  int n_tiles;        // tiles along the output columns
+  int routed_index;   // >= 0: rows [expert_offsets[i], expert_offsets[i+1]);  < 0: rows [0, static_rows)
+  int static_rows;
+  void* out;          // output base
+  long long ld_out;   // output leading dimension in elements
+  const float* scale_a;        // fp8: activation scale (NULL = 1)
+  const float* scale_b0;       // fp8: weight scale of the first box
+  const float* scale_b1;       // fp8: weight scale of the second box
+  const float* out_scale;      // fp8 pass 1: scale_input of w2 (h is multiplied by bf16(1/s) before the cast)
+};
+
+struct alignas(64) GemmParams {
+  CUtensorMap maps[kMaxMaps];
+  GemmGroup groups[kMaxGroups];
+  const int32_t* expert_offsets;
+  int32_t* status;
+  int num_groups;
+};
+
+__device__ __forceinline__ float silu_bf16_steps(float a_bf16) {
+  // the reference computes silu on a bf16 tensor: fp32 math, one rounding to bf16
+  return round_bf16(__fdividef(a_bf16, 1.0f + __expf(-a_bf16)));
+}
+
+template <bool kFp8, bool kSwiglu>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t full_bar[kStages];
+  __shared__ __align__(8) uint64_t empty_bar[kStages];
+  __shared__ __align__(8) uint64_t tmem_full_bar[kAccStages];
+  __shared__ __align__(8) uint64_t tmem_empty_bar[kAccStages];
+  __shared__ __align__(8) uint64_t drain_bar;
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+  __shared__ int s_tile_start[kMaxGroups + 1];
+  __shared__ int s_m_tiles[kMaxGroups];
+  __shared__ int s_row_base[kMaxGroups];
+  __shared__ int s_row_limit[kMaxGroups];
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+
+  if (tid == 0) {
+    for (int s = 0; s < kStages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    for (int s = 0; s < kAccStages; ++s) { mbar_init(&tmem_full_bar[s], 1); mbar_init(&tmem_empty_bar[s], 128); }
+    mbar_init(&drain_bar, 1);
+    fence_mbar_init();
+    abort_flag = 0;
+    int start = 0;
+    for (int g = 0; g < p.num_groups; ++g) {
+      const GemmGroup& grp = p.groups[g];
+      int base, rows, limit;
+      if (grp.routed_index >= 0) {
+        base = p.expert_offsets[grp.routed_index];
+        rows = p.expert_offsets[grp.routed_index + 1] - base;
+        limit = base + rows;
+      } else {
+        base = 0;
+        rows = grp.static_rows;
+        limit = rows;
+      }
+      const int m_tiles = (rows + kBlockM - 1) / kBlockM;
+      s_tile_start[g] = start;
+      s_m_tiles[g] = m_tiles;
+      s_row_base[g] = base;
+      s_row_limit[g] = limit;
+      start += m_tiles * grp.n_tiles;
+    }
+    s_tile_start[p.num_groups] = start;
+  }
+  if (warp == 1) {
+    tmem_alloc(&tmem_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+
+  const uint32_t tmem_base = tmem_slot;
+  const int total_tiles = s_tile_start[p.num_groups];
+  volatile int* abort_ptr = &abort_flag;
+  constexpr int kElemsPerRow = kFp8 ? kRowBytes : kRowBytes / 2;   // K elements per stage
+
+  auto decode = [&](int t, int& g, int& m_tile, int& n_tile) {
+    g = 0;
+    while (t >= s_tile_start[g + 1]) ++g;
+    const int local = t - s_tile_start[g];
+    const int mt = s_m_tiles[g];
+    n_tile = local / mt;
+    m_tile = local - n_tile * mt;
+  };
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        int g, m_tile, n_tile;
+        decode(t, g, m_tile, n_tile);
+        const GemmGroup& grp = p.groups[g];
+        const CUtensorMap* map_a = &p.maps[grp.a_map];
+        const CUtensorMap* map_b0 = &p.maps[grp.b0_map];
+        const CUtensorMap* map_b1 = &p.maps[grp.b1_map];
+        const int a_row = s_row_base[g] + m_tile * kBlockM;
+        const int b_row = n_tile * (kSwiglu ? 128 : kBlockN);
+        const int kb_count = grp.k_blocks;
+        for (int kb = 0; kb < kb_count; ++kb, ++it) {
+          const int s = it % kStages;
+          const uint32_t ph = (it / kStages) & 1u;
+          if (!mbar_wait(&empty_bar[s], ph ^ 1u, abort_ptr)) {
+            atomicCAS(p.status, 0, kStatusProducerTimeout);
+            abort_flag = 1;
+            ok = false;
+            break;
+          }
+          uint8_t* stage = smem + static_cast<size_t>(s) * kStageBytes;
+          mbar_arrive_expect_tx(&full_bar[s], kStageBytes);
+          tma_load_2d(stage, map_a, &full_bar[s], kb * kElemsPerRow, a_row);
+          tma_load_2d(stage + kABytes, map_b0, &full_bar[s], kb * kElemsPerRow, b_row);
+          tma_load_2d(stage + kABytes + kBHalfBytes, map_b1, &full_bar[s], kb * kElemsPerRow,
+                      b_row + grp.b1_row_off);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc<kFp8>(kBlockM, kBlockN);
+      uint32_t it = 0, tile_count = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tile_count) {
+        int g, m_tile, n_tile;
+        decode(t, g, m_tile, n_tile);
+        const int kb_count = p.groups[g].k_blocks;
+        const uint32_t as = tile_count & 1u;
+        const uint32_t aph = (tile_count >> 1) & 1u;
+        if (!mbar_wait(&tmem_empty_bar[as], aph ^ 1u, abort_ptr)) {
+          atomicCAS(p.status, 0, kStatusMmaTimeout);
+          abort_flag = 1;
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + as * kBlockN;
+        for (int kb = 0; kb < kb_count; ++kb, ++it) {
+          const int s = it % kStages;
+          const uint32_t ph = (it / kStages) & 1u;
+          if (!mbar_wait(&full_bar[s], ph, abort_ptr)) {
+            atomicCAS(p.status, 0, kStatusMmaTimeout);
+            abort_flag = 1;
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t a_addr = smem_u32(smem + static_cast<size_t>(s) * kStageBytes);
+          const uint64_t a_desc = umma_desc_k_sw128(a_addr);
+          const uint64_t b_desc = umma_desc_k_sw128(a_addr + kABytes);
+#pragma unroll
+          for (int k = 0; k < kRowBytes / 32; ++k) {
+            // every MMA consumes 32 bytes of K per row: advance the start address by 32 B (2 units of 16 B)
+            umma_ss<kFp8>(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[s]);   // frees the stage once these MMAs have read it
+        }
+        if (ok) umma_commit(&tmem_full_bar[as]);
+      }
+      // make sure nothing issued by this thread is still running before TMEM is released
+      umma_commit(&drain_bar);
+      mbar_wait(&drain_bar, 0, abort_ptr);
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (4 warps)
+    const int quarter = warp & 3;   // TMEM lanes this warp may read: [32*quarter, 32*quarter + 32)
+    uint32_t tile_count = 0;
+    for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++tile_count) {
+      int g, m_tile, n_tile;
+      decode(t, g, m_tile, n_tile);
+      const GemmGroup& grp = p.groups[g];
+      const uint32_t as = tile_count & 1u;
+      const uint32_t aph = (tile_count >> 1) & 1u;
+      bool ok = mbar_wait(&tmem_full_bar[as], aph, abort_ptr);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) {
+        if (lane == 0) { atomicCAS(p.status, 0, kStatusEpilogueTimeout); abort_flag = 1; }
+        break;
+      }
+      tc_fence_after_sync();
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + as * kBlockN;
+      const int row = s_row_base[g] + m_tile * kBlockM + quarter * 32 + lane;
+      const bool valid = row < s_row_limit[g];
+
+      float alpha0 = 1.f, alpha1 = 1.f, out_inv = 1.f;
+      bool out_scaled = false;
+      if constexpr (kFp8) {
+        const float sa = grp.scale_a ? __ldg(grp.scale_a) : 1.f;
+        alpha0 = sa * (grp.scale_b0 ? __ldg(grp.scale_b0) : 1.f);
+        alpha1 = sa * (grp.scale_b1 ? __ldg(grp.scale_b1) : 1.f);
+        if (kSwiglu && grp.out_scale) { out_inv = round_bf16(1.0f / __ldg(grp.out_scale)); out_scaled = true; }
+      }
+
+      if constexpr (kSwiglu) {
+        const long long col0 = static_cast<long long>(n_tile) * 128;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t ra[32], rb[32];
+          tmem_ld_32x32b_x32(taddr + c * 32, ra);
+          tmem_ld_32x32b_x32(taddr + 128 + c * 32, rb);
+          tmem_ld_wait();
+          float h[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            float a = __uint_as_float(ra[j]), b = __uint_as_float(rb[j]);
+            if constexpr (kFp8) { a *= alpha0; b *= alpha1; }
+            a = round_bf16(a);
+            b = round_bf16(b);
+            h[j] = round_bf16(silu_bf16_steps(a) * b);
+            if constexpr (kFp8) { if (out_scaled) h[j] = round_bf16(h[j] * out_inv); }
+          }
+          if (valid) {
+            if constexpr (kFp8) {
+              uint8_t* o = static_cast<uint8_t*>(grp.out) + static_cast<long long>(row) * grp.ld_out + col0 + c * 32;
+              uint32_t w[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                w[j] = static_cast<uint32_t>(f2_to_e4m3x2(h[4 * j], h[4 * j + 1])) |
+                       (static_cast<uint32_t>(f2_to_e4m3x2(h[4 * j + 2], h[4 * j + 3])) << 16);
+              reinterpret_cast<uint4*>(o)[0] = make_uint4(w[0], w[1], w[2], w[3]);
+              reinterpret_cast<uint4*>(o)[1] = make_uint4(w[4], w[5], w[6], w[7]);
+            } else {
+              __nv_bfloat16* o = static_cast<__nv_bfloat16*>(grp.out) + static_cast<long long>(row) * grp.ld_out + col0 + c * 32;
+#pragma unroll
+              for (int j = 0; j < 4; ++j)
+                reinterpret_cast<uint4*>(o)[j] =
+                    make_uint4(pack_bf16x2(h[8 * j], h[8 * j + 1]), pack_bf16x2(h[8 * j + 2], h[8 * j + 3]),
+                               pack_bf16x2(h[8 * j + 4], h[8 * j + 5]), pack_bf16x2(h[8 * j + 6], h[8 * j + 7]));
+            }
+          }
+        }
+      } else {
+        const long long col0 = static_cast<long long>(n_tile) * kBlockN;
+        __nv_bfloat16* o_row = static_cast<__nv_bfloat16*>(grp.out) + static_cast<long long>(row) * grp.ld_out + col0;
+#pragma unroll 1
+        for (int c = 0; c < kBlockN / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(taddr + c * 32, r);
+          tmem_ld_wait();
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            v[j] = __uint_as_float(r[j]);
+            if constexpr (kFp8) v[j] *= (c < 4 ? alpha0 : alpha1);
+          }
+          if (valid) {
+            __nv_bfloat16* o = o_row + c * 32;
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              reinterpret_cast<uint4*>(o)[j] =
+                  make_uint4(pack_bf16x2(v[8 * j], v[8 * j + 1]), pack_bf16x2(v[8 * j + 2], v[8 * j + 3]),
+                             pack_bf16x2(v[8 * j + 4], v[8 * j + 5]), pack_bf16x2(v[8 * j + 6], v[8 * j + 7]));
+          }
+        }
+      }
+      tc_fence_before_sync();
+      mbar_arrive(&tmem_empty_bar[as]);
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  __syncwarp();
+  if (*abort_ptr) {
+    // a wait gave up: give copies still in flight time to land before shared memory is released
+    const long long t0 = clock64();
+    while (clock64() - t0 < 2000000LL) __nanosleep(1000);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ==================================================================================== host side
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+// [rows, cols] row-major with leading dimension ld (elements); boxes of 128 rows x 128 bytes.
+static int make_map(CUtensorMap* map, const void* base, bool fp8, int64_t rows, int64_t cols, int64_t ld) {
+  EncodeTiledFn encode = get_encode_fn();
+  if (!encode) return COMFY_MOE_EDEVICE;
+  const int es = fp8 ? 1 : 2;
+  if (!base || !aligned16(base) || rows <= 0 || cols <= 0 || (ld * es) % 16 != 0) return COMFY_MOE_EINVAL;
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * es};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(kRowBytes / es), 128u};
+  cuuint32_t estr[2] = {1u, 1u};
+  CUresult r = encode(map, fp8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                      const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                      CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? COMFY_MOE_OK : COMFY_MOE_ECUDA;
+}
+
+static int device_sm_count(int* sms) {
+  static int cached_dev = -1, cached_sms = 0, cached_major = 0;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return COMFY_MOE_ECUDA;
+  if (dev != cached_dev) {
+    int n = 0, major = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return COMFY_MOE_ECUDA;
+    if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) return COMFY_MOE_ECUDA;
+    cached_dev = dev; cached_sms = n; cached_major = major;
+  }
+  if (cached_major != 10) return COMFY_MOE_EDEVICE;
+  *sms = cached_sms;
+  return COMFY_MOE_OK;
+}
+
+template <bool kFp8, bool kSwiglu>
+static int launch_gemm(const GemmParams& params, int64_t max_tiles, int sms, cudaStream_t stream) {
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(grouped_gemm_kernel<kFp8, kSwiglu>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(kGemmSmemBytes)) != cudaSuccess)
+      return COMFY_MOE_ECUDA;
+    configured = true;
+  }
+  const int grid = static_cast<int>(max_tiles < sms ? max_tiles : sms);
+  if (grid <= 0) return COMFY_MOE_OK;
+  grouped_gemm_kernel<kFp8, kSwiglu><<<grid, kGemmThreads, kGemmSmemBytes, stream>>>(params);
+  return check_launch();
+}
+
+}  // namespace comfy_b200
+
+using namespace comfy_b200;
+
+extern "C" int comfy_moe_grouped_swiglu(int w_dtype, int n_experts, const ComfyMoeFfnWeights* h_experts,
+                                        const ComfyMoeFfnWeights* h_shared, const int32_t* expert_offsets,
+                                        int64_t rows_cap, int n_tokens, int dim, const void* x_perm, void* h_perm,
+                                        void* y_perm, const void* x_shared, void* h_shared_ws, void* y_shared,
+                                        int32_t* status, void* stream) {
+  if (n_experts < 0 || n_experts > kMaxExperts || dim <= 0 || n_tokens < 0 || rows_cap < 0) return COMFY_MOE_EINVAL;
+  if (w_dtype != COMFY_MOE_BF16 && w_dtype != COMFY_MOE_FP8_E4M3) return COMFY_MOE_EUNSUPPORTED;
+  if (!status) return COMFY_MOE_EINVAL;
+  if (n_experts > 0 && (!h_experts || !expert_offsets || !x_perm || !h_perm || !y_perm || rows_cap <= 0))
+    return COMFY_MOE_EINVAL;
+  const bool has_shared = h_shared != nullptr && n_tokens > 0;
+  if (has_shared && (!x_shared || !h_shared_ws || !y_shared)) return COMFY_MOE_EINVAL;
+  if (n_experts == 0 && !has_shared) return COMFY_MOE_OK;
+  if (dim % kBlockN != 0) return COMFY_MOE_EUNSUPPORTED;
+  const bool fp8 = w_dtype == COMFY_MOE_FP8_E4M3;
+  const int k_elems = fp8 ? kRowBytes : kRowBytes / 2;
+  if (dim % k_elems != 0) return COMFY_MOE_EUNSUPPORTED;
+
+  int sms = 0;
+  int rc = device_sm_count(&sms);
+  if (rc != COMFY_MOE_OK) return rc;
+
+  GemmParams p1, p2;
+  memset(&p1, 0, sizeof(p1));
+  memset(&p2, 0, sizeof(p2));
+  p1.expert_offsets = p2.expert_offsets = expert_offsets;
+  p1.status = p2.status = status;
+  int64_t tiles1 = 0, tiles2 = 0;
+  int n_maps1 = 0, n_maps2 = 0, g = 0;
+
+  int hidden_routed = 0;
+  if (n_experts > 0) {
+    hidden_routed = h_experts[0].hidden;
+    for (int e = 0; e < n_experts; ++e)
+      if (h_experts[e].hidden != hidden_routed) return COMFY_MOE_EUNSUPPORTED;
+    if (hidden_routed <= 0 || hidden_routed % 128 != 0 || hidden_routed % k_elems != 0) return COMFY_MOE_EUNSUPPORTED;
+    // A operands of the routed groups: the permuted activations and the permuted hidden activations
+    if ((rc = make_map(&p1.maps[n_maps1], x_perm, fp8, rows_cap, dim, dim)) != COMFY_MOE_OK) return rc;
+    if ((rc = make_map(&p2.maps[n_maps2], h_perm, fp8, rows_cap, hidden_routed, hidden_routed)) != COMFY_MOE_OK) return rc;
+    const int a1 = n_maps1++, a2 = n_maps2++;
+    const int64_t m_tiles_cap = rows_cap / kBlockM;
+    for (int e = 0; e < n_experts; ++e, ++g) {
+      const ComfyMoeFfnWeights& w = h_experts[e];
+      if (!w.w1 || !w.w2 || !w.w3) return COMFY_MOE_EINVAL;
+      if ((rc = make_map(&p1.maps[n_maps1], w.w1, fp8, w.hidden, dim, w.ld13)) != COMFY_MOE_OK) return rc;
+      if ((rc = make_map(&p1.maps[n_maps1 + 1], w.w3, fp8, w.hidden, dim, w.ld13)) != COMFY_MOE_OK) return rc;
+      if ((rc = make_map(&p2.maps[n_maps2], w.w2, fp8, dim, w.hidden, w.ld2)) != COMFY_MOE_OK) return rc;
+      GemmGroup& g1 = p1.groups[g];
+      g1.a_map = a1; g1.b0_map = n_maps1; g1.b1_map = n_maps1 + 1; g1.b1_row_off = 0;
+      g1.k_blocks = dim / k_elems; g1.n_tiles = w.hidden / 128; g1.routed_index = e; g1.static_rows = 0;
+      g1.out = h_perm; g1.ld_out = w.hidden;
+      g1.scale_a = w.scale_in13; g1.scale_b0 = w.scale_w1; g1.scale_b1 = w.scale_w3; g1.out_scale = w.scale_in2;
+      GemmGroup& g2 = p2.groups[g];
+      g2.a_map = a2; g2.b0_map = n_maps2; g2.b1_map = n_maps2; g2.b1_row_off = 128;
+      g2.k_blocks = w.hidden / k_elems; g2.n_tiles = dim / kBlockN; g2.routed_index = e; g2.static_rows = 0;
+      g2.out = y_perm; g2.ld_out = dim;
+      g2.scale_a = w.scale_in2; g2.scale_b0 = w.scale_w2; g2.scale_b1 = w.scale_w2; g2.out_scale = nullptr;
+      n_maps1 += 2; n_maps2 += 1;
+    }
+    tiles1 += m_tiles_cap * (hidden_routed / 128);
+    tiles2 += m_tiles_cap * (dim / kBlockN);
+  }
+  if (has_shared) {
+    const ComfyMoeFfnWeights& w = *h_shared;
+    if (!w.w1 || !w.w2 || !w.w3) return COMFY_MOE_EINVAL;
+    if (w.hidden <= 0 || w.hidden % 128 != 0 || w.hidden % k_elems != 0) return COMFY_MOE_EUNSUPPORTED;
+    if ((rc = make_map(&p1.maps[n_maps1], x_shared, fp8, n_tokens, dim, dim)) != COMFY_MOE_OK) return rc;
+    if ((rc = make_map(&p1.maps[n_maps1 + 1], w.w1, fp8, w.hidden, dim, w.ld13)) != COMFY_MOE_OK) return rc;
+    if ((rc = make_map(&p1.maps[n_maps1 + 2], w.w3, fp8, w.hidden, dim, w.ld13)) != COMFY_MOE_OK) return rc;
+    if ((rc = make_map(&p2.maps[n_maps2], h_shared_ws, fp8, n_tokens, w.hidden, w.hidden)) != COMFY_MOE_OK) return rc;
+    if ((rc = make_map(&p2.maps[n_maps2 + 1], w.w2, fp8, dim, w.hidden, w.ld2)) != COMFY_MOE_OK) return rc;
+    GemmGroup& g1 = p1.groups[g];
+    g1.a_map = n_maps1; g1.b0_map = n_maps1 + 1; g1.b1_map = n_maps1 + 2; g1.b1_row_off = 0;
+    g1.k_blocks = dim / k_elems; g1.n_tiles = w.hidden / 128; g1.routed_index = -1; g1.static_rows = n_tokens;
+    g1.out = h_shared_ws; g1.ld_out = w.hidden;
+    g1.scale_a = w.scale_in13; g1.scale_b0 = w.scale_w1; g1.scale_b1 = w.scale_w3; g1.out_scale = w.scale_in2;
+    GemmGroup& g2 = p2.groups[g];
+    g2.a_map = n_maps2; g2.b0_map = n_maps2 + 1; g2.b1_map = n_maps2 + 1; g2.b1_row_off = 128;
+    g2.k_blocks = w.hidden / k_elems; g2.n_tiles = dim / kBlockN; g2.routed_index = -1; g2.static_rows = n_tokens;
+    g2.out = y_shared; g2.ld_out = dim;
+    g2.scale_a = w.scale_in2; g2.scale_b0 = w.scale_w2; g2.scale_b1 = w.scale_w2; g2.out_scale = nullptr;
+    const int64_t m_tiles = (n_tokens + kBlockM - 1) / kBlockM;
+    tiles1 += m_tiles * (w.hidden / 128);
+    tiles2 += m_tiles * (dim / kBlockN);
+    ++g;
+  }
+  p1.num_groups = p2.num_groups = g;
+
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (fp8) {
+    if ((rc = launch_gemm<true, true>(p1, tiles1, sms, s)) != COMFY_MOE_OK) return rc;
+    return launch_gemm<true, false>(p2, tiles2, sms, s);
+  }
+  if ((rc = launch_gemm<false, true>(p1, tiles1, sms, s)) != COMFY_MOE_OK) return rc;
+  return launch_gemm<false, false>(p2, tiles2, sms, s);
+}

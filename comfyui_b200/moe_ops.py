@@ -1,0 +1,321 @@
+"""Tensor-level wrappers around the C ABI (include/comfy_b200_moe.h).
+
+PyTorch is used for device memory and streams only: every function here passes raw device pointers
+of tensors it was given (or of workspaces it allocated through torch's caching allocator) to the
+shared library and launches on ``torch.cuda.current_stream()``.  None of them has a PyTorch or CPU
+implementation behind it.
+"""
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass, field
+from typing import List, Optional, Sequence, Tuple
+
+import torch
+
+from . import _native as N
+
+_FP8 = torch.float8_e4m3fn
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _dtype_code(dt: torch.dtype) -> int:
+    if dt == torch.bfloat16:
+        return N.BF16
+    if dt == torch.float32:
+        return N.FP32
+    if dt == _FP8:
+        return N.FP8_E4M3
+    raise ValueError(f"unsupported dtype {dt}")
+
+
+def _need_cuda(*tensors: Optional[torch.Tensor]) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise ValueError("the sm_100a kernels need CUDA tensors; there is no CPU path")
+
+
+def plan_sizes(n_tokens: int, n_experts: int, top_k: int = 2) -> Tuple[int, int]:
+    """(rows_cap, n_blocks) for the permuted buffers and the per-block count scratch."""
+    rows = ctypes.c_int64()
+    blocks = ctypes.c_int()
+    N.check("comfy_moe_plan_sizes", N.load().comfy_moe_plan_sizes(n_tokens, n_experts, top_k, rows, blocks))
+    return rows.value, blocks.value
+
+
+# --------------------------------------------------------------------------------------- weights
+@dataclass
+class FfnPack:
+    """Device pointers of one FeedForwardSwiGLU; keeps the tensors alive."""
+
+    w1: torch.Tensor
+    w3: torch.Tensor
+    w2: torch.Tensor
+    scale_w1: Optional[torch.Tensor] = None
+    scale_w3: Optional[torch.Tensor] = None
+    scale_w2: Optional[torch.Tensor] = None
+    scale_in13: Optional[torch.Tensor] = None
+    scale_in2: Optional[torch.Tensor] = None
+
+    def __post_init__(self):
+        _need_cuda(self.w1, self.w2, self.w3)
+        for w in (self.w1, self.w2, self.w3):
+            if w.dim() != 2 or w.stride(1) != 1:
+                raise ValueError("expert weights must be 2-D with a contiguous last dimension")
+        if self.w1.shape != self.w3.shape or self.w1.stride(0) != self.w3.stride(0):
+            raise ValueError("w1 and w3 must share shape and leading dimension")
+        if self.w2.shape != (self.w1.shape[1], self.w1.shape[0]):
+            raise ValueError("w2 must be [dim, hidden]")
+        for s in (self.scale_w1, self.scale_w3, self.scale_w2, self.scale_in13, self.scale_in2):
+            if s is not None and (s.dtype != torch.float32 or s.numel() != 1 or not s.is_cuda):
+                raise ValueError("scales must be fp32 scalars on the device")
+
+    @property
+    def hidden(self) -> int:
+        return self.w1.shape[0]
+
+    @property
+    def dim(self) -> int:
+        return self.w1.shape[1]
+
+    def fill(self, s: N.FfnWeights) -> None:
+        s.w1, s.w3, s.w2 = self.w1.data_ptr(), self.w3.data_ptr(), self.w2.data_ptr()
+        s.ld13, s.ld2 = self.w1.stride(0), self.w2.stride(0)
+        s.hidden = self.hidden
+        s.reserved = 0
+        for name in ("scale_w1", "scale_w3", "scale_w2", "scale_in13", "scale_in2"):
+            t = getattr(self, name)
+            setattr(s, name, None if t is None else t.data_ptr())
+
+    def struct(self) -> N.FfnWeights:
+        s = N.FfnWeights()
+        self.fill(s)
+        return s
+
+
+@dataclass
+class LayerPack:
+    """Everything comfy_moe_forward needs to know about one MOEFeedForwardSwiGLU."""
+
+    gate: torch.Tensor
+    experts: Sequence[FfnPack]
+    shared: FfnPack
+    top_k: int = 2
+    c_layer: N.Layer = field(init=False)
+
+    def __post_init__(self):
+        _need_cuda(self.gate)
+        if not self.gate.is_contiguous():
+            raise ValueError("gate weight must be contiguous")
+        L = N.Layer()
+        L.dim = self.gate.shape[1]
+        L.n_experts = len(self.experts)
+        L.top_k = self.top_k
+        L.w_dtype = _dtype_code(self.experts[0].w1.dtype)
+        L.gate_dtype = _dtype_code(self.gate.dtype)
+        L.w_gate = self.gate.data_ptr()
+        for i, e in enumerate(self.experts):
+            e.fill(L.experts[i])
+        self.shared.fill(L.shared)
+        self.c_layer = L
+
+    @property
+    def dim(self) -> int:
+        return self.gate.shape[1]
+
+    @property
+    def n_experts(self) -> int:
+        return len(self.experts)
+
+    @property
+    def fp8(self) -> bool:
+        return self.experts[0].w1.dtype == _FP8
+
+
+# --------------------------------------------------------------------------------------- workspace
+class Workspace:
+    """Device buffers for one call of the layer at a given token count.  Owned by the caller."""
+
+    def __init__(self, n_tokens: int, dim: int, n_experts: int, hidden: int, hidden_shared: int, fp8: bool,
+                 device: torch.device, top_k: int = 2):
+        self.n_tokens, self.dim, self.n_experts = n_tokens, dim, n_experts
+        self.hidden, self.hidden_shared, self.fp8 = hidden, hidden_shared, fp8
+        rows_cap, n_blocks = plan_sizes(n_tokens, n_experts, top_k)
+        self.rows_cap, self.n_blocks = rows_cap, n_blocks
+        act = _FP8 if fp8 else torch.bfloat16
+        i32 = dict(dtype=torch.int32, device=device)
+        self.topk_idx = torch.empty((n_tokens, top_k), **i32)
+        self.topk_weight = torch.empty((n_tokens, top_k), dtype=torch.float32, device=device)
+        self.block_counts = torch.empty((max(n_blocks, 1), n_experts), **i32)
+        self.block_offsets = torch.empty((max(n_blocks, 1), n_experts), **i32)
+        self.expert_counts = torch.zeros((n_experts,), **i32)
+        self.expert_offsets = torch.zeros((n_experts + 1,), **i32)
+        self.row_map = torch.empty((n_tokens, top_k), **i32)
+        self.status = torch.zeros((2,), **i32)
+        self.x_perm = torch.empty((rows_cap, dim), dtype=act, device=device)
+        self.x_q = torch.empty((n_tokens, dim), dtype=act, device=device) if fp8 else None
+        self.h_perm = torch.empty((rows_cap, hidden), dtype=act, device=device)
+        self.y_perm = torch.empty((rows_cap, dim), dtype=torch.bfloat16, device=device)
+        self.h_shared = torch.empty((max(n_tokens, 1), hidden_shared), dtype=act, device=device)
+        self.y_shared = torch.empty((max(n_tokens, 1), dim), dtype=torch.bfloat16, device=device)
+        ws = N.Workspace()
+        for name in ("topk_idx", "topk_weight", "block_counts", "block_offsets", "expert_counts", "expert_offsets",
+                     "row_map", "status", "x_perm", "x_q", "h_perm", "y_perm", "h_shared", "y_shared"):
+            t = getattr(self, name)
+            setattr(ws, name, None if t is None else t.data_ptr())
+        ws.rows_cap = rows_cap
+        self.c_ws = ws
+
+    @classmethod
+    def for_layer(cls, layer: LayerPack, n_tokens: int) -> "Workspace":
+        return cls(n_tokens, layer.dim, layer.n_experts, layer.experts[0].hidden, layer.shared.hidden, layer.fp8,
+                   layer.gate.device, layer.top_k)
+
+    def nbytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in vars(self).values() if isinstance(t, torch.Tensor))
+
+
+# --------------------------------------------------------------------------------------- kernels
+def gate_topk(x: torch.Tensor, w_gate: torch.Tensor, *, neartie_eps: float = 1e-6, want_flags: bool = False,
+              topk_idx: Optional[torch.Tensor] = None, topk_weight: Optional[torch.Tensor] = None,
+              block_counts: Optional[torch.Tensor] = None):
+    """Fused MoEGate.forward.  x: bf16 [N, D] contiguous; w_gate: bf16 or fp32 [E, D].
+
+    Returns (topk_idx int32 [N,2], topk_weight fp32 [N,2], block_counts int32 [n_blocks,E],
+    neartie_count int32 [1], neartie_flags uint8 [N] or None).
+    """
+    _need_cuda(x, w_gate)
+    if x.dtype != torch.bfloat16 or x.dim() != 2 or not x.is_contiguous():
+        raise ValueError("x must be a contiguous bf16 [N, D] tensor")
+    n, d = x.shape
+    e = w_gate.shape[0]
+    w_gate = w_gate.contiguous()
+    _, n_blocks = plan_sizes(n, e)
+    dev = x.device
+    if topk_idx is None:
+        topk_idx = torch.empty((n, 2), dtype=torch.int32, device=dev)
+    if topk_weight is None:
+        topk_weight = torch.empty((n, 2), dtype=torch.float32, device=dev)
+    if block_counts is None:
+        block_counts = torch.empty((max(n_blocks, 1), e), dtype=torch.int32, device=dev)
+    count = torch.zeros((1,), dtype=torch.int32, device=dev)
+    flags = torch.zeros((n,), dtype=torch.uint8, device=dev) if want_flags else None
+    rc = N.load().comfy_moe_gate_topk(_ptr(x), _ptr(w_gate), _dtype_code(w_gate.dtype), n, d, e, 2, _ptr(topk_idx),
+                                      _ptr(topk_weight), _ptr(block_counts), _ptr(count), _ptr(flags),
+                                      float(neartie_eps), _stream())
+    N.check("comfy_moe_gate_topk", rc)
+    return topk_idx, topk_weight, block_counts, count, flags
+
+
+def route_plan(block_counts: torch.Tensor, n_tokens: int, n_experts: int):
+    """Per-expert scan of the block counts.  Returns (block_offsets, expert_counts, expert_offsets)."""
+    _need_cuda(block_counts)
+    dev = block_counts.device
+    block_offsets = torch.empty_like(block_counts)
+    expert_counts = torch.empty((n_experts,), dtype=torch.int32, device=dev)
+    expert_offsets = torch.empty((n_experts + 1,), dtype=torch.int32, device=dev)
+    rc = N.load().comfy_moe_route_plan(_ptr(block_counts), n_tokens, n_experts, _ptr(block_offsets),
+                                       _ptr(expert_counts), _ptr(expert_offsets), _stream())
+    N.check("comfy_moe_route_plan", rc)
+    return block_offsets, expert_counts, expert_offsets
+
+
+def permute(x: torch.Tensor, topk_idx: torch.Tensor, block_offsets: torch.Tensor, expert_offsets: torch.Tensor,
+            n_experts: int, *, fp8: bool = False, act_scale: Optional[torch.Tensor] = None,
+            xq_scale: Optional[torch.Tensor] = None, want_xq: bool = False, zero_fill: bool = False):
+    """Row permutation into per-expert blocks.  Returns (x_perm, row_map, x_q or None)."""
+    _need_cuda(x, topk_idx)
+    n, d = x.shape
+    rows_cap, _ = plan_sizes(n, n_experts)
+    act = _FP8 if fp8 else torch.bfloat16
+    alloc = torch.zeros if zero_fill else torch.empty
+    x_perm = alloc((rows_cap, d), dtype=act, device=x.device) if not fp8 else \
+        alloc((rows_cap, d), dtype=torch.uint8, device=x.device).view(_FP8)
+    row_map = torch.empty((n, 2), dtype=torch.int32, device=x.device)
+    x_q = torch.empty((n, d), dtype=_FP8, device=x.device) if (fp8 and want_xq) else None
+    rc = N.load().comfy_moe_permute(_ptr(x), _ptr(topk_idx), _ptr(block_offsets), _ptr(expert_offsets), n, d,
+                                    n_experts, N.FP8_E4M3 if fp8 else N.BF16, _ptr(act_scale), _ptr(x_perm),
+                                    _ptr(x_q), _ptr(xq_scale), _ptr(row_map), _stream())
+    N.check("comfy_moe_permute", rc)
+    return x_perm, row_map, x_q
+
+
+def grouped_swiglu(experts: Sequence[FfnPack], shared: Optional[FfnPack], expert_offsets: Optional[torch.Tensor],
+                   x_perm: Optional[torch.Tensor], x_shared: Optional[torch.Tensor], *,
+                   status: Optional[torch.Tensor] = None, check_status: bool = True):
+    """Both passes of the grouped expert GEMM.  Returns (y_perm or None, y_shared or None, h_perm, h_shared)."""
+    ref = experts[0] if experts else shared
+    dim, fp8 = ref.dim, ref.w1.dtype == _FP8
+    dev = ref.w1.device
+    act = _FP8 if fp8 else torch.bfloat16
+    n_e = len(experts)
+    arr = (N.FfnWeights * max(n_e, 1))()
+    for i, e in enumerate(experts):
+        e.fill(arr[i])
+    rows_cap = 0 if x_perm is None else x_perm.shape[0]
+    h_perm = y_perm = None
+    if n_e:
+        h_perm = torch.empty((rows_cap, experts[0].hidden), dtype=act, device=dev)
+        y_perm = torch.empty((rows_cap, dim), dtype=torch.bfloat16, device=dev)
+    n_tokens = 0 if x_shared is None else x_shared.shape[0]
+    sh = h_sh = y_sh = None
+    if shared is not None and n_tokens > 0:
+        sh = shared.struct()
+        h_sh = torch.empty((n_tokens, shared.hidden), dtype=act, device=dev)
+        y_sh = torch.empty((n_tokens, dim), dtype=torch.bfloat16, device=dev)
+    if status is None:
+        status = torch.zeros((2,), dtype=torch.int32, device=dev)
+    rc = N.load().comfy_moe_grouped_swiglu(
+        N.FP8_E4M3 if fp8 else N.BF16, n_e, arr, ctypes.byref(sh) if sh is not None else None,
+        _ptr(expert_offsets), rows_cap, n_tokens, dim, _ptr(x_perm), _ptr(h_perm), _ptr(y_perm), _ptr(x_shared),
+        _ptr(h_sh), _ptr(y_sh), _ptr(status), _stream())
+    N.check("comfy_moe_grouped_swiglu", rc)
+    if check_status:
+        read_status(status)
+    return y_perm, y_sh, h_perm, h_sh
+
+
+def combine(y_perm: torch.Tensor, row_map: torch.Tensor, topk_weight: torch.Tensor,
+            y_shared: Optional[torch.Tensor], out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[t] = bf16(bf16(bf16(w0*y[r0]) + bf16(w1*y[r1])) + y_shared[t])."""
+    _need_cuda(y_perm, row_map, topk_weight, y_shared)
+    n = row_map.shape[0]
+    d = y_perm.shape[1]
+    if out is None:
+        out = torch.empty((n, d), dtype=torch.bfloat16, device=y_perm.device)
+    rc = N.load().comfy_moe_combine(_ptr(y_perm), _ptr(row_map), _ptr(topk_weight), _ptr(y_shared), n, d, _ptr(out),
+                                    _stream())
+    N.check("comfy_moe_combine", rc)
+    return out
+
+
+def read_status(status: torch.Tensor) -> None:
+    """Synchronises the current stream and raises if a device-side wait gave up."""
+    h = ctypes.c_int32(0)
+    rc = N.load().comfy_moe_read_status(_ptr(status), _stream(), h)
+    if rc != N.OK:
+        raise N.MoeError("comfy_moe_read_status", rc, f"device status word = {h.value}")
+
+
+def moe_forward(layer: LayerPack, x: torch.Tensor, ws: Optional[Workspace] = None,
+                out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The whole layer through comfy_moe_forward.  x: bf16 [N, D] contiguous on the device."""
+    _need_cuda(x)
+    if x.dtype != torch.bfloat16 or x.dim() != 2 or not x.is_contiguous():
+        raise ValueError("x must be a contiguous bf16 [N, D] tensor")
+    n = x.shape[0]
+    if ws is None or ws.n_tokens != n:
+        ws = Workspace.for_layer(layer, n)
+    if out is None:
+        out = torch.empty_like(x)
+    rc = N.load().comfy_moe_forward(ctypes.byref(layer.c_layer), ctypes.byref(ws.c_ws), _ptr(x), n, _ptr(out),
+                                    _stream())
+    N.check("comfy_moe_forward", rc)
+    return out

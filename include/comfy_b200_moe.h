@@ -1,0 +1,183 @@
+/*
+ * C ABI of libcomfy_b200_moe.so: the HiDream mixture-of-experts feed-forward on B200 (sm_100a).
+ *
+ * Conventions
+ *   - every pointer is a DEVICE pointer unless the name starts with `h_`;
+ *   - `stream` is a cudaStream_t passed as void* (NULL = legacy default stream);
+ *   - functions return 0 on success or one of the COMFY_MOE_E* codes; they never throw, never
+ *     allocate device memory and never synchronise unless the comment says so;
+ *   - activations are bf16, row-major, contiguous in the last dimension;
+ *   - expert weights use torch.nn.Linear's layout [out_features, in_features] row-major with a
+ *     leading dimension `ld` in elements (so a row- or column-slice of a weight can be passed
+ *     without copying), dtype bf16 or fp8 e4m3fn with a per-tensor fp32 scale on the device.
+ *
+ * Reference interface replaced (paths inside the ComfyUI tree):
+ *   comfy/ldm/hidream/model.py:242-283   MoEGate
+ *   comfy/ldm/hidream/model.py:215-238   FeedForwardSwiGLU
+ *   comfy/ldm/hidream/model.py:287-346   MOEFeedForwardSwiGLU.forward / moe_infer
+ *   comfy/ops.py:314-358, 379-410        fp8_linear / scaled_fp8_ops.Linear
+ */
+#ifndef COMFY_B200_MOE_H_
+#define COMFY_B200_MOE_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define COMFY_MOE_ABI_VERSION 1
+
+/* Return codes. */
+#define COMFY_MOE_OK 0
+#define COMFY_MOE_EINVAL 1        /* null pointer, negative size, misaligned pointer            */
+#define COMFY_MOE_EUNSUPPORTED 2  /* shape / dtype / expert count outside what the kernels cover */
+#define COMFY_MOE_ECUDA 3         /* a CUDA runtime or driver call failed (launch, encode)       */
+#define COMFY_MOE_ETIMEOUT 4      /* a bounded device-side wait ran out (see comfy_moe_read_status) */
+#define COMFY_MOE_EDEVICE 5       /* not an sm_100 device, or the driver lacks tensor-map support */
+
+/* Element types for weights and for the activations fed to the expert GEMMs. */
+#define COMFY_MOE_BF16 0
+#define COMFY_MOE_FP32 1
+#define COMFY_MOE_FP8_E4M3 2
+
+/* Rows of every routed expert's block start on a multiple of this in the permuted layout. */
+#define COMFY_MOE_ROW_ALIGN 128
+/* Tokens handled by one thread block of the gate / permute kernels (fixes the block-count scratch size). */
+#define COMFY_MOE_TOKENS_PER_BLOCK 32
+#define COMFY_MOE_MAX_EXPERTS 8
+
+int comfy_moe_abi_version(void);
+const char* comfy_moe_error_string(int code);
+
+/* Sizes (in elements / rows) of the buffers a caller must provide for `n_tokens` tokens. Pure host arithmetic.
+ *   rows_cap      rows of x_perm / h / y_perm: top_k*n_tokens + n_experts*COMFY_MOE_ROW_ALIGN
+ *   n_blocks      ceil(n_tokens / COMFY_MOE_TOKENS_PER_BLOCK); block_counts and block_offsets hold n_blocks*n_experts int32
+ */
+int comfy_moe_plan_sizes(int n_tokens, int n_experts, int top_k, int64_t* rows_cap, int* n_blocks);
+
+/* ---- MoEGate.forward (comfy/ldm/hidream/model.py:263-283) --------------------------------------
+ * logits = x . w_gate^T in fp32, softmax over experts, top-2 (largest first, lowest index on exact ties),
+ * no renormalisation.  Also writes, per block of COMFY_MOE_TOKENS_PER_BLOCK tokens, how many routed slots
+ * went to each expert (input of comfy_moe_route_plan).
+ *   x             bf16 [n_tokens, dim]
+ *   w_gate        [n_experts, dim], dtype w_dtype (COMFY_MOE_BF16 or COMFY_MOE_FP32)
+ *   topk_idx      int32 [n_tokens, 2]          topk_weight  fp32 [n_tokens, 2]
+ *   block_counts  int32 [n_blocks, n_experts]  (fully overwritten)
+ *   neartie_count int32 [1], may be NULL: incremented for every token whose 2nd and 3rd scores differ by
+ *                 less than neartie_eps (caller zeroes it);  neartie_flags uint8 [n_tokens], may be NULL.
+ */
+int comfy_moe_gate_topk(const void* x, const void* w_gate, int w_dtype, int n_tokens, int dim, int n_experts,
+                        int top_k, int32_t* topk_idx, float* topk_weight, int32_t* block_counts,
+                        int32_t* neartie_count, uint8_t* neartie_flags, float neartie_eps, void* stream);
+
+/* ---- routing plan: replaces argsort + bincount().cpu().cumsum (model.py:330-332) without a host sync ----
+ *   block_counts   int32 [n_blocks, n_experts]  from the gate
+ *   block_offsets  int32 [n_blocks, n_experts]  out: rows of expert e that precede block b, within e's block
+ *   expert_counts  int32 [n_experts]            out: routed slots per expert (= bincount of topk_idx)
+ *   expert_offsets int32 [n_experts + 1]        out: first row of each expert in the permuted layout, each a
+ *                                               multiple of COMFY_MOE_ROW_ALIGN; [n_experts] = rows in use
+ */
+int comfy_moe_route_plan(const int32_t* block_counts, int n_tokens, int n_experts, int32_t* block_offsets,
+                         int32_t* expert_counts, int32_t* expert_offsets, void* stream);
+
+/* ---- permutation: replaces x[exp_token_idx] gathers (model.py:338-339) ------------------------------
+ * Copies row t of x to row row_map[t*2+k] of x_perm for k = 0,1; order inside an expert block is by slot index
+ * (stable), so the layout is reproducible run to run.
+ *   x_perm      [rows_cap, dim] in act_dtype: COMFY_MOE_BF16 copies; COMFY_MOE_FP8_E4M3 quantises as
+ *               comfy/ops.py:338-343 does (clamp to +-448 then round-to-nearest-even when act_inv_scale is NULL,
+ *               else multiply by bf16(*act_inv_scale) in bf16 first)
+ *   x_q         only for fp8: [n_tokens, dim] e4m3, the un-permuted quantised copy the shared expert reads
+ *               (x_q_inv_scale: its own optional scale); may be NULL
+ *   row_map     int32 [n_tokens, 2] out
+ */
+int comfy_moe_permute(const void* x, const int32_t* topk_idx, const int32_t* block_offsets,
+                      const int32_t* expert_offsets, int n_tokens, int dim, int n_experts, int act_dtype,
+                      const float* act_inv_scale, void* x_perm, void* x_q, const float* x_q_inv_scale,
+                      int32_t* row_map, void* stream);
+
+/* One SwiGLU feed-forward's weights (FeedForwardSwiGLU, model.py:233-238). */
+typedef struct ComfyMoeFfnWeights {
+  const void* w1;         /* [hidden, dim], leading dimension ld13 */
+  const void* w3;         /* [hidden, dim], leading dimension ld13 */
+  const void* w2;         /* [dim, hidden], leading dimension ld2  */
+  int64_t ld13;
+  int64_t ld2;
+  int32_t hidden;         /* multiple of 128 */
+  int32_t reserved;
+  /* fp8 only (NULL = 1.0): per-tensor scales as comfy/ops.py:379-410 stores them */
+  const float* scale_w1;
+  const float* scale_w3;
+  const float* scale_w2;
+  const float* scale_in13; /* scale_input shared by w1 and w3 (they see the same activation) */
+  const float* scale_in2;  /* scale_input of w2 */
+} ComfyMoeFfnWeights;
+
+/* ---- grouped SwiGLU expert GEMM (model.py:238 for every expert, and the shared expert) -------------------
+ * Two launches of one persistent tcgen05/TMEM kernel:
+ *   h      = silu(a . w1^T) * (a . w3^T)    (bf16 roundings after each of the reference's four steps)
+ *   y      = h . w2^T
+ * over the routed groups (rows expert_offsets[e] .. expert_offsets[e+1] of x_perm) and, when `shared` is not
+ * NULL, one more group over the un-permuted rows.
+ *   w_dtype        COMFY_MOE_BF16 or COMFY_MOE_FP8_E4M3 (activations x_perm / x_shared / h_* use the same)
+ *   x_perm         [rows_cap, dim]        h_perm [rows_cap, hidden] workspace   y_perm bf16 [rows_cap, dim]
+ *   x_shared       [n_tokens, dim]        h_shared [n_tokens, hidden_s]         y_shared bf16 [n_tokens, dim]
+ *   status         int32 [1]: the kernels write a non-zero code here if a bounded wait ran out (caller zeroes)
+ */
+int comfy_moe_grouped_swiglu(int w_dtype, int n_experts, const ComfyMoeFfnWeights* h_experts,
+                             const ComfyMoeFfnWeights* h_shared, const int32_t* expert_offsets, int64_t rows_cap,
+                             int n_tokens, int dim, const void* x_perm, void* h_perm, void* y_perm,
+                             const void* x_shared, void* h_shared_ws, void* y_shared, int32_t* status,
+                             void* stream);
+
+/* ---- weighted combine: replaces mul_ + scatter_reduce_ + shared add (model.py:341-345, 324) ---------------
+ * out[t] = bf16( bf16( bf16(w0*y[r0]) + bf16(w1*y[r1]) ) + y_shared[t] ), weights rounded to bf16 first.
+ * y_shared may be NULL (routed part only).  n_partials > 1 sums that many row maps (hidden-split experts).
+ */
+int comfy_moe_combine(const void* y_perm, const int32_t* row_map, const float* topk_weight, const void* y_shared,
+                      int n_tokens, int dim, void* out, void* stream);
+
+/* Everything one layer call needs, for the fused entry point. */
+typedef struct ComfyMoeLayer {
+  int32_t dim;
+  int32_t n_experts;
+  int32_t top_k;
+  int32_t w_dtype;            /* expert weight dtype */
+  int32_t gate_dtype;         /* COMFY_MOE_BF16 or COMFY_MOE_FP32 */
+  int32_t reserved;
+  const void* w_gate;         /* [n_experts, dim] */
+  ComfyMoeFfnWeights experts[COMFY_MOE_MAX_EXPERTS];
+  ComfyMoeFfnWeights shared;
+} ComfyMoeLayer;
+
+typedef struct ComfyMoeWorkspace {
+  int32_t* topk_idx;       /* [n_tokens, 2] */
+  float* topk_weight;      /* [n_tokens, 2] */
+  int32_t* block_counts;   /* [n_blocks, n_experts] */
+  int32_t* block_offsets;  /* [n_blocks, n_experts] */
+  int32_t* expert_counts;  /* [n_experts] */
+  int32_t* expert_offsets; /* [n_experts + 1] */
+  int32_t* row_map;        /* [n_tokens, 2] */
+  int32_t* status;         /* [2]: [0] device wait status, [1] near-tie count */
+  void* x_perm;            /* [rows_cap, dim] act dtype */
+  void* x_q;               /* fp8 only: [n_tokens, dim] */
+  void* h_perm;            /* [rows_cap, hidden] act dtype */
+  void* y_perm;            /* bf16 [rows_cap, dim] */
+  void* h_shared;          /* [n_tokens, hidden_s] act dtype */
+  void* y_shared;          /* bf16 [n_tokens, dim] */
+  int64_t rows_cap;
+} ComfyMoeWorkspace;
+
+/* ---- MOEFeedForwardSwiGLU.forward (model.py:307-325): gate -> plan -> permute -> experts -> combine ----
+ * x, out: bf16 [n_tokens, dim].  The layer struct and the workspace struct live in HOST memory.
+ */
+int comfy_moe_forward(const ComfyMoeLayer* h_layer, const ComfyMoeWorkspace* h_ws, const void* x, int n_tokens,
+                      void* out, void* stream);
+
+/* Synchronises `stream`, copies status[0] to *h_status and returns COMFY_MOE_ETIMEOUT if it is non-zero. */
+int comfy_moe_read_status(const int32_t* status, void* stream, int32_t* h_status);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* COMFY_B200_MOE_H_ */
