@@ -1,0 +1,353 @@
+#!/usr/bin/env python
+"""Benchmark of the HiDream MoE feed-forward layer: tokens/s of one full layer call.
+
+    python bench.py --gpus N --steps K --warmup W            # this repository's sm_100a kernels
+    python bench.py --impl reference --steps K --warmup W    # the reference algorithm on the host cores
+
+A step is one call of the layer (gate -> plan -> permute -> grouped SwiGLU GEMM x2 -> combine, shared expert
+included) on synthetic data: dim 2560, 4 routed experts of hidden 6912 (top-2), shared expert of hidden 3584,
+bf16, 8192 tokens per GPU, weights N(0, 0.02^2), inputs N(0, 1), seeded.  With N > 1 the routed experts are
+expert-parallel (NCCL all-to-all dispatch and combine), every rank owns 8192 tokens (weak scaling) and runs the
+shared expert on them.
+
+One JSON line is printed by rank 0.  `value` is measured with the inputs resident in HBM; `e2e` is the same
+metric through the module call with pinned-host input and output copies inside the timed region; `roofline`
+describes the grouped GEMM (both passes) against the measured bf16 tensor peak; `cpu_baseline` is the CPU
+oracle (a restatement of the reference's PyTorch code) timed on this machine's host cores.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+DIM, HIDDEN_DIM, N_EXPERTS, TOP_K = 2560, 4 * 2560, 4, 2
+HIDDEN, HIDDEN_SHARED = 6912, 3584
+TOKENS_PER_GPU = 8192
+METRIC = "MoE-FFN tokens/s (HiDream MOEFeedForwardSwiGLU layer, dim 2560, 4 experts top-2 + shared)"
+FLOPS_PER_TOKEN_GEMM = 2 * TOP_K * 3 * DIM * HIDDEN + 2 * 3 * DIM * HIDDEN_SHARED
+FLOPS_PER_TOKEN = FLOPS_PER_TOKEN_GEMM + 2 * DIM * N_EXPERTS
+CPU_SAMPLE_TOKENS = 1024
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return dict(source="measured", hbm_gbs=p["hbm_gbs"], tflops_burst=p["bf16_tflops"],
+                    tflops_sustained=p.get("bf16_tflops_sustained", p["bf16_tflops"]))
+    return dict(source="fallback", hbm_gbs=6650.0, tflops_burst=1590.0, tflops_sustained=1400.0)
+
+
+# ------------------------------------------------------------------------------------------ clocks
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML while the timed region runs."""
+
+    REASONS = {
+        0x1: "gpu_idle", 0x2: "applications_clocks_setting", 0x4: "sw_power_cap", 0x8: "hw_slowdown",
+        0x10: "sync_boost", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown",
+        0x80: "hw_power_brake_slowdown", 0x100: "display_clock_setting",
+    }
+
+    def __init__(self, index: int, period_s: float = 0.01):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self.period, self._stop, self._thread, self._h, self._nv = period_s, threading.Event(), None, None, None
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self._nv = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self._nv = None
+
+    def _run(self):
+        nv = self._nv
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM))
+                mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self._h)
+                for bit, name in self.REASONS.items():
+                    if mask & bit and name != "gpu_idle":
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop.wait(self.period)
+
+    def __enter__(self):
+        if self._nv is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": 0}
+        return {"sm_mhz": statistics.median(self.samples), "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+# ------------------------------------------------------------------------------------------ CPU arm
+def oracle_cpu_tokens_per_s(n_tokens: int, steps: int, warmup: int):
+    """The CPU oracle on `n_tokens` of the bench workload, all host threads.  Returns (tokens/s, s/step, cores)."""
+    from oracle import hidream_moe_oracle as O
+
+    layer = {k: v.bfloat16() for k, v in O.make_layer(DIM, HIDDEN_DIM, N_EXPERTS, seed=0).items()}
+    x = O.make_input(TOKENS_PER_GPU, DIM, seed=1).bfloat16()[:n_tokens].contiguous()
+    with torch.no_grad():
+        for _ in range(warmup):
+            O.moe_layer(x, layer, gate_in_fp32=True)
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            O.moe_layer(x, layer, gate_in_fp32=True)
+        dt = (time.perf_counter() - t0) / max(steps, 1)
+    return n_tokens / dt, dt, torch.get_num_threads()
+
+
+def run_reference_arm(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    value, dt, cores = oracle_cpu_tokens_per_s(CPU_SAMPLE_TOKENS, args.steps, max(args.warmup, 1))
+    sample = (f"each step = the first {CPU_SAMPLE_TOKENS} of the {TOKENS_PER_GPU} bench tokens through the CPU oracle "
+              f"(oracle/hidream_moe_oracle.py: the reference's gate + moe_infer + shared expert in PyTorch, bf16)")
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": workload_config(args.gpus),
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+
+
+def workload_config(n_gpus: int):
+    return {
+        "workload": "BASELINE config 2: HiDream MoE FFN layer, bf16 weights and activations, 2 x 4096 tokens per GPU, "
+                    "fp32 gate",
+        "tokens_per_gpu": TOKENS_PER_GPU, "global_tokens": TOKENS_PER_GPU * n_gpus, "dim": DIM, "experts": N_EXPERTS,
+        "top_k": TOP_K, "hidden": HIDDEN, "hidden_shared": HIDDEN_SHARED,
+        "parallelism": "single GPU" if n_gpus == 1 else f"expert-parallel x{n_gpus} (NCCL all-to-all), shared expert "
+                                                        "data-parallel",
+        "l2": "no flush: one step touches 0.48 GB of weights and 0.6 GB of activations, far more than the 126 MB L2",
+    }
+
+
+# ------------------------------------------------------------------------------------------ GPU arm
+def make_synthetic(dev, seed_w: int = 0, seed_x: int = 1):
+    """Seeded synthetic weights and input, generated on the host exactly like the oracle's recipe (same
+    generator, same draw order) without importing it, then moved to the device."""
+    g = torch.Generator().manual_seed(seed_w)
+    state = {}
+
+    def draw(name, shape):
+        state[name] = (torch.randn(shape, generator=g, dtype=torch.float32) * 0.02).bfloat16().to(dev)
+
+    for prefix, h in [("shared_experts", HIDDEN_SHARED)] + [(f"experts.{e}", HIDDEN) for e in range(N_EXPERTS)]:
+        draw(prefix + ".w1.weight", (h, DIM))
+        draw(prefix + ".w2.weight", (DIM, h))
+        draw(prefix + ".w3.weight", (h, DIM))
+    draw("gate.weight", (N_EXPERTS, DIM))
+    gx = torch.Generator().manual_seed(seed_x)
+    x = torch.randn((TOKENS_PER_GPU, DIM), generator=gx, dtype=torch.float32).bfloat16()
+    return state, x
+
+
+def run_gpu_arm(args) -> None:
+    import torch.distributed as dist
+
+    from comfyui_b200 import _native, moe_ops, ops
+    from comfyui_b200.ldm.hidream.model import MOEFeedForwardSwiGLU
+
+    _native.load()   # no fallback: fail here if the extension is not built
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("launch with torchrun --nproc-per-node N for --gpus N > 1")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    state, x_host = make_synthetic(dev, seed_w=0, seed_x=1 + rank)
+    module = MOEFeedForwardSwiGLU(DIM, HIDDEN_DIM, N_EXPERTS, TOP_K, dtype=torch.bfloat16, device=dev,
+                                  operations=ops.disable_weight_init).eval()
+    module.load_state_dict(state, strict=True)
+    x_pinned = x_host.pin_memory()
+    out_pinned = torch.empty_like(x_host).pin_memory()
+    x = x_host.to(dev).view(2, TOKENS_PER_GPU // 2, DIM)
+    n = TOKENS_PER_GPU
+
+    if world > 1:
+        from comfyui_b200.expert_parallel import ExpertParallelMoE
+
+        runner = ExpertParallelMoE(module, dist.group.WORLD)
+        step = lambda inp: runner(inp)                      # noqa: E731
+        launches_per_step = runner.launches_per_step
+    else:
+        assert ops._layer_pack(module, x) is not None, "bench: layer not eligible for the sm_100a kernels"
+        step = lambda inp: module(inp)                      # noqa: E731
+        launches_per_step = 6   # gate, plan, permute, GEMM pass 1, GEMM pass 2, combine
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    with torch.inference_mode():
+        for _ in range(max(args.warmup, 3)):
+            step(x)
+        # ---- device-resident timing: exactly K steps between two events
+        barrier()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with ClockSampler(local_rank) as clocks:
+            ev0.record()
+            for _ in range(args.steps):
+                step(x)
+            ev1.record()
+            barrier()
+        ms_total = ev0.elapsed_time(ev1)
+
+        # ---- end to end: pinned host -> device, layer, device -> pinned host, every step
+        x_dev = torch.empty_like(x)
+        for _ in range(3):
+            x_dev.view(n, DIM).copy_(x_pinned, non_blocking=True)
+            out_pinned.copy_(step(x_dev).view(n, DIM), non_blocking=True)
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            x_dev.view(n, DIM).copy_(x_pinned, non_blocking=True)
+            out_pinned.copy_(step(x_dev).view(n, DIM), non_blocking=True)
+        e1.record()
+        barrier()
+        ms_e2e = e0.elapsed_time(e1)
+
+        # ---- per-stage timing of the same work through the stage-level C ABI (single GPU only)
+        stages = None
+        if world == 1:
+            stages = time_stages(module, x.view(n, DIM), args.steps, moe_ops, ops)
+
+    times = torch.tensor([ms_total, ms_e2e], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    ms_total, ms_e2e = times.tolist()
+
+    if rank == 0:
+        peaks = measured_peaks()
+        ms_step = ms_total / args.steps
+        value = n * world / (ms_step * 1e-3)
+        line = {
+            "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": workload_config(world),
+            "e2e": {"value": n * world / (ms_e2e / args.steps * 1e-3), "unit": "tokens/s",
+                    "h2d_bytes_per_step": x_pinned.numel() * 2, "d2h_bytes_per_step": out_pinned.numel() * 2},
+            "gpu_launches": launches_per_step * args.steps,
+            "clocks": clocks.summary(),
+            "layer_tflops": FLOPS_PER_TOKEN * n * world / (ms_step * 1e-3) / 1e12,
+            "layer_frac_of_nominal_2250": FLOPS_PER_TOKEN * n * world / (ms_step * 1e-3) / 1e12 / 2250.0 / world,
+        }
+        if stages is not None:
+            gemm_ms = stages["grouped_gemm_ms"]
+            achieved = FLOPS_PER_TOKEN_GEMM * n / (gemm_ms * 1e-3) / 1e12
+            peak = peaks["tflops_sustained"]
+            line["roofline"] = {
+                "bound": "tensor", "kernel": "grouped_gemm_kernel (pass 1 SwiGLU + pass 2, one C-ABI call)",
+                "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                "peak_source": f"{peaks['source']}: sustained cuBLAS bf16 (burst {peaks['tflops_burst']})",
+                "frac_of_burst": achieved / peaks["tflops_burst"], "frac_of_nominal_2250": achieved / 2250.0,
+                "traffic": None,
+            }
+            line["stages"] = stages
+            hbm = peaks["hbm_gbs"]
+            line["hbm_kernels"] = {
+                k: {"achieved_gbs": stages[k + "_bytes"] / (stages[k + "_ms"] * 1e-3) / 1e9,
+                    "frac": stages[k + "_bytes"] / (stages[k + "_ms"] * 1e-3) / 1e9 / hbm, "peak_gbs": hbm}
+                for k in ("gate", "permute", "combine")
+            }
+            if not args.no_cpu_baseline:
+                cpu_value, cpu_dt, cores = oracle_cpu_tokens_per_s(CPU_SAMPLE_TOKENS, 20, 2)
+                line["cpu_baseline"] = {
+                    "value": cpu_value, "unit": "tokens/s", "cores": cores, "kind": "port",
+                    "sample": f"20 calls on the first {CPU_SAMPLE_TOKENS} of the {n} bench tokens, CPU oracle "
+                              "(PyTorch bf16, all host threads)",
+                }
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def time_stages(module, x2, steps, moe_ops, ops):
+    """Average duration of every kernel of the layer, measured with CUDA events around stage-level C-ABI calls."""
+    layer = ops._layer_pack(module, x2)
+    n, d = x2.shape
+    e = layer.n_experts
+    names = ["gate", "plan", "permute", "grouped_gemm", "combine"]
+    acc = {k: 0.0 for k in names}
+    status = torch.zeros((2,), dtype=torch.int32, device=x2.device)
+
+    def ev():
+        return torch.cuda.Event(enable_timing=True)
+
+    for it in range(steps + 2):
+        marks = [ev() for _ in range(6)]
+        marks[0].record()
+        idx, w, counts, _, _ = moe_ops.gate_topk(x2, layer.gate)
+        marks[1].record()
+        block_offsets, _, expert_offsets = moe_ops.route_plan(counts, n, e)
+        marks[2].record()
+        x_perm, row_map, _ = moe_ops.permute(x2, idx, block_offsets, expert_offsets, e)
+        marks[3].record()
+        y_perm, y_sh, _, _ = moe_ops.grouped_swiglu(layer.experts, layer.shared, expert_offsets, x_perm, x2,
+                                                    status=status, check_status=False)
+        marks[4].record()
+        moe_ops.combine(y_perm, row_map, w, y_sh)
+        marks[5].record()
+        torch.cuda.synchronize()
+        if it >= 2:
+            for i, k in enumerate(names):
+                acc[k] += marks[i].elapsed_time(marks[i + 1])
+    out = {k + "_ms": v / steps for k, v in acc.items()}
+    out["gate_bytes"] = n * d * 2 + e * d * 2 + n * 2 * 8
+    out["permute_bytes"] = n * d * 2 + n * 2 * d * 2
+    out["combine_bytes"] = n * 2 * d * 2 + n * d * 2 + n * d * 2
+    return out
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU oracle timing (profiling runs)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_gpu_arm(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -24,6 +24,7 @@ EXPORTS = (
     "comfy_moe_error_string",
     "comfy_moe_plan_sizes",
     "comfy_moe_gate_topk",
+    "comfy_moe_route_count",
     "comfy_moe_route_plan",
     "comfy_moe_permute",
     "comfy_moe_grouped_swiglu",
@@ -126,6 +127,7 @@ def load(build_if_missing: bool = False) -> ctypes.CDLL:
         c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
         c_float, c_void_p,
     ]
+    lib.comfy_moe_route_count.argtypes = [c_void_p, c_int, c_int, c_void_p, c_void_p]
     lib.comfy_moe_route_plan.argtypes = [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]
     lib.comfy_moe_permute.argtypes = [
         c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,

@@ -19,8 +19,9 @@ combine_kernel(const __nv_bfloat16* __restrict__ y_perm, const int32_t* __restri
     const int r0 = __ldg(row_map + 2 * t), r1 = __ldg(row_map + 2 * t + 1);
     const float w0 = round_bf16(__ldg(topk_weight + 2 * t));
     const float w1 = round_bf16(__ldg(topk_weight + 2 * t + 1));
-    const uint4* a = reinterpret_cast<const uint4*>(y_perm + static_cast<size_t>(r0) * dim);
-    const uint4* b = reinterpret_cast<const uint4*>(y_perm + static_cast<size_t>(r1) * dim);
+    // a negative row means "this slot was routed nowhere": it contributes zero
+    const uint4* a = r0 >= 0 ? reinterpret_cast<const uint4*>(y_perm + static_cast<size_t>(r0) * dim) : nullptr;
+    const uint4* b = r1 >= 0 ? reinterpret_cast<const uint4*>(y_perm + static_cast<size_t>(r1) * dim) : nullptr;
     const uint4* s = y_shared ? reinterpret_cast<const uint4*>(y_shared + static_cast<size_t>(t) * dim) : nullptr;
     uint4* o = reinterpret_cast<uint4*>(out + static_cast<size_t>(t) * dim);
     constexpr int kBatch = 5;
@@ -30,8 +31,8 @@ combine_kernel(const __nv_bfloat16* __restrict__ y_perm, const int32_t* __restri
       for (int j = 0; j < kBatch; ++j) {
         const int c = c0 + 32 * j;
         if (c < chunks) {
-          va[j] = ld_nc_u4(a + c);
-          vb[j] = ld_nc_u4(b + c);
+          va[j] = a ? ld_nc_u4(a + c) : make_uint4(0, 0, 0, 0);
+          vb[j] = b ? ld_nc_u4(b + c) : make_uint4(0, 0, 0, 0);
           vs[j] = s ? ld_nc_u4(s + c) : make_uint4(0, 0, 0, 0);
         }
       }

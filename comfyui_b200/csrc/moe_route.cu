@@ -145,6 +145,27 @@ gate_topk_kernel(const __nv_bfloat16* __restrict__ x, const void* __restrict__ w
 }
 
 // ------------------------------------------------------------------------------------------------
+// Per-block expert counts for routing that did not come from the gate kernel (moe_infer is public
+// and takes the indices as an argument).  Out-of-range expert ids are counted nowhere.
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kTokensPerBlock * 2)
+route_count_kernel(const int32_t* __restrict__ topk_idx, int n_tokens, int n_experts,
+                   int32_t* __restrict__ block_counts) {
+  __shared__ int hist[kMaxExperts];
+  const int tid = threadIdx.x;
+  if (tid < kMaxExperts) hist[tid] = 0;
+  __syncthreads();
+  const int slot = blockIdx.x * kTokensPerBlock * 2 + tid;
+  const int e = slot < n_tokens * 2 ? topk_idx[slot] : -1;
+  for (int k = 0; k < n_experts; ++k) {
+    const unsigned m = __ballot_sync(0xffffffffu, e == k);
+    if ((tid & 31) == 0 && m) atomicAdd(&hist[k], __popc(m));
+  }
+  __syncthreads();
+  if (tid < n_experts) block_counts[blockIdx.x * n_experts + tid] = hist[tid];
+}
+
+// ------------------------------------------------------------------------------------------------
 // Routing plan: one thread block scans the per-block counts of every expert.
 // ------------------------------------------------------------------------------------------------
 constexpr int kPlanThreads = 1024;
@@ -212,8 +233,8 @@ template <bool kFp8>
 __global__ void __launch_bounds__(kGateThreads)
 permute_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ topk_idx,
                const int32_t* __restrict__ block_offsets, const int32_t* __restrict__ expert_offsets,
-               int n_tokens, int dim, int n_experts, const float* __restrict__ act_inv_scale,
-               void* __restrict__ x_perm, void* __restrict__ x_q, const float* __restrict__ x_q_inv_scale,
+               int n_tokens, int dim, int n_experts, const float* __restrict__ act_scale,
+               void* __restrict__ x_perm, void* __restrict__ x_q, const float* __restrict__ x_q_scale,
                int32_t* __restrict__ row_map) {
   constexpr int kSlots = kTokensPerBlock * 2;  // 64
   __shared__ int dest_s[kSlots];
@@ -226,6 +247,7 @@ permute_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ 
   if (tid < kSlots) {
     const int slot = block_tok0 * 2 + tid;
     if (slot < n_tokens * 2) my_e = topk_idx[slot];
+    if (my_e >= n_experts) my_e = -1;   // an id outside the layer routes nowhere
     for (int e = 0; e < n_experts; ++e) {
       const unsigned m = __ballot_sync(0xffffffffu, my_e == e);
       if (my_e == e) my_rank = __popc(m & ((1u << lane) - 1u));
@@ -239,8 +261,8 @@ permute_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ 
       int before = my_rank;
       for (int w = 0; w < warp; ++w) before += warp_cnt[w][my_e];
       d = expert_offsets[my_e] + block_offsets[blockIdx.x * n_experts + my_e] + before;
-      row_map[block_tok0 * 2 + tid] = d;
     }
+    if (block_tok0 * 2 + tid < n_tokens * 2) row_map[block_tok0 * 2 + tid] = d;
     dest_s[tid] = d;
   }
   __syncthreads();
@@ -248,8 +270,8 @@ permute_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ 
   float inv_p = 1.f, inv_q = 1.f;
   bool scaled_p = false, scaled_q = false;
   if constexpr (kFp8) {
-    if (act_inv_scale) { inv_p = round_bf16(1.0f / __ldg(act_inv_scale)); scaled_p = true; }
-    if (x_q_inv_scale) { inv_q = round_bf16(1.0f / __ldg(x_q_inv_scale)); scaled_q = true; }
+    if (act_scale) { inv_p = round_bf16(1.0f / __ldg(act_scale)); scaled_p = true; }
+    if (x_q_scale) { inv_q = round_bf16(1.0f / __ldg(x_q_scale)); scaled_q = true; }
   }
 
   for (int i = 0; i < kTokensPerWarp; ++i) {
@@ -271,8 +293,8 @@ permute_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ 
 #pragma unroll
         for (int j = 0; j < kBatch; ++j)
           if (c0 + 32 * j < chunks) {
-            o0[c0 + 32 * j] = v[j];
-            o1[c0 + 32 * j] = v[j];
+            if (d0 >= 0) o0[c0 + 32 * j] = v[j];
+            if (d1 >= 0) o1[c0 + 32 * j] = v[j];
           }
       }
     } else {
@@ -309,8 +331,8 @@ permute_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ 
           }
         }
         const uint4 vp = make_uint4(wp[0], wp[1], wp[2], wp[3]);
-        reinterpret_cast<uint4*>(p0)[c] = vp;
-        reinterpret_cast<uint4*>(p1)[c] = vp;
+        if (d0 >= 0) reinterpret_cast<uint4*>(p0)[c] = vp;
+        if (d1 >= 0) reinterpret_cast<uint4*>(p1)[c] = vp;
         if (q) reinterpret_cast<uint4*>(q)[c] = make_uint4(wq[0], wq[1], wq[2], wq[3]);
       }
     }
@@ -365,6 +387,17 @@ extern "C" int comfy_moe_gate_topk(const void* x, const void* w_gate, int w_dtyp
   }
 }
 
+extern "C" int comfy_moe_route_count(const int32_t* topk_idx, int n_tokens, int n_experts, int32_t* block_counts,
+                                     void* stream) {
+  if (n_tokens < 0 || n_experts < 1 || n_experts > kMaxExperts) return COMFY_MOE_EINVAL;
+  if (n_tokens == 0) return COMFY_MOE_OK;
+  if (!topk_idx || !block_counts) return COMFY_MOE_EINVAL;
+  const int n_blocks = (n_tokens + kTokensPerBlock - 1) / kTokensPerBlock;
+  route_count_kernel<<<n_blocks, kTokensPerBlock * 2, 0, static_cast<cudaStream_t>(stream)>>>(
+      topk_idx, n_tokens, n_experts, block_counts);
+  return check_launch();
+}
+
 extern "C" int comfy_moe_route_plan(const int32_t* block_counts, int n_tokens, int n_experts,
                                     int32_t* block_offsets, int32_t* expert_counts, int32_t* expert_offsets,
                                     void* stream) {
@@ -379,8 +412,8 @@ extern "C" int comfy_moe_route_plan(const int32_t* block_counts, int n_tokens, i
 
 extern "C" int comfy_moe_permute(const void* x, const int32_t* topk_idx, const int32_t* block_offsets,
                                  const int32_t* expert_offsets, int n_tokens, int dim, int n_experts,
-                                 int act_dtype, const float* act_inv_scale, void* x_perm, void* x_q,
-                                 const float* x_q_inv_scale, int32_t* row_map, void* stream) {
+                                 int act_dtype, const float* act_scale, void* x_perm, void* x_q,
+                                 const float* x_q_scale, int32_t* row_map, void* stream) {
   if (n_tokens < 0 || dim <= 0 || n_experts < 1 || n_experts > kMaxExperts) return COMFY_MOE_EINVAL;
   if (n_tokens == 0) return COMFY_MOE_OK;
   if (!x || !topk_idx || !block_offsets || !expert_offsets || !x_perm || !row_map) return COMFY_MOE_EINVAL;
@@ -396,7 +429,7 @@ extern "C" int comfy_moe_permute(const void* x, const int32_t* topk_idx, const i
     if ((dim & 15) != 0) return COMFY_MOE_EUNSUPPORTED;
     permute_kernel<true><<<n_blocks, kGateThreads, 0, s>>>(static_cast<const __nv_bfloat16*>(x), topk_idx,
                                                            block_offsets, expert_offsets, n_tokens, dim, n_experts,
-                                                           act_inv_scale, x_perm, x_q, x_q_inv_scale, row_map);
+                                                           act_scale, x_perm, x_q, x_q_scale, row_map);
   } else {
     return COMFY_MOE_EUNSUPPORTED;
   }

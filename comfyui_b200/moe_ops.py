@@ -214,6 +214,19 @@ def gate_topk(x: torch.Tensor, w_gate: torch.Tensor, *, neartie_eps: float = 1e-
     return topk_idx, topk_weight, block_counts, count, flags
 
 
+def route_count(topk_idx: torch.Tensor, n_experts: int) -> torch.Tensor:
+    """Per-block expert counts of caller-supplied int32 routing [N, 2] (what the gate kernel emits itself)."""
+    _need_cuda(topk_idx)
+    if topk_idx.dtype != torch.int32 or not topk_idx.is_contiguous():
+        raise ValueError("topk_idx must be a contiguous int32 tensor")
+    n = topk_idx.numel() // 2
+    _, n_blocks = plan_sizes(n, n_experts)
+    block_counts = torch.empty((max(n_blocks, 1), n_experts), dtype=torch.int32, device=topk_idx.device)
+    rc = N.load().comfy_moe_route_count(_ptr(topk_idx), n, n_experts, _ptr(block_counts), _stream())
+    N.check("comfy_moe_route_count", rc)
+    return block_counts
+
+
 def route_plan(block_counts: torch.Tensor, n_tokens: int, n_experts: int):
     """Per-expert scan of the block counts.  Returns (block_offsets, expert_counts, expert_offsets)."""
     _need_cuda(block_counts)

@@ -1,0 +1,434 @@
+"""Operator namespaces for the HiDream MoE feed-forward, interface-compatible with ``comfy/ops.py``.
+
+What is mirrored (same names, arguments and behaviour, Linear only — the MoE path builds nothing else):
+
+* ``CastWeightBiasOp`` attributes ``comfy_cast_weights`` / ``weight_function`` / ``bias_function``
+  (``comfy/ops.py:97-100``) and ``cast_bias_weight`` (``:61-95``);
+* ``disable_weight_init.Linear`` (``:103-115``), ``manual_cast.Linear`` (``:283-284``);
+* ``fp8_linear`` (``:314-358``), ``fp8_ops.Linear`` (``:360-377``), ``scaled_fp8_ops(...)`` (``:379-428``);
+* ``pick_operations`` (``:449-473``).
+
+What is new: the dispatch shim at the bottom.  ``hidream_moe_forward`` / ``hidream_moe_infer`` /
+``hidream_gate`` / ``swiglu_ffn_forward`` check, on every call, whether the module's current weights
+can be handed to the sm_100a kernels (bf16, or e4m3 with per-tensor scales; resident on the input's
+device; no LoRA closures) and if so run the whole layer there.  They return ``None`` when the call is
+not eligible, and the module then runs its stock PyTorch composition, exactly as the reference would.
+"""
+from __future__ import annotations
+
+import contextlib
+import logging
+from typing import Optional
+
+import torch
+import torch.nn.functional as F
+
+from . import model_management
+
+FP8 = torch.float8_e4m3fn
+
+
+# =========================================================================== reference-compatible part
+def cast_to_input(weight, input, non_blocking=False, copy=True):
+    return model_management.cast_to(weight, input.dtype, input.device, non_blocking=non_blocking, copy=copy)
+
+
+def cast_bias_weight(s, input=None, dtype=None, device=None, bias_dtype=None):
+    """Weight (and bias) of module ``s`` cast for use with ``input``, then passed through the module's
+    ``weight_function`` / ``bias_function`` lists (LoRA closures attached by a model patcher)."""
+    if input is not None:
+        dtype = input.dtype if dtype is None else dtype
+        bias_dtype = dtype if bias_dtype is None else bias_dtype
+        device = input.device if device is None else device
+
+    side = model_management.get_offload_stream(device)
+    in_side = side if side is not None else contextlib.nullcontext()
+    non_blocking = model_management.device_supports_non_blocking(device)
+
+    def prepared(tensor, fns, to_dtype):
+        if tensor is None:
+            return None
+        out = model_management.cast_to(tensor, to_dtype, device, non_blocking=non_blocking, copy=len(fns) > 0,
+                                       stream=side)
+        if fns:
+            with in_side:
+                for fn in fns:
+                    out = fn(out)
+        return out
+
+    bias = prepared(s.bias, s.bias_function, bias_dtype)
+    weight = prepared(s.weight, s.weight_function, dtype)
+    model_management.sync_stream(device, side)
+    return weight, bias
+
+
+class CastWeightBiasOp:
+    comfy_cast_weights = False
+    weight_function = []
+    bias_function = []
+
+
+class disable_weight_init:
+    """Layers that skip parameter initialisation (weights always come from a checkpoint)."""
+
+    class Linear(torch.nn.Linear, CastWeightBiasOp):
+        def reset_parameters(self):
+            return None
+
+        def forward_comfy_cast_weights(self, input):
+            weight, bias = cast_bias_weight(self, input)
+            return F.linear(input, weight, bias)
+
+        def forward(self, *args, **kwargs):
+            if self.comfy_cast_weights or self.weight_function or self.bias_function:
+                return self.forward_comfy_cast_weights(*args, **kwargs)
+            return super().forward(*args, **kwargs)
+
+
+class manual_cast(disable_weight_init):
+    """Weights stored in one dtype and cast to the activation dtype on every call."""
+
+    class Linear(disable_weight_init.Linear):
+        comfy_cast_weights = True
+
+
+def fp8_linear(self, input):
+    """fp8 x fp8 matmul of an e4m3 Linear: quantise the activation, ``torch._scaled_mm`` with per-tensor
+    scales, output in the activation dtype.  Returns None when the weight is not e4m3 (caller falls back)."""
+    w_dtype = self.weight.dtype
+    if w_dtype != FP8:
+        return None
+    was_2d = input.dim() == 2
+    if was_2d:
+        input = input.unsqueeze(1)
+    if input.dim() != 3:
+        return None
+    shape, act_dtype = input.shape, input.dtype
+    w, bias = cast_bias_weight(self, input, dtype=w_dtype, bias_dtype=act_dtype)
+
+    def on_device(scale):
+        if scale is None:
+            return torch.ones((), device=input.device, dtype=torch.float32)
+        return scale.to(input.device)
+
+    scale_weight = on_device(self.scale_weight)
+    if self.scale_input is None:
+        scale_input = on_device(None)
+        input = torch.clamp(input, min=-448, max=448, out=input)   # in place, like the reference
+        xq = input.reshape(-1, shape[2]).to(w_dtype).contiguous()
+    else:
+        scale_input = on_device(self.scale_input)
+        xq = (input * (1.0 / scale_input).to(act_dtype)).reshape(-1, shape[2]).to(w_dtype).contiguous()
+
+    kwargs = dict(out_dtype=act_dtype, scale_a=scale_input, scale_b=scale_weight)
+    if bias is not None:
+        kwargs["bias"] = bias
+    o = torch._scaled_mm(xq, w.t(), **kwargs)
+    if isinstance(o, tuple):
+        o = o[0]
+    if was_2d:
+        return o.reshape(shape[0], -1)
+    return o.reshape((-1, shape[1], self.weight.shape[0]))
+
+
+class fp8_ops(manual_cast):
+    """Unscaled fp8 weights multiplied in fp8 when possible."""
+
+    class Linear(manual_cast.Linear):
+        fp8_matrix_mult = True
+
+        def reset_parameters(self):
+            self.scale_weight = None
+            self.scale_input = None
+            return None
+
+        def forward_comfy_cast_weights(self, input):
+            if not self.training:
+                try:
+                    out = fp8_linear(self, input)
+                    if out is not None:
+                        return out
+                except Exception as e:  # same policy as the reference: log and use the cast path
+                    logging.info("Exception during fp8 op: {}".format(e))
+            weight, bias = cast_bias_weight(self, input)
+            return F.linear(input, weight, bias)
+
+
+def scaled_fp8_ops(fp8_matrix_mult=False, scale_input=False, override_dtype=None):
+    """Namespace factory for per-tensor scaled fp8 weights: ``weight`` e4m3 plus a ``scale_weight`` fp32
+    scalar (and ``scale_input`` when requested) per Linear."""
+    logging.info("Using scaled fp8: fp8 matrix mult: {}, scale input: {}".format(fp8_matrix_mult, scale_input))
+    use_fp8_mm, with_scale_input = fp8_matrix_mult, scale_input
+
+    class scaled_fp8_op(manual_cast):
+        class Linear(manual_cast.Linear):
+            fp8_matrix_mult = use_fp8_mm
+
+            def __init__(self, *args, **kwargs):
+                if override_dtype is not None:
+                    kwargs["dtype"] = override_dtype
+                super().__init__(*args, **kwargs)
+
+            def reset_parameters(self):
+                def unit():
+                    return torch.nn.parameter.Parameter(
+                        data=torch.ones((), device=self.weight.device, dtype=torch.float32), requires_grad=False)
+
+                if not hasattr(self, "scale_weight"):
+                    self.scale_weight = unit()
+                if not with_scale_input:
+                    self.scale_input = None
+                if not hasattr(self, "scale_input"):
+                    self.scale_input = unit()
+                return None
+
+            def forward_comfy_cast_weights(self, input):
+                if use_fp8_mm:
+                    out = fp8_linear(self, input)
+                    if out is not None:
+                        return out
+                weight, bias = cast_bias_weight(self, input)
+                scale = self.scale_weight.to(device=weight.device, dtype=weight.dtype)
+                if weight.numel() < input.numel():
+                    return F.linear(input, weight * scale, bias)
+                return F.linear(input * scale, weight, bias)
+
+            def convert_weight(self, weight, inplace=False, **kwargs):
+                scale = self.scale_weight.to(device=weight.device, dtype=weight.dtype)
+                if inplace:
+                    weight *= scale
+                    return weight
+                return weight * scale
+
+            def set_weight(self, weight, inplace_update=False, seed=None, return_weight=False, **kwargs):
+                scaled = weight / self.scale_weight.to(device=weight.device, dtype=weight.dtype)
+                q = stochastic_rounding(scaled, self.weight.dtype, seed=seed)
+                if return_weight:
+                    return q
+                if inplace_update:
+                    self.weight.data.copy_(q)
+                else:
+                    self.weight = torch.nn.Parameter(q, requires_grad=False)
+
+    return scaled_fp8_op
+
+
+def stochastic_rounding(value: torch.Tensor, dtype: torch.dtype, seed=None) -> torch.Tensor:
+    """Round ``value`` to ``dtype``; for e4m3 each element goes to one of its two neighbouring representable
+    values with probability proportional to proximity (what ``comfy/float.py:50-67`` provides for LoRA-baked
+    fp8 weights).  Other dtypes: a plain cast."""
+    if dtype != FP8:
+        return value.to(dtype)
+    g = torch.Generator(device=value.device)
+    g.manual_seed(0 if seed is None else int(seed))
+    v = value.float().clamp(-448.0, 448.0)
+    mag = v.abs()
+    # spacing of e4m3 at |v|: 2^(floor(log2|v|) - 3), never below the subnormal step 2^-9
+    exp = torch.floor(torch.log2(mag.clamp_min(2.0 ** -9))).clamp(min=-6.0)
+    step = torch.exp2(exp - 3.0)
+    lo = torch.floor(mag / step) * step
+    frac = (mag - lo) / step
+    up = torch.rand(v.shape, generator=g, device=v.device, dtype=torch.float32) < frac
+    out = torch.where(up, lo + step, lo).clamp(max=448.0)
+    return (torch.sign(v) * out).to(dtype)
+
+
+def pick_operations(weight_dtype, compute_dtype, load_device=None, disable_fast_fp8=False, fp8_optimizations=False,
+                    scaled_fp8=None):
+    """Choose the operator namespace for a model, by the same rules as the reference."""
+    fp8_compute = model_management.supports_fp8_compute(load_device)
+    if scaled_fp8 is not None:
+        return scaled_fp8_ops(fp8_matrix_mult=fp8_compute and fp8_optimizations, scale_input=fp8_optimizations,
+                              override_dtype=scaled_fp8)
+    if fp8_compute and fp8_optimizations and not disable_fast_fp8:
+        return fp8_ops
+    if compute_dtype is None or weight_dtype == compute_dtype:
+        return disable_weight_init
+    return manual_cast
+
+
+# =========================================================================== dispatch shim (new)
+# Switches an embedding application can flip.
+ENABLE_SM100_KERNELS = True
+# Read the device status word (one stream synchronisation) after every fused call; for debugging.
+CHECK_STATUS_EVERY_CALL = False
+
+_workspaces = {}
+_WORKSPACE_SLOTS = 4
+
+
+def _tensor_key(t: Optional[torch.Tensor]):
+    if t is None:
+        return None
+    return (t.data_ptr(), t._version, t.dtype, t.device, tuple(t.shape), t.stride(0) if t.dim() else 0)
+
+
+def _linear_state(lin, device):
+    """(weight, scale_weight, scale_input) if this Linear can feed the kernels as it is now, else None."""
+    if lin.weight_function or lin.bias_function or lin.bias is not None:
+        return None
+    w = lin.weight
+    if w.device != device or w.dim() != 2 or w.stride(1) != 1:
+        return None
+    if w.dtype == torch.bfloat16:
+        return (w, None, None)
+    if w.dtype == FP8 and getattr(lin, "fp8_matrix_mult", False) and not lin.training:
+        sw = getattr(lin, "scale_weight", None)
+        si = getattr(lin, "scale_input", None)
+        for s in (sw, si):
+            if s is not None and (s.device != device or s.dtype != torch.float32 or s.numel() != 1):
+                return None
+        return (w, sw, si)
+    return None
+
+
+def _ffn_pack(ffn, device, moe_ops):
+    """FfnPack for a FeedForwardSwiGLU, or None.  Cached on the module, keyed on the identity and version
+    of every tensor, so a patched, re-loaded or moved weight is picked up on the next call."""
+    states = [_linear_state(l, device) for l in (ffn.w1, ffn.w3, ffn.w2)]
+    if any(s is None for s in states):
+        return None
+    key = tuple(_tensor_key(t) for s in states for t in s)
+    cached = getattr(ffn, "_b200_pack", None)
+    if cached is not None and cached[0] == key:
+        return cached[1]
+    (w1, s1, i1), (w3, s3, i3), (w2, s2, i2) = states
+    if w1.dtype != w3.dtype or w1.dtype != w2.dtype or w1.shape != w3.shape or w1.stride(0) != w3.stride(0):
+        return None
+    if (i1 is None) != (i3 is None):
+        return None
+    if i1 is not None and float(i1) != float(i3):   # w1 and w3 must quantise their common input alike
+        return None
+    try:
+        pack = moe_ops.FfnPack(w1.detach(), w3.detach(), w2.detach(), scale_w1=s1, scale_w3=s3, scale_w2=s2,
+                               scale_in13=i1, scale_in2=i2)
+    except ValueError:
+        return None
+    object.__setattr__(ffn, "_b200_pack", (key, pack))
+    return pack
+
+
+def _input_ok(x: torch.Tensor, dim: int) -> bool:
+    return (ENABLE_SM100_KERNELS and x.is_cuda and x.dtype == torch.bfloat16 and x.is_contiguous()
+            and x.shape[-1] == dim and dim % 256 == 0 and x.numel() > 0
+            and model_management.is_sm100(x.device))
+
+
+def _layer_pack(moe, x):
+    """LayerPack for a MOEFeedForwardSwiGLU under the current weights, or None when not eligible."""
+    from . import moe_ops
+
+    gate_w = moe.gate.weight
+    dim = gate_w.shape[1]
+    if not _input_ok(x, dim):
+        return None
+    if moe.num_activated_experts != 2 or not (2 <= len(moe.experts) <= 8):
+        return None
+    if gate_w.device != x.device or gate_w.dtype not in (torch.bfloat16, torch.float32) or not gate_w.is_contiguous():
+        return None
+    packs = [_ffn_pack(e, x.device, moe_ops) for e in moe.experts]
+    shared = _ffn_pack(moe.shared_experts, x.device, moe_ops)
+    if shared is None or any(p is None for p in packs):
+        return None
+    if any(p.w1.dtype != packs[0].w1.dtype or p.hidden != packs[0].hidden for p in packs) or \
+            shared.w1.dtype != packs[0].w1.dtype:
+        return None
+    if packs[0].hidden % 128 or shared.hidden % 128:
+        return None
+    key = (_tensor_key(gate_w),) + tuple(id(p) for p in packs) + (id(shared),)
+    cached = getattr(moe, "_b200_layer", None)
+    if cached is not None and cached[0] == key:
+        return cached[1]
+    layer = None
+    ins = {None if p.scale_in13 is None else float(p.scale_in13) for p in packs}   # host reads: cache misses only
+    if len(ins) == 1:    # the permuted activations are quantised once for all routed experts
+        layer = moe_ops.LayerPack(gate_w.detach(), packs, shared, top_k=2)
+    object.__setattr__(moe, "_b200_layer", (key, layer))
+    return layer
+
+
+def _workspace(layer, n_tokens: int):
+    from . import moe_ops
+
+    key = (n_tokens, layer.dim, layer.n_experts, layer.experts[0].hidden, layer.shared.hidden, layer.fp8,
+           layer.gate.device, torch.cuda.current_stream().cuda_stream)
+    ws = _workspaces.get(key)
+    if ws is None:
+        while len(_workspaces) >= _WORKSPACE_SLOTS:
+            _workspaces.pop(next(iter(_workspaces)))
+        ws = moe_ops.Workspace.for_layer(layer, n_tokens)
+        _workspaces[key] = ws
+    return ws
+
+
+def release_workspaces() -> None:
+    """Drop the cached device workspaces (they are shared by every MoE layer of a model)."""
+    _workspaces.clear()
+
+
+def hidream_moe_forward(moe, x: torch.Tensor) -> Optional[torch.Tensor]:
+    """MOEFeedForwardSwiGLU.forward on the sm_100a kernels, or None when this call is not eligible."""
+    layer = _layer_pack(moe, x)
+    if layer is None:
+        return None
+    from . import moe_ops
+
+    x2 = x.view(-1, x.shape[-1])
+    ws = _workspace(layer, x2.shape[0])
+    out = moe_ops.moe_forward(layer, x2, ws)
+    if CHECK_STATUS_EVERY_CALL:
+        moe_ops.read_status(ws.status)
+    return out.view(x.shape)
+
+
+def hidream_gate(gate, x: torch.Tensor):
+    """MoEGate.forward on the fused gate kernel: (idx int64 [N,2], weight [N,2] in x.dtype) or None."""
+    w = gate.weight
+    if not _input_ok(x, w.shape[1]) or gate.top_k != 2 or w.shape[0] not in (2, 4, 8):
+        return None
+    if w.device != x.device or w.dtype not in (torch.bfloat16, torch.float32):
+        return None
+    from . import moe_ops
+
+    idx, weight, _, _, _ = moe_ops.gate_topk(x.view(-1, x.shape[-1]), w.detach())
+    return idx.to(torch.int64), weight.to(x.dtype)
+
+
+def hidream_moe_infer(moe, x: torch.Tensor, flat_expert_indices: torch.Tensor,
+                      flat_expert_weights: torch.Tensor) -> Optional[torch.Tensor]:
+    """moe_infer (routed experts only, caller-supplied routing) on the kernels, or None."""
+    if x.dim() != 2:
+        return None
+    layer = _layer_pack(moe, x)
+    if layer is None or not flat_expert_indices.is_cuda:
+        return None
+    from . import moe_ops
+
+    n = x.shape[0]
+    e = layer.n_experts
+    idx = flat_expert_indices.reshape(n, 2).to(torch.int32).contiguous()
+    w = flat_expert_weights.reshape(n, 2).to(torch.float32).contiguous()
+    counts = moe_ops.route_count(idx, e)
+    block_offsets, _, expert_offsets = moe_ops.route_plan(counts, n, e)
+    in13 = layer.experts[0].scale_in13
+    x_perm, row_map, _ = moe_ops.permute(x, idx, block_offsets, expert_offsets, e, fp8=layer.fp8, act_scale=in13)
+    y_perm, _, _, _ = moe_ops.grouped_swiglu(layer.experts, None, expert_offsets, x_perm, None,
+                                              check_status=CHECK_STATUS_EVERY_CALL)
+    return moe_ops.combine(y_perm, row_map, w, None)
+
+
+def swiglu_ffn_forward(ffn, x: torch.Tensor) -> Optional[torch.Tensor]:
+    """A dense FeedForwardSwiGLU (the shared expert alone, or a block's text FFN) as a one-group call."""
+    from . import moe_ops
+
+    dim = ffn.w1.weight.shape[1]
+    if not _input_ok(x, dim):
+        return None
+    pack = _ffn_pack(ffn, x.device, moe_ops)
+    if pack is None or pack.hidden % 128:
+        return None
+    x2 = x.view(-1, dim)
+    if pack.w1.dtype == FP8:
+        return None   # the dense fp8 path needs the quantised copy the permutation kernel makes
+    _, y, _, _ = moe_ops.grouped_swiglu([], pack, None, None, x2, check_status=CHECK_STATUS_EVERY_CALL)
+    return y.view(x.shape)

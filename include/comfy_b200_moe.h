@@ -71,6 +71,12 @@ int comfy_moe_gate_topk(const void* x, const void* w_gate, int w_dtype, int n_to
                         int top_k, int32_t* topk_idx, float* topk_weight, int32_t* block_counts,
                         int32_t* neartie_count, uint8_t* neartie_flags, float neartie_eps, void* stream);
 
+/* ---- per-block expert counts for caller-supplied routing (moe_infer takes the indices as an argument,
+ * model.py:328): same output as the gate's block_counts.  Ids outside [0, n_experts) are counted nowhere; the
+ * permutation maps such slots to row -1 and the combine treats them as zero.
+ */
+int comfy_moe_route_count(const int32_t* topk_idx, int n_tokens, int n_experts, int32_t* block_counts, void* stream);
+
 /* ---- routing plan: replaces argsort + bincount().cpu().cumsum (model.py:330-332) without a host sync ----
  *   block_counts   int32 [n_blocks, n_experts]  from the gate
  *   block_offsets  int32 [n_blocks, n_experts]  out: rows of expert e that precede block b, within e's block
@@ -85,15 +91,15 @@ int comfy_moe_route_plan(const int32_t* block_counts, int n_tokens, int n_expert
  * Copies row t of x to row row_map[t*2+k] of x_perm for k = 0,1; order inside an expert block is by slot index
  * (stable), so the layout is reproducible run to run.
  *   x_perm      [rows_cap, dim] in act_dtype: COMFY_MOE_BF16 copies; COMFY_MOE_FP8_E4M3 quantises as
- *               comfy/ops.py:338-343 does (clamp to +-448 then round-to-nearest-even when act_inv_scale is NULL,
- *               else multiply by bf16(*act_inv_scale) in bf16 first)
+ *               comfy/ops.py:338-343 does (clamp to +-448 then round-to-nearest-even when act_scale is NULL,
+ *               else multiply by bf16(1 / *act_scale) in bf16 first; act_scale is the Linear's scale_input)
  *   x_q         only for fp8: [n_tokens, dim] e4m3, the un-permuted quantised copy the shared expert reads
- *               (x_q_inv_scale: its own optional scale); may be NULL
+ *               (x_q_scale: its own optional scale); may be NULL
  *   row_map     int32 [n_tokens, 2] out
  */
 int comfy_moe_permute(const void* x, const int32_t* topk_idx, const int32_t* block_offsets,
                       const int32_t* expert_offsets, int n_tokens, int dim, int n_experts, int act_dtype,
-                      const float* act_inv_scale, void* x_perm, void* x_q, const float* x_q_inv_scale,
+                      const float* act_scale, void* x_perm, void* x_q, const float* x_q_scale,
                       int32_t* row_map, void* stream);
 
 /* One SwiGLU feed-forward's weights (FeedForwardSwiGLU, model.py:233-238). */
@@ -132,7 +138,7 @@ int comfy_moe_grouped_swiglu(int w_dtype, int n_experts, const ComfyMoeFfnWeight
 
 /* ---- weighted combine: replaces mul_ + scatter_reduce_ + shared add (model.py:341-345, 324) ---------------
  * out[t] = bf16( bf16( bf16(w0*y[r0]) + bf16(w1*y[r1]) ) + y_shared[t] ), weights rounded to bf16 first.
- * y_shared may be NULL (routed part only).  n_partials > 1 sums that many row maps (hidden-split experts).
+ * y_shared may be NULL (routed part only, what moe_infer returns).
  */
 int comfy_moe_combine(const void* y_perm, const int32_t* row_map, const float* topk_weight, const void* y_shared,
                       int n_tokens, int dim, void* out, void* stream);

@@ -1,0 +1,119 @@
+"""Generates tests/golden/hidream_moe_small.npz by running the UNMODIFIED reference.
+
+Usage (in a container that has the reference tree; it is not needed at test time):
+
+    python tests/golden/make_golden.py /path/to/ComfyUI
+
+The script imports the reference's ``comfy.ldm.hidream.model.MOEFeedForwardSwiGLU`` and ``comfy.ops`` on
+the CPU, loads seeded synthetic weights through ``load_state_dict(strict=True)`` (which also pins the
+state-dict key set), runs ``MoEGate.forward``, ``MOEFeedForwardSwiGLU.forward`` and ``moe_infer`` and stores
+the results.  bf16 tensors are stored up-cast to fp32 (exact).
+"""
+from __future__ import annotations
+
+import os
+import sys
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(os.path.dirname(HERE))
+sys.path.insert(0, ROOT)
+
+from oracle import hidream_moe_oracle as O  # noqa: E402  (seeded weight recipe only)
+
+DIM, HIDDEN_DIM, E, K = 256, 1024, 4, 2
+BATCH, SEQ = 2, 64
+W_SEED, X_SEED = 0, 1
+
+
+def main(ref_root: str) -> None:
+    sys.path.insert(0, ref_root)
+    from comfy.cli_args import args
+    args.cpu = True
+    import comfy.model_management  # noqa: F401
+    import comfy.ops
+    from comfy.ldm.hidream.model import MOEFeedForwardSwiGLU
+
+    torch.manual_seed(0)
+    out = {}
+    meta = dict(dim=DIM, hidden_dim=HIDDEN_DIM, n_experts=E, top_k=K, batch=BATCH, seq=SEQ, w_seed=W_SEED,
+                x_seed=X_SEED, torch_version=torch.__version__)
+
+    def build(ops, dtype, layer):
+        m = MOEFeedForwardSwiGLU(DIM, HIDDEN_DIM, E, K, dtype=dtype, device="cpu", operations=ops)
+        missing = m.load_state_dict(layer, strict=True)
+        assert not missing.missing_keys and not missing.unexpected_keys
+        return m.eval()
+
+    def f32(t):
+        return t.detach().float().numpy()
+
+    def run_case(name, m, x, gate_in_fp32):
+        n = BATCH * SEQ
+        with torch.no_grad():
+            if gate_in_fp32:
+                idx, w, _ = m.gate(x.float())
+                w = w.to(x.dtype)
+            else:
+                idx, w, _ = m.gate(x)
+            x2 = x.view(n, DIM)
+            routed = m.moe_infer(x2, idx.view(-1), w.view(-1, 1))
+            shared = m.shared_experts(x2)
+            full = routed + shared
+            out[f"{name}/idx"] = idx.numpy().astype(np.int64)
+            out[f"{name}/w"] = f32(w)
+            out[f"{name}/routed"] = f32(routed)
+            out[f"{name}/shared"] = f32(shared)
+            out[f"{name}/out"] = f32(full)
+            if not gate_in_fp32:
+                fwd = m.forward(x.clone())
+                out[f"{name}/forward"] = f32(fwd.view(n, DIM))
+                # the survey's observation: both branches agree bit for bit when fed the same routing
+                meta[f"{name}_forward_equals_infer"] = bool(torch.equal(fwd.view(n, DIM), full))
+
+    x32 = O.make_input(BATCH * SEQ, DIM, X_SEED).view(BATCH, SEQ, DIM)
+    layer32 = O.make_layer(DIM, HIDDEN_DIM, E, W_SEED)
+    out["x_checksum"] = np.array([float(x32.double().sum()), float(x32.double().abs().sum())])
+    out["w_checksum"] = np.array([float(sum(v.double().sum() for v in layer32.values())),
+                                  float(sum(v.double().abs().sum() for v in layer32.values()))])
+
+    # fp32, as shipped (configuration 1 of the benchmark spec, reduced size)
+    m = build(comfy.ops.disable_weight_init, torch.float32, layer32)
+    run_case("fp32", m, x32, gate_in_fp32=False)
+
+    # bf16 as shipped (gate in bf16) and with the fp32 gate of the parity contract
+    xb = x32.bfloat16()
+    layer16 = {k: v.bfloat16() for k, v in layer32.items()}
+    m = build(comfy.ops.disable_weight_init, torch.bfloat16, layer16)
+    run_case("bf16_shipped", m, xb, gate_in_fp32=False)
+    run_case("bf16", m, xb, gate_in_fp32=True)
+
+    # scaled fp8 weights, three flavours of comfy.ops.scaled_fp8_ops
+    layer8 = O.quantize_layer_fp8(layer16)
+    ops = comfy.ops.scaled_fp8_ops(fp8_matrix_mult=False, scale_input=False, override_dtype=torch.float8_e4m3fn)
+    m = build(ops, torch.bfloat16, layer8)
+    run_case("fp8_dequant", m, xb, gate_in_fp32=True)
+
+    ops = comfy.ops.scaled_fp8_ops(fp8_matrix_mult=True, scale_input=False, override_dtype=torch.float8_e4m3fn)
+    m = build(ops, torch.bfloat16, layer8)
+    run_case("fp8_matmul", m, xb, gate_in_fp32=True)
+
+    layer8s = O.quantize_layer_fp8(layer16, scale_input=0.75)
+    ops = comfy.ops.scaled_fp8_ops(fp8_matrix_mult=True, scale_input=True, override_dtype=torch.float8_e4m3fn)
+    m = build(ops, torch.bfloat16, layer8s)
+    run_case("fp8_matmul_scale_input", m, xb, gate_in_fp32=True)
+
+    out["state_dict_keys"] = np.array(sorted(layer8s.keys()))
+    out["meta_keys"] = np.array(sorted(meta.keys()))
+    out["meta_vals"] = np.array([str(meta[k]) for k in sorted(meta.keys())])
+    path = os.path.join(HERE, "hidream_moe_small.npz")
+    np.savez_compressed(path, **out)
+    print("wrote", path, os.path.getsize(path), "bytes")
+    for k in sorted(meta):
+        print(" ", k, meta[k])
+
+
+if __name__ == "__main__":
+    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")

@@ -1,0 +1,113 @@
+"""The drop-in modules on a B200: the call a HiDream block makes, routed to the kernels by the shim."""
+import pytest
+import torch
+
+from oracle import hidream_moe_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+def _module(dev, dim, hidden_dim, operations, layer):
+    from comfyui_b200.ldm.hidream.model import MOEFeedForwardSwiGLU
+
+    mod = MOEFeedForwardSwiGLU(dim, hidden_dim, 4, 2, dtype=torch.bfloat16, device=dev, operations=operations).eval()
+    mod.load_state_dict({k: v.to(dev) for k, v in layer.items()}, strict=True)
+    return mod
+
+
+def test_module_forward_uses_kernels_and_matches_oracle(cuda_device):
+    from comfyui_b200 import _native, ops
+
+    dev = cuda_device
+    dim, hidden_dim, b, s = 512, 2048, 2, 224 + 3
+    layer = {k: v.bfloat16() for k, v in O.make_layer(dim, hidden_dim, 4, seed=0).items()}
+    x = O.make_input(b * s, dim, seed=1).bfloat16()
+    mod = _module(dev, dim, hidden_dim, ops.disable_weight_init, layer)
+    xd = x.to(dev).view(b, s, dim)
+    assert _native._lib is not None or _native.load() is not None
+    with torch.inference_mode():
+        assert ops._layer_pack(mod, xd) is not None
+        out = mod(xd)
+        idx, w, aux = mod.gate(xd)
+    assert out.shape == xd.shape and out.dtype == torch.bfloat16 and aux is None
+    assert idx.dtype == torch.int64 and w.dtype == torch.bfloat16 and idx.shape == (b * s, 2)
+    ref, ridx, rw = O.moe_layer(x, layer, gate_in_fp32=True)
+    assert torch.equal(idx.cpu().sort(dim=1).values, ridx.sort(dim=1).values)
+    torch.testing.assert_close(out.view(-1, dim).cpu().float(), ref.float(), rtol=2e-2, atol=2e-2)
+
+    # moe_infer with caller-supplied routing (routed part only), and the dense shared expert alone
+    with torch.inference_mode():
+        routed = mod.moe_infer(xd.view(-1, dim), ridx.to(dev).view(-1), rw.to(dev).view(-1, 1))
+        shared = mod.shared_experts(xd)
+    ref_routed = O.moe_infer(x, ridx.reshape(-1), rw.reshape(-1, 1), layer)
+    torch.testing.assert_close(routed.cpu().float(), ref_routed.float(), rtol=2e-2, atol=2e-2)
+    ref_shared = O.swiglu_ffn(x, layer, "shared_experts")
+    torch.testing.assert_close(shared.view(-1, dim).cpu().float(), ref_shared.float(), rtol=2e-2, atol=2e-2)
+
+
+def test_weight_replacement_is_picked_up(cuda_device):
+    """A model patcher may replace a Parameter object or update it in place; the cached pack must follow."""
+    from comfyui_b200 import ops
+
+    dev = cuda_device
+    dim, hidden_dim, n = 256, 1024, 200
+    layer = {k: v.bfloat16() for k, v in O.make_layer(dim, hidden_dim, 4, seed=0).items()}
+    x = O.make_input(n, dim, seed=1).bfloat16()
+    mod = _module(dev, dim, hidden_dim, ops.disable_weight_init, layer)
+    xd = x.to(dev).view(1, n, dim)
+    with torch.inference_mode():
+        first = mod(xd).clone()
+    # replace one Parameter object (set_attr_param style) and update another in place (copy_to_param style)
+    layer2 = dict(layer)
+    layer2["experts.1.w2.weight"] = layer["experts.1.w2.weight"] * 2
+    layer2["shared_experts.w1.weight"] = layer["shared_experts.w1.weight"] * 0.5
+    mod.experts[1].w2.weight = torch.nn.Parameter(layer2["experts.1.w2.weight"].to(dev), requires_grad=False)
+    with torch.no_grad():
+        mod.shared_experts.w1.weight.data.copy_(layer2["shared_experts.w1.weight"].to(dev))
+    with torch.inference_mode():
+        second = mod(xd)
+    assert not torch.equal(first, second)
+    ref, _, _ = O.moe_layer(x, layer2, gate_in_fp32=True)
+    torch.testing.assert_close(second.view(-1, dim).cpu().float(), ref.float(), rtol=2e-2, atol=2e-2)
+
+
+def test_ineligible_calls_run_the_stock_composition(cuda_device):
+    """LoRA closure on a Linear, or fp32 activations: the module still answers, through PyTorch, like the reference."""
+    from comfyui_b200 import ops
+
+    dev = cuda_device
+    dim, hidden_dim, n = 256, 1024, 64
+    layer = {k: v.bfloat16() for k, v in O.make_layer(dim, hidden_dim, 4, seed=0).items()}
+    x = O.make_input(n, dim, seed=1).bfloat16()
+    mod = _module(dev, dim, hidden_dim, ops.disable_weight_init, layer)
+    xd = x.to(dev).view(1, n, dim)
+    mod.experts[0].w1.weight_function = [lambda w: w * 1.0]
+    assert ops._layer_pack(mod, xd) is None
+    with torch.inference_mode():
+        out = mod(xd)
+    ref, _, _ = O.moe_layer(x, layer, gate_in_fp32=True)
+    assert out.shape == xd.shape
+    assert float((out.view(-1, dim).cpu().float() - ref.float()).abs().mean()) < 2e-2
+
+
+def test_scaled_fp8_module(cuda_device):
+    from comfyui_b200 import ops
+
+    dev = cuda_device
+    dim, hidden_dim, n = 512, 2048, 300
+    layer = O.quantize_layer_fp8({k: v.bfloat16() for k, v in O.make_layer(dim, hidden_dim, 4, seed=0).items()})
+    x = O.make_input(n, dim, seed=1).bfloat16()
+    operations = ops.scaled_fp8_ops(fp8_matrix_mult=True, scale_input=False, override_dtype=torch.float8_e4m3fn)
+    mod = _module(dev, dim, hidden_dim, operations, layer)
+    xd = x.to(dev).view(1, n, dim)
+    with torch.inference_mode():
+        assert ops._layer_pack(mod, xd) is not None and ops._layer_pack(mod, xd).fp8
+        out = mod(xd).view(-1, dim).cpu()
+        idx, w, _ = mod.gate(xd)
+    ref, _, _ = O.moe_layer(x, layer, mode=O.FP8_MATMUL, routing=(idx.cpu(), w.cpu()))
+    rel = float((out.float() - ref.float()).norm() / ref.float().norm())
+    assert rel < 1e-2, rel
+    # the dequantising flavour (fp8_matrix_mult=False) is not what the kernels compute: stock path
+    operations = ops.scaled_fp8_ops(fp8_matrix_mult=False, scale_input=False, override_dtype=torch.float8_e4m3fn)
+    mod2 = _module(dev, dim, hidden_dim, operations, layer)
+    assert ops._layer_pack(mod2, xd) is None

@@ -1,0 +1,153 @@
+"""Host-side mirror of the reference's module and comfy.ops interface, checked on the CPU against
+outputs of the unmodified reference (golden fixtures)."""
+import numpy as np
+import pytest
+import torch
+
+from comfyui_b200 import model_management, ops
+from comfyui_b200.ldm.hidream.model import FeedForwardSwiGLU, MOEFeedForwardSwiGLU, MoEGate
+from oracle import hidream_moe_oracle as O
+
+
+def _case(golden, dtype, operations, quant=None):
+    m = golden["meta"]
+    dim, hidden_dim, e = int(m["dim"]), int(m["hidden_dim"]), int(m["n_experts"])
+    b, s = int(m["batch"]), int(m["seq"])
+    layer = {k: v.to(dtype) for k, v in O.make_layer(dim, hidden_dim, e, int(m["w_seed"])).items()}
+    if quant is not None:
+        layer = O.quantize_layer_fp8(layer, **quant)
+    x = O.make_input(b * s, dim, int(m["x_seed"])).to(dtype).view(b, s, dim)
+    mod = MOEFeedForwardSwiGLU(dim, hidden_dim, e, 2, dtype=dtype, device="cpu", operations=operations).eval()
+    res = mod.load_state_dict(layer, strict=True)
+    assert not res.missing_keys and not res.unexpected_keys
+    return mod, x, layer
+
+
+def test_state_dict_keys_and_shapes():
+    mod = MOEFeedForwardSwiGLU(2560, 4 * 2560, 4, 2, dtype=torch.bfloat16, device="meta",
+                               operations=ops.disable_weight_init)
+    sd = mod.state_dict()
+    assert len(sd) == 16
+    assert sd["experts.3.w1.weight"].shape == (6912, 2560)
+    assert sd["experts.0.w2.weight"].shape == (2560, 6912)
+    assert sd["shared_experts.w3.weight"].shape == (3584, 2560)
+    assert sd["gate.weight"].shape == (4, 2560)
+    scaled = ops.scaled_fp8_ops(fp8_matrix_mult=True, scale_input=True, override_dtype=torch.float8_e4m3fn)
+    mod8 = MOEFeedForwardSwiGLU(256, 1024, 4, 2, dtype=torch.bfloat16, device="cpu", operations=scaled)
+    sd8 = mod8.state_dict()
+    assert len(sd8) == 16 + 15 * 2
+    assert sd8["experts.1.w2.weight"].dtype == torch.float8_e4m3fn
+    assert sd8["experts.1.w2.scale_weight"].shape == () and sd8["experts.1.w2.scale_input"].dtype == torch.float32
+    assert sd8["gate.weight"].dtype == torch.bfloat16   # the gate is a bare Parameter, not an operations.Linear
+
+
+@pytest.mark.parametrize("name,dtype", [("fp32", torch.float32), ("bf16_shipped", torch.bfloat16)])
+def test_forward_matches_reference(golden, name, dtype):
+    mod, x, _ = _case(golden, dtype, ops.disable_weight_init)
+    with torch.no_grad():
+        out = mod(x).view(-1, x.shape[-1])
+        idx, w, aux = mod.gate(x)
+    assert aux is None and idx.dtype == torch.int64 and w.dtype == dtype
+    ref = torch.from_numpy(golden[f"{name}/forward"])
+    if dtype == torch.float32:
+        torch.testing.assert_close(out, ref, rtol=1e-6, atol=1e-7)
+    else:
+        assert torch.equal(out.float(), ref)
+    g_idx = torch.from_numpy(golden[f"{name}/idx"])
+    assert torch.equal(idx.sort(dim=1).values, g_idx.sort(dim=1).values)
+
+
+@pytest.mark.parametrize("name,fp8_mm,quant", [
+    ("fp8_dequant", False, {}),
+    ("fp8_matmul", True, {}),
+    ("fp8_matmul_scale_input", True, {"scale_input": 0.75}),
+])
+def test_scaled_fp8_namespaces_match_reference(golden, name, fp8_mm, quant):
+    operations = ops.scaled_fp8_ops(fp8_matrix_mult=fp8_mm, scale_input="scale_input" in quant,
+                                    override_dtype=torch.float8_e4m3fn)
+    mod, x, _ = _case(golden, torch.bfloat16, operations, quant)
+    x2 = x.view(-1, x.shape[-1])
+    idx = torch.from_numpy(golden[f"{name}/idx"])
+    w = torch.from_numpy(golden[f"{name}/w"]).bfloat16()
+    with torch.no_grad():
+        out = mod.moe_infer(x2, idx.view(-1), w.view(-1, 1)) + mod.shared_experts(x2)
+    assert torch.equal(out.float(), torch.from_numpy(golden[f"{name}/out"]))
+
+
+def test_pick_operations_rules(monkeypatch):
+    bf16, fp32, e4m3 = torch.bfloat16, torch.float32, torch.float8_e4m3fn
+    monkeypatch.setattr(model_management, "FORCE_FP8_COMPUTE", False)
+    assert ops.pick_operations(bf16, bf16) is ops.disable_weight_init
+    assert ops.pick_operations(bf16, None) is ops.disable_weight_init
+    assert ops.pick_operations(fp32, bf16) is ops.manual_cast
+    scaled = ops.pick_operations(None, bf16, scaled_fp8=e4m3, fp8_optimizations=True)
+    lin = scaled.Linear(8, 8, bias=False)
+    assert lin.weight.dtype == e4m3 and lin.fp8_matrix_mult is False     # no fp8 compute on this CPU-only host
+    monkeypatch.setattr(model_management, "FORCE_FP8_COMPUTE", True)
+    scaled = ops.pick_operations(None, bf16, scaled_fp8=e4m3, fp8_optimizations=True)
+    lin = scaled.Linear(8, 8, bias=False)
+    assert lin.fp8_matrix_mult is True and lin.scale_input is not None
+    assert ops.pick_operations(e4m3, bf16, fp8_optimizations=True) is ops.fp8_ops
+    assert ops.pick_operations(e4m3, bf16, fp8_optimizations=True, disable_fast_fp8=True) is ops.manual_cast
+
+
+def test_cast_bias_weight_and_weight_function():
+    lin = ops.manual_cast.Linear(16, 8, bias=True, dtype=torch.float32)
+    with torch.no_grad():
+        lin.weight.normal_()
+        lin.bias.normal_()
+    x = torch.randn(4, 16).bfloat16()
+    w, b = ops.cast_bias_weight(lin, x)
+    assert w.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
+    torch.testing.assert_close(lin(x), torch.nn.functional.linear(x, w, b))
+    # a LoRA-style closure: applied on a copy, the stored weight stays untouched
+    before = lin.weight.clone()
+    lin.weight_function = [lambda t: t + 1]
+    w2, _ = ops.cast_bias_weight(lin, x)
+    torch.testing.assert_close(w2, w + 1)
+    assert torch.equal(lin.weight, before)
+    plain = ops.disable_weight_init.Linear(16, 8, bias=False, dtype=torch.float32)
+    plain.weight_function = [lambda t: t * 0]
+    with torch.no_grad():
+        plain.weight.normal_()
+    assert float(plain(torch.randn(2, 16)).abs().max()) == 0.0     # forward switches to the cast path
+
+
+def test_cast_to_semantics():
+    w = torch.randn(4, 4)
+    assert model_management.cast_to(w, torch.float32, w.device) is w
+    c = model_management.cast_to(w, torch.float32, w.device, copy=True)
+    assert c is not w and torch.equal(c, w)
+    assert model_management.cast_to(w, torch.bfloat16).dtype == torch.bfloat16
+
+
+def test_shim_declines_ineligible_calls(golden):
+    """CPU tensors, fp32 activations, LoRA closures: the shim returns None and the stock composition runs."""
+    mod, x, _ = _case(golden, torch.bfloat16, ops.disable_weight_init)
+    assert ops.hidream_moe_forward(mod, x) is None
+    assert ops.hidream_gate(mod.gate, x) is None
+    assert ops.swiglu_ffn_forward(mod.shared_experts, x) is None
+    assert ops.hidream_moe_infer(mod, x.view(-1, x.shape[-1]), torch.zeros(256, dtype=torch.int64),
+                                 torch.zeros(256, 1)) is None
+    assert ops._linear_state(mod.experts[0].w1, x.device) is not None
+    mod.experts[0].w1.weight_function = [lambda t: t]
+    assert ops._linear_state(mod.experts[0].w1, x.device) is None
+
+
+def test_stochastic_rounding_is_unbiased_and_exact_on_grid():
+    grid = torch.tensor([0.0, 0.5, 1.0, 1.125, -3.5, 448.0, 2.0 ** -9])
+    assert torch.equal(ops.stochastic_rounding(grid, torch.float8_e4m3fn, seed=1).float(), grid)
+    v = torch.full((20000,), 1.03125)     # a quarter of the way from 1.0 to 1.125
+    q = ops.stochastic_rounding(v, torch.float8_e4m3fn, seed=3).float()
+    assert set(q.unique().tolist()) == {1.0, 1.125}
+    assert abs(float(q.mean()) - 1.03125) < 2e-3
+    assert torch.equal(ops.stochastic_rounding(v, torch.float8_e4m3fn, seed=3).float(), q)
+
+
+def test_ffn_hidden_rounding():
+    ffn = FeedForwardSwiGLU(2560, 4 * 2560, dtype=torch.bfloat16, device="meta", operations=ops.disable_weight_init)
+    assert ffn.w1.weight.shape == (6912, 2560)
+    ffn = FeedForwardSwiGLU(2560, 2 * 2560, dtype=torch.bfloat16, device="meta", operations=ops.disable_weight_init)
+    assert ffn.w1.weight.shape == (3584, 2560)
+    g = MoEGate(64, 4, 2, dtype=torch.float32, device="cpu")
+    assert g.weight.shape == (4, 64) and g.norm_topk_prob is False and g.top_k == 2
