@@ -315,11 +315,11 @@ def time_stages(module, x2, steps, moe_ops, ops):
         marks[0].record()
         idx, w, counts, _, _ = moe_ops.gate_topk(x2, layer.gate)
         marks[1].record()
-        block_offsets, _, expert_offsets = moe_ops.route_plan(counts, n, e)
+        block_offsets, expert_counts, expert_offsets = moe_ops.route_plan(counts, n, e)
         marks[2].record()
         x_perm, row_map, _ = moe_ops.permute(x2, idx, block_offsets, expert_offsets, e)
         marks[3].record()
-        y_perm, y_sh, _, _ = moe_ops.grouped_swiglu(layer.experts, layer.shared, expert_offsets, x_perm, x2,
+        y_perm, y_sh, _, _ = moe_ops.grouped_swiglu(layer.experts, layer.shared, expert_offsets, expert_counts, x_perm, x2,
                                                     status=status, check_status=False)
         marks[4].record()
         moe_ops.combine(y_perm, row_map, w, y_sh)

@@ -134,7 +134,7 @@ def load(build_if_missing: bool = False) -> ctypes.CDLL:
         c_void_p, c_void_p,
     ]
     lib.comfy_moe_grouped_swiglu.argtypes = [
-        c_int, c_int, POINTER(FfnWeights), POINTER(FfnWeights), c_void_p, c_int64, c_int, c_int, c_void_p,
+        c_int, c_int, POINTER(FfnWeights), POINTER(FfnWeights), c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p,
         c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
     ]
     lib.comfy_moe_combine.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]

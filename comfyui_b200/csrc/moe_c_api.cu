@@ -57,7 +57,8 @@ extern "C" int comfy_moe_forward(const ComfyMoeLayer* L, const ComfyMoeWorkspace
                          ws->x_perm, fp8 ? ws->x_q : nullptr, fp8 ? L->shared.scale_in13 : nullptr, ws->row_map,
                          stream);
   if (rc != COMFY_MOE_OK) return rc;
-  rc = comfy_moe_grouped_swiglu(L->w_dtype, L->n_experts, L->experts, &L->shared, ws->expert_offsets, ws->rows_cap,
+  rc = comfy_moe_grouped_swiglu(L->w_dtype, L->n_experts, L->experts, &L->shared, ws->expert_offsets,
+                                ws->expert_counts, ws->rows_cap,
                                 n_tokens, L->dim, ws->x_perm, ws->h_perm, ws->y_perm, fp8 ? ws->x_q : x,
                                 ws->h_shared, ws->y_shared, ws->status, stream);
   if (rc != COMFY_MOE_OK) return rc;

@@ -3,9 +3,11 @@
 // One persistent kernel, launched twice per layer call:
 //   pass 1 (kSwiglu):  h[m, j]  = silu(a[m,:] . w1[j,:]) * (a[m,:] . w3[j,:])
 //   pass 2 (plain):    y[m, n]  = h[m,:] . w2[n,:]
-// over "groups" = the routed experts (rows expert_offsets[e] .. expert_offsets[e+1] of the permuted
-// activations, every block a multiple of 128 rows) plus, optionally, the shared expert over the
-// un-permuted rows.  It replaces the three F.linear calls, F.silu and the product of
+// over "groups" = row ranges [row_start[g], row_start[g] + row_count[g]) of the permuted activations,
+// each with its own expert's weights (start and count live on the device, so no host sync is needed),
+// plus, optionally, the shared expert over the un-permuted rows.  Rows are independent, so a tile may
+// hang over the end of its group: the loads read whatever follows, the stores are predicated.
+// It replaces the three F.linear calls, F.silu and the product of
 // FeedForwardSwiGLU.forward (comfy/ldm/hidream/model.py:238) for all experts at once, and in the
 // fp8 variant the clamp / cast / torch._scaled_mm sequence of comfy/ops.py:338-348.
 //
@@ -49,7 +51,7 @@ struct GemmGroup {
   int b1_row_off;     // its row offset relative to the first box (0 in pass 1, 128 in pass 2)
   int k_blocks;       // K / (kRowBytes / element size)
   int n_tiles;        // tiles along the output columns
-  int routed_index;   // >= 0: rows [expert_offsets[i], expert_offsets[i+1]);  < 0: rows [0, static_rows)
+  int routed_index;   // >= 0: rows [row_start[i], row_start[i] + row_count[i]);  < 0: rows [0, static_rows)
   int static_rows;
   void* out;          // output base
   long long ld_out;   // output leading dimension in elements
@@ -62,7 +64,8 @@ struct GemmGroup {
 struct alignas(64) GemmParams {
   CUtensorMap maps[kMaxMaps];
   GemmGroup groups[kMaxGroups];
-  const int32_t* expert_offsets;
+  const int32_t* row_start;
+  const int32_t* row_count;
   int32_t* status;
   int num_groups;
 };
@@ -104,8 +107,9 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
       const GemmGroup& grp = p.groups[g];
       int base, rows, limit;
       if (grp.routed_index >= 0) {
-        base = p.expert_offsets[grp.routed_index];
-        rows = p.expert_offsets[grp.routed_index + 1] - base;
+        base = p.row_start[grp.routed_index];
+        rows = p.row_count[grp.routed_index];
+        if (rows < 0) rows = 0;
         limit = base + rows;
       } else {
         base = 0;
@@ -138,9 +142,19 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
     g = 0;
     while (t >= s_tile_start[g + 1]) ++g;
     const int local = t - s_tile_start[g];
-    const int mt = s_m_tiles[g];
-    n_tile = local / mt;
-    m_tile = local - n_tile * mt;
+    if constexpr (kSwiglu) {
+      // pass 1: row tiles fastest.  The CTAs running together share a few weight panels (read from HBM
+      // once) and sweep all rows of the group, which stay in L2 (K = dim is short).
+      const int mt = s_m_tiles[g];
+      n_tile = local / mt;
+      m_tile = local - n_tile * mt;
+    } else {
+      // pass 2: column tiles fastest.  K = hidden is long, so a row tile of h is 1.7 MB; running all
+      // column tiles of a few row tiles together reads every row of h from HBM once while w2 stays in L2.
+      const int nt = p.groups[g].n_tiles;
+      m_tile = local / nt;
+      n_tile = local - m_tile * nt;
+    }
   };
 
   if (warp == 0) {
@@ -405,14 +419,14 @@ static int launch_gemm(const GemmParams& params, int64_t max_tiles, int sms, cud
 using namespace comfy_b200;
 
 extern "C" int comfy_moe_grouped_swiglu(int w_dtype, int n_experts, const ComfyMoeFfnWeights* h_experts,
-                                        const ComfyMoeFfnWeights* h_shared, const int32_t* expert_offsets,
-                                        int64_t rows_cap, int n_tokens, int dim, const void* x_perm, void* h_perm,
+                                        const ComfyMoeFfnWeights* h_shared, const int32_t* row_start,
+                                        const int32_t* row_count, int64_t rows_cap, int n_tokens, int dim, const void* x_perm, void* h_perm,
                                         void* y_perm, const void* x_shared, void* h_shared_ws, void* y_shared,
                                         int32_t* status, void* stream) {
   if (n_experts < 0 || n_experts > kMaxExperts || dim <= 0 || n_tokens < 0 || rows_cap < 0) return COMFY_MOE_EINVAL;
   if (w_dtype != COMFY_MOE_BF16 && w_dtype != COMFY_MOE_FP8_E4M3) return COMFY_MOE_EUNSUPPORTED;
   if (!status) return COMFY_MOE_EINVAL;
-  if (n_experts > 0 && (!h_experts || !expert_offsets || !x_perm || !h_perm || !y_perm || rows_cap <= 0))
+  if (n_experts > 0 && (!h_experts || !row_start || !row_count || !x_perm || !h_perm || !y_perm || rows_cap <= 0))
     return COMFY_MOE_EINVAL;
   const bool has_shared = h_shared != nullptr && n_tokens > 0;
   if (has_shared && (!x_shared || !h_shared_ws || !y_shared)) return COMFY_MOE_EINVAL;
@@ -429,7 +443,8 @@ extern "C" int comfy_moe_grouped_swiglu(int w_dtype, int n_experts, const ComfyM
   GemmParams p1, p2;
   memset(&p1, 0, sizeof(p1));
   memset(&p2, 0, sizeof(p2));
-  p1.expert_offsets = p2.expert_offsets = expert_offsets;
+  p1.row_start = p2.row_start = row_start;
+  p1.row_count = p2.row_count = row_count;
   p1.status = p2.status = status;
   int64_t tiles1 = 0, tiles2 = 0;
   int n_maps1 = 0, n_maps2 = 0, g = 0;
@@ -444,7 +459,7 @@ extern "C" int comfy_moe_grouped_swiglu(int w_dtype, int n_experts, const ComfyM
     if ((rc = make_map(&p1.maps[n_maps1], x_perm, fp8, rows_cap, dim, dim)) != COMFY_MOE_OK) return rc;
     if ((rc = make_map(&p2.maps[n_maps2], h_perm, fp8, rows_cap, hidden_routed, hidden_routed)) != COMFY_MOE_OK) return rc;
     const int a1 = n_maps1++, a2 = n_maps2++;
-    const int64_t m_tiles_cap = rows_cap / kBlockM;
+    const int64_t m_tiles_cap = (rows_cap + kBlockM - 1) / kBlockM + n_experts;   // every group may end in a partial tile
     for (int e = 0; e < n_experts; ++e, ++g) {
       const ComfyMoeFfnWeights& w = h_experts[e];
       if (!w.w1 || !w.w2 || !w.w3) return COMFY_MOE_EINVAL;

@@ -2,110 +2,97 @@
 // routing plan (per-expert scan) and the row permutation.  All three are HBM-bound; they
 // replace comfy/ldm/hidream/model.py:263-283 (MoEGate.forward) and :330-339 (argsort,
 // bincount, cumsum on the host, row gathers) without any host synchronisation.
+//
+// Gate and permutation share one thread mapping: a block owns kTokensPerBlock consecutive
+// tokens and thread c owns the 16-byte chunk c of every row (columns 8c .. 8c+7), so a warp
+// touches 512 contiguous bytes per access and several rows are in flight per thread.
 #include "moe_common.cuh"
 
 namespace comfy_b200 {
 
-constexpr int kGateThreads = 256;
-constexpr int kGateWarps = kGateThreads / 32;
-constexpr int kTokensPerWarp = kTokensPerBlock / kGateWarps;  // 4
-static_assert(kTokensPerWarp * kGateWarps == kTokensPerBlock, "block must split evenly over warps");
-static_assert(kTokensPerWarp % 2 == 0, "the gate handles tokens in pairs");
+constexpr int kMaxRowThreads = 512;    // dim / 8 threads per block: dim <= 4096
+
+__host__ __device__ constexpr int round_up32(int v) { return (v + 31) & ~31; }
 
 // ------------------------------------------------------------------------------------------------
-// Gate.  One warp computes two tokens at a time: each lane owns 16-byte chunks (8 bf16) of the row,
-// the gate weight sits in shared memory as fp32, logits are reduced with shuffles, softmax and
-// top-2 are done redundantly in every lane, lane 0 writes.
+// Gate.  Every thread keeps its 8 columns of the gate weight of all experts in registers (fp32).
+// For kTok tokens at a time: load the chunk of each row, form E partial dot products per token,
+// reduce them inside the warp with shuffles, across warps through shared memory; thread i of the
+// block then does softmax, top-2 and the near-tie test for token i.  Summation order is fixed, so
+// the result is reproducible.
 // ------------------------------------------------------------------------------------------------
 template <int E>
-__global__ void __launch_bounds__(kGateThreads)
+__global__ void __launch_bounds__(kMaxRowThreads)
 gate_topk_kernel(const __nv_bfloat16* __restrict__ x, const void* __restrict__ w_gate, int w_dtype, int n_tokens,
                  int dim, int32_t* __restrict__ topk_idx, float* __restrict__ topk_weight,
                  int32_t* __restrict__ block_counts, int32_t* __restrict__ neartie_count,
                  uint8_t* __restrict__ neartie_flags, float neartie_eps) {
-  extern __shared__ __align__(16) float w_s[];  // [E][dim]
+  constexpr int kTok = E <= 4 ? 8 : 4;                 // tokens in flight per thread
+  constexpr int kMaxWarps = kMaxRowThreads / 32;
+  __shared__ float part[2][kTok][kMaxWarps][E];        // double-buffered per-warp partial logits
   __shared__ int hist[E];
 
-  const int tid = threadIdx.x;
-  const int lane = tid & 31;
-  const int warp = tid >> 5;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int n_warps = blockDim.x >> 5;
+  const int chunks = dim >> 3;
+  const bool active = tid < chunks;
 
-  if (tid < E) hist[tid] = 0;
-  if (w_dtype == COMFY_MOE_FP32) {
-    const float* w = static_cast<const float*>(w_gate);
-    for (int i = tid; i < E * dim; i += kGateThreads) w_s[i] = w[i];
-  } else {
-    const __nv_bfloat16* w = static_cast<const __nv_bfloat16*>(w_gate);
-    for (int i = tid; i < E * dim; i += kGateThreads) w_s[i] = __bfloat162float(w[i]);
+  float wreg[E][8];
+#pragma unroll
+  for (int e = 0; e < E; ++e) {
+    if (!active) {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) wreg[e][k] = 0.f;
+    } else if (w_dtype == COMFY_MOE_FP32) {
+      const float4* w = reinterpret_cast<const float4*>(static_cast<const float*>(w_gate) + static_cast<size_t>(e) * dim) + 2 * tid;
+      const float4 a = w[0], b = w[1];
+      wreg[e][0] = a.x; wreg[e][1] = a.y; wreg[e][2] = a.z; wreg[e][3] = a.w;
+      wreg[e][4] = b.x; wreg[e][5] = b.y; wreg[e][6] = b.z; wreg[e][7] = b.w;
+    } else {
+      const uint4 v = *(reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(w_gate) + static_cast<size_t>(e) * dim) + tid);
+      unpack_bf16x8(v, wreg[e]);
+    }
   }
+  if (tid < E) hist[tid] = 0;
   __syncthreads();
 
-  const int chunks = dim >> 3;  // 16-byte chunks per row
   const int block_tok0 = blockIdx.x * kTokensPerBlock;
-
-  for (int pair = 0; pair < kTokensPerWarp / 2; ++pair) {
-    const int t0 = block_tok0 + warp * kTokensPerWarp + pair * 2;
-    const int t1 = t0 + 1;
-    if (t0 >= n_tokens) break;
-    const bool has1 = t1 < n_tokens;
-    const uint4* r0 = reinterpret_cast<const uint4*>(x + static_cast<size_t>(t0) * dim);
-    const uint4* r1 = reinterpret_cast<const uint4*>(x + static_cast<size_t>(has1 ? t1 : t0) * dim);
-
-    float acc0[E], acc1[E];
+  int buf = 0;
+  for (int base = 0; base < kTokensPerBlock; base += kTok, buf ^= 1) {
+    const int t0 = block_tok0 + base;
+    if (t0 >= n_tokens) break;                          // uniform across the block
+    uint4 v[kTok];
 #pragma unroll
-    for (int e = 0; e < E; ++e) { acc0[e] = 0.f; acc1[e] = 0.f; }
-
-    constexpr int kBatch = 5;  // chunks per lane in flight per token
-    for (int c0 = lane; c0 < chunks; c0 += 32 * kBatch) {
-      uint4 v0[kBatch], v1[kBatch];
-#pragma unroll
-      for (int j = 0; j < kBatch; ++j) {
-        const int c = c0 + 32 * j;
-        if (c < chunks) {
-          v0[j] = ld_nc_u4(r0 + c);
-          v1[j] = ld_nc_u4(r1 + c);
-        }
-      }
-#pragma unroll
-      for (int j = 0; j < kBatch; ++j) {
-        const int c = c0 + 32 * j;
-        if (c < chunks) {
-          float f0[8], f1[8];
-          unpack_bf16x8(v0[j], f0);
-          unpack_bf16x8(v1[j], f1);
-#pragma unroll
-          for (int e = 0; e < E; ++e) {
-            const float4 wa = *reinterpret_cast<const float4*>(w_s + e * dim + c * 8);
-            const float4 wb = *reinterpret_cast<const float4*>(w_s + e * dim + c * 8 + 4);
-            const float wv[8] = {wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w};
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              acc0[e] = fmaf(f0[i], wv[i], acc0[e]);
-              acc1[e] = fmaf(f1[i], wv[i], acc1[e]);
-            }
-          }
-        }
-      }
+    for (int i = 0; i < kTok; ++i) {
+      const int t = t0 + i;
+      v[i] = (active && t < n_tokens) ? ld_nc_u4(reinterpret_cast<const uint4*>(x + static_cast<size_t>(t) * dim) + tid)
+                                      : make_uint4(0, 0, 0, 0);
     }
 #pragma unroll
-    for (int e = 0; e < E; ++e) {
+    for (int i = 0; i < kTok; ++i) {
+      float f[8];
+      unpack_bf16x8(v[i], f);
 #pragma unroll
-      for (int off = 16; off > 0; off >>= 1) {
-        acc0[e] += __shfl_xor_sync(0xffffffffu, acc0[e], off);
-        acc1[e] += __shfl_xor_sync(0xffffffffu, acc1[e], off);
+      for (int e = 0; e < E; ++e) {
+        float acc = 0.f;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) acc = fmaf(f[k], wreg[e][k], acc);
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+        if (lane == 0) part[buf][i][warp][e] = acc;
       }
     }
-
-#pragma unroll
-    for (int which = 0; which < 2; ++which) {
-      if (which == 1 && !has1) break;
-      const int t = which == 0 ? t0 : t1;
+    __syncthreads();
+    if (tid < kTok && t0 + tid < n_tokens) {
+      const int t = t0 + tid;
       float s[E];
       float mx = -INFINITY;
 #pragma unroll
       for (int e = 0; e < E; ++e) {
-        s[e] = which == 0 ? acc0[e] : acc1[e];
-        mx = fmaxf(mx, s[e]);
+        float acc = 0.f;
+        for (int w = 0; w < n_warps; ++w) acc += part[buf][tid][w][e];
+        s[e] = acc;
+        mx = fmaxf(mx, acc);
       }
       float sum = 0.f;
 #pragma unroll
@@ -127,18 +114,17 @@ gate_topk_kernel(const __nv_bfloat16* __restrict__ x, const void* __restrict__ w
 #pragma unroll
       for (int e = 0; e < E; ++e) if (e != i0 && e != i1) third = fmaxf(third, s[e]);
 
-      if (lane == 0) {
-        topk_idx[2 * t] = i0;
-        topk_idx[2 * t + 1] = i1;
-        topk_weight[2 * t] = s[i0];
-        topk_weight[2 * t + 1] = s[i1];
-        atomicAdd(&hist[i0], 1);
-        atomicAdd(&hist[i1], 1);
-        const bool tie = (E > 2) && (s[i1] - third < neartie_eps);
-        if (neartie_flags) neartie_flags[t] = tie ? 1 : 0;
-        if (tie && neartie_count) atomicAdd(neartie_count, 1);
-      }
+      topk_idx[2 * t] = i0;
+      topk_idx[2 * t + 1] = i1;
+      topk_weight[2 * t] = s[i0];
+      topk_weight[2 * t + 1] = s[i1];
+      atomicAdd(&hist[i0], 1);                           // integer atomics: order does not matter
+      atomicAdd(&hist[i1], 1);
+      const bool tie = (E > 2) && (s[i1] - third < neartie_eps);
+      if (neartie_flags) neartie_flags[t] = tie ? 1 : 0;
+      if (tie && neartie_count) atomicAdd(neartie_count, 1);
     }
+    // the next iteration writes the other buffer; the one after that is fenced by its own barrier
   }
   __syncthreads();
   if (tid < E) block_counts[blockIdx.x * E + tid] = hist[tid];
@@ -226,17 +212,19 @@ route_plan_kernel(const int32_t* __restrict__ block_counts, int n_blocks, int n_
 
 // ------------------------------------------------------------------------------------------------
 // Permutation.  Block b owns the same tokens as gate block b.  Slots (token, k) are ranked inside
-// the block with warp ballots, which gives a stable, atomic-free placement; then every warp copies
-// its tokens' rows to both destinations with 16-byte accesses.
+// the block with warp ballots, which gives a stable, atomic-free placement; then thread c copies
+// chunk c of every row to both destinations, kTok rows in flight.
+// bf16: chunk = 8 elements (16 B in, 16 B out).  fp8: chunk = 16 elements (32 B in, 16 B out).
 // ------------------------------------------------------------------------------------------------
 template <bool kFp8>
-__global__ void __launch_bounds__(kGateThreads)
+__global__ void __launch_bounds__(kMaxRowThreads)
 permute_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ topk_idx,
                const int32_t* __restrict__ block_offsets, const int32_t* __restrict__ expert_offsets,
                int n_tokens, int dim, int n_experts, const float* __restrict__ act_scale,
                void* __restrict__ x_perm, void* __restrict__ x_q, const float* __restrict__ x_q_scale,
                int32_t* __restrict__ row_map) {
   constexpr int kSlots = kTokensPerBlock * 2;  // 64
+  constexpr int kTok = 8;
   __shared__ int dest_s[kSlots];
   __shared__ int warp_cnt[kSlots / 32][kMaxExperts];
 
@@ -267,49 +255,55 @@ permute_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ 
   }
   __syncthreads();
 
-  float inv_p = 1.f, inv_q = 1.f;
-  bool scaled_p = false, scaled_q = false;
-  if constexpr (kFp8) {
+  const int chunks = kFp8 ? (dim >> 4) : (dim >> 3);
+  if (tid >= chunks) return;
+
+  if constexpr (!kFp8) {
+    __nv_bfloat16* xp = static_cast<__nv_bfloat16*>(x_perm);
+    for (int base = 0; base < kTokensPerBlock; base += kTok) {
+      const int t0 = block_tok0 + base;
+      if (t0 >= n_tokens) break;
+      uint4 v[kTok];
+#pragma unroll
+      for (int i = 0; i < kTok; ++i)
+        if (t0 + i < n_tokens) v[i] = ld_nc_u4(reinterpret_cast<const uint4*>(x + static_cast<size_t>(t0 + i) * dim) + tid);
+#pragma unroll
+      for (int i = 0; i < kTok; ++i) {
+        if (t0 + i < n_tokens) {
+          const int d0 = dest_s[2 * (base + i)], d1 = dest_s[2 * (base + i) + 1];
+          if (d0 >= 0) reinterpret_cast<uint4*>(xp + static_cast<size_t>(d0) * dim)[tid] = v[i];
+          if (d1 >= 0) reinterpret_cast<uint4*>(xp + static_cast<size_t>(d1) * dim)[tid] = v[i];
+        }
+      }
+    }
+  } else {
+    float inv_p = 1.f, inv_q = 1.f;
+    bool scaled_p = false, scaled_q = false;
     if (act_scale) { inv_p = round_bf16(1.0f / __ldg(act_scale)); scaled_p = true; }
     if (x_q_scale) { inv_q = round_bf16(1.0f / __ldg(x_q_scale)); scaled_q = true; }
-  }
-
-  for (int i = 0; i < kTokensPerWarp; ++i) {
-    const int lt = warp * kTokensPerWarp + i;
-    const int t = block_tok0 + lt;
-    if (t >= n_tokens) break;
-    const int d0 = dest_s[2 * lt], d1 = dest_s[2 * lt + 1];
-    const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<size_t>(t) * dim);
-    if constexpr (!kFp8) {
-      uint4* o0 = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(x_perm) + static_cast<size_t>(d0) * dim);
-      uint4* o1 = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(x_perm) + static_cast<size_t>(d1) * dim);
-      const int chunks = dim >> 3;
-      constexpr int kBatch = 5;
-      for (int c0 = lane; c0 < chunks; c0 += 32 * kBatch) {
-        uint4 v[kBatch];
+    const bool same_q = (scaled_q == scaled_p) && (inv_q == inv_p);
+    uint8_t* xp = static_cast<uint8_t*>(x_perm);
+    uint8_t* xq = static_cast<uint8_t*>(x_q);
+    constexpr int kTok8 = 4;
+    for (int base = 0; base < kTokensPerBlock; base += kTok8) {
+      const int t0 = block_tok0 + base;
+      if (t0 >= n_tokens) break;
+      uint4 va[kTok8], vb[kTok8];
 #pragma unroll
-        for (int j = 0; j < kBatch; ++j)
-          if (c0 + 32 * j < chunks) v[j] = ld_nc_u4(src + c0 + 32 * j);
+      for (int i = 0; i < kTok8; ++i)
+        if (t0 + i < n_tokens) {
+          const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<size_t>(t0 + i) * dim) + 2 * tid;
+          va[i] = ld_nc_u4(src);
+          vb[i] = ld_nc_u4(src + 1);
+        }
 #pragma unroll
-        for (int j = 0; j < kBatch; ++j)
-          if (c0 + 32 * j < chunks) {
-            if (d0 >= 0) o0[c0 + 32 * j] = v[j];
-            if (d1 >= 0) o1[c0 + 32 * j] = v[j];
-          }
-      }
-    } else {
-      // 16 bf16 (two 16-byte loads) -> 16 e4m3 bytes (one 16-byte store)
-      uint8_t* p0 = static_cast<uint8_t*>(x_perm) + static_cast<size_t>(d0) * dim;
-      uint8_t* p1 = static_cast<uint8_t*>(x_perm) + static_cast<size_t>(d1) * dim;
-      uint8_t* q = x_q ? static_cast<uint8_t*>(x_q) + static_cast<size_t>(t) * dim : nullptr;
-      const int chunks = dim >> 4;
-      for (int c = lane; c < chunks; c += 32) {
-        const uint4 a = ld_nc_u4(src + 2 * c), b = ld_nc_u4(src + 2 * c + 1);
+      for (int i = 0; i < kTok8; ++i) {
+        if (t0 + i >= n_tokens) continue;
         float f[16];
         {
           float fa[8], fb[8];
-          unpack_bf16x8(a, fa);
-          unpack_bf16x8(b, fb);
+          unpack_bf16x8(va[i], fa);
+          unpack_bf16x8(vb[i], fb);
 #pragma unroll
           for (int k = 0; k < 8; ++k) { f[k] = fa[k]; f[8 + k] = fb[k]; }
         }
@@ -321,7 +315,7 @@ permute_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ 
           for (int m = 0; m < 4; ++m) g[m] = scaled_p ? round_bf16(f[4 * k + m] * inv_p) : f[4 * k + m];
           wp[k] = static_cast<uint32_t>(f2_to_e4m3x2(g[0], g[1])) |
                   (static_cast<uint32_t>(f2_to_e4m3x2(g[2], g[3])) << 16);
-          if (scaled_q == scaled_p && inv_q == inv_p) {
+          if (same_q) {
             wq[k] = wp[k];
           } else {
 #pragma unroll
@@ -331,9 +325,10 @@ permute_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ 
           }
         }
         const uint4 vp = make_uint4(wp[0], wp[1], wp[2], wp[3]);
-        if (d0 >= 0) reinterpret_cast<uint4*>(p0)[c] = vp;
-        if (d1 >= 0) reinterpret_cast<uint4*>(p1)[c] = vp;
-        if (q) reinterpret_cast<uint4*>(q)[c] = make_uint4(wq[0], wq[1], wq[2], wq[3]);
+        const int d0 = dest_s[2 * (base + i)], d1 = dest_s[2 * (base + i) + 1];
+        if (d0 >= 0) reinterpret_cast<uint4*>(xp + static_cast<size_t>(d0) * dim)[tid] = vp;
+        if (d1 >= 0) reinterpret_cast<uint4*>(xp + static_cast<size_t>(d1) * dim)[tid] = vp;
+        if (xq) reinterpret_cast<uint4*>(xq + static_cast<size_t>(t0 + i) * dim)[tid] = make_uint4(wq[0], wq[1], wq[2], wq[3]);
       }
     }
   }
@@ -350,19 +345,17 @@ extern "C" int comfy_moe_plan_sizes(int n_tokens, int n_experts, int top_k, int6
   return COMFY_MOE_OK;
 }
 
+static int row_threads(int dim) {
+  const int t = round_up32(dim >> 3);
+  return t < 64 ? 64 : t;     // the permutation ranks 64 slots with the first two warps
+}
+
 template <int E>
 static int launch_gate(const void* x, const void* w_gate, int w_dtype, int n_tokens, int dim, int32_t* topk_idx,
                        float* topk_weight, int32_t* block_counts, int32_t* neartie_count, uint8_t* neartie_flags,
                        float neartie_eps, cudaStream_t stream) {
-  const size_t smem = static_cast<size_t>(E) * dim * sizeof(float);
-  if (smem > 200 * 1024) return COMFY_MOE_EUNSUPPORTED;
-  if (smem > 48 * 1024) {
-    if (cudaFuncSetAttribute(gate_topk_kernel<E>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             static_cast<int>(smem)) != cudaSuccess)
-      return COMFY_MOE_ECUDA;
-  }
   const int n_blocks = (n_tokens + kTokensPerBlock - 1) / kTokensPerBlock;
-  gate_topk_kernel<E><<<n_blocks, kGateThreads, smem, stream>>>(
+  gate_topk_kernel<E><<<n_blocks, row_threads(dim), 0, stream>>>(
       static_cast<const __nv_bfloat16*>(x), w_gate, w_dtype, n_tokens, dim, topk_idx, topk_weight, block_counts,
       neartie_count, neartie_flags, neartie_eps);
   return check_launch();
@@ -376,7 +369,7 @@ extern "C" int comfy_moe_gate_topk(const void* x, const void* w_gate, int w_dtyp
   if (n_tokens == 0) return COMFY_MOE_OK;
   if (!x || !w_gate || !topk_idx || !topk_weight || !block_counts) return COMFY_MOE_EINVAL;
   if (!aligned16(x) || !aligned16(w_gate)) return COMFY_MOE_EINVAL;
-  if (top_k != 2 || (dim & 7) != 0) return COMFY_MOE_EUNSUPPORTED;
+  if (top_k != 2 || (dim & 7) != 0 || (dim >> 3) > kMaxRowThreads) return COMFY_MOE_EUNSUPPORTED;
   if (w_dtype != COMFY_MOE_BF16 && w_dtype != COMFY_MOE_FP32) return COMFY_MOE_EUNSUPPORTED;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   switch (n_experts) {
@@ -418,18 +411,19 @@ extern "C" int comfy_moe_permute(const void* x, const int32_t* topk_idx, const i
   if (n_tokens == 0) return COMFY_MOE_OK;
   if (!x || !topk_idx || !block_offsets || !expert_offsets || !x_perm || !row_map) return COMFY_MOE_EINVAL;
   if (!aligned16(x) || !aligned16(x_perm) || (x_q && !aligned16(x_q))) return COMFY_MOE_EINVAL;
+  if ((dim >> 3) > kMaxRowThreads) return COMFY_MOE_EUNSUPPORTED;
   const int n_blocks = (n_tokens + kTokensPerBlock - 1) / kTokensPerBlock;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (act_dtype == COMFY_MOE_BF16) {
     if ((dim & 7) != 0) return COMFY_MOE_EUNSUPPORTED;
-    permute_kernel<false><<<n_blocks, kGateThreads, 0, s>>>(static_cast<const __nv_bfloat16*>(x), topk_idx,
-                                                            block_offsets, expert_offsets, n_tokens, dim, n_experts,
-                                                            nullptr, x_perm, nullptr, nullptr, row_map);
+    permute_kernel<false><<<n_blocks, row_threads(dim), 0, s>>>(static_cast<const __nv_bfloat16*>(x), topk_idx,
+                                                                 block_offsets, expert_offsets, n_tokens, dim,
+                                                                 n_experts, nullptr, x_perm, nullptr, nullptr, row_map);
   } else if (act_dtype == COMFY_MOE_FP8_E4M3) {
     if ((dim & 15) != 0) return COMFY_MOE_EUNSUPPORTED;
-    permute_kernel<true><<<n_blocks, kGateThreads, 0, s>>>(static_cast<const __nv_bfloat16*>(x), topk_idx,
-                                                           block_offsets, expert_offsets, n_tokens, dim, n_experts,
-                                                           act_scale, x_perm, x_q, x_q_scale, row_map);
+    permute_kernel<true><<<n_blocks, row_threads(dim), 0, s>>>(static_cast<const __nv_bfloat16*>(x), topk_idx,
+                                                                block_offsets, expert_offsets, n_tokens, dim,
+                                                                n_experts, act_scale, x_perm, x_q, x_q_scale, row_map);
   } else {
     return COMFY_MOE_EUNSUPPORTED;
   }

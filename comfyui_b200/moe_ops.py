@@ -260,10 +260,13 @@ def permute(x: torch.Tensor, topk_idx: torch.Tensor, block_offsets: torch.Tensor
     return x_perm, row_map, x_q
 
 
-def grouped_swiglu(experts: Sequence[FfnPack], shared: Optional[FfnPack], expert_offsets: Optional[torch.Tensor],
-                   x_perm: Optional[torch.Tensor], x_shared: Optional[torch.Tensor], *,
-                   status: Optional[torch.Tensor] = None, check_status: bool = True):
-    """Both passes of the grouped expert GEMM.  Returns (y_perm or None, y_shared or None, h_perm, h_shared)."""
+def grouped_swiglu(experts: Sequence[FfnPack], shared: Optional[FfnPack], row_start: Optional[torch.Tensor],
+                   row_count: Optional[torch.Tensor], x_perm: Optional[torch.Tensor],
+                   x_shared: Optional[torch.Tensor], *, status: Optional[torch.Tensor] = None,
+                   check_status: bool = True):
+    """Both passes of the grouped expert GEMM.  Group g = rows [row_start[g], row_start[g] + row_count[g]) of
+    x_perm with the weights experts[g] (int32 device tensors; the routing plan's expert_offsets and
+    expert_counts on one GPU).  Returns (y_perm or None, y_shared or None, h_perm, h_shared)."""
     ref = experts[0] if experts else shared
     dim, fp8 = ref.dim, ref.w1.dtype == _FP8
     dev = ref.w1.device
@@ -287,7 +290,7 @@ def grouped_swiglu(experts: Sequence[FfnPack], shared: Optional[FfnPack], expert
         status = torch.zeros((2,), dtype=torch.int32, device=dev)
     rc = N.load().comfy_moe_grouped_swiglu(
         N.FP8_E4M3 if fp8 else N.BF16, n_e, arr, ctypes.byref(sh) if sh is not None else None,
-        _ptr(expert_offsets), rows_cap, n_tokens, dim, _ptr(x_perm), _ptr(h_perm), _ptr(y_perm), _ptr(x_shared),
+        _ptr(row_start), _ptr(row_count), rows_cap, n_tokens, dim, _ptr(x_perm), _ptr(h_perm), _ptr(y_perm), _ptr(x_shared),
         _ptr(h_sh), _ptr(y_sh), _ptr(status), _stream())
     N.check("comfy_moe_grouped_swiglu", rc)
     if check_status:

@@ -409,10 +409,10 @@ def hidream_moe_infer(moe, x: torch.Tensor, flat_expert_indices: torch.Tensor,
     idx = flat_expert_indices.reshape(n, 2).to(torch.int32).contiguous()
     w = flat_expert_weights.reshape(n, 2).to(torch.float32).contiguous()
     counts = moe_ops.route_count(idx, e)
-    block_offsets, _, expert_offsets = moe_ops.route_plan(counts, n, e)
+    block_offsets, expert_counts, expert_offsets = moe_ops.route_plan(counts, n, e)
     in13 = layer.experts[0].scale_in13
     x_perm, row_map, _ = moe_ops.permute(x, idx, block_offsets, expert_offsets, e, fp8=layer.fp8, act_scale=in13)
-    y_perm, _, _, _ = moe_ops.grouped_swiglu(layer.experts, None, expert_offsets, x_perm, None,
+    y_perm, _, _, _ = moe_ops.grouped_swiglu(layer.experts, None, expert_offsets, expert_counts, x_perm, None,
                                               check_status=CHECK_STATUS_EVERY_CALL)
     return moe_ops.combine(y_perm, row_map, w, None)
 
@@ -430,5 +430,5 @@ def swiglu_ffn_forward(ffn, x: torch.Tensor) -> Optional[torch.Tensor]:
     x2 = x.view(-1, dim)
     if pack.w1.dtype == FP8:
         return None   # the dense fp8 path needs the quantised copy the permutation kernel makes
-    _, y, _, _ = moe_ops.grouped_swiglu([], pack, None, None, x2, check_status=CHECK_STATUS_EVERY_CALL)
+    _, y, _, _ = moe_ops.grouped_swiglu([], pack, None, None, None, x2, check_status=CHECK_STATUS_EVERY_CALL)
     return y.view(x.shape)

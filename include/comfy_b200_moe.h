@@ -123,18 +123,20 @@ typedef struct ComfyMoeFfnWeights {
  * Two launches of one persistent tcgen05/TMEM kernel:
  *   h      = silu(a . w1^T) * (a . w3^T)    (bf16 roundings after each of the reference's four steps)
  *   y      = h . w2^T
- * over the routed groups (rows expert_offsets[e] .. expert_offsets[e+1] of x_perm) and, when `shared` is not
- * NULL, one more group over the un-permuted rows.
+ * over n_groups row ranges of x_perm, group g = rows [row_start[g], row_start[g] + row_count[g]) with weights
+ * h_groups[g] (start and count are DEVICE arrays: no host sync; several groups may name the same expert), and,
+ * when `h_shared` is not NULL, one more group over the un-permuted rows.  Group starts need no alignment.
  *   w_dtype        COMFY_MOE_BF16 or COMFY_MOE_FP8_E4M3 (activations x_perm / x_shared / h_* use the same)
  *   x_perm         [rows_cap, dim]        h_perm [rows_cap, hidden] workspace   y_perm bf16 [rows_cap, dim]
  *   x_shared       [n_tokens, dim]        h_shared [n_tokens, hidden_s]         y_shared bf16 [n_tokens, dim]
  *   status         int32 [1]: the kernels write a non-zero code here if a bounded wait ran out (caller zeroes)
+ * Requires dim % 256 == 0 and hidden % 128 == 0 (COMFY_MOE_EUNSUPPORTED otherwise).
  */
-int comfy_moe_grouped_swiglu(int w_dtype, int n_experts, const ComfyMoeFfnWeights* h_experts,
-                             const ComfyMoeFfnWeights* h_shared, const int32_t* expert_offsets, int64_t rows_cap,
-                             int n_tokens, int dim, const void* x_perm, void* h_perm, void* y_perm,
-                             const void* x_shared, void* h_shared_ws, void* y_shared, int32_t* status,
-                             void* stream);
+int comfy_moe_grouped_swiglu(int w_dtype, int n_groups, const ComfyMoeFfnWeights* h_groups,
+                             const ComfyMoeFfnWeights* h_shared, const int32_t* row_start,
+                             const int32_t* row_count, int64_t rows_cap, int n_tokens, int dim, const void* x_perm,
+                             void* h_perm, void* y_perm, const void* x_shared, void* h_shared_ws, void* y_shared,
+                             int32_t* status, void* stream);
 
 /* ---- weighted combine: replaces mul_ + scatter_reduce_ + shared add (model.py:341-345, 324) ---------------
  * out[t] = bf16( bf16( bf16(w0*y[r0]) + bf16(w1*y[r1]) ) + y_shared[t] ), weights rounded to bf16 first.
