@@ -12,10 +12,23 @@
 // fp8 variant the clamp / cast / torch._scaled_mm sequence of comfy/ops.py:338-348.
 //
 // CTA layout (192 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer,
-// warps 2-5 = epilogue (TMEM -> registers -> global).  A tile is 128 rows x 256 accumulator
-// columns; in pass 1 the 256 columns are 128 of w1 next to the matching 128 of w3, so one MMA
-// stream yields both halves of the SwiGLU and the epilogue emits 128 columns of h.
-// Shared memory: 4 stages x (A 16 KB + B 32 KB), 128-byte swizzle.  TMEM: 2 x 256 columns, so the
+// warps 2-5 = epilogue (TMEM -> registers -> global).
+//
+// kCtas = 2: two CTAs on an SM pair form a cluster and share one
+// tcgen05.mma.cta_group::2 stream.  A cluster tile is 256 rows x 256 accumulator columns; each CTA
+// loads its own 128 rows of A and HALF of the B tile (128 rows), so shared-memory fill traffic and
+// L2->SM traffic per flop drop by a third against a single-CTA 128 x 256 tile.  In pass 1 the 256
+// accumulator columns are 128 of w1 (loaded by CTA 0) next to the matching 128 of w3 (CTA 1), so one
+// MMA stream yields both halves of the SwiGLU and the epilogue emits 128 columns of h.  All loads are
+// plain (single-destination) TMA loads; the pair is coordinated with mbarriers only:
+//   full[s]        lives in CTA 0; CTA 0's producer arms it with the bytes of both CTAs' loads, both
+//                  CTAs' loads complete on it;
+//   empty[s]       one per CTA; CTA 0's MMA thread commits to both once a stage has been consumed;
+//   tmem_full[a]   one per CTA, committed to by CTA 0's MMA thread when a tile's accumulator is done;
+//   tmem_empty[a]  lives in CTA 0; the epilogue warps of both CTAs arrive on it.
+// kCtas = 1 (the default) is the same code with every pair degenerate (one CTA, 128-row tiles, the CTA
+// loads both B boxes itself).
+// Shared memory: kStages x (A 16 KB + B 32/kCtas KB), 128-byte swizzle.  TMEM: 2 x 256 columns, so the
 // epilogue of tile i overlaps the MMAs of tile i+1.
 #include <cuda.h>
 
@@ -24,20 +37,24 @@
 
 namespace comfy_b200 {
 
-constexpr int kBlockM = 128;
-constexpr int kBlockN = 256;
+constexpr int kBlockM = 128;                      // rows per CTA per tile
+constexpr int kBlockN = 256;                      // accumulator columns per tile
 constexpr int kRowBytes = 128;                    // bytes of K per operand row per stage
-constexpr int kStages = 4;
 constexpr int kAccStages = 2;
 constexpr int kABytes = kBlockM * kRowBytes;      // 16 KB
-constexpr int kBHalfBytes = 128 * kRowBytes;      // 16 KB: one 128-row B box
-constexpr int kBBytes = 2 * kBHalfBytes;          // 32 KB
-constexpr int kStageBytes = kABytes + kBBytes;    // 48 KB
+constexpr int kBBoxBytes = 128 * kRowBytes;       // 16 KB: one 128-row B box
 constexpr int kGemmThreads = 192;
 constexpr int kTmemCols = kAccStages * kBlockN;   // 512
 constexpr int kMaxGroups = kMaxExperts + 1;
 constexpr int kMaxMaps = 2 + 2 * kMaxGroups;
-constexpr size_t kGemmSmemBytes = static_cast<size_t>(kStages) * kStageBytes + 1024;  // + alignment slack
+
+template <int kCtas> struct GemmShape {
+  static constexpr int kTileM = kBlockM * kCtas;
+  static constexpr int kBBoxes = 2 / kCtas;                                  // B boxes each CTA loads
+  static constexpr int kStageBytes = kABytes + kBBoxes * kBBoxBytes;          // 48 KB or 32 KB
+  static constexpr int kStages = kCtas == 1 ? 4 : 6;
+  static constexpr size_t kSmemBytes = static_cast<size_t>(kStages) * kStageBytes + 1024;  // + alignment slack
+};
 
 // Device-side status codes written to *status when a bounded wait gives up.
 constexpr int kStatusProducerTimeout = 1;
@@ -68,6 +85,7 @@ struct alignas(64) GemmParams {
   const int32_t* row_count;
   int32_t* status;
   int num_groups;
+  int exp_mode;   // EXPERIMENT ONLY: 1 = no TMA loads, 2 = no MMAs, 4 = no epilogue math/stores
 };
 
 __device__ __forceinline__ float silu_bf16_steps(float a_bf16) {
@@ -75,9 +93,15 @@ __device__ __forceinline__ float silu_bf16_steps(float a_bf16) {
   return round_bf16(__fdividef(a_bf16, 1.0f + __expf(-a_bf16)));
 }
 
-template <bool kFp8, bool kSwiglu>
+template <bool kFp8, bool kSwiglu, int kCtas>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
+  using Shape = GemmShape<kCtas>;
+  constexpr int kStages = Shape::kStages;
+  constexpr int kStageBytes = Shape::kStageBytes;
+  constexpr int kTileM = Shape::kTileM;
+  constexpr bool kPair = kCtas == 2;
+
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t full_bar[kStages];
   __shared__ __align__(8) uint64_t empty_bar[kStages];
@@ -94,11 +118,14 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int lane = tid & 31;
+  const uint32_t cta_rank = kPair ? cluster_ctarank() : 0u;   // 0 = leader of the pair
+  const int unit = blockIdx.x / kCtas;                         // index of this CTA (pair) among the workers
+  const int n_units = gridDim.x / kCtas;
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
 
   if (tid == 0) {
     for (int s = 0; s < kStages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
-    for (int s = 0; s < kAccStages; ++s) { mbar_init(&tmem_full_bar[s], 1); mbar_init(&tmem_empty_bar[s], 128); }
+    for (int s = 0; s < kAccStages; ++s) { mbar_init(&tmem_full_bar[s], 1); mbar_init(&tmem_empty_bar[s], 4 * kCtas); }
     mbar_init(&drain_bar, 1);
     fence_mbar_init();
     abort_flag = 0;
@@ -116,7 +143,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
         rows = grp.static_rows;
         limit = rows;
       }
-      const int m_tiles = (rows + kBlockM - 1) / kBlockM;
+      const int m_tiles = (rows + kTileM - 1) / kTileM;
       s_tile_start[g] = start;
       s_m_tiles[g] = m_tiles;
       s_row_base[g] = base;
@@ -126,11 +153,13 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
     s_tile_start[p.num_groups] = start;
   }
   if (warp == 1) {
-    tmem_alloc(&tmem_slot, kTmemCols);
-    tmem_relinquish();
+    if constexpr (kPair) { tmem_alloc_pair(&tmem_slot, kTmemCols); tmem_relinquish_pair(); }
+    else { tmem_alloc(&tmem_slot, kTmemCols); tmem_relinquish(); }
   }
+  __syncwarp();
   tc_fence_before_sync();
-  __syncthreads();
+  if constexpr (kPair) cluster_sync_all();     // the peer's barriers must exist before anything signals them
+  else __syncthreads();
   tc_fence_after_sync();
 
   const uint32_t tmem_base = tmem_slot;
@@ -158,23 +187,22 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
   };
 
   if (warp == 0) {
-    // ------------------------------------------------------------------ TMA producer
+    // ------------------------------------------------------------------ TMA producer (both CTAs of a pair)
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      for (int t = unit; t < total_tiles && ok; t += n_units) {
         int g, m_tile, n_tile;
         decode(t, g, m_tile, n_tile);
         const GemmGroup& grp = p.groups[g];
         const CUtensorMap* map_a = &p.maps[grp.a_map];
-        const CUtensorMap* map_b0 = &p.maps[grp.b0_map];
-        const CUtensorMap* map_b1 = &p.maps[grp.b1_map];
-        const int a_row = s_row_base[g] + m_tile * kBlockM;
+        const int a_row = s_row_base[g] + m_tile * kTileM + static_cast<int>(cta_rank) * kBlockM;
         const int b_row = n_tile * (kSwiglu ? 128 : kBlockN);
         const int kb_count = grp.k_blocks;
         for (int kb = 0; kb < kb_count; ++kb, ++it) {
           const int s = it % kStages;
           const uint32_t ph = (it / kStages) & 1u;
+          if ((p.exp_mode & 16) && cta_rank == 1) continue;
           if (!mbar_wait(&empty_bar[s], ph ^ 1u, abort_ptr)) {
             atomicCAS(p.status, 0, kStatusProducerTimeout);
             abort_flag = 1;
@@ -182,21 +210,34 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
             break;
           }
           uint8_t* stage = smem + static_cast<size_t>(s) * kStageBytes;
-          mbar_arrive_expect_tx(&full_bar[s], kStageBytes);
-          tma_load_2d(stage, map_a, &full_bar[s], kb * kElemsPerRow, a_row);
-          tma_load_2d(stage + kABytes, map_b0, &full_bar[s], kb * kElemsPerRow, b_row);
-          tma_load_2d(stage + kABytes + kBHalfBytes, map_b1, &full_bar[s], kb * kElemsPerRow,
-                      b_row + grp.b1_row_off);
+          if (p.exp_mode & 1) {
+            if (cta_rank == 0) mbar_arrive(&full_bar[s]);
+            continue;
+          }
+          if constexpr (kPair) {
+            const uint32_t full_leader = mapa_shared(smem_u32(&full_bar[s]), 0);
+            if (cta_rank == 0) mbar_arrive_expect_tx(&full_bar[s], 2 * kStageBytes);
+            tma_load_2d_pair(stage, map_a, full_leader, kb * kElemsPerRow, a_row);
+            const CUtensorMap* map_b = &p.maps[cta_rank == 0 ? grp.b0_map : grp.b1_map];
+            tma_load_2d_pair(stage + kABytes, map_b, full_leader, kb * kElemsPerRow,
+                             b_row + (cta_rank == 0 ? 0 : grp.b1_row_off));
+          } else {
+            mbar_arrive_expect_tx(&full_bar[s], kStageBytes);
+            tma_load_2d(stage, map_a, &full_bar[s], kb * kElemsPerRow, a_row);
+            tma_load_2d(stage + kABytes, &p.maps[grp.b0_map], &full_bar[s], kb * kElemsPerRow, b_row);
+            tma_load_2d(stage + kABytes + kBBoxBytes, &p.maps[grp.b1_map], &full_bar[s], kb * kElemsPerRow,
+                        b_row + grp.b1_row_off);
+          }
         }
       }
     }
   } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      constexpr uint32_t idesc = umma_idesc<kFp8>(kBlockM, kBlockN);
+    // ------------------------------------------------------------------ MMA issuer (leader CTA only)
+    if (lane == 0 && cta_rank == 0) {
+      constexpr uint32_t idesc = umma_idesc<kFp8>(kTileM, kBlockN);
       uint32_t it = 0, tile_count = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tile_count) {
+      for (int t = unit; t < total_tiles && ok; t += n_units, ++tile_count) {
         int g, m_tile, n_tile;
         decode(t, g, m_tile, n_tile);
         const int kb_count = p.groups[g].k_blocks;
@@ -219,27 +260,52 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
             break;
           }
           tc_fence_after_sync();
+          if (p.exp_mode & 2) {
+            mbar_arrive(&empty_bar[s]);
+            if constexpr (kPair) mbar_arrive_cluster(mapa_shared(smem_u32(&empty_bar[s]), 1));
+            continue;
+          }
           const uint32_t a_addr = smem_u32(smem + static_cast<size_t>(s) * kStageBytes);
           const uint64_t a_desc = umma_desc_k_sw128(a_addr);
           const uint64_t b_desc = umma_desc_k_sw128(a_addr + kABytes);
 #pragma unroll
           for (int k = 0; k < kRowBytes / 32; ++k) {
             // every MMA consumes 32 bytes of K per row: advance the start address by 32 B (2 units of 16 B)
-            umma_ss<kFp8>(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+            if constexpr (kPair) umma_ss_pair<kFp8>(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+            else umma_ss<kFp8>(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
           }
-          umma_commit(&empty_bar[s]);   // frees the stage once these MMAs have read it
+          // free the stage, in both CTAs, once these MMAs have read it
+          if constexpr (kPair) {
+            const uint32_t e_local = smem_u32(&empty_bar[s]);
+            umma_commit_pair(mapa_shared(e_local, 0));
+            if (!(p.exp_mode & 16)) umma_commit_pair(mapa_shared(e_local, 1));
+          } else {
+            umma_commit(&empty_bar[s]);
+          }
         }
-        if (ok) umma_commit(&tmem_full_bar[as]);
+        if (ok && (p.exp_mode & 2)) {
+          mbar_arrive(&tmem_full_bar[as]);
+          if constexpr (kPair) mbar_arrive_cluster(mapa_shared(smem_u32(&tmem_full_bar[as]), 1));
+        } else if (ok) {
+          if constexpr (kPair) {
+            const uint32_t f_local = smem_u32(&tmem_full_bar[as]);
+            umma_commit_pair(mapa_shared(f_local, 0));
+            umma_commit_pair(mapa_shared(f_local, 1));
+          } else {
+            umma_commit(&tmem_full_bar[as]);
+          }
+        }
       }
       // make sure nothing issued by this thread is still running before TMEM is released
-      umma_commit(&drain_bar);
+      if constexpr (kPair) umma_commit_pair(mapa_shared(smem_u32(&drain_bar), 0));
+      else umma_commit(&drain_bar);
       mbar_wait(&drain_bar, 0, abort_ptr);
     }
   } else {
-    // ------------------------------------------------------------------ epilogue (4 warps)
+    // ------------------------------------------------------------------ epilogue (4 warps per CTA)
     const int quarter = warp & 3;   // TMEM lanes this warp may read: [32*quarter, 32*quarter + 32)
     uint32_t tile_count = 0;
-    for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++tile_count) {
+    for (int t = unit; t < total_tiles; t += n_units, ++tile_count) {
       int g, m_tile, n_tile;
       decode(t, g, m_tile, n_tile);
       const GemmGroup& grp = p.groups[g];
@@ -253,8 +319,8 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
       }
       tc_fence_after_sync();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + as * kBlockN;
-      const int row = s_row_base[g] + m_tile * kBlockM + quarter * 32 + lane;
-      const bool valid = row < s_row_limit[g];
+      const int row = s_row_base[g] + m_tile * kTileM + static_cast<int>(cta_rank) * kBlockM + quarter * 32 + lane;
+      const bool valid = (row < s_row_limit[g]) && !(p.exp_mode & 8);
 
       float alpha0 = 1.f, alpha1 = 1.f, out_inv = 1.f;
       bool out_scaled = false;
@@ -265,7 +331,8 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
         if (kSwiglu && grp.out_scale) { out_inv = round_bf16(1.0f / __ldg(grp.out_scale)); out_scaled = true; }
       }
 
-      if constexpr (kSwiglu) {
+      if (p.exp_mode & 4) {
+      } else if constexpr (kSwiglu) {
         const long long col0 = static_cast<long long>(n_tile) * 128;
 #pragma unroll 1
         for (int c = 0; c < 4; ++c) {
@@ -327,8 +394,13 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
           }
         }
       }
+      // hand the accumulator stage back to the MMA thread of the leader CTA: one arrival per warp
       tc_fence_before_sync();
-      mbar_arrive(&tmem_empty_bar[as]);
+      __syncwarp();
+      if (lane == 0) {
+        if constexpr (kPair) mbar_arrive_cluster(mapa_shared(smem_u32(&tmem_empty_bar[as]), 0));
+        else mbar_arrive(&tmem_empty_bar[as]);
+      }
     }
   }
 
@@ -340,10 +412,12 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
     while (clock64() - t0 < 2000000LL) __nanosleep(1000);
   }
   tc_fence_before_sync();
-  __syncthreads();
+  if constexpr (kPair) cluster_sync_all();    // neither CTA may leave while its peer can still touch it
+  else __syncthreads();
   if (warp == 1) {
     tc_fence_after_sync();
-    tmem_dealloc(tmem_base, kTmemCols);
+    if constexpr (kPair) tmem_dealloc_pair(tmem_base, kTmemCols);
+    else tmem_dealloc(tmem_base, kTmemCols);
   }
 }
 
@@ -399,19 +473,52 @@ static int device_sm_count(int* sms) {
   return COMFY_MOE_OK;
 }
 
-template <bool kFp8, bool kSwiglu>
-static int launch_gemm(const GemmParams& params, int64_t max_tiles, int sms, cudaStream_t stream) {
+// CTAs per tile.  Both variants give the same results and, as measured on B200 under its power cap, the same
+// speed (the pair moves a third less data from L2 but its MMA stream runs at lower utilisation), so the
+// simpler single-CTA tile is the default; COMFY_B200_GEMM_CTAS=2 selects the SM-pair variant.
+static int gemm_ctas() {
+  static int ctas = 0;
+  if (ctas == 0) {
+    const char* env = getenv("COMFY_B200_GEMM_CTAS");
+    ctas = (env && env[0] == '2') ? 2 : 1;
+  }
+  return ctas;
+}
+
+template <bool kFp8, bool kSwiglu, int kCtas>
+static int launch_gemm_impl(const GemmParams& params, int64_t max_tiles, int sms, cudaStream_t stream) {
+  auto kernel = grouped_gemm_kernel<kFp8, kSwiglu, kCtas>;
+  constexpr size_t smem = GemmShape<kCtas>::kSmemBytes;
   static bool configured = false;
   if (!configured) {
-    if (cudaFuncSetAttribute(grouped_gemm_kernel<kFp8, kSwiglu>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             static_cast<int>(kGemmSmemBytes)) != cudaSuccess)
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
       return COMFY_MOE_ECUDA;
     configured = true;
   }
-  const int grid = static_cast<int>(max_tiles < sms ? max_tiles : sms);
-  if (grid <= 0) return COMFY_MOE_OK;
-  grouped_gemm_kernel<kFp8, kSwiglu><<<grid, kGemmThreads, kGemmSmemBytes, stream>>>(params);
+  int64_t units = sms / kCtas;
+  if (max_tiles < units) units = max_tiles;
+  if (units <= 0) return COMFY_MOE_OK;
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(static_cast<unsigned>(units * kCtas), 1, 1);
+  cfg.blockDim = dim3(kGemmThreads, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = kCtas;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (cudaLaunchKernelEx(&cfg, kernel, params) != cudaSuccess) return COMFY_MOE_ECUDA;
   return check_launch();
+}
+
+template <bool kFp8, bool kSwiglu>
+static int launch_gemm(const GemmParams& params, int64_t tiles_single, int64_t tiles_pair, int sms, cudaStream_t stream) {
+  if (gemm_ctas() == 1) return launch_gemm_impl<kFp8, kSwiglu, 1>(params, tiles_single, sms, stream);
+  return launch_gemm_impl<kFp8, kSwiglu, 2>(params, tiles_pair, sms, stream);
 }
 
 }  // namespace comfy_b200
@@ -446,7 +553,8 @@ extern "C" int comfy_moe_grouped_swiglu(int w_dtype, int n_experts, const ComfyM
   p1.row_start = p2.row_start = row_start;
   p1.row_count = p2.row_count = row_count;
   p1.status = p2.status = status;
-  int64_t tiles1 = 0, tiles2 = 0;
+  { const char* env = getenv("COMFY_B200_GEMM_EXP"); p1.exp_mode = p2.exp_mode = env ? atoi(env) : 0; }
+  int64_t tiles1[2] = {0, 0}, tiles2[2] = {0, 0};   // upper bounds on tiles, [0] 128-row tiles, [1] 256-row tiles
   int n_maps1 = 0, n_maps2 = 0, g = 0;
 
   int hidden_routed = 0;
@@ -459,7 +567,9 @@ extern "C" int comfy_moe_grouped_swiglu(int w_dtype, int n_experts, const ComfyM
     if ((rc = make_map(&p1.maps[n_maps1], x_perm, fp8, rows_cap, dim, dim)) != COMFY_MOE_OK) return rc;
     if ((rc = make_map(&p2.maps[n_maps2], h_perm, fp8, rows_cap, hidden_routed, hidden_routed)) != COMFY_MOE_OK) return rc;
     const int a1 = n_maps1++, a2 = n_maps2++;
-    const int64_t m_tiles_cap = (rows_cap + kBlockM - 1) / kBlockM + n_experts;   // every group may end in a partial tile
+    // every group may end in a partial tile
+    const int64_t m_tiles_cap[2] = {(rows_cap + kBlockM - 1) / kBlockM + n_experts,
+                                    (rows_cap + 2 * kBlockM - 1) / (2 * kBlockM) + n_experts};
     for (int e = 0; e < n_experts; ++e, ++g) {
       const ComfyMoeFfnWeights& w = h_experts[e];
       if (!w.w1 || !w.w2 || !w.w3) return COMFY_MOE_EINVAL;
@@ -478,8 +588,10 @@ extern "C" int comfy_moe_grouped_swiglu(int w_dtype, int n_experts, const ComfyM
       g2.scale_a = w.scale_in2; g2.scale_b0 = w.scale_w2; g2.scale_b1 = w.scale_w2; g2.out_scale = nullptr;
       n_maps1 += 2; n_maps2 += 1;
     }
-    tiles1 += m_tiles_cap * (hidden_routed / 128);
-    tiles2 += m_tiles_cap * (dim / kBlockN);
+    for (int v = 0; v < 2; ++v) {
+      tiles1[v] += m_tiles_cap[v] * (hidden_routed / 128);
+      tiles2[v] += m_tiles_cap[v] * (dim / kBlockN);
+    }
   }
   if (has_shared) {
     const ComfyMoeFfnWeights& w = *h_shared;
@@ -500,18 +612,21 @@ extern "C" int comfy_moe_grouped_swiglu(int w_dtype, int n_experts, const ComfyM
     g2.k_blocks = w.hidden / k_elems; g2.n_tiles = dim / kBlockN; g2.routed_index = -1; g2.static_rows = n_tokens;
     g2.out = y_shared; g2.ld_out = dim;
     g2.scale_a = w.scale_in2; g2.scale_b0 = w.scale_w2; g2.scale_b1 = w.scale_w2; g2.out_scale = nullptr;
-    const int64_t m_tiles = (n_tokens + kBlockM - 1) / kBlockM;
-    tiles1 += m_tiles * (w.hidden / 128);
-    tiles2 += m_tiles * (dim / kBlockN);
+    for (int v = 0; v < 2; ++v) {
+      const int64_t tile_m = kBlockM * (v + 1);
+      const int64_t m_tiles = (n_tokens + tile_m - 1) / tile_m;
+      tiles1[v] += m_tiles * (w.hidden / 128);
+      tiles2[v] += m_tiles * (dim / kBlockN);
+    }
     ++g;
   }
   p1.num_groups = p2.num_groups = g;
 
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (fp8) {
-    if ((rc = launch_gemm<true, true>(p1, tiles1, sms, s)) != COMFY_MOE_OK) return rc;
-    return launch_gemm<true, false>(p2, tiles2, sms, s);
+    if ((rc = launch_gemm<true, true>(p1, tiles1[0], tiles1[1], sms, s)) != COMFY_MOE_OK) return rc;
+    return launch_gemm<true, false>(p2, tiles2[0], tiles2[1], sms, s);
   }
-  if ((rc = launch_gemm<false, true>(p1, tiles1, sms, s)) != COMFY_MOE_OK) return rc;
-  return launch_gemm<false, false>(p2, tiles2, sms, s);
+  if ((rc = launch_gemm<false, true>(p1, tiles1[0], tiles1[1], sms, s)) != COMFY_MOE_OK) return rc;
+  return launch_gemm<false, false>(p2, tiles2[0], tiles2[1], sms, s);
 }
