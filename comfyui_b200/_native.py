@@ -13,11 +13,12 @@ from . import build as _build
 
 ABI_VERSION = 1
 
-OK, EINVAL, EUNSUPPORTED, ECUDA, ETIMEOUT, EDEVICE = range(6)
+OK, EINVAL, EUNSUPPORTED, ECUDA, ETIMEOUT, EDEVICE, ETOOLARGE = range(7)
 BF16, FP32, FP8_E4M3 = 0, 1, 2
 ROW_ALIGN = 128
 TOKENS_PER_BLOCK = 32
 MAX_EXPERTS = 8
+STATIC_MAX_TOKENS = 131072
 
 EXPORTS = (
     "comfy_moe_abi_version",
@@ -27,6 +28,7 @@ EXPORTS = (
     "comfy_moe_route_count",
     "comfy_moe_route_plan",
     "comfy_moe_permute",
+    "comfy_moe_route_static",
     "comfy_moe_grouped_swiglu",
     "comfy_moe_combine",
     "comfy_moe_forward",
@@ -132,6 +134,10 @@ def load(build_if_missing: bool = False) -> ctypes.CDLL:
     lib.comfy_moe_permute.argtypes = [
         c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
         c_void_p, c_void_p,
+    ]
+    lib.comfy_moe_route_static.argtypes = [
+        c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+        c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
     ]
     lib.comfy_moe_grouped_swiglu.argtypes = [
         c_int, c_int, POINTER(FfnWeights), POINTER(FfnWeights), c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p,

@@ -11,6 +11,8 @@ extern "C" const char* comfy_moe_error_string(int code) {
     case COMFY_MOE_ECUDA: return "a CUDA runtime or driver call failed";
     case COMFY_MOE_ETIMEOUT: return "a bounded device-side wait ran out";
     case COMFY_MOE_EDEVICE: return "device is not sm_100 or the driver lacks tensor-map support";
+    case COMFY_MOE_ETOOLARGE:
+      return "token count exceeds COMFY_MOE_STATIC_MAX_TOKENS, the capacity of the library's built-in scratch array";
     default: return "unknown error code";
   }
 }

@@ -429,3 +429,55 @@ extern "C" int comfy_moe_permute(const void* x, const int32_t* topk_idx, const i
   }
   return check_launch();
 }
+
+// ------------------------------------------------------------------------------------------------
+// Routing without caller-provided scratch.  The per-block counts and offsets that link the gate, the
+// plan and the permutation live in a fixed device array that is part of the library image, so a
+// caller that cannot allocate device memory passes only inputs and outputs.
+// ------------------------------------------------------------------------------------------------
+namespace comfy_b200 {
+constexpr int kStaticMaxBlocks = COMFY_MOE_STATIC_MAX_TOKENS / kTokensPerBlock;
+// [0]: per-block counts, [1]: per-block offsets.  256 KB, held by every GPU that loads the library.
+static __device__ __align__(256) int32_t g_route_scratch[2][kStaticMaxBlocks * kMaxExperts];
+
+// Device address of the array on the current device.  In host code the symbol's name is only a
+// handle; the address kernels can use has to be asked for, once per device, with that device current.
+static int route_scratch_address(int32_t** out) {
+  constexpr int kMaxDevices = 64;
+  static int32_t* cached[kMaxDevices] = {nullptr};
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess) return COMFY_MOE_ECUDA;
+  if (dev < 0 || dev >= kMaxDevices) return COMFY_MOE_EUNSUPPORTED;
+  if (cached[dev] == nullptr) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_route_scratch) != cudaSuccess || p == nullptr) return COMFY_MOE_ECUDA;
+    cached[dev] = static_cast<int32_t*>(p);
+  }
+  *out = cached[dev];
+  return COMFY_MOE_OK;
+}
+}  // namespace comfy_b200
+
+extern "C" int comfy_moe_route_static(const void* x, const void* w_gate, int w_dtype, int n_tokens, int dim,
+                                      int n_experts, int top_k, int act_dtype, const float* act_scale,
+                                      int32_t* topk_idx, float* topk_weight, int32_t* expert_counts,
+                                      int32_t* expert_offsets, void* x_perm, void* x_q, const float* x_q_scale,
+                                      int32_t* row_map, int32_t* neartie_count, void* stream) {
+  if (n_tokens < 0) return COMFY_MOE_EINVAL;
+  if (n_tokens > COMFY_MOE_STATIC_MAX_TOKENS) return COMFY_MOE_ETOOLARGE;   // the fixed scratch is too small
+  if (n_experts < 1 || n_experts > kMaxExperts) return COMFY_MOE_EINVAL;
+  int32_t* scratch = nullptr;
+  int rc = route_scratch_address(&scratch);
+  if (rc != COMFY_MOE_OK) return rc;
+  int32_t* block_counts = scratch;
+  int32_t* block_offsets = scratch + kStaticMaxBlocks * kMaxExperts;
+  // Every scratch word read below is written earlier in this same call (the gate overwrites the counts of
+  // all blocks in use, the plan all their offsets), so nothing left by a previous call is ever consumed.
+  rc = comfy_moe_gate_topk(x, w_gate, w_dtype, n_tokens, dim, n_experts, top_k, topk_idx, topk_weight, block_counts,
+                           neartie_count, nullptr, 1e-6f, stream);
+  if (rc != COMFY_MOE_OK) return rc;
+  rc = comfy_moe_route_plan(block_counts, n_tokens, n_experts, block_offsets, expert_counts, expert_offsets, stream);
+  if (rc != COMFY_MOE_OK) return rc;
+  return comfy_moe_permute(x, topk_idx, block_offsets, expert_offsets, n_tokens, dim, n_experts, act_dtype, act_scale,
+                           x_perm, x_q, x_q_scale, row_map, stream);
+}

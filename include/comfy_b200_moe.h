@@ -35,6 +35,7 @@ extern "C" {
 #define COMFY_MOE_ECUDA 3         /* a CUDA runtime or driver call failed (launch, encode)       */
 #define COMFY_MOE_ETIMEOUT 4      /* a bounded device-side wait ran out (see comfy_moe_read_status) */
 #define COMFY_MOE_EDEVICE 5       /* not an sm_100 device, or the driver lacks tensor-map support */
+#define COMFY_MOE_ETOOLARGE 6     /* more tokens than the library's built-in scratch array can serve */
 
 /* Element types for weights and for the activations fed to the expert GEMMs. */
 #define COMFY_MOE_BF16 0
@@ -46,6 +47,8 @@ extern "C" {
 /* Tokens handled by one thread block of the gate / permute kernels (fixes the block-count scratch size). */
 #define COMFY_MOE_TOKENS_PER_BLOCK 32
 #define COMFY_MOE_MAX_EXPERTS 8
+/* Largest token count comfy_moe_route_static accepts (its scratch is a fixed array inside the library). */
+#define COMFY_MOE_STATIC_MAX_TOKENS 131072
 
 int comfy_moe_abi_version(void);
 const char* comfy_moe_error_string(int code);
@@ -101,6 +104,30 @@ int comfy_moe_permute(const void* x, const int32_t* topk_idx, const int32_t* blo
                       const int32_t* expert_offsets, int n_tokens, int dim, int n_experts, int act_dtype,
                       const float* act_scale, void* x_perm, void* x_q, const float* x_q_scale,
                       int32_t* row_map, void* stream);
+
+/* ---- gate + routing plan + permutation for callers that cannot allocate device memory -----------------
+ * (No counterpart in the reference: it has no allocation-free mode.)
+ * Some hosts of this library may not call cudaMalloc or any allocator between set-up and tear-down: real-time
+ * loops that reserve all their device memory at start-up, plugins that are handed a fixed device arena by their
+ * host application, processes whose whole device-memory budget is committed before the first frame.  The three
+ * routing entry points above need two scratch arrays (block_counts,
+ * block_offsets) from the caller; this one does the same three steps with that scratch in a fixed 256 KB device
+ * array that is part of the library, so only inputs and outputs are passed.  It calls no allocator of any kind.
+ *   inputs    x, w_gate, w_dtype, act_dtype, act_scale, x_q_scale          as comfy_moe_gate_topk / comfy_moe_permute
+ *   outputs   topk_idx, topk_weight, expert_counts, expert_offsets, x_perm, x_q (may be NULL), row_map,
+ *             neartie_count (may be NULL; caller zeroes)                    exactly what the three calls produce
+ * Limits and rules:
+ *   - n_tokens <= COMFY_MOE_STATIC_MAX_TOKENS, else COMFY_MOE_ETOOLARGE (nothing is launched);
+ *   - the first call on each device looks up the array's device address (one cudaGetSymbolAddress); make that
+ *     first call outside any stream capture;
+ *   - all calls on a device share the one array, so two calls that can overlap on the GPU (different streams
+ *     without an ordering between them) race; keep them on one stream or order them with events.  Nothing in the
+ *     array has to be cleared between calls: every word a call reads it has written itself.
+ */
+int comfy_moe_route_static(const void* x, const void* w_gate, int w_dtype, int n_tokens, int dim, int n_experts,
+                           int top_k, int act_dtype, const float* act_scale, int32_t* topk_idx, float* topk_weight,
+                           int32_t* expert_counts, int32_t* expert_offsets, void* x_perm, void* x_q,
+                           const float* x_q_scale, int32_t* row_map, int32_t* neartie_count, void* stream);
 
 /* One SwiGLU feed-forward's weights (FeedForwardSwiGLU, model.py:233-238). */
 typedef struct ComfyMoeFfnWeights {
