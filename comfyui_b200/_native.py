@@ -31,6 +31,7 @@ EXPORTS = (
     "comfy_moe_route_static",
     "comfy_moe_grouped_swiglu",
     "comfy_moe_combine",
+    "comfy_moe_combine_partials",
     "comfy_moe_forward",
     "comfy_moe_read_status",
 )
@@ -144,6 +145,8 @@ def load(build_if_missing: bool = False) -> ctypes.CDLL:
         c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
     ]
     lib.comfy_moe_combine.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]
+    lib.comfy_moe_combine_partials.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p,
+                                               c_void_p]
     lib.comfy_moe_forward.argtypes = [POINTER(Layer), POINTER(Workspace), c_void_p, c_int, c_void_p, c_void_p]
     lib.comfy_moe_read_status.argtypes = [c_void_p, c_void_p, POINTER(c_int32)]
     for name in EXPORTS:

@@ -11,8 +11,12 @@ namespace comfy_b200 {
 constexpr int kCombineMaxThreads = 512;          // dim / 8 threads per block: dim <= 4096
 constexpr int kTokensPerCombineBlock = 8;
 
+// kTwo: every row has two partial results (an expert whose hidden dimension is split over two GPUs); their sum,
+// rounded to bf16, stands in for the expert output the reference rounds once.
+template <bool kTwo>
 __global__ void __launch_bounds__(kCombineMaxThreads)
-combine_kernel(const __nv_bfloat16* __restrict__ y_perm, const int32_t* __restrict__ row_map,
+combine_kernel(const __nv_bfloat16* __restrict__ y_perm, const __nv_bfloat16* __restrict__ y_perm_b,
+               const int32_t* __restrict__ row_map,
                const float* __restrict__ topk_weight, const __nv_bfloat16* __restrict__ y_shared, int n_tokens,
                int dim, __nv_bfloat16* __restrict__ out) {
   constexpr int kTok = 4;
@@ -23,11 +27,13 @@ combine_kernel(const __nv_bfloat16* __restrict__ y_perm, const int32_t* __restri
     const int t0 = block_tok0 + base;
     if (t0 >= n_tokens) break;
     uint4 va[kTok], vb[kTok], vs[kTok];
+    uint4 va2[kTwo ? kTok : 1], vb2[kTwo ? kTok : 1];
     float w0[kTok], w1[kTok];
 #pragma unroll
     for (int i = 0; i < kTok; ++i) {
       const int t = t0 + i;
       va[i] = vb[i] = vs[i] = make_uint4(0, 0, 0, 0);
+      if constexpr (kTwo) va2[i] = vb2[i] = make_uint4(0, 0, 0, 0);
       w0[i] = w1[i] = 0.f;
       if (t < n_tokens) {
         // a negative row means "this slot was routed nowhere": it contributes zero
@@ -36,6 +42,10 @@ combine_kernel(const __nv_bfloat16* __restrict__ y_perm, const int32_t* __restri
         w1[i] = round_bf16(__ldg(topk_weight + 2 * t + 1));
         if (r0 >= 0) va[i] = ld_nc_u4(reinterpret_cast<const uint4*>(y_perm + static_cast<size_t>(r0) * dim) + tid);
         if (r1 >= 0) vb[i] = ld_nc_u4(reinterpret_cast<const uint4*>(y_perm + static_cast<size_t>(r1) * dim) + tid);
+        if constexpr (kTwo) {
+          if (r0 >= 0) va2[i] = ld_nc_u4(reinterpret_cast<const uint4*>(y_perm_b + static_cast<size_t>(r0) * dim) + tid);
+          if (r1 >= 0) vb2[i] = ld_nc_u4(reinterpret_cast<const uint4*>(y_perm_b + static_cast<size_t>(r1) * dim) + tid);
+        }
         if (y_shared) vs[i] = ld_nc_u4(reinterpret_cast<const uint4*>(y_shared + static_cast<size_t>(t) * dim) + tid);
       }
     }
@@ -47,6 +57,13 @@ combine_kernel(const __nv_bfloat16* __restrict__ y_perm, const int32_t* __restri
       unpack_bf16x8(va[i], fa);
       unpack_bf16x8(vb[i], fb);
       unpack_bf16x8(vs[i], fs);
+      if constexpr (kTwo) {
+        float ga[8], gb[8];
+        unpack_bf16x8(va2[i], ga);
+        unpack_bf16x8(vb2[i], gb);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) { fa[k] = round_bf16(fa[k] + ga[k]); fb[k] = round_bf16(fb[k] + gb[k]); }
+      }
 #pragma unroll
       for (int k = 0; k < 8; ++k) {
         const float p0 = round_bf16(w0[i] * fa[k]);
@@ -64,17 +81,37 @@ combine_kernel(const __nv_bfloat16* __restrict__ y_perm, const int32_t* __restri
 
 using namespace comfy_b200;
 
-extern "C" int comfy_moe_combine(const void* y_perm, const int32_t* row_map, const float* topk_weight,
-                                 const void* y_shared, int n_tokens, int dim, void* out, void* stream) {
+static int launch_combine(const void* y_perm, const void* y_perm_b, const int32_t* row_map, const float* topk_weight,
+                          const void* y_shared, int n_tokens, int dim, void* out, void* stream) {
   if (n_tokens < 0 || dim <= 0) return COMFY_MOE_EINVAL;
   if (n_tokens == 0) return COMFY_MOE_OK;
   if (!y_perm || !row_map || !topk_weight || !out) return COMFY_MOE_EINVAL;
-  if (!aligned16(y_perm) || !aligned16(out) || (y_shared && !aligned16(y_shared))) return COMFY_MOE_EINVAL;
+  if (!aligned16(y_perm) || !aligned16(out) || (y_shared && !aligned16(y_shared)) || (y_perm_b && !aligned16(y_perm_b)))
+    return COMFY_MOE_EINVAL;
   if ((dim & 7) != 0 || (dim >> 3) > kCombineMaxThreads) return COMFY_MOE_EUNSUPPORTED;
   const int threads = ((dim >> 3) + 31) & ~31;
   const int blocks = (n_tokens + kTokensPerCombineBlock - 1) / kTokensPerCombineBlock;
-  combine_kernel<<<blocks, threads, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(y_perm), row_map, topk_weight, static_cast<const __nv_bfloat16*>(y_shared),
-      n_tokens, dim, static_cast<__nv_bfloat16*>(out));
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const __nv_bfloat16* ya = static_cast<const __nv_bfloat16*>(y_perm);
+  const __nv_bfloat16* yb = static_cast<const __nv_bfloat16*>(y_perm_b);
+  const __nv_bfloat16* ys = static_cast<const __nv_bfloat16*>(y_shared);
+  if (yb)
+    combine_kernel<true><<<blocks, threads, 0, s>>>(ya, yb, row_map, topk_weight, ys, n_tokens, dim,
+                                                    static_cast<__nv_bfloat16*>(out));
+  else
+    combine_kernel<false><<<blocks, threads, 0, s>>>(ya, nullptr, row_map, topk_weight, ys, n_tokens, dim,
+                                                     static_cast<__nv_bfloat16*>(out));
   return check_launch();
+}
+
+extern "C" int comfy_moe_combine(const void* y_perm, const int32_t* row_map, const float* topk_weight,
+                                 const void* y_shared, int n_tokens, int dim, void* out, void* stream) {
+  return launch_combine(y_perm, nullptr, row_map, topk_weight, y_shared, n_tokens, dim, out, stream);
+}
+
+extern "C" int comfy_moe_combine_partials(const void* y_perm_a, const void* y_perm_b, const int32_t* row_map,
+                                          const float* topk_weight, const void* y_shared, int n_tokens, int dim,
+                                          void* out, void* stream) {
+  if (!y_perm_b) return COMFY_MOE_EINVAL;
+  return launch_combine(y_perm_a, y_perm_b, row_map, topk_weight, y_shared, n_tokens, dim, out, stream);
 }

@@ -1,0 +1,244 @@
+"""Expert-parallel execution of one HiDream MoE feed-forward across the GPUs of one node.
+
+The reference is single-process and has no counterpart to this file; the partitioning follows from the layer
+(``comfy/ldm/hidream/model.py:287-346``): rows are independent, the only coupling is that a token's two experts may
+live on another GPU.
+
+* Tokens are data-parallel: every rank owns its own ``[n, D]`` slice, runs the gate, the shared expert (weights
+  replicated) and the final combine on it.
+* Routed experts are expert-parallel.  With E experts on G ranks: G <= E -> E/G consecutive experts per rank;
+  G = 2E -> expert e lives on ranks 2e and 2e+1, each holding one half of the hidden dimension (rows of w1/w3,
+  columns of w2, passed to the kernels as strided views without copying); the two partial outputs are summed by the
+  token's owner.
+* One exchange each way.  After the local gate / plan / permutation every rank all-gathers its E-bin histogram
+  (the one host synchronisation of the call, like the reference's ``bincount().cpu()``), then rows travel as
+  point-to-point transfers batched into one NCCL group (an all-to-all with exact, per-pair row counts).  The
+  permutation kernel already wrote the rows grouped by expert, i.e. by destination, so the send side needs no
+  packing; received rows land in local HBM ordered (local expert, source rank), which the grouped GEMM consumes in
+  place as one row range per local expert.  Results return the same way and the combine kernel reads them through
+  the row map it already has.  No kernel reads peer memory.
+
+``ExpertParallelMoE`` contains only this host logic.  The arithmetic is delegated to a ``kernels`` object:
+``CudaKernels`` (the sm_100a kernels through the C ABI) in production; the CPU tests plug in a stand-in so the
+exchange logic can run under gloo.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import List, Optional, Sequence, Tuple
+
+import torch
+import torch.distributed as dist
+
+
+@dataclass
+class Placement:
+    """Which routed experts (and which hidden slice of them) a rank computes."""
+
+    world: int
+    n_experts: int
+
+    def __post_init__(self):
+        g, e = self.world, self.n_experts
+        if g <= e:
+            if e % g:
+                raise ValueError(f"{e} experts do not divide over {g} ranks")
+            self.experts_per_rank, self.hidden_splits = e // g, 1
+        else:
+            if g % e:
+                raise ValueError(f"{g} ranks do not divide over {e} experts")
+            self.experts_per_rank, self.hidden_splits = 1, g // e
+
+    def local_experts(self, rank: int) -> List[int]:
+        first = (rank // self.hidden_splits) * self.experts_per_rank
+        return list(range(first, first + self.experts_per_rank))
+
+    def hidden_part(self, rank: int) -> int:
+        return rank % self.hidden_splits
+
+    def owners(self, expert: int) -> List[int]:
+        first = (expert // self.experts_per_rank) * self.hidden_splits
+        return list(range(first, first + self.hidden_splits))
+
+
+def exchange_plan(counts: Sequence[Sequence[int]], rank: int, place: Placement):
+    """Pure host arithmetic of one exchange.  ``counts[s][e]`` = routed slots of source rank s for expert e.
+
+    Returns (recv_start, recv_rows, group_start, group_count):
+      recv_start[j][s]  first row, in this rank's receive buffer, of the rows source s sends for local expert j;
+      recv_rows         total rows received;
+      group_start[j], group_count[j]  the row range local expert j computes on (all sources, contiguous).
+    """
+    local = place.local_experts(rank)
+    recv_start, group_start, group_count = [], [], []
+    row = 0
+    for e in local:
+        group_start.append(row)
+        starts = []
+        for s in range(place.world):
+            starts.append(row)
+            row += int(counts[s][e])
+        recv_start.append(starts)
+        group_count.append(row - group_start[-1])
+    return recv_start, row, group_start, group_count
+
+
+class CudaKernels:
+    """The sm_100a kernels behind the C ABI, bound to one loaded MOEFeedForwardSwiGLU module."""
+
+    def __init__(self, module, place: Placement, rank: int):
+        from . import moe_ops, ops
+
+        self.M = moe_ops
+        self.module = module
+        dev = module.gate.weight.device
+        self.gate_w = module.gate.weight.detach()
+        self.n_experts = len(module.experts)
+        self.shared = ops._ffn_pack(module.shared_experts, dev, moe_ops)
+        if self.shared is None:
+            raise ValueError("shared expert weights are not eligible for the sm_100a kernels")
+        part, splits = place.hidden_part(rank), place.hidden_splits
+        self.local = []
+        for e in place.local_experts(rank):
+            ffn = module.experts[e]
+            full = ops._ffn_pack(ffn, dev, moe_ops)
+            if full is None:
+                raise ValueError(f"expert {e} weights are not eligible for the sm_100a kernels")
+            if splits == 1:
+                self.local.append(full)
+            else:
+                h = full.hidden // splits
+                if h % 128:
+                    raise ValueError("hidden slice must be a multiple of 128")
+                lo, hi = part * h, (part + 1) * h
+                self.local.append(moe_ops.FfnPack(full.w1[lo:hi], full.w3[lo:hi], full.w2[:, lo:hi],
+                                                  scale_w1=full.scale_w1, scale_w3=full.scale_w3,
+                                                  scale_w2=full.scale_w2, scale_in13=full.scale_in13,
+                                                  scale_in2=full.scale_in2))
+        self.fp8 = self.shared.w1.dtype == torch.float8_e4m3fn
+        if self.fp8:
+            raise ValueError("expert-parallel execution covers bf16 weights")
+
+    launches_local = 3      # gate, plan, permutation
+
+    def route(self, x):
+        M = self.M
+        n = x.shape[0]
+        idx, w, block_counts, _, _ = M.gate_topk(x, self.gate_w)
+        block_offsets, counts, offsets = M.route_plan(block_counts, n, self.n_experts)
+        x_perm, row_map, _ = M.permute(x, idx, block_offsets, offsets, self.n_experts)
+        return idx, w, counts, offsets, x_perm, row_map
+
+    def shared_expert(self, x):
+        _, y, _, _ = self.M.grouped_swiglu([], self.shared, None, None, None, x, check_status=False)
+        return y
+
+    def routed_experts(self, rows, group_start, group_count):
+        dev = rows.device
+        start = torch.tensor(group_start, dtype=torch.int32).to(dev, non_blocking=True)
+        count = torch.tensor(group_count, dtype=torch.int32).to(dev, non_blocking=True)
+        y, _, _, _ = self.M.grouped_swiglu(self.local, None, start, count, rows, None, check_status=False)
+        return y
+
+    def combine(self, partials, row_map, w, y_shared):
+        return self.M.combine(partials[0], row_map, w, y_shared, y_perm_b=partials[1] if len(partials) > 1 else None)
+
+    def empty_rows(self, rows, dim, like):
+        return torch.empty((max(rows, 1), dim), dtype=like.dtype, device=like.device)
+
+
+class ExpertParallelMoE:
+    """Callable: ``out = ep(x)`` with x this rank's tokens ``[B, S, D]`` or ``[n, D]`` (bf16 on the GPU)."""
+
+    def __init__(self, module, group=None, kernels=None):
+        self.group = group if group is not None else dist.group.WORLD
+        self.rank = dist.get_rank(self.group)
+        self.world = dist.get_world_size(self.group)
+        self.n_experts = len(module.experts)
+        self.place = Placement(self.world, self.n_experts)
+        self.kernels = kernels if kernels is not None else CudaKernels(module, self.place, self.rank)
+        self.last_counts = None          # [world][E] routed slots of the last call, for reporting
+        # gate, plan, permute, shared GEMM x2, routed GEMM x2, combine
+        self.launches_per_step = 8
+
+    # -- communication helpers ------------------------------------------------------------------
+    def _peer(self, r: int) -> int:
+        return dist.get_global_rank(self.group, r) if self.group is not dist.group.WORLD else r
+
+    def _gather_counts(self, counts: torch.Tensor) -> List[List[int]]:
+        flat = torch.empty((self.world * self.n_experts,), dtype=counts.dtype, device=counts.device)
+        dist.all_gather_into_tensor(flat, counts.contiguous(), group=self.group)
+        return flat.view(self.world, self.n_experts).cpu().tolist()      # the one host sync of the call
+
+    def _exchange(self, sends: List[Tuple[torch.Tensor, int]], recvs: List[Tuple[torch.Tensor, int]]):
+        ops = []
+        for t, peer in sends:
+            if t.shape[0]:
+                ops.append(dist.P2POp(dist.isend, t, self._peer(peer), group=self.group))
+        for t, peer in recvs:
+            if t.shape[0]:
+                ops.append(dist.P2POp(dist.irecv, t, self._peer(peer), group=self.group))
+        return dist.batch_isend_irecv(ops) if ops else []
+
+    # -- one layer call -------------------------------------------------------------------------
+    def __call__(self, x: torch.Tensor) -> torch.Tensor:
+        shape = x.shape
+        x2 = x.reshape(-1, shape[-1])
+        k, place, rank = self.kernels, self.place, self.rank
+        dim = x2.shape[1]
+
+        idx, w, counts_dev, offsets_dev, x_perm, row_map = k.route(x2)
+        counts = self._gather_counts(counts_dev)
+        self.last_counts = counts
+        mine = counts[rank]
+        # first row of every expert in my permuted buffer: expert blocks start on multiples of 128 rows
+        my_offset, row = [], 0
+        for e in range(self.n_experts):
+            my_offset.append(row)
+            row += -(-mine[e] // 128) * 128
+
+        recv_start, recv_rows, group_start, group_count = exchange_plan(counts, rank, place)
+        recv = k.empty_rows(recv_rows, dim, x_perm)
+        local = place.local_experts(rank)
+
+        # dispatch: my rows of expert e go to every rank that computes (a slice of) e
+        sends, recvs = [], []
+        for e in range(self.n_experts):
+            rows = x_perm[my_offset[e]: my_offset[e] + mine[e]]
+            for q in place.owners(e):
+                if q != rank:
+                    sends.append((rows, q))
+        for j, e in enumerate(local):
+            for s in range(self.world):
+                dst = recv[recv_start[j][s]: recv_start[j][s] + counts[s][e]]
+                if s == rank:
+                    dst.copy_(x_perm[my_offset[e]: my_offset[e] + mine[e]])
+                else:
+                    recvs.append((dst, s))
+        pending = self._exchange(sends, recvs)
+        y_shared = k.shared_expert(x2)            # overlaps the transfer
+        for h in pending:
+            h.wait()
+
+        y_recv = k.routed_experts(recv, group_start, group_count)
+
+        # return: partial outputs go back to the rows' owners, into buffers laid out like x_perm
+        partials = [k.empty_rows(x_perm.shape[0], dim, y_recv) for _ in range(place.hidden_splits)]
+        sends, recvs = [], []
+        for j, e in enumerate(local):
+            for s in range(self.world):
+                src = y_recv[recv_start[j][s]: recv_start[j][s] + counts[s][e]]
+                if s == rank:
+                    partials[place.hidden_part(rank)][my_offset[e]: my_offset[e] + mine[e]].copy_(src)
+                else:
+                    sends.append((src, s))
+        for e in range(self.n_experts):
+            for q in place.owners(e):
+                if q != rank:
+                    dst = partials[place.hidden_part(q)][my_offset[e]: my_offset[e] + mine[e]]
+                    recvs.append((dst, q))
+        for h in self._exchange(sends, recvs):
+            h.wait()
+
+        out = k.combine(partials, row_map, w, y_shared)
+        return out.view(shape)

@@ -299,15 +299,22 @@ def grouped_swiglu(experts: Sequence[FfnPack], shared: Optional[FfnPack], row_st
 
 
 def combine(y_perm: torch.Tensor, row_map: torch.Tensor, topk_weight: torch.Tensor,
-            y_shared: Optional[torch.Tensor], out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """out[t] = bf16(bf16(bf16(w0*y[r0]) + bf16(w1*y[r1])) + y_shared[t])."""
-    _need_cuda(y_perm, row_map, topk_weight, y_shared)
+            y_shared: Optional[torch.Tensor], out: Optional[torch.Tensor] = None,
+            y_perm_b: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[t] = bf16(bf16(bf16(w0*y[r0]) + bf16(w1*y[r1])) + y_shared[t]); with y_perm_b every y is the bf16 sum of
+    two partial results (hidden-split experts)."""
+    _need_cuda(y_perm, row_map, topk_weight, y_shared, y_perm_b)
     n = row_map.shape[0]
     d = y_perm.shape[1]
     if out is None:
         out = torch.empty((n, d), dtype=torch.bfloat16, device=y_perm.device)
-    rc = N.load().comfy_moe_combine(_ptr(y_perm), _ptr(row_map), _ptr(topk_weight), _ptr(y_shared), n, d, _ptr(out),
-                                    _stream())
+    lib = N.load()
+    if y_perm_b is None:
+        rc = lib.comfy_moe_combine(_ptr(y_perm), _ptr(row_map), _ptr(topk_weight), _ptr(y_shared), n, d, _ptr(out),
+                                   _stream())
+    else:
+        rc = lib.comfy_moe_combine_partials(_ptr(y_perm), _ptr(y_perm_b), _ptr(row_map), _ptr(topk_weight),
+                                            _ptr(y_shared), n, d, _ptr(out), _stream())
     N.check("comfy_moe_combine", rc)
     return out
 

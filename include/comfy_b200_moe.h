@@ -172,6 +172,14 @@ int comfy_moe_grouped_swiglu(int w_dtype, int n_groups, const ComfyMoeFfnWeights
 int comfy_moe_combine(const void* y_perm, const int32_t* row_map, const float* topk_weight, const void* y_shared,
                       int n_tokens, int dim, void* out, void* stream);
 
+/* Same, for experts whose hidden dimension is split over two GPUs (no counterpart in the reference, which is
+ * single-GPU): every row has two partial results, y = bf16(y_a + y_b) replaces the expert output the reference
+ * rounds once, then the combine proceeds as above.  Both buffers use the layout row_map refers to.
+ */
+int comfy_moe_combine_partials(const void* y_perm_a, const void* y_perm_b, const int32_t* row_map,
+                               const float* topk_weight, const void* y_shared, int n_tokens, int dim, void* out,
+                               void* stream);
+
 /* Everything one layer call needs, for the fused entry point. */
 typedef struct ComfyMoeLayer {
   int32_t dim;

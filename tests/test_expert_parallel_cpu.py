@@ -1,0 +1,144 @@
+"""Host logic of the expert-parallel layer under gloo on the CPU (world sizes 2 and 4).
+
+The kernels cannot run here, so a CPU stand-in with the same interface (built on the oracle's arithmetic) is
+plugged into ExpertParallelMoE: what is tested is the placement, the count exchange, the split sizes, the
+ordering of the point-to-point transfers, the receive layout handed to the grouped GEMM and the way partial
+results of hidden-split experts come back.
+"""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from comfyui_b200.expert_parallel import ExpertParallelMoE, Placement, exchange_plan
+from oracle import hidream_moe_oracle as O
+
+DIM, HIDDEN_DIM = 128, 512
+
+
+class OracleKernels:
+    """CPU stand-in for CudaKernels: same methods, PyTorch arithmetic with the kernels' rounding points."""
+
+    def __init__(self, layer, place, rank):
+        self.layer, self.place, self.rank = layer, place, rank
+        self.n_experts = layer["gate.weight"].shape[0]
+        self.local = []
+        part, splits = place.hidden_part(rank), place.hidden_splits
+        for e in place.local_experts(rank):
+            w1, w2, w3 = (layer[f"experts.{e}.{k}.weight"] for k in ("w1", "w2", "w3"))
+            h = w1.shape[0] // splits
+            lo, hi = part * h, (part + 1) * h
+            self.local.append({"f.w1.weight": w1[lo:hi], "f.w3.weight": w3[lo:hi], "f.w2.weight": w2[:, lo:hi]})
+
+    def route(self, x):
+        idx, w = O.gate(x.float(), self.layer["gate.weight"].float())
+        idx = idx.sort(dim=1).values.to(torch.int32)      # any fixed pair order will do
+        w = torch.gather(O.gate_scores_fp64(x, self.layer["gate.weight"]).float(), 1, idx.long())
+        flat = idx.flatten().long()
+        counts = torch.bincount(flat, minlength=self.n_experts).to(torch.int32)
+        offsets = torch.zeros(self.n_experts + 1, dtype=torch.int32)
+        for e in range(self.n_experts):
+            offsets[e + 1] = offsets[e] + -(-int(counts[e]) // 128) * 128
+        rows_cap = 2 * x.shape[0] + 128 * self.n_experts
+        x_perm = torch.zeros((rows_cap, x.shape[1]), dtype=x.dtype)
+        row_map = torch.empty_like(flat, dtype=torch.int32)
+        for e in range(self.n_experts):
+            slots = (flat == e).nonzero().flatten()          # ascending slot index: the stable order
+            dest = offsets[e] + torch.arange(slots.numel(), dtype=torch.int32)
+            row_map[slots] = dest
+            x_perm[dest.long()] = x[slots // 2]
+        return idx, w, counts, offsets, x_perm, row_map.view(-1, 2)
+
+    def shared_expert(self, x):
+        return O.swiglu_ffn(x, self.layer, "shared_experts")
+
+    def routed_experts(self, rows, group_start, group_count):
+        y = torch.zeros((rows.shape[0], rows.shape[1]), dtype=rows.dtype)
+        for j, (s, c) in enumerate(zip(group_start, group_count)):
+            if c:
+                y[s:s + c] = O.swiglu_ffn(rows[s:s + c], self.local[j], "f")
+        return y
+
+    def combine(self, partials, row_map, w, y_shared):
+        y = partials[0] if len(partials) == 1 else (partials[0].float() + partials[1].float()).to(partials[0].dtype)
+        wb = w.to(y.dtype)
+        contrib = y[row_map.long()] * wb.unsqueeze(-1)
+        routed = (contrib[:, 0].float() + contrib[:, 1].float()).to(y.dtype)
+        return routed + y_shared
+
+    def empty_rows(self, rows, dim, like):
+        return torch.zeros((max(rows, 1), dim), dtype=like.dtype)
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, n_experts, tokens_per_rank, out_dir):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    torch.set_num_threads(1)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        layer = {k: v.bfloat16() for k, v in O.make_layer(DIM, HIDDEN_DIM, n_experts, seed=0).items()}
+        n = tokens_per_rank[rank]
+        x = O.make_input(n, DIM, seed=100 + rank).bfloat16()
+
+        class _Module:      # ExpertParallelMoE only needs the expert count from the module when kernels are given
+            experts = [None] * n_experts
+
+        place = Placement(world, n_experts)
+        ep = ExpertParallelMoE(_Module(), kernels=OracleKernels(layer, place, rank))
+        out = ep(x.view(1, n, DIM)).view(n, DIM)
+        # single-process answer for the same tokens, same routing convention as the stand-in
+        k = OracleKernels(layer, Placement(1, n_experts), 0)
+        idx, w, _, _, _, _ = k.route(x)
+        ref, _, _ = O.moe_layer(x, layer, routing=(idx.long(), w.bfloat16()))
+        torch.save({"out": out, "ref": ref, "counts": ep.last_counts}, os.path.join(out_dir, f"rank{rank}.pt"))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,n_experts,tokens", [
+    (2, 4, [96, 40]),          # two experts per rank, ragged token counts
+    (4, 4, [33, 0, 64, 7]),    # one expert per rank, one rank without tokens
+    (4, 2, [50, 50, 20, 31]),  # more ranks than experts: every expert's hidden dimension split over two ranks
+])
+def test_expert_parallel_matches_single_process(tmp_path, world, n_experts, tokens):
+    port = _free_port()
+    mp.spawn(_worker, args=(world, port, n_experts, tokens, str(tmp_path)), nprocs=world, join=True)
+    split = world > n_experts
+    for rank in range(world):
+        r = torch.load(tmp_path / f"rank{rank}.pt")
+        assert r["out"].shape == r["ref"].shape
+        if tokens[rank] == 0:
+            continue
+        if split:
+            # two partial sums rounded to bf16 and added: one extra rounding against the single-GPU result
+            torch.testing.assert_close(r["out"].float(), r["ref"].float(), rtol=2e-2, atol=2e-2)
+        else:
+            assert torch.equal(r["out"], r["ref"]), f"rank {rank} differs"
+        assert [sum(c) for c in r["counts"]] == [2 * t for t in tokens]
+
+
+def test_placement_and_exchange_plan():
+    p = Placement(2, 4)
+    assert p.local_experts(0) == [0, 1] and p.local_experts(1) == [2, 3] and p.owners(2) == [1]
+    p = Placement(4, 4)
+    assert p.local_experts(3) == [3] and p.hidden_splits == 1
+    p = Placement(8, 4)
+    assert p.local_experts(5) == [2] and p.hidden_part(5) == 1 and p.owners(2) == [4, 5] and p.hidden_splits == 2
+    p1 = Placement(1, 4)
+    assert p1.local_experts(0) == [0, 1, 2, 3]
+    with pytest.raises(ValueError):
+        Placement(3, 4)
+    counts = [[5, 1, 0, 2], [3, 3, 3, 3]]
+    recv_start, rows, gstart, gcount = exchange_plan(counts, 1, Placement(2, 4))
+    assert recv_start == [[0, 0], [3, 5]] and rows == 8 and gstart == [0, 3] and gcount == [3, 5]
+    recv_start, rows, gstart, gcount = exchange_plan(counts, 0, Placement(2, 4))
+    assert recv_start == [[0, 5], [8, 9]] and rows == 12 and gcount == [8, 4]
