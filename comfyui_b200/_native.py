@@ -104,7 +104,8 @@ _lib = None
 
 
 def lib_path() -> str:
-    return _build.LIB_PATH
+    """Path of the shared library; COMFY_B200_LIB overrides it (comparison builds)."""
+    return os.environ.get("COMFY_B200_LIB") or _build.LIB_PATH
 
 
 def load(build_if_missing: bool = False) -> ctypes.CDLL:

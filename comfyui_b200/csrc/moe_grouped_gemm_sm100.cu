@@ -14,7 +14,7 @@
 // CTA layout (192 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer,
 // warps 2-5 = epilogue (TMEM -> registers -> global).
 //
-// kCtas = 2: two CTAs on an SM pair form a cluster and share one
+// kCtas = 2 (the default): two CTAs on an SM pair form a cluster and share one
 // tcgen05.mma.cta_group::2 stream.  A cluster tile is 256 rows x 256 accumulator columns; each CTA
 // loads its own 128 rows of A and HALF of the B tile (128 rows), so shared-memory fill traffic and
 // L2->SM traffic per flop drop by a third against a single-CTA 128 x 256 tile.  In pass 1 the 256
@@ -26,8 +26,8 @@
 //   empty[s]       one per CTA; CTA 0's MMA thread commits to both once a stage has been consumed;
 //   tmem_full[a]   one per CTA, committed to by CTA 0's MMA thread when a tile's accumulator is done;
 //   tmem_empty[a]  lives in CTA 0; the epilogue warps of both CTAs arrive on it.
-// kCtas = 1 (the default) is the same code with every pair degenerate (one CTA, 128-row tiles, the CTA
-// loads both B boxes itself).
+// kCtas = 1 is the same code with every pair degenerate (one CTA, 128-row tiles, the CTA loads both B
+// boxes itself).
 // Shared memory: kStages x (A 16 KB + B 32/kCtas KB), 128-byte swizzle.  TMEM: 2 x 256 columns, so the
 // epilogue of tile i overlaps the MMAs of tile i+1.
 #include <cuda.h>
@@ -43,17 +43,18 @@ constexpr int kRowBytes = 128;                    // bytes of K per operand row 
 constexpr int kAccStages = 2;
 constexpr int kABytes = kBlockM * kRowBytes;      // 16 KB
 constexpr int kBBoxBytes = 128 * kRowBytes;       // 16 KB: one 128-row B box
+constexpr int kOutStageBytes = 2 * kABytes;      // epilogue staging tile: 128 rows x 256 bytes
 constexpr int kGemmThreads = 192;
 constexpr int kTmemCols = kAccStages * kBlockN;   // 512
 constexpr int kMaxGroups = kMaxExperts + 1;
-constexpr int kMaxMaps = 2 + 2 * kMaxGroups;
+constexpr int kMaxMaps = 4 + 2 * kMaxGroups;
 
 template <int kCtas> struct GemmShape {
   static constexpr int kTileM = kBlockM * kCtas;
   static constexpr int kBBoxes = 2 / kCtas;                                  // B boxes each CTA loads
   static constexpr int kStageBytes = kABytes + kBBoxes * kBBoxBytes;          // 48 KB or 32 KB
   static constexpr int kStages = kCtas == 1 ? 4 : 6;
-  static constexpr size_t kSmemBytes = static_cast<size_t>(kStages) * kStageBytes + 1024;  // + alignment slack
+  static constexpr size_t kSmemBytes = static_cast<size_t>(kStages) * kStageBytes + kOutStageBytes + 1024;  // + alignment slack
 };
 
 // Device-side status codes written to *status when a bounded wait gives up.
@@ -70,6 +71,8 @@ struct GemmGroup {
   int n_tiles;        // tiles along the output columns
   int routed_index;   // >= 0: rows [row_start[i], row_start[i] + row_count[i]);  < 0: rows [0, static_rows)
   int static_rows;
+  int out_map;        // tensor map of the output (TMA stores)
+  int reserved;
   void* out;          // output base
   long long ld_out;   // output leading dimension in elements
   const float* scale_a;        // fp8: activation scale (NULL = 1)
@@ -85,7 +88,6 @@ struct alignas(64) GemmParams {
   const int32_t* row_count;
   int32_t* status;
   int num_groups;
-  int exp_mode;   // EXPERIMENT ONLY: 1 = no TMA loads, 2 = no MMAs, 4 = no epilogue math/stores
 };
 
 __device__ __forceinline__ float silu_bf16_steps(float a_bf16) {
@@ -186,34 +188,31 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
     }
   };
 
+  // The producer and MMA warps stay converged: every lane runs the loops and the waits, and the instructions
+  // that must come from a single thread are issued under elect.sync.  (Running these loops in one divergent
+  // lane costs about 40 extra cycles per MMA and caps the tensor pipe near 78 %; measured.)
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer (both CTAs of a pair)
-    if (lane == 0) {
-      uint32_t it = 0;
-      bool ok = true;
-      for (int t = unit; t < total_tiles && ok; t += n_units) {
-        int g, m_tile, n_tile;
-        decode(t, g, m_tile, n_tile);
-        const GemmGroup& grp = p.groups[g];
-        const CUtensorMap* map_a = &p.maps[grp.a_map];
-        const int a_row = s_row_base[g] + m_tile * kTileM + static_cast<int>(cta_rank) * kBlockM;
-        const int b_row = n_tile * (kSwiglu ? 128 : kBlockN);
-        const int kb_count = grp.k_blocks;
-        for (int kb = 0; kb < kb_count; ++kb, ++it) {
-          const int s = it % kStages;
-          const uint32_t ph = (it / kStages) & 1u;
-          if ((p.exp_mode & 16) && cta_rank == 1) continue;
-          if (!mbar_wait(&empty_bar[s], ph ^ 1u, abort_ptr)) {
-            atomicCAS(p.status, 0, kStatusProducerTimeout);
-            abort_flag = 1;
-            ok = false;
-            break;
-          }
-          uint8_t* stage = smem + static_cast<size_t>(s) * kStageBytes;
-          if (p.exp_mode & 1) {
-            if (cta_rank == 0) mbar_arrive(&full_bar[s]);
-            continue;
-          }
+    uint32_t it = 0;
+    bool ok = true;
+    for (int t = unit; t < total_tiles && ok; t += n_units) {
+      int g, m_tile, n_tile;
+      decode(t, g, m_tile, n_tile);
+      const GemmGroup& grp = p.groups[g];
+      const CUtensorMap* map_a = &p.maps[grp.a_map];
+      const int a_row = s_row_base[g] + m_tile * kTileM + static_cast<int>(cta_rank) * kBlockM;
+      const int b_row = n_tile * (kSwiglu ? 128 : kBlockN);
+      const int kb_count = grp.k_blocks;
+      for (int kb = 0; kb < kb_count; ++kb, ++it) {
+        const int s = it % kStages;
+        const uint32_t ph = (it / kStages) & 1u;
+        ok = mbar_wait_warp(&empty_bar[s], ph ^ 1u, abort_ptr);
+        if (!ok) {
+          if (lane == 0) { atomicCAS(p.status, 0, kStatusProducerTimeout); abort_flag = 1; }
+          break;
+        }
+        uint8_t* stage = smem + static_cast<size_t>(s) * kStageBytes;
+        if (elect_one()) {
           if constexpr (kPair) {
             const uint32_t full_leader = mapa_shared(smem_u32(&full_bar[s]), 0);
             if (cta_rank == 0) mbar_arrive_expect_tx(&full_bar[s], 2 * kStageBytes);
@@ -229,11 +228,12 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
                         b_row + grp.b1_row_off);
           }
         }
+        __syncwarp();
       }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer (leader CTA only)
-    if (lane == 0 && cta_rank == 0) {
+    if (cta_rank == 0) {
       constexpr uint32_t idesc = umma_idesc<kFp8>(kTileM, kBlockN);
       uint32_t it = 0, tile_count = 0;
       bool ok = true;
@@ -243,9 +243,9 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
         const int kb_count = p.groups[g].k_blocks;
         const uint32_t as = tile_count & 1u;
         const uint32_t aph = (tile_count >> 1) & 1u;
-        if (!mbar_wait(&tmem_empty_bar[as], aph ^ 1u, abort_ptr)) {
-          atomicCAS(p.status, 0, kStatusMmaTimeout);
-          abort_flag = 1;
+        ok = mbar_wait_warp(&tmem_empty_bar[as], aph ^ 1u, abort_ptr);
+        if (!ok) {
+          if (lane == 0) { atomicCAS(p.status, 0, kStatusMmaTimeout); abort_flag = 1; }
           break;
         }
         tc_fence_after_sync();
@@ -253,40 +253,36 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
         for (int kb = 0; kb < kb_count; ++kb, ++it) {
           const int s = it % kStages;
           const uint32_t ph = (it / kStages) & 1u;
-          if (!mbar_wait(&full_bar[s], ph, abort_ptr)) {
-            atomicCAS(p.status, 0, kStatusMmaTimeout);
-            abort_flag = 1;
-            ok = false;
+          ok = mbar_wait_warp(&full_bar[s], ph, abort_ptr);
+          if (!ok) {
+            if (lane == 0) { atomicCAS(p.status, 0, kStatusMmaTimeout); abort_flag = 1; }
             break;
           }
           tc_fence_after_sync();
-          if (p.exp_mode & 2) {
-            mbar_arrive(&empty_bar[s]);
-            if constexpr (kPair) mbar_arrive_cluster(mapa_shared(smem_u32(&empty_bar[s]), 1));
-            continue;
-          }
-          const uint32_t a_addr = smem_u32(smem + static_cast<size_t>(s) * kStageBytes);
-          const uint64_t a_desc = umma_desc_k_sw128(a_addr);
-          const uint64_t b_desc = umma_desc_k_sw128(a_addr + kABytes);
+          if (elect_one()) {
+            {
+              const uint32_t a_addr = smem_u32(smem + static_cast<size_t>(s) * kStageBytes);
+              const uint64_t a_desc = umma_desc_k_sw128(a_addr);
+              const uint64_t b_desc = umma_desc_k_sw128(a_addr + kABytes);
 #pragma unroll
-          for (int k = 0; k < kRowBytes / 32; ++k) {
-            // every MMA consumes 32 bytes of K per row: advance the start address by 32 B (2 units of 16 B)
-            if constexpr (kPair) umma_ss_pair<kFp8>(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
-            else umma_ss<kFp8>(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+              for (int k = 0; k < kRowBytes / 32; ++k) {
+                // every MMA consumes 32 bytes of K per row: advance the start address by 32 B (2 units of 16 B)
+                if constexpr (kPair) umma_ss_pair<kFp8>(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+                else umma_ss<kFp8>(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+              }
+              // free the stage, in both CTAs, once these MMAs have read it
+              if constexpr (kPair) {
+                const uint32_t e_local = smem_u32(&empty_bar[s]);
+                umma_commit_pair(mapa_shared(e_local, 0));
+                umma_commit_pair(mapa_shared(e_local, 1));
+              } else {
+                umma_commit(&empty_bar[s]);
+              }
+            }
           }
-          // free the stage, in both CTAs, once these MMAs have read it
-          if constexpr (kPair) {
-            const uint32_t e_local = smem_u32(&empty_bar[s]);
-            umma_commit_pair(mapa_shared(e_local, 0));
-            if (!(p.exp_mode & 16)) umma_commit_pair(mapa_shared(e_local, 1));
-          } else {
-            umma_commit(&empty_bar[s]);
-          }
+          __syncwarp();
         }
-        if (ok && (p.exp_mode & 2)) {
-          mbar_arrive(&tmem_full_bar[as]);
-          if constexpr (kPair) mbar_arrive_cluster(mapa_shared(smem_u32(&tmem_full_bar[as]), 1));
-        } else if (ok) {
+        if (ok && elect_one()) {
           if constexpr (kPair) {
             const uint32_t f_local = smem_u32(&tmem_full_bar[as]);
             umma_commit_pair(mapa_shared(f_local, 0));
@@ -295,15 +291,27 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
             umma_commit(&tmem_full_bar[as]);
           }
         }
+        __syncwarp();
       }
-      // make sure nothing issued by this thread is still running before TMEM is released
-      if constexpr (kPair) umma_commit_pair(mapa_shared(smem_u32(&drain_bar), 0));
-      else umma_commit(&drain_bar);
+      // make sure nothing issued by this warp is still running before TMEM is released
+      if (elect_one()) {
+        if constexpr (kPair) umma_commit_pair(mapa_shared(smem_u32(&drain_bar), 0));
+        else umma_commit(&drain_bar);
+      }
+      __syncwarp();
       mbar_wait(&drain_bar, 0, abort_ptr);
     }
   } else {
     // ------------------------------------------------------------------ epilogue (4 warps per CTA)
+    // TMEM -> registers -> (math) -> swizzled staging tile in shared memory -> TMA store.  Full 128-byte lines
+    // leave the SM instead of 16-byte pieces of 32 different rows.  A tile that hangs over the end of its group
+    // (its last rows belong to the next group) is written with predicated stores from registers instead.
     const int quarter = warp & 3;   // TMEM lanes this warp may read: [32*quarter, 32*quarter + 32)
+    const bool issuer = warp == 2 && lane == 0;
+    uint8_t* stage_out = smem + static_cast<size_t>(kStages) * kStageBytes;    // kOutStageBytes, 1024-aligned
+    const int r_in_tile = quarter * 32 + lane;
+    uint8_t* stage_row = stage_out + r_in_tile * 128;
+    const int sw = r_in_tile & 7;
     uint32_t tile_count = 0;
     for (int t = unit; t < total_tiles; t += n_units, ++tile_count) {
       int g, m_tile, n_tile;
@@ -311,16 +319,19 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
       const GemmGroup& grp = p.groups[g];
       const uint32_t as = tile_count & 1u;
       const uint32_t aph = (tile_count >> 1) & 1u;
-      bool ok = mbar_wait(&tmem_full_bar[as], aph, abort_ptr);
-      ok = __all_sync(0xffffffffu, ok);
+      const bool ok = mbar_wait_warp(&tmem_full_bar[as], aph, abort_ptr);
       if (!ok) {
         if (lane == 0) { atomicCAS(p.status, 0, kStatusEpilogueTimeout); abort_flag = 1; }
         break;
       }
       tc_fence_after_sync();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + as * kBlockN;
-      const int row = s_row_base[g] + m_tile * kTileM + static_cast<int>(cta_rank) * kBlockM + quarter * 32 + lane;
-      const bool valid = (row < s_row_limit[g]) && !(p.exp_mode & 8);
+      const int row0 = s_row_base[g] + m_tile * kTileM + static_cast<int>(cta_rank) * kBlockM;
+      const int row = row0 + r_in_tile;
+      const bool valid = (row < s_row_limit[g]);
+      // whole tile inside the group (or clipped by the tensor's own bounds, for the un-permuted group)
+      const bool tile_tma = (grp.routed_index < 0 || row0 + kBlockM <= s_row_limit[g]);
+      const CUtensorMap* map_out = &p.maps[grp.out_map];
 
       float alpha0 = 1.f, alpha1 = 1.f, out_inv = 1.f;
       bool out_scaled = false;
@@ -331,9 +342,12 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
         if (kSwiglu && grp.out_scale) { out_inv = round_bf16(1.0f / __ldg(grp.out_scale)); out_scaled = true; }
       }
 
-      if (p.exp_mode & 4) {
-      } else if constexpr (kSwiglu) {
-        const long long col0 = static_cast<long long>(n_tile) * 128;
+      if constexpr (kSwiglu) {
+        const int col0 = n_tile * 128;
+        if (tile_tma) {
+          if (issuer) bulk_wait_read_all();         // the previous tile's store has finished reading the staging tile
+          named_bar_sync(1, 128);
+        }
 #pragma unroll 1
         for (int c = 0; c < 4; ++c) {
           uint32_t ra[32], rb[32];
@@ -350,58 +364,118 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
             h[j] = round_bf16(silu_bf16_steps(a) * b);
             if constexpr (kFp8) { if (out_scaled) h[j] = round_bf16(h[j] * out_inv); }
           }
-          if (valid) {
-            if constexpr (kFp8) {
-              uint8_t* o = static_cast<uint8_t*>(grp.out) + static_cast<long long>(row) * grp.ld_out + col0 + c * 32;
-              uint32_t w[8];
+          if constexpr (kFp8) {
+            uint32_t w[8];
 #pragma unroll
-              for (int j = 0; j < 8; ++j)
-                w[j] = static_cast<uint32_t>(f2_to_e4m3x2(h[4 * j], h[4 * j + 1])) |
-                       (static_cast<uint32_t>(f2_to_e4m3x2(h[4 * j + 2], h[4 * j + 3])) << 16);
+            for (int j = 0; j < 8; ++j)
+              w[j] = static_cast<uint32_t>(f2_to_e4m3x2(h[4 * j], h[4 * j + 1])) |
+                     (static_cast<uint32_t>(f2_to_e4m3x2(h[4 * j + 2], h[4 * j + 3])) << 16);
+            if (tile_tma) {
+              // one 128-byte row per tile row: this chunk is pieces 2c and 2c+1
+              *reinterpret_cast<uint4*>(stage_row + (((2 * c) ^ sw) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+              *reinterpret_cast<uint4*>(stage_row + (((2 * c + 1) ^ sw) << 4)) = make_uint4(w[4], w[5], w[6], w[7]);
+            } else if (valid) {
+              uint8_t* o = static_cast<uint8_t*>(grp.out) + static_cast<long long>(row) * grp.ld_out + col0 + c * 32;
               reinterpret_cast<uint4*>(o)[0] = make_uint4(w[0], w[1], w[2], w[3]);
               reinterpret_cast<uint4*>(o)[1] = make_uint4(w[4], w[5], w[6], w[7]);
-            } else {
-              __nv_bfloat16* o = static_cast<__nv_bfloat16*>(grp.out) + static_cast<long long>(row) * grp.ld_out + col0 + c * 32;
+            }
+          } else {
+            uint4 q[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              q[j] = make_uint4(pack_bf16x2(h[8 * j], h[8 * j + 1]), pack_bf16x2(h[8 * j + 2], h[8 * j + 3]),
+                                pack_bf16x2(h[8 * j + 4], h[8 * j + 5]), pack_bf16x2(h[8 * j + 6], h[8 * j + 7]));
+            if (tile_tma) {
+              // two boxes of 64 columns (128 bytes per row each): chunk c is pieces 4(c&1) .. +3 of box c>>1
+              uint8_t* box_row = stage_row + (c >> 1) * kABytes;
 #pragma unroll
               for (int j = 0; j < 4; ++j)
-                reinterpret_cast<uint4*>(o)[j] =
-                    make_uint4(pack_bf16x2(h[8 * j], h[8 * j + 1]), pack_bf16x2(h[8 * j + 2], h[8 * j + 3]),
-                               pack_bf16x2(h[8 * j + 4], h[8 * j + 5]), pack_bf16x2(h[8 * j + 6], h[8 * j + 7]));
+                *reinterpret_cast<uint4*>(box_row + ((((c & 1) * 4 + j) ^ sw) << 4)) = q[j];
+            } else if (valid) {
+              __nv_bfloat16* o = static_cast<__nv_bfloat16*>(grp.out) + static_cast<long long>(row) * grp.ld_out + col0 + c * 32;
+#pragma unroll
+              for (int j = 0; j < 4; ++j) reinterpret_cast<uint4*>(o)[j] = q[j];
             }
           }
         }
+        // every TMEM read of this tile is done: hand the accumulator stage back before the store is issued
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) {
+          if constexpr (kPair) mbar_arrive_cluster(mapa_shared(smem_u32(&tmem_empty_bar[as]), 0));
+          else mbar_arrive(&tmem_empty_bar[as]);
+        }
+        if (tile_tma) {
+          fence_proxy_async_smem();
+          named_bar_sync(1, 128);
+          if (issuer) {
+            if constexpr (kFp8) {
+              tma_store_2d(map_out, stage_out, col0, row0);
+            } else {
+              tma_store_2d(map_out, stage_out, col0, row0);
+              tma_store_2d(map_out, stage_out + kABytes, col0 + 64, row0);
+            }
+            bulk_commit_group();
+          }
+        }
       } else {
-        const long long col0 = static_cast<long long>(n_tile) * kBlockN;
+        const int col0 = n_tile * kBlockN;
         __nv_bfloat16* o_row = static_cast<__nv_bfloat16*>(grp.out) + static_cast<long long>(row) * grp.ld_out + col0;
 #pragma unroll 1
-        for (int c = 0; c < kBlockN / 32; ++c) {
-          uint32_t r[32];
-          tmem_ld_32x32b_x32(taddr + c * 32, r);
-          tmem_ld_wait();
-          float v[32];
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            v[j] = __uint_as_float(r[j]);
-            if constexpr (kFp8) v[j] *= (c < 4 ? alpha0 : alpha1);
+        for (int half = 0; half < 2; ++half) {
+          if (tile_tma) {
+            if (issuer) bulk_wait_read_all();
+            named_bar_sync(1, 128);
           }
-          if (valid) {
-            __nv_bfloat16* o = o_row + c * 32;
+#pragma unroll 1
+          for (int cc = 0; cc < 4; ++cc) {
+            const int c = half * 4 + cc;
+            uint32_t r[32];
+            tmem_ld_32x32b_x32(taddr + c * 32, r);
+            tmem_ld_wait();
+            float v[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              v[j] = __uint_as_float(r[j]);
+              if constexpr (kFp8) v[j] *= (c < 4 ? alpha0 : alpha1);
+            }
+            uint4 q[4];
 #pragma unroll
             for (int j = 0; j < 4; ++j)
-              reinterpret_cast<uint4*>(o)[j] =
-                  make_uint4(pack_bf16x2(v[8 * j], v[8 * j + 1]), pack_bf16x2(v[8 * j + 2], v[8 * j + 3]),
-                             pack_bf16x2(v[8 * j + 4], v[8 * j + 5]), pack_bf16x2(v[8 * j + 6], v[8 * j + 7]));
+              q[j] = make_uint4(pack_bf16x2(v[8 * j], v[8 * j + 1]), pack_bf16x2(v[8 * j + 2], v[8 * j + 3]),
+                                pack_bf16x2(v[8 * j + 4], v[8 * j + 5]), pack_bf16x2(v[8 * j + 6], v[8 * j + 7]));
+            if (tile_tma) {
+              uint8_t* box_row = stage_row + (cc >> 1) * kABytes;
+#pragma unroll
+              for (int j = 0; j < 4; ++j)
+                *reinterpret_cast<uint4*>(box_row + ((((cc & 1) * 4 + j) ^ sw) << 4)) = q[j];
+            } else if (valid) {
+              __nv_bfloat16* o = o_row + c * 32;
+#pragma unroll
+              for (int j = 0; j < 4; ++j) reinterpret_cast<uint4*>(o)[j] = q[j];
+            }
+          }
+          if (half == 1) {
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) {
+              if constexpr (kPair) mbar_arrive_cluster(mapa_shared(smem_u32(&tmem_empty_bar[as]), 0));
+              else mbar_arrive(&tmem_empty_bar[as]);
+            }
+          }
+          if (tile_tma) {
+            fence_proxy_async_smem();
+            named_bar_sync(1, 128);
+            if (issuer) {
+              tma_store_2d(map_out, stage_out, col0 + half * 128, row0);
+              tma_store_2d(map_out, stage_out + kABytes, col0 + half * 128 + 64, row0);
+              bulk_commit_group();
+            }
           }
         }
       }
-      // hand the accumulator stage back to the MMA thread of the leader CTA: one arrival per warp
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) {
-        if constexpr (kPair) mbar_arrive_cluster(mapa_shared(smem_u32(&tmem_empty_bar[as]), 0));
-        else mbar_arrive(&tmem_empty_bar[as]);
-      }
     }
+    if (issuer) bulk_wait_all();     // stores must have left shared memory (and landed) before the CTA exits
   }
 
   // ------------------------------------------------------------------ teardown
@@ -473,14 +547,14 @@ static int device_sm_count(int* sms) {
   return COMFY_MOE_OK;
 }
 
-// CTAs per tile.  Both variants give the same results and, as measured on B200 under its power cap, the same
-// speed (the pair moves a third less data from L2 but its MMA stream runs at lower utilisation), so the
-// simpler single-CTA tile is the default; COMFY_B200_GEMM_CTAS=2 selects the SM-pair variant.
+// CTAs per tile: SM pairs (cta_group::2) by default; they move a third less data from L2 per flop, which
+// under the B200's power cap shows up as higher clocks.  COMFY_B200_GEMM_CTAS=1 selects the single-CTA
+// variant of the same kernel (same results) for comparison runs.
 static int gemm_ctas() {
   static int ctas = 0;
   if (ctas == 0) {
     const char* env = getenv("COMFY_B200_GEMM_CTAS");
-    ctas = (env && env[0] == '2') ? 2 : 1;
+    ctas = (env && env[0] == '1') ? 1 : 2;
   }
   return ctas;
 }
@@ -553,7 +627,6 @@ extern "C" int comfy_moe_grouped_swiglu(int w_dtype, int n_experts, const ComfyM
   p1.row_start = p2.row_start = row_start;
   p1.row_count = p2.row_count = row_count;
   p1.status = p2.status = status;
-  { const char* env = getenv("COMFY_B200_GEMM_EXP"); p1.exp_mode = p2.exp_mode = env ? atoi(env) : 0; }
   int64_t tiles1[2] = {0, 0}, tiles2[2] = {0, 0};   // upper bounds on tiles, [0] 128-row tiles, [1] 256-row tiles
   int n_maps1 = 0, n_maps2 = 0, g = 0;
 
@@ -567,6 +640,10 @@ extern "C" int comfy_moe_grouped_swiglu(int w_dtype, int n_experts, const ComfyM
     if ((rc = make_map(&p1.maps[n_maps1], x_perm, fp8, rows_cap, dim, dim)) != COMFY_MOE_OK) return rc;
     if ((rc = make_map(&p2.maps[n_maps2], h_perm, fp8, rows_cap, hidden_routed, hidden_routed)) != COMFY_MOE_OK) return rc;
     const int a1 = n_maps1++, a2 = n_maps2++;
+    // outputs: pass 1 stores h through the same map pass 2 reads it with; pass 2 stores y_perm
+    if ((rc = make_map(&p1.maps[n_maps1], h_perm, fp8, rows_cap, hidden_routed, hidden_routed)) != COMFY_MOE_OK) return rc;
+    if ((rc = make_map(&p2.maps[n_maps2], y_perm, false, rows_cap, dim, dim)) != COMFY_MOE_OK) return rc;
+    const int o1 = n_maps1++, o2 = n_maps2++;
     // every group may end in a partial tile
     const int64_t m_tiles_cap[2] = {(rows_cap + kBlockM - 1) / kBlockM + n_experts,
                                     (rows_cap + 2 * kBlockM - 1) / (2 * kBlockM) + n_experts};
@@ -579,10 +656,10 @@ extern "C" int comfy_moe_grouped_swiglu(int w_dtype, int n_experts, const ComfyM
       GemmGroup& g1 = p1.groups[g];
       g1.a_map = a1; g1.b0_map = n_maps1; g1.b1_map = n_maps1 + 1; g1.b1_row_off = 0;
       g1.k_blocks = dim / k_elems; g1.n_tiles = w.hidden / 128; g1.routed_index = e; g1.static_rows = 0;
-      g1.out = h_perm; g1.ld_out = w.hidden;
+      g1.out = h_perm; g1.ld_out = w.hidden; g1.out_map = o1;
       g1.scale_a = w.scale_in13; g1.scale_b0 = w.scale_w1; g1.scale_b1 = w.scale_w3; g1.out_scale = w.scale_in2;
       GemmGroup& g2 = p2.groups[g];
-      g2.a_map = a2; g2.b0_map = n_maps2; g2.b1_map = n_maps2; g2.b1_row_off = 128;
+      g2.a_map = a2; g2.b0_map = n_maps2; g2.b1_map = n_maps2; g2.b1_row_off = 128; g2.out_map = o2;
       g2.k_blocks = w.hidden / k_elems; g2.n_tiles = dim / kBlockN; g2.routed_index = e; g2.static_rows = 0;
       g2.out = y_perm; g2.ld_out = dim;
       g2.scale_a = w.scale_in2; g2.scale_b0 = w.scale_w2; g2.scale_b1 = w.scale_w2; g2.out_scale = nullptr;
@@ -602,15 +679,17 @@ extern "C" int comfy_moe_grouped_swiglu(int w_dtype, int n_experts, const ComfyM
     if ((rc = make_map(&p1.maps[n_maps1 + 2], w.w3, fp8, w.hidden, dim, w.ld13)) != COMFY_MOE_OK) return rc;
     if ((rc = make_map(&p2.maps[n_maps2], h_shared_ws, fp8, n_tokens, w.hidden, w.hidden)) != COMFY_MOE_OK) return rc;
     if ((rc = make_map(&p2.maps[n_maps2 + 1], w.w2, fp8, dim, w.hidden, w.ld2)) != COMFY_MOE_OK) return rc;
+    if ((rc = make_map(&p1.maps[n_maps1 + 3], h_shared_ws, fp8, n_tokens, w.hidden, w.hidden)) != COMFY_MOE_OK) return rc;
+    if ((rc = make_map(&p2.maps[n_maps2 + 2], y_shared, false, n_tokens, dim, dim)) != COMFY_MOE_OK) return rc;
     GemmGroup& g1 = p1.groups[g];
     g1.a_map = n_maps1; g1.b0_map = n_maps1 + 1; g1.b1_map = n_maps1 + 2; g1.b1_row_off = 0;
     g1.k_blocks = dim / k_elems; g1.n_tiles = w.hidden / 128; g1.routed_index = -1; g1.static_rows = n_tokens;
-    g1.out = h_shared_ws; g1.ld_out = w.hidden;
+    g1.out = h_shared_ws; g1.ld_out = w.hidden; g1.out_map = n_maps1 + 3;
     g1.scale_a = w.scale_in13; g1.scale_b0 = w.scale_w1; g1.scale_b1 = w.scale_w3; g1.out_scale = w.scale_in2;
     GemmGroup& g2 = p2.groups[g];
     g2.a_map = n_maps2; g2.b0_map = n_maps2 + 1; g2.b1_map = n_maps2 + 1; g2.b1_row_off = 128;
     g2.k_blocks = w.hidden / k_elems; g2.n_tiles = dim / kBlockN; g2.routed_index = -1; g2.static_rows = n_tokens;
-    g2.out = y_shared; g2.ld_out = dim;
+    g2.out = y_shared; g2.ld_out = dim; g2.out_map = n_maps2 + 2;
     g2.scale_a = w.scale_in2; g2.scale_b0 = w.scale_w2; g2.scale_b1 = w.scale_w2; g2.out_scale = nullptr;
     for (int v = 0; v < 2; ++v) {
       const int64_t tile_m = kBlockM * (v + 1);
