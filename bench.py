@@ -277,7 +277,9 @@ def run_gpu_arm(args) -> None:
                 "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
                 "peak_source": f"{peaks['source']}: sustained cuBLAS bf16 (burst {peaks['tflops_burst']})",
                 "frac_of_burst": achieved / peaks["tflops_burst"], "frac_of_nominal_2250": achieved / 2250.0,
-                "traffic": None,
+                # dram__bytes_read + dram__bytes_write of the two launches, from the ncu capture summarised in
+                # profiles/grouped_gemm_bf16_8192tokens.md (same workload)
+                "traffic": 1.573e9, "algorithmic_bytes": 1.30e9,
             }
             line["stages"] = stages
             hbm = peaks["hbm_gbs"]
@@ -299,40 +301,66 @@ def run_gpu_arm(args) -> None:
 
 
 def time_stages(module, x2, steps, moe_ops, ops):
-    """Average duration of every kernel of the layer, measured with CUDA events around stage-level C-ABI calls."""
+    """Average duration of every kernel of the layer: the same six launches as comfy_moe_forward, issued through
+    the stage-level C-ABI entry points on a pre-allocated workspace with a CUDA event between stages.  All steps are
+    queued before the one synchronisation at the end, so the events are not separated by host latency."""
+    import ctypes
+
+    from comfyui_b200 import _native as N
+
+    lib = N.load()
     layer = ops._layer_pack(module, x2)
     n, d = x2.shape
     e = layer.n_experts
+    ws = moe_ops.Workspace.for_layer(layer, n)
+    out = torch.empty_like(x2)
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    P = lambda t: ctypes.c_void_p(t.data_ptr())      # noqa: E731
+    experts = (N.FfnWeights * e)()
+    for i, pack in enumerate(layer.experts):
+        pack.fill(experts[i])
+    shared = layer.shared.struct()
     names = ["gate", "plan", "permute", "grouped_gemm", "combine"]
-    acc = {k: 0.0 for k in names}
-    status = torch.zeros((2,), dtype=torch.int32, device=x2.device)
+
+    def one_step(marks):
+        rc = 0
+        marks[0].record()
+        rc |= lib.comfy_moe_gate_topk(P(x2), P(layer.gate), N.BF16 if layer.gate.dtype == torch.bfloat16 else N.FP32, n, d,
+                                      e, 2, P(ws.topk_idx), P(ws.topk_weight), P(ws.block_counts), None, None, 1e-6,
+                                      stream)
+        marks[1].record()
+        rc |= lib.comfy_moe_route_plan(P(ws.block_counts), n, e, P(ws.block_offsets), P(ws.expert_counts),
+                                       P(ws.expert_offsets), stream)
+        marks[2].record()
+        rc |= lib.comfy_moe_permute(P(x2), P(ws.topk_idx), P(ws.block_offsets), P(ws.expert_offsets), n, d, e, N.BF16,
+                                    None, P(ws.x_perm), None, None, P(ws.row_map), stream)
+        marks[3].record()
+        rc |= lib.comfy_moe_grouped_swiglu(N.BF16, e, experts, ctypes.byref(shared), P(ws.expert_offsets),
+                                           P(ws.expert_counts), ws.rows_cap, n, d, P(ws.x_perm), P(ws.h_perm),
+                                           P(ws.y_perm), P(x2), P(ws.h_shared), P(ws.y_shared), P(ws.status), stream)
+        marks[4].record()
+        rc |= lib.comfy_moe_combine(P(ws.y_perm), P(ws.row_map), P(ws.topk_weight), P(ws.y_shared), n, d, P(out), stream)
+        marks[5].record()
+        if rc:
+            raise RuntimeError("stage-level C-ABI call failed")
 
     def ev():
         return torch.cuda.Event(enable_timing=True)
 
-    for it in range(steps + 2):
-        marks = [ev() for _ in range(6)]
-        marks[0].record()
-        idx, w, counts, _, _ = moe_ops.gate_topk(x2, layer.gate)
-        marks[1].record()
-        block_offsets, expert_counts, expert_offsets = moe_ops.route_plan(counts, n, e)
-        marks[2].record()
-        x_perm, row_map, _ = moe_ops.permute(x2, idx, block_offsets, expert_offsets, e)
-        marks[3].record()
-        y_perm, y_sh, _, _ = moe_ops.grouped_swiglu(layer.experts, layer.shared, expert_offsets, expert_counts, x_perm, x2,
-                                                    status=status, check_status=False)
-        marks[4].record()
-        moe_ops.combine(y_perm, row_map, w, y_sh)
-        marks[5].record()
-        torch.cuda.synchronize()
-        if it >= 2:
-            for i, k in enumerate(names):
-                acc[k] += marks[i].elapsed_time(marks[i + 1])
-    out = {k + "_ms": v / steps for k, v in acc.items()}
-    out["gate_bytes"] = n * d * 2 + e * d * 2 + n * 2 * 8
-    out["permute_bytes"] = n * d * 2 + n * 2 * d * 2
-    out["combine_bytes"] = n * 2 * d * 2 + n * d * 2 + n * d * 2
-    return out
+    for _ in range(3):
+        one_step([ev() for _ in range(6)])
+    torch.cuda.synchronize()
+    all_marks = [[ev() for _ in range(6)] for _ in range(steps)]
+    for marks in all_marks:
+        one_step(marks)
+    torch.cuda.synchronize()
+    res = {}
+    for i, k in enumerate(names):
+        res[k + "_ms"] = sum(m[i].elapsed_time(m[i + 1]) for m in all_marks) / steps
+    res["gate_bytes"] = n * d * 2 + e * d * 2 + n * 2 * 8
+    res["permute_bytes"] = n * d * 2 + n * 2 * d * 2
+    res["combine_bytes"] = n * 2 * d * 2 + n * d * 2 + n * d * 2
+    return res
 
 
 def main() -> None:

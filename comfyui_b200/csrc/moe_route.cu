@@ -16,10 +16,13 @@ __host__ __device__ constexpr int round_up32(int v) { return (v + 31) & ~31; }
 
 // ------------------------------------------------------------------------------------------------
 // Gate.  Every thread keeps its 8 columns of the gate weight of all experts in registers (fp32).
-// For kTok tokens at a time: load the chunk of each row, form E partial dot products per token,
-// reduce them inside the warp with shuffles, across warps through shared memory; thread i of the
-// block then does softmax, top-2 and the near-tie test for token i.  Summation order is fixed, so
-// the result is reproducible.
+// A round handles kTok = 32 / E tokens: each thread forms the kTok x E = 32 partial dot products of
+// its chunk, a butterfly exchange reduces them across the warp so that lane l ends up with the
+// warp's sum of partial l (31 shuffles instead of 160), one float per lane goes to shared memory,
+// and after the barrier warp 0 finishes the round: lane l = (token l / E, expert l % E) sums the
+// warps' partials in a fixed order, the E lanes of a token do softmax, ranking and the near-tie
+// test with shuffles.  The loads of the next round are issued before the reduction of the current
+// one.  Summation order is fixed, so the result is reproducible.
 // ------------------------------------------------------------------------------------------------
 template <int E>
 __global__ void __launch_bounds__(kMaxRowThreads)
@@ -27,9 +30,12 @@ gate_topk_kernel(const __nv_bfloat16* __restrict__ x, const void* __restrict__ w
                  int dim, int32_t* __restrict__ topk_idx, float* __restrict__ topk_weight,
                  int32_t* __restrict__ block_counts, int32_t* __restrict__ neartie_count,
                  uint8_t* __restrict__ neartie_flags, float neartie_eps) {
-  constexpr int kTok = E <= 4 ? 8 : 4;                 // tokens in flight per thread
+  static_assert(E == 2 || E == 4 || E == 8, "a token's experts must fill a power-of-two group of lanes");
+  constexpr int kTok = 32 / E;                         // tokens per round
+  constexpr int kRounds = kTokensPerBlock / kTok;
+  constexpr bool kPrefetch = kTok <= 8;                // 16 rows in flight twice would not fit the registers
   constexpr int kMaxWarps = kMaxRowThreads / 32;
-  __shared__ float part[2][kTok][kMaxWarps][E];        // double-buffered per-warp partial logits
+  __shared__ float part[2][kMaxWarps][32];             // double-buffered per-warp partial logits
   __shared__ int hist[E];
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -57,17 +63,26 @@ gate_topk_kernel(const __nv_bfloat16* __restrict__ x, const void* __restrict__ w
   __syncthreads();
 
   const int block_tok0 = blockIdx.x * kTokensPerBlock;
-  int buf = 0;
-  for (int base = 0; base < kTokensPerBlock; base += kTok, buf ^= 1) {
-    const int t0 = block_tok0 + base;
-    if (t0 >= n_tokens) break;                          // uniform across the block
-    uint4 v[kTok];
+  auto load_round = [&](uint4 (&v)[kTok], int round) {
 #pragma unroll
     for (int i = 0; i < kTok; ++i) {
-      const int t = t0 + i;
+      const int t = block_tok0 + round * kTok + i;
       v[i] = (active && t < n_tokens) ? ld_nc_u4(reinterpret_cast<const uint4*>(x + static_cast<size_t>(t) * dim) + tid)
                                       : make_uint4(0, 0, 0, 0);
     }
+  };
+
+  uint4 v[kTok], vn[kPrefetch ? kTok : 1];
+  load_round(v, 0);
+#pragma unroll 1
+  for (int round = 0; round < kRounds; ++round) {
+    const int t0 = block_tok0 + round * kTok;
+    if (t0 >= n_tokens) break;                          // uniform across the block
+    const int buf = round & 1;
+    if constexpr (kPrefetch) {
+      if (round + 1 < kRounds) load_round(vn, round + 1);
+    }
+    float pl[32];                                       // partial logit of (token i, expert e) at i * E + e
 #pragma unroll
     for (int i = 0; i < kTok; ++i) {
       float f[8];
@@ -77,54 +92,65 @@ gate_topk_kernel(const __nv_bfloat16* __restrict__ x, const void* __restrict__ w
         float acc = 0.f;
 #pragma unroll
         for (int k = 0; k < 8; ++k) acc = fmaf(f[k], wreg[e][k], acc);
-#pragma unroll
-        for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
-        if (lane == 0) part[buf][i][warp][e] = acc;
+        pl[i * E + e] = acc;
       }
     }
+    // butterfly: after the step with distance h a lane keeps the half of its values whose index has the
+    // same bit h as its lane id; at the end lane l holds the warp-wide sum of value l
+#pragma unroll
+    for (int h = 16; h >= 1; h >>= 1) {
+      const bool upper = (lane & h) != 0;
+#pragma unroll
+      for (int j = 0; j < h; ++j) {
+        const float send = upper ? pl[j] : pl[j + h];
+        const float keep = upper ? pl[j + h] : pl[j];
+        pl[j] = keep + __shfl_xor_sync(0xffffffffu, send, h);
+      }
+    }
+    part[buf][warp][lane] = pl[0];
     __syncthreads();
-    if (tid < kTok && t0 + tid < n_tokens) {
-      const int t = t0 + tid;
-      float s[E];
-      float mx = -INFINITY;
+    if (warp == 0) {
+      float logit = 0.f;
+      for (int w = 0; w < n_warps; ++w) logit += part[buf][w][lane];
+      const int e = lane % E;
+      const int t = t0 + lane / E;
+      float mx = logit;
 #pragma unroll
-      for (int e = 0; e < E; ++e) {
-        float acc = 0.f;
-        for (int w = 0; w < n_warps; ++w) acc += part[buf][tid][w][e];
-        s[e] = acc;
-        mx = fmaxf(mx, acc);
+      for (int off = 1; off < E; off <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+      const float ex = expf(logit - mx);
+      float sum = ex;
+#pragma unroll
+      for (int off = 1; off < E; off <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+      const float s = ex / sum;
+      // rank inside the token's group: larger score first, lower expert index first on exact ties
+      int rank = 0;
+#pragma unroll
+      for (int o = 1; o < E; ++o) {
+        const float so = __shfl_xor_sync(0xffffffffu, s, o);
+        const int eo = e ^ o;
+        rank += (so > s || (so == s && eo < e)) ? 1 : 0;
       }
-      float sum = 0.f;
+      float third = (rank == 2) ? s : -1.f;
 #pragma unroll
-      for (int e = 0; e < E; ++e) {
-        s[e] = expf(s[e] - mx);
-        sum += s[e];
+      for (int off = 1; off < E; off <<= 1) third = fmaxf(third, __shfl_xor_sync(0xffffffffu, third, off));
+      if (t < n_tokens && rank < 2) {
+        topk_idx[2 * t + rank] = e;
+        topk_weight[2 * t + rank] = s;
+        atomicAdd(&hist[e], 1);                          // integer atomics: order does not matter
+        if (rank == 1) {
+          const bool tie = (E > 2) && (s - third < neartie_eps);
+          if (neartie_flags) neartie_flags[t] = tie ? 1 : 0;
+          if (tie && neartie_count) atomicAdd(neartie_count, 1);
+        }
       }
-#pragma unroll
-      for (int e = 0; e < E; ++e) s[e] = s[e] / sum;
-
-      // top-2, strict '>' keeps the lowest index on exact ties
-      int i0 = 0;
-#pragma unroll
-      for (int e = 1; e < E; ++e) if (s[e] > s[i0]) i0 = e;
-      int i1 = (i0 == 0) ? 1 : 0;
-#pragma unroll
-      for (int e = 0; e < E; ++e) if (e != i0 && e != i1 && s[e] > s[i1]) i1 = e;
-      float third = -1.f;
-#pragma unroll
-      for (int e = 0; e < E; ++e) if (e != i0 && e != i1) third = fmaxf(third, s[e]);
-
-      topk_idx[2 * t] = i0;
-      topk_idx[2 * t + 1] = i1;
-      topk_weight[2 * t] = s[i0];
-      topk_weight[2 * t + 1] = s[i1];
-      atomicAdd(&hist[i0], 1);                           // integer atomics: order does not matter
-      atomicAdd(&hist[i1], 1);
-      const bool tie = (E > 2) && (s[i1] - third < neartie_eps);
-      if (neartie_flags) neartie_flags[t] = tie ? 1 : 0;
-      if (tie && neartie_count) atomicAdd(neartie_count, 1);
     }
-    // the next iteration writes the other buffer; the one after that is fenced by its own barrier
+    // the next round writes the other buffer; the one after that is fenced by the barrier in between
+    if constexpr (kPrefetch) {
+#pragma unroll
+      for (int i = 0; i < kTok; ++i) v[i] = vn[i];
+    } else {
+      if (round + 1 < kRounds) load_round(v, round + 1);
+    }
   }
   __syncthreads();
   if (tid < E) block_counts[blockIdx.x * E + tid] = hist[tid];
