@@ -105,18 +105,21 @@ class ClockSampler:
 
 
 # ------------------------------------------------------------------------------------------ CPU arm
-def oracle_cpu_tokens_per_s(n_tokens: int, steps: int, warmup: int):
+def oracle_cpu_tokens_per_s(n_tokens: int, steps: int, warmup: int, dtype: str = "bf16"):
     """The CPU oracle on `n_tokens` of the bench workload, all host threads.  Returns (tokens/s, s/step, cores)."""
     from oracle import hidream_moe_oracle as O
 
     layer = {k: v.bfloat16() for k, v in O.make_layer(DIM, HIDDEN_DIM, N_EXPERTS, seed=0).items()}
+    mode = O.PLAIN
+    if dtype == "fp8":
+        layer, mode = O.quantize_layer_fp8(layer), O.FP8_MATMUL
     x = O.make_input(TOKENS_PER_GPU, DIM, seed=1).bfloat16()[:n_tokens].contiguous()
     with torch.no_grad():
         for _ in range(warmup):
-            O.moe_layer(x, layer, gate_in_fp32=True)
+            O.moe_layer(x, layer, mode=mode, gate_in_fp32=True)
         t0 = time.perf_counter()
         for _ in range(steps):
-            O.moe_layer(x, layer, gate_in_fp32=True)
+            O.moe_layer(x, layer, mode=mode, gate_in_fp32=True)
         dt = (time.perf_counter() - t0) / max(steps, 1)
     return n_tokens / dt, dt, torch.get_num_threads()
 
@@ -125,24 +128,27 @@ def run_reference_arm(args) -> None:
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    value, dt, cores = oracle_cpu_tokens_per_s(CPU_SAMPLE_TOKENS, args.steps, max(args.warmup, 1))
+    value, dt, cores = oracle_cpu_tokens_per_s(CPU_SAMPLE_TOKENS, args.steps, max(args.warmup, 1), args.dtype)
     sample = (f"each step = the first {CPU_SAMPLE_TOKENS} of the {TOKENS_PER_GPU} bench tokens through the CPU oracle "
-              f"(oracle/hidream_moe_oracle.py: the reference's gate + moe_infer + shared expert in PyTorch, bf16)")
+              f"(oracle/hidream_moe_oracle.py: the reference's gate + moe_infer + shared expert in PyTorch)")
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": workload_config(args.gpus),
+        "scaling": "weak", "vs_baseline": None, "dtype": args.dtype, "data": "synthetic",
+        "config": workload_config(args.gpus, args.dtype),
         "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line))
 
 
-def workload_config(n_gpus: int):
+def workload_config(n_gpus: int, dtype: str = "bf16"):
+    what = ("BASELINE config 2: HiDream MoE FFN layer, bf16 weights and activations, 2 x 4096 tokens per GPU, fp32 gate"
+            if dtype == "bf16" else
+            "BASELINE config 3: HiDream MoE FFN layer, expert and shared weights e4m3 with per-tensor fp32 scales, bf16 "
+            "activations quantised to e4m3 for the matmuls, 2 x 4096 tokens per GPU, fp32 gate")
     return {
-        "workload": "BASELINE config 2: HiDream MoE FFN layer, bf16 weights and activations, 2 x 4096 tokens per GPU, "
-                    "fp32 gate",
+        "workload": what,
         "tokens_per_gpu": TOKENS_PER_GPU, "global_tokens": TOKENS_PER_GPU * n_gpus, "dim": DIM, "experts": N_EXPERTS,
         "top_k": TOP_K, "hidden": HIDDEN, "hidden_shared": HIDDEN_SHARED,
         "parallelism": "single GPU" if n_gpus == 1 else f"expert-parallel x{n_gpus} (NCCL all-to-all), shared expert "
@@ -152,7 +158,7 @@ def workload_config(n_gpus: int):
 
 
 # ------------------------------------------------------------------------------------------ GPU arm
-def make_synthetic(dev, seed_w: int = 0, seed_x: int = 1):
+def make_synthetic(dev, seed_w: int = 0, seed_x: int = 1, fp8: bool = False):
     """Seeded synthetic weights and input, generated on the host exactly like the oracle's recipe (same
     generator, same draw order) without importing it, then moved to the device."""
     g = torch.Generator().manual_seed(seed_w)
@@ -166,6 +172,13 @@ def make_synthetic(dev, seed_w: int = 0, seed_x: int = 1):
         draw(prefix + ".w2.weight", (DIM, h))
         draw(prefix + ".w3.weight", (h, DIM))
     draw("gate.weight", (N_EXPERTS, DIM))
+    if fp8:
+        # per-tensor scaled e4m3 (BASELINE config 3): s = max|w| / 448, wq = (w / s).to(e4m3); the gate stays bf16
+        for k in [k for k in state if k != "gate.weight"]:
+            w = state[k].float()
+            sc = (w.abs().max() / 448.0).reshape(())
+            state[k] = (w / sc).to(torch.float8_e4m3fn)
+            state[k[: -len(".weight")] + ".scale_weight"] = sc.to(torch.float32)
     gx = torch.Generator().manual_seed(seed_x)
     x = torch.randn((TOKENS_PER_GPU, DIM), generator=gx, dtype=torch.float32).bfloat16()
     return state, x
@@ -189,9 +202,12 @@ def run_gpu_arm(args) -> None:
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
 
-    state, x_host = make_synthetic(dev, seed_w=0, seed_x=1 + rank)
+    fp8 = args.dtype == "fp8"
+    state, x_host = make_synthetic(dev, seed_w=0, seed_x=1 + rank, fp8=fp8)
+    operations = ops.disable_weight_init if not fp8 else ops.scaled_fp8_ops(
+        fp8_matrix_mult=True, scale_input=False, override_dtype=torch.float8_e4m3fn)
     module = MOEFeedForwardSwiGLU(DIM, HIDDEN_DIM, N_EXPERTS, TOP_K, dtype=torch.bfloat16, device=dev,
-                                  operations=ops.disable_weight_init).eval()
+                                  operations=operations).eval()
     module.load_state_dict(state, strict=True)
     x_pinned = x_host.pin_memory()
     out_pinned = torch.empty_like(x_host).pin_memory()
@@ -248,6 +264,7 @@ def run_gpu_arm(args) -> None:
         if world == 1:
             stages = time_stages(module, x.view(n, DIM), args.steps, moe_ops, ops)
 
+
     times = torch.tensor([ms_total, ms_e2e], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
@@ -260,26 +277,29 @@ def run_gpu_arm(args) -> None:
         line = {
             "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": workload_config(world),
+            "vs_baseline": None, "dtype": args.dtype, "data": "synthetic", "config": workload_config(world, args.dtype),
             "e2e": {"value": n * world / (ms_e2e / args.steps * 1e-3), "unit": "tokens/s",
                     "h2d_bytes_per_step": x_pinned.numel() * 2, "d2h_bytes_per_step": out_pinned.numel() * 2},
             "gpu_launches": launches_per_step * args.steps,
             "clocks": clocks.summary(),
             "layer_tflops": FLOPS_PER_TOKEN * n * world / (ms_step * 1e-3) / 1e12,
-            "layer_frac_of_nominal_2250": FLOPS_PER_TOKEN * n * world / (ms_step * 1e-3) / 1e12 / 2250.0 / world,
+            "layer_frac_of_nominal": FLOPS_PER_TOKEN * n / (ms_step * 1e-3) / 1e12 / (4500.0 if fp8 else 2250.0),
         }
         if stages is not None:
             gemm_ms = stages["grouped_gemm_ms"]
             achieved = FLOPS_PER_TOKEN_GEMM * n / (gemm_ms * 1e-3) / 1e12
-            peak = peaks["tflops_sustained"]
+            # fp8: no measured fp8 denominator exists; twice the measured bf16 figure is used and named as such
+            peak = peaks["tflops_sustained"] * (2.0 if fp8 else 1.0)
             line["roofline"] = {
                 "bound": "tensor", "kernel": "grouped_gemm_kernel (pass 1 SwiGLU + pass 2, one C-ABI call)",
                 "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-                "peak_source": f"{peaks['source']}: sustained cuBLAS bf16 (burst {peaks['tflops_burst']})",
-                "frac_of_burst": achieved / peaks["tflops_burst"], "frac_of_nominal_2250": achieved / 2250.0,
+                "peak_source": f"{peaks['source']}: sustained cuBLAS bf16 (burst {peaks['tflops_burst']})"
+                               + (" x 2 for fp8" if fp8 else ""),
+                "frac_of_burst": achieved / (peaks["tflops_burst"] * (2.0 if fp8 else 1.0)),
+                "frac_of_nominal": achieved / (4500.0 if fp8 else 2250.0),
                 # dram__bytes_read + dram__bytes_write of the two launches, from the ncu capture summarised in
                 # profiles/grouped_gemm_bf16_8192tokens.md (same workload)
-                "traffic": 1.573e9, "algorithmic_bytes": 1.30e9,
+                "traffic": None if fp8 else 1.573e9, "algorithmic_bytes": None if fp8 else 1.30e9,
             }
             line["stages"] = stages
             hbm = peaks["hbm_gbs"]
@@ -289,11 +309,11 @@ def run_gpu_arm(args) -> None:
                 for k in ("gate", "permute", "combine")
             }
             if not args.no_cpu_baseline:
-                cpu_value, cpu_dt, cores = oracle_cpu_tokens_per_s(CPU_SAMPLE_TOKENS, 20, 2)
+                cpu_value, cpu_dt, cores = oracle_cpu_tokens_per_s(CPU_SAMPLE_TOKENS, 20, 2, args.dtype)
                 line["cpu_baseline"] = {
                     "value": cpu_value, "unit": "tokens/s", "cores": cores, "kind": "port",
                     "sample": f"20 calls on the first {CPU_SAMPLE_TOKENS} of the {n} bench tokens, CPU oracle "
-                              "(PyTorch bf16, all host threads)",
+                              "(PyTorch, all host threads)",
                 }
         print(json.dumps(line))
     if world > 1:
@@ -321,6 +341,7 @@ def time_stages(module, x2, steps, moe_ops, ops):
         pack.fill(experts[i])
     shared = layer.shared.struct()
     names = ["gate", "plan", "permute", "grouped_gemm", "combine"]
+    act = N.FP8_E4M3 if layer.fp8 else N.BF16
 
     def one_step(marks):
         rc = 0
@@ -332,12 +353,13 @@ def time_stages(module, x2, steps, moe_ops, ops):
         rc |= lib.comfy_moe_route_plan(P(ws.block_counts), n, e, P(ws.block_offsets), P(ws.expert_counts),
                                        P(ws.expert_offsets), stream)
         marks[2].record()
-        rc |= lib.comfy_moe_permute(P(x2), P(ws.topk_idx), P(ws.block_offsets), P(ws.expert_offsets), n, d, e, N.BF16,
-                                    None, P(ws.x_perm), None, None, P(ws.row_map), stream)
+        rc |= lib.comfy_moe_permute(P(x2), P(ws.topk_idx), P(ws.block_offsets), P(ws.expert_offsets), n, d, e, act,
+                                    None, P(ws.x_perm), P(ws.x_q) if layer.fp8 else None, None, P(ws.row_map), stream)
         marks[3].record()
-        rc |= lib.comfy_moe_grouped_swiglu(N.BF16, e, experts, ctypes.byref(shared), P(ws.expert_offsets),
+        rc |= lib.comfy_moe_grouped_swiglu(act, e, experts, ctypes.byref(shared), P(ws.expert_offsets),
                                            P(ws.expert_counts), ws.rows_cap, n, d, P(ws.x_perm), P(ws.h_perm),
-                                           P(ws.y_perm), P(x2), P(ws.h_shared), P(ws.y_shared), P(ws.status), stream)
+                                           P(ws.y_perm), P(ws.x_q) if layer.fp8 else P(x2), P(ws.h_shared),
+                                           P(ws.y_shared), P(ws.status), stream)
         marks[4].record()
         rc |= lib.comfy_moe_combine(P(ws.y_perm), P(ws.row_map), P(ws.topk_weight), P(ws.y_shared), n, d, P(out), stream)
         marks[5].record()
@@ -358,7 +380,7 @@ def time_stages(module, x2, steps, moe_ops, ops):
     for i, k in enumerate(names):
         res[k + "_ms"] = sum(m[i].elapsed_time(m[i + 1]) for m in all_marks) / steps
     res["gate_bytes"] = n * d * 2 + e * d * 2 + n * 2 * 8
-    res["permute_bytes"] = n * d * 2 + n * 2 * d * 2
+    res["permute_bytes"] = n * d * 2 + (n * 2 * d * 2 if not layer.fp8 else n * 3 * d)
     res["combine_bytes"] = n * 2 * d * 2 + n * d * 2 + n * d * 2
     return res
 
@@ -369,6 +391,8 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp8"],
+                    help="bf16 (BASELINE config 2, the default) or per-tensor scaled fp8 e4m3 expert weights (config 3)")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU oracle timing (profiling runs)")
     args = ap.parse_args()
     if args.impl == "reference":

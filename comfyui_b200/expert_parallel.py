@@ -158,6 +158,8 @@ class ExpertParallelMoE:
         self.place = Placement(self.world, self.n_experts)
         self.kernels = kernels if kernels is not None else CudaKernels(module, self.place, self.rank)
         self.last_counts = None          # [world][E] routed slots of the last call, for reporting
+        self._side = None                # side stream for the count exchange and the dispatch (CUDA only)
+        self._pinned = None
         # gate, plan, permute, shared GEMM x2, routed GEMM x2, combine
         self.launches_per_step = 8
 
@@ -186,9 +188,31 @@ class ExpertParallelMoE:
         x2 = x.reshape(-1, shape[-1])
         k, place, rank = self.kernels, self.place, self.rank
         dim = x2.shape[1]
+        cuda = x2.is_cuda
 
         idx, w, counts_dev, offsets_dev, x_perm, row_map = k.route(x2)
-        counts = self._gather_counts(counts_dev)
+
+        # The count exchange, the host's planning and the dispatch run on a side stream that only depends on the
+        # routing kernels, so the shared expert (main stream) computes underneath them.
+        if cuda:
+            main = torch.cuda.current_stream()
+            if self._side is None:
+                self._side = torch.cuda.Stream(device=x2.device)
+                self._pinned = torch.empty((self.world * self.n_experts,), dtype=torch.int32).pin_memory()
+            side = self._side
+            side.wait_stream(main)
+            with torch.cuda.stream(side):
+                flat = torch.empty((self.world * self.n_experts,), dtype=counts_dev.dtype, device=x2.device)
+                dist.all_gather_into_tensor(flat, counts_dev.contiguous(), group=self.group)
+                self._pinned.copy_(flat, non_blocking=True)
+                done = torch.cuda.Event()
+                done.record(side)
+            y_shared = k.shared_expert(x2)
+            done.synchronize()                                     # the one host synchronisation of the call
+            counts = self._pinned.view(self.world, self.n_experts).tolist()
+        else:
+            counts = self._gather_counts(counts_dev)
+            y_shared = k.shared_expert(x2)
         self.last_counts = counts
         mine = counts[rank]
         # first row of every expert in my permuted buffer: expert blocks start on multiples of 128 rows
@@ -202,7 +226,7 @@ class ExpertParallelMoE:
         local = place.local_experts(rank)
 
         # dispatch: my rows of expert e go to every rank that computes (a slice of) e
-        sends, recvs = [], []
+        sends, recvs, copies = [], [], []
         for e in range(self.n_experts):
             rows = x_perm[my_offset[e]: my_offset[e] + mine[e]]
             for q in place.owners(e):
@@ -212,13 +236,23 @@ class ExpertParallelMoE:
             for s in range(self.world):
                 dst = recv[recv_start[j][s]: recv_start[j][s] + counts[s][e]]
                 if s == rank:
-                    dst.copy_(x_perm[my_offset[e]: my_offset[e] + mine[e]])
+                    copies.append((dst, x_perm[my_offset[e]: my_offset[e] + mine[e]]))
                 else:
                     recvs.append((dst, s))
-        pending = self._exchange(sends, recvs)
-        y_shared = k.shared_expert(x2)            # overlaps the transfer
-        for h in pending:
-            h.wait()
+        if cuda:
+            recv.record_stream(side)
+            x_perm.record_stream(side)
+            with torch.cuda.stream(side):
+                for dst, src in copies:
+                    dst.copy_(src)
+                for h in self._exchange(sends, recvs):
+                    h.wait()
+            main.wait_stream(side)
+        else:
+            for dst, src in copies:
+                dst.copy_(src)
+            for h in self._exchange(sends, recvs):
+                h.wait()
 
         y_recv = k.routed_experts(recv, group_start, group_count)
 
