@@ -142,3 +142,43 @@ def test_placement_and_exchange_plan():
     assert recv_start == [[0, 0], [3, 5]] and rows == 8 and gstart == [0, 3] and gcount == [3, 5]
     recv_start, rows, gstart, gcount = exchange_plan(counts, 0, Placement(2, 4))
     assert recv_start == [[0, 5], [8, 9]] and rows == 12 and gcount == [8, 4]
+
+
+def _dropout_worker(rank, world, port, out_dir):
+    import datetime
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    torch.set_num_threads(1)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=5))
+    layer = {k: v.bfloat16() for k, v in O.make_layer(DIM, HIDDEN_DIM, 4, seed=0).items()}
+
+    class _Module:
+        experts = [None] * 4
+
+    ep = ExpertParallelMoE(_Module(), kernels=OracleKernels(layer, Placement(world, 4), rank))
+    x = O.make_input(16, DIM, seed=rank).bfloat16()
+    ep(x)                                                   # one healthy step
+    if rank == 1:
+        # this rank leaves between steps, with nothing of its own in flight
+        torch.save({"left": True}, os.path.join(out_dir, "rank1.pt"))
+        os._exit(0)
+    try:
+        ep(x)
+        outcome = "completed"
+    except Exception as exc:                                # the count exchange cannot complete without the peer
+        outcome = type(exc).__name__
+    torch.save({"outcome": outcome}, os.path.join(out_dir, "rank0.pt"))
+    os._exit(0)
+
+
+def test_rank_leaving_between_steps_is_detected(tmp_path):
+    """Failure detection on the host: a rank that exits between two layer calls makes the survivor's next count
+    exchange raise (connection loss or the process-group timeout) instead of hanging."""
+    port = _free_port()
+    ctx = mp.spawn(_dropout_worker, args=(2, port, str(tmp_path)), nprocs=2, join=False)
+    for p in ctx.processes:
+        p.join(timeout=120)
+        assert not p.is_alive(), "a rank hung after its peer left"
+    assert torch.load(tmp_path / "rank1.pt")["left"]
+    assert torch.load(tmp_path / "rank0.pt")["outcome"] != "completed"

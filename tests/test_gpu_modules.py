@@ -111,3 +111,17 @@ def test_scaled_fp8_module(cuda_device):
     operations = ops.scaled_fp8_ops(fp8_matrix_mult=False, scale_input=False, override_dtype=torch.float8_e4m3fn)
     mod2 = _module(dev, dim, hidden_dim, operations, layer)
     assert ops._layer_pack(mod2, xd) is None
+
+
+def test_device_status_word_is_reported(cuda_device):
+    """Failure reporting without provoking a failure: the kernels write a code to the status word when a bounded
+    wait gives up; here the word is set from the host and the host-side plumbing must turn it into an error."""
+    from comfyui_b200 import _native as N
+    from comfyui_b200 import moe_ops as M
+
+    status = torch.zeros((2,), dtype=torch.int32, device=cuda_device)
+    M.read_status(status)                                   # clean word: no error
+    status[0] = 2                                           # the code the MMA role would leave
+    with pytest.raises(N.MoeError) as err:
+        M.read_status(status)
+    assert err.value.code == N.ETIMEOUT and "status word = 2" in str(err.value)

@@ -341,3 +341,37 @@ def test_caller_supplied_routing_with_bad_ids(M, cuda_device):
     assert int(ec2.sum()) == 2 * n - 2
     _, row_map, _ = M.permute(x.to(dev), bad, bo, eo, e)
     assert row_map.cpu()[0, 0] == -1 and row_map.cpu()[1, 1] == -1
+
+
+def test_config5_skewed_full_size(M, cuda_device):
+    """BASELINE configuration 5 on one GPU: 8 x 16384 tokens, router skewed so one expert takes ~60 % of the top-1
+    picks.  The oracle cannot run 131 072 tokens in seconds, so parity uses the independence of rows: a random
+    sample of tokens is recomputed by the oracle with the routing the kernels chose, and the routing itself is
+    checked against the oracle's fp32 gate on that sample; counts are checked globally."""
+    n, dim, hidden_dim, e = 8 * 16384, 2560, 10240, 4
+    layer = {k: v.bfloat16() for k, v in O.make_layer(dim, hidden_dim, e, seed=0).items()}
+    x = O.make_input(n, dim, seed=1).bfloat16()
+    O.skew_router(layer, x, 1.16)
+    pack = _layer_to_packs(M, layer, cuda_device, e)
+    ws = M.Workspace.for_layer(pack, n)
+    xd = x.to(cuda_device)
+    out = M.moe_forward(pack, xd, ws)
+    M.read_status(ws.status)
+    again = M.moe_forward(pack, xd, ws).cpu()
+    out = out.cpu()
+    assert torch.equal(out, again)
+    idx = ws.topk_idx.cpu().long()
+    counts = ws.expert_counts.cpu()
+    assert int(counts.sum()) == 2 * n
+    assert counts.tolist() == torch.bincount(idx.flatten(), minlength=e).tolist()
+    top1_share = float((idx[:, 0] == 0).float().mean())
+    assert 0.5 < top1_share < 0.7 and 0.36 < float(counts[0]) / (2 * n) < 0.47
+    print(f"config 5: expert counts {counts.tolist()}, expert 0 wins {top1_share:.3f} of top-1")
+    sample = torch.randperm(n, generator=torch.Generator().manual_seed(3))[:1536]
+    xs = x[sample]
+    ridx, _ = O.gate(xs.float(), layer["gate.weight"].float())
+    same = _routing_sets_equal(idx[sample], ridx)
+    assert int((~same).sum()) <= int(ws.status[1])
+    w = ws.topk_weight.cpu()[sample].bfloat16()
+    ref, _, _ = O.moe_layer(xs, layer, routing=(idx[sample], w))
+    torch.testing.assert_close(out[sample].float(), ref.float(), rtol=BF16_RTOL, atol=BF16_ATOL)
