@@ -11,7 +11,7 @@ from ctypes import POINTER, Structure, c_char_p, c_float, c_int, c_int32, c_int6
 
 from . import build as _build
 
-ABI_VERSION = 1
+ABI_VERSION = 2
 
 OK, EINVAL, EUNSUPPORTED, ECUDA, ETIMEOUT, EDEVICE, ETOOLARGE = range(7)
 BF16, FP32, FP8_E4M3 = 0, 1, 2
@@ -33,6 +33,10 @@ EXPORTS = (
     "comfy_moe_combine",
     "comfy_moe_combine_partials",
     "comfy_moe_forward",
+    "comfy_moe_ln_modulate",
+    "comfy_moe_gate_residual",
+    "comfy_moe_combine_block",
+    "comfy_moe_ffn_block",
     "comfy_moe_read_status",
 )
 
@@ -91,6 +95,7 @@ class Workspace(Structure):
         ("h_shared", c_void_p),
         ("y_shared", c_void_p),
         ("rows_cap", c_int64),
+        ("x_mod", c_void_p),
     ]
 
 
@@ -149,6 +154,13 @@ def load(build_if_missing: bool = False) -> ctypes.CDLL:
     lib.comfy_moe_combine_partials.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p,
                                                c_void_p]
     lib.comfy_moe_forward.argtypes = [POINTER(Layer), POINTER(Workspace), c_void_p, c_int, c_void_p, c_void_p]
+    lib.comfy_moe_ln_modulate.argtypes = [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_float, c_void_p,
+                                          c_void_p]
+    lib.comfy_moe_gate_residual.argtypes = [c_void_p, c_void_p, c_int64, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]
+    lib.comfy_moe_combine_block.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_int,
+                                            c_int, c_int, c_void_p, c_void_p]
+    lib.comfy_moe_ffn_block.argtypes = [POINTER(Layer), POINTER(Workspace), c_void_p, c_void_p, c_void_p, c_void_p,
+                                        c_int64, c_int, c_int, c_float, c_void_p, c_void_p]
     lib.comfy_moe_read_status.argtypes = [c_void_p, c_void_p, POINTER(c_int32)]
     for name in EXPORTS:
         if name not in ("comfy_moe_error_string",):

@@ -19,6 +19,7 @@ LIB_PATH = os.path.join(PKG_DIR, LIB_NAME)
 SOURCES = [
     "moe_route.cu",
     "moe_combine.cu",
+    "moe_block_glue.cu",
     "moe_grouped_gemm_sm100.cu",
     "moe_c_api.cu",
 ]

@@ -26,10 +26,18 @@ extern "C" int comfy_moe_read_status(const int32_t* status, void* stream, int32_
   return *h_status == 0 ? COMFY_MOE_OK : COMFY_MOE_ETIMEOUT;
 }
 
+// Block epilogue requested by comfy_moe_ffn_block: gate * (.) + residual folded into the combine.
+struct BlockEpilogue {
+  const void* gate;
+  int64_t gate_batch_stride;
+  const void* residual;
+  int tokens_per_batch;
+};
+
 // MOEFeedForwardSwiGLU.forward (comfy/ldm/hidream/model.py:307-325) as six launches on one stream:
 // gate, routing plan, permutation, two passes of the grouped GEMM, combine.
-extern "C" int comfy_moe_forward(const ComfyMoeLayer* L, const ComfyMoeWorkspace* ws, const void* x, int n_tokens,
-                                 void* out, void* stream) {
+static int forward_impl(const ComfyMoeLayer* L, const ComfyMoeWorkspace* ws, const void* x, int n_tokens, void* out,
+                        void* stream, const BlockEpilogue* epi) {
   if (!L || !ws || n_tokens < 0) return COMFY_MOE_EINVAL;
   if (n_tokens == 0) return COMFY_MOE_OK;
   if (!x || !out) return COMFY_MOE_EINVAL;
@@ -60,9 +68,31 @@ extern "C" int comfy_moe_forward(const ComfyMoeLayer* L, const ComfyMoeWorkspace
                          stream);
   if (rc != COMFY_MOE_OK) return rc;
   rc = comfy_moe_grouped_swiglu(L->w_dtype, L->n_experts, L->experts, &L->shared, ws->expert_offsets,
-                                ws->expert_counts, ws->rows_cap,
-                                n_tokens, L->dim, ws->x_perm, ws->h_perm, ws->y_perm, fp8 ? ws->x_q : x,
-                                ws->h_shared, ws->y_shared, ws->status, stream);
+                                ws->expert_counts, ws->rows_cap, n_tokens, L->dim, ws->x_perm, ws->h_perm, ws->y_perm,
+                                fp8 ? ws->x_q : x, ws->h_shared, ws->y_shared, ws->status, stream);
   if (rc != COMFY_MOE_OK) return rc;
+  if (epi)
+    return comfy_moe_combine_block(ws->y_perm, ws->row_map, ws->topk_weight, ws->y_shared, epi->gate,
+                                   epi->gate_batch_stride, epi->residual, n_tokens, epi->tokens_per_batch, L->dim, out,
+                                   stream);
   return comfy_moe_combine(ws->y_perm, ws->row_map, ws->topk_weight, ws->y_shared, n_tokens, L->dim, out, stream);
+}
+
+extern "C" int comfy_moe_forward(const ComfyMoeLayer* L, const ComfyMoeWorkspace* ws, const void* x, int n_tokens,
+                                 void* out, void* stream) {
+  return forward_impl(L, ws, x, n_tokens, out, stream, nullptr);
+}
+
+// Feed-forward half of a HiDream block (comfy/ldm/hidream/model.py:429-433): LayerNorm + modulation, the MoE,
+// gate * (.) + residual.
+extern "C" int comfy_moe_ffn_block(const ComfyMoeLayer* L, const ComfyMoeWorkspace* ws, const void* x,
+                                   const void* shift, const void* scale, const void* gate, int64_t mod_batch_stride,
+                                   int n_tokens, int tokens_per_batch, float eps, void* out, void* stream) {
+  if (!L || !ws || !ws->x_mod) return COMFY_MOE_EINVAL;
+  if (n_tokens == 0) return COMFY_MOE_OK;
+  int rc = comfy_moe_ln_modulate(x, shift, scale, mod_batch_stride, n_tokens, tokens_per_batch, L->dim, eps, ws->x_mod,
+                                 stream);
+  if (rc != COMFY_MOE_OK) return rc;
+  const BlockEpilogue epi = {gate, mod_batch_stride, x, tokens_per_batch};
+  return forward_impl(L, ws, ws->x_mod, n_tokens, out, stream, &epi);
 }

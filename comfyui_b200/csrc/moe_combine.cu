@@ -18,7 +18,8 @@ __global__ void __launch_bounds__(kCombineMaxThreads)
 combine_kernel(const __nv_bfloat16* __restrict__ y_perm, const __nv_bfloat16* __restrict__ y_perm_b,
                const int32_t* __restrict__ row_map,
                const float* __restrict__ topk_weight, const __nv_bfloat16* __restrict__ y_shared, int n_tokens,
-               int dim, __nv_bfloat16* __restrict__ out) {
+               int dim, __nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ gate,
+               long long gate_batch_stride, const __nv_bfloat16* __restrict__ residual, int tokens_per_batch) {
   constexpr int kTok = 4;
   const int tid = threadIdx.x;
   if (tid >= (dim >> 3)) return;
@@ -71,6 +72,14 @@ combine_kernel(const __nv_bfloat16* __restrict__ y_perm, const __nv_bfloat16* __
         const float routed = round_bf16(p0 + p1);
         r[k] = y_shared ? routed + fs[k] : routed;
       }
+      if (gate) {
+        // block epilogue (comfy/ldm/hidream/model.py:432-433): gate_mlp * ff(x) + x, each step rounded to bf16
+        float fg[8], fr[8];
+        unpack_bf16x8(*(reinterpret_cast<const uint4*>(gate + (t / tokens_per_batch) * gate_batch_stride) + tid), fg);
+        unpack_bf16x8(ld_nc_u4(reinterpret_cast<const uint4*>(residual + static_cast<size_t>(t) * dim) + tid), fr);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) r[k] = round_bf16(fg[k] * round_bf16(r[k])) + fr[k];
+      }
       reinterpret_cast<uint4*>(out + static_cast<size_t>(t) * dim)[tid] =
           make_uint4(pack_bf16x2(r[0], r[1]), pack_bf16x2(r[2], r[3]), pack_bf16x2(r[4], r[5]), pack_bf16x2(r[6], r[7]));
     }
@@ -82,7 +91,9 @@ combine_kernel(const __nv_bfloat16* __restrict__ y_perm, const __nv_bfloat16* __
 using namespace comfy_b200;
 
 static int launch_combine(const void* y_perm, const void* y_perm_b, const int32_t* row_map, const float* topk_weight,
-                          const void* y_shared, int n_tokens, int dim, void* out, void* stream) {
+                          const void* y_shared, int n_tokens, int dim, void* out, void* stream,
+                          const void* gate = nullptr, long long gate_batch_stride = 0, const void* residual = nullptr,
+                          int tokens_per_batch = 1) {
   if (n_tokens < 0 || dim <= 0) return COMFY_MOE_EINVAL;
   if (n_tokens == 0) return COMFY_MOE_OK;
   if (!y_perm || !row_map || !topk_weight || !out) return COMFY_MOE_EINVAL;
@@ -95,12 +106,18 @@ static int launch_combine(const void* y_perm, const void* y_perm_b, const int32_
   const __nv_bfloat16* ya = static_cast<const __nv_bfloat16*>(y_perm);
   const __nv_bfloat16* yb = static_cast<const __nv_bfloat16*>(y_perm_b);
   const __nv_bfloat16* ys = static_cast<const __nv_bfloat16*>(y_shared);
+  const __nv_bfloat16* g = static_cast<const __nv_bfloat16*>(gate);
+  const __nv_bfloat16* res = static_cast<const __nv_bfloat16*>(residual);
+  if (g && (!res || !aligned16(g) || !aligned16(res) || (gate_batch_stride % 8) != 0 || tokens_per_batch <= 0))
+    return COMFY_MOE_EINVAL;
   if (yb)
     combine_kernel<true><<<blocks, threads, 0, s>>>(ya, yb, row_map, topk_weight, ys, n_tokens, dim,
-                                                    static_cast<__nv_bfloat16*>(out));
+                                                    static_cast<__nv_bfloat16*>(out), g, gate_batch_stride, res,
+                                                    tokens_per_batch);
   else
     combine_kernel<false><<<blocks, threads, 0, s>>>(ya, nullptr, row_map, topk_weight, ys, n_tokens, dim,
-                                                     static_cast<__nv_bfloat16*>(out));
+                                                     static_cast<__nv_bfloat16*>(out), g, gate_batch_stride, res,
+                                                     tokens_per_batch);
   return check_launch();
 }
 
@@ -114,4 +131,13 @@ extern "C" int comfy_moe_combine_partials(const void* y_perm_a, const void* y_pe
                                           void* out, void* stream) {
   if (!y_perm_b) return COMFY_MOE_EINVAL;
   return launch_combine(y_perm_a, y_perm_b, row_map, topk_weight, y_shared, n_tokens, dim, out, stream);
+}
+
+extern "C" int comfy_moe_combine_block(const void* y_perm, const int32_t* row_map, const float* topk_weight,
+                                       const void* y_shared, const void* gate, int64_t gate_batch_stride,
+                                       const void* residual, int n_tokens, int tokens_per_batch, int dim, void* out,
+                                       void* stream) {
+  if (!gate || !residual) return COMFY_MOE_EINVAL;
+  return launch_combine(y_perm, nullptr, row_map, topk_weight, y_shared, n_tokens, dim, out, stream, gate,
+                        gate_batch_stride, residual, tokens_per_batch);
 }

@@ -144,3 +144,22 @@ class MOEFeedForwardSwiGLU(nn.Module):
                 acc.scatter_reduce_(0, tok.view(-1, 1).repeat(1, x.shape[-1]), y, reduce="sum")
             begin = end
         return acc
+
+
+def block_feed_forward(norm, ff, tokens, shift, scale, gate):
+    """Feed-forward half of a HiDream transformer block (``model.py:429-433`` for the single-stream block,
+    ``:515-523`` for the image and the text side of the double-stream block):
+
+        tokens + gate * ff(norm(tokens) * (1 + scale) + shift)
+
+    ``norm`` is the block's ``operations.LayerNorm(dim, eps=1e-6, elementwise_affine=False)``, ``ff`` its
+    ``MOEFeedForwardSwiGLU`` or ``FeedForwardSwiGLU``; shift / scale / gate are the ``[B, 1, dim]`` chunks of the adaLN
+    output.  A block's forward calls this instead of spelling the four lines out, so that the kernels can fuse the
+    element-wise passes with the feed-forward."""
+    fast = b200_ops.hidream_block_ffn(norm, ff, tokens, shift, scale, gate)
+    if fast is not None:
+        return fast
+    wtype = tokens.dtype
+    normed = norm(tokens).to(dtype=wtype)
+    normed = normed * (1 + scale) + shift
+    return gate * ff(normed.to(dtype=wtype)) + tokens

@@ -165,13 +165,20 @@ class Workspace:
         self.y_perm = torch.empty((rows_cap, dim), dtype=torch.bfloat16, device=device)
         self.h_shared = torch.empty((max(n_tokens, 1), hidden_shared), dtype=act, device=device)
         self.y_shared = torch.empty((max(n_tokens, 1), dim), dtype=torch.bfloat16, device=device)
+        self.x_mod = None          # allocated on first use by moe_ffn_block
         ws = N.Workspace()
         for name in ("topk_idx", "topk_weight", "block_counts", "block_offsets", "expert_counts", "expert_offsets",
                      "row_map", "status", "x_perm", "x_q", "h_perm", "y_perm", "h_shared", "y_shared"):
             t = getattr(self, name)
             setattr(ws, name, None if t is None else t.data_ptr())
         ws.rows_cap = rows_cap
+        ws.x_mod = None
         self.c_ws = ws
+
+    def need_x_mod(self) -> None:
+        if self.x_mod is None:
+            self.x_mod = torch.empty((max(self.n_tokens, 1), self.dim), dtype=torch.bfloat16, device=self.x_perm.device)
+            self.c_ws.x_mod = self.x_mod.data_ptr()
 
     @classmethod
     def for_layer(cls, layer: LayerPack, n_tokens: int) -> "Workspace":
@@ -341,4 +348,59 @@ def moe_forward(layer: LayerPack, x: torch.Tensor, ws: Optional[Workspace] = Non
     rc = N.load().comfy_moe_forward(ctypes.byref(layer.c_layer), ctypes.byref(ws.c_ws), _ptr(x), n, _ptr(out),
                                     _stream())
     N.check("comfy_moe_forward", rc)
+    return out
+
+
+# --------------------------------------------------------------------------------------- block glue
+def _modulation(*vectors: torch.Tensor) -> int:
+    """Common batch stride (elements) of bf16 [B, D] / [B, 1, D] modulation vectors that are views of one tensor."""
+    strides = set()
+    for v in vectors:
+        _need_cuda(v)
+        if v.dtype != torch.bfloat16 or v.stride(-1) != 1:
+            raise ValueError("modulation vectors must be bf16 with a contiguous last dimension")
+        strides.add(v.stride(0) if v.shape[0] > 1 else 0)
+    if len(strides) != 1:
+        raise ValueError("modulation vectors must share one batch stride")
+    return strides.pop()
+
+
+def ln_modulate(x: torch.Tensor, shift: torch.Tensor, scale: torch.Tensor, tokens_per_batch: int, eps: float = 1e-6,
+                out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """LayerNorm(x) * (1 + scale) + shift in one pass.  x: bf16 [N, D]; shift, scale: bf16 [B, D] views."""
+    _need_cuda(x)
+    n, d = x.shape
+    stride = _modulation(shift, scale)
+    if out is None:
+        out = torch.empty_like(x)
+    rc = N.load().comfy_moe_ln_modulate(_ptr(x), _ptr(shift), _ptr(scale), stride, n, tokens_per_batch, d, float(eps),
+                                        _ptr(out), _stream())
+    N.check("comfy_moe_ln_modulate", rc)
+    return out
+
+
+def gate_residual(y: torch.Tensor, gate: torch.Tensor, residual: torch.Tensor, tokens_per_batch: int) -> torch.Tensor:
+    """gate * y + residual with PyTorch's bf16 rounding points.  y, residual: bf16 [N, D]; gate: bf16 [B, D] view."""
+    _need_cuda(y, residual)
+    n, d = y.shape
+    out = torch.empty_like(y)
+    rc = N.load().comfy_moe_gate_residual(_ptr(y), _ptr(gate), _modulation(gate), _ptr(residual), n, tokens_per_batch, d,
+                                          _ptr(out), _stream())
+    N.check("comfy_moe_gate_residual", rc)
+    return out
+
+
+def moe_ffn_block(layer: LayerPack, x: torch.Tensor, shift: torch.Tensor, scale: torch.Tensor, gate: torch.Tensor,
+                  tokens_per_batch: int, eps: float = 1e-6, ws: Optional[Workspace] = None) -> torch.Tensor:
+    """gate * MoE(LayerNorm(x) * (1 + scale) + shift) + x through comfy_moe_ffn_block.  x: bf16 [N, D]."""
+    _need_cuda(x)
+    n = x.shape[0]
+    if ws is None or ws.n_tokens != n:
+        ws = Workspace.for_layer(layer, n)
+    ws.need_x_mod()
+    out = torch.empty_like(x)
+    rc = N.load().comfy_moe_ffn_block(ctypes.byref(layer.c_layer), ctypes.byref(ws.c_ws), _ptr(x), _ptr(shift),
+                                      _ptr(scale), _ptr(gate), _modulation(shift, scale, gate), n, tokens_per_batch,
+                                      float(eps), _ptr(out), _stream())
+    N.check("comfy_moe_ffn_block", rc)
     return out

@@ -85,10 +85,35 @@ class disable_weight_init:
             return super().forward(*args, **kwargs)
 
 
+class _LayerNorm(torch.nn.LayerNorm, CastWeightBiasOp):
+    """operations.LayerNorm (``comfy/ops.py:173-189``): the HiDream blocks build their norms through it."""
+
+    def reset_parameters(self):
+        return None
+
+    def forward_comfy_cast_weights(self, input):
+        if self.weight is not None:
+            weight, bias = cast_bias_weight(self, input)
+        else:
+            weight, bias = None, None
+        return F.layer_norm(input, self.normalized_shape, weight, bias, self.eps)
+
+    def forward(self, *args, **kwargs):
+        if self.comfy_cast_weights or self.weight_function or self.bias_function:
+            return self.forward_comfy_cast_weights(*args, **kwargs)
+        return super().forward(*args, **kwargs)
+
+
+disable_weight_init.LayerNorm = _LayerNorm
+
+
 class manual_cast(disable_weight_init):
     """Weights stored in one dtype and cast to the activation dtype on every call."""
 
     class Linear(disable_weight_init.Linear):
+        comfy_cast_weights = True
+
+    class LayerNorm(disable_weight_init.LayerNorm):
         comfy_cast_weights = True
 
 
@@ -432,3 +457,48 @@ def swiglu_ffn_forward(ffn, x: torch.Tensor) -> Optional[torch.Tensor]:
         return None   # the dense fp8 path needs the quantised copy the permutation kernel makes
     _, y, _, _ = moe_ops.grouped_swiglu([], pack, None, None, None, x2, check_status=CHECK_STATUS_EVERY_CALL)
     return y.view(x.shape)
+
+
+def _modulation_ok(x: torch.Tensor, *vectors: torch.Tensor) -> bool:
+    """shift / scale / gate as the blocks produce them: bf16 chunks [B, 1, D] of one adaLN output on x's device."""
+    b, d = x.shape[0], x.shape[-1]
+    strides = set()
+    for v in vectors:
+        if v is None or v.device != x.device or v.dtype != torch.bfloat16 or v.shape[-1] != d or v.stride(-1) != 1:
+            return False
+        if v.numel() != b * d or v.shape[0] != b or v.data_ptr() % 16 or v.stride(0) % 8:
+            return False
+        strides.add(v.stride(0))
+    return len(strides) == 1
+
+
+def hidream_block_ffn(norm, ff, x: torch.Tensor, shift: torch.Tensor, scale: torch.Tensor,
+                      gate: torch.Tensor) -> Optional[torch.Tensor]:
+    """Feed-forward half of a HiDream block, ``gate * ff(norm(x) * (1 + scale) + shift) + x``, on the kernels:
+    LayerNorm + modulation in one pass, the MoE (or dense SwiGLU) feed-forward, and the gate / residual epilogue
+    folded into the combine.  ``norm`` is the block's LayerNorm module (no affine).  None when not eligible."""
+    if x.dim() != 3 or getattr(norm, "weight", None) is not None or getattr(norm, "bias", None) is not None:
+        return None
+    if not _modulation_ok(x, shift, scale, gate):
+        return None
+    from . import moe_ops
+
+    b, s, d = x.shape
+    x2 = x.view(-1, d)
+    if hasattr(ff, "experts"):
+        layer = _layer_pack(ff, x)
+        if layer is None:
+            return None
+        ws = _workspace(layer, x2.shape[0])
+        out = moe_ops.moe_ffn_block(layer, x2, shift, scale, gate, s, norm.eps, ws)
+        if CHECK_STATUS_EVERY_CALL:
+            moe_ops.read_status(ws.status)
+        return out.view(x.shape)
+    if not _input_ok(x, ff.w1.weight.shape[1]):
+        return None
+    pack = _ffn_pack(ff, x.device, moe_ops)
+    if pack is None or pack.hidden % 128 or pack.w1.dtype == FP8:
+        return None
+    x_mod = moe_ops.ln_modulate(x2, shift, scale, s, norm.eps)
+    _, y, _, _ = moe_ops.grouped_swiglu([], pack, None, None, None, x_mod, check_status=CHECK_STATUS_EVERY_CALL)
+    return moe_ops.gate_residual(y, gate, x2, s).view(x.shape)

@@ -26,7 +26,7 @@
 extern "C" {
 #endif
 
-#define COMFY_MOE_ABI_VERSION 1
+#define COMFY_MOE_ABI_VERSION 2
 
 /* Return codes. */
 #define COMFY_MOE_OK 0
@@ -209,6 +209,7 @@ typedef struct ComfyMoeWorkspace {
   void* h_shared;          /* [n_tokens, hidden_s] act dtype */
   void* y_shared;          /* bf16 [n_tokens, dim] */
   int64_t rows_cap;
+  void* x_mod;             /* bf16 [n_tokens, dim]: normalised + modulated input; only comfy_moe_ffn_block needs it */
 } ComfyMoeWorkspace;
 
 /* ---- MOEFeedForwardSwiGLU.forward (model.py:307-325): gate -> plan -> permute -> experts -> combine ----
@@ -216,6 +217,32 @@ typedef struct ComfyMoeWorkspace {
  */
 int comfy_moe_forward(const ComfyMoeLayer* h_layer, const ComfyMoeWorkspace* h_ws, const void* x, int n_tokens,
                       void* out, void* stream);
+
+/* ---- the element-wise passes a HiDream block runs around its feed-forward (model.py:429-433, 515-523) --------
+ * Modulation vectors (shift, scale, gate) are bf16 [batch, dim] views with `*_batch_stride` elements between batch
+ * elements (they are chunks of one adaLN output in the reference, so the stride is a multiple of dim); token t
+ * belongs to batch element t / tokens_per_batch.
+ *
+ * comfy_moe_ln_modulate:   out = LayerNorm(x) * (1 + scale) + shift      LayerNorm: eps, no affine, fp32 statistics,
+ *                          bf16 output; (1 + scale), the product and the sum each rounded to bf16 as PyTorch does.
+ * comfy_moe_gate_residual: out = gate * y + residual                      for a dense feed-forward (text tokens).
+ * comfy_moe_combine_block: comfy_moe_combine followed by "gate * (.) + residual" in the same pass.
+ */
+int comfy_moe_ln_modulate(const void* x, const void* shift, const void* scale, int64_t mod_batch_stride, int n_tokens,
+                          int tokens_per_batch, int dim, float eps, void* out, void* stream);
+int comfy_moe_gate_residual(const void* y, const void* gate, int64_t gate_batch_stride, const void* residual,
+                            int n_tokens, int tokens_per_batch, int dim, void* out, void* stream);
+int comfy_moe_combine_block(const void* y_perm, const int32_t* row_map, const float* topk_weight, const void* y_shared,
+                            const void* gate, int64_t gate_batch_stride, const void* residual, int n_tokens,
+                            int tokens_per_batch, int dim, void* out, void* stream);
+
+/* ---- feed-forward half of a HiDream block with a MoE (model.py:429-433 / 515-523), seven launches ----------
+ *   out = gate * MOEFeedForwardSwiGLU(LayerNorm(x) * (1 + scale) + shift) + x
+ * x, out: bf16 [n_tokens, dim] (out may alias nothing else); h_ws->x_mod must be set.
+ */
+int comfy_moe_ffn_block(const ComfyMoeLayer* h_layer, const ComfyMoeWorkspace* h_ws, const void* x, const void* shift,
+                        const void* scale, const void* gate, int64_t mod_batch_stride, int n_tokens,
+                        int tokens_per_batch, float eps, void* out, void* stream);
 
 /* Synchronises `stream`, copies status[0] to *h_status and returns COMFY_MOE_ETIMEOUT if it is non-zero. */
 int comfy_moe_read_status(const int32_t* status, void* stream, int32_t* h_status);

@@ -167,6 +167,33 @@ def moe_layer(x: torch.Tensor, layer: Layer, mode: str = PLAIN, gate_in_fp32: bo
     return out, idx, w
 
 
+def block_ffn(x: torch.Tensor, layer: Layer, shift: torch.Tensor, scale: torch.Tensor, gate_mlp: torch.Tensor,
+              eps: float = 1e-6, mode: str = PLAIN, dense_prefix: Optional[str] = None, **moe_kw) -> torch.Tensor:
+    """Feed-forward half of a HiDream block (model.py:429-433; :515-523 for the double-stream block):
+    LayerNorm without affine -> * (1 + scale) + shift -> feed-forward -> gate * (.) + x.
+    x [B, S, D]; shift / scale / gate_mlp [B, 1, D].  ``dense_prefix`` selects a plain FeedForwardSwiGLU (the text
+    side, ``ff_t``) instead of the MoE; ``moe_kw`` goes to moe_layer (routing, gate_in_fp32, branch)."""
+    wtype = x.dtype
+    b, s, d = x.shape
+    normed = F.layer_norm(x, (d,), None, None, eps).to(dtype=wtype)
+    normed = normed * (1 + scale) + shift
+    flat = normed.to(dtype=wtype).reshape(-1, d)
+    if dense_prefix is not None:
+        ff = swiglu_ffn(flat, layer, dense_prefix, mode)
+    else:
+        ff, _, _ = moe_layer(flat, layer, mode=mode, **moe_kw)
+    return gate_mlp * ff.view(b, s, d) + x
+
+
+def make_modulation(batch: int, dim: int, seed: int = 2, dtype: torch.dtype = torch.bfloat16):
+    """Seeded stand-in for one adaLN output: a [B, 6*dim] tensor chunked into six [B, 1, dim] views like the
+    blocks do (model.py:419-420); returns (shift_mlp, scale_mlp, gate_mlp), i.e. chunks 3, 4, 5."""
+    g = torch.Generator().manual_seed(seed)
+    ada = (torch.randn((batch, 6 * dim), generator=g, dtype=torch.float32) * 0.5).to(dtype)
+    chunks = ada[:, None].chunk(6, dim=-1)
+    return chunks[3], chunks[4], chunks[5]
+
+
 # ------------------------------------------------------------------------------------------- synthetic layers
 def make_layer(dim: int, hidden_dim: int, num_experts: int = 4, seed: int = 0, dtype: torch.dtype = torch.float32,
                std: float = 0.02) -> Layer:

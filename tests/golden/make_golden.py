@@ -90,6 +90,21 @@ def main(ref_root: str) -> None:
     run_case("bf16_shipped", m, xb, gate_in_fp32=False)
     run_case("bf16", m, xb, gate_in_fp32=True)
 
+    # feed-forward half of a block exactly as HiDreamImageSingleTransformerBlock.forward spells it
+    # (comfy/ldm/hidream/model.py:429-433), with the reference's LayerNorm op and the bf16 module built above
+    norm3 = comfy.ops.disable_weight_init.LayerNorm(DIM, eps=1e-06, elementwise_affine=False)
+    shift_mlp, scale_mlp, gate_mlp = O.make_modulation(BATCH, DIM)
+    with torch.no_grad():
+        image_tokens = xb
+        wtype = image_tokens.dtype
+        norm_image_tokens = norm3(image_tokens).to(dtype=wtype)
+        norm_image_tokens = norm_image_tokens * (1 + scale_mlp) + shift_mlp
+        ff_output_i = gate_mlp * m(norm_image_tokens.to(dtype=wtype))
+        out["block_bf16/normed"] = f32(norm_image_tokens.reshape(-1, DIM))
+        out["block_bf16/out"] = f32((ff_output_i + image_tokens).reshape(-1, DIM))
+        dense = gate_mlp * m.shared_experts(norm_image_tokens) + image_tokens
+        out["block_bf16/dense_out"] = f32(dense.reshape(-1, DIM))
+
     # scaled fp8 weights, three flavours of comfy.ops.scaled_fp8_ops
     layer8 = O.quantize_layer_fp8(layer16)
     ops = comfy.ops.scaled_fp8_ops(fp8_matrix_mult=False, scale_input=False, override_dtype=torch.float8_e4m3fn)

@@ -47,7 +47,7 @@ def test_struct_layouts_match_header():
 
     assert ctypes.sizeof(N.FfnWeights) == 3 * 8 + 2 * 8 + 2 * 4 + 5 * 8
     assert ctypes.sizeof(N.Layer) == 6 * 4 + 8 + (N.MAX_EXPERTS + 1) * ctypes.sizeof(N.FfnWeights)
-    assert ctypes.sizeof(N.Workspace) == 15 * 8
+    assert ctypes.sizeof(N.Workspace) == 16 * 8
 
 
 def test_plan_sizes(lib):

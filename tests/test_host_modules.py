@@ -151,3 +151,19 @@ def test_ffn_hidden_rounding():
     assert ffn.w1.weight.shape == (3584, 2560)
     g = MoEGate(64, 4, 2, dtype=torch.float32, device="cpu")
     assert g.weight.shape == (4, 64) and g.norm_topk_prob is False and g.top_k == 2
+
+
+def test_block_feed_forward_stock_path_matches_reference(golden):
+    """block_feed_forward with CPU tensors runs the stock composition: the reference block's lines, bit for bit."""
+    from comfyui_b200.ldm.hidream.model import block_feed_forward
+
+    mod, x, _ = _case(golden, torch.bfloat16, ops.disable_weight_init)
+    b, s, dim = x.shape
+    norm = ops.disable_weight_init.LayerNorm(dim, eps=1e-06, elementwise_affine=False)
+    shift, scale, gate = O.make_modulation(b, dim)
+    assert ops.hidream_block_ffn(norm, mod, x, shift, scale, gate) is None
+    with torch.no_grad():
+        out = block_feed_forward(norm, mod, x, shift, scale, gate)
+        dense = block_feed_forward(norm, mod.shared_experts, x, shift, scale, gate)
+    assert torch.equal(out.reshape(-1, dim).float(), torch.from_numpy(golden["block_bf16/out"]))
+    assert torch.equal(dense.reshape(-1, dim).float(), torch.from_numpy(golden["block_bf16/dense_out"]))

@@ -116,3 +116,17 @@ def test_empty_and_single_expert_routing():
     torch.testing.assert_close(out, ref, rtol=1e-5, atol=1e-6)
     masked = O.moe_forward_masked(x, idx, w, layer)
     torch.testing.assert_close(masked, ref, rtol=1e-5, atol=1e-6)
+
+
+def test_block_ffn_matches_reference(golden):
+    """LayerNorm + modulation + MoE + gate/residual as the single-stream block spells it (model.py:429-433)."""
+    m = golden["meta"]
+    b, s, dim = int(m["batch"]), int(m["seq"]), int(m["dim"])
+    x, layer = _setup(golden)
+    x = x.bfloat16().view(b, s, dim)
+    layer = {k: v.bfloat16() for k, v in layer.items()}
+    shift, scale, gate = O.make_modulation(b, dim)
+    out = O.block_ffn(x, layer, shift, scale, gate, gate_in_fp32=False, branch="masked")
+    assert torch.equal(out.reshape(-1, dim).float(), torch.from_numpy(golden["block_bf16/out"]))
+    dense = O.block_ffn(x, layer, shift, scale, gate, dense_prefix="shared_experts")
+    assert torch.equal(dense.reshape(-1, dim).float(), torch.from_numpy(golden["block_bf16/dense_out"]))
