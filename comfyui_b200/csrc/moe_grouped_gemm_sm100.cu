@@ -167,6 +167,27 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
   const uint32_t tmem_base = tmem_slot;
   const int total_tiles = s_tile_start[p.num_groups];
   volatile int* abort_ptr = &abort_flag;
+
+  // Which tiles this CTA (pair) computes, in order.  Tiles are dealt round-robin.  In pass 2 the trailing
+  // un-permuted group (the shared expert) has a shorter K than the routed groups, so its tiles cost about half:
+  // they are dealt in a second round-robin that first serves the workers that got one routed tile fewer, which
+  // evens out the load (12.1 -> 11.6 routed-tile units on the busiest worker for the HiDream shapes).
+  int main_tiles = total_tiles;
+  if (!kSwiglu && p.num_groups > 1 && p.groups[p.num_groups - 1].routed_index < 0)
+    main_tiles = s_tile_start[p.num_groups - 1];
+  const int my_main = unit < main_tiles ? (main_tiles - unit + n_units - 1) / n_units : 0;
+  const int rr = main_tiles % n_units;                        // workers [0, rr) hold one main tile more
+  const int light = n_units - rr;                             // number of workers served by the first partial round
+  const int pos = (unit - rr + n_units) % n_units;            // my place in the order rr, rr+1, ..., rr-1
+  auto tile_at = [&](int i) -> int {
+    if (i < my_main) return unit + i * n_units;
+    const int q = i - my_main;
+    int j;
+    if (pos < light) j = q == 0 ? pos : light + pos + (q - 1) * n_units;
+    else j = light + pos + q * n_units;
+    const int t = main_tiles + j;
+    return t < total_tiles ? t : -1;
+  };
   constexpr int kElemsPerRow = kFp8 ? kRowBytes : kRowBytes / 2;   // K elements per stage
 
   auto decode = [&](int t, int& g, int& m_tile, int& n_tile) {
@@ -195,7 +216,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
     // ------------------------------------------------------------------ TMA producer (both CTAs of a pair)
     uint32_t it = 0;
     bool ok = true;
-    for (int t = unit; t < total_tiles && ok; t += n_units) {
+    for (int i = 0, t; (t = tile_at(i)) >= 0 && ok; ++i) {
       int g, m_tile, n_tile;
       decode(t, g, m_tile, n_tile);
       const GemmGroup& grp = p.groups[g];
@@ -237,7 +258,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
       constexpr uint32_t idesc = umma_idesc<kFp8>(kTileM, kBlockN);
       uint32_t it = 0, tile_count = 0;
       bool ok = true;
-      for (int t = unit; t < total_tiles && ok; t += n_units, ++tile_count) {
+      for (int i = 0, t; (t = tile_at(i)) >= 0 && ok; ++i, ++tile_count) {
         int g, m_tile, n_tile;
         decode(t, g, m_tile, n_tile);
         const int kb_count = p.groups[g].k_blocks;
@@ -313,7 +334,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
     uint8_t* stage_row = stage_out + r_in_tile * 128;
     const int sw = r_in_tile & 7;
     uint32_t tile_count = 0;
-    for (int t = unit; t < total_tiles; t += n_units, ++tile_count) {
+    for (int i = 0, t; (t = tile_at(i)) >= 0; ++i, ++tile_count) {
       int g, m_tile, n_tile;
       decode(t, g, m_tile, n_tile);
       const GemmGroup& grp = p.groups[g];
@@ -563,11 +584,15 @@ template <bool kFp8, bool kSwiglu, int kCtas>
 static int launch_gemm_impl(const GemmParams& params, int64_t max_tiles, int sms, cudaStream_t stream) {
   auto kernel = grouped_gemm_kernel<kFp8, kSwiglu, kCtas>;
   constexpr size_t smem = GemmShape<kCtas>::kSmemBytes;
-  static bool configured = false;
-  if (!configured) {
+  // the shared-memory opt-in is a per-device property of the kernel
+  constexpr int kMaxDevices = 64;
+  static bool configured[kMaxDevices] = {false};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return COMFY_MOE_ECUDA;
+  if (dev < 0 || dev >= kMaxDevices || !configured[dev]) {
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
       return COMFY_MOE_ECUDA;
-    configured = true;
+    if (dev >= 0 && dev < kMaxDevices) configured[dev] = true;
   }
   int64_t units = sms / kCtas;
   if (max_tiles < units) units = max_tiles;
