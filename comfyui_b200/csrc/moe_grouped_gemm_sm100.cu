@@ -110,6 +110,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
   __shared__ __align__(8) uint64_t tmem_full_bar[kAccStages];
   __shared__ __align__(8) uint64_t tmem_empty_bar[kAccStages];
   __shared__ __align__(8) uint64_t drain_bar;
+  __shared__ __align__(8) uint64_t epi_bar;        // the four epilogue warps meet here (bounded, unlike bar.sync)
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
   __shared__ int s_tile_start[kMaxGroups + 1];
@@ -129,6 +130,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
     for (int s = 0; s < kStages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
     for (int s = 0; s < kAccStages; ++s) { mbar_init(&tmem_full_bar[s], 1); mbar_init(&tmem_empty_bar[s], 4 * kCtas); }
     mbar_init(&drain_bar, 1);
+    mbar_init(&epi_bar, 128);
     fence_mbar_init();
     abort_flag = 0;
     int start = 0;
@@ -333,8 +335,17 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
     const int r_in_tile = quarter * 32 + lane;
     uint8_t* stage_row = stage_out + r_in_tile * 128;
     const int sw = r_in_tile & 7;
+    uint32_t epi_phase = 0;
+    bool epi_ok = true;
+    // All 128 epilogue threads arrive and wait with the usual clock budget; a warp that gave up elsewhere can
+    // therefore never leave the others parked at a hardware barrier.
+    auto epi_sync = [&]() {
+      mbar_arrive(&epi_bar);
+      if (!mbar_wait_warp(&epi_bar, epi_phase, abort_ptr)) epi_ok = false;
+      epi_phase ^= 1u;
+    };
     uint32_t tile_count = 0;
-    for (int i = 0, t; (t = tile_at(i)) >= 0; ++i, ++tile_count) {
+    for (int i = 0, t; epi_ok && (t = tile_at(i)) >= 0; ++i, ++tile_count) {
       int g, m_tile, n_tile;
       decode(t, g, m_tile, n_tile);
       const GemmGroup& grp = p.groups[g];
@@ -367,7 +378,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
         const int col0 = n_tile * 128;
         if (tile_tma) {
           if (issuer) bulk_wait_read_all();         // the previous tile's store has finished reading the staging tile
-          named_bar_sync(1, 128);
+          epi_sync();
         }
 #pragma unroll 1
         for (int c = 0; c < 4; ++c) {
@@ -428,7 +439,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
         }
         if (tile_tma) {
           fence_proxy_async_smem();
-          named_bar_sync(1, 128);
+          epi_sync();
           if (issuer) {
             if constexpr (kFp8) {
               tma_store_2d(map_out, stage_out, col0, row0);
@@ -446,7 +457,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
         for (int half = 0; half < 2; ++half) {
           if (tile_tma) {
             if (issuer) bulk_wait_read_all();
-            named_bar_sync(1, 128);
+            epi_sync();
           }
 #pragma unroll 1
           for (int cc = 0; cc < 4; ++cc) {
@@ -486,7 +497,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
           }
           if (tile_tma) {
             fence_proxy_async_smem();
-            named_bar_sync(1, 128);
+            epi_sync();
             if (issuer) {
               tma_store_2d(map_out, stage_out, col0 + half * 128, row0);
               tma_store_2d(map_out, stage_out + kABytes, col0 + half * 128 + 64, row0);
@@ -496,6 +507,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
         }
       }
     }
+    if (!epi_ok && lane == 0) { atomicCAS(p.status, 0, kStatusEpilogueTimeout); abort_flag = 1; }
     if (issuer) bulk_wait_all();     // stores must have left shared memory (and landed) before the CTA exits
   }
 

@@ -114,11 +114,6 @@ __device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bu
 // all committed bulk stores of this thread have completed
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
-// barrier among a subset of the CTA's warps (id 1..15; 0 is __syncthreads)
-__device__ __forceinline__ void named_bar_sync(int id, int n_threads) {
-  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(n_threads) : "memory");
-}
-
 // ---------------------------------------------------------------- CTA pairs (clusters of two)
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
