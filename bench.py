@@ -223,7 +223,7 @@ def run_gpu_arm(args) -> None:
     else:
         assert ops._layer_pack(module, x) is not None, "bench: layer not eligible for the sm_100a kernels"
         step = lambda inp: module(inp)                      # noqa: E731
-        launches_per_step = 6   # gate, plan, permute, GEMM pass 1, GEMM pass 2, combine
+        launches_per_step = 5   # gate, plan + permute, GEMM pass 1, GEMM pass 2, combine
 
     def barrier():
         if world > 1:
@@ -355,7 +355,7 @@ def time_end_to_end(step, x_pinned, out_pinned, n, dev, steps, barrier):
 
 
 def time_stages(module, x2, steps, moe_ops, ops):
-    """Average duration of every kernel of the layer: the same six launches as comfy_moe_forward, issued through
+    """Average duration of every kernel of the layer: the launches of comfy_moe_forward (which fuses plan and permute into one), issued through
     the stage-level C-ABI entry points on a pre-allocated workspace with a CUDA event between stages.  All steps are
     queued before the one synchronisation at the end, so the events are not separated by host latency."""
     import ctypes

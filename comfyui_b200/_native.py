@@ -28,6 +28,7 @@ EXPORTS = (
     "comfy_moe_route_count",
     "comfy_moe_route_plan",
     "comfy_moe_permute",
+    "comfy_moe_plan_permute",
     "comfy_moe_route_static",
     "comfy_moe_grouped_swiglu",
     "comfy_moe_combine",
@@ -141,6 +142,10 @@ def load(build_if_missing: bool = False) -> ctypes.CDLL:
     lib.comfy_moe_permute.argtypes = [
         c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
         c_void_p, c_void_p,
+    ]
+    lib.comfy_moe_plan_permute.argtypes = [
+        c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+        c_void_p, c_void_p, c_void_p, c_void_p,
     ]
     lib.comfy_moe_route_static.argtypes = [
         c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,

@@ -34,8 +34,8 @@ struct BlockEpilogue {
   int tokens_per_batch;
 };
 
-// MOEFeedForwardSwiGLU.forward (comfy/ldm/hidream/model.py:307-325) as six launches on one stream:
-// gate, routing plan, permutation, two passes of the grouped GEMM, combine.
+// MOEFeedForwardSwiGLU.forward (comfy/ldm/hidream/model.py:307-325) as five launches on one stream:
+// gate, routing plan + permutation, two passes of the grouped GEMM, combine.
 static int forward_impl(const ComfyMoeLayer* L, const ComfyMoeWorkspace* ws, const void* x, int n_tokens, void* out,
                         void* stream, const BlockEpilogue* epi) {
   if (!L || !ws || n_tokens < 0) return COMFY_MOE_EINVAL;
@@ -59,13 +59,10 @@ static int forward_impl(const ComfyMoeLayer* L, const ComfyMoeWorkspace* ws, con
   rc = comfy_moe_gate_topk(x, L->w_gate, L->gate_dtype, n_tokens, L->dim, L->n_experts, L->top_k, ws->topk_idx,
                            ws->topk_weight, ws->block_counts, ws->status + 1, nullptr, 1e-6f, stream);
   if (rc != COMFY_MOE_OK) return rc;
-  rc = comfy_moe_route_plan(ws->block_counts, n_tokens, L->n_experts, ws->block_offsets, ws->expert_counts,
-                            ws->expert_offsets, stream);
-  if (rc != COMFY_MOE_OK) return rc;
-  rc = comfy_moe_permute(x, ws->topk_idx, ws->block_offsets, ws->expert_offsets, n_tokens, L->dim, L->n_experts,
-                         fp8 ? COMFY_MOE_FP8_E4M3 : COMFY_MOE_BF16, fp8 ? L->experts[0].scale_in13 : nullptr,
-                         ws->x_perm, fp8 ? ws->x_q : nullptr, fp8 ? L->shared.scale_in13 : nullptr, ws->row_map,
-                         stream);
+  rc = comfy_moe_plan_permute(x, ws->topk_idx, ws->block_counts, n_tokens, L->dim, L->n_experts,
+                              fp8 ? COMFY_MOE_FP8_E4M3 : COMFY_MOE_BF16, fp8 ? L->experts[0].scale_in13 : nullptr,
+                              ws->block_offsets, ws->expert_counts, ws->expert_offsets, ws->x_perm,
+                              fp8 ? ws->x_q : nullptr, fp8 ? L->shared.scale_in13 : nullptr, ws->row_map, stream);
   if (rc != COMFY_MOE_OK) return rc;
   rc = comfy_moe_grouped_swiglu(L->w_dtype, L->n_experts, L->experts, &L->shared, ws->expert_offsets,
                                 ws->expert_counts, ws->rows_cap, n_tokens, L->dim, ws->x_perm, ws->h_perm, ws->y_perm,

@@ -242,20 +242,71 @@ route_plan_kernel(const int32_t* __restrict__ block_counts, int n_blocks, int n_
 // chunk c of every row to both destinations, kTok rows in flight.
 // bf16: chunk = 8 elements (16 B in, 16 B out).  fp8: chunk = 16 elements (32 B in, 16 B out).
 // ------------------------------------------------------------------------------------------------
-template <bool kFp8>
+// kPlan: the routing plan is folded in.  Instead of reading block_offsets / expert_offsets (written by
+// route_plan_kernel) every block sums the per-block counts of the blocks before it and of all blocks itself
+// (n_blocks * E integers, a few KB from L2), which saves a launch and a serial single-block scan; block 0 also
+// publishes expert_counts / expert_offsets for the grouped GEMM.  Used for up to kFusedPlanMaxBlocks blocks.
+constexpr int kFusedPlanMaxBlocks = 2048;
+
+template <bool kFp8, bool kPlan>
 __global__ void __launch_bounds__(kMaxRowThreads)
 permute_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ topk_idx,
                const int32_t* __restrict__ block_offsets, const int32_t* __restrict__ expert_offsets,
                int n_tokens, int dim, int n_experts, const float* __restrict__ act_scale,
                void* __restrict__ x_perm, void* __restrict__ x_q, const float* __restrict__ x_q_scale,
-               int32_t* __restrict__ row_map) {
+               int32_t* __restrict__ row_map, const int32_t* __restrict__ block_counts, int n_blocks,
+               int32_t* __restrict__ expert_counts_out, int32_t* __restrict__ expert_offsets_out) {
   constexpr int kSlots = kTokensPerBlock * 2;  // 64
   constexpr int kTok = 8;
   __shared__ int dest_s[kSlots];
   __shared__ int warp_cnt[kSlots / 32][kMaxExperts];
+  __shared__ int s_before[kMaxExperts];      // rows of expert e that belong to earlier blocks
+  __shared__ int s_start[kMaxExperts];       // first row of expert e in the permuted layout
+  __shared__ int s_part[kMaxRowThreads / 32][2 * kMaxExperts];
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int block_tok0 = blockIdx.x * kTokensPerBlock;
+
+  if constexpr (kPlan) {
+    int acc[2 * kMaxExperts];               // [e] = counts of earlier blocks, [kMaxExperts + e] = counts of all blocks
+#pragma unroll
+    for (int k = 0; k < 2 * kMaxExperts; ++k) acc[k] = 0;
+    for (int b = tid; b < n_blocks; b += blockDim.x) {
+#pragma unroll
+      for (int e = 0; e < kMaxExperts; ++e) {
+        if (e < n_experts) {
+          const int c = __ldg(block_counts + b * n_experts + e);
+          acc[kMaxExperts + e] += c;
+          if (b < static_cast<int>(blockIdx.x)) acc[e] += c;
+        }
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < 2 * kMaxExperts; ++k) {
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) acc[k] += __shfl_xor_sync(0xffffffffu, acc[k], off);
+      if (lane == 0) s_part[warp][k] = acc[k];
+    }
+    __syncthreads();
+    if (tid == 0) {
+      const int n_warps = blockDim.x >> 5;
+      int row = 0;
+      for (int e = 0; e < n_experts; ++e) {
+        int before = 0, total = 0;
+        for (int w = 0; w < n_warps; ++w) { before += s_part[w][e]; total += s_part[w][kMaxExperts + e]; }
+        s_before[e] = before;
+        s_start[e] = row;
+        if (blockIdx.x == 0) { expert_counts_out[e] = total; expert_offsets_out[e] = row; }
+        row += (total + kRowAlign - 1) / kRowAlign * kRowAlign;
+      }
+      if (blockIdx.x == 0) expert_offsets_out[n_experts] = row;
+    }
+  } else {
+    if (tid < n_experts) {
+      s_before[tid] = block_offsets[blockIdx.x * n_experts + tid];
+      s_start[tid] = expert_offsets[tid];
+    }
+  }
 
   int my_e = -1, my_rank = 0;
   if (tid < kSlots) {
@@ -274,7 +325,7 @@ permute_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ 
     if (my_e >= 0) {
       int before = my_rank;
       for (int w = 0; w < warp; ++w) before += warp_cnt[w][my_e];
-      d = expert_offsets[my_e] + block_offsets[blockIdx.x * n_experts + my_e] + before;
+      d = s_start[my_e] + s_before[my_e] + before;
     }
     if (block_tok0 * 2 + tid < n_tokens * 2) row_map[block_tok0 * 2 + tid] = d;
     dest_s[tid] = d;
@@ -442,14 +493,54 @@ extern "C" int comfy_moe_permute(const void* x, const int32_t* topk_idx, const i
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (act_dtype == COMFY_MOE_BF16) {
     if ((dim & 7) != 0) return COMFY_MOE_EUNSUPPORTED;
-    permute_kernel<false><<<n_blocks, row_threads(dim), 0, s>>>(static_cast<const __nv_bfloat16*>(x), topk_idx,
-                                                                 block_offsets, expert_offsets, n_tokens, dim,
-                                                                 n_experts, nullptr, x_perm, nullptr, nullptr, row_map);
+    permute_kernel<false, false><<<n_blocks, row_threads(dim), 0, s>>>(
+        static_cast<const __nv_bfloat16*>(x), topk_idx, block_offsets, expert_offsets, n_tokens, dim, n_experts, nullptr,
+        x_perm, nullptr, nullptr, row_map, nullptr, 0, nullptr, nullptr);
   } else if (act_dtype == COMFY_MOE_FP8_E4M3) {
     if ((dim & 15) != 0) return COMFY_MOE_EUNSUPPORTED;
-    permute_kernel<true><<<n_blocks, row_threads(dim), 0, s>>>(static_cast<const __nv_bfloat16*>(x), topk_idx,
-                                                                block_offsets, expert_offsets, n_tokens, dim,
-                                                                n_experts, act_scale, x_perm, x_q, x_q_scale, row_map);
+    permute_kernel<true, false><<<n_blocks, row_threads(dim), 0, s>>>(
+        static_cast<const __nv_bfloat16*>(x), topk_idx, block_offsets, expert_offsets, n_tokens, dim, n_experts,
+        act_scale, x_perm, x_q, x_q_scale, row_map, nullptr, 0, nullptr, nullptr);
+  } else {
+    return COMFY_MOE_EUNSUPPORTED;
+  }
+  return check_launch();
+}
+
+// Routing plan and permutation in one launch (what comfy_moe_forward uses for up to kFusedPlanMaxBlocks blocks of
+// tokens); same outputs as comfy_moe_route_plan followed by comfy_moe_permute, block_offsets excepted.
+extern "C" int comfy_moe_plan_permute(const void* x, const int32_t* topk_idx, const int32_t* block_counts,
+                                      int n_tokens, int dim, int n_experts, int act_dtype, const float* act_scale,
+                                      int32_t* block_offsets_scratch, int32_t* expert_counts, int32_t* expert_offsets,
+                                      void* x_perm, void* x_q, const float* x_q_scale, int32_t* row_map, void* stream) {
+  if (n_tokens < 0 || dim <= 0 || n_experts < 1 || n_experts > kMaxExperts) return COMFY_MOE_EINVAL;
+  if (!expert_counts || !expert_offsets) return COMFY_MOE_EINVAL;
+  const int n_blocks = (n_tokens + kTokensPerBlock - 1) / kTokensPerBlock;
+  if (n_tokens == 0 || n_blocks > kFusedPlanMaxBlocks) {
+    // no rows, or too many blocks for every block to re-sum the counts: the two-launch form
+    int rc = comfy_moe_route_plan(block_counts, n_tokens, n_experts, block_offsets_scratch, expert_counts,
+                                  expert_offsets, stream);
+    if (rc != COMFY_MOE_OK) return rc;
+    return comfy_moe_permute(x, topk_idx, block_offsets_scratch, expert_offsets, n_tokens, dim, n_experts, act_dtype,
+                             act_scale, x_perm, x_q, x_q_scale, row_map, stream);
+  }
+  if (!x || !topk_idx || !block_counts || !x_perm || !row_map) return COMFY_MOE_EINVAL;
+  if (!aligned16(x) || !aligned16(x_perm) || (x_q && !aligned16(x_q))) return COMFY_MOE_EINVAL;
+  if ((dim >> 3) > kMaxRowThreads) return COMFY_MOE_EUNSUPPORTED;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const __nv_bfloat16* xp = static_cast<const __nv_bfloat16*>(x);
+  if (act_dtype == COMFY_MOE_BF16) {
+    if ((dim & 7) != 0) return COMFY_MOE_EUNSUPPORTED;
+    permute_kernel<false, true><<<n_blocks, row_threads(dim), 0, s>>>(xp, topk_idx, nullptr, nullptr, n_tokens, dim,
+                                                                       n_experts, nullptr, x_perm, nullptr, nullptr,
+                                                                       row_map, block_counts, n_blocks, expert_counts,
+                                                                       expert_offsets);
+  } else if (act_dtype == COMFY_MOE_FP8_E4M3) {
+    if ((dim & 15) != 0) return COMFY_MOE_EUNSUPPORTED;
+    permute_kernel<true, true><<<n_blocks, row_threads(dim), 0, s>>>(xp, topk_idx, nullptr, nullptr, n_tokens, dim,
+                                                                      n_experts, act_scale, x_perm, x_q, x_q_scale,
+                                                                      row_map, block_counts, n_blocks, expert_counts,
+                                                                      expert_offsets);
   } else {
     return COMFY_MOE_EUNSUPPORTED;
   }

@@ -9,7 +9,7 @@ HiDream transformer block can build these instead and load the same checkpoint:
 
 Every ``forward`` first offers the call to the dispatch shim in ``comfyui_b200.ops``; when the call is
 eligible (B200, bf16 activations, bf16 or scaled-e4m3 weights resident on the device, no LoRA closures)
-the whole layer runs as six kernel launches.  Otherwise the module's own PyTorch composition below runs,
+the whole layer runs as five kernel launches.  Otherwise the module's own PyTorch composition below runs,
 which is what the reference executes everywhere.
 
 One deliberate numerical difference on the kernel path: the gate is evaluated in fp32 on the bf16

@@ -267,6 +267,27 @@ def permute(x: torch.Tensor, topk_idx: torch.Tensor, block_offsets: torch.Tensor
     return x_perm, row_map, x_q
 
 
+def plan_permute(x: torch.Tensor, topk_idx: torch.Tensor, block_counts: torch.Tensor, n_experts: int, *,
+                 fp8: bool = False, zero_fill: bool = False):
+    """route_plan + permute in one launch.  Returns (x_perm, row_map, expert_counts, expert_offsets)."""
+    _need_cuda(x, topk_idx, block_counts)
+    n, d = x.shape
+    dev = x.device
+    rows_cap, _ = plan_sizes(n, n_experts)
+    alloc = torch.zeros if zero_fill else torch.empty
+    x_perm = alloc((rows_cap, d), dtype=torch.uint8, device=dev).view(_FP8) if fp8 else \
+        alloc((rows_cap, d), dtype=torch.bfloat16, device=dev)
+    row_map = torch.empty((n, 2), dtype=torch.int32, device=dev)
+    scratch = torch.empty_like(block_counts)
+    counts = torch.empty((n_experts,), dtype=torch.int32, device=dev)
+    offsets = torch.empty((n_experts + 1,), dtype=torch.int32, device=dev)
+    rc = N.load().comfy_moe_plan_permute(_ptr(x), _ptr(topk_idx), _ptr(block_counts), n, d, n_experts,
+                                         N.FP8_E4M3 if fp8 else N.BF16, None, _ptr(scratch), _ptr(counts),
+                                         _ptr(offsets), _ptr(x_perm), None, None, _ptr(row_map), _stream())
+    N.check("comfy_moe_plan_permute", rc)
+    return x_perm, row_map, counts, offsets
+
+
 def grouped_swiglu(experts: Sequence[FfnPack], shared: Optional[FfnPack], row_start: Optional[torch.Tensor],
                    row_count: Optional[torch.Tensor], x_perm: Optional[torch.Tensor],
                    x_shared: Optional[torch.Tensor], *, status: Optional[torch.Tensor] = None,

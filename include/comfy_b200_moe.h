@@ -105,6 +105,16 @@ int comfy_moe_permute(const void* x, const int32_t* topk_idx, const int32_t* blo
                       const float* act_scale, void* x_perm, void* x_q, const float* x_q_scale,
                       int32_t* row_map, void* stream);
 
+/* ---- routing plan and permutation in one launch: comfy_moe_route_plan + comfy_moe_permute -------------------
+ * Same outputs (expert_counts, expert_offsets, x_perm, x_q, row_map).  Every block re-sums the per-block counts it
+ * needs instead of waiting for a separate single-block scan; beyond 2048 blocks of tokens (65 536 tokens) the call
+ * falls back to the two launches and then uses block_offsets_scratch [n_blocks, n_experts].
+ */
+int comfy_moe_plan_permute(const void* x, const int32_t* topk_idx, const int32_t* block_counts, int n_tokens, int dim,
+                           int n_experts, int act_dtype, const float* act_scale, int32_t* block_offsets_scratch,
+                           int32_t* expert_counts, int32_t* expert_offsets, void* x_perm, void* x_q,
+                           const float* x_q_scale, int32_t* row_map, void* stream);
+
 /* ---- gate + routing plan + permutation for callers that cannot allocate device memory -----------------
  * (No counterpart in the reference: it has no allocation-free mode.)
  * Some hosts of this library may not call cudaMalloc or any allocator between set-up and tear-down: real-time
@@ -212,7 +222,7 @@ typedef struct ComfyMoeWorkspace {
   void* x_mod;             /* bf16 [n_tokens, dim]: normalised + modulated input; only comfy_moe_ffn_block needs it */
 } ComfyMoeWorkspace;
 
-/* ---- MOEFeedForwardSwiGLU.forward (model.py:307-325): gate -> plan -> permute -> experts -> combine ----
+/* ---- MOEFeedForwardSwiGLU.forward (model.py:307-325): gate -> plan+permute -> experts -> combine ----
  * x, out: bf16 [n_tokens, dim].  The layer struct and the workspace struct live in HOST memory.
  */
 int comfy_moe_forward(const ComfyMoeLayer* h_layer, const ComfyMoeWorkspace* h_ws, const void* x, int n_tokens,
@@ -236,7 +246,7 @@ int comfy_moe_combine_block(const void* y_perm, const int32_t* row_map, const fl
                             const void* gate, int64_t gate_batch_stride, const void* residual, int n_tokens,
                             int tokens_per_batch, int dim, void* out, void* stream);
 
-/* ---- feed-forward half of a HiDream block with a MoE (model.py:429-433 / 515-523), seven launches ----------
+/* ---- feed-forward half of a HiDream block with a MoE (model.py:429-433 / 515-523), six launches ----------
  *   out = gate * MOEFeedForwardSwiGLU(LayerNorm(x) * (1 + scale) + shift) + x
  * x, out: bf16 [n_tokens, dim] (out may alias nothing else); h_ws->x_mod must be set.
  */

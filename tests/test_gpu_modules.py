@@ -190,3 +190,33 @@ def test_block_feed_forward_on_kernels(cuda_device, golden):
     gref = torch.from_numpy(golden["block_bf16/out"])
     close = (gout.float() - gref).abs() <= 2e-2 + 2e-2 * gref.abs()
     assert int((~close).any(dim=-1).sum()) <= 3
+
+
+def test_layer_call_replays_from_a_cuda_graph(cuda_device):
+    """The layer makes no host synchronisation and, once its workspace exists, no allocation of its own, so a
+    sampler can record the call into a CUDA graph and replay it with new inputs."""
+    from comfyui_b200 import ops
+
+    dev = cuda_device
+    dim, hidden_dim, n = 512, 2048, 640
+    layer = {k: v.bfloat16() for k, v in O.make_layer(dim, hidden_dim, 4, seed=0).items()}
+    mod = _module(dev, dim, hidden_dim, ops.disable_weight_init, layer)
+    x_static = O.make_input(n, dim, seed=1).bfloat16().to(dev).view(1, n, dim)
+    side = torch.cuda.Stream(device=dev)
+    with torch.inference_mode():
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):          # warm-up on the capture stream: workspace, function attributes
+            for _ in range(2):
+                mod(x_static)
+        torch.cuda.current_stream().wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            y_static = mod(x_static)
+        for seed in (7, 8):
+            x_new = O.make_input(n, dim, seed=seed).bfloat16().to(dev).view(1, n, dim)
+            x_static.copy_(x_new)
+            graph.replay()
+            torch.cuda.synchronize()
+            eager = mod(x_new)
+            assert torch.equal(y_static, eager)
+    ops.release_workspaces()

@@ -90,6 +90,11 @@ def test_gate_plan_permute_combine(M, cuda_device, n, d, e):
         assert bool((r[1:] > r[:-1]).all())
     assert torch.equal(x_perm.cpu()[rm], x.repeat_interleave(2, dim=0))
 
+    # plan and permutation fused into one launch: identical outputs
+    xp_f, rm_f, ec_f, eo_f = M.plan_permute(x.to(dev), idx, counts, e, zero_fill=True)
+    assert torch.equal(xp_f, x_perm) and torch.equal(rm_f, row_map)
+    assert torch.equal(ec_f, expert_counts) and torch.equal(eo_f, expert_offsets)
+
     # fp8 permutation = the reference's clamp + cast (comfy/ops.py:338-340), with and without scale_input
     xq_ref = x.float().clamp(-448, 448).to(torch.float8_e4m3fn)
     xp8, rm8, xq = M.permute(x.to(dev), idx, block_offsets, expert_offsets, e, fp8=True, want_xq=True, zero_fill=True)
