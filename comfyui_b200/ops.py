@@ -278,8 +278,6 @@ ENABLE_SM100_KERNELS = True
 # Read the device status word (one stream synchronisation) after every fused call; for debugging.
 CHECK_STATUS_EVERY_CALL = False
 
-_workspaces = {}
-_WORKSPACE_SLOTS = 4
 
 
 def _tensor_key(t: Optional[torch.Tensor]):
@@ -373,36 +371,41 @@ def _layer_pack(moe, x):
 
 
 def _workspace(layer, n_tokens: int):
-    from . import moe_ops
+    from . import torch_ops
 
-    key = (n_tokens, layer.dim, layer.n_experts, layer.experts[0].hidden, layer.shared.hidden, layer.fp8,
-           layer.gate.device, torch.cuda.current_stream().cuda_stream)
-    ws = _workspaces.get(key)
-    if ws is None:
-        while len(_workspaces) >= _WORKSPACE_SLOTS:
-            _workspaces.pop(next(iter(_workspaces)))
-        ws = moe_ops.Workspace.for_layer(layer, n_tokens)
-        _workspaces[key] = ws
-    return ws
+    return torch_ops._workspace(layer, n_tokens)
 
 
 def release_workspaces() -> None:
     """Drop the cached device workspaces (they are shared by every MoE layer of a model)."""
-    _workspaces.clear()
+    from . import torch_ops
+
+    torch_ops.release_workspaces()
+
+
+def _op_args(layer):
+    """List arguments of the registered torch ops for this layer, cached on the pack."""
+    from . import torch_ops
+
+    args = getattr(layer, "_op_args", None)
+    if args is None:
+        args = torch_ops.layer_args(layer)
+        layer._op_args = args
+    return args
 
 
 def hidream_moe_forward(moe, x: torch.Tensor) -> Optional[torch.Tensor]:
-    """MOEFeedForwardSwiGLU.forward on the sm_100a kernels, or None when this call is not eligible."""
+    """MOEFeedForwardSwiGLU.forward on the sm_100a kernels, or None when this call is not eligible.
+    Goes through the registered operator ``torch.ops.comfyui_b200.hidream_moe``."""
     layer = _layer_pack(moe, x)
     if layer is None:
         return None
-    from . import moe_ops
+    from . import moe_ops, torch_ops  # noqa: F401  (importing torch_ops registers the operators)
 
     x2 = x.view(-1, x.shape[-1])
-    ws = _workspace(layer, x2.shape[0])
-    out = moe_ops.moe_forward(layer, x2, ws)
+    out = torch.ops.comfyui_b200.hidream_moe(x2, layer.gate, *_op_args(layer))
     if CHECK_STATUS_EVERY_CALL:
-        moe_ops.read_status(ws.status)
+        moe_ops.read_status(_workspace(layer, x2.shape[0]).status)
     return out.view(x.shape)
 
 
@@ -413,10 +416,10 @@ def hidream_gate(gate, x: torch.Tensor):
         return None
     if w.device != x.device or w.dtype not in (torch.bfloat16, torch.float32):
         return None
-    from . import moe_ops
+    from . import torch_ops  # noqa: F401  (registers the operators)
 
-    idx, weight, _, _, _ = moe_ops.gate_topk(x.view(-1, x.shape[-1]), w.detach())
-    return idx.to(torch.int64), weight.to(x.dtype)
+    idx, weight = torch.ops.comfyui_b200.hidream_gate(x.view(-1, x.shape[-1]), w.detach())
+    return idx, weight.to(x.dtype)
 
 
 def hidream_moe_infer(moe, x: torch.Tensor, flat_expert_indices: torch.Tensor,
@@ -489,10 +492,12 @@ def hidream_block_ffn(norm, ff, x: torch.Tensor, shift: torch.Tensor, scale: tor
         layer = _layer_pack(ff, x)
         if layer is None:
             return None
-        ws = _workspace(layer, x2.shape[0])
-        out = moe_ops.moe_ffn_block(layer, x2, shift, scale, gate, s, norm.eps, ws)
+        from . import torch_ops  # noqa: F401  (registers the operators)
+
+        out = torch.ops.comfyui_b200.hidream_moe_block(x2, shift, scale, gate, s, float(norm.eps), layer.gate,
+                                                       *_op_args(layer))
         if CHECK_STATUS_EVERY_CALL:
-            moe_ops.read_status(ws.status)
+            moe_ops.read_status(_workspace(layer, x2.shape[0]).status)
         return out.view(x.shape)
     if not _input_ok(x, ff.w1.weight.shape[1]):
         return None

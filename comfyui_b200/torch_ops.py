@@ -1,0 +1,123 @@
+"""torch.library registration of the C-ABI kernels (namespace ``comfyui_b200``).
+
+The dispatch shim in ``comfyui_b200.ops`` calls these ops, so the layer shows up in PyTorch's dispatcher like any
+other operator: it can be traced (fake / meta implementations give shapes and dtypes without touching a GPU), and
+profilers attribute its time to one named op.  The real implementations only marshal pointers into the shared
+library; there is no PyTorch arithmetic behind them.
+
+Weights travel as lists with one entry per routed expert followed by the shared expert (E + 1 entries):
+``w1``, ``w3``, ``w2`` and, for scaled fp8, ``scale_w1``, ``scale_w3``, ``scale_w2`` (fp32 scalars; empty lists for bf16)
+plus ``scale_in13`` / ``scale_in2`` (either empty, or E + 1 entries).
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Sequence
+
+import torch
+
+from . import moe_ops
+
+_packs = {}
+_PACK_SLOTS = 128      # a HiDream model has 48 MoE layers
+
+
+def _key(tensors: Sequence[torch.Tensor]):
+    return tuple((t.data_ptr(), t._version, t.dtype, tuple(t.shape), t.stride(0) if t.dim() else 0) for t in tensors)
+
+
+def _opt(lst: List[torch.Tensor], i: int) -> Optional[torch.Tensor]:
+    return lst[i] if lst else None
+
+
+def _layer(gate, w1, w3, w2, scale_w1, scale_w3, scale_w2, scale_in13, scale_in2) -> moe_ops.LayerPack:
+    """LayerPack for these tensors, cached on their identity and version."""
+    all_t = [gate, *w1, *w3, *w2, *scale_w1, *scale_w3, *scale_w2, *scale_in13, *scale_in2]
+    key = _key(all_t)
+    hit = _packs.get(key)
+    if hit is not None:
+        return hit
+    ffns = [moe_ops.FfnPack(w1[i], w3[i], w2[i], scale_w1=_opt(scale_w1, i), scale_w3=_opt(scale_w3, i),
+                            scale_w2=_opt(scale_w2, i), scale_in13=_opt(scale_in13, i), scale_in2=_opt(scale_in2, i))
+            for i in range(len(w1))]
+    layer = moe_ops.LayerPack(gate, ffns[:-1], ffns[-1], top_k=2)
+    while len(_packs) >= _PACK_SLOTS:
+        _packs.pop(next(iter(_packs)))
+    _packs[key] = layer
+    return layer
+
+
+_workspaces = {}
+
+
+def _workspace(layer: moe_ops.LayerPack, n_tokens: int) -> moe_ops.Workspace:
+    key = (n_tokens, layer.dim, layer.n_experts, layer.experts[0].hidden, layer.shared.hidden, layer.fp8,
+           layer.gate.device, torch.cuda.current_stream().cuda_stream)
+    ws = _workspaces.get(key)
+    if ws is None:
+        while len(_workspaces) >= 4:
+            _workspaces.pop(next(iter(_workspaces)))
+        ws = moe_ops.Workspace.for_layer(layer, n_tokens)
+        _workspaces[key] = ws
+    return ws
+
+
+def release_workspaces() -> None:
+    _workspaces.clear()
+    _packs.clear()
+
+
+@torch.library.custom_op("comfyui_b200::hidream_moe", mutates_args=())
+def hidream_moe(x: torch.Tensor, gate: torch.Tensor, w1: List[torch.Tensor], w3: List[torch.Tensor],
+                w2: List[torch.Tensor], scale_w1: List[torch.Tensor], scale_w3: List[torch.Tensor],
+                scale_w2: List[torch.Tensor], scale_in13: List[torch.Tensor],
+                scale_in2: List[torch.Tensor]) -> torch.Tensor:
+    """MOEFeedForwardSwiGLU.forward on x [N, D] (bf16, contiguous, CUDA)."""
+    layer = _layer(gate, w1, w3, w2, scale_w1, scale_w3, scale_w2, scale_in13, scale_in2)
+    return moe_ops.moe_forward(layer, x, _workspace(layer, x.shape[0]))
+
+
+@hidream_moe.register_fake
+def _(x, gate, w1, w3, w2, scale_w1, scale_w3, scale_w2, scale_in13, scale_in2):
+    return torch.empty_like(x)
+
+
+@torch.library.custom_op("comfyui_b200::hidream_moe_block", mutates_args=())
+def hidream_moe_block(x: torch.Tensor, shift: torch.Tensor, scale: torch.Tensor, gate_mlp: torch.Tensor,
+                      tokens_per_batch: int, eps: float, gate: torch.Tensor, w1: List[torch.Tensor],
+                      w3: List[torch.Tensor], w2: List[torch.Tensor], scale_w1: List[torch.Tensor],
+                      scale_w3: List[torch.Tensor], scale_w2: List[torch.Tensor], scale_in13: List[torch.Tensor],
+                      scale_in2: List[torch.Tensor]) -> torch.Tensor:
+    """gate_mlp * MoE(LayerNorm(x) * (1 + scale) + shift) + x on x [N, D]."""
+    layer = _layer(gate, w1, w3, w2, scale_w1, scale_w3, scale_w2, scale_in13, scale_in2)
+    return moe_ops.moe_ffn_block(layer, x, shift, scale, gate_mlp, tokens_per_batch, eps, _workspace(layer, x.shape[0]))
+
+
+@hidream_moe_block.register_fake
+def _(x, shift, scale, gate_mlp, tokens_per_batch, eps, gate, w1, w3, w2, scale_w1, scale_w3, scale_w2, scale_in13,
+      scale_in2):
+    return torch.empty_like(x)
+
+
+@torch.library.custom_op("comfyui_b200::hidream_gate", mutates_args=())
+def hidream_gate(x: torch.Tensor, gate: torch.Tensor) -> List[torch.Tensor]:
+    """MoEGate.forward on x [N, D]: [topk_idx int64 [N, 2], topk_weight fp32 [N, 2]]."""
+    idx, weight, _, _, _ = moe_ops.gate_topk(x, gate)
+    return [idx.to(torch.int64), weight]
+
+
+@hidream_gate.register_fake
+def _(x, gate):
+    n = x.shape[0]
+    return [x.new_empty((n, 2), dtype=torch.int64), x.new_empty((n, 2), dtype=torch.float32)]
+
+
+def layer_args(layer: moe_ops.LayerPack):
+    """The list arguments of the ops above for a LayerPack (routed experts first, shared expert last)."""
+    ffns = list(layer.experts) + [layer.shared]
+
+    def col(name):
+        vals = [getattr(f, name) for f in ffns]
+        return [] if any(v is None for v in vals) else vals
+
+    return ([f.w1 for f in ffns], [f.w3 for f in ffns], [f.w2 for f in ffns], col("scale_w1"), col("scale_w3"),
+            col("scale_w2"), col("scale_in13"), col("scale_in2"))

@@ -167,3 +167,22 @@ def test_block_feed_forward_stock_path_matches_reference(golden):
         dense = block_feed_forward(norm, mod.shared_experts, x, shift, scale, gate)
     assert torch.equal(out.reshape(-1, dim).float(), torch.from_numpy(golden["block_bf16/out"]))
     assert torch.equal(dense.reshape(-1, dim).float(), torch.from_numpy(golden["block_bf16/dense_out"]))
+
+
+def test_registered_torch_ops_trace_without_a_gpu():
+    """The kernels are registered with torch.library; their fake implementations give shapes and dtypes on the
+    meta device, so tracing a model that contains the layer needs no GPU."""
+    from comfyui_b200 import torch_ops  # noqa: F401
+
+    meta = dict(dtype=torch.bfloat16, device="meta")
+    x, gate = torch.empty(64, 256, **meta), torch.empty(4, 256, **meta)
+    w13, w2 = [torch.empty(768, 256, **meta)] * 5, [torch.empty(256, 768, **meta)] * 5
+    out = torch.ops.comfyui_b200.hidream_moe(x, gate, w13, w13, w2, [], [], [], [], [])
+    assert out.shape == x.shape and out.dtype == torch.bfloat16
+    idx, w = torch.ops.comfyui_b200.hidream_gate(x, gate)
+    assert idx.shape == (64, 2) and idx.dtype == torch.int64 and w.dtype == torch.float32
+    mod = torch.empty(2, 256, **meta)
+    blk = torch.ops.comfyui_b200.hidream_moe_block(x, mod, mod, mod, 32, 1e-6, gate, w13, w13, w2, [], [], [], [], [])
+    assert blk.shape == x.shape
+    schema = str(torch.ops.comfyui_b200.hidream_moe.default._schema)
+    assert "Tensor[] w1" in schema and "-> Tensor" in schema
