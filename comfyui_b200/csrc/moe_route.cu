@@ -3,9 +3,8 @@
 // replace comfy/ldm/hidream/model.py:263-283 (MoEGate.forward) and :330-339 (argsort,
 // bincount, cumsum on the host, row gathers) without any host synchronisation.
 //
-// Gate and permutation share one thread mapping: a block owns kTokensPerBlock consecutive
-// tokens and thread c owns the 16-byte chunk c of every row (columns 8c .. 8c+7), so a warp
-// touches 512 contiguous bytes per access and several rows are in flight per thread.
+// A block owns kTokensPerBlock consecutive tokens in both the gate and the permutation; every access is a
+// 16-byte chunk per lane, 512 contiguous bytes per warp, with several rows in flight per thread.
 #include "moe_common.cuh"
 
 namespace comfy_b200 {
@@ -15,141 +14,118 @@ constexpr int kMaxRowThreads = 512;    // dim / 8 threads per block: dim <= 4096
 __host__ __device__ constexpr int round_up32(int v) { return (v + 31) & ~31; }
 
 // ------------------------------------------------------------------------------------------------
-// Gate.  Every thread keeps its 8 columns of the gate weight of all experts in registers (fp32).
-// A round handles kTok = 32 / E tokens: each thread forms the kTok x E = 32 partial dot products of
-// its chunk, a butterfly exchange reduces them across the warp so that lane l ends up with the
-// warp's sum of partial l (31 shuffles instead of 160), one float per lane goes to shared memory,
-// and after the barrier warp 0 finishes the round: lane l = (token l / E, expert l % E) sums the
-// warps' partials in a fixed order, the E lanes of a token do softmax, ranking and the near-tie
-// test with shuffles.  The loads of the next round are issued before the reduction of the current
-// one.  Summation order is fixed, so the result is reproducible.
+// Gate.  The gate weight sits in shared memory (as stored: bf16 or fp32); a warp
+// handles two tokens at a time, lane l owning chunks l, l + 32, ... of both rows (up to 20 sixteen-byte
+// loads in flight per lane), so no block barrier separates the rows; the 2 x E dot products are reduced
+// with shuffles and every lane finishes softmax / top-2 redundantly.
 // ------------------------------------------------------------------------------------------------
-template <int E>
-__global__ void __launch_bounds__(kMaxRowThreads)
-gate_topk_kernel(const __nv_bfloat16* __restrict__ x, const void* __restrict__ w_gate, int w_dtype, int n_tokens,
-                 int dim, int32_t* __restrict__ topk_idx, float* __restrict__ topk_weight,
-                 int32_t* __restrict__ block_counts, int32_t* __restrict__ neartie_count,
-                 uint8_t* __restrict__ neartie_flags, float neartie_eps) {
-  static_assert(E == 2 || E == 4 || E == 8, "a token's experts must fill a power-of-two group of lanes");
-  constexpr int kTok = 32 / E;                         // tokens per round
-  constexpr int kRounds = kTokensPerBlock / kTok;
-  constexpr bool kPrefetch = kTok <= 8;                // 16 rows in flight twice would not fit the registers
-  constexpr int kMaxWarps = kMaxRowThreads / 32;
-  __shared__ float part[2][kMaxWarps][32];             // double-buffered per-warp partial logits
+constexpr int kGateWarpThreads = 256;
+constexpr int kGateWarpBatch = 10;
+
+template <int E, bool kW32>
+__global__ void __launch_bounds__(kGateWarpThreads)
+gate_topk_kernel(const __nv_bfloat16* __restrict__ x, const void* __restrict__ w_gate, int n_tokens, int dim,
+                      int32_t* __restrict__ topk_idx, float* __restrict__ topk_weight,
+                      int32_t* __restrict__ block_counts, int32_t* __restrict__ neartie_count,
+                      uint8_t* __restrict__ neartie_flags, float neartie_eps) {
+  extern __shared__ uint4 w_s[];                       // E rows of dim elements, 16-byte vectors
   __shared__ int hist[E];
-
+  constexpr int kTokPerWarp = kTokensPerBlock / (kGateWarpThreads / 32);   // 4
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int n_warps = blockDim.x >> 5;
   const int chunks = dim >> 3;
-  const bool active = tid < chunks;
-
-  float wreg[E][8];
-#pragma unroll
-  for (int e = 0; e < E; ++e) {
-    if (!active) {
-#pragma unroll
-      for (int k = 0; k < 8; ++k) wreg[e][k] = 0.f;
-    } else if (w_dtype == COMFY_MOE_FP32) {
-      const float4* w = reinterpret_cast<const float4*>(static_cast<const float*>(w_gate) + static_cast<size_t>(e) * dim) + 2 * tid;
-      const float4 a = w[0], b = w[1];
-      wreg[e][0] = a.x; wreg[e][1] = a.y; wreg[e][2] = a.z; wreg[e][3] = a.w;
-      wreg[e][4] = b.x; wreg[e][5] = b.y; wreg[e][6] = b.z; wreg[e][7] = b.w;
-    } else {
-      const uint4 v = *(reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(w_gate) + static_cast<size_t>(e) * dim) + tid);
-      unpack_bf16x8(v, wreg[e]);
-    }
+  const int row_vecs = kW32 ? chunks * 2 : chunks;     // 16-byte vectors per weight row
+  {
+    const uint4* src = static_cast<const uint4*>(w_gate);
+    for (int i = tid; i < E * row_vecs; i += kGateWarpThreads) w_s[i] = src[i];
   }
   if (tid < E) hist[tid] = 0;
   __syncthreads();
 
   const int block_tok0 = blockIdx.x * kTokensPerBlock;
-  auto load_round = [&](uint4 (&v)[kTok], int round) {
-#pragma unroll
-    for (int i = 0; i < kTok; ++i) {
-      const int t = block_tok0 + round * kTok + i;
-      v[i] = (active && t < n_tokens) ? ld_nc_u4(reinterpret_cast<const uint4*>(x + static_cast<size_t>(t) * dim) + tid)
-                                      : make_uint4(0, 0, 0, 0);
-    }
-  };
-
-  uint4 v[kTok], vn[kPrefetch ? kTok : 1];
-  load_round(v, 0);
 #pragma unroll 1
-  for (int round = 0; round < kRounds; ++round) {
-    const int t0 = block_tok0 + round * kTok;
-    if (t0 >= n_tokens) break;                          // uniform across the block
-    const int buf = round & 1;
-    if constexpr (kPrefetch) {
-      if (round + 1 < kRounds) load_round(vn, round + 1);
-    }
-    float pl[32];                                       // partial logit of (token i, expert e) at i * E + e
+  for (int pair = 0; pair < kTokPerWarp / 2; ++pair) {
+    const int t0 = block_tok0 + warp * kTokPerWarp + pair * 2;
+    if (t0 >= n_tokens) break;
+    const bool has1 = t0 + 1 < n_tokens;
+    const uint4* r0 = reinterpret_cast<const uint4*>(x + static_cast<size_t>(t0) * dim);
+    const uint4* r1 = reinterpret_cast<const uint4*>(x + static_cast<size_t>(has1 ? t0 + 1 : t0) * dim);
+    float acc0[E], acc1[E];
 #pragma unroll
-    for (int i = 0; i < kTok; ++i) {
-      float f[8];
-      unpack_bf16x8(v[i], f);
+    for (int e = 0; e < E; ++e) { acc0[e] = 0.f; acc1[e] = 0.f; }
+    for (int c0 = lane; c0 < chunks; c0 += 32 * kGateWarpBatch) {
+      uint4 v0[kGateWarpBatch], v1[kGateWarpBatch];
 #pragma unroll
-      for (int e = 0; e < E; ++e) {
-        float acc = 0.f;
-#pragma unroll
-        for (int k = 0; k < 8; ++k) acc = fmaf(f[k], wreg[e][k], acc);
-        pl[i * E + e] = acc;
+      for (int j = 0; j < kGateWarpBatch; ++j) {
+        const int c = c0 + 32 * j;
+        if (c < chunks) { v0[j] = ld_nc_u4(r0 + c); v1[j] = ld_nc_u4(r1 + c); }
       }
-    }
-    // butterfly: after the step with distance h a lane keeps the half of its values whose index has the
-    // same bit h as its lane id; at the end lane l holds the warp-wide sum of value l
 #pragma unroll
-    for (int h = 16; h >= 1; h >>= 1) {
-      const bool upper = (lane & h) != 0;
+      for (int j = 0; j < kGateWarpBatch; ++j) {
+        const int c = c0 + 32 * j;
+        if (c < chunks) {
+          float f0[8], f1[8];
+          unpack_bf16x8(v0[j], f0);
+          unpack_bf16x8(v1[j], f1);
 #pragma unroll
-      for (int j = 0; j < h; ++j) {
-        const float send = upper ? pl[j] : pl[j + h];
-        const float keep = upper ? pl[j + h] : pl[j];
-        pl[j] = keep + __shfl_xor_sync(0xffffffffu, send, h);
-      }
-    }
-    part[buf][warp][lane] = pl[0];
-    __syncthreads();
-    if (warp == 0) {
-      float logit = 0.f;
-      for (int w = 0; w < n_warps; ++w) logit += part[buf][w][lane];
-      const int e = lane % E;
-      const int t = t0 + lane / E;
-      float mx = logit;
+          for (int e = 0; e < E; ++e) {
+            float wv[8];
+            if constexpr (kW32) {
+              const float4 a = reinterpret_cast<const float4*>(w_s)[e * row_vecs + 2 * c];
+              const float4 b = reinterpret_cast<const float4*>(w_s)[e * row_vecs + 2 * c + 1];
+              wv[0] = a.x; wv[1] = a.y; wv[2] = a.z; wv[3] = a.w; wv[4] = b.x; wv[5] = b.y; wv[6] = b.z; wv[7] = b.w;
+            } else {
+              unpack_bf16x8(w_s[e * row_vecs + c], wv);
+            }
 #pragma unroll
-      for (int off = 1; off < E; off <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
-      const float ex = expf(logit - mx);
-      float sum = ex;
-#pragma unroll
-      for (int off = 1; off < E; off <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
-      const float s = ex / sum;
-      // rank inside the token's group: larger score first, lower expert index first on exact ties
-      int rank = 0;
-#pragma unroll
-      for (int o = 1; o < E; ++o) {
-        const float so = __shfl_xor_sync(0xffffffffu, s, o);
-        const int eo = e ^ o;
-        rank += (so > s || (so == s && eo < e)) ? 1 : 0;
-      }
-      float third = (rank == 2) ? s : -1.f;
-#pragma unroll
-      for (int off = 1; off < E; off <<= 1) third = fmaxf(third, __shfl_xor_sync(0xffffffffu, third, off));
-      if (t < n_tokens && rank < 2) {
-        topk_idx[2 * t + rank] = e;
-        topk_weight[2 * t + rank] = s;
-        atomicAdd(&hist[e], 1);                          // integer atomics: order does not matter
-        if (rank == 1) {
-          const bool tie = (E > 2) && (s - third < neartie_eps);
-          if (neartie_flags) neartie_flags[t] = tie ? 1 : 0;
-          if (tie && neartie_count) atomicAdd(neartie_count, 1);
+            for (int k = 0; k < 8; ++k) {
+              acc0[e] = fmaf(f0[k], wv[k], acc0[e]);
+              acc1[e] = fmaf(f1[k], wv[k], acc1[e]);
+            }
+          }
         }
       }
     }
-    // the next round writes the other buffer; the one after that is fenced by the barrier in between
-    if constexpr (kPrefetch) {
 #pragma unroll
-      for (int i = 0; i < kTok; ++i) v[i] = vn[i];
-    } else {
-      if (round + 1 < kRounds) load_round(v, round + 1);
+    for (int e = 0; e < E; ++e) {
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) {
+        acc0[e] += __shfl_xor_sync(0xffffffffu, acc0[e], off);
+        acc1[e] += __shfl_xor_sync(0xffffffffu, acc1[e], off);
+      }
+    }
+#pragma unroll
+    for (int which = 0; which < 2; ++which) {
+      if (which == 1 && !has1) break;
+      const int t = t0 + which;
+      float sc[E];
+      float mx = -INFINITY;
+#pragma unroll
+      for (int e = 0; e < E; ++e) { sc[e] = which == 0 ? acc0[e] : acc1[e]; mx = fmaxf(mx, sc[e]); }
+      float sum = 0.f;
+#pragma unroll
+      for (int e = 0; e < E; ++e) { sc[e] = expf(sc[e] - mx); sum += sc[e]; }
+#pragma unroll
+      for (int e = 0; e < E; ++e) sc[e] = sc[e] / sum;
+      int i0 = 0;                                        // strict '>' keeps the lowest index on exact ties
+#pragma unroll
+      for (int e = 1; e < E; ++e) if (sc[e] > sc[i0]) i0 = e;
+      int i1 = (i0 == 0) ? 1 : 0;
+#pragma unroll
+      for (int e = 0; e < E; ++e) if (e != i0 && e != i1 && sc[e] > sc[i1]) i1 = e;
+      float third = -1.f;
+#pragma unroll
+      for (int e = 0; e < E; ++e) if (e != i0 && e != i1) third = fmaxf(third, sc[e]);
+      if (lane == 0) {
+        topk_idx[2 * t] = i0;
+        topk_idx[2 * t + 1] = i1;
+        topk_weight[2 * t] = sc[i0];
+        topk_weight[2 * t + 1] = sc[i1];
+        atomicAdd(&hist[i0], 1);
+        atomicAdd(&hist[i1], 1);
+        const bool tie = (E > 2) && (sc[i1] - third < neartie_eps);
+        if (neartie_flags) neartie_flags[t] = tie ? 1 : 0;
+        if (tie && neartie_count) atomicAdd(neartie_count, 1);
+      }
     }
   }
   __syncthreads();
@@ -432,9 +408,16 @@ static int launch_gate(const void* x, const void* w_gate, int w_dtype, int n_tok
                        float* topk_weight, int32_t* block_counts, int32_t* neartie_count, uint8_t* neartie_flags,
                        float neartie_eps, cudaStream_t stream) {
   const int n_blocks = (n_tokens + kTokensPerBlock - 1) / kTokensPerBlock;
-  gate_topk_kernel<E><<<n_blocks, row_threads(dim), 0, stream>>>(
-      static_cast<const __nv_bfloat16*>(x), w_gate, w_dtype, n_tokens, dim, topk_idx, topk_weight, block_counts,
-      neartie_count, neartie_flags, neartie_eps);
+  const bool w32 = w_dtype == COMFY_MOE_FP32;
+  const size_t smem = static_cast<size_t>(E) * dim * (w32 ? 4 : 2);
+  if (smem > 200 * 1024) return COMFY_MOE_EUNSUPPORTED;
+  auto kern = w32 ? gate_topk_kernel<E, true> : gate_topk_kernel<E, false>;
+  if (smem > 48 * 1024 &&
+      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
+    return COMFY_MOE_ECUDA;
+  kern<<<n_blocks, kGateWarpThreads, smem, stream>>>(static_cast<const __nv_bfloat16*>(x), w_gate, n_tokens, dim,
+                                                      topk_idx, topk_weight, block_counts, neartie_count, neartie_flags,
+                                                      neartie_eps);
   return check_launch();
 }
 
