@@ -220,3 +220,28 @@ def test_layer_call_replays_from_a_cuda_graph(cuda_device):
             eager = mod(x_new)
             assert torch.equal(y_static, eager)
     ops.release_workspaces()
+
+
+def test_unscaled_fp8_ops_module(cuda_device):
+    """comfy.ops.fp8_ops: e4m3 weights without scales (scale_weight = scale_input = None), fp8 matmul."""
+    from comfyui_b200 import ops
+
+    dev = cuda_device
+    dim, hidden_dim, n = 256, 1024, 200
+    layer = {k: v.bfloat16() for k, v in O.make_layer(dim, hidden_dim, 4, seed=0, std=0.5).items()}
+    layer = {k: (v.to(torch.float8_e4m3fn) if k != "gate.weight" else v) for k, v in layer.items()}
+    x = (O.make_input(n, dim, seed=1) * 0.1).bfloat16()
+    from comfyui_b200.ldm.hidream.model import MOEFeedForwardSwiGLU
+
+    mod = MOEFeedForwardSwiGLU(dim, hidden_dim, 4, 2, dtype=torch.float8_e4m3fn, device=dev, operations=ops.fp8_ops).eval()
+    mod.gate.weight = torch.nn.Parameter(layer["gate.weight"].to(dev), requires_grad=False)
+    mod.load_state_dict({k: v.to(dev) for k, v in layer.items()}, strict=True)
+    xd = x.to(dev).view(1, n, dim)
+    with torch.inference_mode():
+        pack = ops._layer_pack(mod, xd)
+        assert pack is not None and pack.fp8 and pack.experts[0].scale_w1 is None
+        out = mod(xd).view(-1, dim).cpu()
+        idx, w, _ = mod.gate(xd)
+    ref, _, _ = O.moe_layer(x, layer, mode=O.FP8_MATMUL, routing=(idx.cpu(), w.cpu()))
+    rel = float((out.float() - ref.float()).norm() / ref.float().norm())
+    assert rel < 1e-2, rel

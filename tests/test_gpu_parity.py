@@ -192,7 +192,7 @@ def _full_layer_case(M, dev, n, dim, hidden_dim, e, mode, seed=0, skew=None, sca
 FULL_CASES = [
     # n, dim, hidden_dim, experts
     (1, 256, 1024, 4), (2, 256, 1024, 4), (3, 256, 1024, 4), (127, 256, 1024, 4), (128, 256, 1024, 4),
-    (129, 256, 1024, 4), (300, 512, 2048, 4), (1000, 512, 2048, 8), (4480, 2560, 10240, 4),
+    (129, 256, 1024, 4), (300, 512, 2048, 4), (1000, 512, 2048, 8), (100, 256, 1024, 2), (4480, 2560, 10240, 4),
 ]
 
 
