@@ -11,8 +11,8 @@
 // FeedForwardSwiGLU.forward (comfy/ldm/hidream/model.py:238) for all experts at once, and in the
 // fp8 variant the clamp / cast / torch._scaled_mm sequence of comfy/ops.py:338-348.
 //
-// CTA layout (192 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer,
-// warps 2-5 = epilogue (TMEM -> registers -> global).
+// CTA layout (320 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer,
+// warps 2-9 = epilogue (TMEM -> registers -> global): two warps per TMEM lane quarter, half of the columns each.
 //
 // kCtas = 2 (the default): two CTAs on an SM pair form a cluster and share one
 // tcgen05.mma.cta_group::2 stream.  A cluster tile is 256 rows x 256 accumulator columns; each CTA
@@ -44,7 +44,8 @@ constexpr int kAccStages = 2;
 constexpr int kABytes = kBlockM * kRowBytes;      // 16 KB
 constexpr int kBBoxBytes = 128 * kRowBytes;       // 16 KB: one 128-row B box
 constexpr int kOutStageBytes = 2 * kABytes;      // epilogue staging tile: 128 rows x 256 bytes
-constexpr int kGemmThreads = 192;
+constexpr int kEpilogueWarps = 8;                 // two per TMEM lane quarter, each taking half of the columns
+constexpr int kGemmThreads = 64 + 32 * kEpilogueWarps;
 constexpr int kTmemCols = kAccStages * kBlockN;   // 512
 constexpr int kMaxGroups = kMaxExperts + 1;
 constexpr int kMaxMaps = 4 + 2 * kMaxGroups;
@@ -110,7 +111,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
   __shared__ __align__(8) uint64_t tmem_full_bar[kAccStages];
   __shared__ __align__(8) uint64_t tmem_empty_bar[kAccStages];
   __shared__ __align__(8) uint64_t drain_bar;
-  __shared__ __align__(8) uint64_t epi_bar;        // the four epilogue warps meet here (bounded, unlike bar.sync)
+  __shared__ __align__(8) uint64_t epi_bar;        // the epilogue warps meet here (bounded, unlike bar.sync)
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
   __shared__ int s_tile_start[kMaxGroups + 1];
@@ -128,9 +129,9 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
 
   if (tid == 0) {
     for (int s = 0; s < kStages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
-    for (int s = 0; s < kAccStages; ++s) { mbar_init(&tmem_full_bar[s], 1); mbar_init(&tmem_empty_bar[s], 4 * kCtas); }
+    for (int s = 0; s < kAccStages; ++s) { mbar_init(&tmem_full_bar[s], 1); mbar_init(&tmem_empty_bar[s], kEpilogueWarps * kCtas); }
     mbar_init(&drain_bar, 1);
-    mbar_init(&epi_bar, 128);
+    mbar_init(&epi_bar, 32 * kEpilogueWarps);
     fence_mbar_init();
     abort_flag = 0;
     int start = 0;
@@ -325,11 +326,12 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
       mbar_wait(&drain_bar, 0, abort_ptr);
     }
   } else {
-    // ------------------------------------------------------------------ epilogue (4 warps per CTA)
+    // ------------------------------------------------------------------ epilogue (8 warps per CTA)
     // TMEM -> registers -> (math) -> swizzled staging tile in shared memory -> TMA store.  Full 128-byte lines
     // leave the SM instead of 16-byte pieces of 32 different rows.  A tile that hangs over the end of its group
     // (its last rows belong to the next group) is written with predicated stores from registers instead.
     const int quarter = warp & 3;   // TMEM lanes this warp may read: [32*quarter, 32*quarter + 32)
+    const int col_half = (warp - 2) >> 2;   // which half of the tile's columns this warp converts
     const bool issuer = warp == 2 && lane == 0;
     uint8_t* stage_out = smem + static_cast<size_t>(kStages) * kStageBytes;    // kOutStageBytes, 1024-aligned
     const int r_in_tile = quarter * 32 + lane;
@@ -337,7 +339,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
     const int sw = r_in_tile & 7;
     uint32_t epi_phase = 0;
     bool epi_ok = true;
-    // All 128 epilogue threads arrive and wait with the usual clock budget; a warp that gave up elsewhere can
+    // All epilogue threads arrive and wait with the usual clock budget; a warp that gave up elsewhere can
     // therefore never leave the others parked at a hardware barrier.
     auto epi_sync = [&]() {
       mbar_arrive(&epi_bar);
@@ -381,7 +383,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
           epi_sync();
         }
 #pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 2 * col_half; c < 2 * col_half + 2; ++c) {
           uint32_t ra[32], rb[32];
           tmem_ld_32x32b_x32(taddr + c * 32, ra);
           tmem_ld_32x32b_x32(taddr + 128 + c * 32, rb);
@@ -460,7 +462,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
             epi_sync();
           }
 #pragma unroll 1
-          for (int cc = 0; cc < 4; ++cc) {
+          for (int cc = 2 * col_half; cc < 2 * col_half + 2; ++cc) {
             const int c = half * 4 + cc;
             uint32_t r[32];
             tmem_ld_32x32b_x32(taddr + c * 32, r);
