@@ -251,8 +251,10 @@ def run_gpu_arm(args) -> None:
 
         # ---- per-stage timing of the same work through the stage-level C ABI (single GPU only)
         stages = None
+        gpu_bar = None
         if world == 1:
             stages = time_stages(module, x.view(n, DIM), args.steps, moe_ops, ops)
+            gpu_bar = time_stock_composition(module, x, ops)
 
 
     times = torch.tensor([ms_total, ms_e2e], dtype=torch.float64, device=dev)
@@ -292,6 +294,7 @@ def run_gpu_arm(args) -> None:
                 "traffic": None if fp8 else 1.573e9, "algorithmic_bytes": None if fp8 else 1.30e9,
             }
             line["stages"] = stages
+            line["gpu_bar"] = gpu_bar
             hbm = peaks["hbm_gbs"]
             line["hbm_kernels"] = {
                 k: {"achieved_gbs": stages[k + "_bytes"] / (stages[k + "_ms"] * 1e-3) / 1e9,
@@ -417,6 +420,41 @@ def time_stages(module, x2, steps, moe_ops, ops):
     res["permute_bytes"] = n * d * 2 + (n * 2 * d * 2 if not layer.fp8 else n * 3 * d)
     res["combine_bytes"] = n * 2 * d * 2 + n * d * 2 + n * d * 2
     return res
+
+
+def time_stock_composition(module, x, ops, steps: int = 10):
+    """The same module with the sm_100a kernels switched off: forward() then runs the composition the reference
+    ships (masked branch, one library GEMM per Linear, boolean-mask gathers, host syncs), and moe_infer the sorted
+    variant.  This is what the layer costs on this GPU today; it is reported next to the headline, never as it."""
+    def timed(fn):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / steps
+
+    n = x.shape[0] * x.shape[1]
+    x2 = x.view(n, x.shape[-1])
+    saved = ops.ENABLE_SM100_KERNELS
+    ops.ENABLE_SM100_KERNELS = False
+    try:
+        ms_forward = timed(lambda: module(x))
+
+        def infer():
+            idx, w, _ = module.gate(x)
+            return module.moe_infer(x2, idx.view(-1), w.view(-1, 1)) + module.shared_experts(x2)
+
+        ms_infer = timed(infer)
+    finally:
+        ops.ENABLE_SM100_KERNELS = saved
+    return {"what": "same module and weights, sm_100a kernels off: stock PyTorch composition on this GPU",
+            "forward_ms": ms_forward, "forward_tokens_per_s": n / (ms_forward * 1e-3),
+            "moe_infer_ms": ms_infer, "moe_infer_tokens_per_s": n / (ms_infer * 1e-3), "steps": steps}
 
 
 def main() -> None:

@@ -91,9 +91,17 @@ struct alignas(64) GemmParams {
   int num_groups;
 };
 
-__device__ __forceinline__ float silu_bf16_steps(float a_bf16) {
-  // the reference computes silu on a bf16 tensor: fp32 math, one rounding to bf16
-  return round_bf16(__fdividef(a_bf16, 1.0f + __expf(-a_bf16)));
+// The SwiGLU epilogue works on pairs of neighbouring columns held as bf16x2, so that every rounding the reference
+// performs on its bf16 tensors (after w1 x, after w3 x, after silu, after the product) is one packed conversion or one
+// packed multiply for two elements.  silu itself is fp32 math on the rounded value, as PyTorch computes it.
+__device__ __forceinline__ float silu_f32(float a) { return __fdividef(a, 1.0f + __expf(-a)); }
+__device__ __forceinline__ float bf16x2_lo(uint32_t v) { return __uint_as_float(v << 16); }
+__device__ __forceinline__ float bf16x2_hi(uint32_t v) { return __uint_as_float(v & 0xffff0000u); }
+__device__ __forceinline__ uint32_t mul_bf16x2(uint32_t a, uint32_t b) {
+  // the fp32 product of two bf16 values is exact, so one rounding here equals "multiply in fp32, round to bf16"
+  uint32_t d;
+  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
 }
 
 template <bool kFp8, bool kSwiglu, int kCtas>
@@ -368,42 +376,63 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
       const CUtensorMap* map_out = &p.maps[grp.out_map];
 
       float alpha0 = 1.f, alpha1 = 1.f, out_inv = 1.f;
+      uint32_t out_inv2 = 0;
       bool out_scaled = false;
       if constexpr (kFp8) {
         const float sa = grp.scale_a ? __ldg(grp.scale_a) : 1.f;
         alpha0 = sa * (grp.scale_b0 ? __ldg(grp.scale_b0) : 1.f);
         alpha1 = sa * (grp.scale_b1 ? __ldg(grp.scale_b1) : 1.f);
         if (kSwiglu && grp.out_scale) { out_inv = round_bf16(1.0f / __ldg(grp.out_scale)); out_scaled = true; }
+        out_inv2 = pack_bf16x2(out_inv, out_inv);
       }
+
+      // hand the accumulator stage back to the MMA warp: called once every TMEM read of the tile has landed in
+      // registers, i.e. before the math and the stores, so the next tile's MMAs never wait for them
+      auto release_tmem = [&]() {
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) {
+          if constexpr (kPair) mbar_arrive_cluster(mapa_shared(smem_u32(&tmem_empty_bar[as]), 0));
+          else mbar_arrive(&tmem_empty_bar[as]);
+        }
+      };
 
       if constexpr (kSwiglu) {
         const int col0 = n_tile * 128;
+        const int c_first = 2 * col_half;           // this warp's two chunks of 32 output columns
+        uint32_t ra[2][32], rb[2][32];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          tmem_ld_32x32b_x32(taddr + (c_first + i) * 32, ra[i]);
+          tmem_ld_32x32b_x32(taddr + 128 + (c_first + i) * 32, rb[i]);
+        }
+        tmem_ld_wait();
+        release_tmem();
         if (tile_tma) {
           if (issuer) bulk_wait_read_all();         // the previous tile's store has finished reading the staging tile
           epi_sync();
         }
-#pragma unroll 1
-        for (int c = 2 * col_half; c < 2 * col_half + 2; ++c) {
-          uint32_t ra[32], rb[32];
-          tmem_ld_32x32b_x32(taddr + c * 32, ra);
-          tmem_ld_32x32b_x32(taddr + 128 + c * 32, rb);
-          tmem_ld_wait();
-          float h[32];
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            float a = __uint_as_float(ra[j]), b = __uint_as_float(rb[j]);
-            if constexpr (kFp8) { a *= alpha0; b *= alpha1; }
-            a = round_bf16(a);
-            b = round_bf16(b);
-            h[j] = round_bf16(silu_bf16_steps(a) * b);
-            if constexpr (kFp8) { if (out_scaled) h[j] = round_bf16(h[j] * out_inv); }
+        for (int i = 0; i < 2; ++i) {
+          const int c = c_first + i;
+          uint32_t hp[16];                        // h for columns 2j, 2j+1 of this chunk, bf16x2
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            float a0 = __uint_as_float(ra[i][2 * j]), a1 = __uint_as_float(ra[i][2 * j + 1]);
+            float b0 = __uint_as_float(rb[i][2 * j]), b1 = __uint_as_float(rb[i][2 * j + 1]);
+            if constexpr (kFp8) { a0 *= alpha0; a1 *= alpha0; b0 *= alpha1; b1 *= alpha1; }
+            const uint32_t a2 = pack_bf16x2(a0, a1);
+            const uint32_t b2 = pack_bf16x2(b0, b1);
+            const uint32_t s2 = pack_bf16x2(silu_f32(bf16x2_lo(a2)), silu_f32(bf16x2_hi(a2)));
+            hp[j] = mul_bf16x2(s2, b2);
+            if constexpr (kFp8) { if (out_scaled) hp[j] = mul_bf16x2(hp[j], out_inv2); }
           }
           if constexpr (kFp8) {
             uint32_t w[8];
 #pragma unroll
             for (int j = 0; j < 8; ++j)
-              w[j] = static_cast<uint32_t>(f2_to_e4m3x2(h[4 * j], h[4 * j + 1])) |
-                     (static_cast<uint32_t>(f2_to_e4m3x2(h[4 * j + 2], h[4 * j + 3])) << 16);
+              w[j] = static_cast<uint32_t>(f2_to_e4m3x2(bf16x2_lo(hp[2 * j]), bf16x2_hi(hp[2 * j]))) |
+                     (static_cast<uint32_t>(f2_to_e4m3x2(bf16x2_lo(hp[2 * j + 1]), bf16x2_hi(hp[2 * j + 1]))) << 16);
             if (tile_tma) {
               // one 128-byte row per tile row: this chunk is pieces 2c and 2c+1
               *reinterpret_cast<uint4*>(stage_row + (((2 * c) ^ sw) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
@@ -416,9 +445,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
           } else {
             uint4 q[4];
 #pragma unroll
-            for (int j = 0; j < 4; ++j)
-              q[j] = make_uint4(pack_bf16x2(h[8 * j], h[8 * j + 1]), pack_bf16x2(h[8 * j + 2], h[8 * j + 3]),
-                                pack_bf16x2(h[8 * j + 4], h[8 * j + 5]), pack_bf16x2(h[8 * j + 6], h[8 * j + 7]));
+            for (int j = 0; j < 4; ++j) q[j] = make_uint4(hp[4 * j], hp[4 * j + 1], hp[4 * j + 2], hp[4 * j + 3]);
             if (tile_tma) {
               // two boxes of 64 columns (128 bytes per row each): chunk c is pieces 4(c&1) .. +3 of box c>>1
               uint8_t* box_row = stage_row + (c >> 1) * kABytes;
@@ -432,52 +459,48 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
             }
           }
         }
-        // every TMEM read of this tile is done: hand the accumulator stage back before the store is issued
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) {
-          if constexpr (kPair) mbar_arrive_cluster(mapa_shared(smem_u32(&tmem_empty_bar[as]), 0));
-          else mbar_arrive(&tmem_empty_bar[as]);
-        }
         if (tile_tma) {
           fence_proxy_async_smem();
           epi_sync();
           if (issuer) {
-            if constexpr (kFp8) {
-              tma_store_2d(map_out, stage_out, col0, row0);
-            } else {
-              tma_store_2d(map_out, stage_out, col0, row0);
-              tma_store_2d(map_out, stage_out + kABytes, col0 + 64, row0);
-            }
+            tma_store_2d(map_out, stage_out, col0, row0);
+            if constexpr (!kFp8) tma_store_2d(map_out, stage_out + kABytes, col0 + 64, row0);
             bulk_commit_group();
           }
         }
       } else {
         const int col0 = n_tile * kBlockN;
         __nv_bfloat16* o_row = static_cast<__nv_bfloat16*>(grp.out) + static_cast<long long>(row) * grp.ld_out + col0;
-#pragma unroll 1
+        // this warp's four chunks of 32 columns: two in each 128-column half of the tile, all read up front
+        uint32_t r[4][32];
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          tmem_ld_32x32b_x32(taddr + ((i >> 1) * 4 + 2 * col_half + (i & 1)) * 32, r[i]);
+        tmem_ld_wait();
+        release_tmem();
+#pragma unroll
         for (int half = 0; half < 2; ++half) {
           if (tile_tma) {
             if (issuer) bulk_wait_read_all();
             epi_sync();
           }
-#pragma unroll 1
-          for (int cc = 2 * col_half; cc < 2 * col_half + 2; ++cc) {
-            const int c = half * 4 + cc;
-            uint32_t r[32];
-            tmem_ld_32x32b_x32(taddr + c * 32, r);
-            tmem_ld_wait();
-            float v[32];
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              v[j] = __uint_as_float(r[j]);
-              if constexpr (kFp8) v[j] *= (c < 4 ? alpha0 : alpha1);
-            }
+          for (int k = 0; k < 2; ++k) {
+            const int cc = 2 * col_half + k;      // chunk inside the half
+            const int c = half * 4 + cc;          // chunk inside the tile
+            const uint32_t* rv = r[half * 2 + k];
             uint4 q[4];
 #pragma unroll
-            for (int j = 0; j < 4; ++j)
-              q[j] = make_uint4(pack_bf16x2(v[8 * j], v[8 * j + 1]), pack_bf16x2(v[8 * j + 2], v[8 * j + 3]),
-                                pack_bf16x2(v[8 * j + 4], v[8 * j + 5]), pack_bf16x2(v[8 * j + 6], v[8 * j + 7]));
+            for (int j = 0; j < 4; ++j) {
+              float v[8];
+#pragma unroll
+              for (int m = 0; m < 8; ++m) {
+                v[m] = __uint_as_float(rv[8 * j + m]);
+                if constexpr (kFp8) v[m] *= (half == 0 ? alpha0 : alpha1);
+              }
+              q[j] = make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]),
+                                pack_bf16x2(v[6], v[7]));
+            }
             if (tile_tma) {
               uint8_t* box_row = stage_row + (cc >> 1) * kABytes;
 #pragma unroll
@@ -487,14 +510,6 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
               __nv_bfloat16* o = o_row + c * 32;
 #pragma unroll
               for (int j = 0; j < 4; ++j) reinterpret_cast<uint4*>(o)[j] = q[j];
-            }
-          }
-          if (half == 1) {
-            tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) {
-              if constexpr (kPair) mbar_arrive_cluster(mapa_shared(smem_u32(&tmem_empty_bar[as]), 0));
-              else mbar_arrive(&tmem_empty_bar[as]);
             }
           }
           if (tile_tma) {
