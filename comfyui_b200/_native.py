@@ -11,7 +11,7 @@ from ctypes import POINTER, Structure, c_char_p, c_float, c_int, c_int32, c_int6
 
 from . import build as _build
 
-ABI_VERSION = 2
+ABI_VERSION = 3
 
 OK, EINVAL, EUNSUPPORTED, ECUDA, ETIMEOUT, EDEVICE, ETOOLARGE = range(7)
 BF16, FP32, FP8_E4M3 = 0, 1, 2
@@ -31,9 +31,11 @@ EXPORTS = (
     "comfy_moe_plan_permute",
     "comfy_moe_route_static",
     "comfy_moe_grouped_swiglu",
+    "comfy_moe_grouped_gelu_mlp",
     "comfy_moe_combine",
     "comfy_moe_combine_partials",
     "comfy_moe_forward",
+    "comfy_moe_forward_gelu_mlp",
     "comfy_moe_ln_modulate",
     "comfy_moe_gate_residual",
     "comfy_moe_combine_block",
@@ -74,6 +76,35 @@ class Layer(Structure):
         ("w_gate", c_void_p),
         ("experts", FfnWeights * MAX_EXPERTS),
         ("shared", FfnWeights),
+    ]
+
+
+class MlpWeights(Structure):
+    """struct ComfyMoeMlpWeights"""
+
+    _fields_ = [
+        ("w1", c_void_p),
+        ("b1", c_void_p),
+        ("w2", c_void_p),
+        ("b2", c_void_p),
+        ("ld1", c_int64),
+        ("ld2", c_int64),
+        ("hidden", c_int32),
+        ("reserved", c_int32),
+    ]
+
+
+class MlpLayer(Structure):
+    """struct ComfyMoeMlpLayer"""
+
+    _fields_ = [
+        ("dim", c_int32),
+        ("n_experts", c_int32),
+        ("top_k", c_int32),
+        ("gate_dtype", c_int32),
+        ("w_gate", c_void_p),
+        ("experts", MlpWeights * MAX_EXPERTS),
+        ("shared", MlpWeights),
     ]
 
 
@@ -155,6 +186,12 @@ def load(build_if_missing: bool = False) -> ctypes.CDLL:
         c_int, c_int, POINTER(FfnWeights), POINTER(FfnWeights), c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p,
         c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
     ]
+    lib.comfy_moe_grouped_gelu_mlp.argtypes = [
+        c_int, POINTER(MlpWeights), POINTER(MlpWeights), c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p,
+        c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+    ]
+    lib.comfy_moe_forward_gelu_mlp.argtypes = [POINTER(MlpLayer), POINTER(Workspace), c_void_p, c_int, c_void_p,
+                                               c_void_p]
     lib.comfy_moe_combine.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]
     lib.comfy_moe_combine_partials.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p,
                                                c_void_p]

@@ -80,6 +80,38 @@ extern "C" int comfy_moe_forward(const ComfyMoeLayer* L, const ComfyMoeWorkspace
   return forward_impl(L, ws, x, n_tokens, out, stream, nullptr);
 }
 
+// MoEBlock.forward in eval mode (comfy/ldm/hunyuan3dv2_1/hunyuandit.py:130-185): the same five launches with the
+// GELU-MLP expert passes in the middle.
+extern "C" int comfy_moe_forward_gelu_mlp(const ComfyMoeMlpLayer* L, const ComfyMoeWorkspace* ws, const void* x,
+                                          int n_tokens, void* out, void* stream) {
+  if (!L || !ws || n_tokens < 0) return COMFY_MOE_EINVAL;
+  if (n_tokens == 0) return COMFY_MOE_OK;
+  if (!x || !out) return COMFY_MOE_EINVAL;
+  if (L->top_k != 2 || L->n_experts < 2 || L->n_experts > COMFY_MOE_MAX_EXPERTS) return COMFY_MOE_EUNSUPPORTED;
+  if (!ws->topk_idx || !ws->topk_weight || !ws->block_counts || !ws->block_offsets || !ws->expert_counts ||
+      !ws->expert_offsets || !ws->row_map || !ws->status || !ws->x_perm || !ws->h_perm || !ws->y_perm ||
+      !ws->h_shared || !ws->y_shared)
+    return COMFY_MOE_EINVAL;
+  int64_t rows_need = 0;
+  int rc = comfy_moe_plan_sizes(n_tokens, L->n_experts, L->top_k, &rows_need, nullptr);
+  if (rc != COMFY_MOE_OK) return rc;
+  if (ws->rows_cap < rows_need) return COMFY_MOE_EINVAL;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (cudaMemsetAsync(ws->status, 0, 2 * sizeof(int32_t), s) != cudaSuccess) return COMFY_MOE_ECUDA;
+  rc = comfy_moe_gate_topk(x, L->w_gate, L->gate_dtype, n_tokens, L->dim, L->n_experts, L->top_k, ws->topk_idx,
+                           ws->topk_weight, ws->block_counts, ws->status + 1, nullptr, 1e-6f, stream);
+  if (rc != COMFY_MOE_OK) return rc;
+  rc = comfy_moe_plan_permute(x, ws->topk_idx, ws->block_counts, n_tokens, L->dim, L->n_experts, COMFY_MOE_BF16,
+                              nullptr, ws->block_offsets, ws->expert_counts, ws->expert_offsets, ws->x_perm, nullptr,
+                              nullptr, ws->row_map, stream);
+  if (rc != COMFY_MOE_OK) return rc;
+  rc = comfy_moe_grouped_gelu_mlp(L->n_experts, L->experts, &L->shared, ws->expert_offsets, ws->expert_counts,
+                                  ws->rows_cap, n_tokens, L->dim, ws->x_perm, ws->h_perm, ws->y_perm, x, ws->h_shared,
+                                  ws->y_shared, ws->status, stream);
+  if (rc != COMFY_MOE_OK) return rc;
+  return comfy_moe_combine(ws->y_perm, ws->row_map, ws->topk_weight, ws->y_shared, n_tokens, L->dim, out, stream);
+}
+
 // Feed-forward half of a HiDream block (comfy/ldm/hidream/model.py:429-433): LayerNorm + modulation, the MoE,
 // gate * (.) + residual.
 extern "C" int comfy_moe_ffn_block(const ComfyMoeLayer* L, const ComfyMoeWorkspace* ws, const void* x,

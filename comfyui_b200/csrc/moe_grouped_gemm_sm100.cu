@@ -80,6 +80,9 @@ struct GemmGroup {
   const float* scale_b0;       // fp8: weight scale of the first box
   const float* scale_b1;       // fp8: weight scale of the second box
   const float* out_scale;      // fp8 pass 1: scale_input of w2 (h is multiplied by bf16(1/s) before the cast)
+  const __nv_bfloat16* bias;   // kBiasAct instantiations: bias over the output columns (NULL = none)
+  int gelu;                    // kBiasAct instantiations: 1 = exact (erf) GELU on the bf16-rounded sum
+  int reserved2;
 };
 
 struct alignas(64) GemmParams {
@@ -89,6 +92,7 @@ struct alignas(64) GemmParams {
   const int32_t* row_count;
   int32_t* status;
   int num_groups;
+  int m_fastest;      // plain passes: 1 = row tiles fastest (short K, wide N), 0 = column tiles fastest
 };
 
 // The SwiGLU epilogue works on pairs of neighbouring columns held as bf16x2, so that every rounding the reference
@@ -104,7 +108,7 @@ __device__ __forceinline__ uint32_t mul_bf16x2(uint32_t a, uint32_t b) {
   return d;
 }
 
-template <bool kFp8, bool kSwiglu, int kCtas>
+template <bool kFp8, bool kSwiglu, int kCtas, bool kBiasAct = false>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
   using Shape = GemmShape<kCtas>;
@@ -205,7 +209,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
     g = 0;
     while (t >= s_tile_start[g + 1]) ++g;
     const int local = t - s_tile_start[g];
-    if constexpr (kSwiglu) {
+    if (kSwiglu || p.m_fastest) {
       // pass 1: row tiles fastest.  The CTAs running together share a few weight panels (read from HBM
       // once) and sweep all rows of the group, which stay in L2 (K = dim is short).
       const int mt = s_m_tiles[g];
@@ -498,6 +502,23 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
                 v[m] = __uint_as_float(rv[8 * j + m]);
                 if constexpr (kFp8) v[m] *= (half == 0 ? alpha0 : alpha1);
               }
+              if constexpr (kBiasAct) {
+                // nn.Linear with a bias: the sum is formed in fp32 and rounded once; GELU (exact, erf) is then
+                // fp32 math on that bf16 value, rounded once more by the pack below
+                if (grp.bias) {
+                  float bv[8];
+                  unpack_bf16x8(__ldg(reinterpret_cast<const uint4*>(grp.bias + col0 + c * 32) + j), bv);
+#pragma unroll
+                  for (int m = 0; m < 8; ++m) v[m] += bv[m];
+                }
+                if (grp.gelu) {
+#pragma unroll
+                  for (int m = 0; m < 8; ++m) {
+                    const float t = round_bf16(v[m]);
+                    v[m] = 0.5f * t * (1.0f + erff(t * 0.70710678118654752440f));
+                  }
+                }
+              }
               q[j] = make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]),
                                 pack_bf16x2(v[6], v[7]));
             }
@@ -609,9 +630,9 @@ static int gemm_ctas() {
   return ctas;
 }
 
-template <bool kFp8, bool kSwiglu, int kCtas>
+template <bool kFp8, bool kSwiglu, int kCtas, bool kBiasAct = false>
 static int launch_gemm_impl(const GemmParams& params, int64_t max_tiles, int sms, cudaStream_t stream) {
-  auto kernel = grouped_gemm_kernel<kFp8, kSwiglu, kCtas>;
+  auto kernel = grouped_gemm_kernel<kFp8, kSwiglu, kCtas, kBiasAct>;
   constexpr size_t smem = GemmShape<kCtas>::kSmemBytes;
   // the shared-memory opt-in is a per-device property of the kernel
   constexpr int kMaxDevices = 64;
@@ -643,10 +664,10 @@ static int launch_gemm_impl(const GemmParams& params, int64_t max_tiles, int sms
   return check_launch();
 }
 
-template <bool kFp8, bool kSwiglu>
+template <bool kFp8, bool kSwiglu, bool kBiasAct = false>
 static int launch_gemm(const GemmParams& params, int64_t tiles_single, int64_t tiles_pair, int sms, cudaStream_t stream) {
-  if (gemm_ctas() == 1) return launch_gemm_impl<kFp8, kSwiglu, 1>(params, tiles_single, sms, stream);
-  return launch_gemm_impl<kFp8, kSwiglu, 2>(params, tiles_pair, sms, stream);
+  if (gemm_ctas() == 1) return launch_gemm_impl<kFp8, kSwiglu, 1, kBiasAct>(params, tiles_single, sms, stream);
+  return launch_gemm_impl<kFp8, kSwiglu, 2, kBiasAct>(params, tiles_pair, sms, stream);
 }
 
 }  // namespace comfy_b200
@@ -762,4 +783,105 @@ extern "C" int comfy_moe_grouped_swiglu(int w_dtype, int n_experts, const ComfyM
   }
   if ((rc = launch_gemm<false, true>(p1, tiles1[0], tiles1[1], sms, s)) != COMFY_MOE_OK) return rc;
   return launch_gemm<false, false>(p2, tiles2[0], tiles2[1], sms, s);
+}
+
+// GELU-MLP experts (Linear + bias, exact GELU, Linear + bias): the feed-forward of the Hunyuan3D-2.1 MoE block
+// (comfy/ldm/hunyuan3dv2_1/hunyuandit.py:8-50).  Both launches are plain passes of the same kernel with the
+// bias / activation epilogue; the first one walks row tiles fastest because its K (= dim) is short and its N wide.
+extern "C" int comfy_moe_grouped_gelu_mlp(int n_experts, const ComfyMoeMlpWeights* h_experts,
+                                          const ComfyMoeMlpWeights* h_shared, const int32_t* row_start,
+                                          const int32_t* row_count, int64_t rows_cap, int n_tokens, int dim,
+                                          const void* x_perm, void* h_perm, void* y_perm, const void* x_shared,
+                                          void* h_shared_ws, void* y_shared, int32_t* status, void* stream) {
+  if (n_experts < 0 || n_experts > kMaxExperts || dim <= 0 || n_tokens < 0 || rows_cap < 0) return COMFY_MOE_EINVAL;
+  if (!status) return COMFY_MOE_EINVAL;
+  if (n_experts > 0 && (!h_experts || !row_start || !row_count || !x_perm || !h_perm || !y_perm || rows_cap <= 0))
+    return COMFY_MOE_EINVAL;
+  const bool has_shared = h_shared != nullptr && n_tokens > 0;
+  if (has_shared && (!x_shared || !h_shared_ws || !y_shared)) return COMFY_MOE_EINVAL;
+  if (n_experts == 0 && !has_shared) return COMFY_MOE_OK;
+  constexpr int k_elems = kRowBytes / 2;
+  if (dim % kBlockN != 0) return COMFY_MOE_EUNSUPPORTED;
+
+  int sms = 0;
+  int rc = device_sm_count(&sms);
+  if (rc != COMFY_MOE_OK) return rc;
+
+  GemmParams p1, p2;
+  memset(&p1, 0, sizeof(p1));
+  memset(&p2, 0, sizeof(p2));
+  p1.row_start = p2.row_start = row_start;
+  p1.row_count = p2.row_count = row_count;
+  p1.status = p2.status = status;
+  p1.m_fastest = 1;
+  int64_t tiles1[2] = {0, 0}, tiles2[2] = {0, 0};
+  int n_maps1 = 0, n_maps2 = 0, g = 0;
+
+  auto weights_ok = [&](const ComfyMoeMlpWeights& w) -> int {
+    if (!w.w1 || !w.w2) return COMFY_MOE_EINVAL;
+    if ((w.b1 && !aligned16(w.b1)) || (w.b2 && !aligned16(w.b2))) return COMFY_MOE_EINVAL;
+    if (w.hidden <= 0 || w.hidden % kBlockN != 0) return COMFY_MOE_EUNSUPPORTED;
+    return COMFY_MOE_OK;
+  };
+  auto fill = [&](GemmGroup& g1, GemmGroup& g2, const ComfyMoeMlpWeights& w, int a1, int b1, int o1, int a2, int b2,
+                  int o2, int routed_index, int static_rows, void* h_out, void* y_out) {
+    g1.a_map = a1; g1.b0_map = b1; g1.b1_map = b1; g1.b1_row_off = 128; g1.out_map = o1;
+    g1.k_blocks = dim / k_elems; g1.n_tiles = w.hidden / kBlockN; g1.routed_index = routed_index;
+    g1.static_rows = static_rows; g1.out = h_out; g1.ld_out = w.hidden;
+    g1.bias = static_cast<const __nv_bfloat16*>(w.b1); g1.gelu = 1;
+    g2.a_map = a2; g2.b0_map = b2; g2.b1_map = b2; g2.b1_row_off = 128; g2.out_map = o2;
+    g2.k_blocks = w.hidden / k_elems; g2.n_tiles = dim / kBlockN; g2.routed_index = routed_index;
+    g2.static_rows = static_rows; g2.out = y_out; g2.ld_out = dim;
+    g2.bias = static_cast<const __nv_bfloat16*>(w.b2); g2.gelu = 0;
+  };
+
+  if (n_experts > 0) {
+    const int hidden = h_experts[0].hidden;
+    for (int e = 0; e < n_experts; ++e) {
+      if ((rc = weights_ok(h_experts[e])) != COMFY_MOE_OK) return rc;
+      if (h_experts[e].hidden != hidden) return COMFY_MOE_EUNSUPPORTED;
+    }
+    if ((rc = make_map(&p1.maps[0], x_perm, false, rows_cap, dim, dim)) != COMFY_MOE_OK) return rc;
+    if ((rc = make_map(&p1.maps[1], h_perm, false, rows_cap, hidden, hidden)) != COMFY_MOE_OK) return rc;
+    if ((rc = make_map(&p2.maps[0], h_perm, false, rows_cap, hidden, hidden)) != COMFY_MOE_OK) return rc;
+    if ((rc = make_map(&p2.maps[1], y_perm, false, rows_cap, dim, dim)) != COMFY_MOE_OK) return rc;
+    n_maps1 = n_maps2 = 2;
+    const int64_t m_tiles_cap[2] = {(rows_cap + kBlockM - 1) / kBlockM + n_experts,
+                                    (rows_cap + 2 * kBlockM - 1) / (2 * kBlockM) + n_experts};
+    for (int e = 0; e < n_experts; ++e, ++g) {
+      const ComfyMoeMlpWeights& w = h_experts[e];
+      if ((rc = make_map(&p1.maps[n_maps1], w.w1, false, w.hidden, dim, w.ld1)) != COMFY_MOE_OK) return rc;
+      if ((rc = make_map(&p2.maps[n_maps2], w.w2, false, dim, w.hidden, w.ld2)) != COMFY_MOE_OK) return rc;
+      fill(p1.groups[g], p2.groups[g], w, 0, n_maps1, 1, 0, n_maps2, 1, e, 0, h_perm, y_perm);
+      ++n_maps1; ++n_maps2;
+    }
+    for (int v = 0; v < 2; ++v) {
+      tiles1[v] += m_tiles_cap[v] * (hidden / kBlockN);
+      tiles2[v] += m_tiles_cap[v] * (dim / kBlockN);
+    }
+  }
+  if (has_shared) {
+    const ComfyMoeMlpWeights& w = *h_shared;
+    if ((rc = weights_ok(w)) != COMFY_MOE_OK) return rc;
+    if ((rc = make_map(&p1.maps[n_maps1], x_shared, false, n_tokens, dim, dim)) != COMFY_MOE_OK) return rc;
+    if ((rc = make_map(&p1.maps[n_maps1 + 1], w.w1, false, w.hidden, dim, w.ld1)) != COMFY_MOE_OK) return rc;
+    if ((rc = make_map(&p1.maps[n_maps1 + 2], h_shared_ws, false, n_tokens, w.hidden, w.hidden)) != COMFY_MOE_OK) return rc;
+    if ((rc = make_map(&p2.maps[n_maps2], h_shared_ws, false, n_tokens, w.hidden, w.hidden)) != COMFY_MOE_OK) return rc;
+    if ((rc = make_map(&p2.maps[n_maps2 + 1], w.w2, false, dim, w.hidden, w.ld2)) != COMFY_MOE_OK) return rc;
+    if ((rc = make_map(&p2.maps[n_maps2 + 2], y_shared, false, n_tokens, dim, dim)) != COMFY_MOE_OK) return rc;
+    fill(p1.groups[g], p2.groups[g], w, n_maps1, n_maps1 + 1, n_maps1 + 2, n_maps2, n_maps2 + 1, n_maps2 + 2, -1,
+         n_tokens, h_shared_ws, y_shared);
+    for (int v = 0; v < 2; ++v) {
+      const int64_t tile_m = kBlockM * (v + 1);
+      const int64_t m_tiles = (n_tokens + tile_m - 1) / tile_m;
+      tiles1[v] += m_tiles * (w.hidden / kBlockN);
+      tiles2[v] += m_tiles * (dim / kBlockN);
+    }
+    ++g;
+  }
+  p1.num_groups = p2.num_groups = g;
+
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if ((rc = launch_gemm<false, false, true>(p1, tiles1[0], tiles1[1], sms, s)) != COMFY_MOE_OK) return rc;
+  return launch_gemm<false, false, true>(p2, tiles2[0], tiles2[1], sms, s);
 }

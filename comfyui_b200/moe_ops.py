@@ -425,3 +425,130 @@ def moe_ffn_block(layer: LayerPack, x: torch.Tensor, shift: torch.Tensor, scale:
                                       float(eps), _ptr(out), _stream())
     N.check("comfy_moe_ffn_block", rc)
     return out
+
+
+# --------------------------------------------------------------------------------------- GELU-MLP experts
+@dataclass
+class MlpPack:
+    """Device pointers of one GELU feed-forward (Linear + bias, GELU, Linear + bias); keeps the tensors alive."""
+
+    w1: torch.Tensor
+    b1: Optional[torch.Tensor]
+    w2: torch.Tensor
+    b2: Optional[torch.Tensor]
+
+    def __post_init__(self):
+        _need_cuda(self.w1, self.w2, self.b1, self.b2)
+        for w in (self.w1, self.w2):
+            if w.dtype != torch.bfloat16 or w.dim() != 2 or w.stride(1) != 1:
+                raise ValueError("expert weights must be 2-D bf16 with a contiguous last dimension")
+        if self.w2.shape != (self.w1.shape[1], self.w1.shape[0]):
+            raise ValueError("w2 must be [dim, hidden]")
+        for b, n in ((self.b1, self.w1.shape[0]), (self.b2, self.w2.shape[0])):
+            if b is not None and (b.dtype != torch.bfloat16 or b.shape != (n,) or not b.is_contiguous()):
+                raise ValueError("biases must be contiguous bf16 vectors over the output features")
+
+    @property
+    def hidden(self) -> int:
+        return self.w1.shape[0]
+
+    @property
+    def dim(self) -> int:
+        return self.w1.shape[1]
+
+    def fill(self, s: N.MlpWeights) -> None:
+        s.w1, s.w2 = self.w1.data_ptr(), self.w2.data_ptr()
+        s.b1 = None if self.b1 is None else self.b1.data_ptr()
+        s.b2 = None if self.b2 is None else self.b2.data_ptr()
+        s.ld1, s.ld2 = self.w1.stride(0), self.w2.stride(0)
+        s.hidden = self.hidden
+        s.reserved = 0
+
+    def struct(self) -> N.MlpWeights:
+        s = N.MlpWeights()
+        self.fill(s)
+        return s
+
+
+@dataclass
+class MlpLayerPack:
+    """Everything comfy_moe_forward_gelu_mlp needs to know about one MoEBlock."""
+
+    gate: torch.Tensor
+    experts: Sequence[MlpPack]
+    shared: MlpPack
+    top_k: int = 2
+    c_layer: N.MlpLayer = field(init=False)
+    fp8 = False
+
+    def __post_init__(self):
+        _need_cuda(self.gate)
+        if not self.gate.is_contiguous():
+            raise ValueError("gate weight must be contiguous")
+        L = N.MlpLayer()
+        L.dim = self.gate.shape[1]
+        L.n_experts = len(self.experts)
+        L.top_k = self.top_k
+        L.gate_dtype = _dtype_code(self.gate.dtype)
+        L.w_gate = self.gate.data_ptr()
+        for i, e in enumerate(self.experts):
+            e.fill(L.experts[i])
+        self.shared.fill(L.shared)
+        self.c_layer = L
+
+    @property
+    def dim(self) -> int:
+        return self.gate.shape[1]
+
+    @property
+    def n_experts(self) -> int:
+        return len(self.experts)
+
+
+def grouped_gelu_mlp(experts: Sequence[MlpPack], shared: Optional[MlpPack], row_start: Optional[torch.Tensor],
+                     row_count: Optional[torch.Tensor], x_perm: Optional[torch.Tensor],
+                     x_shared: Optional[torch.Tensor], *, check_status: bool = True):
+    """Both passes of the grouped GELU-MLP expert GEMM; arguments as grouped_swiglu.
+    Returns (y_perm or None, y_shared or None, h_perm, h_shared)."""
+    ref = experts[0] if experts else shared
+    dim, dev = ref.dim, ref.w1.device
+    n_e = len(experts)
+    arr = (N.MlpWeights * max(n_e, 1))()
+    for i, e in enumerate(experts):
+        e.fill(arr[i])
+    rows_cap = 0 if x_perm is None else x_perm.shape[0]
+    h_perm = y_perm = None
+    if n_e:
+        h_perm = torch.empty((rows_cap, experts[0].hidden), dtype=torch.bfloat16, device=dev)
+        y_perm = torch.empty((rows_cap, dim), dtype=torch.bfloat16, device=dev)
+    n_tokens = 0 if x_shared is None else x_shared.shape[0]
+    sh = h_sh = y_sh = None
+    if shared is not None and n_tokens > 0:
+        sh = shared.struct()
+        h_sh = torch.empty((n_tokens, shared.hidden), dtype=torch.bfloat16, device=dev)
+        y_sh = torch.empty((n_tokens, dim), dtype=torch.bfloat16, device=dev)
+    status = torch.zeros((2,), dtype=torch.int32, device=dev)
+    rc = N.load().comfy_moe_grouped_gelu_mlp(
+        n_e, arr, ctypes.byref(sh) if sh is not None else None, _ptr(row_start), _ptr(row_count), rows_cap, n_tokens,
+        dim, _ptr(x_perm), _ptr(h_perm), _ptr(y_perm), _ptr(x_shared), _ptr(h_sh), _ptr(y_sh), _ptr(status), _stream())
+    N.check("comfy_moe_grouped_gelu_mlp", rc)
+    if check_status:
+        read_status(status)
+    return y_perm, y_sh, h_perm, h_sh
+
+
+def moe_mlp_forward(layer: MlpLayerPack, x: torch.Tensor, ws: Optional[Workspace] = None,
+                    out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """MoEBlock.forward (eval) through comfy_moe_forward_gelu_mlp.  x: bf16 [N, D] contiguous on the device."""
+    _need_cuda(x)
+    if x.dtype != torch.bfloat16 or x.dim() != 2 or not x.is_contiguous():
+        raise ValueError("x must be a contiguous bf16 [N, D] tensor")
+    n = x.shape[0]
+    if ws is None or ws.n_tokens != n:
+        ws = Workspace.for_layer(layer, n)
+    if out is None:
+        out = torch.empty_like(x)
+    rc = N.load().comfy_moe_forward_gelu_mlp(ctypes.byref(layer.c_layer), ctypes.byref(ws.c_ws), _ptr(x), n,
+                                             _ptr(out), _stream())
+    N.check("comfy_moe_forward_gelu_mlp", rc)
+    return out

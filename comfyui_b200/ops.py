@@ -462,6 +462,123 @@ def swiglu_ffn_forward(ffn, x: torch.Tensor) -> Optional[torch.Tensor]:
     return y.view(x.shape)
 
 
+# ---- Hunyuan3D-2.1 MoE block (GELU feed-forwards with biases) ------------------------------------------------
+def _biased_linear_state(lin, device):
+    """(weight, bias or None) if this Linear can feed the GELU-MLP kernels as it is now, else None."""
+    if lin.weight_function or lin.bias_function:
+        return None
+    w, b = lin.weight, lin.bias
+    if w.device != device or w.dtype != torch.bfloat16 or w.dim() != 2 or w.stride(1) != 1:
+        return None
+    if b is not None and (b.device != device or b.dtype != torch.bfloat16 or not b.is_contiguous()):
+        return None
+    return (w, b)
+
+
+def _mlp_pack(ffn, device, moe_ops):
+    """MlpPack for a FeedForward (net.0.proj, net.2), or None; cached on the module like _ffn_pack."""
+    states = [_biased_linear_state(l, device) for l in (ffn.net[0].proj, ffn.net[2])]
+    if any(s is None for s in states):
+        return None
+    key = tuple(_tensor_key(t) for s in states for t in s)
+    cached = getattr(ffn, "_b200_pack", None)
+    if cached is not None and cached[0] == key:
+        return cached[1]
+    (w1, b1), (w2, b2) = states
+    try:
+        pack = moe_ops.MlpPack(w1.detach(), None if b1 is None else b1.detach(), w2.detach(),
+                               None if b2 is None else b2.detach())
+    except ValueError:
+        return None
+    object.__setattr__(ffn, "_b200_pack", (key, pack))
+    return pack
+
+
+def _mlp_layer_pack(moe, x):
+    """MlpLayerPack for a MoEBlock under the current weights, or None when not eligible."""
+    from . import moe_ops
+
+    gate_w = moe.gate.weight
+    dim = gate_w.shape[1]
+    if not _input_ok(x, dim) or moe.training:
+        return None
+    if moe.moe_top_k != 2 or len(moe.experts) not in (2, 4, 8):
+        return None
+    if gate_w.device != x.device or gate_w.dtype not in (torch.bfloat16, torch.float32) or not gate_w.is_contiguous():
+        return None
+    packs = [_mlp_pack(e, x.device, moe_ops) for e in moe.experts]
+    shared = _mlp_pack(moe.shared_experts, x.device, moe_ops)
+    if shared is None or any(p is None for p in packs):
+        return None
+    if any(p.hidden != packs[0].hidden or (p.b1 is None) != (packs[0].b1 is None) or
+           (p.b2 is None) != (packs[0].b2 is None) for p in packs + [shared]):
+        return None
+    if packs[0].hidden % 256:
+        return None
+    key = (_tensor_key(gate_w),) + tuple(id(p) for p in packs) + (id(shared),)
+    cached = getattr(moe, "_b200_layer", None)
+    if cached is not None and cached[0] == key:
+        return cached[1]
+    layer = moe_ops.MlpLayerPack(gate_w.detach(), packs, shared, top_k=2)
+    object.__setattr__(moe, "_b200_layer", (key, layer))
+    return layer
+
+
+def hunyuan3d_moe_forward(moe, x: torch.Tensor) -> Optional[torch.Tensor]:
+    """MoEBlock.forward (eval mode) on the sm_100a kernels, or None when this call is not eligible.
+    Goes through the registered operator ``torch.ops.comfyui_b200.hunyuan3d_moe``."""
+    layer = _mlp_layer_pack(moe, x)
+    if layer is None:
+        return None
+    from . import moe_ops, torch_ops
+
+    args = getattr(layer, "_op_args", None)
+    if args is None:
+        args = torch_ops.mlp_layer_args(layer)
+        layer._op_args = args
+    x2 = x.view(-1, x.shape[-1])
+    out = torch.ops.comfyui_b200.hunyuan3d_moe(x2, layer.gate, *args)
+    if CHECK_STATUS_EVERY_CALL:
+        moe_ops.read_status(_workspace(layer, x2.shape[0]).status)
+    return out.view(x.shape)
+
+
+def hunyuan3d_moe_infer(moe, x: torch.Tensor, flat_expert_indices: torch.Tensor,
+                        flat_expert_weights: torch.Tensor) -> Optional[torch.Tensor]:
+    """MoEBlock.moe_infer (routed experts only, caller-supplied routing) on the kernels, or None."""
+    if x.dim() != 2:
+        return None
+    layer = _mlp_layer_pack(moe, x)
+    if layer is None or not flat_expert_indices.is_cuda:
+        return None
+    from . import moe_ops
+
+    n, e = x.shape[0], layer.n_experts
+    idx = flat_expert_indices.reshape(n, 2).to(torch.int32).contiguous()
+    w = flat_expert_weights.reshape(n, 2).to(torch.float32).contiguous()
+    counts = moe_ops.route_count(idx, e)
+    block_offsets, expert_counts, expert_offsets = moe_ops.route_plan(counts, n, e)
+    x_perm, row_map, _ = moe_ops.permute(x, idx, block_offsets, expert_offsets, e)
+    y_perm, _, _, _ = moe_ops.grouped_gelu_mlp(layer.experts, None, expert_offsets, expert_counts, x_perm, None,
+                                                check_status=CHECK_STATUS_EVERY_CALL)
+    return moe_ops.combine(y_perm, row_map, w, None)
+
+
+def gelu_ffn_forward(ffn, x: torch.Tensor) -> Optional[torch.Tensor]:
+    """A dense GELU FeedForward (the shared expert alone) as a one-group call."""
+    from . import moe_ops
+
+    dim = ffn.net[0].proj.weight.shape[1]
+    if not _input_ok(x, dim):
+        return None
+    pack = _mlp_pack(ffn, x.device, moe_ops)
+    if pack is None or pack.hidden % 256:
+        return None
+    _, y, _, _ = moe_ops.grouped_gelu_mlp([], pack, None, None, None, x.view(-1, dim),
+                                          check_status=CHECK_STATUS_EVERY_CALL)
+    return y.view(x.shape)
+
+
 def _modulation_ok(x: torch.Tensor, *vectors: torch.Tensor) -> bool:
     """shift / scale / gate as the blocks produce them: bf16 chunks [B, 1, D] of one adaLN output on x's device."""
     b, d = x.shape[0], x.shape[-1]

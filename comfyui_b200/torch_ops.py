@@ -64,6 +64,7 @@ def _workspace(layer: moe_ops.LayerPack, n_tokens: int) -> moe_ops.Workspace:
 def release_workspaces() -> None:
     _workspaces.clear()
     _packs.clear()
+    _mlp_packs.clear()
 
 
 @torch.library.custom_op("comfyui_b200::hidream_moe", mutates_args=())
@@ -109,6 +110,48 @@ def hidream_gate(x: torch.Tensor, gate: torch.Tensor) -> List[torch.Tensor]:
 def _(x, gate):
     n = x.shape[0]
     return [x.new_empty((n, 2), dtype=torch.int64), x.new_empty((n, 2), dtype=torch.float32)]
+
+
+_mlp_packs = {}
+
+
+def _mlp_layer(gate, w1, b1, w2, b2) -> moe_ops.MlpLayerPack:
+    """MlpLayerPack for these tensors, cached on their identity and version."""
+    key = _key([gate, *w1, *b1, *w2, *b2])
+    hit = _mlp_packs.get(key)
+    if hit is not None:
+        return hit
+    ffns = [moe_ops.MlpPack(w1[i], _opt(b1, i), w2[i], _opt(b2, i)) for i in range(len(w1))]
+    layer = moe_ops.MlpLayerPack(gate, ffns[:-1], ffns[-1], top_k=2)
+    while len(_mlp_packs) >= _PACK_SLOTS:
+        _mlp_packs.pop(next(iter(_mlp_packs)))
+    _mlp_packs[key] = layer
+    return layer
+
+
+@torch.library.custom_op("comfyui_b200::hunyuan3d_moe", mutates_args=())
+def hunyuan3d_moe(x: torch.Tensor, gate: torch.Tensor, w1: List[torch.Tensor], b1: List[torch.Tensor],
+                  w2: List[torch.Tensor], b2: List[torch.Tensor]) -> torch.Tensor:
+    """MoEBlock.forward (eval) of Hunyuan3D-2.1 on x [N, D] (bf16, contiguous, CUDA).  Weight lists hold the routed
+    experts followed by the shared expert; the bias lists are either empty or of the same length."""
+    layer = _mlp_layer(gate, w1, b1, w2, b2)
+    return moe_ops.moe_mlp_forward(layer, x, _workspace(layer, x.shape[0]))
+
+
+@hunyuan3d_moe.register_fake
+def _(x, gate, w1, b1, w2, b2):
+    return torch.empty_like(x)
+
+
+def mlp_layer_args(layer: moe_ops.MlpLayerPack):
+    """The list arguments of hunyuan3d_moe for an MlpLayerPack (routed experts first, shared expert last)."""
+    ffns = list(layer.experts) + [layer.shared]
+
+    def col(name):
+        vals = [getattr(f, name) for f in ffns]
+        return [] if any(v is None for v in vals) else vals
+
+    return [f.w1 for f in ffns], col("b1"), [f.w2 for f in ffns], col("b2")
 
 
 def layer_args(layer: moe_ops.LayerPack):

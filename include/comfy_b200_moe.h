@@ -26,7 +26,7 @@
 extern "C" {
 #endif
 
-#define COMFY_MOE_ABI_VERSION 2
+#define COMFY_MOE_ABI_VERSION 3
 
 /* Return codes. */
 #define COMFY_MOE_OK 0
@@ -175,6 +175,28 @@ int comfy_moe_grouped_swiglu(int w_dtype, int n_groups, const ComfyMoeFfnWeights
                              void* h_perm, void* y_perm, const void* x_shared, void* h_shared_ws, void* y_shared,
                              int32_t* status, void* stream);
 
+/* ---- grouped GELU-MLP expert GEMM: the experts of the Hunyuan3D-2.1 MoE block ----------------------------------
+ * Replaces FeedForward.forward = Linear(dim, hidden, bias) -> exact GELU -> Linear(hidden, dim, bias)
+ * (comfy/ldm/hunyuan3dv2_1/hunyuandit.py:8-50) for every routed expert and the shared expert:
+ *   h = bf16( gelu( bf16(a . w1^T + b1) ) )        y = bf16( h . w2^T + b2 )
+ * bf16 only.  Arguments as comfy_moe_grouped_swiglu.  Requires dim % 256 == 0 and hidden % 256 == 0.
+ */
+typedef struct ComfyMoeMlpWeights {
+  const void* w1;         /* net.0.proj.weight [hidden, dim], leading dimension ld1 */
+  const void* b1;         /* net.0.proj.bias [hidden] or NULL */
+  const void* w2;         /* net.2.weight [dim, hidden], leading dimension ld2 */
+  const void* b2;         /* net.2.bias [dim] or NULL */
+  int64_t ld1;
+  int64_t ld2;
+  int32_t hidden;
+  int32_t reserved;
+} ComfyMoeMlpWeights;
+
+int comfy_moe_grouped_gelu_mlp(int n_groups, const ComfyMoeMlpWeights* h_groups, const ComfyMoeMlpWeights* h_shared,
+                               const int32_t* row_start, const int32_t* row_count, int64_t rows_cap, int n_tokens,
+                               int dim, const void* x_perm, void* h_perm, void* y_perm, const void* x_shared,
+                               void* h_shared_ws, void* y_shared, int32_t* status, void* stream);
+
 /* ---- weighted combine: replaces mul_ + scatter_reduce_ + shared add (model.py:341-345, 324) ---------------
  * out[t] = bf16( bf16( bf16(w0*y[r0]) + bf16(w1*y[r1]) ) + y_shared[t] ), weights rounded to bf16 first.
  * y_shared may be NULL (routed part only, what moe_infer returns).
@@ -227,6 +249,23 @@ typedef struct ComfyMoeWorkspace {
  */
 int comfy_moe_forward(const ComfyMoeLayer* h_layer, const ComfyMoeWorkspace* h_ws, const void* x, int n_tokens,
                       void* out, void* stream);
+
+/* ---- MoEBlock.forward in eval mode (comfy/ldm/hunyuan3dv2_1/hunyuandit.py:130-185): gate -> plan+permute ->
+ * GELU-MLP experts -> combine (index_add_ of the weighted expert outputs, then + shared_experts(x)).
+ * Same workspace struct as comfy_moe_forward (x_q unused); up to COMFY_MOE_MAX_EXPERTS experts, top-2.
+ */
+typedef struct ComfyMoeMlpLayer {
+  int32_t dim;
+  int32_t n_experts;
+  int32_t top_k;
+  int32_t gate_dtype;         /* COMFY_MOE_BF16 or COMFY_MOE_FP32 */
+  const void* w_gate;         /* [n_experts, dim] */
+  ComfyMoeMlpWeights experts[COMFY_MOE_MAX_EXPERTS];
+  ComfyMoeMlpWeights shared;
+} ComfyMoeMlpLayer;
+
+int comfy_moe_forward_gelu_mlp(const ComfyMoeMlpLayer* h_layer, const ComfyMoeWorkspace* h_ws, const void* x,
+                               int n_tokens, void* out, void* stream);
 
 /* ---- the element-wise passes a HiDream block runs around its feed-forward (model.py:429-433, 515-523) --------
  * Modulation vectors (shift, scale, gate) are bf16 [batch, dim] views with `*_batch_stride` elements between batch

@@ -1,4 +1,4 @@
-"""Generates tests/golden/hidream_moe_small.npz by running the UNMODIFIED reference.
+"""Generates tests/golden/hidream_moe_small.npz and hunyuan3d_moe_small.npz by running the UNMODIFIED reference.
 
 Usage (in a container that has the reference tree; it is not needed at test time):
 
@@ -22,6 +22,7 @@ ROOT = os.path.dirname(os.path.dirname(HERE))
 sys.path.insert(0, ROOT)
 
 from oracle import hidream_moe_oracle as O  # noqa: E402  (seeded weight recipe only)
+from oracle import hunyuan3d_moe_oracle as H  # noqa: E402  (seeded weight recipe only)
 
 DIM, HIDDEN_DIM, E, K = 256, 1024, 4, 2
 BATCH, SEQ = 2, 64
@@ -130,5 +131,53 @@ def main(ref_root: str) -> None:
         print(" ", k, meta[k])
 
 
+def hunyuan3d(ref_root: str) -> None:
+    """MoEBlock of comfy/ldm/hunyuan3dv2_1/hunyuandit.py at reduced size: 8 experts, top-2, GELU feed-forwards."""
+    import comfy.ops
+    from comfy.ldm.hunyuan3dv2_1.hunyuandit import MoEBlock
+
+    dim, inner, n_exp, k, batch, seq = 256, 1024, 8, 2, 2, 64
+    n = batch * seq
+    out = {}
+
+    def f32(t):
+        return t.detach().float().numpy()
+
+    x32 = H.make_input(n, dim, X_SEED).view(batch, seq, dim)
+    for name, dtype in (("fp32", torch.float32), ("bf16", torch.bfloat16)):
+        layer = H.make_layer(dim, inner, n_exp, W_SEED, dtype=dtype)
+        m = MoEBlock(dim, num_experts=n_exp, moe_top_k=k, ff_inner_dim=inner, operations=comfy.ops.disable_weight_init,
+                     device="cpu", dtype=dtype)
+        res = m.load_state_dict(layer, strict=True)
+        assert not res.missing_keys and not res.unexpected_keys
+        x = x32.to(dtype)
+        with torch.no_grad():
+            m.eval()
+            out[f"{name}/forward"] = f32(m(x.clone()).view(n, dim))            # as shipped: gate in x.dtype
+            idx_s, w_s, _ = m.gate(x)
+            out[f"{name}/idx_shipped"] = idx_s.numpy().astype(np.int64)
+            out[f"{name}/w_shipped"] = f32(w_s)
+            idx, w, _ = m.gate(x.float())                                         # the parity contract's fp32 gate
+            w = w.to(dtype)
+            x2 = x.view(n, dim)
+            routed = m.moe_infer(x2, idx.view(-1), w.view(-1, 1))
+            shared = m.shared_experts(x2)
+            out[f"{name}/idx"] = idx.numpy().astype(np.int64)
+            out[f"{name}/w"] = f32(w)
+            out[f"{name}/routed"] = f32(routed)
+            out[f"{name}/shared"] = f32(shared)
+            out[f"{name}/out"] = f32(routed + shared)
+            m.train()
+            out[f"{name}/forward_train_branch"] = f32(m(x.clone()).view(n, dim))
+    out["state_dict_keys"] = np.array(sorted(layer.keys()))
+    out["meta_keys"] = np.array(["dim", "inner", "n_experts", "top_k", "batch", "seq", "w_seed", "x_seed", "torch_version"])
+    out["meta_vals"] = np.array([str(v) for v in (dim, inner, n_exp, k, batch, seq, W_SEED, X_SEED, torch.__version__)])
+    path = os.path.join(HERE, "hunyuan3d_moe_small.npz")
+    np.savez_compressed(path, **out)
+    print("wrote", path, os.path.getsize(path), "bytes")
+
+
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    main(root)
+    hunyuan3d(root)
