@@ -291,8 +291,8 @@ def run_gpu_arm(args) -> None:
                 "frac_of_burst": achieved / (peaks["tflops_burst"] * (2.0 if fp8 else 1.0)),
                 "frac_of_nominal": achieved / (4500.0 if fp8 else 2250.0),
                 # dram__bytes_read + dram__bytes_write of the two launches, from the ncu capture summarised in
-                # profiles/grouped_gemm_bf16_8192tokens.md (same workload)
-                "traffic": None if fp8 else 1.573e9, "algorithmic_bytes": None if fp8 else 1.30e9,
+                # profiles/grouped_gemm_{bf16,fp8}_8192tokens.md (same workload)
+                "traffic": 0.658e9 if fp8 else 1.587e9, "algorithmic_bytes": 0.71e9 if fp8 else 1.30e9,
             }
             line["stages"] = stages
             line["gpu_bar"] = gpu_bar
