@@ -142,7 +142,18 @@ def run_reference_arm(args) -> None:
     print(json.dumps(line))
 
 
-def workload_config(n_gpus: int, dtype: str = "bf16"):
+def workload_config(n_gpus: int, dtype: str = "bf16", tokens_per_gpu: int = TOKENS_PER_GPU, config5: bool = False):
+    if config5:
+        return {
+            "workload": "BASELINE config 5: HiDream MoE FFN layer, bf16, 8 x 16384 tokens in total, skewed router "
+                        f"(gate.weight[0, 0] = {SKEW_BIAS} on a constant input feature: expert 0 takes about 60 % of the "
+                        "top-1 picks), fp32 gate",
+            "tokens_per_gpu": tokens_per_gpu, "global_tokens": tokens_per_gpu * n_gpus, "dim": DIM, "experts": N_EXPERTS,
+            "top_k": TOP_K, "hidden": HIDDEN, "hidden_shared": HIDDEN_SHARED,
+            "parallelism": "single GPU" if n_gpus == 1 else f"expert-parallel x{n_gpus} (NCCL all-to-all), shared "
+                                                            "expert data-parallel",
+            "l2": "no flush: one step touches gigabytes of activations",
+        }
     what = ("BASELINE config 2: HiDream MoE FFN layer, bf16 weights and activations, 2 x 4096 tokens per GPU, fp32 gate"
             if dtype == "bf16" else
             "BASELINE config 3: HiDream MoE FFN layer, expert and shared weights e4m3 with per-tensor fp32 scales, bf16 "
@@ -158,7 +169,12 @@ def workload_config(n_gpus: int, dtype: str = "bf16"):
 
 
 # ------------------------------------------------------------------------------------------ GPU arm
-def make_synthetic(dev, seed_w: int = 0, seed_x: int = 1, fp8: bool = False):
+SKEW_BIAS = 1.16          # config 5: expert 0 wins about 60 % of the top-1 picks
+CONFIG5_TOKENS = 131072   # 8 images of 2048 x 2048 (16384 tokens each)
+
+
+def make_synthetic(dev, seed_w: int = 0, seed_x: int = 1, fp8: bool = False, n_tokens: int = TOKENS_PER_GPU,
+                   skew: bool = False):
     """Seeded synthetic weights and input, generated on the host exactly like the oracle's recipe (same
     generator, same draw order) without importing it, then moved to the device."""
     g = torch.Generator().manual_seed(seed_w)
@@ -180,7 +196,12 @@ def make_synthetic(dev, seed_w: int = 0, seed_x: int = 1, fp8: bool = False):
             state[k] = (w / sc).to(torch.float8_e4m3fn)
             state[k[: -len(".weight")] + ".scale_weight"] = sc.to(torch.float32)
     gx = torch.Generator().manual_seed(seed_x)
-    x = torch.randn((TOKENS_PER_GPU, DIM), generator=gx, dtype=torch.float32).bfloat16()
+    x = torch.randn((n_tokens, DIM), generator=gx, dtype=torch.float32).bfloat16()
+    if skew:
+        # the gate has no bias term: a constant input feature and one weight column stand in for it
+        x[:, 0] = 1
+        state["gate.weight"][:, 0] = 0
+        state["gate.weight"][0, 0] = SKEW_BIAS
     return state, x
 
 
@@ -203,7 +224,9 @@ def run_gpu_arm(args) -> None:
         dist.init_process_group("nccl", device_id=dev)
 
     fp8 = args.dtype == "fp8"
-    state, x_host = make_synthetic(dev, seed_w=0, seed_x=1 + rank, fp8=fp8)
+    config5 = args.workload == "config5"
+    n = CONFIG5_TOKENS // world if config5 else TOKENS_PER_GPU
+    state, x_host = make_synthetic(dev, seed_w=0, seed_x=1 + rank, fp8=fp8, n_tokens=n, skew=config5)
     operations = ops.disable_weight_init if not fp8 else ops.scaled_fp8_ops(
         fp8_matrix_mult=True, scale_input=False, override_dtype=torch.float8_e4m3fn)
     module = MOEFeedForwardSwiGLU(DIM, HIDDEN_DIM, N_EXPERTS, TOP_K, dtype=torch.bfloat16, device=dev,
@@ -211,8 +234,7 @@ def run_gpu_arm(args) -> None:
     module.load_state_dict(state, strict=True)
     x_pinned = x_host.pin_memory()
     out_pinned = torch.empty_like(x_host).pin_memory()
-    x = x_host.to(dev).view(2, TOKENS_PER_GPU // 2, DIM)
-    n = TOKENS_PER_GPU
+    x = x_host.to(dev).view(2, n // 2, DIM)
 
     if world > 1:
         from comfyui_b200.expert_parallel import ExpertParallelMoE
@@ -269,8 +291,10 @@ def run_gpu_arm(args) -> None:
         value = n * world / (ms_step * 1e-3)
         line = {
             "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": args.dtype, "data": "synthetic", "config": workload_config(world, args.dtype),
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True,
+            "scaling": "strong" if config5 else "weak",
+            "vs_baseline": None, "dtype": args.dtype, "data": "synthetic",
+            "config": workload_config(world, args.dtype, n, config5),
             "e2e": {"value": n * world / (ms_e2e / args.steps * 1e-3), "unit": "tokens/s",
                     "h2d_bytes_per_step": x_pinned.numel() * 2, "d2h_bytes_per_step": out_pinned.numel() * 2},
             "gpu_launches": launches_per_step * args.steps,
@@ -278,6 +302,20 @@ def run_gpu_arm(args) -> None:
             "layer_tflops": FLOPS_PER_TOKEN * n * world / (ms_step * 1e-3) / 1e12,
             "layer_frac_of_nominal": FLOPS_PER_TOKEN * n / (ms_step * 1e-3) / 1e12 / (4500.0 if fp8 else 2250.0),
         }
+        if config5:
+            # realised routing: slots per expert over all GPUs, and the rows each GPU's routed experts process
+            if world > 1:
+                per_expert = [sum(c[e] for c in runner.last_counts) for e in range(N_EXPERTS)]
+                owners = [runner.place.owners(e) for e in range(N_EXPERTS)]
+                rows = [sum(per_expert[e] for e in range(N_EXPERTS) if r in owners[e]) for r in range(world)]
+            else:
+                from comfyui_b200 import torch_ops
+
+                layer = ops._layer_pack(module, x)
+                per_expert = torch_ops._workspace(layer, n).expert_counts.tolist()
+                rows = [sum(per_expert)]
+            line["routing"] = {"slots_per_expert": per_expert, "share_of_expert_0": per_expert[0] / sum(per_expert),
+                               "routed_rows_per_gpu": rows}
         if stages is not None:
             gemm_ms = stages["grouped_gemm_ms"]
             achieved = FLOPS_PER_TOKEN_GEMM * n / (gemm_ms * 1e-3) / 1e12
@@ -515,8 +553,10 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="hidream", choices=["hidream", "hunyuan3d"],
-                    help="hidream = the headline layer; hunyuan3d = the sibling GELU-MLP MoE block (one GPU, bf16)")
+    ap.add_argument("--workload", default="hidream", choices=["hidream", "config5", "hunyuan3d"],
+                    help="hidream = the headline layer (8192 tokens per GPU, weak scaling); config5 = 131072 tokens in "
+                         "total with a skewed router (strong scaling); hunyuan3d = the sibling GELU-MLP MoE block "
+                         "(one GPU, bf16)")
     ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp8"],
                     help="bf16 (BASELINE config 2, the default) or per-tensor scaled fp8 e4m3 expert weights (config 3)")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU oracle and the stock-composition timings (profiling runs)")

@@ -47,6 +47,7 @@ constexpr int kOutStageBytes = 2 * kABytes;      // epilogue staging tile: 128 r
 constexpr int kEpilogueWarps = 8;                 // two per TMEM lane quarter, each taking half of the columns
 constexpr int kGemmThreads = 64 + 32 * kEpilogueWarps;
 constexpr int kTmemCols = kAccStages * kBlockN;   // 512
+constexpr int kBandTiles = 32;                    // row tiles per band of a row-fastest pass (8192 rows on SM pairs)
 constexpr int kMaxGroups = kMaxExperts + 1;
 constexpr int kMaxMaps = 4 + 2 * kMaxGroups;
 
@@ -210,11 +211,19 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
     while (t >= s_tile_start[g + 1]) ++g;
     const int local = t - s_tile_start[g];
     if (kSwiglu || p.m_fastest) {
-      // pass 1: row tiles fastest.  The CTAs running together share a few weight panels (read from HBM
-      // once) and sweep all rows of the group, which stay in L2 (K = dim is short).
+      // pass 1: row tiles fastest inside a band of kBandTiles row tiles.  The CTAs running together share a few
+      // weight panels and sweep the band's rows, which stay in L2 (K = dim is short: a band is at most 42 MB)
+      // while every weight panel passes once per band.  A group with fewer row tiles than a band (the HiDream
+      // shapes at 8192 tokens) is one band: weights read from HBM once.  Without the bands a group of 100 000
+      // rows would re-read all of its activations from HBM for every weight panel.
       const int mt = s_m_tiles[g];
-      n_tile = local / mt;
-      m_tile = local - n_tile * mt;
+      const int per_band = kBandTiles * p.groups[g].n_tiles;
+      const int band = local / per_band;
+      const int rem = local - band * per_band;
+      const int m0 = band * kBandTiles;
+      const int in_band = (mt - m0) < kBandTiles ? (mt - m0) : kBandTiles;
+      n_tile = rem / in_band;
+      m_tile = m0 + (rem - n_tile * in_band);
     } else {
       // pass 2: column tiles fastest.  K = hidden is long, so a row tile of h is 1.7 MB; running all
       // column tiles of a few row tiles together reads every row of h from HBM once while w2 stays in L2.
