@@ -142,6 +142,12 @@ def run_reference_arm(args) -> None:
     print(json.dumps(line))
 
 
+def ep_transport() -> str:
+    if os.environ.get("COMFY_B200_EP_TRANSPORT", "peer") == "nccl":
+        return "NCCL point-to-point dispatch and combine"
+    return "dispatch and combine by the kernels over NVLink peer memory, NCCL all-gather of the routing histograms"
+
+
 def workload_config(n_gpus: int, dtype: str = "bf16", tokens_per_gpu: int = TOKENS_PER_GPU, config5: bool = False):
     if config5:
         return {
@@ -150,7 +156,7 @@ def workload_config(n_gpus: int, dtype: str = "bf16", tokens_per_gpu: int = TOKE
                         "top-1 picks), fp32 gate",
             "tokens_per_gpu": tokens_per_gpu, "global_tokens": tokens_per_gpu * n_gpus, "dim": DIM, "experts": N_EXPERTS,
             "top_k": TOP_K, "hidden": HIDDEN, "hidden_shared": HIDDEN_SHARED,
-            "parallelism": "single GPU" if n_gpus == 1 else f"expert-parallel x{n_gpus} (NCCL all-to-all), shared "
+            "parallelism": "single GPU" if n_gpus == 1 else f"expert-parallel x{n_gpus} ({ep_transport()}), shared "
                                                             "expert data-parallel",
             "l2": "no flush: one step touches gigabytes of activations",
         }
@@ -162,7 +168,7 @@ def workload_config(n_gpus: int, dtype: str = "bf16", tokens_per_gpu: int = TOKE
         "workload": what,
         "tokens_per_gpu": TOKENS_PER_GPU, "global_tokens": TOKENS_PER_GPU * n_gpus, "dim": DIM, "experts": N_EXPERTS,
         "top_k": TOP_K, "hidden": HIDDEN, "hidden_shared": HIDDEN_SHARED,
-        "parallelism": "single GPU" if n_gpus == 1 else f"expert-parallel x{n_gpus} (NCCL all-to-all), shared expert "
+        "parallelism": "single GPU" if n_gpus == 1 else f"expert-parallel x{n_gpus} ({ep_transport()}), shared expert "
                                                         "data-parallel",
         "l2": "no flush: one step touches 0.48 GB of weights and 0.6 GB of activations, far more than the 126 MB L2",
     }
@@ -237,9 +243,14 @@ def run_gpu_arm(args) -> None:
     x = x_host.to(dev).view(2, n // 2, DIM)
 
     if world > 1:
-        from comfyui_b200.expert_parallel import ExpertParallelMoE
+        from comfyui_b200.expert_parallel import ExpertParallelMoE, PeerExpertParallelMoE
 
-        runner = ExpertParallelMoE(module, dist.group.WORLD)
+        # default: rows move over peer memory inside the kernels; COMFY_B200_EP_TRANSPORT=nccl selects the
+        # host-planned NCCL exchange (bf16 only)
+        if os.environ.get("COMFY_B200_EP_TRANSPORT", "peer") == "nccl":
+            runner = ExpertParallelMoE(module, dist.group.WORLD)
+        else:
+            runner = PeerExpertParallelMoE(module, dist.group.WORLD)
         step = lambda inp: runner(inp)                      # noqa: E731
         launches_per_step = runner.launches_per_step
     else:
@@ -265,6 +276,8 @@ def run_gpu_arm(args) -> None:
             ev1.record()
             barrier()
         ms_total = ev0.elapsed_time(ev1)
+        if world > 1 and hasattr(runner, "check"):
+            runner.check()          # no flag wait ran out, every routed row fitted its receive buffer
 
         # ---- end to end: every step copies its input from pinned host memory and its output back to pinned host
         # memory.  The copies run on their own streams with two buffers each, the way a serving loop would feed
@@ -305,7 +318,8 @@ def run_gpu_arm(args) -> None:
         if config5:
             # realised routing: slots per expert over all GPUs, and the rows each GPU's routed experts process
             if world > 1:
-                per_expert = [sum(c[e] for c in runner.last_counts) for e in range(N_EXPERTS)]
+                last = runner.last_counts_host if hasattr(runner, "last_counts_host") else runner.last_counts
+                per_expert = [sum(c[e] for c in last) for e in range(N_EXPERTS)]
                 owners = [runner.place.owners(e) for e in range(N_EXPERTS)]
                 rows = [sum(per_expert[e] for e in range(N_EXPERTS) if r in owners[e]) for r in range(world)]
             else:

@@ -7,11 +7,11 @@ from __future__ import annotations
 
 import ctypes
 import os
-from ctypes import POINTER, Structure, c_char_p, c_float, c_int, c_int32, c_int64, c_uint8, c_void_p
+from ctypes import POINTER, Structure, c_char_p, c_float, c_int, c_int32, c_int64, c_uint8, c_uint32, c_void_p
 
 from . import build as _build
 
-ABI_VERSION = 3
+ABI_VERSION = 4
 
 OK, EINVAL, EUNSUPPORTED, ECUDA, ETIMEOUT, EDEVICE, ETOOLARGE = range(7)
 BF16, FP32, FP8_E4M3 = 0, 1, 2
@@ -19,6 +19,8 @@ ROW_ALIGN = 128
 TOKENS_PER_BLOCK = 32
 MAX_EXPERTS = 8
 STATIC_MAX_TOKENS = 131072
+MAX_RANKS = 8
+EP_ARRIVED, EP_DONE = 0, 1
 
 EXPORTS = (
     "comfy_moe_abi_version",
@@ -41,6 +43,10 @@ EXPORTS = (
     "comfy_moe_combine_block",
     "comfy_moe_ffn_block",
     "comfy_moe_read_status",
+    "comfy_moe_ep_dispatch",
+    "comfy_moe_ep_signal",
+    "comfy_moe_ep_wait",
+    "comfy_moe_ep_combine",
 )
 
 
@@ -105,6 +111,23 @@ class MlpLayer(Structure):
         ("w_gate", c_void_p),
         ("experts", MlpWeights * MAX_EXPERTS),
         ("shared", MlpWeights),
+    ]
+
+
+class PeerPlan(Structure):
+    """struct ComfyMoePeerPlan"""
+
+    _fields_ = [
+        ("world", c_int32),
+        ("rank", c_int32),
+        ("n_experts", c_int32),
+        ("hidden_splits", c_int32),
+        ("owner0", c_int32 * MAX_EXPERTS),
+        ("owner1", c_int32 * MAX_EXPERTS),
+        ("cap_rows", c_int64),
+        ("peer_recv", c_void_p * MAX_RANKS),
+        ("peer_y", c_void_p * MAX_RANKS),
+        ("peer_flags", c_void_p * MAX_RANKS),
     ]
 
 
@@ -204,6 +227,14 @@ def load(build_if_missing: bool = False) -> ctypes.CDLL:
     lib.comfy_moe_ffn_block.argtypes = [POINTER(Layer), POINTER(Workspace), c_void_p, c_void_p, c_void_p, c_void_p,
                                         c_int64, c_int, c_int, c_float, c_void_p, c_void_p]
     lib.comfy_moe_read_status.argtypes = [c_void_p, c_void_p, POINTER(c_int32)]
+    lib.comfy_moe_ep_dispatch.argtypes = [
+        POINTER(PeerPlan), c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
+        c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+    ]
+    lib.comfy_moe_ep_signal.argtypes = [POINTER(PeerPlan), c_int, c_uint32, c_void_p]
+    lib.comfy_moe_ep_wait.argtypes = [POINTER(PeerPlan), c_int, c_uint32, c_void_p, c_void_p]
+    lib.comfy_moe_ep_combine.argtypes = [POINTER(PeerPlan), c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                         c_void_p, c_void_p]
     for name in EXPORTS:
         if name not in ("comfy_moe_error_string",):
             getattr(lib, name).restype = c_int

@@ -23,7 +23,8 @@ extern "C" int comfy_moe_read_status(const int32_t* status, void* stream, int32_
   if (cudaMemcpyAsync(h_status, status, sizeof(int32_t), cudaMemcpyDeviceToHost, s) != cudaSuccess)
     return COMFY_MOE_ECUDA;
   if (cudaStreamSynchronize(s) != cudaSuccess) return COMFY_MOE_ECUDA;
-  return *h_status == 0 ? COMFY_MOE_OK : COMFY_MOE_ETIMEOUT;
+  if (*h_status == 0) return COMFY_MOE_OK;
+  return *h_status == 8 ? COMFY_MOE_ETOOLARGE : COMFY_MOE_ETIMEOUT;   // 8: routed rows exceed a peer receive buffer
 }
 
 // Block epilogue requested by comfy_moe_ffn_block: gate * (.) + residual folded into the combine.

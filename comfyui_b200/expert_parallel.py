@@ -86,7 +86,7 @@ def exchange_plan(counts: Sequence[Sequence[int]], rank: int, place: Placement):
 class CudaKernels:
     """The sm_100a kernels behind the C ABI, bound to one loaded MOEFeedForwardSwiGLU module."""
 
-    def __init__(self, module, place: Placement, rank: int):
+    def __init__(self, module, place: Placement, rank: int, allow_fp8: bool = False):
         from . import moe_ops, ops
 
         self.M = moe_ops
@@ -116,8 +116,8 @@ class CudaKernels:
                                                   scale_w2=full.scale_w2, scale_in13=full.scale_in13,
                                                   scale_in2=full.scale_in2))
         self.fp8 = self.shared.w1.dtype == torch.float8_e4m3fn
-        if self.fp8:
-            raise ValueError("expert-parallel execution covers bf16 weights")
+        if self.fp8 and not allow_fp8:
+            raise ValueError("the NCCL transport covers bf16 weights; scaled fp8 runs on the peer-memory transport")
 
     launches_local = 3      # gate, plan, permutation
 
@@ -276,3 +276,192 @@ class ExpertParallelMoE:
 
         out = k.combine(partials, row_map, w, y_shared)
         return out.view(shape)
+
+
+# ====================================================================================================
+# Peer-memory transport: dispatch and combine by the kernels themselves over NVLink, no host synchronisation
+# ====================================================================================================
+def _align(v: int, a: int = 256) -> int:
+    return (v + a - 1) // a * a
+
+
+class PeerBuffers:
+    """One rank's receive buffer, result buffer and flag block, plus every peer's as mapped in this process.
+
+    ``create`` allocates them in symmetric memory (``torch.distributed._symmetric_memory``: one allocation per rank,
+    exchanged and mapped at a rendezvous, done once per shape).  ``emulate`` builds the same structure for several
+    ranks living on ONE device, which is how the addressing logic is tested without a second GPU."""
+
+    FLAG_BYTES = 256
+
+    def __init__(self, place: Placement, rank: int, cap_rows: int, dim: int, act_dtype: torch.dtype, bases: List[int],
+                 mine: torch.Tensor, keep=None):
+        from . import _native as N
+
+        self.place, self.rank, self.cap_rows, self.dim, self.act_dtype = place, rank, cap_rows, dim, act_dtype
+        es = 1 if act_dtype == torch.float8_e4m3fn else 2
+        off_recv = self.FLAG_BYTES
+        off_y = off_recv + _align(cap_rows * dim * es)
+        self.nbytes = off_y + _align(cap_rows * dim * 2)
+        self._keep = (mine, keep)
+        raw = mine.view(torch.uint8)
+        self.flags = raw[: self.FLAG_BYTES].view(torch.int32)
+        self.recv = raw[off_recv: off_recv + cap_rows * dim * es].view(act_dtype).view(cap_rows, dim)
+        self.y = raw[off_y: off_y + cap_rows * dim * 2].view(torch.bfloat16).view(cap_rows, dim)
+        plan = N.PeerPlan()
+        plan.world, plan.rank, plan.n_experts, plan.hidden_splits = place.world, rank, place.n_experts, place.hidden_splits
+        for e in range(place.n_experts):
+            owners = place.owners(e)
+            plan.owner0[e] = owners[0]
+            plan.owner1[e] = owners[1] if len(owners) > 1 else -1
+        plan.cap_rows = cap_rows
+        for r, base in enumerate(bases):
+            plan.peer_flags[r] = base
+            plan.peer_recv[r] = base + off_recv
+            plan.peer_y[r] = base + off_y
+        self.plan = plan
+
+    @staticmethod
+    def size(cap_rows: int, dim: int, act_dtype: torch.dtype) -> int:
+        es = 1 if act_dtype == torch.float8_e4m3fn else 2
+        return PeerBuffers.FLAG_BYTES + _align(cap_rows * dim * es) + _align(cap_rows * dim * 2)
+
+    @classmethod
+    def create(cls, place: Placement, rank: int, cap_rows: int, dim: int, act_dtype: torch.dtype, device, group):
+        import os
+
+        # plain peer mappings are all the kernels need; no NVLink multicast object is bound to the buffers
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        import torch.distributed._symmetric_memory as symm_mem
+
+        buf = symm_mem.empty(cls.size(cap_rows, dim, act_dtype), dtype=torch.uint8, device=device)
+        handle = symm_mem.rendezvous(buf, group)
+        buf[: cls.FLAG_BYTES].zero_()
+        torch.cuda.synchronize(device)
+        dist.barrier(group=group)           # every rank's flags are zero before anyone raises one
+        return cls(place, rank, cap_rows, dim, act_dtype, [int(p) for p in handle.buffer_ptrs], buf, keep=handle)
+
+    @classmethod
+    def emulate(cls, place: Placement, cap_rows: int, dim: int, act_dtype: torch.dtype, device) -> List["PeerBuffers"]:
+        bufs = [torch.zeros(cls.size(cap_rows, dim, act_dtype), dtype=torch.uint8, device=device)
+                for _ in range(place.world)]
+        bases = [b.data_ptr() for b in bufs]
+        return [cls(place, r, cap_rows, dim, act_dtype, bases, bufs[r], keep=bufs) for r in range(place.world)]
+
+
+class PeerExpertParallelMoE:
+    """``out = ep(x)``: the expert-parallel layer with the rows moved by the kernels over peer memory.
+
+    One stream, no host synchronisation: gate -> plan -> all-gather of the 4-bin histograms (NCCL, device to
+    device) -> dispatch kernel (writes rows into the owners' receive buffers) -> flag -> shared expert -> wait ->
+    grouped GEMM on the received rows -> flag -> wait -> combine kernel (reads results from the owners).
+    The three ``phase_*`` methods are the step cut at its two flag waits, so a test can drive several ranks that
+    live on one GPU in lock step."""
+
+    def __init__(self, module, group=None, *, max_tokens: Optional[int] = None, buffers: Optional[PeerBuffers] = None,
+                 place: Optional[Placement] = None, rank: Optional[int] = None):
+        from . import _native as N, moe_ops
+
+        self.N, self.M = N, moe_ops
+        self.lib = N.load()
+        self.module = module
+        self.group = group
+        if buffers is None:
+            self.group = group if group is not None else dist.group.WORLD
+            rank, world = dist.get_rank(self.group), dist.get_world_size(self.group)
+            place = Placement(world, len(module.experts))
+        self.rank, self.place, self.world = rank, place, place.world
+        self.n_experts = place.n_experts
+        self.kernels = CudaKernels(module, place, rank, allow_fp8=True)
+        self.fp8 = self.kernels.fp8
+        self.buffers = buffers
+        self.max_tokens = max_tokens
+        self.epoch = 0
+        self.last_counts = None
+        self._state = None
+        # gate, plan, dispatch, 2 flags, 2 waits, shared GEMM x2, routed GEMM x2, combine
+        self.launches_per_step = 12
+
+    def _ensure_buffers(self, n: int, dim: int, device):
+        if self.buffers is not None:
+            return
+        cap_tokens = self.max_tokens if self.max_tokens is not None else n
+        # a token sends at most one slot to a given expert: world * tokens rows per local expert at most
+        cap_rows = self.world * cap_tokens * min(2, self.place.experts_per_rank)
+        act = torch.float8_e4m3fn if self.fp8 else torch.bfloat16
+        self.buffers = PeerBuffers.create(self.place, self.rank, cap_rows, dim, act, device, self.group)
+
+    # -- the three phases of a step ---------------------------------------------------------------
+    def phase_route(self, x2: torch.Tensor, counts_all: Optional[torch.Tensor] = None, gather=None):
+        """Gate, plan, histogram exchange, dispatch, "arrived" flag.  ``gather(counts) -> [world, E]`` replaces the
+        collective in single-GPU emulation."""
+        M, N, k = self.M, self.N, self.kernels
+        n, dim = x2.shape
+        dev = x2.device
+        self._ensure_buffers(n, dim, dev)
+        b = self.buffers
+        self.epoch += 1
+        idx, w, block_counts, _, _ = M.gate_topk(x2, k.gate_w)
+        block_offsets, counts, _ = M.route_plan(block_counts, n, self.n_experts)
+        if gather is not None:
+            counts_all = gather(counts)
+        elif counts_all is None:
+            counts_all = torch.empty((self.world, self.n_experts), dtype=torch.int32, device=dev)
+            dist.all_gather_into_tensor(counts_all.view(-1), counts.contiguous(), group=self.group)
+        row_map = torch.empty((n, 2), dtype=torch.int32, device=dev)
+        groups = torch.zeros((2, max(self.place.experts_per_rank, 1)), dtype=torch.int32, device=dev)
+        status = torch.zeros((2,), dtype=torch.int32, device=dev)
+        x_q = torch.empty((n, dim), dtype=torch.float8_e4m3fn, device=dev) if self.fp8 else None
+        in13 = k.local[0].scale_in13 if self.fp8 else None
+        in13_shared = k.shared.scale_in13 if self.fp8 else None
+        P, S = M._ptr, M._stream
+        N.check("comfy_moe_ep_dispatch", self.lib.comfy_moe_ep_dispatch(
+            b.plan, P(x2), P(idx), P(block_offsets), P(counts_all), n, dim, N.FP8_E4M3 if self.fp8 else N.BF16, P(in13),
+            P(x_q), P(in13_shared), P(row_map), P(groups[0]), P(groups[1]), P(status), S()))
+        N.check("comfy_moe_ep_signal", self.lib.comfy_moe_ep_signal(b.plan, N.EP_ARRIVED, self.epoch, S()))
+        self._state = dict(x2=x2, x_q=x_q, idx=idx, w=w, row_map=row_map, groups=groups, status=status,
+                           counts_all=counts_all)
+
+    def phase_experts(self):
+        """Shared expert on the local tokens, then (after every rank's rows arrived) the local routed experts."""
+        M, N, k, b, st = self.M, self.N, self.kernels, self.buffers, self._state
+        S = M._stream
+        st["y_shared"] = k.shared_expert(st["x_q"] if self.fp8 else st["x2"])
+        N.check("comfy_moe_ep_wait", self.lib.comfy_moe_ep_wait(b.plan, N.EP_ARRIVED, self.epoch, M._ptr(st["status"]), S()))
+        hidden = k.local[0].hidden
+        h_ws = getattr(self, "_h_ws", None)
+        if h_ws is None or h_ws.shape != (b.cap_rows, hidden) or h_ws.device != b.recv.device:
+            h_ws = torch.empty((b.cap_rows, hidden), dtype=b.act_dtype, device=b.recv.device)
+            self._h_ws = h_ws
+        M.grouped_swiglu(k.local, None, st["groups"][0], st["groups"][1], b.recv, None, status=st["status"],
+                         check_status=False, h_perm=h_ws, y_perm=b.y)
+        N.check("comfy_moe_ep_signal", self.lib.comfy_moe_ep_signal(b.plan, N.EP_DONE, self.epoch, S()))
+
+    def phase_combine(self) -> torch.Tensor:
+        """After every rank's results are in place: the weighted combine, reading them where they are."""
+        M, N, b, st = self.M, self.N, self.buffers, self._state
+        P, S = M._ptr, M._stream
+        n, dim = st["x2"].shape
+        N.check("comfy_moe_ep_wait", self.lib.comfy_moe_ep_wait(b.plan, N.EP_DONE, self.epoch, P(st["status"]), S()))
+        out = torch.empty((n, dim), dtype=torch.bfloat16, device=st["x2"].device)
+        N.check("comfy_moe_ep_combine", self.lib.comfy_moe_ep_combine(
+            b.plan, P(st["idx"]), P(st["row_map"]), P(st["w"]), P(st["y_shared"]), n, dim, P(out), S()))
+        self.last_status = st["status"]
+        self._last_counts_dev = st["counts_all"]
+        return out
+
+    def __call__(self, x: torch.Tensor) -> torch.Tensor:
+        shape = x.shape
+        x2 = x.reshape(-1, shape[-1])
+        self.phase_route(x2)
+        self.phase_experts()
+        return self.phase_combine().view(shape)
+
+    @property
+    def last_counts_host(self) -> List[List[int]]:
+        """[world][E] routed slots of the last call (one device-to-host copy; for reporting only)."""
+        return self._last_counts_dev.tolist()
+
+    def check(self) -> None:
+        """Synchronises and raises if a flag wait ran out or the rows did not fit the receive buffers."""
+        self.M.read_status(self.last_status)

@@ -291,10 +291,13 @@ def plan_permute(x: torch.Tensor, topk_idx: torch.Tensor, block_counts: torch.Te
 def grouped_swiglu(experts: Sequence[FfnPack], shared: Optional[FfnPack], row_start: Optional[torch.Tensor],
                    row_count: Optional[torch.Tensor], x_perm: Optional[torch.Tensor],
                    x_shared: Optional[torch.Tensor], *, status: Optional[torch.Tensor] = None,
-                   check_status: bool = True):
+                   check_status: bool = True, h_perm: Optional[torch.Tensor] = None,
+                   y_perm: Optional[torch.Tensor] = None):
     """Both passes of the grouped expert GEMM.  Group g = rows [row_start[g], row_start[g] + row_count[g]) of
     x_perm with the weights experts[g] (int32 device tensors; the routing plan's expert_offsets and
-    expert_counts on one GPU).  Returns (y_perm or None, y_shared or None, h_perm, h_shared)."""
+    expert_counts on one GPU).  ``h_perm`` / ``y_perm`` may be given (buffers of x_perm's row count, e.g. a result
+    buffer that peers read); otherwise they are allocated.  Returns (y_perm or None, y_shared or None, h_perm,
+    h_shared)."""
     ref = experts[0] if experts else shared
     dim, fp8 = ref.dim, ref.w1.dtype == _FP8
     dev = ref.w1.device
@@ -304,10 +307,16 @@ def grouped_swiglu(experts: Sequence[FfnPack], shared: Optional[FfnPack], row_st
     for i, e in enumerate(experts):
         e.fill(arr[i])
     rows_cap = 0 if x_perm is None else x_perm.shape[0]
-    h_perm = y_perm = None
     if n_e:
-        h_perm = torch.empty((rows_cap, experts[0].hidden), dtype=act, device=dev)
-        y_perm = torch.empty((rows_cap, dim), dtype=torch.bfloat16, device=dev)
+        if h_perm is None:
+            h_perm = torch.empty((rows_cap, experts[0].hidden), dtype=act, device=dev)
+        if y_perm is None:
+            y_perm = torch.empty((rows_cap, dim), dtype=torch.bfloat16, device=dev)
+        if h_perm.shape != (rows_cap, experts[0].hidden) or y_perm.shape != (rows_cap, dim) or \
+                not h_perm.is_contiguous() or not y_perm.is_contiguous():
+            raise ValueError("h_perm / y_perm must be contiguous buffers with x_perm's row count")
+    else:
+        h_perm = y_perm = None
     n_tokens = 0 if x_shared is None else x_shared.shape[0]
     sh = h_sh = y_sh = None
     if shared is not None and n_tokens > 0:

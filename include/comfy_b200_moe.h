@@ -26,7 +26,7 @@
 extern "C" {
 #endif
 
-#define COMFY_MOE_ABI_VERSION 3
+#define COMFY_MOE_ABI_VERSION 4
 
 /* Return codes. */
 #define COMFY_MOE_OK 0
@@ -266,6 +266,52 @@ typedef struct ComfyMoeMlpLayer {
 
 int comfy_moe_forward_gelu_mlp(const ComfyMoeMlpLayer* h_layer, const ComfyMoeWorkspace* h_ws, const void* x,
                                int n_tokens, void* out, void* stream);
+
+/* ---- expert parallelism over peer memory (one process per GPU, NVLink peer access) ---------------------------
+ * No counterpart in the reference (it runs on one GPU).  Tokens stay with their rank; expert e is computed by rank
+ * owner0[e] (and, with hidden_splits == 2, by owner1[e], each holding half of the hidden dimension).  Every rank owns
+ * a receive buffer [cap_rows, dim] (activation dtype), a result buffer [cap_rows, dim] (bf16) and a flag block
+ * (2 * COMFY_MOE_MAX_RANKS zero-initialised uint32), all mapped into every peer; peer_*[r] are rank r's buffers as
+ * mapped in the calling process.  One step on each rank, all on one stream:
+ *   gate, route_plan -> all-gather of expert_counts into counts_all [world, n_experts] (any collective) ->
+ *   comfy_moe_ep_dispatch -> comfy_moe_ep_signal(ARRIVED) -> (shared expert) -> comfy_moe_ep_wait(ARRIVED) ->
+ *   comfy_moe_grouped_swiglu over (group_start, group_count) on the receive buffer, results into the result buffer ->
+ *   comfy_moe_ep_signal(DONE) -> comfy_moe_ep_wait(DONE) -> comfy_moe_ep_combine.
+ * `epoch` must grow by one per step, equally on all ranks.  A wait that runs out of its clock budget (about two
+ * seconds) writes a code to `status`; so does a dispatch whose rows do not fit cap_rows (comfy_moe_read_status
+ * returns COMFY_MOE_ETIMEOUT / COMFY_MOE_ETOOLARGE).
+ *   comfy_moe_ep_dispatch  permutation into the owners' receive buffers (quantising to e4m3 on the way for
+ *                          act_dtype FP8, which also fills x_q for the shared expert); row_map[t, k] = row at the
+ *                          owner; group_start / group_count [local experts] = this rank's own work list.
+ *   comfy_moe_ep_combine   comfy_moe_combine with every routed row read from its owner's result buffer (two
+ *                          partial rows summed, rounded to bf16, with a hidden split).
+ */
+#define COMFY_MOE_MAX_RANKS 8
+#define COMFY_MOE_EP_ARRIVED 0
+#define COMFY_MOE_EP_DONE 1
+
+typedef struct ComfyMoePeerPlan {
+  int32_t world;
+  int32_t rank;
+  int32_t n_experts;
+  int32_t hidden_splits;                      /* 1 or 2 */
+  int32_t owner0[COMFY_MOE_MAX_EXPERTS];
+  int32_t owner1[COMFY_MOE_MAX_EXPERTS];      /* used when hidden_splits == 2 */
+  int64_t cap_rows;
+  void* peer_recv[COMFY_MOE_MAX_RANKS];
+  void* peer_y[COMFY_MOE_MAX_RANKS];
+  uint32_t* peer_flags[COMFY_MOE_MAX_RANKS];
+} ComfyMoePeerPlan;
+
+int comfy_moe_ep_dispatch(const ComfyMoePeerPlan* h_plan, const void* x, const int32_t* topk_idx,
+                          const int32_t* block_offsets, const int32_t* counts_all, int n_tokens, int dim,
+                          int act_dtype, const float* act_scale, void* x_q, const float* x_q_scale, int32_t* row_map,
+                          int32_t* group_start, int32_t* group_count, int32_t* status, void* stream);
+int comfy_moe_ep_signal(const ComfyMoePeerPlan* h_plan, int kind, uint32_t epoch, void* stream);
+int comfy_moe_ep_wait(const ComfyMoePeerPlan* h_plan, int kind, uint32_t epoch, int32_t* status, void* stream);
+int comfy_moe_ep_combine(const ComfyMoePeerPlan* h_plan, const int32_t* topk_idx, const int32_t* row_map,
+                         const float* topk_weight, const void* y_shared, int n_tokens, int dim, void* out,
+                         void* stream);
 
 /* ---- the element-wise passes a HiDream block runs around its feed-forward (model.py:429-433, 515-523) --------
  * Modulation vectors (shift, scale, gate) are bf16 [batch, dim] views with `*_batch_stride` elements between batch

@@ -1,0 +1,148 @@
+"""Expert parallelism over peer memory.
+
+Single GPU: the ranks of a 2-, 4- or 8-way placement are emulated on one device (every rank's receive / result /
+flag buffers are ordinary allocations of that device, the phases of a step are run rank after rank), which checks
+the dispatch addressing, the flag kernels, the grouped GEMM on received rows and the peer combine against the
+single-GPU layer.  Flags are always raised before they are waited for, so no kernel ever waits on another launch.
+
+Several GPUs (skipped with fewer): child processes, one per GPU, symmetric memory, NCCL only for the histogram
+all-gather.
+"""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from oracle import hidream_moe_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+DIM, HIDDEN_DIM, E = 512, 2048, 4
+
+
+def _module(dev, fp8=False, n_experts=E):
+    from comfyui_b200 import ops
+    from comfyui_b200.ldm.hidream.model import MOEFeedForwardSwiGLU
+
+    layer = {k: v.bfloat16() for k, v in O.make_layer(DIM, HIDDEN_DIM, n_experts, seed=0).items()}
+    operations = ops.disable_weight_init
+    if fp8:
+        layer = O.quantize_layer_fp8(layer)
+        operations = ops.scaled_fp8_ops(fp8_matrix_mult=True, scale_input=False, override_dtype=torch.float8_e4m3fn)
+    module = MOEFeedForwardSwiGLU(DIM, HIDDEN_DIM, n_experts, 2, dtype=torch.bfloat16, device=dev,
+                                  operations=operations).eval()
+    module.load_state_dict({k: v.to(dev) for k, v in layer.items()}, strict=True)
+    return module
+
+
+@pytest.mark.parametrize("world,fp8", [(2, False), (4, False), (8, False), (2, True), (8, True)])
+def test_emulated_ranks_on_one_gpu(cuda_device, world, fp8):
+    from comfyui_b200 import moe_ops as M
+    from comfyui_b200.expert_parallel import PeerBuffers, PeerExpertParallelMoE, Placement
+
+    dev = cuda_device
+    module = _module(dev, fp8)
+    place = Placement(world, E)
+    tokens = [1000, 700, 333, 1, 512, 129, 64, 2048][:world]
+    xs = [O.make_input(n, DIM, seed=100 + r).bfloat16().to(dev) for r, n in enumerate(tokens)]
+    cap_rows = sum(tokens) * min(2, place.experts_per_rank)
+    act = torch.float8_e4m3fn if fp8 else torch.bfloat16
+    bufs = PeerBuffers.emulate(place, cap_rows, DIM, act, dev)
+    ranks = [PeerExpertParallelMoE(module, buffers=bufs[r], place=place, rank=r) for r in range(world)]
+    with torch.inference_mode():
+        for step in range(2):           # the second step re-uses every buffer and flag
+            counts = []
+            for x in xs:
+                _, _, bc, _, _ = M.gate_topk(x, module.gate.weight)
+                counts.append(M.route_plan(bc, x.shape[0], E)[1])
+            counts_all = torch.stack(counts).contiguous()
+            for r in range(world):
+                ranks[r].phase_route(xs[r], counts_all=counts_all)
+            for r in range(world):
+                ranks[r].phase_experts()
+            outs = [ranks[r].phase_combine() for r in range(world)]
+            for r in range(world):
+                ranks[r].check()
+                single = module(xs[r].view(1, -1, DIM)).view(-1, DIM)
+                if place.hidden_splits == 1:
+                    assert torch.equal(outs[r], single), f"step {step} rank {r}"
+                else:
+                    torch.testing.assert_close(outs[r].float(), single.float(), rtol=2e-2, atol=2e-2)
+    assert counts_all.sum(dim=1).tolist() == [2 * t for t in tokens]
+
+
+def test_receive_buffer_too_small_is_reported(cuda_device):
+    """Rows that do not fit the receive buffers are not written; the status word says so."""
+    from comfyui_b200 import _native as N, moe_ops as M
+    from comfyui_b200.expert_parallel import PeerBuffers, PeerExpertParallelMoE, Placement
+
+    dev = cuda_device
+    module = _module(dev)
+    place = Placement(2, E)
+    xs = [O.make_input(256, DIM, seed=7 + r).bfloat16().to(dev) for r in range(2)]
+    bufs = PeerBuffers.emulate(place, 128, DIM, torch.bfloat16, dev)       # 1024 routed rows will not fit
+    ranks = [PeerExpertParallelMoE(module, buffers=bufs[r], place=place, rank=r) for r in range(2)]
+    with torch.inference_mode():
+        counts = [M.route_plan(M.gate_topk(x, module.gate.weight)[2], 256, E)[1] for x in xs]
+        counts_all = torch.stack(counts).contiguous()
+        for r in range(2):
+            ranks[r].phase_route(xs[r], counts_all=counts_all)
+        for r in range(2):
+            ranks[r].phase_experts()
+        for r in range(2):
+            ranks[r].phase_combine()
+        with pytest.raises(N.MoeError) as err:
+            ranks[0].check()
+        assert err.value.code == N.ETOOLARGE
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, tokens, fp8, out_dir):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        from comfyui_b200.expert_parallel import PeerExpertParallelMoE
+
+        module = _module(dev, fp8)
+        n = tokens[rank]
+        x = O.make_input(n, DIM, seed=100 + rank).bfloat16().to(dev).view(1, n, DIM)
+        ep = PeerExpertParallelMoE(module, max_tokens=max(tokens))
+        with torch.inference_mode():
+            outs = [ep(x) for _ in range(3)]
+            ep.check()
+            single = module(x)
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.save({"outs": [o.cpu() for o in outs], "single": single.cpu(), "counts": ep.last_counts_host},
+                   os.path.join(out_dir, f"rank{rank}.pt"))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,fp8", [(2, False), (2, True), (4, False), (8, False)])
+def test_peer_expert_parallel_on_gpus(tmp_path, cuda_device, world, fp8):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    tokens = [1000, 700, 333, 1, 512, 129, 64, 2048][:world]
+    mp.spawn(_worker, args=(world, _free_port(), tokens, fp8, str(tmp_path)), nprocs=world, join=True)
+    for rank in range(world):
+        r = torch.load(tmp_path / f"rank{rank}.pt")
+        for o in r["outs"][1:]:
+            assert torch.equal(o, r["outs"][0])
+        if world <= E:
+            assert torch.equal(r["outs"][0], r["single"]), f"rank {rank}"
+        else:
+            torch.testing.assert_close(r["outs"][0].float(), r["single"].float(), rtol=2e-2, atol=2e-2)
+        assert [sum(c) for c in r["counts"]] == [2 * t for t in tokens]
