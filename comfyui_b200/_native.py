@@ -11,7 +11,7 @@ from ctypes import POINTER, Structure, c_char_p, c_float, c_int, c_int32, c_int6
 
 from . import build as _build
 
-ABI_VERSION = 4
+ABI_VERSION = 5
 
 OK, EINVAL, EUNSUPPORTED, ECUDA, ETIMEOUT, EDEVICE, ETOOLARGE = range(7)
 BF16, FP32, FP8_E4M3 = 0, 1, 2
@@ -34,6 +34,7 @@ EXPORTS = (
     "comfy_moe_route_static",
     "comfy_moe_grouped_swiglu",
     "comfy_moe_grouped_gelu_mlp",
+    "comfy_moe_grouped_swiglu_scatter",
     "comfy_moe_combine",
     "comfy_moe_combine_partials",
     "comfy_moe_forward",
@@ -229,7 +230,11 @@ def load(build_if_missing: bool = False) -> ctypes.CDLL:
     lib.comfy_moe_read_status.argtypes = [c_void_p, c_void_p, POINTER(c_int32)]
     lib.comfy_moe_ep_dispatch.argtypes = [
         POINTER(PeerPlan), c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
-        c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+        c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+    ]
+    lib.comfy_moe_grouped_swiglu_scatter.argtypes = [
+        c_int, c_int, POINTER(FfnWeights), c_void_p, c_void_p, c_int64, c_int, c_void_p, c_void_p, POINTER(c_void_p),
+        c_void_p, c_int64, c_void_p, c_void_p,
     ]
     lib.comfy_moe_ep_signal.argtypes = [POINTER(PeerPlan), c_int, c_uint32, c_void_p]
     lib.comfy_moe_ep_wait.argtypes = [POINTER(PeerPlan), c_int, c_uint32, c_void_p, c_void_p]

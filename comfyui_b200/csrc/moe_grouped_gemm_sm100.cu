@@ -94,6 +94,8 @@ struct alignas(64) GemmParams {
   int32_t* status;
   int num_groups;
   int m_fastest;      // plain passes: 1 = row tiles fastest (short K, wide N), 0 = column tiles fastest
+  const int32_t* out_shift;   // optional, device, per routed group: output row = input row + out_shift[i] (results that
+                              // are written straight into another buffer's layout, e.g. a peer's return buffer)
 };
 
 // The SwiGLU epilogue works on pairs of neighbouring columns held as bf16x2, so that every rounding the reference
@@ -131,6 +133,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
   __shared__ int s_m_tiles[kMaxGroups];
   __shared__ int s_row_base[kMaxGroups];
   __shared__ int s_row_limit[kMaxGroups];
+  __shared__ int s_out_shift[kMaxGroups];
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
@@ -166,6 +169,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
       s_m_tiles[g] = m_tiles;
       s_row_base[g] = base;
       s_row_limit[g] = limit;
+      s_out_shift[g] = (p.out_shift && grp.routed_index >= 0) ? p.out_shift[grp.routed_index] : 0;
       start += m_tiles * grp.n_tiles;
     }
     s_tile_start[p.num_groups] = start;
@@ -381,11 +385,12 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
       }
       tc_fence_after_sync();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + as * kBlockN;
-      const int row0 = s_row_base[g] + m_tile * kTileM + static_cast<int>(cta_rank) * kBlockM;
+      const int row_in0 = s_row_base[g] + m_tile * kTileM + static_cast<int>(cta_rank) * kBlockM;
+      const bool valid = (row_in0 + r_in_tile < s_row_limit[g]);
+      const int row0 = row_in0 + s_out_shift[g];     // where the tile's first row goes in the output
       const int row = row0 + r_in_tile;
-      const bool valid = (row < s_row_limit[g]);
       // whole tile inside the group (or clipped by the tensor's own bounds, for the un-permuted group)
-      const bool tile_tma = (grp.routed_index < 0 || row0 + kBlockM <= s_row_limit[g]);
+      const bool tile_tma = (grp.routed_index < 0 || row_in0 + kBlockM <= s_row_limit[g]);
       const CUtensorMap* map_out = &p.maps[grp.out_map];
 
       float alpha0 = 1.f, alpha1 = 1.f, out_inv = 1.f;
@@ -683,12 +688,18 @@ static int launch_gemm(const GemmParams& params, int64_t tiles_single, int64_t t
 
 using namespace comfy_b200;
 
-extern "C" int comfy_moe_grouped_swiglu(int w_dtype, int n_experts, const ComfyMoeFfnWeights* h_experts,
-                                        const ComfyMoeFfnWeights* h_shared, const int32_t* row_start,
-                                        const int32_t* row_count, int64_t rows_cap, int n_tokens, int dim, const void* x_perm, void* h_perm,
-                                        void* y_perm, const void* x_shared, void* h_shared_ws, void* y_shared,
-                                        int32_t* status, void* stream) {
+// Both passes for n_experts routed groups and the optional un-permuted group.  With `y_out` (one base pointer per
+// routed group, any of them possibly another GPU's memory) the second pass writes group i's rows to
+// y_out[i] at row (input row + y_row_shift[i]) instead of into y_perm.
+static int grouped_swiglu_impl(int w_dtype, int n_experts, const ComfyMoeFfnWeights* h_experts,
+                               const ComfyMoeFfnWeights* h_shared, const int32_t* row_start,
+                               const int32_t* row_count, int64_t rows_cap, int n_tokens, int dim, const void* x_perm,
+                               void* h_perm, void* y_perm, const void* x_shared, void* h_shared_ws, void* y_shared,
+                               int32_t* status, void* stream, void* const* y_out, const int32_t* y_row_shift,
+                               int64_t y_rows_cap) {
   if (n_experts < 0 || n_experts > kMaxExperts || dim <= 0 || n_tokens < 0 || rows_cap < 0) return COMFY_MOE_EINVAL;
+  if (y_out && (!y_row_shift || y_rows_cap <= 0)) return COMFY_MOE_EINVAL;
+  if (y_out && !y_perm) y_perm = y_out[0];     // only its non-nullness is checked below
   if (w_dtype != COMFY_MOE_BF16 && w_dtype != COMFY_MOE_FP8_E4M3) return COMFY_MOE_EUNSUPPORTED;
   if (!status) return COMFY_MOE_EINVAL;
   if (n_experts > 0 && (!h_experts || !row_start || !row_count || !x_perm || !h_perm || !y_perm || rows_cap <= 0))
@@ -726,8 +737,10 @@ extern "C" int comfy_moe_grouped_swiglu(int w_dtype, int n_experts, const ComfyM
     const int a1 = n_maps1++, a2 = n_maps2++;
     // outputs: pass 1 stores h through the same map pass 2 reads it with; pass 2 stores y_perm
     if ((rc = make_map(&p1.maps[n_maps1], h_perm, fp8, rows_cap, hidden_routed, hidden_routed)) != COMFY_MOE_OK) return rc;
-    if ((rc = make_map(&p2.maps[n_maps2], y_perm, false, rows_cap, dim, dim)) != COMFY_MOE_OK) return rc;
+    if ((rc = make_map(&p2.maps[n_maps2], y_perm, false, y_out ? y_rows_cap : rows_cap, dim, dim)) != COMFY_MOE_OK)
+      return rc;
     const int o1 = n_maps1++, o2 = n_maps2++;
+    if (y_out) p2.out_shift = y_row_shift;
     // every group may end in a partial tile
     const int64_t m_tiles_cap[2] = {(rows_cap + kBlockM - 1) / kBlockM + n_experts,
                                     (rows_cap + 2 * kBlockM - 1) / (2 * kBlockM) + n_experts};
@@ -748,6 +761,12 @@ extern "C" int comfy_moe_grouped_swiglu(int w_dtype, int n_experts, const ComfyM
       g2.out = y_perm; g2.ld_out = dim;
       g2.scale_a = w.scale_in2; g2.scale_b0 = w.scale_w2; g2.scale_b1 = w.scale_w2; g2.out_scale = nullptr;
       n_maps1 += 2; n_maps2 += 1;
+      if (y_out) {
+        if (!y_out[e]) return COMFY_MOE_EINVAL;
+        if ((rc = make_map(&p2.maps[n_maps2], y_out[e], false, y_rows_cap, dim, dim)) != COMFY_MOE_OK) return rc;
+        g2.out = y_out[e];
+        g2.out_map = n_maps2++;
+      }
     }
     for (int v = 0; v < 2; ++v) {
       tiles1[v] += m_tiles_cap[v] * (hidden_routed / 128);
@@ -792,6 +811,26 @@ extern "C" int comfy_moe_grouped_swiglu(int w_dtype, int n_experts, const ComfyM
   }
   if ((rc = launch_gemm<false, true>(p1, tiles1[0], tiles1[1], sms, s)) != COMFY_MOE_OK) return rc;
   return launch_gemm<false, false>(p2, tiles2[0], tiles2[1], sms, s);
+}
+
+extern "C" int comfy_moe_grouped_swiglu(int w_dtype, int n_experts, const ComfyMoeFfnWeights* h_experts,
+                                        const ComfyMoeFfnWeights* h_shared, const int32_t* row_start,
+                                        const int32_t* row_count, int64_t rows_cap, int n_tokens, int dim,
+                                        const void* x_perm, void* h_perm, void* y_perm, const void* x_shared,
+                                        void* h_shared_ws, void* y_shared, int32_t* status, void* stream) {
+  return grouped_swiglu_impl(w_dtype, n_experts, h_experts, h_shared, row_start, row_count, rows_cap, n_tokens, dim,
+                             x_perm, h_perm, y_perm, x_shared, h_shared_ws, y_shared, status, stream, nullptr, nullptr, 0);
+}
+
+extern "C" int comfy_moe_grouped_swiglu_scatter(int w_dtype, int n_groups, const ComfyMoeFfnWeights* h_groups,
+                                                const int32_t* row_start, const int32_t* row_count, int64_t rows_cap,
+                                                int dim, const void* x_perm, void* h_perm, void* const* h_y_out,
+                                                const int32_t* y_row_shift, int64_t y_rows_cap, int32_t* status,
+                                                void* stream) {
+  if (!h_y_out || n_groups <= 0) return COMFY_MOE_EINVAL;
+  return grouped_swiglu_impl(w_dtype, n_groups, h_groups, nullptr, row_start, row_count, rows_cap, 0, dim, x_perm,
+                             h_perm, nullptr, nullptr, nullptr, nullptr, status, stream, h_y_out, y_row_shift,
+                             y_rows_cap);
 }
 
 // GELU-MLP experts (Linear + bias, exact GELU, Linear + bias): the feed-forward of the Hunyuan3D-2.1 MoE block

@@ -56,9 +56,10 @@ dispatch_kernel(const __grid_constant__ PeerParams p, const __nv_bfloat16* __res
                 const int32_t* __restrict__ counts_all, int n_tokens, int dim, long long cap_rows,
                 const float* __restrict__ act_scale, void* __restrict__ x_q, const float* __restrict__ x_q_scale,
                 int32_t* __restrict__ row_map, int32_t* __restrict__ group_start, int32_t* __restrict__ group_count,
-                int32_t* __restrict__ status) {
+                int32_t* __restrict__ y_row_shift, int32_t* __restrict__ status) {
   constexpr int kSlots = kTokensPerBlock * 2;
   __shared__ int s_base[kMaxExperts];           // row of this rank's first slot of expert e at the expert's owner(s)
+  __shared__ int s_local[kMaxExperts];          // the same slot's row in this rank's own (compact, expert-major) order
   __shared__ int warp_cnt[kSlots / 32][kMaxExperts];
   __shared__ uint8_t* s_dst[kSlots][2];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -74,14 +75,34 @@ dispatch_kernel(const __grid_constant__ PeerParams p, const __nv_bfloat16* __res
     for (int s = 0; s < p.world; ++s) total += counts_all[s * p.n_experts + e];
     const int end_of_group = recv_row_base(p, counts_all, q, e, 0) + total;
     if (end_of_group > cap_rows) { base = -1; atomicCAS(status, 0, kStatusPeerCapacity); }
-    s_base[e] = (base < 0 || n_tokens == 0) ? -1 : base + block_offsets[blockIdx.x * p.n_experts + e];
+    const int in_block = n_tokens == 0 ? 0 : block_offsets[blockIdx.x * p.n_experts + e];
+    s_base[e] = (base < 0 || n_tokens == 0) ? -1 : base + in_block;
+    int local = 0;
+    for (int f = 0; f < e; ++f) local += counts_all[p.rank * p.n_experts + f];
+    s_local[e] = local + in_block;
     if (blockIdx.x == 0) {
-      // this rank's own work list: one row range per local expert, all sources together
+      // this rank's own work list
       int j = 0;
       for (int f = 0; f < e; ++f) j += (p.owner[f][0] == p.rank || p.owner[f][1] == p.rank) ? 1 : 0;
       if (p.owner[e][0] == p.rank || p.owner[e][1] == p.rank) {
-        group_start[j] = recv_row_base(p, counts_all, p.rank, e, 0);
-        group_count[j] = end_of_group > cap_rows ? 0 : total;
+        const bool fits = end_of_group <= cap_rows;
+        if (y_row_shift == nullptr) {
+          // one row range per local expert, all sources together; results stay in this rank's result buffer
+          group_start[j] = recv_row_base(p, counts_all, p.rank, e, 0);
+          group_count[j] = fits ? total : 0;
+        } else {
+          // one row range per (local expert, source): the results of source s go straight into s's return buffer,
+          // at the rows s's own expert-major order gives them
+          for (int src = 0; src < p.world; ++src) {
+            const int g = j * p.world + src;
+            const int start = recv_row_base(p, counts_all, p.rank, e, src);
+            int src_local = 0;
+            for (int f = 0; f < e; ++f) src_local += counts_all[src * p.n_experts + f];
+            group_start[g] = start;
+            group_count[g] = fits ? counts_all[src * p.n_experts + e] : 0;
+            y_row_shift[g] = src_local - start;
+          }
+        }
       }
     }
   }
@@ -105,7 +126,12 @@ dispatch_kernel(const __grid_constant__ PeerParams p, const __nv_bfloat16* __res
       for (int w = 0; w < warp; ++w) before += warp_cnt[w][my_e];
       d = s_base[my_e] + before;
     }
-    if (block_tok0 * 2 + tid < n_tokens * 2) row_map[block_tok0 * 2 + tid] = d;
+    if (block_tok0 * 2 + tid < n_tokens * 2) {
+      // pull mode: the row at the owner; push mode: the row of this rank's return buffer the owner writes
+      int m = d;
+      if (y_row_shift != nullptr && d >= 0) m = s_local[my_e] + (d - s_base[my_e]);
+      row_map[block_tok0 * 2 + tid] = m;
+    }
     for (int o = 0; o < 2; ++o) {
       const int q = (d >= 0) ? p.owner[my_e][o] : -1;
       s_dst[tid][o] = q >= 0 ? p.recv[q] + static_cast<size_t>(d) * row_bytes : nullptr;
@@ -303,8 +329,8 @@ using namespace comfy_b200;
 extern "C" int comfy_moe_ep_dispatch(const ComfyMoePeerPlan* plan, const void* x, const int32_t* topk_idx,
                                      const int32_t* block_offsets, const int32_t* counts_all, int n_tokens, int dim,
                                      int act_dtype, const float* act_scale, void* x_q, const float* x_q_scale,
-                                     int32_t* row_map, int32_t* group_start, int32_t* group_count, int32_t* status,
-                                     void* stream) {
+                                     int32_t* row_map, int32_t* group_start, int32_t* group_count,
+                                     int32_t* y_row_shift, int32_t* status, void* stream) {
   PeerParams p;
   int rc = fill_params(plan, &p);
   if (rc != COMFY_MOE_OK) return rc;
@@ -323,11 +349,11 @@ extern "C" int comfy_moe_ep_dispatch(const ComfyMoePeerPlan* plan, const void* x
   if (fp8)
     dispatch_kernel<true><<<n_blocks, threads, 0, s>>>(p, xp, topk_idx, block_offsets, counts_all, n_tokens, dim,
                                                        plan->cap_rows, act_scale, x_q, x_q_scale, row_map, group_start,
-                                                       group_count, status);
+                                                       group_count, y_row_shift, status);
   else
     dispatch_kernel<false><<<n_blocks, threads, 0, s>>>(p, xp, topk_idx, block_offsets, counts_all, n_tokens, dim,
                                                         plan->cap_rows, nullptr, nullptr, nullptr, row_map, group_start,
-                                                        group_count, status);
+                                                        group_count, y_row_shift, status);
   return check_launch();
 }
 

@@ -286,28 +286,34 @@ def _align(v: int, a: int = 256) -> int:
 
 
 class PeerBuffers:
-    """One rank's receive buffer, result buffer and flag block, plus every peer's as mapped in this process.
+    """One rank's receive buffer, result buffer, return buffers and flag block, plus every peer's as mapped in this
+    process.
 
     ``create`` allocates them in symmetric memory (``torch.distributed._symmetric_memory``: one allocation per rank,
     exchanged and mapped at a rendezvous, done once per shape).  ``emulate`` builds the same structure for several
-    ranks living on ONE device, which is how the addressing logic is tested without a second GPU."""
+    ranks living on ONE device, which is how the addressing logic is tested without a second GPU.
+
+    recv [cap_rows, dim]           rows other ranks routed to this rank's experts (activation dtype)
+    y    [cap_rows, dim] bf16      this rank's expert outputs, read by the peers (pull variant of the return path)
+    ret  [splits, ret_rows, dim]   expert outputs for this rank's own slots, written by the owners (push variant)"""
 
     FLAG_BYTES = 256
 
-    def __init__(self, place: Placement, rank: int, cap_rows: int, dim: int, act_dtype: torch.dtype, bases: List[int],
-                 mine: torch.Tensor, keep=None):
+    def __init__(self, place: Placement, rank: int, cap_rows: int, ret_rows: int, dim: int, act_dtype: torch.dtype,
+                 bases: List[int], mine: torch.Tensor, keep=None):
         from . import _native as N
 
-        self.place, self.rank, self.cap_rows, self.dim, self.act_dtype = place, rank, cap_rows, dim, act_dtype
+        self.place, self.rank, self.cap_rows, self.ret_rows = place, rank, cap_rows, ret_rows
+        self.dim, self.act_dtype = dim, act_dtype
+        off_recv, off_y, off_ret, total = self.layout(cap_rows, ret_rows, dim, act_dtype, place.hidden_splits)
         es = 1 if act_dtype == torch.float8_e4m3fn else 2
-        off_recv = self.FLAG_BYTES
-        off_y = off_recv + _align(cap_rows * dim * es)
-        self.nbytes = off_y + _align(cap_rows * dim * 2)
         self._keep = (mine, keep)
         raw = mine.view(torch.uint8)
         self.flags = raw[: self.FLAG_BYTES].view(torch.int32)
         self.recv = raw[off_recv: off_recv + cap_rows * dim * es].view(act_dtype).view(cap_rows, dim)
         self.y = raw[off_y: off_y + cap_rows * dim * 2].view(torch.bfloat16).view(cap_rows, dim)
+        ret_bytes = place.hidden_splits * ret_rows * dim * 2
+        self.ret = raw[off_ret: off_ret + ret_bytes].view(torch.bfloat16).view(place.hidden_splits, ret_rows, dim)
         plan = N.PeerPlan()
         plan.world, plan.rank, plan.n_experts, plan.hidden_splits = place.world, rank, place.n_experts, place.hidden_splits
         for e in range(place.n_experts):
@@ -320,33 +326,44 @@ class PeerBuffers:
             plan.peer_recv[r] = base + off_recv
             plan.peer_y[r] = base + off_y
         self.plan = plan
-
-    @staticmethod
-    def size(cap_rows: int, dim: int, act_dtype: torch.dtype) -> int:
-        es = 1 if act_dtype == torch.float8_e4m3fn else 2
-        return PeerBuffers.FLAG_BYTES + _align(cap_rows * dim * es) + _align(cap_rows * dim * 2)
+        # where this rank's partial results go at every rank: that rank's return buffer of this rank's hidden part
+        part_bytes = ret_rows * dim * 2
+        self.peer_ret = [base + off_ret + place.hidden_part(rank) * part_bytes for base in bases]
 
     @classmethod
-    def create(cls, place: Placement, rank: int, cap_rows: int, dim: int, act_dtype: torch.dtype, device, group):
+    def layout(cls, cap_rows: int, ret_rows: int, dim: int, act_dtype: torch.dtype, splits: int):
+        es = 1 if act_dtype == torch.float8_e4m3fn else 2
+        off_recv = cls.FLAG_BYTES
+        off_y = off_recv + _align(cap_rows * dim * es)
+        off_ret = off_y + _align(cap_rows * dim * 2)
+        return off_recv, off_y, off_ret, off_ret + _align(splits * ret_rows * dim * 2)
+
+    @classmethod
+    def create(cls, place: Placement, rank: int, cap_rows: int, ret_rows: int, dim: int, act_dtype: torch.dtype,
+               device, group):
         import os
 
         # plain peer mappings are all the kernels need; no NVLink multicast object is bound to the buffers
         os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         import torch.distributed._symmetric_memory as symm_mem
 
-        buf = symm_mem.empty(cls.size(cap_rows, dim, act_dtype), dtype=torch.uint8, device=device)
+        total = cls.layout(cap_rows, ret_rows, dim, act_dtype, place.hidden_splits)[3]
+        buf = symm_mem.empty(total, dtype=torch.uint8, device=device)
         handle = symm_mem.rendezvous(buf, group)
         buf[: cls.FLAG_BYTES].zero_()
         torch.cuda.synchronize(device)
         dist.barrier(group=group)           # every rank's flags are zero before anyone raises one
-        return cls(place, rank, cap_rows, dim, act_dtype, [int(p) for p in handle.buffer_ptrs], buf, keep=handle)
+        return cls(place, rank, cap_rows, ret_rows, dim, act_dtype, [int(p) for p in handle.buffer_ptrs], buf,
+                   keep=handle)
 
     @classmethod
-    def emulate(cls, place: Placement, cap_rows: int, dim: int, act_dtype: torch.dtype, device) -> List["PeerBuffers"]:
-        bufs = [torch.zeros(cls.size(cap_rows, dim, act_dtype), dtype=torch.uint8, device=device)
-                for _ in range(place.world)]
+    def emulate(cls, place: Placement, cap_rows: int, ret_rows: int, dim: int, act_dtype: torch.dtype,
+                device) -> List["PeerBuffers"]:
+        total = cls.layout(cap_rows, ret_rows, dim, act_dtype, place.hidden_splits)[3]
+        bufs = [torch.zeros(total, dtype=torch.uint8, device=device) for _ in range(place.world)]
         bases = [b.data_ptr() for b in bufs]
-        return [cls(place, r, cap_rows, dim, act_dtype, bases, bufs[r], keep=bufs) for r in range(place.world)]
+        return [cls(place, r, cap_rows, ret_rows, dim, act_dtype, bases, bufs[r], keep=bufs)
+                for r in range(place.world)]
 
 
 class PeerExpertParallelMoE:
@@ -359,8 +376,16 @@ class PeerExpertParallelMoE:
     live on one GPU in lock step."""
 
     def __init__(self, module, group=None, *, max_tokens: Optional[int] = None, buffers: Optional[PeerBuffers] = None,
-                 place: Optional[Placement] = None, rank: Optional[int] = None):
+                 place: Optional[Placement] = None, rank: Optional[int] = None, push_results: Optional[bool] = None):
+        import os
+
         from . import _native as N, moe_ops
+
+        if push_results is None:
+            push_results = os.environ.get("COMFY_B200_EP_RETURN", "push") != "pull"
+        # push: the expert GEMM writes every result row into the return buffer of the rank that owns the token
+        # while it computes; pull: results stay with the expert's rank and the combine kernel fetches them
+        self.push = push_results
 
         self.N, self.M = N, moe_ops
         self.lib = N.load()
@@ -389,7 +414,7 @@ class PeerExpertParallelMoE:
         # a token sends at most one slot to a given expert: world * tokens rows per local expert at most
         cap_rows = self.world * cap_tokens * min(2, self.place.experts_per_rank)
         act = torch.float8_e4m3fn if self.fp8 else torch.bfloat16
-        self.buffers = PeerBuffers.create(self.place, self.rank, cap_rows, dim, act, device, self.group)
+        self.buffers = PeerBuffers.create(self.place, self.rank, cap_rows, 2 * cap_tokens, dim, act, device, self.group)
 
     # -- the three phases of a step ---------------------------------------------------------------
     def phase_route(self, x2: torch.Tensor, counts_all: Optional[torch.Tensor] = None, gather=None):
@@ -409,7 +434,10 @@ class PeerExpertParallelMoE:
             counts_all = torch.empty((self.world, self.n_experts), dtype=torch.int32, device=dev)
             dist.all_gather_into_tensor(counts_all.view(-1), counts.contiguous(), group=self.group)
         row_map = torch.empty((n, 2), dtype=torch.int32, device=dev)
-        groups = torch.zeros((2, max(self.place.experts_per_rank, 1)), dtype=torch.int32, device=dev)
+        if 2 * n > b.ret_rows:
+            raise ValueError(f"{n} tokens do not fit the return buffers ({b.ret_rows} rows); pass max_tokens")
+        n_groups = self.place.experts_per_rank * (self.world if self.push else 1)
+        groups = torch.zeros((3, n_groups), dtype=torch.int32, device=dev)      # start, count, output row shift
         status = torch.zeros((2,), dtype=torch.int32, device=dev)
         x_q = torch.empty((n, dim), dtype=torch.float8_e4m3fn, device=dev) if self.fp8 else None
         in13 = k.local[0].scale_in13 if self.fp8 else None
@@ -417,7 +445,8 @@ class PeerExpertParallelMoE:
         P, S = M._ptr, M._stream
         N.check("comfy_moe_ep_dispatch", self.lib.comfy_moe_ep_dispatch(
             b.plan, P(x2), P(idx), P(block_offsets), P(counts_all), n, dim, N.FP8_E4M3 if self.fp8 else N.BF16, P(in13),
-            P(x_q), P(in13_shared), P(row_map), P(groups[0]), P(groups[1]), P(status), S()))
+            P(x_q), P(in13_shared), P(row_map), P(groups[0]), P(groups[1]), P(groups[2]) if self.push else None,
+            P(status), S()))
         N.check("comfy_moe_ep_signal", self.lib.comfy_moe_ep_signal(b.plan, N.EP_ARRIVED, self.epoch, S()))
         self._state = dict(x2=x2, x_q=x_q, idx=idx, w=w, row_map=row_map, groups=groups, status=status,
                            counts_all=counts_all)
@@ -433,8 +462,13 @@ class PeerExpertParallelMoE:
         if h_ws is None or h_ws.shape != (b.cap_rows, hidden) or h_ws.device != b.recv.device:
             h_ws = torch.empty((b.cap_rows, hidden), dtype=b.act_dtype, device=b.recv.device)
             self._h_ws = h_ws
-        M.grouped_swiglu(k.local, None, st["groups"][0], st["groups"][1], b.recv, None, status=st["status"],
-                         check_status=False, h_perm=h_ws, y_perm=b.y)
+        if self.push:
+            packs = [pack for pack in k.local for _ in range(self.world)]        # group (j, s) uses expert j's weights
+            M.grouped_swiglu_scatter(packs, st["groups"][0], st["groups"][1], b.recv, h_ws,
+                                     b.peer_ret * len(k.local), st["groups"][2], b.ret_rows, st["status"])
+        else:
+            M.grouped_swiglu(k.local, None, st["groups"][0], st["groups"][1], b.recv, None, status=st["status"],
+                             check_status=False, h_perm=h_ws, y_perm=b.y)
         N.check("comfy_moe_ep_signal", self.lib.comfy_moe_ep_signal(b.plan, N.EP_DONE, self.epoch, S()))
 
     def phase_combine(self) -> torch.Tensor:
@@ -443,9 +477,13 @@ class PeerExpertParallelMoE:
         P, S = M._ptr, M._stream
         n, dim = st["x2"].shape
         N.check("comfy_moe_ep_wait", self.lib.comfy_moe_ep_wait(b.plan, N.EP_DONE, self.epoch, P(st["status"]), S()))
-        out = torch.empty((n, dim), dtype=torch.bfloat16, device=st["x2"].device)
-        N.check("comfy_moe_ep_combine", self.lib.comfy_moe_ep_combine(
-            b.plan, P(st["idx"]), P(st["row_map"]), P(st["w"]), P(st["y_shared"]), n, dim, P(out), S()))
+        if self.push:
+            out = M.combine(b.ret[0], st["row_map"], st["w"], st["y_shared"],
+                            y_perm_b=b.ret[1] if self.place.hidden_splits == 2 else None)
+        else:
+            out = torch.empty((n, dim), dtype=torch.bfloat16, device=st["x2"].device)
+            N.check("comfy_moe_ep_combine", self.lib.comfy_moe_ep_combine(
+                b.plan, P(st["idx"]), P(st["row_map"]), P(st["w"]), P(st["y_shared"]), n, dim, P(out), S()))
         self.last_status = st["status"]
         self._last_counts_dev = st["counts_all"]
         return out

@@ -335,6 +335,25 @@ def grouped_swiglu(experts: Sequence[FfnPack], shared: Optional[FfnPack], row_st
     return y_perm, y_sh, h_perm, h_sh
 
 
+def grouped_swiglu_scatter(groups: Sequence[FfnPack], row_start: torch.Tensor, row_count: torch.Tensor,
+                           x_perm: torch.Tensor, h_perm: torch.Tensor, y_out_ptrs: Sequence[int],
+                           y_row_shift: torch.Tensor, y_rows_cap: int, status: torch.Tensor) -> None:
+    """Both passes of the grouped expert GEMM over routed groups, group i's results written to the buffer at address
+    ``y_out_ptrs[i]`` (bf16 [y_rows_cap, dim], possibly another GPU's memory) at row + y_row_shift[i]."""
+    n_g = len(groups)
+    if len(y_out_ptrs) != n_g:
+        raise ValueError("one output buffer per group")
+    fp8 = groups[0].w1.dtype == _FP8
+    arr = (N.FfnWeights * n_g)()
+    for i, e in enumerate(groups):
+        e.fill(arr[i])
+    outs = (ctypes.c_void_p * n_g)(*[int(p) for p in y_out_ptrs])
+    rc = N.load().comfy_moe_grouped_swiglu_scatter(
+        N.FP8_E4M3 if fp8 else N.BF16, n_g, arr, _ptr(row_start), _ptr(row_count), x_perm.shape[0], groups[0].dim,
+        _ptr(x_perm), _ptr(h_perm), outs, _ptr(y_row_shift), y_rows_cap, _ptr(status), _stream())
+    N.check("comfy_moe_grouped_swiglu_scatter", rc)
+
+
 def combine(y_perm: torch.Tensor, row_map: torch.Tensor, topk_weight: torch.Tensor,
             y_shared: Optional[torch.Tensor], out: Optional[torch.Tensor] = None,
             y_perm_b: Optional[torch.Tensor] = None) -> torch.Tensor:

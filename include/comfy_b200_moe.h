@@ -26,7 +26,7 @@
 extern "C" {
 #endif
 
-#define COMFY_MOE_ABI_VERSION 4
+#define COMFY_MOE_ABI_VERSION 5
 
 /* Return codes. */
 #define COMFY_MOE_OK 0
@@ -197,6 +197,15 @@ int comfy_moe_grouped_gelu_mlp(int n_groups, const ComfyMoeMlpWeights* h_groups,
                                int dim, const void* x_perm, void* h_perm, void* y_perm, const void* x_shared,
                                void* h_shared_ws, void* y_shared, int32_t* status, void* stream);
 
+/* comfy_moe_grouped_swiglu for routed groups only, with the second pass writing group i's results to
+ * y_out[i] + (row + y_row_shift[i]) * dim instead of one y_perm (y_out: HOST array of n_groups device pointers to
+ * bf16 [y_rows_cap, dim] buffers, which may be another GPU's memory mapped here; y_row_shift: DEVICE array).
+ * No counterpart in the reference; used by the expert-parallel path to return results while the GEMM runs. */
+int comfy_moe_grouped_swiglu_scatter(int w_dtype, int n_groups, const ComfyMoeFfnWeights* h_groups,
+                                     const int32_t* row_start, const int32_t* row_count, int64_t rows_cap, int dim,
+                                     const void* x_perm, void* h_perm, void* const* h_y_out,
+                                     const int32_t* y_row_shift, int64_t y_rows_cap, int32_t* status, void* stream);
+
 /* ---- weighted combine: replaces mul_ + scatter_reduce_ + shared add (model.py:341-345, 324) ---------------
  * out[t] = bf16( bf16( bf16(w0*y[r0]) + bf16(w1*y[r1]) ) + y_shared[t] ), weights rounded to bf16 first.
  * y_shared may be NULL (routed part only, what moe_infer returns).
@@ -285,6 +294,11 @@ int comfy_moe_forward_gelu_mlp(const ComfyMoeMlpLayer* h_layer, const ComfyMoeWo
  *                          owner; group_start / group_count [local experts] = this rank's own work list.
  *   comfy_moe_ep_combine   comfy_moe_combine with every routed row read from its owner's result buffer (two
  *                          partial rows summed, rounded to bf16, with a hidden split).
+ * Push variant of the return path (y_row_shift not NULL): the work list has one row range per (local expert, source
+ * rank), [local experts * world] entries, and y_row_shift[i] = (first row of that range in the source's own
+ * expert-major order) - (first row of the range here); comfy_moe_grouped_swiglu_scatter then writes the results of
+ * range i into the source rank's return buffer (y_out[i], that rank's memory) while it computes, row_map holds rows
+ * of the local return buffer, and the plain comfy_moe_combine / comfy_moe_combine_partials finish the step.
  */
 #define COMFY_MOE_MAX_RANKS 8
 #define COMFY_MOE_EP_ARRIVED 0
@@ -306,7 +320,8 @@ typedef struct ComfyMoePeerPlan {
 int comfy_moe_ep_dispatch(const ComfyMoePeerPlan* h_plan, const void* x, const int32_t* topk_idx,
                           const int32_t* block_offsets, const int32_t* counts_all, int n_tokens, int dim,
                           int act_dtype, const float* act_scale, void* x_q, const float* x_q_scale, int32_t* row_map,
-                          int32_t* group_start, int32_t* group_count, int32_t* status, void* stream);
+                          int32_t* group_start, int32_t* group_count, int32_t* y_row_shift, int32_t* status,
+                          void* stream);
 int comfy_moe_ep_signal(const ComfyMoePeerPlan* h_plan, int kind, uint32_t epoch, void* stream);
 int comfy_moe_ep_wait(const ComfyMoePeerPlan* h_plan, int kind, uint32_t epoch, int32_t* status, void* stream);
 int comfy_moe_ep_combine(const ComfyMoePeerPlan* h_plan, const int32_t* topk_idx, const int32_t* row_map,

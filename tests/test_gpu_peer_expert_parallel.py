@@ -38,8 +38,9 @@ def _module(dev, fp8=False, n_experts=E):
     return module
 
 
+@pytest.mark.parametrize("push", [True, False], ids=["push", "pull"])
 @pytest.mark.parametrize("world,fp8", [(2, False), (4, False), (8, False), (2, True), (8, True)])
-def test_emulated_ranks_on_one_gpu(cuda_device, world, fp8):
+def test_emulated_ranks_on_one_gpu(cuda_device, world, fp8, push):
     from comfyui_b200 import moe_ops as M
     from comfyui_b200.expert_parallel import PeerBuffers, PeerExpertParallelMoE, Placement
 
@@ -50,8 +51,9 @@ def test_emulated_ranks_on_one_gpu(cuda_device, world, fp8):
     xs = [O.make_input(n, DIM, seed=100 + r).bfloat16().to(dev) for r, n in enumerate(tokens)]
     cap_rows = sum(tokens) * min(2, place.experts_per_rank)
     act = torch.float8_e4m3fn if fp8 else torch.bfloat16
-    bufs = PeerBuffers.emulate(place, cap_rows, DIM, act, dev)
-    ranks = [PeerExpertParallelMoE(module, buffers=bufs[r], place=place, rank=r) for r in range(world)]
+    bufs = PeerBuffers.emulate(place, cap_rows, 2 * max(tokens), DIM, act, dev)
+    ranks = [PeerExpertParallelMoE(module, buffers=bufs[r], place=place, rank=r, push_results=push)
+             for r in range(world)]
     with torch.inference_mode():
         for step in range(2):           # the second step re-uses every buffer and flag
             counts = []
@@ -83,7 +85,7 @@ def test_receive_buffer_too_small_is_reported(cuda_device):
     module = _module(dev)
     place = Placement(2, E)
     xs = [O.make_input(256, DIM, seed=7 + r).bfloat16().to(dev) for r in range(2)]
-    bufs = PeerBuffers.emulate(place, 128, DIM, torch.bfloat16, dev)       # 1024 routed rows will not fit
+    bufs = PeerBuffers.emulate(place, 128, 512, DIM, torch.bfloat16, dev)  # 1024 routed rows will not fit
     ranks = [PeerExpertParallelMoE(module, buffers=bufs[r], place=place, rank=r) for r in range(2)]
     with torch.inference_mode():
         counts = [M.route_plan(M.gate_topk(x, module.gate.weight)[2], 256, E)[1] for x in xs]
@@ -105,7 +107,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, tokens, fp8, out_dir):
+def _worker(rank, world, port, tokens, fp8, push, out_dir):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
@@ -118,7 +120,7 @@ def _worker(rank, world, port, tokens, fp8, out_dir):
         module = _module(dev, fp8)
         n = tokens[rank]
         x = O.make_input(n, DIM, seed=100 + rank).bfloat16().to(dev).view(1, n, DIM)
-        ep = PeerExpertParallelMoE(module, max_tokens=max(tokens))
+        ep = PeerExpertParallelMoE(module, max_tokens=max(tokens), push_results=push)
         with torch.inference_mode():
             outs = [ep(x) for _ in range(3)]
             ep.check()
@@ -131,12 +133,13 @@ def _worker(rank, world, port, tokens, fp8, out_dir):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world,fp8", [(2, False), (2, True), (4, False), (8, False)])
-def test_peer_expert_parallel_on_gpus(tmp_path, cuda_device, world, fp8):
+@pytest.mark.parametrize("world,fp8,push", [(2, False, True), (2, False, False), (2, True, True), (4, False, True),
+                                            (8, False, True), (8, True, True)])
+def test_peer_expert_parallel_on_gpus(tmp_path, cuda_device, world, fp8, push):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     tokens = [1000, 700, 333, 1, 512, 129, 64, 2048][:world]
-    mp.spawn(_worker, args=(world, _free_port(), tokens, fp8, str(tmp_path)), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, _free_port(), tokens, fp8, push, str(tmp_path)), nprocs=world, join=True)
     for rank in range(world):
         r = torch.load(tmp_path / f"rank{rank}.pt")
         for o in r["outs"][1:]:
