@@ -61,7 +61,7 @@ class FfnWeights(Structure):
         ("ld13", c_int64),
         ("ld2", c_int64),
         ("hidden", c_int32),
-        ("reserved", c_int32),
+        ("max_sms", c_int32),
         ("scale_w1", c_void_p),
         ("scale_w3", c_void_p),
         ("scale_w2", c_void_p),

@@ -715,6 +715,10 @@ static int grouped_swiglu_impl(int w_dtype, int n_experts, const ComfyMoeFfnWeig
   int sms = 0;
   int rc = device_sm_count(&sms);
   if (rc != COMFY_MOE_OK) return rc;
+  {
+    const int limit = h_shared ? h_shared->max_sms : (n_experts > 0 && h_experts ? h_experts[0].max_sms : 0);
+    if (limit >= 2 && limit < sms) sms = limit & ~1;
+  }
 
   GemmParams p1, p2;
   memset(&p1, 0, sizeof(p1));

@@ -116,6 +116,7 @@ class CudaKernels:
                                                   scale_w2=full.scale_w2, scale_in13=full.scale_in13,
                                                   scale_in2=full.scale_in2))
         self.fp8 = self.shared.w1.dtype == torch.float8_e4m3fn
+        self._limited = {}
         if self.fp8 and not allow_fp8:
             raise ValueError("the NCCL transport covers bf16 weights; scaled fp8 runs on the peer-memory transport")
 
@@ -129,8 +130,16 @@ class CudaKernels:
         x_perm, row_map, _ = M.permute(x, idx, block_offsets, offsets, self.n_experts)
         return idx, w, counts, offsets, x_perm, row_map
 
-    def shared_expert(self, x):
-        _, y, _, _ = self.M.grouped_swiglu([], self.shared, None, None, None, x, check_status=False)
+    def shared_expert(self, x, max_sms: int = 0):
+        pack = self.shared
+        if max_sms > 0:
+            import dataclasses
+
+            pack = self._limited.get(max_sms)
+            if pack is None:
+                pack = dataclasses.replace(self.shared, max_sms=max_sms)
+                self._limited[max_sms] = pack
+        _, y, _, _ = self.M.grouped_swiglu([], pack, None, None, None, x, check_status=False)
         return y
 
     def routed_experts(self, rows, group_start, group_count):
@@ -386,6 +395,9 @@ class PeerExpertParallelMoE:
         # push: the expert GEMM writes every result row into the return buffer of the rank that owns the token
         # while it computes; pull: results stay with the expert's rank and the combine kernel fetches them
         self.push = push_results
+        # SMs kept free for the routing kernels while the shared expert runs beside them (0 = run them in turn)
+        self.front_sms = int(os.environ.get("COMFY_B200_EP_FRONT_SMS", "16"))
+        self._side = None
 
         self.N, self.M = N, moe_ops
         self.lib = N.load()
@@ -451,11 +463,12 @@ class PeerExpertParallelMoE:
         self._state = dict(x2=x2, x_q=x_q, idx=idx, w=w, row_map=row_map, groups=groups, status=status,
                            counts_all=counts_all)
 
-    def phase_experts(self):
-        """Shared expert on the local tokens, then (after every rank's rows arrived) the local routed experts."""
+    def phase_experts(self, y_shared: Optional[torch.Tensor] = None):
+        """Shared expert on the local tokens (unless the caller already ran it beside the routing kernels), then,
+        after every rank's rows arrived, the local routed experts."""
         M, N, k, b, st = self.M, self.N, self.kernels, self.buffers, self._state
         S = M._stream
-        st["y_shared"] = k.shared_expert(st["x_q"] if self.fp8 else st["x2"])
+        st["y_shared"] = y_shared if y_shared is not None else k.shared_expert(st["x_q"] if self.fp8 else st["x2"])
         N.check("comfy_moe_ep_wait", self.lib.comfy_moe_ep_wait(b.plan, N.EP_ARRIVED, self.epoch, M._ptr(st["status"]), S()))
         hidden = k.local[0].hidden
         h_ws = getattr(self, "_h_ws", None)
@@ -491,9 +504,29 @@ class PeerExpertParallelMoE:
     def __call__(self, x: torch.Tensor) -> torch.Tensor:
         shape = x.shape
         x2 = x.reshape(-1, shape[-1])
+        if self.front_sms <= 0 or self.fp8:
+            self.phase_route(x2)
+            self.phase_experts()
+            return self.phase_combine().view(shape)
+        # bf16: the shared expert needs only x, so it is launched first, on a side stream and on all but
+        # `front_sms` SMs; the gate, the histogram all-gather and the dispatch kernel (NVLink-bound) run beside it on
+        # the SMs left free, and the routed experts start when both are done.  (For fp8 the shared expert reads the
+        # quantised copy the dispatch kernel makes, so the order stays gate -> dispatch -> shared.)
+        main = torch.cuda.current_stream()
+        if self._side is None:
+            self._side = torch.cuda.Stream(device=x2.device)
+        side = self._side
+        side.wait_stream(main)
+        with torch.cuda.stream(side):
+            y_shared = self.kernels.shared_expert(x2, max_sms=self._sm_count(x2.device) - self.front_sms)
         self.phase_route(x2)
-        self.phase_experts()
+        main.wait_stream(side)
+        y_shared.record_stream(main)
+        self.phase_experts(y_shared)
         return self.phase_combine().view(shape)
+
+    def _sm_count(self, device) -> int:
+        return torch.cuda.get_device_properties(device).multi_processor_count
 
     @property
     def last_counts_host(self) -> List[List[int]]:

@@ -63,6 +63,7 @@ class FfnPack:
     scale_w2: Optional[torch.Tensor] = None
     scale_in13: Optional[torch.Tensor] = None
     scale_in2: Optional[torch.Tensor] = None
+    max_sms: int = 0        # 0 = all; see ComfyMoeFfnWeights.max_sms
 
     def __post_init__(self):
         _need_cuda(self.w1, self.w2, self.w3)
@@ -89,7 +90,7 @@ class FfnPack:
         s.w1, s.w3, s.w2 = self.w1.data_ptr(), self.w3.data_ptr(), self.w2.data_ptr()
         s.ld13, s.ld2 = self.w1.stride(0), self.w2.stride(0)
         s.hidden = self.hidden
-        s.reserved = 0
+        s.max_sms = self.max_sms
         for name in ("scale_w1", "scale_w3", "scale_w2", "scale_in13", "scale_in2"):
             t = getattr(self, name)
             setattr(s, name, None if t is None else t.data_ptr())

@@ -147,7 +147,9 @@ typedef struct ComfyMoeFfnWeights {
   int64_t ld13;
   int64_t ld2;
   int32_t hidden;         /* multiple of 128 */
-  int32_t reserved;
+  int32_t max_sms;        /* 0 = all SMs.  Read from the shared-expert struct (else from the first group) of a grouped
+                             call: its launches then occupy at most this many SMs, the rest stay free for kernels
+                             that run beside them on other streams */
   /* fp8 only (NULL = 1.0): per-tensor scales as comfy/ops.py:379-410 stores them */
   const float* scale_w1;
   const float* scale_w3;
