@@ -182,3 +182,33 @@ def test_rank_leaving_between_steps_is_detected(tmp_path):
         assert not p.is_alive(), "a rank hung after its peer left"
     assert torch.load(tmp_path / "rank1.pt")["left"]
     assert torch.load(tmp_path / "rank0.pt")["outcome"] != "completed"
+
+
+def test_peer_buffer_layout_and_plan():
+    """Host side of the peer-memory transport: buffer layout, owner tables and peer addresses (no GPU needed)."""
+    from comfyui_b200.expert_parallel import PeerBuffers, Placement
+
+    for world, splits in ((2, 1), (4, 1), (8, 2)):
+        place = Placement(world, 4)
+        cap, ret, dim = 384, 256, 512
+        off_recv, off_y, off_ret, total = PeerBuffers.layout(cap, ret, dim, torch.bfloat16, place.hidden_splits)
+        assert off_recv == 256 and off_y >= off_recv + cap * dim * 2 and off_ret >= off_y + cap * dim * 2
+        assert total >= off_ret + splits * ret * dim * 2 and all(o % 256 == 0 for o in (off_recv, off_y, off_ret))
+        bufs = [torch.zeros(total, dtype=torch.uint8) for _ in range(world)]
+        bases = [b.data_ptr() for b in bufs]
+        for rank in range(world):
+            pb = PeerBuffers(place, rank, cap, ret, dim, torch.bfloat16, bases, bufs[rank])
+            assert pb.recv.shape == (cap, dim) and pb.y.shape == (cap, dim) and pb.ret.shape == (splits, ret, dim)
+            assert pb.recv.data_ptr() == bases[rank] + off_recv and pb.ret.data_ptr() == bases[rank] + off_ret
+            plan = pb.plan
+            assert (plan.world, plan.rank, plan.n_experts, plan.hidden_splits, plan.cap_rows) == (world, rank, 4, splits, cap)
+            for e in range(4):
+                owners = place.owners(e)
+                assert plan.owner0[e] == owners[0] and plan.owner1[e] == (owners[1] if splits == 2 else -1)
+            assert [plan.peer_recv[r] for r in range(world)] == [b + off_recv for b in bases]
+            assert [plan.peer_flags[r] for r in range(world)] == bases
+            # this rank's results go into the return buffer of its own hidden part at every rank
+            part = place.hidden_part(rank)
+            assert pb.peer_ret == [b + off_ret + part * ret * dim * 2 for b in bases]
+        # fp8 activations halve the receive buffer only
+        assert PeerBuffers.layout(cap, ret, dim, torch.float8_e4m3fn, splits)[1] == off_recv + cap * dim
