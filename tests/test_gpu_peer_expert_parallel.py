@@ -76,6 +76,36 @@ def test_emulated_ranks_on_one_gpu(cuda_device, world, fp8, push):
     assert counts_all.sum(dim=1).tolist() == [2 * t for t in tokens]
 
 
+def test_rank_without_tokens(cuda_device):
+    """A rank that owns experts but has no tokens of its own still serves the others (and gets an empty output)."""
+    from comfyui_b200 import moe_ops as M
+    from comfyui_b200.expert_parallel import PeerBuffers, PeerExpertParallelMoE, Placement
+
+    dev = cuda_device
+    module = _module(dev)
+    place = Placement(2, E)
+    tokens = [0, 300]
+    xs = [O.make_input(n, DIM, seed=50 + r).bfloat16().to(dev) for r, n in enumerate(tokens)]
+    bufs = PeerBuffers.emulate(place, 1024, 1024, DIM, torch.bfloat16, dev)
+    ranks = [PeerExpertParallelMoE(module, buffers=bufs[r], place=place, rank=r) for r in range(2)]
+    with torch.inference_mode():
+        counts = []
+        for x in xs:
+            _, _, bc, _, _ = M.gate_topk(x, module.gate.weight)
+            counts.append(M.route_plan(bc, x.shape[0], E)[1])
+        counts_all = torch.stack(counts).contiguous()
+        assert counts_all[0].sum().item() == 0
+        for r in range(2):
+            ranks[r].phase_route(xs[r], counts_all=counts_all)
+        for r in range(2):
+            ranks[r].phase_experts()
+        outs = [ranks[r].phase_combine() for r in range(2)]
+        for r in range(2):
+            ranks[r].check()
+        assert outs[0].shape == (0, DIM)
+        assert torch.equal(outs[1], module(xs[1].view(1, -1, DIM)).view(-1, DIM))
+
+
 def test_receive_buffer_too_small_is_reported(cuda_device):
     """Rows that do not fit the receive buffers are not written; the status word says so."""
     from comfyui_b200 import _native as N, moe_ops as M
