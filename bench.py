@@ -250,7 +250,7 @@ def run_gpu_arm(args) -> None:
         if os.environ.get("COMFY_B200_EP_TRANSPORT", "peer") == "nccl":
             runner = ExpertParallelMoE(module, dist.group.WORLD)
         else:
-            runner = PeerExpertParallelMoE(module, dist.group.WORLD)
+            runner = PeerExpertParallelMoE(module, dist.group.WORLD, max_tokens=n)
         step = lambda inp: runner(inp)                      # noqa: E731
         launches_per_step = runner.launches_per_step
     else:

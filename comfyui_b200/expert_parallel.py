@@ -416,8 +416,9 @@ class PeerExpertParallelMoE:
         self.epoch = 0
         self.last_counts = None
         self._state = None
-        # gate, plan, dispatch, 2 flags, 2 waits, shared GEMM x2, routed GEMM x2, combine
-        self.launches_per_step = 12
+        # gate, plan, dispatch, 2 flags, 2 waits, shared GEMM x2, routed GEMM x2, combine (+ the shared expert's
+        # input quantiser for fp8 when it runs beside the routing kernels)
+        self.launches_per_step = 12 + (1 if (self.fp8 and self.front_sms > 0) else 0)
 
     def _ensure_buffers(self, n: int, dim: int, device):
         if self.buffers is not None:
@@ -429,7 +430,8 @@ class PeerExpertParallelMoE:
         self.buffers = PeerBuffers.create(self.place, self.rank, cap_rows, 2 * cap_tokens, dim, act, device, self.group)
 
     # -- the three phases of a step ---------------------------------------------------------------
-    def phase_route(self, x2: torch.Tensor, counts_all: Optional[torch.Tensor] = None, gather=None):
+    def phase_route(self, x2: torch.Tensor, counts_all: Optional[torch.Tensor] = None, gather=None,
+                    want_xq: bool = True):
         """Gate, plan, histogram exchange, dispatch, "arrived" flag.  ``gather(counts) -> [world, E]`` replaces the
         collective in single-GPU emulation."""
         M, N, k = self.M, self.N, self.kernels
@@ -451,7 +453,7 @@ class PeerExpertParallelMoE:
         n_groups = self.place.experts_per_rank * (self.world if self.push else 1)
         groups = torch.zeros((3, n_groups), dtype=torch.int32, device=dev)      # start, count, output row shift
         status = torch.zeros((2,), dtype=torch.int32, device=dev)
-        x_q = torch.empty((n, dim), dtype=torch.float8_e4m3fn, device=dev) if self.fp8 else None
+        x_q = torch.empty((n, dim), dtype=torch.float8_e4m3fn, device=dev) if (self.fp8 and want_xq) else None
         in13 = k.local[0].scale_in13 if self.fp8 else None
         in13_shared = k.shared.scale_in13 if self.fp8 else None
         P, S = M._ptr, M._stream
@@ -504,22 +506,23 @@ class PeerExpertParallelMoE:
     def __call__(self, x: torch.Tensor) -> torch.Tensor:
         shape = x.shape
         x2 = x.reshape(-1, shape[-1])
-        if self.front_sms <= 0 or self.fp8:
+        if self.front_sms <= 0:
             self.phase_route(x2)
             self.phase_experts()
             return self.phase_combine().view(shape)
-        # bf16: the shared expert needs only x, so it is launched first, on a side stream and on all but
-        # `front_sms` SMs; the gate, the histogram all-gather and the dispatch kernel (NVLink-bound) run beside it on
-        # the SMs left free, and the routed experts start when both are done.  (For fp8 the shared expert reads the
-        # quantised copy the dispatch kernel makes, so the order stays gate -> dispatch -> shared.)
+        # The shared expert needs only x, so it is launched first, on a side stream and on all but `front_sms` SMs;
+        # the gate, the histogram all-gather and the dispatch kernel (NVLink-bound) run beside it on the SMs left
+        # free, and the routed experts start when both are done.  For fp8 its input is quantised by a kernel of its
+        # own first (the dispatch kernel's quantised copy would come too late).
         main = torch.cuda.current_stream()
         if self._side is None:
             self._side = torch.cuda.Stream(device=x2.device)
         side = self._side
         side.wait_stream(main)
         with torch.cuda.stream(side):
-            y_shared = self.kernels.shared_expert(x2, max_sms=self._sm_count(x2.device) - self.front_sms)
-        self.phase_route(x2)
+            xs = self.M.quantize_e4m3(x2, self.kernels.shared.scale_in13) if self.fp8 else x2
+            y_shared = self.kernels.shared_expert(xs, max_sms=self._sm_count(x2.device) - self.front_sms)
+        self.phase_route(x2, want_xq=False)
         main.wait_stream(side)
         y_shared.record_stream(main)
         self.phase_experts(y_shared)

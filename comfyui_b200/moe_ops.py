@@ -376,6 +376,17 @@ def combine(y_perm: torch.Tensor, row_map: torch.Tensor, topk_weight: torch.Tens
     return out
 
 
+def quantize_e4m3(x: torch.Tensor, scale: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """bf16 -> e4m3 as the reference's fp8 Linear quantises its input (optional bf16(1/scale) multiply, clamp, RNE)."""
+    _need_cuda(x, scale)
+    if x.dtype != torch.bfloat16 or not x.is_contiguous():
+        raise ValueError("x must be a contiguous bf16 tensor")
+    if out is None:
+        out = torch.empty(x.shape, dtype=_FP8, device=x.device)
+    N.check("comfy_moe_quantize_e4m3", N.load().comfy_moe_quantize_e4m3(_ptr(x), _ptr(scale), x.numel(), _ptr(out), _stream()))
+    return out
+
+
 def read_status(status: torch.Tensor) -> None:
     """Synchronises the current stream and raises if a device-side wait gave up."""
     h = ctypes.c_int32(0)

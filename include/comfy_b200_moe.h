@@ -26,7 +26,7 @@
 extern "C" {
 #endif
 
-#define COMFY_MOE_ABI_VERSION 5
+#define COMFY_MOE_ABI_VERSION 6
 
 /* Return codes. */
 #define COMFY_MOE_OK 0
@@ -277,6 +277,13 @@ typedef struct ComfyMoeMlpLayer {
 
 int comfy_moe_forward_gelu_mlp(const ComfyMoeMlpLayer* h_layer, const ComfyMoeWorkspace* h_ws, const void* x,
                                int n_tokens, void* out, void* stream);
+
+/* ---- activation quantiser on its own (comfy/ops.py:338-343) --------------------------------------------------
+ * out = e4m3( clamp( scale ? bf16(x * bf16(1 / scale)) : x, +-448 ) ), round to nearest even; x bf16, n_elements a
+ * multiple of 16.  What comfy_moe_permute does on the way, for callers that need the quantised copy before the
+ * permutation runs (the expert-parallel path quantises the shared expert's input beside the routing kernels).
+ */
+int comfy_moe_quantize_e4m3(const void* x, const float* scale, int64_t n_elements, void* out, void* stream);
 
 /* ---- expert parallelism over peer memory (one process per GPU, NVLink peer access) ---------------------------
  * No counterpart in the reference (it runs on one GPU).  Tokens stay with their rank; expert e is computed by rank

@@ -245,3 +245,20 @@ def test_unscaled_fp8_ops_module(cuda_device):
     ref, _, _ = O.moe_layer(x, layer, mode=O.FP8_MATMUL, routing=(idx.cpu(), w.cpu()))
     rel = float((out.float() - ref.float()).norm() / ref.float().norm())
     assert rel < 1e-2, rel
+
+
+def test_quantize_e4m3_matches_reference_cast(cuda_device):
+    """The stand-alone activation quantiser: clamp + cast of comfy/ops.py:338-340, and the scale_input form of :342-343."""
+    from comfyui_b200 import moe_ops as M
+
+    g = torch.Generator().manual_seed(5)
+    x = (torch.randn((257, 512), generator=g) * 40).bfloat16()
+    x[0, :8] = torch.tensor([448., 449., 464., 1000., -1000., 2.0 ** -10, 0.001, -0.0]).bfloat16()
+    got = M.quantize_e4m3(x.to(cuda_device)).cpu()
+    want = torch.clamp(x, min=-448, max=448).to(torch.float8_e4m3fn)
+    assert torch.equal(got.view(torch.uint8), want.view(torch.uint8))
+    scale = torch.tensor(0.75, dtype=torch.float32)
+    got = M.quantize_e4m3(x.to(cuda_device), scale.to(cuda_device)).cpu()
+    inv = (1.0 / scale).to(torch.bfloat16)
+    want = torch.clamp(x * inv, min=-448, max=448).to(torch.float8_e4m3fn)      # the kernel saturates where the
+    assert torch.equal(got.view(torch.uint8), want.view(torch.uint8))           # reference's unclamped cast gives NaN
