@@ -293,6 +293,13 @@ def run_gpu_arm(args) -> None:
                 gpu_bar = time_stock_composition(module, x, ops)
 
 
+        if args.timeline and rank == 0:
+            print_timeline(step, x)
+        elif args.timeline:
+            for _ in range(3):          # the other ranks take the same three steps
+                step(x)
+            torch.cuda.synchronize()
+
     times = torch.tensor([ms_total, ms_e2e], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
@@ -475,6 +482,28 @@ def time_stages(module, x2, steps, moe_ops, ops):
     return res
 
 
+def print_timeline(step, x) -> None:
+    """Kernel timeline of one step on this rank (torch.profiler / CUPTI), printed to stderr: start offset, duration,
+    kernel name.  Three steps are profiled and the middle one is shown."""
+    from torch.profiler import ProfilerActivity, profile
+
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        for _ in range(3):
+            step(x)
+        torch.cuda.synchronize()
+    evs = [e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA]
+    evs.sort(key=lambda e: e.time_range.start)
+    gates = [i for i, e in enumerate(evs) if "gate_topk" in e.name]
+    if len(gates) < 3:
+        print("timeline: no gate kernels found", file=sys.stderr)
+        return
+    lo, hi = gates[1], gates[2]
+    t0 = evs[lo].time_range.start
+    print("timeline of one step (offset us, duration us, kernel):", file=sys.stderr)
+    for e in evs[lo:hi]:
+        print(f"{e.time_range.start - t0:9.1f} {e.time_range.elapsed_us():8.1f}  {e.name[:100]}", file=sys.stderr)
+
+
 def time_stock_composition(module, x, ops, steps: int = 10):
     """The same module with the sm_100a kernels switched off: forward() then runs the composition the reference
     ships (masked branch, one library GEMM per Linear, boolean-mask gathers, host syncs), and moe_infer the sorted
@@ -573,6 +602,8 @@ def main() -> None:
                          "(one GPU, bf16)")
     ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp8"],
                     help="bf16 (BASELINE config 2, the default) or per-tensor scaled fp8 e4m3 expert weights (config 3)")
+    ap.add_argument("--timeline", action="store_true",
+                    help="after the timing, print the kernel timeline of one step on rank 0 to stderr (torch.profiler)")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU oracle and the stock-composition timings (profiling runs)")
     args = ap.parse_args()
     if args.impl == "reference":
