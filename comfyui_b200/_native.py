@@ -11,7 +11,7 @@ from ctypes import POINTER, Structure, c_char_p, c_float, c_int, c_int32, c_int6
 
 from . import build as _build
 
-ABI_VERSION = 6
+ABI_VERSION = 7
 
 OK, EINVAL, EUNSUPPORTED, ECUDA, ETIMEOUT, EDEVICE, ETOOLARGE = range(7)
 BF16, FP32, FP8_E4M3 = 0, 1, 2
@@ -45,6 +45,7 @@ EXPORTS = (
     "comfy_moe_ffn_block",
     "comfy_moe_read_status",
     "comfy_moe_quantize_e4m3",
+    "comfy_attn_rmsnorm_rope",
     "comfy_moe_ep_dispatch",
     "comfy_moe_ep_signal",
     "comfy_moe_ep_wait",
@@ -238,6 +239,8 @@ def load(build_if_missing: bool = False) -> ctypes.CDLL:
         c_void_p, c_int64, c_void_p, c_void_p,
     ]
     lib.comfy_moe_quantize_e4m3.argtypes = [c_void_p, c_void_p, c_int64, c_void_p, c_void_p]
+    lib.comfy_attn_rmsnorm_rope.argtypes = [c_void_p, c_int64, c_void_p, c_float, c_void_p, c_int64, c_int, c_int, c_int,
+                                            c_int, c_int, c_int, c_void_p, c_int64, c_int, c_void_p]
     lib.comfy_moe_ep_signal.argtypes = [POINTER(PeerPlan), c_int, c_uint32, c_void_p]
     lib.comfy_moe_ep_wait.argtypes = [POINTER(PeerPlan), c_int, c_uint32, c_void_p, c_void_p]
     lib.comfy_moe_ep_combine.argtypes = [POINTER(PeerPlan), c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,

@@ -163,3 +163,100 @@ def block_feed_forward(norm, ff, tokens, shift, scale, gate):
     normed = norm(tokens).to(dtype=wtype)
     normed = normed * (1 + scale) + shift
     return gate * ff(normed.to(dtype=wtype)) + tokens
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# Joint attention of the block (``comfy/ldm/hidream/model.py:75-213``).  The six projections and the output
+# projections stay ``operations.Linear`` calls and the attention itself stays PyTorch's scaled-dot-product attention,
+# as in the reference on a CUDA device; what the kernels take over is everything in between.
+# ---------------------------------------------------------------------------------------------------------------
+def _apply_rope1(x, freqs_cis):
+    """``comfy/ldm/flux/math.py:38-44``: fp32 2x2 rotation of neighbouring pairs, rounded back to x's dtype."""
+    x_ = x.to(dtype=freqs_cis.dtype).reshape(*x.shape[:-1], -1, 1, 2)
+    x_out = freqs_cis[..., 0] * x_[..., 0]
+    x_out.addcmul_(freqs_cis[..., 1], x_[..., 1])
+    return x_out.reshape(*x.shape).type_as(x)
+
+
+def attention(query, key, value, transformer_options={}):
+    """[B, S, H, D] x 3 -> [B, S, H * D] (``model.py:75-76`` over ``attention_pytorch``)."""
+    b, s, h, d = query.shape
+    out = F.scaled_dot_product_attention(query.transpose(1, 2), key.transpose(1, 2), value.transpose(1, 2),
+                                         attn_mask=None, dropout_p=0.0, is_causal=False)
+    return out.transpose(1, 2).reshape(b, s, h * d)
+
+
+class HiDreamAttnProcessor_flashattn:
+    """Processor of ``HiDreamAttention`` (``model.py:79-146``)."""
+
+    def __call__(self, attn, image_tokens, image_tokens_masks=None, text_tokens=None, rope=None, transformer_options={},
+                 *args, **kwargs):
+        dtype, b = image_tokens.dtype, image_tokens.shape[0]
+        n_img = image_tokens.shape[1]
+        fast = b200_ops.hidream_qkv(attn, image_tokens, text_tokens, rope, image_tokens_masks)
+        if fast is not None:
+            query, key, value = fast
+        else:
+            query = attn.q_rms_norm(attn.to_q(image_tokens)).to(dtype=dtype)
+            key = attn.k_rms_norm(attn.to_k(image_tokens)).to(dtype=dtype)
+            value = attn.to_v(image_tokens)
+            head_dim = key.shape[-1] // attn.heads
+            query, key, value = (t.view(b, -1, attn.heads, head_dim) for t in (query, key, value))
+            if image_tokens_masks is not None:
+                key = key * image_tokens_masks.view(b, -1, 1, 1)
+            if not attn.single:
+                query_t = attn.q_rms_norm_t(attn.to_q_t(text_tokens)).to(dtype=dtype)
+                key_t = attn.k_rms_norm_t(attn.to_k_t(text_tokens)).to(dtype=dtype)
+                value_t = attn.to_v_t(text_tokens)
+                query_t, key_t, value_t = (t.view(b, -1, attn.heads, head_dim) for t in (query_t, key_t, value_t))
+                query = torch.cat([query, query_t], dim=1)
+                key = torch.cat([key, key_t], dim=1)
+                value = torch.cat([value, value_t], dim=1)
+            if query.shape[-1] == rope.shape[-3] * 2:
+                query, key = _apply_rope1(query, rope), _apply_rope1(key, rope)
+            else:
+                q1, q2 = query.chunk(2, dim=-1)
+                k1, k2 = key.chunk(2, dim=-1)
+                query = torch.cat([_apply_rope1(q1, rope), q2], dim=-1)
+                key = torch.cat([_apply_rope1(k1, rope), k2], dim=-1)
+
+        hidden = attention(query, key, value, transformer_options=transformer_options)
+        if attn.single:
+            return attn.to_out(hidden)
+        hidden_i, hidden_t = torch.split(hidden, [n_img, hidden.shape[1] - n_img], dim=1)
+        return attn.to_out(hidden_i), attn.to_out_t(hidden_t)
+
+
+class HiDreamAttention(nn.Module):
+    """Projections and norms of the block's attention (``model.py:148-213``); same constructor and state-dict keys:
+    ``to_q/to_k/to_v/to_out.{weight,bias}``, ``q_rms_norm/k_rms_norm.weight`` and the ``_t`` set unless ``single``."""
+
+    def __init__(self, query_dim: int, heads: int = 8, dim_head: int = 64, upcast_attention: bool = False,
+                 upcast_softmax: bool = False, scale_qk: bool = True, eps: float = 1e-5, processor=None,
+                 out_dim: int = None, single: bool = False, dtype=None, device=None, operations=None):
+        super().__init__()
+        self.inner_dim = out_dim if out_dim is not None else dim_head * heads
+        self.query_dim = query_dim
+        self.upcast_attention = upcast_attention
+        self.upcast_softmax = upcast_softmax
+        self.out_dim = out_dim if out_dim is not None else query_dim
+        self.scale_qk = scale_qk
+        self.scale = dim_head ** -0.5 if self.scale_qk else 1.0
+        self.heads = out_dim // dim_head if out_dim is not None else heads
+        self.sliceable_head_dim = heads
+        self.single = single
+        self.linear_cls = operations.Linear
+        kw = dict(dtype=dtype, device=device)
+        for sfx in ([""] if single else ["", "_t"]):
+            setattr(self, "to_q" + sfx, operations.Linear(query_dim, self.inner_dim, **kw))
+            setattr(self, "to_k" + sfx, operations.Linear(self.inner_dim, self.inner_dim, **kw))
+            setattr(self, "to_v" + sfx, operations.Linear(self.inner_dim, self.inner_dim, **kw))
+            setattr(self, "to_out" + sfx, operations.Linear(self.inner_dim, self.out_dim, **kw))
+            setattr(self, "q_rms_norm" + sfx, operations.RMSNorm(self.inner_dim, eps, **kw))
+            setattr(self, "k_rms_norm" + sfx, operations.RMSNorm(self.inner_dim, eps, **kw))
+        self.processor = processor
+
+    def forward(self, norm_image_tokens, image_tokens_masks=None, norm_text_tokens=None, rope=None,
+                transformer_options={}):
+        return self.processor(self, image_tokens=norm_image_tokens, image_tokens_masks=image_tokens_masks,
+                              text_tokens=norm_text_tokens, rope=rope, transformer_options=transformer_options)

@@ -592,3 +592,33 @@ def moe_mlp_forward(layer: MlpLayerPack, x: torch.Tensor, ws: Optional[Workspace
                                              _ptr(out), _stream())
     N.check("comfy_moe_forward_gelu_mlp", rc)
     return out
+
+
+# --------------------------------------------------------------------------------------- attention glue
+def rmsnorm_rope(x: torch.Tensor, weight: Optional[torch.Tensor], eps: float, rope: Optional[torch.Tensor],
+                 heads: int, out: torch.Tensor, out_row_offset: int = 0, rope_row_offset: int = 0) -> torch.Tensor:
+    """RMSNorm (optional) + rotary embedding (optional) of one projected tensor, written into rows
+    [out_row_offset, out_row_offset + S) of every batch element of ``out`` [B, S_total, heads, head_dim].
+
+    x: bf16 [B, S, heads * head_dim] (last dim contiguous, rows evenly strided); weight: bf16 [heads * head_dim] or
+    None; rope: fp32 [B or 1, S_rope, 1, pairs, 2, 2] or None, rotated rows start at ``rope_row_offset``."""
+    _need_cuda(x, weight, rope, out)
+    b, s, inner = x.shape
+    head_dim = inner // heads
+    if x.dtype != torch.bfloat16 or x.stride(2) != 1 or x.stride(0) != s * x.stride(1):
+        raise ValueError("x must be bf16 [B, S, inner] with evenly strided rows")
+    if out.dtype != torch.bfloat16 or out.shape[0] != b or out.shape[2:] != (heads, head_dim) or \
+            not out[0].is_contiguous() or out_row_offset + s > out.shape[1]:
+        raise ValueError("out must be bf16 [B, S_total, heads, head_dim] with room for the rows")
+    rope_stride = pairs = 0
+    if rope is not None:
+        if rope.dtype != torch.float32 or rope.dim() != 6 or rope.shape[2] != 1 or rope.shape[4:] != (2, 2) or \
+                not rope[0].is_contiguous() or rope_row_offset + s > rope.shape[1]:
+            raise ValueError("rope must be fp32 [B or 1, S_rope, 1, pairs, 2, 2]")
+        pairs = rope.shape[3]
+        rope_stride = rope.stride(0) if rope.shape[0] > 1 else 0
+    rc = N.load().comfy_attn_rmsnorm_rope(_ptr(x), x.stride(1), _ptr(weight), eps, _ptr(rope), rope_stride,
+                                          rope_row_offset, pairs, b * s, s, heads, head_dim, _ptr(out), out.stride(0),
+                                          out_row_offset, _stream())
+    N.check("comfy_attn_rmsnorm_rope", rc)
+    return out

@@ -107,6 +107,31 @@ class _LayerNorm(torch.nn.LayerNorm, CastWeightBiasOp):
 disable_weight_init.LayerNorm = _LayerNorm
 
 
+class _RMSNorm(torch.nn.RMSNorm, CastWeightBiasOp):
+    """operations.RMSNorm (``comfy/ops.py``, over ``comfy/rmsnorm.py:14-20``): ``torch.nn.functional.rms_norm`` with the
+    weight cast to the activation's dtype and device; HiDream's attention builds its q / k norms through it."""
+
+    def reset_parameters(self):
+        self.bias = None
+        return None
+
+    def forward_comfy_cast_weights(self, input):
+        weight = None
+        if self.weight is not None:
+            weight, _ = cast_bias_weight(self, input)
+        return F.rms_norm(input, self.normalized_shape, weight, self.eps)
+
+    def forward(self, input):
+        if self.comfy_cast_weights or self.weight_function or self.bias_function:
+            return self.forward_comfy_cast_weights(input)
+        weight = None if self.weight is None else model_management.cast_to(self.weight, dtype=input.dtype,
+                                                                          device=input.device)
+        return F.rms_norm(input, self.normalized_shape, weight, self.eps)
+
+
+disable_weight_init.RMSNorm = _RMSNorm
+
+
 class manual_cast(disable_weight_init):
     """Weights stored in one dtype and cast to the activation dtype on every call."""
 
@@ -114,6 +139,9 @@ class manual_cast(disable_weight_init):
         comfy_cast_weights = True
 
     class LayerNorm(disable_weight_init.LayerNorm):
+        comfy_cast_weights = True
+
+    class RMSNorm(disable_weight_init.RMSNorm):
         comfy_cast_weights = True
 
 
@@ -460,6 +488,61 @@ def swiglu_ffn_forward(ffn, x: torch.Tensor) -> Optional[torch.Tensor]:
         return None   # the dense fp8 path needs the quantised copy the permutation kernel makes
     _, y, _, _ = moe_ops.grouped_swiglu([], pack, None, None, None, x2, check_status=CHECK_STATUS_EVERY_CALL)
     return y.view(x.shape)
+
+
+# ---- q / k / v glue of the HiDream attention processor ----------------------------------------------------------
+def _norm_weight(norm, device):
+    """bf16 weight of an RMSNorm that can feed the kernel as it is now, else None."""
+    if getattr(norm, "weight_function", None) or getattr(norm, "bias_function", None) or norm.weight is None:
+        return None
+    w = norm.weight
+    if w.device != device or w.dtype != torch.bfloat16 or not w.is_contiguous():
+        return None
+    return w.detach()
+
+
+def hidream_qkv(attn, image_tokens: torch.Tensor, text_tokens: Optional[torch.Tensor], rope: torch.Tensor,
+                image_tokens_masks=None):
+    """What ``HiDreamAttnProcessor_flashattn`` does between the six projections and the attention call
+    (``comfy/ldm/hidream/model.py:97-137``): q / k RMSNorm, concatenation of image and text tokens, rotary embedding.
+    Returns (query, key, value) as [B, S_img + S_txt, heads, head_dim], or None when the call is not eligible (the
+    projections themselves stay ``operations.Linear`` calls, i.e. library GEMMs, as in the reference)."""
+    x = image_tokens
+    if image_tokens_masks is not None or not ENABLE_SM100_KERNELS or rope is None:
+        return None
+    if not (x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 3 and model_management.is_sm100(x.device)):
+        return None
+    if rope.dtype != torch.float32 or rope.device != x.device or rope.dim() != 6 or not rope.is_contiguous():
+        return None
+    heads = attn.heads
+    inner = attn.inner_dim
+    head_dim = inner // heads
+    pairs = rope.shape[-3]
+    if inner > 4096 or head_dim % 8 or pairs * 2 > head_dim or rope.shape[0] not in (1, x.shape[0]):
+        return None
+    joint = not attn.single
+    if joint and (text_tokens is None or text_tokens.dtype != x.dtype or text_tokens.device != x.device):
+        return None
+    norms = [attn.q_rms_norm, attn.k_rms_norm] + ([attn.q_rms_norm_t, attn.k_rms_norm_t] if joint else [])
+    weights = [_norm_weight(n, x.device) for n in norms]
+    if any(w is None for w in weights) or any(abs(n.eps - norms[0].eps) > 0 for n in norms):
+        return None
+    from . import moe_ops
+
+    b, s_img = x.shape[0], x.shape[1]
+    s_txt = text_tokens.shape[1] if joint else 0
+    if rope.shape[1] < s_img + s_txt:
+        return None
+    eps = norms[0].eps if norms[0].eps is not None else torch.finfo(x.dtype).eps
+    q, k, v = (torch.empty((b, s_img + s_txt, heads, head_dim), dtype=x.dtype, device=x.device) for _ in range(3))
+    moe_ops.rmsnorm_rope(attn.to_q(x), weights[0], eps, rope, heads, q)
+    moe_ops.rmsnorm_rope(attn.to_k(x), weights[1], eps, rope, heads, k)
+    moe_ops.rmsnorm_rope(attn.to_v(x), None, eps, None, heads, v)
+    if joint:
+        moe_ops.rmsnorm_rope(attn.to_q_t(text_tokens), weights[2], eps, rope, heads, q, s_img, s_img)
+        moe_ops.rmsnorm_rope(attn.to_k_t(text_tokens), weights[3], eps, rope, heads, k, s_img, s_img)
+        moe_ops.rmsnorm_rope(attn.to_v_t(text_tokens), None, eps, None, heads, v, s_img, 0)
+    return q, k, v
 
 
 # ---- Hunyuan3D-2.1 MoE block (GELU feed-forwards with biases) ------------------------------------------------

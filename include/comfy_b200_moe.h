@@ -26,7 +26,7 @@
 extern "C" {
 #endif
 
-#define COMFY_MOE_ABI_VERSION 6
+#define COMFY_MOE_ABI_VERSION 7
 
 /* Return codes. */
 #define COMFY_MOE_OK 0
@@ -277,6 +277,22 @@ typedef struct ComfyMoeMlpLayer {
 
 int comfy_moe_forward_gelu_mlp(const ComfyMoeMlpLayer* h_layer, const ComfyMoeWorkspace* h_ws, const void* x,
                                int n_tokens, void* out, void* stream);
+
+/* ---- q / k / v glue of the HiDream attention processor (model.py:97-137) ------------------------------------------
+ * One pass per projected tensor x [n_tokens, heads * head_dim] (bf16, row stride ld_x):
+ *   n   = rms_norm(x, weight, eps) over the whole row as torch.nn.functional.rms_norm computes it for bf16 (fp32
+ *         statistics, x * rstd * weight rounded once); weight NULL = no normalisation (the value projection);
+ *   out = apply_rope(n, rope) of comfy/ldm/flux/math.py:38-47 on the first rope_pairs pairs of every head (fp32
+ *         rotation f[i][0] * n[2p] + f[i][1] * n[2p+1], rounded to bf16); rope NULL = no rotation.
+ * Token t = (b, s) with s < tokens_per_batch is written to out + b * out_batch_stride + (out_row_offset + s) * inner
+ * and rotated with rope + b * rope_batch_stride + (rope_row_offset + s) * rope_pairs * 4 (fp32 [.., pairs, 2, 2]), so
+ * the image part and the text part of a joint sequence land in one [B, S_img + S_txt, heads, head_dim] buffer without
+ * the reference's torch.cat.  inner <= 4096, head_dim % 8 == 0.
+ */
+int comfy_attn_rmsnorm_rope(const void* x, int64_t ld_x, const void* weight, float eps, const float* rope,
+                            int64_t rope_batch_stride, int rope_row_offset, int rope_pairs, int n_tokens,
+                            int tokens_per_batch, int heads, int head_dim, void* out, int64_t out_batch_stride,
+                            int out_row_offset, void* stream);
 
 /* ---- activation quantiser on its own (comfy/ops.py:338-343) --------------------------------------------------
  * out = e4m3( clamp( scale ? bf16(x * bf16(1 / scale)) : x, +-448 ) ), round to nearest even; x bf16, n_elements a

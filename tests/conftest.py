@@ -35,6 +35,17 @@ def golden_hunyuan3d():
 
 
 @pytest.fixture(scope="session")
+def golden_attention():
+    import numpy as np
+
+    path = os.path.join(ROOT, "tests", "golden", "hidream_attention_small.npz")
+    with np.load(path, allow_pickle=False) as z:
+        data = {k: z[k] for k in z.files}
+    data["meta"] = dict(zip(data.pop("meta_keys").tolist(), data.pop("meta_vals").tolist()))
+    return data
+
+
+@pytest.fixture(scope="session")
 def cuda_device():
     import torch
 

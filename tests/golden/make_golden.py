@@ -23,6 +23,7 @@ sys.path.insert(0, ROOT)
 
 from oracle import hidream_moe_oracle as O  # noqa: E402  (seeded weight recipe only)
 from oracle import hunyuan3d_moe_oracle as H  # noqa: E402  (seeded weight recipe only)
+from oracle import hidream_attention_oracle as A  # noqa: E402  (seeded weight recipe only)
 
 DIM, HIDDEN_DIM, E, K = 256, 1024, 4, 2
 BATCH, SEQ = 2, 64
@@ -177,7 +178,77 @@ def hunyuan3d(ref_root: str) -> None:
     print("wrote", path, os.path.getsize(path), "bytes")
 
 
+def attention(ref_root: str) -> None:
+    """HiDreamAttention with HiDreamAttnProcessor_flashattn (comfy/ldm/hidream/model.py:79-213) at reduced size, as a
+    double-stream (image + text) and as a single-stream block; q, k, v are captured where the processor hands them to
+    the attention call."""
+    import comfy.ldm.hidream.model as RM
+    import comfy.ops
+
+    heads, head_dim, axes = 4, 64, [32, 16, 16]
+    dim = heads * head_dim
+    batch, hh, ww, n_text = 2, 6, 8, 16
+    out = {}
+    captured = {}
+    stock = RM.attention
+
+    def spy(query, key, value, transformer_options={}):
+        captured.update(q=query.clone(), k=key.clone(), v=value.clone())
+        return stock(query, key, value, transformer_options=transformer_options)
+
+    RM.attention = spy
+    # On a CUDA device the reference selects attention_pytorch (comfy/ldm/modules/attention.py:634-635); with --cpu it
+    # would pick the sub-quadratic variant.  The fixtures pin the function a B200 runs.
+    import comfy.ldm.modules.attention as RA
+
+    stock_select = RM.optimized_attention
+    RM.optimized_attention = RA.attention_pytorch
+
+    def f32(t):
+        return t.detach().float().numpy()
+
+    ids = A.make_ids(batch, hh, ww, n_text)
+    freqs = RM.EmbedND(theta=10000, axes_dim=axes)(ids)
+    out["rope"] = f32(freqs)
+    g = torch.Generator().manual_seed(X_SEED)
+    img32 = torch.randn((batch, hh * ww, dim), generator=g)
+    txt32 = torch.randn((batch, n_text, dim), generator=g)
+    out["x_checksum"] = np.array([float(img32.double().sum()), float(txt32.double().sum())])
+    for name, dtype in (("fp32", torch.float32), ("bf16", torch.bfloat16)):
+        for single in (False, True):
+            tag = f"{name}/{'single' if single else 'double'}"
+            layer = A.make_layer(dim, heads, head_dim, single, seed=W_SEED, dtype=dtype)
+            m = RM.HiDreamAttention(query_dim=dim, heads=heads, dim_head=head_dim,
+                                    processor=RM.HiDreamAttnProcessor_flashattn(), single=single, dtype=dtype,
+                                    device="cpu", operations=comfy.ops.disable_weight_init)
+            res = m.load_state_dict(layer, strict=True)
+            assert not res.missing_keys and not res.unexpected_keys
+            img, txt = img32.to(dtype), txt32.to(dtype)
+            with torch.no_grad():
+                if single:
+                    # a single-stream block attends over the concatenated sequence with the image projections
+                    seq = torch.cat([img, txt], dim=1)
+                    y = m(seq, None, None, rope=freqs)
+                    out[f"{tag}/out"] = f32(y)
+                else:
+                    yi, yt = m(img, None, txt, rope=freqs)
+                    out[f"{tag}/out_i"], out[f"{tag}/out_t"] = f32(yi), f32(yt)
+            for k in ("q", "k", "v"):
+                out[f"{tag}/{k}"] = f32(captured[k])
+            out[f"{tag}/keys"] = np.array(sorted(layer.keys()))
+    RM.attention = stock
+    RM.optimized_attention = stock_select
+    out["meta_keys"] = np.array(["heads", "head_dim", "axes", "batch", "height", "width", "n_text", "w_seed", "x_seed",
+                                 "torch_version"])
+    out["meta_vals"] = np.array([str(v) for v in (heads, head_dim, axes, batch, hh, ww, n_text, W_SEED, X_SEED,
+                                                  torch.__version__)])
+    path = os.path.join(HERE, "hidream_attention_small.npz")
+    np.savez_compressed(path, **out)
+    print("wrote", path, os.path.getsize(path), "bytes")
+
+
 if __name__ == "__main__":
     root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
     main(root)
     hunyuan3d(root)
+    attention(root)
