@@ -23,7 +23,7 @@ def _declared_functions():
         if fn.endswith(".h"):
             text = open(os.path.join(inc, fn)).read()
             text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-            names += re.findall(r"\b(comfy_moe_\w+)\s*\(", text)
+            names += re.findall(r"\b(comfy_(?:moe|attn)_\w+)\s*\(", text)
     return sorted(set(names))
 
 
