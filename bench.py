@@ -590,13 +590,101 @@ def run_hunyuan3d(args) -> None:
     }))
 
 
+def run_dit_body(args) -> None:
+    """Side workload (not the headline): the transformer body of BASELINE config 4, i.e. 16 double-stream and 32
+    single-stream HiDream blocks (dim 2560, 20 heads x 128, MoE feed-forward on the image tokens), random-init bf16,
+    2 x 4096 image tokens + 2 x 384 text tokens (128 T5 + 2 x 128 Llama), one pass = one denoising step without the
+    embedders and the final layer.  Timed with the kernels and, on the same modules, as PyTorch composes it."""
+    from comfyui_b200 import _native, ops
+    from comfyui_b200.ldm.hidream import model as M
+
+    _native.load()
+    dev = torch.device("cuda", 0)
+    dim, heads, head_dim, b, s_img, s_txt = 2560, 20, 128, 2, 4096, 384
+    n_double, n_single = args.double_blocks, args.single_blocks
+    torch.manual_seed(0)
+
+    def build(single):
+        cls = M.HiDreamImageSingleTransformerBlock if single else M.HiDreamImageTransformerBlock
+        blk = cls(dim, heads, head_dim, 4, 2, dtype=torch.bfloat16, device=dev, operations=ops.disable_weight_init).eval()
+        with torch.no_grad():
+            for name, p in blk.named_parameters():
+                if "rms_norm" in name:
+                    p.fill_(1.0)
+                elif name.endswith("bias"):
+                    p.normal_(0.0, 0.02)
+                else:
+                    p.normal_(0.0, 0.02)
+        return blk
+
+    doubles = [build(False) for _ in range(n_double)]
+    singles = [build(True) for _ in range(n_single)]
+    img = torch.randn((b, s_img, dim), device=dev).bfloat16()
+    txt = torch.randn((b, s_txt, dim), device=dev).bfloat16()
+    ada = torch.randn((b, dim), device=dev).bfloat16()
+    # the model's position ids: (0, row, column) for the 64 x 64 patches, zeros for text tokens
+    ids = torch.zeros((b, s_img + s_txt, 3), device=dev)
+    ids[:, :s_img, 1] = torch.arange(64, device=dev).repeat_interleave(64)
+    ids[:, :s_img, 2] = torch.arange(64, device=dev).repeat(64)
+    omega = [1.0 / (10000 ** torch.linspace(0, (d - 2) / d, steps=d // 2, dtype=torch.float64, device=dev))
+             for d in (64, 32, 32)]
+    ang = torch.cat([ids[..., i, None].float() * omega[i].float() for i in range(3)], dim=-1)
+    rope = torch.stack([ang.cos(), -ang.sin(), ang.sin(), ang.cos()], dim=-1).reshape(b, s_img + s_txt, 1, 64, 2, 2)
+    rope = rope.float().contiguous()
+
+    def step():
+        x, t = img, txt
+        for blk in doubles:
+            x, t = blk(x, None, t, ada, rope)
+        seq = torch.cat([x, t], dim=1)
+        for blk in singles:
+            seq = blk(seq, None, None, ada, rope)
+        return seq
+
+    def timed(steps, warmup):
+        for _ in range(warmup):
+            step()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            step()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / steps
+
+    steps = min(args.steps, 10)
+    with torch.inference_mode():
+        with ClockSampler(0) as clocks:
+            ms = timed(steps, 3)
+        ops.ENABLE_SM100_KERNELS = False
+        try:
+            ms_stock = timed(max(steps // 2, 2), 2)
+        finally:
+            ops.ENABLE_SM100_KERNELS = True
+    print(json.dumps({
+        "metric": "denoising-step body, ms (HiDream-I1 transformer blocks, bf16)", "value": ms, "unit": "ms",
+        "n_gpus": 1, "steps": steps, "warmup": 3, "ms_per_step": ms, "higher_is_better": False, "dtype": "bf16",
+        "data": "synthetic",
+        "config": {"workload": f"BASELINE config 4 without embedders and final layer: {n_double} double-stream + "
+                               f"{n_single} single-stream blocks, 2 x (4096 image + 384 text) tokens, random-init bf16",
+                   "dim": dim, "heads": heads, "head_dim": head_dim, "experts": 4, "top_k": 2},
+        "clocks": clocks.summary(),
+        "gpu_bar": {"what": "same modules and weights, sm_100a kernels off: stock PyTorch composition on this GPU",
+                    "ms_per_step": ms_stock},
+        "speedup_vs_stock": ms_stock / ms,
+    }))
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="hidream", choices=["hidream", "config5", "hunyuan3d"],
+    ap.add_argument("--double-blocks", type=int, default=16, help="dit_body: number of double-stream blocks")
+    ap.add_argument("--single-blocks", type=int, default=32, help="dit_body: number of single-stream blocks")
+    ap.add_argument("--workload", default="hidream", choices=["hidream", "config5", "hunyuan3d", "dit_body"],
                     help="hidream = the headline layer (8192 tokens per GPU, weak scaling); config5 = 131072 tokens in "
                          "total with a skewed router (strong scaling); hunyuan3d = the sibling GELU-MLP MoE block "
                          "(one GPU, bf16)")
@@ -610,6 +698,8 @@ def main() -> None:
         run_reference_arm(args)
     elif args.workload == "hunyuan3d":
         run_hunyuan3d(args)
+    elif args.workload == "dit_body":
+        run_dit_body(args)
     else:
         run_gpu_arm(args)
 

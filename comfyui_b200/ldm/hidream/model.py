@@ -260,3 +260,117 @@ class HiDreamAttention(nn.Module):
                 transformer_options={}):
         return self.processor(self, image_tokens=norm_image_tokens, image_tokens_masks=image_tokens_masks,
                               text_tokens=norm_text_tokens, rope=rope, transformer_options=transformer_options)
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# The two transformer blocks (``comfy/ldm/hidream/model.py:363-575``): same constructors, attribute names and
+# state-dict keys; their forwards are the reference's lines with the element-wise passes handed to the kernels where
+# a call is eligible (each helper falls back to the PyTorch composition on its own).
+# ---------------------------------------------------------------------------------------------------------------
+def _modulated_norm(norm, tokens, shift, scale):
+    fast = b200_ops.hidream_modulated_norm(norm, tokens, shift, scale)
+    if fast is not None:
+        return fast
+    wtype = tokens.dtype
+    return norm(tokens).to(dtype=wtype) * (1 + scale) + shift
+
+
+def _gated_residual(y, gate, tokens):
+    fast = b200_ops.hidream_gated_residual(y, gate, tokens)
+    if fast is not None:
+        return fast
+    return gate * y + tokens
+
+
+class BlockType:
+    TransformerBlock = 1
+    SingleTransformerBlock = 2
+
+
+def _block_ffn(dim, num_routed_experts, num_activated_experts, kw):
+    if num_routed_experts > 0:
+        return MOEFeedForwardSwiGLU(dim=dim, hidden_dim=4 * dim, num_routed_experts=num_routed_experts,
+                                    num_activated_experts=num_activated_experts, **kw)
+    return FeedForwardSwiGLU(dim=dim, hidden_dim=4 * dim, **kw)
+
+
+class HiDreamImageSingleTransformerBlock(nn.Module):
+    """Single-stream block (``model.py:363-434``): one modulated attention and one modulated MoE feed-forward over the
+    concatenated image + text sequence."""
+
+    def __init__(self, dim: int, num_attention_heads: int, attention_head_dim: int, num_routed_experts: int = 4,
+                 num_activated_experts: int = 2, dtype=None, device=None, operations=None):
+        super().__init__()
+        kw = dict(dtype=dtype, device=device, operations=operations)
+        self.num_attention_heads = num_attention_heads
+        self.adaLN_modulation = nn.Sequential(nn.SiLU(), operations.Linear(dim, 6 * dim, bias=True, dtype=dtype,
+                                                                           device=device))
+        self.norm1_i = operations.LayerNorm(dim, eps=1e-06, elementwise_affine=False, dtype=dtype, device=device)
+        self.attn1 = HiDreamAttention(query_dim=dim, heads=num_attention_heads, dim_head=attention_head_dim,
+                                      processor=HiDreamAttnProcessor_flashattn(), single=True, **kw)
+        self.norm3_i = operations.LayerNorm(dim, eps=1e-06, elementwise_affine=False, dtype=dtype, device=device)
+        self.ff_i = _block_ffn(dim, num_routed_experts, num_activated_experts, kw)
+
+    def forward(self, image_tokens, image_tokens_masks=None, text_tokens=None, adaln_input=None, rope=None,
+                transformer_options={}):
+        shift_msa, scale_msa, gate_msa, shift_mlp, scale_mlp, gate_mlp = \
+            self.adaLN_modulation(adaln_input)[:, None].chunk(6, dim=-1)
+        normed = _modulated_norm(self.norm1_i, image_tokens, shift_msa, scale_msa)
+        attn_out = self.attn1(normed, image_tokens_masks, rope=rope, transformer_options=transformer_options)
+        image_tokens = _gated_residual(attn_out, gate_msa, image_tokens)
+        return block_feed_forward(self.norm3_i, self.ff_i, image_tokens, shift_mlp, scale_mlp, gate_mlp)
+
+
+class HiDreamImageTransformerBlock(nn.Module):
+    """Double-stream block (``model.py:437-524``): joint attention over image and text tokens with separate
+    projections, a MoE feed-forward for the image tokens and a dense SwiGLU feed-forward for the text tokens."""
+
+    def __init__(self, dim: int, num_attention_heads: int, attention_head_dim: int, num_routed_experts: int = 4,
+                 num_activated_experts: int = 2, dtype=None, device=None, operations=None):
+        super().__init__()
+        kw = dict(dtype=dtype, device=device, operations=operations)
+        self.num_attention_heads = num_attention_heads
+        self.adaLN_modulation = nn.Sequential(nn.SiLU(), operations.Linear(dim, 12 * dim, bias=True, dtype=dtype,
+                                                                           device=device))
+        ln = dict(eps=1e-06, elementwise_affine=False)
+        self.norm1_i = operations.LayerNorm(dim, dtype=dtype, device=device, **ln)
+        self.norm1_t = operations.LayerNorm(dim, dtype=dtype, device=device, **ln)
+        self.attn1 = HiDreamAttention(query_dim=dim, heads=num_attention_heads, dim_head=attention_head_dim,
+                                      processor=HiDreamAttnProcessor_flashattn(), single=False, **kw)
+        self.norm3_i = operations.LayerNorm(dim, dtype=dtype, device=device, **ln)
+        self.ff_i = _block_ffn(dim, num_routed_experts, num_activated_experts, kw)
+        self.norm3_t = operations.LayerNorm(dim, **ln)
+        self.ff_t = FeedForwardSwiGLU(dim=dim, hidden_dim=4 * dim, **kw)
+
+    def forward(self, image_tokens, image_tokens_masks=None, text_tokens=None, adaln_input=None, rope=None,
+                transformer_options={}):
+        (shift_msa_i, scale_msa_i, gate_msa_i, shift_mlp_i, scale_mlp_i, gate_mlp_i,
+         shift_msa_t, scale_msa_t, gate_msa_t, shift_mlp_t, scale_mlp_t, gate_mlp_t) = \
+            self.adaLN_modulation(adaln_input)[:, None].chunk(12, dim=-1)
+        normed_i = _modulated_norm(self.norm1_i, image_tokens, shift_msa_i, scale_msa_i)
+        normed_t = _modulated_norm(self.norm1_t, text_tokens, shift_msa_t, scale_msa_t)
+        attn_i, attn_t = self.attn1(normed_i, image_tokens_masks, normed_t, rope=rope,
+                                    transformer_options=transformer_options)
+        image_tokens = _gated_residual(attn_i, gate_msa_i, image_tokens)
+        text_tokens = _gated_residual(attn_t, gate_msa_t, text_tokens)
+        image_tokens = block_feed_forward(self.norm3_i, self.ff_i, image_tokens, shift_mlp_i, scale_mlp_i, gate_mlp_i)
+        text_tokens = block_feed_forward(self.norm3_t, self.ff_t, text_tokens, shift_mlp_t, scale_mlp_t, gate_mlp_t)
+        return image_tokens, text_tokens
+
+
+class HiDreamImageBlock(nn.Module):
+    """Wrapper the model stacks (``model.py:527-575``): ``.block`` is one of the two classes above."""
+
+    def __init__(self, dim: int, num_attention_heads: int, attention_head_dim: int, num_routed_experts: int = 4,
+                 num_activated_experts: int = 2, block_type=BlockType.TransformerBlock, dtype=None, device=None,
+                 operations=None):
+        super().__init__()
+        cls = {BlockType.TransformerBlock: HiDreamImageTransformerBlock,
+               BlockType.SingleTransformerBlock: HiDreamImageSingleTransformerBlock}[block_type]
+        self.block = cls(dim, num_attention_heads, attention_head_dim, num_routed_experts, num_activated_experts,
+                         dtype=dtype, device=device, operations=operations)
+
+    def forward(self, image_tokens, image_tokens_masks=None, text_tokens=None, adaln_input=None, rope=None,
+                transformer_options={}):
+        return self.block(image_tokens, image_tokens_masks, text_tokens, adaln_input, rope,
+                          transformer_options=transformer_options)

@@ -707,3 +707,28 @@ def hidream_block_ffn(norm, ff, x: torch.Tensor, shift: torch.Tensor, scale: tor
     x_mod = moe_ops.ln_modulate(x2, shift, scale, s, norm.eps)
     _, y, _, _ = moe_ops.grouped_swiglu([], pack, None, None, None, x_mod, check_status=CHECK_STATUS_EVERY_CALL)
     return moe_ops.gate_residual(y, gate, x2, s).view(x.shape)
+
+
+def hidream_modulated_norm(norm, x: torch.Tensor, shift: torch.Tensor, scale: torch.Tensor) -> Optional[torch.Tensor]:
+    """``norm(x) * (1 + scale) + shift`` (``comfy/ldm/hidream/model.py:415-416``, ``:497-500``) in one pass, or None."""
+    if x.dim() != 3 or getattr(norm, "weight", None) is not None or getattr(norm, "bias", None) is not None:
+        return None
+    if not _input_ok(x, x.shape[-1]) or not _modulation_ok(x, shift, scale):
+        return None
+    from . import moe_ops
+
+    b, s, d = x.shape
+    return moe_ops.ln_modulate(x.view(-1, d), shift, scale, s, norm.eps).view(x.shape)
+
+
+def hidream_gated_residual(y: torch.Tensor, gate: torch.Tensor, residual: torch.Tensor) -> Optional[torch.Tensor]:
+    """``gate * y + residual`` (``model.py:424``, ``:512-513``) in one pass, or None."""
+    x = residual
+    if x.dim() != 3 or y.shape != x.shape or y.dtype != x.dtype or not y.is_contiguous():
+        return None
+    if not _input_ok(x, x.shape[-1]) or not _modulation_ok(x, gate):
+        return None
+    from . import moe_ops
+
+    b, s, d = x.shape
+    return moe_ops.gate_residual(y.view(-1, d), gate, x.view(-1, d), s).view(x.shape)

@@ -46,6 +46,17 @@ def golden_attention():
 
 
 @pytest.fixture(scope="session")
+def golden_block():
+    import numpy as np
+
+    path = os.path.join(ROOT, "tests", "golden", "hidream_block_small.npz")
+    with np.load(path, allow_pickle=False) as z:
+        data = {k: z[k] for k in z.files}
+    data["meta"] = dict(zip(data.pop("meta_keys").tolist(), data.pop("meta_vals").tolist()))
+    return data
+
+
+@pytest.fixture(scope="session")
 def cuda_device():
     import torch
 

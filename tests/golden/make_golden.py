@@ -24,6 +24,7 @@ sys.path.insert(0, ROOT)
 from oracle import hidream_moe_oracle as O  # noqa: E402  (seeded weight recipe only)
 from oracle import hunyuan3d_moe_oracle as H  # noqa: E402  (seeded weight recipe only)
 from oracle import hidream_attention_oracle as A  # noqa: E402  (seeded weight recipe only)
+from oracle import hidream_block_oracle as B  # noqa: E402  (seeded weight recipe only)
 
 DIM, HIDDEN_DIM, E, K = 256, 1024, 4, 2
 BATCH, SEQ = 2, 64
@@ -247,8 +248,57 @@ def attention(ref_root: str) -> None:
     print("wrote", path, os.path.getsize(path), "bytes")
 
 
+def blocks(ref_root: str) -> None:
+    """HiDreamImageTransformerBlock and HiDreamImageSingleTransformerBlock (comfy/ldm/hidream/model.py:363-524) at
+    reduced size, as shipped (MoE gate in the activation dtype), with the attention variant a CUDA device selects."""
+    import comfy.ldm.hidream.model as RM
+    import comfy.ldm.modules.attention as RA
+    import comfy.ops
+
+    heads, head_dim, axes, n_exp = 4, 64, [32, 16, 16], 4
+    dim = heads * head_dim
+    batch, hh, ww, n_text = 2, 6, 8, 16
+    stock_select = RM.optimized_attention
+    RM.optimized_attention = RA.attention_pytorch
+    out = {}
+
+    def f32(t):
+        return t.detach().float().numpy()
+
+    freqs = RM.EmbedND(theta=10000, axes_dim=axes)(A.make_ids(batch, hh, ww, n_text))
+    g = torch.Generator().manual_seed(X_SEED)
+    img32 = torch.randn((batch, hh * ww, dim), generator=g)
+    txt32 = torch.randn((batch, n_text, dim), generator=g)
+    ada32 = torch.randn((batch, dim), generator=g)
+    for name, dtype in (("fp32", torch.float32), ("bf16", torch.bfloat16)):
+        img, txt, ada = img32.to(dtype), txt32.to(dtype), ada32.to(dtype)
+        for single in (False, True):
+            cls = RM.HiDreamImageSingleTransformerBlock if single else RM.HiDreamImageTransformerBlock
+            layer = B.make_layer(dim, heads, head_dim, n_exp, single, seed=W_SEED, dtype=dtype)
+            m = cls(dim, heads, head_dim, n_exp, 2, dtype=dtype, device="cpu", operations=comfy.ops.disable_weight_init)
+            res = m.load_state_dict(layer, strict=True)
+            assert not res.missing_keys and not res.unexpected_keys
+            tag = f"{name}/{'single' if single else 'double'}"
+            with torch.no_grad():
+                if single:
+                    out[f"{tag}/out"] = f32(m(torch.cat([img, txt], dim=1), None, None, ada, freqs))
+                else:
+                    yi, yt = m(img, None, txt, ada, freqs)
+                    out[f"{tag}/out_i"], out[f"{tag}/out_t"] = f32(yi), f32(yt)
+            out[f"{tag}/keys"] = np.array(sorted(layer.keys()))
+    RM.optimized_attention = stock_select
+    out["meta_keys"] = np.array(["heads", "head_dim", "axes", "n_experts", "batch", "height", "width", "n_text",
+                                 "w_seed", "x_seed", "torch_version"])
+    out["meta_vals"] = np.array([str(v) for v in (heads, head_dim, axes, n_exp, batch, hh, ww, n_text, W_SEED, X_SEED,
+                                                  torch.__version__)])
+    path = os.path.join(HERE, "hidream_block_small.npz")
+    np.savez_compressed(path, **out)
+    print("wrote", path, os.path.getsize(path), "bytes")
+
+
 if __name__ == "__main__":
     root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
     main(root)
     hunyuan3d(root)
     attention(root)
+    blocks(root)
