@@ -485,7 +485,7 @@ def swiglu_ffn_forward(ffn, x: torch.Tensor) -> Optional[torch.Tensor]:
         return None
     x2 = x.view(-1, dim)
     if pack.w1.dtype == FP8:
-        return None   # the dense fp8 path needs the quantised copy the permutation kernel makes
+        x2 = moe_ops.quantize_e4m3(x2, pack.scale_in13)     # the activation quantiser of comfy/ops.py:338-343
     _, y, _, _ = moe_ops.grouped_swiglu([], pack, None, None, None, x2, check_status=CHECK_STATUS_EVERY_CALL)
     return y.view(x.shape)
 
@@ -702,9 +702,11 @@ def hidream_block_ffn(norm, ff, x: torch.Tensor, shift: torch.Tensor, scale: tor
     if not _input_ok(x, ff.w1.weight.shape[1]):
         return None
     pack = _ffn_pack(ff, x.device, moe_ops)
-    if pack is None or pack.hidden % 128 or pack.w1.dtype == FP8:
+    if pack is None or pack.hidden % 128:
         return None
     x_mod = moe_ops.ln_modulate(x2, shift, scale, s, norm.eps)
+    if pack.w1.dtype == FP8:
+        x_mod = moe_ops.quantize_e4m3(x_mod, pack.scale_in13)
     _, y, _, _ = moe_ops.grouped_swiglu([], pack, None, None, None, x_mod, check_status=CHECK_STATUS_EVERY_CALL)
     return moe_ops.gate_residual(y, gate, x2, s).view(x.shape)
 

@@ -113,6 +113,30 @@ def test_scaled_fp8_module(cuda_device):
     assert ops._layer_pack(mod2, xd) is None
 
 
+@pytest.mark.parametrize("scale_input", [None, 0.75])
+def test_scaled_fp8_dense_ffn(cuda_device, scale_input):
+    """The shared expert of a scaled-fp8 module called on its own (what a block's text feed-forward is): the input is
+    quantised by the stand-alone quantiser, then one group of the fp8 GEMM."""
+    from comfyui_b200 import ops
+
+    dev = cuda_device
+    dim, hidden_dim, n = 512, 2048, 300
+    layer = O.quantize_layer_fp8({k: v.bfloat16() for k, v in O.make_layer(dim, hidden_dim, 4, seed=0).items()},
+                                 scale_input=scale_input)
+    x = O.make_input(n, dim, seed=1).bfloat16()
+    operations = ops.scaled_fp8_ops(fp8_matrix_mult=True, scale_input=scale_input is not None,
+                                    override_dtype=torch.float8_e4m3fn)
+    mod = _module(dev, dim, hidden_dim, operations, layer)
+    xd = x.to(dev).view(1, n, dim)
+    with torch.inference_mode():
+        fast = ops.swiglu_ffn_forward(mod.shared_experts, xd)
+        assert fast is not None
+        out = mod.shared_experts(xd).view(-1, dim).cpu()
+    ref = O.swiglu_ffn(x.clone(), layer, "shared_experts", O.FP8_MATMUL)
+    rel = float((out.float() - ref.float()).norm() / ref.float().norm())
+    assert rel < 1e-2, rel
+
+
 def test_device_status_word_is_reported(cuda_device):
     """Failure reporting without provoking a failure: the kernels write a code to the status word when a bounded
     wait gives up; here the word is set from the host and the host-side plumbing must turn it into an error."""
