@@ -151,7 +151,7 @@ def ep_transport() -> str:
 def workload_config(n_gpus: int, dtype: str = "bf16", tokens_per_gpu: int = TOKENS_PER_GPU, config5: bool = False):
     if config5:
         return {
-            "workload": "BASELINE config 5: HiDream MoE FFN layer, bf16, 8 x 16384 tokens in total, skewed router "
+            "workload": "benchmark configuration 5: HiDream MoE FFN layer, bf16, 8 x 16384 tokens in total, skewed router "
                         f"(gate.weight[0, 0] = {SKEW_BIAS} on a constant input feature: expert 0 takes about 60 % of the "
                         "top-1 picks), fp32 gate",
             "tokens_per_gpu": tokens_per_gpu, "global_tokens": tokens_per_gpu * n_gpus, "dim": DIM, "experts": N_EXPERTS,
@@ -160,9 +160,9 @@ def workload_config(n_gpus: int, dtype: str = "bf16", tokens_per_gpu: int = TOKE
                                                             "expert data-parallel",
             "l2": "no flush: one step touches gigabytes of activations",
         }
-    what = ("BASELINE config 2: HiDream MoE FFN layer, bf16 weights and activations, 2 x 4096 tokens per GPU, fp32 gate"
+    what = ("benchmark configuration 2: HiDream MoE FFN layer, bf16 weights and activations, 2 x 4096 tokens per GPU, fp32 gate"
             if dtype == "bf16" else
-            "BASELINE config 3: HiDream MoE FFN layer, expert and shared weights e4m3 with per-tensor fp32 scales, bf16 "
+            "benchmark configuration 3: HiDream MoE FFN layer, expert and shared weights e4m3 with per-tensor fp32 scales, bf16 "
             "activations quantised to e4m3 for the matmuls, 2 x 4096 tokens per GPU, fp32 gate")
     return {
         "workload": what,
@@ -195,7 +195,7 @@ def make_synthetic(dev, seed_w: int = 0, seed_x: int = 1, fp8: bool = False, n_t
         draw(prefix + ".w3.weight", (h, DIM))
     draw("gate.weight", (N_EXPERTS, DIM))
     if fp8:
-        # per-tensor scaled e4m3 (BASELINE config 3): s = max|w| / 448, wq = (w / s).to(e4m3); the gate stays bf16
+        # per-tensor scaled e4m3 (benchmark configuration 3): s = max|w| / 448, wq = (w / s).to(e4m3); the gate stays bf16
         for k in [k for k in state if k != "gate.weight"]:
             w = state[k].float()
             sc = (w.abs().max() / 448.0).reshape(())
@@ -544,16 +544,19 @@ def run_hunyuan3d(args) -> None:
     GELU feed-forwards of inner width 8192 with biases, 2 x 4096 latent tokens, bf16, one GPU."""
     from comfyui_b200 import _native, ops
     from comfyui_b200.ldm.hunyuan3dv2_1.hunyuandit import MoEBlock
-    from oracle import hunyuan3d_moe_oracle as H   # seeded weight recipe only
 
     _native.load()
     dev = torch.device("cuda", 0)
     dim, inner, e, n = 2048, 8192, 8, 8192
-    layer = H.make_layer(dim, inner, e, seed=0, dtype=torch.bfloat16)
     mod = MoEBlock(dim, num_experts=e, moe_top_k=2, ff_inner_dim=inner, operations=ops.disable_weight_init, device=dev,
                    dtype=torch.bfloat16).eval()
-    mod.load_state_dict(layer, strict=True)
-    x = H.make_input(n, dim, seed=1).bfloat16().to(dev).view(2, n // 2, dim)
+    g = torch.Generator().manual_seed(0)
+    with torch.no_grad():
+        for name, p in mod.named_parameters():      # weights N(0, 0.02^2), biases five times wider, seeded
+            std = 0.1 if name.endswith("bias") else 0.02
+            p.copy_((torch.randn(p.shape, generator=g, dtype=torch.float32) * std).to(torch.bfloat16))
+    gx = torch.Generator().manual_seed(1)
+    x = torch.randn((n, dim), generator=gx, dtype=torch.float32).bfloat16().to(dev).view(2, n // 2, dim)
     flops = n * (2 * 2 * 2 * dim * inner + 2 * 2 * dim * inner + 2 * dim * e)
 
     def timed(steps, warmup):
@@ -591,7 +594,7 @@ def run_hunyuan3d(args) -> None:
 
 
 def run_dit_body(args) -> None:
-    """Side workload (not the headline): the transformer body of BASELINE config 4, i.e. 16 double-stream and 32
+    """Side workload (not the headline): the transformer body of benchmark configuration 4, i.e. 16 double-stream and 32
     single-stream HiDream blocks (dim 2560, 20 heads x 128, MoE feed-forward on the image tokens), random-init bf16,
     2 x 4096 image tokens + 2 x 384 text tokens (128 T5 + 2 x 128 Llama), one pass = one denoising step without the
     embedders and the final layer.  Timed with the kernels and, on the same modules, as PyTorch composes it."""
@@ -666,7 +669,7 @@ def run_dit_body(args) -> None:
         "metric": "denoising-step body, ms (HiDream-I1 transformer blocks, bf16)", "value": ms, "unit": "ms",
         "n_gpus": 1, "steps": steps, "warmup": 3, "ms_per_step": ms, "higher_is_better": False, "dtype": "bf16",
         "data": "synthetic",
-        "config": {"workload": f"BASELINE config 4 without embedders and final layer: {n_double} double-stream + "
+        "config": {"workload": f"benchmark configuration 4 without embedders and final layer: {n_double} double-stream + "
                                f"{n_single} single-stream blocks, 2 x (4096 image + 384 text) tokens, random-init bf16",
                    "dim": dim, "heads": heads, "head_dim": head_dim, "experts": 4, "top_k": 2},
         "clocks": clocks.summary(),
@@ -689,7 +692,7 @@ def main() -> None:
                          "total with a skewed router (strong scaling); hunyuan3d = the sibling GELU-MLP MoE block "
                          "(one GPU, bf16)")
     ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp8"],
-                    help="bf16 (BASELINE config 2, the default) or per-tensor scaled fp8 e4m3 expert weights (config 3)")
+                    help="bf16 (benchmark configuration 2, the default) or per-tensor scaled fp8 e4m3 expert weights (configuration 3)")
     ap.add_argument("--timeline", action="store_true",
                     help="after the timing, print the kernel timeline of one step on rank 0 to stderr (torch.profiler)")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU oracle and the stock-composition timings (profiling runs)")

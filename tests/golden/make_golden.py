@@ -297,7 +297,7 @@ def blocks(ref_root: str) -> None:
 
 
 if __name__ == "__main__":
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("COMFYUI_ROOT", "ComfyUI")
     main(root)
     hunyuan3d(root)
     attention(root)

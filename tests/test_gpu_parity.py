@@ -210,7 +210,7 @@ def test_full_layer_bf16(M, cuda_device, n, dim, hidden_dim, e):
 
 
 def test_full_layer_bf16_benchmark_size(M, cuda_device):
-    """BASELINE configuration 2: 2 x 4096 tokens, dim 2560, bf16.  Also run-to-run bit reproducibility."""
+    """Benchmark configuration 2: 2 x 4096 tokens, dim 2560, bf16.  Also run-to-run bit reproducibility."""
     layer, x, out, ws = _full_layer_case(M, cuda_device, 8192, 2560, 10240, 4, O.PLAIN)
     ref, ridx, _ = O.moe_layer(x, layer, gate_in_fp32=True)
     idx = ws.topk_idx.cpu().long()
@@ -229,7 +229,7 @@ def test_full_layer_bf16_benchmark_size(M, cuda_device):
 
 
 def test_fp32_config1_inputs(M, cuda_device):
-    """BASELINE configuration 1 (fp32 on the CPU, 4096 tokens) is the truth; the kernels see the same seeded
+    """Benchmark configuration 1 (fp32 on the CPU, 4096 tokens) is the truth; the kernels see the same seeded
     tensors rounded to bf16 and must stay within the bf16 tolerance on identically routed tokens."""
     n, dim, hidden_dim = 4096, 2560, 10240
     layer32 = O.make_layer(dim, hidden_dim, 4, seed=0)
@@ -349,7 +349,7 @@ def test_caller_supplied_routing_with_bad_ids(M, cuda_device):
 
 
 def test_config5_skewed_full_size(M, cuda_device):
-    """BASELINE configuration 5 on one GPU: 8 x 16384 tokens, router skewed so one expert takes ~60 % of the top-1
+    """Benchmark configuration 5 on one GPU: 8 x 16384 tokens, router skewed so one expert takes ~60 % of the top-1
     picks.  The oracle cannot run 131 072 tokens in seconds, so parity uses the independence of rows: a random
     sample of tokens is recomputed by the oracle with the routing the kernels chose, and the routing itself is
     checked against the oracle's fp32 gate on that sample; counts are checked globally."""
