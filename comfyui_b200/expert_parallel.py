@@ -335,6 +335,7 @@ class PeerBuffers:
             plan.peer_recv[r] = base + off_recv
             plan.peer_y[r] = base + off_y
         self.plan = plan
+        self.epoch = 0       # steps taken on these buffers; the flags carry it, so it belongs to the buffers
         # where this rank's partial results go at every rank: that rank's return buffer of this rank's hidden part
         part_bytes = ret_rows * dim * 2
         self.peer_ret = [base + off_ret + place.hidden_part(rank) * part_bytes for base in bases]
@@ -346,6 +347,21 @@ class PeerBuffers:
         off_y = off_recv + _align(cap_rows * dim * es)
         off_ret = off_y + _align(cap_rows * dim * 2)
         return off_recv, off_y, off_ret, off_ret + _align(splits * ret_rows * dim * 2)
+
+    _shared = {}
+
+    @classmethod
+    def shared(cls, place: Placement, rank: int, cap_rows: int, ret_rows: int, dim: int, act_dtype: torch.dtype,
+               device, group) -> "PeerBuffers":
+        """Buffers for this shape, created once and then shared by every layer that asks for them (the layers of a
+        model run one after the other on one stream, and the step order that makes single buffers safe holds across
+        layers just as it does across calls of one layer)."""
+        key = (id(group), place.world, place.n_experts, rank, cap_rows, ret_rows, dim, act_dtype, str(device))
+        got = cls._shared.get(key)
+        if got is None:
+            got = cls.create(place, rank, cap_rows, ret_rows, dim, act_dtype, device, group)
+            cls._shared[key] = got
+        return got
 
     @classmethod
     def create(cls, place: Placement, rank: int, cap_rows: int, ret_rows: int, dim: int, act_dtype: torch.dtype,
@@ -413,7 +429,6 @@ class PeerExpertParallelMoE:
         self.fp8 = self.kernels.fp8
         self.buffers = buffers
         self.max_tokens = max_tokens
-        self.epoch = 0
         self.last_counts = None
         self._state = None
         # gate, plan, dispatch, 2 flags, 2 waits, shared GEMM x2, routed GEMM x2, combine (+ the shared expert's
@@ -427,7 +442,7 @@ class PeerExpertParallelMoE:
         # a token sends at most one slot to a given expert: world * tokens rows per local expert at most
         cap_rows = self.world * cap_tokens * min(2, self.place.experts_per_rank)
         act = torch.float8_e4m3fn if self.fp8 else torch.bfloat16
-        self.buffers = PeerBuffers.create(self.place, self.rank, cap_rows, 2 * cap_tokens, dim, act, device, self.group)
+        self.buffers = PeerBuffers.shared(self.place, self.rank, cap_rows, 2 * cap_tokens, dim, act, device, self.group)
 
     # -- the three phases of a step ---------------------------------------------------------------
     def phase_route(self, x2: torch.Tensor, counts_all: Optional[torch.Tensor] = None, gather=None,
@@ -439,7 +454,7 @@ class PeerExpertParallelMoE:
         dev = x2.device
         self._ensure_buffers(n, dim, dev)
         b = self.buffers
-        self.epoch += 1
+        b.epoch += 1
         idx, w, block_counts, _, _ = M.gate_topk(x2, k.gate_w)
         block_offsets, counts, _ = M.route_plan(block_counts, n, self.n_experts)
         if gather is not None:
@@ -461,7 +476,7 @@ class PeerExpertParallelMoE:
             b.plan, P(x2), P(idx), P(block_offsets), P(counts_all), n, dim, N.FP8_E4M3 if self.fp8 else N.BF16, P(in13),
             P(x_q), P(in13_shared), P(row_map), P(groups[0]), P(groups[1]), P(groups[2]) if self.push else None,
             P(status), S()))
-        N.check("comfy_moe_ep_signal", self.lib.comfy_moe_ep_signal(b.plan, N.EP_ARRIVED, self.epoch, S()))
+        N.check("comfy_moe_ep_signal", self.lib.comfy_moe_ep_signal(b.plan, N.EP_ARRIVED, b.epoch, S()))
         self._state = dict(x2=x2, x_q=x_q, idx=idx, w=w, row_map=row_map, groups=groups, status=status,
                            counts_all=counts_all)
 
@@ -471,7 +486,7 @@ class PeerExpertParallelMoE:
         M, N, k, b, st = self.M, self.N, self.kernels, self.buffers, self._state
         S = M._stream
         st["y_shared"] = y_shared if y_shared is not None else k.shared_expert(st["x_q"] if self.fp8 else st["x2"])
-        N.check("comfy_moe_ep_wait", self.lib.comfy_moe_ep_wait(b.plan, N.EP_ARRIVED, self.epoch, M._ptr(st["status"]), S()))
+        N.check("comfy_moe_ep_wait", self.lib.comfy_moe_ep_wait(b.plan, N.EP_ARRIVED, b.epoch, M._ptr(st["status"]), S()))
         hidden = k.local[0].hidden
         h_ws = getattr(self, "_h_ws", None)
         if h_ws is None or h_ws.shape != (b.cap_rows, hidden) or h_ws.device != b.recv.device:
@@ -484,14 +499,14 @@ class PeerExpertParallelMoE:
         else:
             M.grouped_swiglu(k.local, None, st["groups"][0], st["groups"][1], b.recv, None, status=st["status"],
                              check_status=False, h_perm=h_ws, y_perm=b.y)
-        N.check("comfy_moe_ep_signal", self.lib.comfy_moe_ep_signal(b.plan, N.EP_DONE, self.epoch, S()))
+        N.check("comfy_moe_ep_signal", self.lib.comfy_moe_ep_signal(b.plan, N.EP_DONE, b.epoch, S()))
 
     def phase_combine(self) -> torch.Tensor:
         """After every rank's results are in place: the weighted combine, reading them where they are."""
         M, N, b, st = self.M, self.N, self.buffers, self._state
         P, S = M._ptr, M._stream
         n, dim = st["x2"].shape
-        N.check("comfy_moe_ep_wait", self.lib.comfy_moe_ep_wait(b.plan, N.EP_DONE, self.epoch, P(st["status"]), S()))
+        N.check("comfy_moe_ep_wait", self.lib.comfy_moe_ep_wait(b.plan, N.EP_DONE, b.epoch, P(st["status"]), S()))
         if self.push:
             out = M.combine(b.ret[0], st["row_map"], st["w"], st["y_shared"],
                             y_perm_b=b.ret[1] if self.place.hidden_splits == 2 else None)

@@ -76,6 +76,40 @@ def test_emulated_ranks_on_one_gpu(cuda_device, world, fp8, push):
     assert counts_all.sum(dim=1).tolist() == [2 * t for t in tokens]
 
 
+def test_two_layers_share_the_buffers(cuda_device):
+    """The layers of a model use one set of buffers and one epoch counter, one after the other."""
+    from comfyui_b200 import moe_ops as M
+    from comfyui_b200.expert_parallel import PeerBuffers, PeerExpertParallelMoE, Placement
+
+    dev, world = cuda_device, 2
+    place = Placement(world, E)
+    tokens = [400, 250]
+    xs = [O.make_input(n, DIM, seed=70 + r).bfloat16().to(dev) for r, n in enumerate(tokens)]
+    bufs = PeerBuffers.emulate(place, 2 * sum(tokens), 2 * max(tokens), DIM, torch.bfloat16, dev)
+    mods = []
+    for seed in (0, 1):
+        m = _module(dev)
+        with torch.no_grad():
+            for p in m.parameters():
+                p.mul_(1.0 + 0.25 * seed)
+        mods.append(m)
+    layers = [[PeerExpertParallelMoE(m, buffers=bufs[r], place=place, rank=r) for r in range(world)] for m in mods]
+    with torch.inference_mode():
+        for which in (0, 1, 0, 1):
+            mod, ranks = mods[which], layers[which]
+            counts = [M.route_plan(M.gate_topk(x, mod.gate.weight)[2], x.shape[0], E)[1] for x in xs]
+            counts_all = torch.stack(counts).contiguous()
+            for r in range(world):
+                ranks[r].phase_route(xs[r], counts_all=counts_all)
+            for r in range(world):
+                ranks[r].phase_experts()
+            outs = [ranks[r].phase_combine() for r in range(world)]
+            for r in range(world):
+                ranks[r].check()
+                assert torch.equal(outs[r], mod(xs[r].view(1, -1, DIM)).view(-1, DIM)), f"layer {which} rank {r}"
+    assert bufs[0].epoch == 4 and bufs[1].epoch == 4
+
+
 def test_rank_without_tokens(cuda_device):
     """A rank that owns experts but has no tokens of its own still serves the others (and gets an empty output)."""
     from comfyui_b200 import moe_ops as M
