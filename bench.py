@@ -607,15 +607,29 @@ def run_dit_body(args) -> None:
     n_double, n_single = args.double_blocks, args.single_blocks
     torch.manual_seed(0)
 
+    fp8 = args.dtype == "fp8"
+    operations = ops.disable_weight_init if not fp8 else ops.scaled_fp8_ops(
+        fp8_matrix_mult=True, scale_input=False, override_dtype=torch.float8_e4m3fn)
+
     def build(single):
         cls = M.HiDreamImageSingleTransformerBlock if single else M.HiDreamImageTransformerBlock
-        blk = cls(dim, heads, head_dim, 4, 2, dtype=torch.bfloat16, device=dev, operations=ops.disable_weight_init).eval()
+        blk = cls(dim, heads, head_dim, 4, 2, dtype=torch.bfloat16, device=dev, operations=operations).eval()
         with torch.no_grad():
+            for mod in blk.modules():
+                w = getattr(mod, "weight", None)
+                if isinstance(mod, torch.nn.Linear) and w is not None and w.dtype == torch.float8_e4m3fn:
+                    # scaled fp8 checkpoint convention: s = max|w| / 448, weight = (w / s) in e4m3, scale_weight = s
+                    full = torch.randn(w.shape, device=dev) * 0.02
+                    sc = full.abs().max() / 448.0
+                    w.copy_((full / sc).to(torch.float8_e4m3fn))
+                    mod.scale_weight.fill_(float(sc))
+                    if mod.bias is not None:
+                        mod.bias.copy_((torch.randn(mod.bias.shape, device=dev) * 0.02).to(mod.bias.dtype))
             for name, p in blk.named_parameters():
+                if p.dtype == torch.float8_e4m3fn or name.endswith("scale_weight"):
+                    continue
                 if "rms_norm" in name:
                     p.fill_(1.0)
-                elif name.endswith("bias"):
-                    p.normal_(0.0, 0.02)
                 else:
                     p.normal_(0.0, 0.02)
         return blk
@@ -666,11 +680,12 @@ def run_dit_body(args) -> None:
         finally:
             ops.ENABLE_SM100_KERNELS = True
     print(json.dumps({
-        "metric": "denoising-step body, ms (HiDream-I1 transformer blocks, bf16)", "value": ms, "unit": "ms",
-        "n_gpus": 1, "steps": steps, "warmup": 3, "ms_per_step": ms, "higher_is_better": False, "dtype": "bf16",
+        "metric": "denoising-step body, ms (HiDream-I1 transformer blocks)", "value": ms, "unit": "ms",
+        "n_gpus": 1, "steps": steps, "warmup": 3, "ms_per_step": ms, "higher_is_better": False, "dtype": args.dtype,
         "data": "synthetic",
         "config": {"workload": f"benchmark configuration 4 without embedders and final layer: {n_double} double-stream + "
-                               f"{n_single} single-stream blocks, 2 x (4096 image + 384 text) tokens, random-init bf16",
+                               f"{n_single} single-stream blocks, 2 x (4096 image + 384 text) tokens, random-init "
+                               + ("scaled fp8 e4m3 Linears (fp8 matrix multiplication), bf16 activations" if fp8 else "bf16"),
                    "dim": dim, "heads": heads, "head_dim": head_dim, "experts": 4, "top_k": 2},
         "clocks": clocks.summary(),
         "gpu_bar": {"what": "same modules and weights, sm_100a kernels off: stock PyTorch composition on this GPU",
