@@ -11,10 +11,10 @@ from ctypes import POINTER, Structure, c_char_p, c_float, c_int, c_int32, c_int6
 
 from . import build as _build
 
-ABI_VERSION = 7
+ABI_VERSION = 8
 
 OK, EINVAL, EUNSUPPORTED, ECUDA, ETIMEOUT, EDEVICE, ETOOLARGE = range(7)
-BF16, FP32, FP8_E4M3 = 0, 1, 2
+BF16, FP32, FP8_E4M3, FP16 = 0, 1, 2, 3
 ROW_ALIGN = 128
 TOKENS_PER_BLOCK = 32
 MAX_EXPERTS = 8
@@ -45,6 +45,7 @@ EXPORTS = (
     "comfy_moe_ffn_block",
     "comfy_moe_read_status",
     "comfy_moe_quantize_e4m3",
+    "comfy_moe_stochastic_round_e4m3",
     "comfy_attn_rmsnorm_rope",
     "comfy_moe_ep_dispatch",
     "comfy_moe_ep_signal",
@@ -241,6 +242,7 @@ def load(build_if_missing: bool = False) -> ctypes.CDLL:
     lib.comfy_moe_quantize_e4m3.argtypes = [c_void_p, c_void_p, c_int64, c_void_p, c_void_p]
     lib.comfy_attn_rmsnorm_rope.argtypes = [c_void_p, c_int64, c_void_p, c_float, c_void_p, c_int64, c_int, c_int, c_int,
                                             c_int, c_int, c_int, c_void_p, c_int64, c_int, c_void_p]
+    lib.comfy_moe_stochastic_round_e4m3.argtypes = [c_void_p, c_int, c_void_p, c_int64, c_void_p, c_void_p]
     lib.comfy_moe_ep_signal.argtypes = [POINTER(PeerPlan), c_int, c_uint32, c_void_p]
     lib.comfy_moe_ep_wait.argtypes = [POINTER(PeerPlan), c_int, c_uint32, c_void_p, c_void_p]
     lib.comfy_moe_ep_combine.argtypes = [POINTER(PeerPlan), c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,

@@ -23,6 +23,7 @@ SOURCES = [
     "moe_grouped_gemm_sm100.cu",
     "moe_peer.cu",
     "attn_glue.cu",
+    "weight_ingest.cu",
     "moe_c_api.cu",
 ]
 HEADERS = ["moe_common.cuh", "ptx_sm100.cuh", os.path.join("..", "..", "include", "comfy_b200_moe.h")]

@@ -622,3 +622,19 @@ def rmsnorm_rope(x: torch.Tensor, weight: Optional[torch.Tensor], eps: float, ro
                                           out_row_offset, _stream())
     N.check("comfy_attn_rmsnorm_rope", rc)
     return out
+
+
+# --------------------------------------------------------------------------------------- weight ingest
+def stochastic_round_e4m3(x: torch.Tensor, rand: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """One slice of the reference's stochastic rounding to e4m3: x fp32 / bf16 / fp16 (contiguous), rand the fp16
+    uniforms the reference would draw for it.  Returns the e4m3 tensor (``out`` if given)."""
+    _need_cuda(x, rand, out)
+    codes = {torch.float32: N.FP32, torch.bfloat16: N.BF16, torch.float16: N.FP16}
+    if x.dtype not in codes or not x.is_contiguous() or rand.dtype != torch.float16 or rand.shape != x.shape or \
+            not rand.is_contiguous():
+        raise ValueError("x must be contiguous fp32 / bf16 / fp16 and rand fp16 of the same shape")
+    if out is None:
+        out = torch.empty(x.shape, dtype=_FP8, device=x.device)
+    N.check("comfy_moe_stochastic_round_e4m3",
+            N.load().comfy_moe_stochastic_round_e4m3(_ptr(x), codes[x.dtype], _ptr(rand), x.numel(), _ptr(out), _stream()))
+    return out

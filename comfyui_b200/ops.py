@@ -266,24 +266,62 @@ def scaled_fp8_ops(fp8_matrix_mult=False, scale_input=False, override_dtype=None
     return scaled_fp8_op
 
 
-def stochastic_rounding(value: torch.Tensor, dtype: torch.dtype, seed=None) -> torch.Tensor:
-    """Round ``value`` to ``dtype``; for e4m3 each element goes to one of its two neighbouring representable
-    values with probability proportional to proximity (what ``comfy/float.py:50-67`` provides for LoRA-baked
-    fp8 weights).  Other dtypes: a plain cast."""
-    if dtype != FP8:
-        return value.to(dtype)
-    g = torch.Generator(device=value.device)
-    g.manual_seed(0 if seed is None else int(seed))
-    v = value.float().clamp(-448.0, 448.0)
-    mag = v.abs()
-    # spacing of e4m3 at |v|: 2^(floor(log2|v|) - 3), never below the subnormal step 2^-9
-    exp = torch.floor(torch.log2(mag.clamp_min(2.0 ** -9))).clamp(min=-6.0)
-    step = torch.exp2(exp - 3.0)
-    lo = torch.floor(mag / step) * step
-    frac = (mag - lo) / step
-    up = torch.rand(v.shape, generator=g, device=v.device, dtype=torch.float32) < frac
-    out = torch.where(up, lo + step, lo).clamp(max=448.0)
-    return (torch.sign(v) * out).to(dtype)
+_FP8_FORMATS = {torch.float8_e4m3fn: (4, 3, 7), torch.float8_e5m2: (5, 2, 15)}     # exponent bits, mantissa bits, bias
+
+
+def _stochastic_round_fp8_slice(x: torch.Tensor, dtype: torch.dtype, generator) -> torch.Tensor:
+    """One slice of ``comfy/float.py:14-46``: every step is an fp16 tensor operation, as in the reference (so each
+    result is rounded to fp16 before the next step), the random offsets are fp16 uniforms drawn from ``generator``."""
+    e_bits, m_bits, bias = _FP8_FORMATS[dtype]
+    x = x.half()
+    sign = torch.sign(x)
+    mag = x.abs()
+    sign = torch.where(mag == 0, 0, sign)
+    exponent = torch.clamp(torch.floor(torch.log2(mag)) + bias, 0, 2 ** e_bits - 1)
+    normal = ~(exponent == 0)
+    scaled = torch.where(normal,
+                         (mag / (2.0 ** (exponent - bias)) - 1.0) * (2 ** m_bits),
+                         mag / (2.0 ** (-bias + 1 - m_bits)))
+    scaled += torch.rand(scaled.size(), dtype=scaled.dtype, layout=scaled.layout, device=scaled.device,
+                         generator=generator)
+    frac = scaled.floor() / (2 ** m_bits)
+    sign *= torch.where(normal, (2.0 ** (exponent - bias)) * (1.0 + frac), (2.0 ** (-bias + 1)) * frac)
+    info = torch.finfo(dtype)
+    torch.clamp(sign, min=info.min, max=info.max, out=sign)
+    return sign
+
+
+def stochastic_rounding(value: torch.Tensor, dtype: torch.dtype, seed=0) -> torch.Tensor:
+    """``comfy/float.py:50-67``: fp8 targets are rounded stochastically (each element to one of its two neighbouring
+    representable values, the upper one with probability equal to its fractional position), in row slices of about
+    4096 x 4096 elements that draw from one generator seeded with ``seed``; every other dtype is a plain cast.
+    On a B200 the e4m3 case runs as one fused kernel per slice, fed the same random numbers."""
+    if dtype not in _FP8_FORMATS:
+        return value.to(dtype=dtype)
+    generator = torch.Generator(device=value.device)
+    generator.manual_seed(0 if seed is None else int(seed))
+    output = torch.empty_like(value, dtype=dtype)
+    num_slices = max(1, (value.numel() / (4096 * 4096)))
+    slice_size = max(1, round(value.shape[0] / num_slices))
+    for i in range(0, value.shape[0], slice_size):
+        part = value[i:i + slice_size]
+        fast = _stochastic_round_kernel(part, dtype, generator, output[i:i + slice_size])
+        if fast is None:
+            output[i:i + slice_size].copy_(_stochastic_round_fp8_slice(part, dtype, generator))
+    return output
+
+
+def _stochastic_round_kernel(part: torch.Tensor, dtype: torch.dtype, generator, out: torch.Tensor):
+    """The fused kernel for one slice, or None when the slice is not eligible (then the composition above runs)."""
+    if not ENABLE_SM100_KERNELS or dtype != FP8 or not part.is_cuda or not model_management.is_sm100(part.device):
+        return None
+    if part.dtype not in (torch.float32, torch.bfloat16, torch.float16) or not part.is_contiguous() or \
+            not out.is_contiguous() or part.numel() == 0:
+        return None
+    from . import moe_ops
+
+    rand = torch.rand(part.size(), dtype=torch.float16, device=part.device, generator=generator)
+    return moe_ops.stochastic_round_e4m3(part, rand, out)
 
 
 def pick_operations(weight_dtype, compute_dtype, load_device=None, disable_fast_fp8=False, fp8_optimizations=False,

@@ -26,7 +26,7 @@
 extern "C" {
 #endif
 
-#define COMFY_MOE_ABI_VERSION 7
+#define COMFY_MOE_ABI_VERSION 8
 
 /* Return codes. */
 #define COMFY_MOE_OK 0
@@ -41,6 +41,7 @@ extern "C" {
 #define COMFY_MOE_BF16 0
 #define COMFY_MOE_FP32 1
 #define COMFY_MOE_FP8_E4M3 2
+#define COMFY_MOE_FP16 3
 
 /* Rows of every routed expert's block start on a multiple of this in the permuted layout. */
 #define COMFY_MOE_ROW_ALIGN 128
@@ -300,6 +301,16 @@ int comfy_attn_rmsnorm_rope(const void* x, int64_t ld_x, const void* weight, flo
  * permutation runs (the expert-parallel path quantises the shared expert's input beside the routing kernels).
  */
 int comfy_moe_quantize_e4m3(const void* x, const float* scale, int64_t n_elements, void* out, void* stream);
+
+/* ---- weight ingest: stochastic rounding to e4m3 (comfy/float.py:3-46) ------------------------------------------
+ * What scaled_fp8_ops.Linear.set_weight (comfy/ops.py:418-426) applies to a LoRA-patched weight after dividing it by
+ * scale_weight: manual_stochastic_round_to_float8 on one slice.  x: fp32, bf16 or fp16 (x_dtype), rand_fp16: the
+ * uniform [0, 1) numbers the reference draws with torch.rand(..., dtype=float16, generator=...) for the slice, out:
+ * e4m3 bytes.  Every fp16 rounding of the reference's tensor operations is reproduced, so the same random numbers give
+ * the same bytes.
+ */
+int comfy_moe_stochastic_round_e4m3(const void* x, int x_dtype, const void* rand_fp16, int64_t n_elements, void* out,
+                                    void* stream);
 
 /* ---- expert parallelism over peer memory (one process per GPU, NVLink peer access) ---------------------------
  * No counterpart in the reference (it runs on one GPU).  Tokens stay with their rank; expert e is computed by rank

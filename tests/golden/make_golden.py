@@ -296,9 +296,44 @@ def blocks(ref_root: str) -> None:
     print("wrote", path, os.path.getsize(path), "bytes")
 
 
+def rounding_input(dtype):
+    """Seeded tensor with the edge cases of the stochastic rounding in its first row."""
+    g = torch.Generator().manual_seed(11)
+    v = (torch.randn((96, 160), generator=g) * 3).to(dtype)
+    edge = [0.0, -0.0, 448.0, 500.0, -1000.0, 2.0 ** -9, 2.0 ** -10, 1.999, 0.9995, 255.9, -0.0625, 3.0e-3, 7.0e4,
+            float("inf"), -float("inf"), 15.99]
+    v[0, :len(edge)] = torch.tensor(edge).to(dtype)
+    return v
+
+
+def weight_rounding(ref_root: str) -> None:
+    """comfy.float.stochastic_rounding (comfy/float.py:50-67) and scaled_fp8_ops.Linear.set_weight
+    (comfy/ops.py:418-426) on seeded tensors with the CPU generator."""
+    import comfy.float
+    import comfy.ops
+
+    out = {}
+    for name, dtype in (("fp32", torch.float32), ("bf16", torch.bfloat16)):
+        v = rounding_input(dtype)
+        for tname, target in (("e4m3", torch.float8_e4m3fn), ("e5m2", torch.float8_e5m2)):
+            for seed in (0, 7):
+                q = comfy.float.stochastic_rounding(v.clone(), target, seed=seed)
+                out[f"{name}/{tname}/seed{seed}"] = q.view(torch.uint8).numpy()
+    ops = comfy.ops.scaled_fp8_ops(fp8_matrix_mult=True, scale_input=False, override_dtype=torch.float8_e4m3fn)
+    lin = ops.Linear(160, 96, bias=False, dtype=torch.bfloat16, device="cpu")
+    lin.scale_weight.data.fill_(0.0123)
+    lin.set_weight(rounding_input(torch.float32), seed=3)
+    out["set_weight/seed3"] = lin.weight.data.view(torch.uint8).numpy()
+    out["torch_version"] = np.array([torch.__version__])
+    path = os.path.join(HERE, "weight_rounding.npz")
+    np.savez_compressed(path, **out)
+    print("wrote", path, os.path.getsize(path), "bytes")
+
+
 if __name__ == "__main__":
     root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("COMFYUI_ROOT", "ComfyUI")
     main(root)
+    weight_rounding(root)
     hunyuan3d(root)
     attention(root)
     blocks(root)
