@@ -400,6 +400,8 @@ class PeerExpertParallelMoE:
     The three ``phase_*`` methods are the step cut at its two flag waits, so a test can drive several ranks that
     live on one GPU in lock step."""
 
+    _tensors = {}       # scratch tensors by shape, shared by all layers (see _scratch)
+
     def __init__(self, module, group=None, *, max_tokens: Optional[int] = None, buffers: Optional[PeerBuffers] = None,
                  place: Optional[Placement] = None, rank: Optional[int] = None, push_results: Optional[bool] = None):
         import os
@@ -431,6 +433,8 @@ class PeerExpertParallelMoE:
         self.max_tokens = max_tokens
         self.last_counts = None
         self._state = None
+        self._scratch_cache = {}
+        self._h_ws = None
         # gate, plan, dispatch, 2 flags, 2 waits, shared GEMM x2, routed GEMM x2, combine (+ the shared expert's
         # input quantiser for fp8 when it runs beside the routing kernels)
         self.launches_per_step = 12 + (1 if (self.fp8 and self.front_sms > 0) else 0)
@@ -444,84 +448,173 @@ class PeerExpertParallelMoE:
         act = torch.float8_e4m3fn if self.fp8 else torch.bfloat16
         self.buffers = PeerBuffers.shared(self.place, self.rank, cap_rows, 2 * cap_tokens, dim, act, device, self.group)
 
-    # -- the three phases of a step ---------------------------------------------------------------
-    def phase_route(self, x2: torch.Tensor, counts_all: Optional[torch.Tensor] = None, gather=None,
-                    want_xq: bool = True):
-        """Gate, plan, histogram exchange, dispatch, "arrived" flag.  ``gather(counts) -> [world, E]`` replaces the
-        collective in single-GPU emulation."""
-        M, N, k = self.M, self.N, self.kernels
-        n, dim = x2.shape
-        dev = x2.device
-        self._ensure_buffers(n, dim, dev)
-        b = self.buffers
-        b.epoch += 1
-        idx, w, block_counts, _, _ = M.gate_topk(x2, k.gate_w)
-        block_offsets, counts, _ = M.route_plan(block_counts, n, self.n_experts)
-        if gather is not None:
-            counts_all = gather(counts)
-        elif counts_all is None:
-            counts_all = torch.empty((self.world, self.n_experts), dtype=torch.int32, device=dev)
-            dist.all_gather_into_tensor(counts_all.view(-1), counts.contiguous(), group=self.group)
-        row_map = torch.empty((n, 2), dtype=torch.int32, device=dev)
+    # -- per-shape scratch: every tensor and every ctypes argument of a step, made once -----------------
+    def _scratch(self, n: int, dim: int, device):
+        key = (n, dim, str(device))
+        sc = self._scratch_cache.get(key)
+        if sc is not None:
+            return sc
+        import ctypes
+
+        N, k, b = self.N, self.kernels, self.buffers
         if 2 * n > b.ret_rows:
             raise ValueError(f"{n} tokens do not fit the return buffers ({b.ret_rows} rows); pass max_tokens")
-        n_groups = self.place.experts_per_rank * (self.world if self.push else 1)
-        groups = torch.zeros((3, n_groups), dtype=torch.int32, device=dev)      # start, count, output row shift
-        status = torch.zeros((2,), dtype=torch.int32, device=dev)
-        x_q = torch.empty((n, dim), dtype=torch.float8_e4m3fn, device=dev) if (self.fp8 and want_xq) else None
-        in13 = k.local[0].scale_in13 if self.fp8 else None
-        in13_shared = k.shared.scale_in13 if self.fp8 else None
-        P, S = M._ptr, M._stream
-        N.check("comfy_moe_ep_dispatch", self.lib.comfy_moe_ep_dispatch(
-            b.plan, P(x2), P(idx), P(block_offsets), P(counts_all), n, dim, N.FP8_E4M3 if self.fp8 else N.BF16, P(in13),
-            P(x_q), P(in13_shared), P(row_map), P(groups[0]), P(groups[1]), P(groups[2]) if self.push else None,
-            P(status), S()))
-        N.check("comfy_moe_ep_signal", self.lib.comfy_moe_ep_signal(b.plan, N.EP_ARRIVED, b.epoch, S()))
-        self._state = dict(x2=x2, x_q=x_q, idx=idx, w=w, row_map=row_map, groups=groups, status=status,
-                           counts_all=counts_all)
+        e, world = self.n_experts, self.world
+        i32 = dict(dtype=torch.int32, device=device)
+        n_blocks = max((n + N.TOKENS_PER_BLOCK - 1) // N.TOKENS_PER_BLOCK, 1)
+        n_groups = self.place.experts_per_rank * (world if self.push else 1)
+        act = torch.float8_e4m3fn if self.fp8 else torch.bfloat16
+        sc = type("Scratch", (), {})()
+        # the tensors are shared by every layer of the same shape on these buffers (layers run one after the other on
+        # one stream); what is per layer are the weight structs further down
+        hidden = k.local[0].hidden
+        tkey = (id(b), n, dim, e, world, n_groups, k.shared.hidden, hidden, self.fp8, str(device))
+        t = PeerExpertParallelMoE._tensors.get(tkey)
+        if t is None:
+            t = dict(
+                idx=torch.empty((n, 2), **i32), w=torch.empty((n, 2), dtype=torch.float32, device=device),
+                block_counts=torch.empty((n_blocks, e), **i32), block_offsets=torch.empty((n_blocks, e), **i32),
+                counts=torch.empty((e,), **i32), offsets=torch.empty((e + 1,), **i32),
+                counts_all=torch.empty((world, e), **i32), row_map=torch.empty((n, 2), **i32),
+                groups=torch.zeros((3, n_groups), **i32),              # start, count, output row shift
+                status=torch.zeros((2,), **i32),                        # [0] device status, [1] near-tie count
+                x_q=torch.empty((n, dim), dtype=act, device=device) if self.fp8 else None,
+                h_shared=torch.empty((max(n, 1), k.shared.hidden), dtype=act, device=device),
+                y_shared=torch.empty((max(n, 1), dim), dtype=torch.bfloat16, device=device),
+                h_ws=torch.empty((b.cap_rows, hidden), dtype=b.act_dtype, device=b.recv.device))
+            PeerExpertParallelMoE._tensors[tkey] = t
+        for name, value in t.items():
+            setattr(sc, name, value)
+        self._h_ws = t["h_ws"]
+        P = lambda t: None if t is None else ctypes.c_void_p(t.data_ptr())                    # noqa: E731
+        sc.p = {name: P(getattr(sc, name)) for name in ("idx", "w", "block_counts", "block_offsets", "counts",
+                                                        "offsets", "counts_all", "row_map", "status", "x_q",
+                                                        "h_shared", "y_shared")}
+        sc.p["near"] = ctypes.c_void_p(sc.status.data_ptr() + 4)
+        sc.p["g_start"], sc.p["g_count"], sc.p["g_shift"] = (P(sc.groups[i]) for i in range(3))
+        sc.p["recv"], sc.p["y"], sc.p["h_ws"] = P(b.recv), P(b.y), P(self._h_ws)
+        sc.p["ret0"] = P(b.ret[0])
+        sc.p["ret1"] = P(b.ret[1]) if self.place.hidden_splits == 2 else None
+        sc.p["gate_w"] = P(k.gate_w)
+        sc.gate_dtype = N.BF16 if k.gate_w.dtype == torch.bfloat16 else N.FP32
+        sc.p["in13"] = P(k.local[0].scale_in13) if self.fp8 else None
+        sc.p["in13_shared"] = P(k.shared.scale_in13) if self.fp8 else None
+        # weights: the shared expert (all SMs, and on all but front_sms), the local experts once per group
+        sc.shared = k.shared.struct()
+        sc.shared_limited = k.shared.struct()
+        sc.shared_limited.max_sms = max(self._sm_count(device) - self.front_sms, 2) if self.front_sms > 0 else 0
+        per_group = [pack for pack in k.local for _ in range(world if self.push else 1)]
+        sc.group_weights = (N.FfnWeights * len(per_group))()
+        for i, pack in enumerate(per_group):
+            pack.fill(sc.group_weights[i])
+        sc.y_out = (ctypes.c_void_p * len(per_group))(*[int(p) for p in b.peer_ret * len(k.local)]) if self.push else None
+        sc.n_groups = len(per_group)
+        self._scratch_cache[key] = sc
+        return sc
 
-    def phase_experts(self, y_shared: Optional[torch.Tensor] = None):
+    @staticmethod
+    def _stream_ptr():
+        import ctypes
+
+        return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    def _shared_expert(self, sc, x_in: torch.Tensor, n: int, dim: int, limited: bool):
+        import ctypes
+
+        N = self.N
+        w = sc.shared_limited if limited else sc.shared
+        N.check("comfy_moe_grouped_swiglu", self.lib.comfy_moe_grouped_swiglu(
+            N.FP8_E4M3 if self.fp8 else N.BF16, 0, None, ctypes.byref(w), None, None, 0, n, dim, None, None, None,
+            ctypes.c_void_p(x_in.data_ptr()), sc.p["h_shared"], sc.p["y_shared"], sc.p["status"], self._stream_ptr()))
+
+    # -- the three phases of a step ---------------------------------------------------------------
+    def phase_route(self, x2: torch.Tensor, counts_all: Optional[torch.Tensor] = None, want_xq: bool = True):
+        """Gate, plan, histogram exchange, dispatch, "arrived" flag.  ``counts_all`` [world, E] replaces the
+        collective in single-GPU emulation."""
+        import ctypes
+
+        N, lib = self.N, self.lib
+        n, dim = x2.shape
+        self._ensure_buffers(n, dim, x2.device)
+        b = self.buffers
+        sc = self._scratch(n, dim, x2.device)
+        p = sc.p
+        b.epoch += 1
+        sc.status.zero_()
+        S = self._stream_ptr()
+        px = ctypes.c_void_p(x2.data_ptr())
+        if n > 0:
+            N.check("comfy_moe_gate_topk", lib.comfy_moe_gate_topk(px, p["gate_w"], sc.gate_dtype, n, dim, self.n_experts,
+                                                                  2, p["idx"], p["w"], p["block_counts"], p["near"], None,
+                                                                  1e-6, S))
+        N.check("comfy_moe_route_plan", lib.comfy_moe_route_plan(p["block_counts"], n, self.n_experts,
+                                                                 p["block_offsets"], p["counts"], p["offsets"], S))
+        if counts_all is not None:
+            sc.counts_all.copy_(counts_all)
+        else:
+            dist.all_gather_into_tensor(sc.counts_all.view(-1), sc.counts, group=self.group)
+        N.check("comfy_moe_ep_dispatch", lib.comfy_moe_ep_dispatch(
+            b.plan, px, p["idx"], p["block_offsets"], p["counts_all"], n, dim, N.FP8_E4M3 if self.fp8 else N.BF16,
+            p["in13"], p["x_q"] if want_xq else None, p["in13_shared"], p["row_map"], p["g_start"], p["g_count"],
+            p["g_shift"] if self.push else None, p["status"], S))
+        N.check("comfy_moe_ep_signal", lib.comfy_moe_ep_signal(b.plan, N.EP_ARRIVED, b.epoch, S))
+        self._state = (sc, x2)
+
+    def phase_experts(self, shared_done: bool = False):
         """Shared expert on the local tokens (unless the caller already ran it beside the routing kernels), then,
         after every rank's rows arrived, the local routed experts."""
-        M, N, k, b, st = self.M, self.N, self.kernels, self.buffers, self._state
-        S = M._stream
-        st["y_shared"] = y_shared if y_shared is not None else k.shared_expert(st["x_q"] if self.fp8 else st["x2"])
-        N.check("comfy_moe_ep_wait", self.lib.comfy_moe_ep_wait(b.plan, N.EP_ARRIVED, b.epoch, M._ptr(st["status"]), S()))
-        hidden = k.local[0].hidden
-        h_ws = getattr(self, "_h_ws", None)
-        if h_ws is None or h_ws.shape != (b.cap_rows, hidden) or h_ws.device != b.recv.device:
-            h_ws = torch.empty((b.cap_rows, hidden), dtype=b.act_dtype, device=b.recv.device)
-            self._h_ws = h_ws
+        N, lib, b = self.N, self.lib, self.buffers
+        sc, x2 = self._state
+        p = sc.p
+        n, dim = x2.shape
+        if not shared_done and n > 0:
+            self._shared_expert(sc, sc.x_q if self.fp8 else x2, n, dim, limited=False)
+        S = self._stream_ptr()
+        N.check("comfy_moe_ep_wait", lib.comfy_moe_ep_wait(b.plan, N.EP_ARRIVED, b.epoch, p["status"], S))
+        act = N.FP8_E4M3 if self.fp8 else N.BF16
         if self.push:
-            packs = [pack for pack in k.local for _ in range(self.world)]        # group (j, s) uses expert j's weights
-            M.grouped_swiglu_scatter(packs, st["groups"][0], st["groups"][1], b.recv, h_ws,
-                                     b.peer_ret * len(k.local), st["groups"][2], b.ret_rows, st["status"])
+            N.check("comfy_moe_grouped_swiglu_scatter", lib.comfy_moe_grouped_swiglu_scatter(
+                act, sc.n_groups, sc.group_weights, p["g_start"], p["g_count"], b.cap_rows, dim, p["recv"], p["h_ws"],
+                sc.y_out, p["g_shift"], b.ret_rows, p["status"], S))
         else:
-            M.grouped_swiglu(k.local, None, st["groups"][0], st["groups"][1], b.recv, None, status=st["status"],
-                             check_status=False, h_perm=h_ws, y_perm=b.y)
-        N.check("comfy_moe_ep_signal", self.lib.comfy_moe_ep_signal(b.plan, N.EP_DONE, b.epoch, S()))
+            N.check("comfy_moe_grouped_swiglu", lib.comfy_moe_grouped_swiglu(
+                act, sc.n_groups, sc.group_weights, None, p["g_start"], p["g_count"], b.cap_rows, 0, dim, p["recv"],
+                p["h_ws"], p["y"], None, None, None, p["status"], S))
+        N.check("comfy_moe_ep_signal", lib.comfy_moe_ep_signal(b.plan, N.EP_DONE, b.epoch, S))
 
     def phase_combine(self) -> torch.Tensor:
-        """After every rank's results are in place: the weighted combine, reading them where they are."""
-        M, N, b, st = self.M, self.N, self.buffers, self._state
-        P, S = M._ptr, M._stream
-        n, dim = st["x2"].shape
-        N.check("comfy_moe_ep_wait", self.lib.comfy_moe_ep_wait(b.plan, N.EP_DONE, b.epoch, P(st["status"]), S()))
-        if self.push:
-            out = M.combine(b.ret[0], st["row_map"], st["w"], st["y_shared"],
-                            y_perm_b=b.ret[1] if self.place.hidden_splits == 2 else None)
+        """After every rank's results are in place: the weighted combine (local for the push variant of the return
+        path, reading the owners' result buffers for the pull variant)."""
+        import ctypes
+
+        N, lib, b = self.N, self.lib, self.buffers
+        sc, x2 = self._state
+        p = sc.p
+        n, dim = x2.shape
+        S = self._stream_ptr()
+        N.check("comfy_moe_ep_wait", lib.comfy_moe_ep_wait(b.plan, N.EP_DONE, b.epoch, p["status"], S))
+        out = torch.empty((n, dim), dtype=torch.bfloat16, device=x2.device)
+        po = ctypes.c_void_p(out.data_ptr())
+        if n == 0:
+            pass
+        elif not self.push:
+            N.check("comfy_moe_ep_combine", lib.comfy_moe_ep_combine(b.plan, p["idx"], p["row_map"], p["w"],
+                                                                    p["y_shared"], n, dim, po, S))
+        elif p["ret1"] is not None:
+            N.check("comfy_moe_combine_partials", lib.comfy_moe_combine_partials(p["ret0"], p["ret1"], p["row_map"],
+                                                                                p["w"], p["y_shared"], n, dim, po, S))
         else:
-            out = torch.empty((n, dim), dtype=torch.bfloat16, device=st["x2"].device)
-            N.check("comfy_moe_ep_combine", self.lib.comfy_moe_ep_combine(
-                b.plan, P(st["idx"]), P(st["row_map"]), P(st["w"]), P(st["y_shared"]), n, dim, P(out), S()))
-        self.last_status = st["status"]
-        self._last_counts_dev = st["counts_all"]
+            N.check("comfy_moe_combine", lib.comfy_moe_combine(p["ret0"], p["row_map"], p["w"], p["y_shared"], n, dim,
+                                                              po, S))
+        self.last_status = sc.status
+        self._last_counts_dev = sc.counts_all
         return out
 
     def __call__(self, x: torch.Tensor) -> torch.Tensor:
         shape = x.shape
         x2 = x.reshape(-1, shape[-1])
-        if self.front_sms <= 0:
+        n, dim = x2.shape
+        if self.front_sms <= 0 or n == 0:
             self.phase_route(x2)
             self.phase_experts()
             return self.phase_combine().view(shape)
@@ -529,18 +622,21 @@ class PeerExpertParallelMoE:
         # the gate, the histogram all-gather and the dispatch kernel (NVLink-bound) run beside it on the SMs left
         # free, and the routed experts start when both are done.  For fp8 its input is quantised by a kernel of its
         # own first (the dispatch kernel's quantised copy would come too late).
+        self._ensure_buffers(n, dim, x2.device)
+        sc = self._scratch(n, dim, x2.device)
         main = torch.cuda.current_stream()
         if self._side is None:
             self._side = torch.cuda.Stream(device=x2.device)
         side = self._side
         side.wait_stream(main)
         with torch.cuda.stream(side):
-            xs = self.M.quantize_e4m3(x2, self.kernels.shared.scale_in13) if self.fp8 else x2
-            y_shared = self.kernels.shared_expert(xs, max_sms=self._sm_count(x2.device) - self.front_sms)
+            if self.fp8:
+                self.N.check("comfy_moe_quantize_e4m3", self.lib.comfy_moe_quantize_e4m3(
+                    x2.data_ptr(), sc.p["in13_shared"], x2.numel(), sc.p["x_q"], self._stream_ptr()))
+            self._shared_expert(sc, sc.x_q if self.fp8 else x2, n, dim, limited=True)
         self.phase_route(x2, want_xq=False)
         main.wait_stream(side)
-        y_shared.record_stream(main)
-        self.phase_experts(y_shared)
+        self.phase_experts(shared_done=True)
         return self.phase_combine().view(shape)
 
     def _sm_count(self, device) -> int:
