@@ -212,3 +212,31 @@ def test_peer_buffer_layout_and_plan():
             assert pb.peer_ret == [b + off_ret + part * ret * dim * 2 for b in bases]
         # fp8 activations halve the receive buffer only
         assert PeerBuffers.layout(cap, ret, dim, torch.float8_e4m3fn, splits)[1] == off_recv + cap * dim
+
+
+def test_receive_layout_of_both_transports_agree():
+    """The NCCL transport plans the receive buffer on the host (exchange_plan); the peer-memory transport's dispatch
+    kernel derives a row's place from the all-gathered histograms alone.  Both are "local experts in order, each
+    holding the rows of source 0, 1, ..."; this restates the kernel's formula and checks it against the host plan."""
+    from comfyui_b200.expert_parallel import Placement, exchange_plan
+
+    def kernel_row_base(counts, place, q, e, source):          # recv_row_base of csrc/moe_peer.cu
+        row = 0
+        for f in range(e):
+            if q in place.owners(f):
+                row += sum(counts[s][f] for s in range(place.world))
+        return row + sum(counts[s][e] for s in range(source))
+
+    g = torch.Generator().manual_seed(0)
+    for world in (2, 4, 8):
+        place = Placement(world, 4)
+        counts = torch.randint(0, 500, (world, 4), generator=g).tolist()
+        counts[1] = [0, 0, 0, 0]                                # a rank without tokens
+        for rank in range(world):
+            recv_start, recv_rows, group_start, group_count = exchange_plan(counts, rank, place)
+            for j, e in enumerate(place.local_experts(rank)):
+                assert group_start[j] == kernel_row_base(counts, place, rank, e, 0)
+                assert group_count[j] == sum(counts[s][e] for s in range(world))
+                for s in range(world):
+                    assert recv_start[j][s] == kernel_row_base(counts, place, rank, e, s)
+            assert recv_rows == sum(sum(counts[s][e] for s in range(world)) for e in place.local_experts(rank))
