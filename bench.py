@@ -247,7 +247,16 @@ def run_gpu_arm(args) -> None:
 
         # default: rows move over peer memory inside the kernels; COMFY_B200_EP_TRANSPORT=nccl selects the
         # host-planned NCCL exchange (bf16 only)
-        if os.environ.get("COMFY_B200_EP_TRANSPORT", "peer") == "nccl":
+        transport = os.environ.get("COMFY_B200_EP_TRANSPORT", "peer")
+        if transport != "nccl":
+            try:        # the same answer on every rank: a missing module, not a failed rendezvous
+                import torch.distributed._symmetric_memory as symm_mem
+
+                symm_mem.empty, symm_mem.rendezvous
+            except (ImportError, AttributeError):
+                transport = "nccl"
+                os.environ["COMFY_B200_EP_TRANSPORT"] = "nccl"     # workload_config() names the transport used
+        if transport == "nccl":
             runner = ExpertParallelMoE(module, dist.group.WORLD)
         else:
             runner = PeerExpertParallelMoE(module, dist.group.WORLD, max_tokens=n)
