@@ -10,17 +10,20 @@ live on another GPU.
   G = 2E -> expert e lives on ranks 2e and 2e+1, each holding one half of the hidden dimension (rows of w1/w3,
   columns of w2, passed to the kernels as strided views without copying); the two partial outputs are summed by the
   token's owner.
-* One exchange each way.  After the local gate / plan / permutation every rank all-gathers its E-bin histogram
-  (the one host synchronisation of the call, like the reference's ``bincount().cpu()``), then rows travel as
-  point-to-point transfers batched into one NCCL group (an all-to-all with exact, per-pair row counts).  The
-  permutation kernel already wrote the rows grouped by expert, i.e. by destination, so the send side needs no
-  packing; received rows land in local HBM ordered (local expert, source rank), which the grouped GEMM consumes in
-  place as one row range per local expert.  Results return the same way and the combine kernel reads them through
-  the row map it already has.  No kernel reads peer memory.
+* One exchange each way, with two transports:
 
-``ExpertParallelMoE`` contains only this host logic.  The arithmetic is delegated to a ``kernels`` object:
-``CudaKernels`` (the sm_100a kernels through the C ABI) in production; the CPU tests plug in a stand-in so the
-exchange logic can run under gloo.
+  ``PeerExpertParallelMoE`` (the default of ``bench.py``): every rank's receive and return buffers live in symmetric
+  memory mapped into all peers; the dispatch kernel writes each routed row straight into its expert's rank, the expert
+  GEMM writes each result straight back into the token owner's return buffer, epoch flags in peer memory order the
+  steps, and the only collective is an NCCL all-gather of the E-bin histograms.  No host synchronisation.
+
+  ``ExpertParallelMoE``: the histograms are all-gathered and read on the host (one synchronisation per call, like the
+  reference's ``bincount().cpu()``), then rows travel as point-to-point transfers batched into one NCCL group (an
+  all-to-all with exact per-pair row counts).  The permutation kernel already wrote the rows grouped by expert, i.e.
+  by destination, so the send side needs no packing; received rows land in local HBM ordered (local expert, source
+  rank), which the grouped GEMM consumes in place.  Its arithmetic is delegated to a ``kernels`` object: ``CudaKernels``
+  (the sm_100a kernels through the C ABI) in production; the CPU tests plug in a stand-in so the exchange logic can
+  run under gloo.
 """
 from __future__ import annotations
 
