@@ -331,6 +331,18 @@ def run_gpu_arm(args) -> None:
             "layer_tflops": FLOPS_PER_TOKEN * n * world / (ms_step * 1e-3) / 1e12,
             "layer_frac_of_nominal": FLOPS_PER_TOKEN * n / (ms_step * 1e-3) / 1e12 / (4500.0 if fp8 else 2250.0),
         }
+        if world > 1:
+            # no per-kernel timing in the multi-GPU loop: the grouped GEMM's FLOPs per GPU over the WHOLE step (routing,
+            # exchange, flag waits and combine included), i.e. a lower bound on what the kernel itself reaches
+            peak = peaks["tflops_sustained"] * (2.0 if fp8 else 1.0)
+            achieved = FLOPS_PER_TOKEN_GEMM * n / (ms_step * 1e-3) / 1e12
+            line["roofline"] = {
+                "bound": "tensor", "kernel": "grouped_gemm_kernel (per GPU; time = the whole expert-parallel step)",
+                "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                "peak_source": f"{peaks['source']}: sustained cuBLAS bf16 (burst {peaks['tflops_burst']})"
+                               + (" x 2 for fp8" if fp8 else ""),
+                "frac_of_nominal": achieved / (4500.0 if fp8 else 2250.0), "traffic": None,
+            }
         if config5:
             # realised routing: slots per expert over all GPUs, and the rows each GPU's routed experts process
             if world > 1:
