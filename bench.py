@@ -7,13 +7,18 @@
 A step is one call of the layer (gate -> plan -> permute -> grouped SwiGLU GEMM x2 -> combine, shared expert
 included) on synthetic data: dim 2560, 4 routed experts of hidden 6912 (top-2), shared expert of hidden 3584,
 bf16, 8192 tokens per GPU, weights N(0, 0.02^2), inputs N(0, 1), seeded.  With N > 1 the routed experts are
-expert-parallel (NCCL all-to-all dispatch and combine), every rank owns 8192 tokens (weak scaling) and runs the
-shared expert on them.
+expert-parallel (rows dispatched and results returned by the kernels themselves over NVLink peer memory; the one
+collective is an NCCL all-gather of the routing histograms), every rank owns 8192 tokens (weak scaling) and runs
+the shared expert on them.
 
 One JSON line is printed by rank 0.  `value` is measured with the inputs resident in HBM; `e2e` is the same
 metric through the module call with pinned-host input and output copies inside the timed region; `roofline`
 describes the grouped GEMM (both passes) against the measured bf16 tensor peak; `cpu_baseline` is the CPU
-oracle (a restatement of the reference's PyTorch code) timed on this machine's host cores.
+oracle (a restatement of the reference's PyTorch code) timed on this machine's host cores.  After the headline
+loop, and outside its timed region, the default run adds sub-objects to the same line: `sustained` (the same
+loop for more than a second, at the power-capped clock), `fp8` (benchmark configuration 3, same measurements),
+`config5` (131 072 tokens in total, skewed router, strong scaling) and, with N > 1, `ep_parity` (every rank
+compares the expert-parallel output of its tokens with the single-GPU layer).
 """
 from __future__ import annotations
 
@@ -105,10 +110,19 @@ class ClockSampler:
 
 
 # ------------------------------------------------------------------------------------------ CPU arm
+def use_all_host_threads() -> int:
+    """torch.distributed.run exports OMP_NUM_THREADS=1 to its workers; the CPU arm is meant to use every host core at
+    every N, so the thread count is set explicitly."""
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    return torch.get_num_threads()
+
+
 def oracle_cpu_tokens_per_s(n_tokens: int, steps: int, warmup: int, dtype: str = "bf16"):
     """The CPU oracle on `n_tokens` of the bench workload, all host threads.  Returns (tokens/s, s/step, cores)."""
     from oracle import hidream_moe_oracle as O
 
+    cores = use_all_host_threads()
     layer = {k: v.bfloat16() for k, v in O.make_layer(DIM, HIDDEN_DIM, N_EXPERTS, seed=0).items()}
     mode = O.PLAIN
     if dtype == "fp8":
@@ -121,23 +135,102 @@ def oracle_cpu_tokens_per_s(n_tokens: int, steps: int, warmup: int, dtype: str =
         for _ in range(steps):
             O.moe_layer(x, layer, mode=mode, gate_in_fp32=True)
         dt = (time.perf_counter() - t0) / max(steps, 1)
-    return n_tokens / dt, dt, torch.get_num_threads()
+    return n_tokens / dt, dt, cores
+
+
+def oracle_cpu_config1(reps: int = 3):
+    """Benchmark configuration 1 on the host cores: the layer in fp32 on [1, 4096, 2560], timed both ways the
+    reference can run it: `forward` (the masked branch it really takes) and `moe_infer` + shared expert.  Best of
+    `reps` after one warm-up call each."""
+    from oracle import hidream_moe_oracle as O
+
+    cores = use_all_host_threads()
+    n = 4096
+    layer = O.make_layer(DIM, HIDDEN_DIM, N_EXPERTS, seed=0)
+    x = O.make_input(n, DIM, seed=1)
+
+    def forward():
+        return O.moe_layer(x, layer, gate_in_fp32=True, branch="masked")
+
+    def infer():
+        idx, w = O.gate(x, layer["gate.weight"])
+        return O.moe_infer(x, idx.reshape(-1), w.reshape(-1, 1), layer) + O.swiglu_ffn(x, layer, "shared_experts")
+
+    out = {"workload": "benchmark configuration 1: fp32, 4096 tokens, dim 2560, 4 experts top-2 + shared", "cores": cores,
+           "reps": reps}
+    with torch.no_grad():
+        for name, fn in (("forward", forward), ("moe_infer_plus_shared", infer)):
+            fn()
+            best = min(_timed(fn) for _ in range(reps))
+            out[name] = {"s_per_call": best, "tokens_per_s": n / best,
+                         "tflops": FLOPS_PER_TOKEN * n / best / 1e12}
+    return out
+
+
+def _timed(fn) -> float:
+    t0 = time.perf_counter()
+    fn()
+    return time.perf_counter() - t0
+
+
+def cpu_arm(n_tokens: int, steps: int, warmup: int, dtype: str):
+    """The layer on the host cores: the unmodified reference modules when oracle/_ref holds them (bf16 / fp32; its
+    fp8 path, torch._scaled_mm on the CPU, would take hours), else the oracle's restatement.
+    Returns (tokens/s, s/step, cores, kind, description)."""
+    from oracle import build_ref
+
+    if dtype == "bf16" and build_ref.available():
+        from oracle import ref_runner
+
+        r = ref_runner.time_layer(n_tokens, steps, warmup)
+        return (r["tokens_per_s"], r["s_per_step"], r["cores"], "reference",
+                "the reference's own MoEGate (on x.float()), moe_infer and shared expert, unmodified modules collected "
+                "under oracle/_ref, bf16 on the CPU")
+    value, dt, cores = oracle_cpu_tokens_per_s(n_tokens, steps, warmup, dtype)
+    return (value, dt, cores, "port", "CPU oracle (oracle/hidream_moe_oracle.py: the reference's gate + moe_infer + "
+                                      "shared expert restated in PyTorch)")
+
+
+def cpu_config1(reps: int):
+    from oracle import build_ref
+
+    if build_ref.available():
+        from oracle import ref_runner
+
+        out = ref_runner.time_config1(reps)
+        out["kind"] = "reference"
+        return out
+    out = oracle_cpu_config1(reps)
+    out["kind"] = "port"
+    return out
+
+
+def cpu_baseline_object(dtype: str, reps: int):
+    value, dt, cores, kind, what = cpu_arm(CPU_SAMPLE_TOKENS, reps, 2, dtype)
+    return {
+        "value": value, "unit": "tokens/s", "cores": cores, "kind": kind,
+        "sample": f"{reps} calls on the first {CPU_SAMPLE_TOKENS} of the {TOKENS_PER_GPU} bench tokens ({dtype}): {what}, "
+                  f"{cores} host threads",
+        "config1_fp32": cpu_config1(reps=2),
+    }
 
 
 def run_reference_arm(args) -> None:
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    value, dt, cores = oracle_cpu_tokens_per_s(CPU_SAMPLE_TOKENS, args.steps, max(args.warmup, 1), args.dtype)
-    sample = (f"each step = the first {CPU_SAMPLE_TOKENS} of the {TOKENS_PER_GPU} bench tokens through the CPU oracle "
-              f"(oracle/hidream_moe_oracle.py: the reference's gate + moe_infer + shared expert in PyTorch)")
+    value, dt, cores, kind, what = cpu_arm(CPU_SAMPLE_TOKENS, args.steps, max(args.warmup, 1), args.dtype)
+    sample = (f"each step = the first {CPU_SAMPLE_TOKENS} of the {TOKENS_PER_GPU} bench tokens: {what}, {cores} host "
+              "threads at every N")
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": args.dtype, "data": "synthetic",
         "config": workload_config(args.gpus, args.dtype),
-        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample},
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": cores, "kind": kind, "sample": sample},
         "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "host": {"os_cpu_count": os.cpu_count(), "torch_threads": cores},
+        "config1_fp32": cpu_config1(reps=3),
     }
     print(json.dumps(line))
 
@@ -211,11 +304,254 @@ def make_synthetic(dev, seed_w: int = 0, seed_x: int = 1, fp8: bool = False, n_t
     return state, x
 
 
+def timed_region_peak(peaks, timed_ms: float, fp8: bool):
+    """Tensor-peak denominator that matches how long the timed region ran: the measured burst figure for a region
+    under a second (the GPU has not reached its power-capped clock yet), the sustained one beyond."""
+    burst = timed_ms < 1000.0
+    peak = (peaks["tflops_burst"] if burst else peaks["tflops_sustained"]) * (2.0 if fp8 else 1.0)
+    label = (f"{peaks['source']}: cuBLAS bf16 {'burst' if burst else 'sustained'} figure "
+             f"({peaks['tflops_burst']} burst / {peaks['tflops_sustained']} sustained), chosen because the timed region "
+             f"lasted {timed_ms:.0f} ms" + ("; x 2 for fp8 (no measured fp8 figure exists)" if fp8 else ""))
+    return peak, label
+
+
+class Arm:
+    """One workload on this rank: the module, its input, and the callable that runs one layer call."""
+
+    def __init__(self, dev, world, rank, fp8: bool, config5: bool):
+        import torch.distributed as dist
+
+        from comfyui_b200 import ops
+        from comfyui_b200.ldm.hidream.model import MOEFeedForwardSwiGLU
+
+        self.dev, self.world, self.rank, self.fp8, self.config5 = dev, world, rank, fp8, config5
+        self.n = n = CONFIG5_TOKENS // world if config5 else TOKENS_PER_GPU
+        state, self.x_host = make_synthetic(dev, seed_w=0, seed_x=1 + rank, fp8=fp8, n_tokens=n, skew=config5)
+        operations = ops.disable_weight_init if not fp8 else ops.scaled_fp8_ops(
+            fp8_matrix_mult=True, scale_input=False, override_dtype=torch.float8_e4m3fn)
+        self.module = MOEFeedForwardSwiGLU(DIM, HIDDEN_DIM, N_EXPERTS, TOP_K, dtype=torch.bfloat16, device=dev,
+                                           operations=operations).eval()
+        self.module.load_state_dict(state, strict=True)
+        self.x = self.x_host.to(dev).view(2, n // 2, DIM)
+        self.runner = None
+        if world > 1:
+            from comfyui_b200.expert_parallel import ExpertParallelMoE, PeerExpertParallelMoE
+
+            # default: rows move over peer memory inside the kernels; COMFY_B200_EP_TRANSPORT=nccl selects the
+            # host-planned NCCL exchange (bf16 only)
+            transport = os.environ.get("COMFY_B200_EP_TRANSPORT", "peer")
+            if transport != "nccl":
+                try:        # the same answer on every rank: a missing module, not a failed rendezvous
+                    import torch.distributed._symmetric_memory as symm_mem
+
+                    symm_mem.empty, symm_mem.rendezvous
+                except (ImportError, AttributeError):
+                    transport = "nccl"
+                    os.environ["COMFY_B200_EP_TRANSPORT"] = "nccl"     # workload_config() names the transport used
+            if transport == "nccl":
+                self.runner = ExpertParallelMoE(self.module, dist.group.WORLD)
+            else:
+                self.runner = PeerExpertParallelMoE(self.module, dist.group.WORLD, max_tokens=n)
+            self.step = lambda inp: self.runner(inp)                      # noqa: E731
+            self.launches_per_step = self.runner.launches_per_step
+        else:
+            assert ops._layer_pack(self.module, self.x) is not None, "bench: layer not eligible for the sm_100a kernels"
+            self.step = lambda inp: self.module(inp)                      # noqa: E731
+            self.launches_per_step = 5   # gate, plan + permute, GEMM pass 1, GEMM pass 2, combine
+
+    def check(self):
+        if self.runner is not None and hasattr(self.runner, "check"):
+            self.runner.check()          # no flag wait ran out, every routed row fitted its receive buffer
+
+    def routing(self):
+        """Realised routing of the last call: slots per expert over all GPUs, rows each GPU's routed experts process."""
+        from comfyui_b200 import ops, torch_ops
+
+        if self.world > 1:
+            r = self.runner
+            last = r.last_counts_host if hasattr(r, "last_counts_host") else r.last_counts
+            per_expert = [sum(c[e] for c in last) for e in range(N_EXPERTS)]
+            owners = [r.place.owners(e) for e in range(N_EXPERTS)]
+            rows = [sum(per_expert[e] for e in range(N_EXPERTS) if q in owners[e]) for q in range(self.world)]
+        else:
+            layer = ops._layer_pack(self.module, self.x)
+            per_expert = torch_ops._workspace(layer, self.n).expert_counts.tolist()
+            rows = [sum(per_expert)]
+        return {"slots_per_expert": per_expert, "share_of_expert_0": per_expert[0] / max(sum(per_expert), 1),
+                "routed_rows_per_gpu": rows}
+
+
+def time_steps(arm, steps: int, barrier, local_rank: int):
+    """Milliseconds for exactly `steps` layer calls (inputs resident in HBM) between two CUDA events on the launching
+    stream, with the SM clock sampled meanwhile."""
+    barrier()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local_rank) as clocks:
+        ev0.record()
+        for _ in range(steps):
+            arm.step(arm.x)
+        ev1.record()
+        barrier()
+    return ev0.elapsed_time(ev1), clocks.summary()
+
+
+def max_over_ranks(values, dev, world):
+    import torch.distributed as dist
+
+    t = torch.tensor(values, dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return t.tolist()
+
+
+def measure(arm, args, barrier, local_rank, peaks, *, steps: int, warmup: int, e2e: bool, sustained: bool,
+            stages: bool, gpu_bar: bool):
+    """All figures of one workload as a dict (identical on every rank; only rank 0 prints it)."""
+    from comfyui_b200 import moe_ops, ops
+
+    dev, world, n, fp8 = arm.dev, arm.world, arm.n, arm.fp8
+    res = {}
+    with torch.inference_mode():
+        for _ in range(max(warmup, 3)):
+            arm.step(arm.x)
+        ms_total, clocks = time_steps(arm, steps, barrier, local_rank)
+        arm.check()
+        ms_e2e = 0.0
+        if e2e:
+            # end to end: every step copies its input from pinned host memory and its output back to pinned host
+            # memory.  The copies run on their own streams with two buffers each, the way a serving loop would feed
+            # the layer: step i's upload and step i-1's download overlap step i's compute; nothing is skipped.
+            x_pinned = arm.x_host.pin_memory()
+            out_pinned = torch.empty_like(arm.x_host).pin_memory()
+            ms_e2e = time_end_to_end(arm.step, x_pinned, out_pinned, n, dev, steps, barrier)
+        ms_total, ms_e2e = max_over_ranks([ms_total, ms_e2e], dev, world)
+        ms_step = ms_total / steps
+        res.update({
+            "value": n * world / (ms_step * 1e-3), "unit": "tokens/s", "steps": steps, "ms_per_step": ms_step,
+            "dtype": "fp8" if fp8 else "bf16", "clocks": clocks,
+            "layer_tflops": FLOPS_PER_TOKEN * n * world / (ms_step * 1e-3) / 1e12,
+            "layer_frac_of_nominal": FLOPS_PER_TOKEN * n / (ms_step * 1e-3) / 1e12 / (4500.0 if fp8 else 2250.0),
+        })
+        if e2e:
+            e2e_s = ms_e2e / steps * 1e-3
+            res["e2e"] = {"value": n * world / e2e_s, "unit": "tokens/s",
+                          "h2d_bytes_per_step": arm.x_host.numel() * 2, "d2h_bytes_per_step": arm.x_host.numel() * 2,
+                          "ms_per_step": ms_e2e / steps,
+                          # both copies of a step overlap the compute of its neighbours, so a step cannot be shorter than
+                          # the slower of one copy direction and the compute: the achieved rate names the limiter
+                          "host_link_gbs_per_direction_per_gpu": arm.x_host.numel() * 2 / e2e_s / 1e9}
+        if arm.config5:
+            res["routing"] = arm.routing()
+
+        if sustained:
+            # the same loop for at least 1.2 s: the GPU settles at its power-capped clock
+            k_long = max(steps, int(1200.0 / ms_step) + 1)
+            ms_long, clocks_long = time_steps(arm, k_long, barrier, local_rank)
+            (ms_long,) = max_over_ranks([ms_long], dev, world)
+            ms_l = ms_long / k_long
+            res["sustained"] = {
+                "steps": k_long, "timed_region_ms": ms_long, "ms_per_step": ms_l, "value": n * world / (ms_l * 1e-3),
+                "unit": "tokens/s", "layer_tflops_per_gpu": FLOPS_PER_TOKEN * n / (ms_l * 1e-3) / 1e12,
+                "layer_frac_of_nominal": FLOPS_PER_TOKEN * n / (ms_l * 1e-3) / 1e12 / (4500.0 if fp8 else 2250.0),
+                "clocks": clocks_long,
+            }
+
+        if world > 1:
+            # no per-kernel timing in the multi-GPU loop: the grouped GEMM's FLOPs per GPU over the WHOLE step (routing,
+            # exchange, flag waits and combine included), i.e. a lower bound on what the kernel itself reaches
+            peak, label = timed_region_peak(peaks, ms_total, fp8)
+            achieved = FLOPS_PER_TOKEN_GEMM * n / (ms_step * 1e-3) / 1e12
+            res["roofline"] = {
+                "bound": "tensor", "kernel": "grouped_gemm_kernel (per GPU; time = the whole expert-parallel step)",
+                "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak, "peak_source": label,
+                "frac_of_nominal": achieved / (4500.0 if fp8 else 2250.0), "traffic": None,
+            }
+        elif stages:
+            # per-stage timing of the same work through the stage-level C ABI
+            st = time_stages(arm.module, arm.x.view(n, DIM), steps, moe_ops, ops)
+            gemm_ms = st["grouped_gemm_ms"]
+            achieved = FLOPS_PER_TOKEN_GEMM * n / (gemm_ms * 1e-3) / 1e12
+            peak, label = timed_region_peak(peaks, st["timed_region_ms"], fp8)
+            roof = {
+                "bound": "tensor", "kernel": "grouped_gemm_kernel (pass 1 SwiGLU + pass 2, one C-ABI call)",
+                "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak, "peak_source": label,
+                "frac_of_burst": achieved / (peaks["tflops_burst"] * (2.0 if fp8 else 1.0)),
+                "frac_of_sustained": achieved / (peaks["tflops_sustained"] * (2.0 if fp8 else 1.0)),
+                "frac_of_nominal": achieved / (4500.0 if fp8 else 2250.0), "traffic": None,
+            }
+            if not arm.config5:
+                # DRAM bytes of the two launches are not measured in this run: they come from the ncu capture of this
+                # same workload that the named file summarises
+                roof["traffic"] = TRAFFIC_FROM_CAPTURE["fp8" if fp8 else "bf16"]["traffic"]
+                roof["algorithmic_bytes"] = TRAFFIC_FROM_CAPTURE["fp8" if fp8 else "bf16"]["algorithmic_bytes"]
+                roof["traffic_source"] = TRAFFIC_FROM_CAPTURE["fp8" if fp8 else "bf16"]["source"]
+            res["roofline"] = roof
+            res["stages"] = st
+            hbm = peaks["hbm_gbs"]
+            res["hbm_kernels"] = {
+                k: {"achieved_gbs": st[k + "_bytes"] / (st[k + "_ms"] * 1e-3) / 1e9,
+                    "frac": st[k + "_bytes"] / (st[k + "_ms"] * 1e-3) / 1e9 / hbm, "peak_gbs": hbm}
+                for k in ("gate", "permute", "combine")
+            }
+            if sustained:
+                k_long = max(steps, int(1200.0 / max(sum(st[k + "_ms"] for k in STAGE_NAMES), 1e-3)) + 1)
+                with ClockSampler(local_rank) as clocks_st:
+                    st_long = time_stages(arm.module, arm.x.view(n, DIM), k_long, moe_ops, ops)
+                a_long = FLOPS_PER_TOKEN_GEMM * n / (st_long["grouped_gemm_ms"] * 1e-3) / 1e12
+                mult = 2.0 if fp8 else 1.0
+                res["sustained"]["grouped_gemm"] = {
+                    "steps": k_long, "timed_region_ms": st_long["timed_region_ms"], "ms": st_long["grouped_gemm_ms"],
+                    "tflops": a_long, "frac_of_sustained_peak": a_long / (peaks["tflops_sustained"] * mult),
+                    "frac_of_nominal": a_long / (4500.0 if fp8 else 2250.0),
+                    "peak_source": f"{peaks['source']}: cuBLAS bf16 sustained {peaks['tflops_sustained']} TFLOP/s"
+                                   + (" x 2 for fp8" if fp8 else ""),
+                    "clocks": clocks_st.summary(),
+                }
+            if gpu_bar:
+                res["gpu_bar"] = time_stock_composition(arm.module, arm.x, ops)
+    return res
+
+
+# dram__bytes_read.sum + dram__bytes_write.sum of the two grouped-GEMM launches of one layer call at 8192 tokens, from
+# ncu captures of exactly this workload (not measured by bench.py itself)
+TRAFFIC_FROM_CAPTURE = {
+    "bf16": {"traffic": 1.587e9, "algorithmic_bytes": 1.30e9, "source": "profiles/grouped_gemm_bf16_8192tokens.md"},
+    "fp8": {"traffic": 0.658e9, "algorithmic_bytes": 0.71e9, "source": "profiles/grouped_gemm_fp8_8192tokens.md"},
+}
+STAGE_NAMES = ["gate", "plan", "permute", "grouped_gemm", "combine"]
+
+
+def expert_parallel_parity(arm):
+    """Every rank runs its own tokens through the single-GPU layer with the full weights it holds anyway and compares
+    the expert-parallel result with it: bit for bit without a hidden split, within the bf16 tolerance with one (the sum
+    of two partial results is rounded once more)."""
+    import torch.distributed as dist
+
+    from comfyui_b200 import ops
+
+    with torch.inference_mode():
+        ep = arm.runner(arm.x).clone()
+        arm.check()
+        assert ops._layer_pack(arm.module, arm.x) is not None
+        single = arm.module(arm.x)
+        torch.cuda.synchronize()
+    split = getattr(arm.runner.place, "hidden_splits", 1) > 1
+    exact = bool(torch.equal(ep, single))
+    diff = float((ep.float() - single.float()).abs().max())
+    close = bool(torch.allclose(ep.float(), single.float(), rtol=2e-2, atol=2e-2))
+    ok = close if split else exact
+    t = torch.tensor([0.0 if ok else 1.0, 0.0 if exact else 1.0, diff], dtype=torch.float64, device=arm.dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    bad, inexact, diff = t.tolist()
+    return {"ok": bad == 0.0, "bit_identical": inexact == 0.0, "max_abs_diff": diff,
+            "criterion": "rtol = atol = 2e-2 (hidden dimension split over two GPUs)" if split else "torch.equal",
+            "against": "the single-GPU layer on the same rank, same tokens, full weights", "tokens_per_gpu": arm.n}
+
+
 def run_gpu_arm(args) -> None:
     import torch.distributed as dist
 
-    from comfyui_b200 import _native, moe_ops, ops
-    from comfyui_b200.ldm.hidream.model import MOEFeedForwardSwiGLU
+    from comfyui_b200 import _native
 
     _native.load()   # no fallback: fail here if the extension is not built
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -229,166 +565,74 @@ def run_gpu_arm(args) -> None:
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
 
-    fp8 = args.dtype == "fp8"
-    config5 = args.workload == "config5"
-    n = CONFIG5_TOKENS // world if config5 else TOKENS_PER_GPU
-    state, x_host = make_synthetic(dev, seed_w=0, seed_x=1 + rank, fp8=fp8, n_tokens=n, skew=config5)
-    operations = ops.disable_weight_init if not fp8 else ops.scaled_fp8_ops(
-        fp8_matrix_mult=True, scale_input=False, override_dtype=torch.float8_e4m3fn)
-    module = MOEFeedForwardSwiGLU(DIM, HIDDEN_DIM, N_EXPERTS, TOP_K, dtype=torch.bfloat16, device=dev,
-                                  operations=operations).eval()
-    module.load_state_dict(state, strict=True)
-    x_pinned = x_host.pin_memory()
-    out_pinned = torch.empty_like(x_host).pin_memory()
-    x = x_host.to(dev).view(2, n // 2, DIM)
-
-    if world > 1:
-        from comfyui_b200.expert_parallel import ExpertParallelMoE, PeerExpertParallelMoE
-
-        # default: rows move over peer memory inside the kernels; COMFY_B200_EP_TRANSPORT=nccl selects the
-        # host-planned NCCL exchange (bf16 only)
-        transport = os.environ.get("COMFY_B200_EP_TRANSPORT", "peer")
-        if transport != "nccl":
-            try:        # the same answer on every rank: a missing module, not a failed rendezvous
-                import torch.distributed._symmetric_memory as symm_mem
-
-                symm_mem.empty, symm_mem.rendezvous
-            except (ImportError, AttributeError):
-                transport = "nccl"
-                os.environ["COMFY_B200_EP_TRANSPORT"] = "nccl"     # workload_config() names the transport used
-        if transport == "nccl":
-            runner = ExpertParallelMoE(module, dist.group.WORLD)
-        else:
-            runner = PeerExpertParallelMoE(module, dist.group.WORLD, max_tokens=n)
-        step = lambda inp: runner(inp)                      # noqa: E731
-        launches_per_step = runner.launches_per_step
-    else:
-        assert ops._layer_pack(module, x) is not None, "bench: layer not eligible for the sm_100a kernels"
-        step = lambda inp: module(inp)                      # noqa: E731
-        launches_per_step = 5   # gate, plan + permute, GEMM pass 1, GEMM pass 2, combine
-
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    with torch.inference_mode():
-        for _ in range(max(args.warmup, 3)):
-            step(x)
-        # ---- device-resident timing: exactly K steps between two events
-        barrier()
-        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        with ClockSampler(local_rank) as clocks:
-            ev0.record()
-            for _ in range(args.steps):
-                step(x)
-            ev1.record()
-            barrier()
-        ms_total = ev0.elapsed_time(ev1)
-        if world > 1 and hasattr(runner, "check"):
-            runner.check()          # no flag wait ran out, every routed row fitted its receive buffer
+    peaks = measured_peaks()
+    fp8 = args.dtype == "fp8"
+    config5 = args.workload == "config5"
+    extras = args.workload == "hidream" and not args.headline_only
+    warmup = max(args.warmup, 3)
 
-        # ---- end to end: every step copies its input from pinned host memory and its output back to pinned host
-        # memory.  The copies run on their own streams with two buffers each, the way a serving loop would feed
-        # the layer: step i's upload and step i-1's download overlap step i's compute; nothing is skipped.
-        ms_e2e = time_end_to_end(step, x_pinned, out_pinned, n, dev, args.steps, barrier)
+    arm = Arm(dev, world, rank, fp8, config5)
+    res = measure(arm, args, barrier, local_rank, peaks, steps=args.steps, warmup=warmup, e2e=True,
+                  sustained=extras, stages=True, gpu_bar=not args.no_cpu_baseline)
+    line = {
+        "metric": METRIC, "value": res.pop("value"), "unit": res.pop("unit"), "n_gpus": world, "steps": args.steps,
+        "warmup": warmup, "ms_per_step": res.pop("ms_per_step"), "higher_is_better": True,
+        "scaling": "strong" if config5 else "weak", "vs_baseline": None, "dtype": args.dtype, "data": "synthetic",
+        "config": workload_config(world, args.dtype, arm.n, config5),
+        "gpu_launches": arm.launches_per_step * args.steps,
+    }
+    res.pop("steps"), res.pop("dtype")
+    line.update(res)
 
-        # ---- per-stage timing of the same work through the stage-level C ABI (single GPU only)
-        stages = None
-        gpu_bar = None
-        if world == 1:
-            stages = time_stages(module, x.view(n, DIM), args.steps, moe_ops, ops)
-            if not args.no_cpu_baseline:
-                gpu_bar = time_stock_composition(module, x, ops)
+    if extras:
+        # Sub-objects of the same line, measured after the headline and outside its timed region: expert-parallel
+        # parity, the other dtype (benchmark configuration 3 when the headline is configuration 2), configuration 5.
+        if world > 1:
+            line["ep_parity"] = {args.dtype: expert_parallel_parity(arm)}
+        del arm
+        torch.cuda.empty_cache()
+        other = "bf16" if fp8 else "fp8"
+        arm2 = Arm(dev, world, rank, not fp8, False)
+        sub = measure(arm2, args, barrier, local_rank, peaks, steps=args.steps, warmup=warmup, e2e=True,
+                      sustained=True, stages=True, gpu_bar=False)
+        sub["config"] = workload_config(world, other, arm2.n, False)["workload"]
+        sub["gpu_launches"] = arm2.launches_per_step * args.steps
+        line[other] = sub
+        if world > 1:
+            line["ep_parity"][other] = expert_parallel_parity(arm2)
+        del arm2
+        torch.cuda.empty_cache()
+        arm5 = Arm(dev, world, rank, False, True)
+        k5 = max(3, min(args.steps, 10 if world == 1 else 20))
+        sub = measure(arm5, args, barrier, local_rank, peaks, steps=k5, warmup=3, e2e=False, sustained=False,
+                      stages=True, gpu_bar=False)
+        sub["config"] = workload_config(world, "bf16", arm5.n, True)["workload"]
+        sub["scaling"] = "strong"
+        sub["tokens_per_gpu"] = arm5.n
+        sub["gpu_launches"] = arm5.launches_per_step * k5
+        line["config5"] = sub
+        if world > 1:
+            line["ep_parity"]["config5"] = expert_parallel_parity(arm5)
+        arm = arm5
 
+    if world == 1 and not args.no_cpu_baseline and rank == 0:
+        line["cpu_baseline"] = cpu_baseline_object(args.dtype, reps=10)
 
-        if args.timeline and rank == 0:
-            print_timeline(step, x)
-        elif args.timeline:
-            for _ in range(3):          # the other ranks take the same three steps
-                step(x)
-            torch.cuda.synchronize()
-
-    times = torch.tensor([ms_total, ms_e2e], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    ms_total, ms_e2e = times.tolist()
+    if args.timeline:
+        with torch.inference_mode():
+            if rank == 0:
+                print_timeline(arm.step, arm.x)
+            else:
+                for _ in range(3):          # the other ranks take the same three steps
+                    arm.step(arm.x)
+                torch.cuda.synchronize()
 
     if rank == 0:
-        peaks = measured_peaks()
-        ms_step = ms_total / args.steps
-        value = n * world / (ms_step * 1e-3)
-        line = {
-            "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True,
-            "scaling": "strong" if config5 else "weak",
-            "vs_baseline": None, "dtype": args.dtype, "data": "synthetic",
-            "config": workload_config(world, args.dtype, n, config5),
-            "e2e": {"value": n * world / (ms_e2e / args.steps * 1e-3), "unit": "tokens/s",
-                    "h2d_bytes_per_step": x_pinned.numel() * 2, "d2h_bytes_per_step": out_pinned.numel() * 2},
-            "gpu_launches": launches_per_step * args.steps,
-            "clocks": clocks.summary(),
-            "layer_tflops": FLOPS_PER_TOKEN * n * world / (ms_step * 1e-3) / 1e12,
-            "layer_frac_of_nominal": FLOPS_PER_TOKEN * n / (ms_step * 1e-3) / 1e12 / (4500.0 if fp8 else 2250.0),
-        }
-        if world > 1:
-            # no per-kernel timing in the multi-GPU loop: the grouped GEMM's FLOPs per GPU over the WHOLE step (routing,
-            # exchange, flag waits and combine included), i.e. a lower bound on what the kernel itself reaches
-            peak = peaks["tflops_sustained"] * (2.0 if fp8 else 1.0)
-            achieved = FLOPS_PER_TOKEN_GEMM * n / (ms_step * 1e-3) / 1e12
-            line["roofline"] = {
-                "bound": "tensor", "kernel": "grouped_gemm_kernel (per GPU; time = the whole expert-parallel step)",
-                "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-                "peak_source": f"{peaks['source']}: sustained cuBLAS bf16 (burst {peaks['tflops_burst']})"
-                               + (" x 2 for fp8" if fp8 else ""),
-                "frac_of_nominal": achieved / (4500.0 if fp8 else 2250.0), "traffic": None,
-            }
-        if config5:
-            # realised routing: slots per expert over all GPUs, and the rows each GPU's routed experts process
-            if world > 1:
-                last = runner.last_counts_host if hasattr(runner, "last_counts_host") else runner.last_counts
-                per_expert = [sum(c[e] for c in last) for e in range(N_EXPERTS)]
-                owners = [runner.place.owners(e) for e in range(N_EXPERTS)]
-                rows = [sum(per_expert[e] for e in range(N_EXPERTS) if r in owners[e]) for r in range(world)]
-            else:
-                from comfyui_b200 import torch_ops
-
-                layer = ops._layer_pack(module, x)
-                per_expert = torch_ops._workspace(layer, n).expert_counts.tolist()
-                rows = [sum(per_expert)]
-            line["routing"] = {"slots_per_expert": per_expert, "share_of_expert_0": per_expert[0] / sum(per_expert),
-                               "routed_rows_per_gpu": rows}
-        if stages is not None:
-            gemm_ms = stages["grouped_gemm_ms"]
-            achieved = FLOPS_PER_TOKEN_GEMM * n / (gemm_ms * 1e-3) / 1e12
-            # fp8: no measured fp8 denominator exists; twice the measured bf16 figure is used and named as such
-            peak = peaks["tflops_sustained"] * (2.0 if fp8 else 1.0)
-            line["roofline"] = {
-                "bound": "tensor", "kernel": "grouped_gemm_kernel (pass 1 SwiGLU + pass 2, one C-ABI call)",
-                "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-                "peak_source": f"{peaks['source']}: sustained cuBLAS bf16 (burst {peaks['tflops_burst']})"
-                               + (" x 2 for fp8" if fp8 else ""),
-                "frac_of_burst": achieved / (peaks["tflops_burst"] * (2.0 if fp8 else 1.0)),
-                "frac_of_nominal": achieved / (4500.0 if fp8 else 2250.0),
-                # dram__bytes_read + dram__bytes_write of the two launches, from the ncu capture summarised in
-                # profiles/grouped_gemm_{bf16,fp8}_8192tokens.md (same workload)
-                "traffic": 0.658e9 if fp8 else 1.587e9, "algorithmic_bytes": 0.71e9 if fp8 else 1.30e9,
-            }
-            line["stages"] = stages
-            line["gpu_bar"] = gpu_bar
-            hbm = peaks["hbm_gbs"]
-            line["hbm_kernels"] = {
-                k: {"achieved_gbs": stages[k + "_bytes"] / (stages[k + "_ms"] * 1e-3) / 1e9,
-                    "frac": stages[k + "_bytes"] / (stages[k + "_ms"] * 1e-3) / 1e9 / hbm, "peak_gbs": hbm}
-                for k in ("gate", "permute", "combine")
-            }
-            if not args.no_cpu_baseline:
-                cpu_value, cpu_dt, cores = oracle_cpu_tokens_per_s(CPU_SAMPLE_TOKENS, 20, 2, args.dtype)
-                line["cpu_baseline"] = {
-                    "value": cpu_value, "unit": "tokens/s", "cores": cores, "kind": "port",
-                    "sample": f"20 calls on the first {CPU_SAMPLE_TOKENS} of the {n} bench tokens, CPU oracle "
-                              "(PyTorch, all host threads)",
-                }
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
@@ -458,7 +702,7 @@ def time_stages(module, x2, steps, moe_ops, ops):
     for i, pack in enumerate(layer.experts):
         pack.fill(experts[i])
     shared = layer.shared.struct()
-    names = ["gate", "plan", "permute", "grouped_gemm", "combine"]
+    names = STAGE_NAMES
     act = N.FP8_E4M3 if layer.fp8 else N.BF16
 
     def one_step(marks):
@@ -472,7 +716,8 @@ def time_stages(module, x2, steps, moe_ops, ops):
                                        P(ws.expert_offsets), stream)
         marks[2].record()
         rc |= lib.comfy_moe_permute(P(x2), P(ws.topk_idx), P(ws.block_offsets), P(ws.expert_offsets), n, d, e, act,
-                                    None, P(ws.x_perm), P(ws.x_q) if layer.fp8 else None, None, P(ws.row_map), stream)
+                                    None, P(ws.x_perm), P(ws.x_q) if layer.fp8 else None, None, P(ws.row_map), None,
+                                    stream)
         marks[3].record()
         rc |= lib.comfy_moe_grouped_swiglu(act, e, experts, ctypes.byref(shared), P(ws.expert_offsets),
                                            P(ws.expert_counts), ws.rows_cap, n, d, P(ws.x_perm), P(ws.h_perm),
@@ -494,7 +739,7 @@ def time_stages(module, x2, steps, moe_ops, ops):
     for marks in all_marks:
         one_step(marks)
     torch.cuda.synchronize()
-    res = {}
+    res = {"steps": steps, "timed_region_ms": all_marks[0][0].elapsed_time(all_marks[-1][5])}
     for i, k in enumerate(names):
         res[k + "_ms"] = sum(m[i].elapsed_time(m[i + 1]) for m in all_marks) / steps
     res["gate_bytes"] = n * d * 2 + e * d * 2 + n * 2 * 8
@@ -732,6 +977,9 @@ def main() -> None:
     ap.add_argument("--timeline", action="store_true",
                     help="after the timing, print the kernel timeline of one step on rank 0 to stderr (torch.profiler)")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU oracle and the stock-composition timings (profiling runs)")
+    ap.add_argument("--headline-only", action="store_true",
+                    help="hidream workload: skip the sub-objects (sustained loop, the other dtype, configuration 5, "
+                         "expert-parallel parity) that the default run adds to the line")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)

@@ -11,7 +11,7 @@ from ctypes import POINTER, Structure, c_char_p, c_float, c_int, c_int32, c_int6
 
 from . import build as _build
 
-ABI_VERSION = 8
+ABI_VERSION = 9
 
 OK, EINVAL, EUNSUPPORTED, ECUDA, ETIMEOUT, EDEVICE, ETOOLARGE = range(7)
 BF16, FP32, FP8_E4M3, FP16 = 0, 1, 2, 3
@@ -19,6 +19,7 @@ ROW_ALIGN = 128
 TOKENS_PER_BLOCK = 32
 MAX_EXPERTS = 8
 STATIC_MAX_TOKENS = 131072
+STATUS_WORDS = 4        # [0] sticky device status, [1] near-ties of the last gate call, [2] e4m3 overflows, [3] reserved
 MAX_RANKS = 8
 EP_ARRIVED, EP_DONE = 0, 1
 
@@ -50,6 +51,7 @@ EXPORTS = (
     "comfy_moe_ep_dispatch",
     "comfy_moe_ep_signal",
     "comfy_moe_ep_wait",
+    "comfy_moe_ep_wait_budget",
     "comfy_moe_ep_combine",
 )
 
@@ -199,11 +201,11 @@ def load(build_if_missing: bool = False) -> ctypes.CDLL:
     lib.comfy_moe_route_plan.argtypes = [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]
     lib.comfy_moe_permute.argtypes = [
         c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
-        c_void_p, c_void_p,
+        c_void_p, c_void_p, c_void_p,
     ]
     lib.comfy_moe_plan_permute.argtypes = [
         c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-        c_void_p, c_void_p, c_void_p, c_void_p,
+        c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
     ]
     lib.comfy_moe_route_static.argtypes = [
         c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -239,12 +241,13 @@ def load(build_if_missing: bool = False) -> ctypes.CDLL:
         c_int, c_int, POINTER(FfnWeights), c_void_p, c_void_p, c_int64, c_int, c_void_p, c_void_p, POINTER(c_void_p),
         c_void_p, c_int64, c_void_p, c_void_p,
     ]
-    lib.comfy_moe_quantize_e4m3.argtypes = [c_void_p, c_void_p, c_int64, c_void_p, c_void_p]
+    lib.comfy_moe_quantize_e4m3.argtypes = [c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p]
     lib.comfy_attn_rmsnorm_rope.argtypes = [c_void_p, c_int64, c_void_p, c_float, c_void_p, c_int64, c_int, c_int, c_int,
                                             c_int, c_int, c_int, c_void_p, c_int64, c_int, c_void_p]
     lib.comfy_moe_stochastic_round_e4m3.argtypes = [c_void_p, c_int, c_void_p, c_int64, c_void_p, c_void_p]
     lib.comfy_moe_ep_signal.argtypes = [POINTER(PeerPlan), c_int, c_uint32, c_void_p]
     lib.comfy_moe_ep_wait.argtypes = [POINTER(PeerPlan), c_int, c_uint32, c_void_p, c_void_p]
+    lib.comfy_moe_ep_wait_budget.argtypes = [POINTER(PeerPlan), c_int, c_uint32, c_int64, c_void_p, c_void_p]
     lib.comfy_moe_ep_combine.argtypes = [POINTER(PeerPlan), c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                          c_void_p, c_void_p]
     for name in EXPORTS:

@@ -105,13 +105,15 @@ gate_residual_kernel(const __nv_bfloat16* __restrict__ y, const __nv_bfloat16* _
   }
 }
 
-// bf16 -> e4m3 with the activation quantiser of comfy/ops.py:338-343: optional multiply by bf16(1 / scale) rounded to
-// bf16, clamp to +-448, round to nearest even.  32 bytes read and 16 written per thread and step.
+// bf16 -> e4m3 with the activation quantiser of comfy/ops.py:338-343.  Without a scale: clamp to +-448, round to
+// nearest even.  With one: multiply by bf16(1 / scale), rounded to bf16, and cast WITHOUT a clamp, as the reference does;
+// what overflows becomes NaN and is counted.  32 bytes read and 16 written per thread and step.
 __global__ void __launch_bounds__(256)
 quantize_e4m3_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ scale, long long n_chunks,
-                     uint8_t* __restrict__ out) {
+                     uint8_t* __restrict__ out, int32_t* __restrict__ overflow_count) {
   float inv = 1.f;
   bool scaled = false;
+  int ovf = 0;
   if (scale) { inv = round_bf16(1.0f / __ldg(scale)); scaled = true; }
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n_chunks;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
@@ -130,10 +132,14 @@ quantize_e4m3_kernel(const __nv_bfloat16* __restrict__ x, const float* __restric
       float g[4];
 #pragma unroll
       for (int m = 0; m < 4; ++m) g[m] = scaled ? round_bf16(f[4 * k + m] * inv) : f[4 * k + m];
-      w[k] = static_cast<uint32_t>(f2_to_e4m3x2(g[0], g[1])) | (static_cast<uint32_t>(f2_to_e4m3x2(g[2], g[3])) << 16);
+      w[k] = scaled ? (static_cast<uint32_t>(f2_to_e4m3x2_nosat(g[0], g[1], ovf)) |
+                       (static_cast<uint32_t>(f2_to_e4m3x2_nosat(g[2], g[3], ovf)) << 16))
+                    : (static_cast<uint32_t>(f2_to_e4m3x2(g[0], g[1])) |
+                       (static_cast<uint32_t>(f2_to_e4m3x2(g[2], g[3])) << 16));
     }
     reinterpret_cast<uint4*>(out)[i] = make_uint4(w[0], w[1], w[2], w[3]);
   }
+  if (ovf && overflow_count) atomicAdd(overflow_count, ovf);
 }
 
 }  // namespace comfy_b200
@@ -189,7 +195,8 @@ extern "C" int comfy_moe_gate_residual(const void* y, const void* gate, int64_t 
   return check_launch();
 }
 
-extern "C" int comfy_moe_quantize_e4m3(const void* x, const float* scale, int64_t n_elements, void* out, void* stream) {
+extern "C" int comfy_moe_quantize_e4m3(const void* x, const float* scale, int64_t n_elements, void* out,
+                                       int32_t* overflow_count, void* stream) {
   if (n_elements < 0) return COMFY_MOE_EINVAL;
   if (n_elements == 0) return COMFY_MOE_OK;
   if (!x || !out || !aligned16(x) || !aligned16(out)) return COMFY_MOE_EINVAL;
@@ -198,6 +205,6 @@ extern "C" int comfy_moe_quantize_e4m3(const void* x, const float* scale, int64_
   long long blocks = (chunks + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;
   quantize_e4m3_kernel<<<static_cast<int>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(x), scale, chunks, static_cast<uint8_t*>(out));
+      static_cast<const __nv_bfloat16*>(x), scale, chunks, static_cast<uint8_t*>(out), overflow_count);
   return check_launch();
 }

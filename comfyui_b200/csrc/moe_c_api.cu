@@ -17,13 +17,17 @@ extern "C" const char* comfy_moe_error_string(int code) {
   }
 }
 
-extern "C" int comfy_moe_read_status(const int32_t* status, void* stream, int32_t* h_status) {
+// The status word is sticky: kernels only ever move it from 0 to a code (atomicCAS), no entry point clears it on
+// the way in, and this function clears it once it has handed a code to the host.  So a code left by any layer of a
+// model is still there when the host looks, however many layers ran after it.
+extern "C" int comfy_moe_read_status(int32_t* status, void* stream, int32_t* h_status) {
   if (!status || !h_status) return COMFY_MOE_EINVAL;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (cudaMemcpyAsync(h_status, status, sizeof(int32_t), cudaMemcpyDeviceToHost, s) != cudaSuccess)
     return COMFY_MOE_ECUDA;
   if (cudaStreamSynchronize(s) != cudaSuccess) return COMFY_MOE_ECUDA;
   if (*h_status == 0) return COMFY_MOE_OK;
+  if (cudaMemsetAsync(status, 0, sizeof(int32_t), s) != cudaSuccess) return COMFY_MOE_ECUDA;
   return *h_status == 8 ? COMFY_MOE_ETOOLARGE : COMFY_MOE_ETIMEOUT;   // 8: routed rows exceed a peer receive buffer
 }
 
@@ -55,7 +59,8 @@ static int forward_impl(const ComfyMoeLayer* L, const ComfyMoeWorkspace* ws, con
   if (fp8 && !ws->x_q) return COMFY_MOE_EINVAL;
 
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (cudaMemsetAsync(ws->status, 0, 2 * sizeof(int32_t), s) != cudaSuccess) return COMFY_MOE_ECUDA;
+  // only the near-tie counter starts from zero; the status word keeps whatever an earlier call left in it
+  if (cudaMemsetAsync(ws->status + 1, 0, sizeof(int32_t), s) != cudaSuccess) return COMFY_MOE_ECUDA;
 
   rc = comfy_moe_gate_topk(x, L->w_gate, L->gate_dtype, n_tokens, L->dim, L->n_experts, L->top_k, ws->topk_idx,
                            ws->topk_weight, ws->block_counts, ws->status + 1, nullptr, 1e-6f, stream);
@@ -63,7 +68,8 @@ static int forward_impl(const ComfyMoeLayer* L, const ComfyMoeWorkspace* ws, con
   rc = comfy_moe_plan_permute(x, ws->topk_idx, ws->block_counts, n_tokens, L->dim, L->n_experts,
                               fp8 ? COMFY_MOE_FP8_E4M3 : COMFY_MOE_BF16, fp8 ? L->experts[0].scale_in13 : nullptr,
                               ws->block_offsets, ws->expert_counts, ws->expert_offsets, ws->x_perm,
-                              fp8 ? ws->x_q : nullptr, fp8 ? L->shared.scale_in13 : nullptr, ws->row_map, stream);
+                              fp8 ? ws->x_q : nullptr, fp8 ? L->shared.scale_in13 : nullptr, ws->row_map,
+                              ws->status + 2, stream);
   if (rc != COMFY_MOE_OK) return rc;
   rc = comfy_moe_grouped_swiglu(L->w_dtype, L->n_experts, L->experts, &L->shared, ws->expert_offsets,
                                 ws->expert_counts, ws->rows_cap, n_tokens, L->dim, ws->x_perm, ws->h_perm, ws->y_perm,
@@ -98,13 +104,13 @@ extern "C" int comfy_moe_forward_gelu_mlp(const ComfyMoeMlpLayer* L, const Comfy
   if (rc != COMFY_MOE_OK) return rc;
   if (ws->rows_cap < rows_need) return COMFY_MOE_EINVAL;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (cudaMemsetAsync(ws->status, 0, 2 * sizeof(int32_t), s) != cudaSuccess) return COMFY_MOE_ECUDA;
+  if (cudaMemsetAsync(ws->status + 1, 0, sizeof(int32_t), s) != cudaSuccess) return COMFY_MOE_ECUDA;
   rc = comfy_moe_gate_topk(x, L->w_gate, L->gate_dtype, n_tokens, L->dim, L->n_experts, L->top_k, ws->topk_idx,
                            ws->topk_weight, ws->block_counts, ws->status + 1, nullptr, 1e-6f, stream);
   if (rc != COMFY_MOE_OK) return rc;
   rc = comfy_moe_plan_permute(x, ws->topk_idx, ws->block_counts, n_tokens, L->dim, L->n_experts, COMFY_MOE_BF16,
                               nullptr, ws->block_offsets, ws->expert_counts, ws->expert_offsets, ws->x_perm, nullptr,
-                              nullptr, ws->row_map, stream);
+                              nullptr, ws->row_map, nullptr, stream);
   if (rc != COMFY_MOE_OK) return rc;
   rc = comfy_moe_grouped_gelu_mlp(L->n_experts, L->experts, &L->shared, ws->expert_offsets, ws->expert_counts,
                                   ws->rows_cap, n_tokens, L->dim, ws->x_perm, ws->h_perm, ws->y_perm, x, ws->h_shared,

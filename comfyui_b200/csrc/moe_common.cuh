@@ -52,4 +52,20 @@ __device__ __forceinline__ uint16_t f2_to_e4m3x2(float lo, float hi) {
   return static_cast<uint16_t>(__nv_cvt_float2_to_fp8x2(make_float2(lo, hi), __NV_SATFINITE, __NV_E4M3));
 }
 
+// The same conversion for a value the reference casts WITHOUT clamping first (comfy/ops.py:342-343, the branch taken
+// when the Linear has a scale_input): torch's cast to float8_e4m3fn does not saturate.  Everything that rounds past
+// 448, i.e. |v| > 464 (464 itself is the tie that still rounds to 448), and NaN become NaN, byte 0x7f with the sign
+// of the input.  `overflow` counts the elements this happened to.
+__device__ __forceinline__ uint16_t f2_to_e4m3x2_nosat(float lo, float hi, int& overflow) {
+  uint16_t r = f2_to_e4m3x2(lo, hi);
+  if (!(fabsf(lo) <= 464.f)) { r = (r & 0xff00u) | 0x7fu | ((__float_as_uint(lo) >> 24) & 0x80u); ++overflow; }
+  if (!(fabsf(hi) <= 464.f)) { r = (r & 0x00ffu) | 0x7f00u | ((__float_as_uint(hi) >> 16) & 0x8000u); ++overflow; }
+  return r;
+}
+
+// Layout of a status block (int32 [COMFY_MOE_STATUS_WORDS]).
+constexpr int kStatusWord = 0;          // sticky device status code
+constexpr int kStatusNearTies = 1;      // near-tie tokens of the last gate call
+constexpr int kStatusE4m3Overflow = 2;  // elements the no-clamp quantiser turned into NaN (accumulates)
+
 }  // namespace comfy_b200

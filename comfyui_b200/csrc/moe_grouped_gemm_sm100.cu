@@ -451,6 +451,20 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
             for (int j = 0; j < 8; ++j)
               w[j] = static_cast<uint32_t>(f2_to_e4m3x2(bf16x2_lo(hp[2 * j]), bf16x2_hi(hp[2 * j]))) |
                      (static_cast<uint32_t>(f2_to_e4m3x2(bf16x2_lo(hp[2 * j + 1]), bf16x2_hi(hp[2 * j + 1]))) << 16);
+            if (out_scaled) {
+              // w2 has a scale_input: the reference casts h * (1 / scale) without a clamp, so what lies beyond the e4m3
+              // range is NaN there.  Rare by construction; the saturated bytes are patched only when a value qualifies.
+              int ovf = 0;
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                const float lo = bf16x2_lo(hp[j]), hi = bf16x2_hi(hp[j]);
+                if (!(fabsf(lo) <= 464.f) || !(fabsf(hi) <= 464.f)) {
+                  const uint32_t pair = f2_to_e4m3x2_nosat(lo, hi, ovf);
+                  w[j >> 1] = (j & 1) ? ((w[j >> 1] & 0x0000ffffu) | (pair << 16)) : ((w[j >> 1] & 0xffff0000u) | pair);
+                }
+              }
+              if (ovf && valid) atomicAdd(p.status + kStatusE4m3Overflow, ovf);
+            }
             if (tile_tma) {
               // one 128-byte row per tile row: this chunk is pieces 2c and 2c+1
               *reinterpret_cast<uint4*>(stage_row + (((2 * c) ^ sw) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);

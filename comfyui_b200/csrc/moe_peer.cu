@@ -172,6 +172,7 @@ dispatch_kernel(const __grid_constant__ PeerParams p, const __nv_bfloat16* __res
     if (x_q_scale) { inv_q = round_bf16(1.0f / __ldg(x_q_scale)); scaled_q = true; }
     const bool same_q = (scaled_q == scaled_p) && (inv_q == inv_p);
     uint8_t* xq = static_cast<uint8_t*>(x_q);
+    int ovf = 0;
     constexpr int kTok8 = 4;
     for (int base = 0; base < kTokensPerBlock; base += kTok8) {
       const int t0 = block_tok0 + base;
@@ -201,13 +202,21 @@ dispatch_kernel(const __grid_constant__ PeerParams p, const __nv_bfloat16* __res
           float g[4];
 #pragma unroll
           for (int m = 0; m < 4; ++m) g[m] = scaled_p ? round_bf16(f[4 * k + m] * inv_p) : f[4 * k + m];
-          wp[k] = static_cast<uint32_t>(f2_to_e4m3x2(g[0], g[1])) | (static_cast<uint32_t>(f2_to_e4m3x2(g[2], g[3])) << 16);
+          wp[k] = scaled_p ? (static_cast<uint32_t>(f2_to_e4m3x2_nosat(g[0], g[1], ovf)) |
+                              (static_cast<uint32_t>(f2_to_e4m3x2_nosat(g[2], g[3], ovf)) << 16))
+                           : (static_cast<uint32_t>(f2_to_e4m3x2(g[0], g[1])) |
+                              (static_cast<uint32_t>(f2_to_e4m3x2(g[2], g[3])) << 16));
           if (same_q) {
             wq[k] = wp[k];
           } else {
+            int ovf_q = 0;
 #pragma unroll
             for (int m = 0; m < 4; ++m) g[m] = scaled_q ? round_bf16(f[4 * k + m] * inv_q) : f[4 * k + m];
-            wq[k] = static_cast<uint32_t>(f2_to_e4m3x2(g[0], g[1])) | (static_cast<uint32_t>(f2_to_e4m3x2(g[2], g[3])) << 16);
+            wq[k] = scaled_q ? (static_cast<uint32_t>(f2_to_e4m3x2_nosat(g[0], g[1], ovf_q)) |
+                                (static_cast<uint32_t>(f2_to_e4m3x2_nosat(g[2], g[3], ovf_q)) << 16))
+                             : (static_cast<uint32_t>(f2_to_e4m3x2(g[0], g[1])) |
+                                (static_cast<uint32_t>(f2_to_e4m3x2(g[2], g[3])) << 16));
+            if (xq) ovf += ovf_q;
           }
         }
         const uint4 vp = make_uint4(wp[0], wp[1], wp[2], wp[3]);
@@ -221,6 +230,7 @@ dispatch_kernel(const __grid_constant__ PeerParams p, const __nv_bfloat16* __res
         if (xq) reinterpret_cast<uint4*>(xq + static_cast<size_t>(t0 + i) * dim)[tid] = make_uint4(wq[0], wq[1], wq[2], wq[3]);
       }
     }
+    if (ovf) atomicAdd(status + kStatusE4m3Overflow, ovf);
   }
 }
 
@@ -366,15 +376,19 @@ extern "C" int comfy_moe_ep_signal(const ComfyMoePeerPlan* plan, int kind, uint3
   return check_launch();
 }
 
-extern "C" int comfy_moe_ep_wait(const ComfyMoePeerPlan* plan, int kind, uint32_t epoch, int32_t* status,
-                                 void* stream) {
+extern "C" int comfy_moe_ep_wait_budget(const ComfyMoePeerPlan* plan, int kind, uint32_t epoch, int64_t budget_cycles,
+                                        int32_t* status, void* stream) {
   PeerParams p;
   int rc = fill_params(plan, &p);
   if (rc != COMFY_MOE_OK) return rc;
-  if (kind < 0 || kind > 1 || !status) return COMFY_MOE_EINVAL;
-  const long long budget = 4000000000LL;      // about two seconds of SM clocks
-  peer_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(p, kind, epoch, budget, status);
+  if (kind < 0 || kind > 1 || !status || budget_cycles <= 0) return COMFY_MOE_EINVAL;
+  peer_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(p, kind, epoch, budget_cycles, status);
   return check_launch();
+}
+
+extern "C" int comfy_moe_ep_wait(const ComfyMoePeerPlan* plan, int kind, uint32_t epoch, int32_t* status,
+                                 void* stream) {
+  return comfy_moe_ep_wait_budget(plan, kind, epoch, COMFY_MOE_EP_WAIT_CYCLES, status, stream);
 }
 
 extern "C" int comfy_moe_ep_combine(const ComfyMoePeerPlan* plan, const int32_t* topk_idx, const int32_t* row_map,

@@ -231,7 +231,8 @@ permute_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ 
                int n_tokens, int dim, int n_experts, const float* __restrict__ act_scale,
                void* __restrict__ x_perm, void* __restrict__ x_q, const float* __restrict__ x_q_scale,
                int32_t* __restrict__ row_map, const int32_t* __restrict__ block_counts, int n_blocks,
-               int32_t* __restrict__ expert_counts_out, int32_t* __restrict__ expert_offsets_out) {
+               int32_t* __restrict__ expert_counts_out, int32_t* __restrict__ expert_offsets_out,
+               int32_t* __restrict__ overflow_count) {
   constexpr int kSlots = kTokensPerBlock * 2;  // 64
   constexpr int kTok = 8;
   __shared__ int dest_s[kSlots];
@@ -337,6 +338,7 @@ permute_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ 
     const bool same_q = (scaled_q == scaled_p) && (inv_q == inv_p);
     uint8_t* xp = static_cast<uint8_t*>(x_perm);
     uint8_t* xq = static_cast<uint8_t*>(x_q);
+    int ovf = 0;                 // elements the reference's unclamped cast turns into NaN (scaled variants only)
     constexpr int kTok8 = 4;
     for (int base = 0; base < kTokensPerBlock; base += kTok8) {
       const int t0 = block_tok0 + base;
@@ -366,15 +368,21 @@ permute_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ 
           float g[4];
 #pragma unroll
           for (int m = 0; m < 4; ++m) g[m] = scaled_p ? round_bf16(f[4 * k + m] * inv_p) : f[4 * k + m];
-          wp[k] = static_cast<uint32_t>(f2_to_e4m3x2(g[0], g[1])) |
-                  (static_cast<uint32_t>(f2_to_e4m3x2(g[2], g[3])) << 16);
+          wp[k] = scaled_p ? (static_cast<uint32_t>(f2_to_e4m3x2_nosat(g[0], g[1], ovf)) |
+                              (static_cast<uint32_t>(f2_to_e4m3x2_nosat(g[2], g[3], ovf)) << 16))
+                           : (static_cast<uint32_t>(f2_to_e4m3x2(g[0], g[1])) |
+                              (static_cast<uint32_t>(f2_to_e4m3x2(g[2], g[3])) << 16));
           if (same_q) {
             wq[k] = wp[k];
           } else {
+            int ovf_q = 0;       // the shared expert's copy: counted only when no routed copy is made of the same value
 #pragma unroll
             for (int m = 0; m < 4; ++m) g[m] = scaled_q ? round_bf16(f[4 * k + m] * inv_q) : f[4 * k + m];
-            wq[k] = static_cast<uint32_t>(f2_to_e4m3x2(g[0], g[1])) |
-                    (static_cast<uint32_t>(f2_to_e4m3x2(g[2], g[3])) << 16);
+            wq[k] = scaled_q ? (static_cast<uint32_t>(f2_to_e4m3x2_nosat(g[0], g[1], ovf_q)) |
+                                (static_cast<uint32_t>(f2_to_e4m3x2_nosat(g[2], g[3], ovf_q)) << 16))
+                             : (static_cast<uint32_t>(f2_to_e4m3x2(g[0], g[1])) |
+                                (static_cast<uint32_t>(f2_to_e4m3x2(g[2], g[3])) << 16));
+            if (xq) ovf += ovf_q;
           }
         }
         const uint4 vp = make_uint4(wp[0], wp[1], wp[2], wp[3]);
@@ -384,6 +392,7 @@ permute_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ 
         if (xq) reinterpret_cast<uint4*>(xq + static_cast<size_t>(t0 + i) * dim)[tid] = make_uint4(wq[0], wq[1], wq[2], wq[3]);
       }
     }
+    if (ovf && overflow_count) atomicAdd(overflow_count, ovf);
   }
 }
 
@@ -466,7 +475,7 @@ extern "C" int comfy_moe_route_plan(const int32_t* block_counts, int n_tokens, i
 extern "C" int comfy_moe_permute(const void* x, const int32_t* topk_idx, const int32_t* block_offsets,
                                  const int32_t* expert_offsets, int n_tokens, int dim, int n_experts,
                                  int act_dtype, const float* act_scale, void* x_perm, void* x_q,
-                                 const float* x_q_scale, int32_t* row_map, void* stream) {
+                                 const float* x_q_scale, int32_t* row_map, int32_t* overflow_count, void* stream) {
   if (n_tokens < 0 || dim <= 0 || n_experts < 1 || n_experts > kMaxExperts) return COMFY_MOE_EINVAL;
   if (n_tokens == 0) return COMFY_MOE_OK;
   if (!x || !topk_idx || !block_offsets || !expert_offsets || !x_perm || !row_map) return COMFY_MOE_EINVAL;
@@ -478,12 +487,12 @@ extern "C" int comfy_moe_permute(const void* x, const int32_t* topk_idx, const i
     if ((dim & 7) != 0) return COMFY_MOE_EUNSUPPORTED;
     permute_kernel<false, false><<<n_blocks, row_threads(dim), 0, s>>>(
         static_cast<const __nv_bfloat16*>(x), topk_idx, block_offsets, expert_offsets, n_tokens, dim, n_experts, nullptr,
-        x_perm, nullptr, nullptr, row_map, nullptr, 0, nullptr, nullptr);
+        x_perm, nullptr, nullptr, row_map, nullptr, 0, nullptr, nullptr, nullptr);
   } else if (act_dtype == COMFY_MOE_FP8_E4M3) {
     if ((dim & 15) != 0) return COMFY_MOE_EUNSUPPORTED;
     permute_kernel<true, false><<<n_blocks, row_threads(dim), 0, s>>>(
         static_cast<const __nv_bfloat16*>(x), topk_idx, block_offsets, expert_offsets, n_tokens, dim, n_experts,
-        act_scale, x_perm, x_q, x_q_scale, row_map, nullptr, 0, nullptr, nullptr);
+        act_scale, x_perm, x_q, x_q_scale, row_map, nullptr, 0, nullptr, nullptr, overflow_count);
   } else {
     return COMFY_MOE_EUNSUPPORTED;
   }
@@ -495,7 +504,8 @@ extern "C" int comfy_moe_permute(const void* x, const int32_t* topk_idx, const i
 extern "C" int comfy_moe_plan_permute(const void* x, const int32_t* topk_idx, const int32_t* block_counts,
                                       int n_tokens, int dim, int n_experts, int act_dtype, const float* act_scale,
                                       int32_t* block_offsets_scratch, int32_t* expert_counts, int32_t* expert_offsets,
-                                      void* x_perm, void* x_q, const float* x_q_scale, int32_t* row_map, void* stream) {
+                                      void* x_perm, void* x_q, const float* x_q_scale, int32_t* row_map,
+                                      int32_t* overflow_count, void* stream) {
   if (n_tokens < 0 || dim <= 0 || n_experts < 1 || n_experts > kMaxExperts) return COMFY_MOE_EINVAL;
   if (!expert_counts || !expert_offsets) return COMFY_MOE_EINVAL;
   const int n_blocks = (n_tokens + kTokensPerBlock - 1) / kTokensPerBlock;
@@ -505,7 +515,7 @@ extern "C" int comfy_moe_plan_permute(const void* x, const int32_t* topk_idx, co
                                   expert_offsets, stream);
     if (rc != COMFY_MOE_OK) return rc;
     return comfy_moe_permute(x, topk_idx, block_offsets_scratch, expert_offsets, n_tokens, dim, n_experts, act_dtype,
-                             act_scale, x_perm, x_q, x_q_scale, row_map, stream);
+                             act_scale, x_perm, x_q, x_q_scale, row_map, overflow_count, stream);
   }
   if (!x || !topk_idx || !block_counts || !x_perm || !row_map) return COMFY_MOE_EINVAL;
   if (!aligned16(x) || !aligned16(x_perm) || (x_q && !aligned16(x_q))) return COMFY_MOE_EINVAL;
@@ -517,13 +527,13 @@ extern "C" int comfy_moe_plan_permute(const void* x, const int32_t* topk_idx, co
     permute_kernel<false, true><<<n_blocks, row_threads(dim), 0, s>>>(xp, topk_idx, nullptr, nullptr, n_tokens, dim,
                                                                        n_experts, nullptr, x_perm, nullptr, nullptr,
                                                                        row_map, block_counts, n_blocks, expert_counts,
-                                                                       expert_offsets);
+                                                                       expert_offsets, nullptr);
   } else if (act_dtype == COMFY_MOE_FP8_E4M3) {
     if ((dim & 15) != 0) return COMFY_MOE_EUNSUPPORTED;
     permute_kernel<true, true><<<n_blocks, row_threads(dim), 0, s>>>(xp, topk_idx, nullptr, nullptr, n_tokens, dim,
                                                                       n_experts, act_scale, x_perm, x_q, x_q_scale,
                                                                       row_map, block_counts, n_blocks, expert_counts,
-                                                                      expert_offsets);
+                                                                      expert_offsets, overflow_count);
   } else {
     return COMFY_MOE_EUNSUPPORTED;
   }
@@ -579,5 +589,5 @@ extern "C" int comfy_moe_route_static(const void* x, const void* w_gate, int w_d
   rc = comfy_moe_route_plan(block_counts, n_tokens, n_experts, block_offsets, expert_counts, expert_offsets, stream);
   if (rc != COMFY_MOE_OK) return rc;
   return comfy_moe_permute(x, topk_idx, block_offsets, expert_offsets, n_tokens, dim, n_experts, act_dtype, act_scale,
-                           x_perm, x_q, x_q_scale, row_map, stream);
+                           x_perm, x_q, x_q_scale, row_map, nullptr, stream);
 }

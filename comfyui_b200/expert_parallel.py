@@ -120,6 +120,18 @@ class CudaKernels:
                                                   scale_in2=full.scale_in2))
         self.fp8 = self.shared.w1.dtype == torch.float8_e4m3fn
         self._limited = {}
+        if self.fp8:
+            # every rank quantises the rows it sends with ONE activation scale, and the expert's rank dequantises with
+            # its own scale_input: all routed experts (local or not) must therefore carry the same scale_input
+            scales = []
+            for e in range(self.n_experts):
+                pack = ops._ffn_pack(module.experts[e], dev, moe_ops)
+                if pack is None:
+                    raise ValueError(f"expert {e} weights are not eligible for the sm_100a kernels")
+                scales.append(None if pack.scale_in13 is None else float(pack.scale_in13))
+            if len(set(scales)) != 1:
+                raise ValueError("expert-parallel fp8 needs one scale_input shared by w1/w3 of all routed experts "
+                                 f"(found {scales}): the dispatch quantises each row once for whichever rank computes it")
         if self.fp8 and not allow_fp8:
             raise ValueError("the NCCL transport covers bf16 weights; scaled fp8 runs on the peer-memory transport")
 
@@ -480,12 +492,14 @@ class PeerExpertParallelMoE:
                 counts=torch.empty((e,), **i32), offsets=torch.empty((e + 1,), **i32),
                 counts_all=torch.empty((world, e), **i32), row_map=torch.empty((n, 2), **i32),
                 groups=torch.zeros((3, n_groups), **i32),              # start, count, output row shift
-                status=torch.zeros((2,), **i32),                        # [0] device status, [1] near-tie count
+                status=torch.zeros((N.STATUS_WORDS,), **i32),           # device status, near-ties, e4m3 overflows
                 x_q=torch.empty((n, dim), dtype=act, device=device) if self.fp8 else None,
                 h_shared=torch.empty((max(n, 1), k.shared.hidden), dtype=act, device=device),
                 y_shared=torch.empty((max(n, 1), dim), dtype=torch.bfloat16, device=device),
                 h_ws=torch.empty((b.cap_rows, hidden), dtype=b.act_dtype, device=b.recv.device))
             PeerExpertParallelMoE._tensors[tkey] = t
+            moe_ops_status = self.M._status_words
+            moe_ops_status.add(t["status"])
         for name, value in t.items():
             setattr(sc, name, value)
         self._h_ws = t["h_ws"]
@@ -494,6 +508,7 @@ class PeerExpertParallelMoE:
                                                         "offsets", "counts_all", "row_map", "status", "x_q",
                                                         "h_shared", "y_shared")}
         sc.p["near"] = ctypes.c_void_p(sc.status.data_ptr() + 4)
+        sc.p["overflow"] = ctypes.c_void_p(sc.status.data_ptr() + 8)
         sc.p["g_start"], sc.p["g_count"], sc.p["g_shift"] = (P(sc.groups[i]) for i in range(3))
         sc.p["recv"], sc.p["y"], sc.p["h_ws"] = P(b.recv), P(b.y), P(self._h_ws)
         sc.p["ret0"] = P(b.ret[0])
@@ -543,7 +558,7 @@ class PeerExpertParallelMoE:
         sc = self._scratch(n, dim, x2.device)
         p = sc.p
         b.epoch += 1
-        sc.status.zero_()
+        sc.status[1:2].zero_()    # the near-tie counter only: the status word is sticky until check() has read it
         S = self._stream_ptr()
         px = ctypes.c_void_p(x2.data_ptr())
         if n > 0:
@@ -635,7 +650,8 @@ class PeerExpertParallelMoE:
         with torch.cuda.stream(side):
             if self.fp8:
                 self.N.check("comfy_moe_quantize_e4m3", self.lib.comfy_moe_quantize_e4m3(
-                    x2.data_ptr(), sc.p["in13_shared"], x2.numel(), sc.p["x_q"], self._stream_ptr()))
+                    x2.data_ptr(), sc.p["in13_shared"], x2.numel(), sc.p["x_q"],
+                    sc.p["overflow"], self._stream_ptr()))
             self._shared_expert(sc, sc.x_q if self.fp8 else x2, n, dim, limited=True)
         self.phase_route(x2, want_xq=False)
         main.wait_stream(side)

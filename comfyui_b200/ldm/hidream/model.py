@@ -44,6 +44,10 @@ class FeedForwardSwiGLU(nn.Module):
         self.w2 = operations.Linear(hidden_dim, dim, **make)
         self.w3 = operations.Linear(dim, hidden_dim, **make)
 
+    def _apply(self, fn, *args, **kwargs):
+        b200_ops.drop_packs(self)       # .to() / .cuda() / .cpu() replace the weights the packs point into
+        return super()._apply(fn, *args, **kwargs)
+
     def forward(self, x):
         fast = b200_ops.swiglu_ffn_forward(self, x)
         if fast is not None:
@@ -102,6 +106,10 @@ class MOEFeedForwardSwiGLU(nn.Module):
         self.gate = MoEGate(embed_dim=dim, num_routed_experts=num_routed_experts,
                             num_activated_experts=num_activated_experts, **kw)
         self.num_activated_experts = num_activated_experts
+
+    def _apply(self, fn, *args, **kwargs):
+        b200_ops.drop_packs(self)
+        return super()._apply(fn, *args, **kwargs)
 
     def forward(self, x):
         fast = b200_ops.hidream_moe_forward(self, x)

@@ -54,6 +54,10 @@ class FeedForward(nn.Module):
             operations.Linear(inner_dim, dim_out, device=device, dtype=dtype),
         ])
 
+    def _apply(self, fn, *args, **kwargs):
+        b200_ops.drop_packs(self)       # .to() / .cuda() / .cpu() replace the weights the packs point into
+        return super()._apply(fn, *args, **kwargs)
+
     def forward(self, hidden_states: torch.Tensor) -> torch.Tensor:
         if not (self.training and self.net[1].p > 0):
             fast = b200_ops.gelu_ffn_forward(self, hidden_states)
@@ -122,6 +126,10 @@ class MoEBlock(nn.Module):
         self.experts = nn.ModuleList([FeedForward(dim, **kw) for _ in range(num_experts)])
         self.gate = MoEGate(dim, num_experts=num_experts, num_experts_per_tok=moe_top_k, device=device, dtype=dtype)
         self.shared_experts = FeedForward(dim, **kw)
+
+    def _apply(self, fn, *args, **kwargs):
+        b200_ops.drop_packs(self)       # .to() / .cuda() / .cpu() replace the weights the packs point into
+        return super()._apply(fn, *args, **kwargs)
 
     def forward(self, hidden_states) -> torch.Tensor:
         fast = b200_ops.hunyuan3d_moe_forward(self, hidden_states)

@@ -8,6 +8,7 @@ implementation behind it.
 from __future__ import annotations
 
 import ctypes
+import weakref
 from dataclasses import dataclass, field
 from typing import List, Optional, Sequence, Tuple
 
@@ -40,6 +41,30 @@ def _need_cuda(*tensors: Optional[torch.Tensor]) -> None:
     for t in tensors:
         if t is not None and not t.is_cuda:
             raise ValueError("the sm_100a kernels need CUDA tensors; there is no CPU path")
+
+
+# Status words (int32 [2]: [0] the sticky device status word, [1] a near-tie counter) that calls of this module
+# have used and nobody has dropped yet; check_all_status() reads them all.
+_status_words = weakref.WeakSet()
+_device_status = {}
+
+
+def device_status(device) -> torch.Tensor:
+    """The status word shared by every call on `device` that brings no workspace of its own (dense feed-forwards)."""
+    key = str(device)
+    st = _device_status.get(key)
+    if st is None:
+        st = torch.zeros((N.STATUS_WORDS,), dtype=torch.int32, device=device)
+        _device_status[key] = st
+        _status_words.add(st)
+    return st
+
+
+def check_all_status() -> None:
+    """Reads every live status word (one stream synchronisation each) and raises for the first code found.  Status
+    words are sticky, so calling this once after a model forward covers every layer of it."""
+    for st in list(_status_words):
+        read_status(st)
 
 
 def plan_sizes(n_tokens: int, n_experts: int, top_k: int = 2) -> Tuple[int, int]:
@@ -159,7 +184,8 @@ class Workspace:
         self.expert_counts = torch.zeros((n_experts,), **i32)
         self.expert_offsets = torch.zeros((n_experts + 1,), **i32)
         self.row_map = torch.empty((n_tokens, top_k), **i32)
-        self.status = torch.zeros((2,), **i32)
+        self.status = torch.zeros((N.STATUS_WORDS,), **i32)
+        _status_words.add(self.status)
         self.x_perm = torch.empty((rows_cap, dim), dtype=act, device=device)
         self.x_q = torch.empty((n_tokens, dim), dtype=act, device=device) if fp8 else None
         self.h_perm = torch.empty((rows_cap, hidden), dtype=act, device=device)
@@ -250,8 +276,10 @@ def route_plan(block_counts: torch.Tensor, n_tokens: int, n_experts: int):
 
 def permute(x: torch.Tensor, topk_idx: torch.Tensor, block_offsets: torch.Tensor, expert_offsets: torch.Tensor,
             n_experts: int, *, fp8: bool = False, act_scale: Optional[torch.Tensor] = None,
-            xq_scale: Optional[torch.Tensor] = None, want_xq: bool = False, zero_fill: bool = False):
-    """Row permutation into per-expert blocks.  Returns (x_perm, row_map, x_q or None)."""
+            xq_scale: Optional[torch.Tensor] = None, want_xq: bool = False, zero_fill: bool = False,
+            overflow_count: Optional[torch.Tensor] = None):
+    """Row permutation into per-expert blocks.  Returns (x_perm, row_map, x_q or None).  ``overflow_count`` (int32 [1],
+    fp8 with a scale only) grows by the number of elements the reference's unclamped cast turns into NaN."""
     _need_cuda(x, topk_idx)
     n, d = x.shape
     rows_cap, _ = plan_sizes(n, n_experts)
@@ -263,7 +291,7 @@ def permute(x: torch.Tensor, topk_idx: torch.Tensor, block_offsets: torch.Tensor
     x_q = torch.empty((n, d), dtype=_FP8, device=x.device) if (fp8 and want_xq) else None
     rc = N.load().comfy_moe_permute(_ptr(x), _ptr(topk_idx), _ptr(block_offsets), _ptr(expert_offsets), n, d,
                                     n_experts, N.FP8_E4M3 if fp8 else N.BF16, _ptr(act_scale), _ptr(x_perm),
-                                    _ptr(x_q), _ptr(xq_scale), _ptr(row_map), _stream())
+                                    _ptr(x_q), _ptr(xq_scale), _ptr(row_map), _ptr(overflow_count), _stream())
     N.check("comfy_moe_permute", rc)
     return x_perm, row_map, x_q
 
@@ -284,7 +312,7 @@ def plan_permute(x: torch.Tensor, topk_idx: torch.Tensor, block_counts: torch.Te
     offsets = torch.empty((n_experts + 1,), dtype=torch.int32, device=dev)
     rc = N.load().comfy_moe_plan_permute(_ptr(x), _ptr(topk_idx), _ptr(block_counts), n, d, n_experts,
                                          N.FP8_E4M3 if fp8 else N.BF16, None, _ptr(scratch), _ptr(counts),
-                                         _ptr(offsets), _ptr(x_perm), None, None, _ptr(row_map), _stream())
+                                         _ptr(offsets), _ptr(x_perm), None, None, _ptr(row_map), None, _stream())
     N.check("comfy_moe_plan_permute", rc)
     return x_perm, row_map, counts, offsets
 
@@ -293,12 +321,13 @@ def grouped_swiglu(experts: Sequence[FfnPack], shared: Optional[FfnPack], row_st
                    row_count: Optional[torch.Tensor], x_perm: Optional[torch.Tensor],
                    x_shared: Optional[torch.Tensor], *, status: Optional[torch.Tensor] = None,
                    check_status: bool = True, h_perm: Optional[torch.Tensor] = None,
-                   y_perm: Optional[torch.Tensor] = None):
+                   y_perm: Optional[torch.Tensor] = None, h_shared: Optional[torch.Tensor] = None,
+                   y_shared: Optional[torch.Tensor] = None):
     """Both passes of the grouped expert GEMM.  Group g = rows [row_start[g], row_start[g] + row_count[g]) of
     x_perm with the weights experts[g] (int32 device tensors; the routing plan's expert_offsets and
     expert_counts on one GPU).  ``h_perm`` / ``y_perm`` may be given (buffers of x_perm's row count, e.g. a result
-    buffer that peers read); otherwise they are allocated.  Returns (y_perm or None, y_shared or None, h_perm,
-    h_shared)."""
+    buffer that peers read), and so may ``h_shared`` / ``y_shared`` ([n_tokens, hidden_s] / [n_tokens, dim]);
+    otherwise they are allocated.  Returns (y_perm or None, y_shared or None, h_perm, h_shared)."""
     ref = experts[0] if experts else shared
     dim, fp8 = ref.dim, ref.w1.dtype == _FP8
     dev = ref.w1.device
@@ -322,10 +351,13 @@ def grouped_swiglu(experts: Sequence[FfnPack], shared: Optional[FfnPack], row_st
     sh = h_sh = y_sh = None
     if shared is not None and n_tokens > 0:
         sh = shared.struct()
-        h_sh = torch.empty((n_tokens, shared.hidden), dtype=act, device=dev)
-        y_sh = torch.empty((n_tokens, dim), dtype=torch.bfloat16, device=dev)
+        h_sh = h_shared if h_shared is not None else torch.empty((n_tokens, shared.hidden), dtype=act, device=dev)
+        y_sh = y_shared if y_shared is not None else torch.empty((n_tokens, dim), dtype=torch.bfloat16, device=dev)
+        if h_sh.shape != (n_tokens, shared.hidden) or y_sh.shape != (n_tokens, dim) or not h_sh.is_contiguous() or \
+                not y_sh.is_contiguous():
+            raise ValueError("h_shared / y_shared must be contiguous [n_tokens, hidden] / [n_tokens, dim] buffers")
     if status is None:
-        status = torch.zeros((2,), dtype=torch.int32, device=dev)
+        status = device_status(dev)
     rc = N.load().comfy_moe_grouped_swiglu(
         N.FP8_E4M3 if fp8 else N.BF16, n_e, arr, ctypes.byref(sh) if sh is not None else None,
         _ptr(row_start), _ptr(row_count), rows_cap, n_tokens, dim, _ptr(x_perm), _ptr(h_perm), _ptr(y_perm), _ptr(x_shared),
@@ -376,14 +408,19 @@ def combine(y_perm: torch.Tensor, row_map: torch.Tensor, topk_weight: torch.Tens
     return out
 
 
-def quantize_e4m3(x: torch.Tensor, scale: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """bf16 -> e4m3 as the reference's fp8 Linear quantises its input (optional bf16(1/scale) multiply, clamp, RNE)."""
+def quantize_e4m3(x: torch.Tensor, scale: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+                  overflow_count: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """bf16 -> e4m3 as the reference's fp8 Linear quantises its input: clamp and round without a scale; multiply by
+    bf16(1 / scale) and cast without a clamp (overflow -> NaN, counted in ``overflow_count`` int32 [1]) with one."""
     _need_cuda(x, scale)
     if x.dtype != torch.bfloat16 or not x.is_contiguous():
         raise ValueError("x must be a contiguous bf16 tensor")
     if out is None:
         out = torch.empty(x.shape, dtype=_FP8, device=x.device)
-    N.check("comfy_moe_quantize_e4m3", N.load().comfy_moe_quantize_e4m3(_ptr(x), _ptr(scale), x.numel(), _ptr(out), _stream()))
+    if overflow_count is None:
+        overflow_count = device_status(x.device)[2:3]
+    N.check("comfy_moe_quantize_e4m3", N.load().comfy_moe_quantize_e4m3(_ptr(x), _ptr(scale), x.numel(), _ptr(out),
+                                                                        _ptr(overflow_count), _stream()))
     return out
 
 
@@ -567,7 +604,7 @@ def grouped_gelu_mlp(experts: Sequence[MlpPack], shared: Optional[MlpPack], row_
         sh = shared.struct()
         h_sh = torch.empty((n_tokens, shared.hidden), dtype=torch.bfloat16, device=dev)
         y_sh = torch.empty((n_tokens, dim), dtype=torch.bfloat16, device=dev)
-    status = torch.zeros((2,), dtype=torch.int32, device=dev)
+    status = device_status(dev)
     rc = N.load().comfy_moe_grouped_gelu_mlp(
         n_e, arr, ctypes.byref(sh) if sh is not None else None, _ptr(row_start), _ptr(row_count), rows_cap, n_tokens,
         dim, _ptr(x_perm), _ptr(h_perm), _ptr(y_perm), _ptr(x_shared), _ptr(h_sh), _ptr(y_sh), _ptr(status), _stream())

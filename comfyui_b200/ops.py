@@ -442,6 +442,15 @@ def _workspace(layer, n_tokens: int):
     return torch_ops._workspace(layer, n_tokens)
 
 
+def check_device_status() -> None:
+    """Synchronises and raises ``MoeError`` if any kernel call since the last check left a code in a device status
+    word (a bounded wait that ran out, routed rows that did not fit a peer buffer).  The words are sticky, so one call
+    at a natural synchronisation point, e.g. after a model forward, covers every layer that ran."""
+    from . import moe_ops
+
+    moe_ops.check_all_status()
+
+
 def release_workspaces() -> None:
     """Drop the cached device workspaces (they are shared by every MoE layer of a model)."""
     from . import torch_ops
@@ -455,9 +464,19 @@ def _op_args(layer):
 
     args = getattr(layer, "_op_args", None)
     if args is None:
-        args = torch_ops.layer_args(layer)
+        args = torch_ops.register(layer)
         layer._op_args = args
     return args
+
+
+def drop_packs(module) -> None:
+    """Forgets the pointer packs cached on a module tree (they hold views of the weights they were built from, i.e.
+    keep that device memory alive).  The drop-in modules call this from ``_apply``, so ``model.to(offload_device)``,
+    which is how a model patcher unloads a model, frees the expert weights at once; after replacing Parameters by
+    hand, call it (or just call the module again: stale packs are replaced on the next call)."""
+    for m in module.modules():
+        m.__dict__.pop("_b200_pack", None)
+        m.__dict__.pop("_b200_layer", None)
 
 
 def hidream_moe_forward(moe, x: torch.Tensor) -> Optional[torch.Tensor]:
@@ -655,7 +674,7 @@ def hunyuan3d_moe_forward(moe, x: torch.Tensor) -> Optional[torch.Tensor]:
 
     args = getattr(layer, "_op_args", None)
     if args is None:
-        args = torch_ops.mlp_layer_args(layer)
+        args = torch_ops.register(layer)
         layer._op_args = args
     x2 = x.view(-1, x.shape[-1])
     out = torch.ops.comfyui_b200.hunyuan3d_moe(x2, layer.gate, *args)

@@ -11,14 +11,28 @@ plus ``scale_in13`` / ``scale_in2`` (either empty, or E + 1 entries).
 """
 from __future__ import annotations
 
+import weakref
+from collections import OrderedDict
 from typing import List, Optional, Sequence
 
 import torch
 
 from . import moe_ops
 
-_packs = {}
-_PACK_SLOTS = 128      # a HiDream model has 48 MoE layers
+# Packs (ctypes structs + the tensors they point into) by the identity and version of every tensor.  The packs the
+# dispatch shim builds belong to their module (cached on it, dropped with it, or when its weights move); this table
+# only finds them again from the operator's tensor arguments and must not keep them, or their weights, alive: after a
+# model has been unloaded its expert weights (23 GB for a HiDream-I1) would otherwise stay on the GPU.  Packs made for
+# direct calls of the operators (no module behind them) are kept in a two-entry table of their own.
+_packs = weakref.WeakValueDictionary()
+_direct_packs = OrderedDict()
+_DIRECT_SLOTS = 2
+
+
+def _remember(table: OrderedDict, key, value) -> None:
+    while len(table) >= _DIRECT_SLOTS:
+        table.popitem(last=False)
+    table[key] = value
 
 
 def _key(tensors: Sequence[torch.Tensor]):
@@ -40,10 +54,21 @@ def _layer(gate, w1, w3, w2, scale_w1, scale_w3, scale_w2, scale_in13, scale_in2
                             scale_w2=_opt(scale_w2, i), scale_in13=_opt(scale_in13, i), scale_in2=_opt(scale_in2, i))
             for i in range(len(w1))]
     layer = moe_ops.LayerPack(gate, ffns[:-1], ffns[-1], top_k=2)
-    while len(_packs) >= _PACK_SLOTS:
-        _packs.pop(next(iter(_packs)))
     _packs[key] = layer
+    _remember(_direct_packs, key, layer)
     return layer
+
+
+def register(layer) -> tuple:
+    """Makes a pack the dispatch shim built findable from the operator's arguments (without keeping it alive) and
+    returns those list arguments."""
+    if isinstance(layer, moe_ops.MlpLayerPack):
+        args = mlp_layer_args(layer)
+        _mlp_packs[_key([layer.gate, *args[0], *args[1], *args[2], *args[3]])] = layer
+    else:
+        args = layer_args(layer)
+        _packs[_key([layer.gate] + [t for lst in args for t in lst])] = layer
+    return args
 
 
 _workspaces = {}
@@ -62,9 +87,12 @@ def _workspace(layer: moe_ops.LayerPack, n_tokens: int) -> moe_ops.Workspace:
 
 
 def release_workspaces() -> None:
+    """Drops the device workspaces (0.5 GB at 8192 tokens, shared by all layers) and every pack this module holds."""
     _workspaces.clear()
     _packs.clear()
+    _direct_packs.clear()
     _mlp_packs.clear()
+    _direct_mlp_packs.clear()
 
 
 @torch.library.custom_op("comfyui_b200::hidream_moe", mutates_args=())
@@ -112,7 +140,8 @@ def _(x, gate):
     return [x.new_empty((n, 2), dtype=torch.int64), x.new_empty((n, 2), dtype=torch.float32)]
 
 
-_mlp_packs = {}
+_mlp_packs = weakref.WeakValueDictionary()
+_direct_mlp_packs = OrderedDict()
 
 
 def _mlp_layer(gate, w1, b1, w2, b2) -> moe_ops.MlpLayerPack:
@@ -123,9 +152,8 @@ def _mlp_layer(gate, w1, b1, w2, b2) -> moe_ops.MlpLayerPack:
         return hit
     ffns = [moe_ops.MlpPack(w1[i], _opt(b1, i), w2[i], _opt(b2, i)) for i in range(len(w1))]
     layer = moe_ops.MlpLayerPack(gate, ffns[:-1], ffns[-1], top_k=2)
-    while len(_mlp_packs) >= _PACK_SLOTS:
-        _mlp_packs.pop(next(iter(_mlp_packs)))
     _mlp_packs[key] = layer
+    _remember(_direct_mlp_packs, key, layer)
     return layer
 
 
@@ -160,7 +188,12 @@ def layer_args(layer: moe_ops.LayerPack):
 
     def col(name):
         vals = [getattr(f, name) for f in ffns]
-        return [] if any(v is None for v in vals) else vals
+        if all(v is None for v in vals):
+            return []
+        if any(v is None for v in vals):
+            raise ValueError(f"{name} is set on some feed-forwards of the layer and missing on others: the operator's "
+                             "list arguments cannot express that")
+        return vals
 
     return ([f.w1 for f in ffns], [f.w3 for f in ffns], [f.w2 for f in ffns], col("scale_w1"), col("scale_w3"),
             col("scale_w2"), col("scale_in13"), col("scale_in2"))

@@ -26,7 +26,7 @@
 extern "C" {
 #endif
 
-#define COMFY_MOE_ABI_VERSION 8
+#define COMFY_MOE_ABI_VERSION 9
 
 /* Return codes. */
 #define COMFY_MOE_OK 0
@@ -48,6 +48,10 @@ extern "C" {
 /* Tokens handled by one thread block of the gate / permute kernels (fixes the block-count scratch size). */
 #define COMFY_MOE_TOKENS_PER_BLOCK 32
 #define COMFY_MOE_MAX_EXPERTS 8
+/* A status block is this many int32 words: [0] the sticky device status word (see comfy_moe_read_status), [1] tokens
+ * the last gate call flagged as near-ties, [2] elements that the activation quantiser turned into NaN because the
+ * reference casts them to e4m3 without a clamp (accumulates; see comfy_moe_permute), [3] reserved. */
+#define COMFY_MOE_STATUS_WORDS 4
 /* Largest token count comfy_moe_route_static accepts (its scratch is a fixed array inside the library). */
 #define COMFY_MOE_STATIC_MAX_TOKENS 131072
 
@@ -94,17 +98,21 @@ int comfy_moe_route_plan(const int32_t* block_counts, int n_tokens, int n_expert
 /* ---- permutation: replaces x[exp_token_idx] gathers (model.py:338-339) ------------------------------
  * Copies row t of x to row row_map[t*2+k] of x_perm for k = 0,1; order inside an expert block is by slot index
  * (stable), so the layout is reproducible run to run.
- *   x_perm      [rows_cap, dim] in act_dtype: COMFY_MOE_BF16 copies; COMFY_MOE_FP8_E4M3 quantises as
- *               comfy/ops.py:338-343 does (clamp to +-448 then round-to-nearest-even when act_scale is NULL,
- *               else multiply by bf16(1 / *act_scale) in bf16 first; act_scale is the Linear's scale_input)
+ *   x_perm      [rows_cap, dim] in act_dtype: COMFY_MOE_BF16 copies; COMFY_MOE_FP8_E4M3 quantises exactly as
+ *               comfy/ops.py:338-343 does.  act_scale NULL (the Linear has no scale_input): clamp to +-448, then
+ *               round to nearest even (:339-340).  act_scale given: multiply by bf16(1 / *act_scale) in bf16 and cast
+ *               WITHOUT a clamp (:342-343); torch's cast does not saturate, so |v| > 464 and NaN become NaN (byte
+ *               0x7f | sign), here as there.
  *   x_q         only for fp8: [n_tokens, dim] e4m3, the un-permuted quantised copy the shared expert reads
  *               (x_q_scale: its own optional scale); may be NULL
  *   row_map     int32 [n_tokens, 2] out
+ *   overflow_count  int32 [1], may be NULL: incremented by the number of elements the unclamped cast turned into NaN
+ *               (never touched when both scales are NULL), so that such inputs are flagged, not only reproduced
  */
 int comfy_moe_permute(const void* x, const int32_t* topk_idx, const int32_t* block_offsets,
                       const int32_t* expert_offsets, int n_tokens, int dim, int n_experts, int act_dtype,
                       const float* act_scale, void* x_perm, void* x_q, const float* x_q_scale,
-                      int32_t* row_map, void* stream);
+                      int32_t* row_map, int32_t* overflow_count, void* stream);
 
 /* ---- routing plan and permutation in one launch: comfy_moe_route_plan + comfy_moe_permute -------------------
  * Same outputs (expert_counts, expert_offsets, x_perm, x_q, row_map).  Every block re-sums the per-block counts it
@@ -114,7 +122,7 @@ int comfy_moe_permute(const void* x, const int32_t* topk_idx, const int32_t* blo
 int comfy_moe_plan_permute(const void* x, const int32_t* topk_idx, const int32_t* block_counts, int n_tokens, int dim,
                            int n_experts, int act_dtype, const float* act_scale, int32_t* block_offsets_scratch,
                            int32_t* expert_counts, int32_t* expert_offsets, void* x_perm, void* x_q,
-                           const float* x_q_scale, int32_t* row_map, void* stream);
+                           const float* x_q_scale, int32_t* row_map, int32_t* overflow_count, void* stream);
 
 /* ---- gate + routing plan + permutation for callers that cannot allocate device memory -----------------
  * (No counterpart in the reference: it has no allocation-free mode.)
@@ -129,8 +137,10 @@ int comfy_moe_plan_permute(const void* x, const int32_t* topk_idx, const int32_t
  *             neartie_count (may be NULL; caller zeroes)                    exactly what the three calls produce
  * Limits and rules:
  *   - n_tokens <= COMFY_MOE_STATIC_MAX_TOKENS, else COMFY_MOE_ETOOLARGE (nothing is launched);
- *   - the first call on each device looks up the array's device address (one cudaGetSymbolAddress); make that
- *     first call outside any stream capture;
+ *   - the first call on each device looks up the array's device address (one cudaGetSymbolAddress) and keeps it for
+ *     the life of the process; make that first call outside any stream capture, and from one thread (the table of
+ *     addresses is filled without a lock; later calls only read it).  The address is not looked up again: after a
+ *     cudaDeviceReset in the same process it would be stale, so do not use this entry point across a device reset;
  *   - all calls on a device share the one array, so two calls that can overlap on the GPU (different streams
  *     without an ordering between them) race; keep them on one stream or order them with events.  Nothing in the
  *     array has to be cleared between calls: every word a call reads it has written itself.
@@ -169,7 +179,8 @@ typedef struct ComfyMoeFfnWeights {
  *   w_dtype        COMFY_MOE_BF16 or COMFY_MOE_FP8_E4M3 (activations x_perm / x_shared / h_* use the same)
  *   x_perm         [rows_cap, dim]        h_perm [rows_cap, hidden] workspace   y_perm bf16 [rows_cap, dim]
  *   x_shared       [n_tokens, dim]        h_shared [n_tokens, hidden_s]         y_shared bf16 [n_tokens, dim]
- *   status         int32 [1]: the kernels write a non-zero code here if a bounded wait ran out (caller zeroes)
+ *   status         int32 [COMFY_MOE_STATUS_WORDS]: the kernels write a non-zero code to word 0 if a bounded wait ran out (sticky: zeroed by the
+ *                  caller once, then only by comfy_moe_read_status after it reported a code)
  * Requires dim % 256 == 0 and hidden % 128 == 0 (COMFY_MOE_EUNSUPPORTED otherwise).
  */
 int comfy_moe_grouped_swiglu(int w_dtype, int n_groups, const ComfyMoeFfnWeights* h_groups,
@@ -245,7 +256,8 @@ typedef struct ComfyMoeWorkspace {
   int32_t* expert_counts;  /* [n_experts] */
   int32_t* expert_offsets; /* [n_experts + 1] */
   int32_t* row_map;        /* [n_tokens, 2] */
-  int32_t* status;         /* [2]: [0] device wait status, [1] near-tie count */
+  int32_t* status;         /* [COMFY_MOE_STATUS_WORDS]: [0] device status word (sticky, see comfy_moe_read_status),
+                              [1] near-tie count of the last call, [2] e4m3 overflow count (accumulates) */
   void* x_perm;            /* [rows_cap, dim] act dtype */
   void* x_q;               /* fp8 only: [n_tokens, dim] */
   void* h_perm;            /* [rows_cap, hidden] act dtype */
@@ -296,11 +308,15 @@ int comfy_attn_rmsnorm_rope(const void* x, int64_t ld_x, const void* weight, flo
                             int out_row_offset, void* stream);
 
 /* ---- activation quantiser on its own (comfy/ops.py:338-343) --------------------------------------------------
- * out = e4m3( clamp( scale ? bf16(x * bf16(1 / scale)) : x, +-448 ) ), round to nearest even; x bf16, n_elements a
- * multiple of 16.  What comfy_moe_permute does on the way, for callers that need the quantised copy before the
- * permutation runs (the expert-parallel path quantises the shared expert's input beside the routing kernels).
+ * scale NULL:  out = e4m3(clamp(x, +-448))                 (:339-340; round to nearest even)
+ * scale given: out = e4m3(bf16(x * bf16(1 / scale)))       (:342-343; NO clamp: beyond the e4m3 range the result is
+ *              NaN, as in the reference, and *overflow_count (may be NULL) grows by the number of such elements)
+ * x bf16, n_elements a multiple of 16.  What comfy_moe_permute does on the way, for callers that need the quantised
+ * copy before the permutation runs (the expert-parallel path quantises the shared expert's input beside the routing
+ * kernels).
  */
-int comfy_moe_quantize_e4m3(const void* x, const float* scale, int64_t n_elements, void* out, void* stream);
+int comfy_moe_quantize_e4m3(const void* x, const float* scale, int64_t n_elements, void* out, int32_t* overflow_count,
+                            void* stream);
 
 /* ---- weight ingest: stochastic rounding to e4m3 (comfy/float.py:3-46) ------------------------------------------
  * What scaled_fp8_ops.Linear.set_weight (comfy/ops.py:418-426) applies to a LoRA-patched weight after dividing it by
@@ -360,6 +376,12 @@ int comfy_moe_ep_dispatch(const ComfyMoePeerPlan* h_plan, const void* x, const i
                           void* stream);
 int comfy_moe_ep_signal(const ComfyMoePeerPlan* h_plan, int kind, uint32_t epoch, void* stream);
 int comfy_moe_ep_wait(const ComfyMoePeerPlan* h_plan, int kind, uint32_t epoch, int32_t* status, void* stream);
+/* The same wait with the clock budget as an argument (SM cycles; comfy_moe_ep_wait uses COMFY_MOE_EP_WAIT_CYCLES).
+ * When the budget runs out before every flag has reached `epoch`, the kernel writes code 7 to *status and returns;
+ * the context stays usable and comfy_moe_read_status reports COMFY_MOE_ETIMEOUT. */
+#define COMFY_MOE_EP_WAIT_CYCLES 4000000000LL   /* about two seconds of SM clocks */
+int comfy_moe_ep_wait_budget(const ComfyMoePeerPlan* h_plan, int kind, uint32_t epoch, int64_t budget_cycles,
+                             int32_t* status, void* stream);
 int comfy_moe_ep_combine(const ComfyMoePeerPlan* h_plan, const int32_t* topk_idx, const int32_t* row_map,
                          const float* topk_weight, const void* y_shared, int n_tokens, int dim, void* out,
                          void* stream);
@@ -390,8 +412,15 @@ int comfy_moe_ffn_block(const ComfyMoeLayer* h_layer, const ComfyMoeWorkspace* h
                         const void* scale, const void* gate, int64_t mod_batch_stride, int n_tokens,
                         int tokens_per_batch, float eps, void* out, void* stream);
 
-/* Synchronises `stream`, copies status[0] to *h_status and returns COMFY_MOE_ETIMEOUT if it is non-zero. */
-int comfy_moe_read_status(const int32_t* status, void* stream, int32_t* h_status);
+/* The device status word.  Kernels move it from 0 to a code when something went wrong on the device (1-3: a bounded
+ * wait of the grouped GEMM's producer / MMA / epilogue role ran out; 7: a peer's flag did not arrive in time; 8: routed
+ * rows did not fit a peer receive buffer and were dropped) and never overwrite a code that is already there; no entry
+ * point clears it on the way in.  A caller may therefore share one word among all layers of a model and look at it at
+ * a natural synchronisation point (end of a model forward).
+ * comfy_moe_read_status synchronises `stream`, copies status[0] to *h_status and returns COMFY_MOE_OK for 0,
+ * COMFY_MOE_ETOOLARGE for code 8 and COMFY_MOE_ETIMEOUT for any other code; a non-zero word is cleared once it has
+ * been reported. */
+int comfy_moe_read_status(int32_t* status, void* stream, int32_t* h_status);
 
 #ifdef __cplusplus
 }

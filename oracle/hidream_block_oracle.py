@@ -42,15 +42,17 @@ def _norm_mod(x, shift, scale):
 
 
 def single_block(layer: Layer, tokens: torch.Tensor, adaln_input: torch.Tensor, freqs: torch.Tensor, heads: int,
-                 gate_in_fp32: bool = False) -> torch.Tensor:
+                 gate_in_fp32: bool = False, routing_out=None) -> torch.Tensor:
     shift_msa, scale_msa, gate_msa, shift_mlp, scale_mlp, gate_mlp = _modulation(layer, adaln_input, 6)
     attn = A.processor(_sub(layer, "attn1."), _norm_mod(tokens, shift_msa, scale_msa), None, freqs, heads)
     tokens = gate_msa * attn + tokens
-    return O.block_ffn(tokens, _sub(layer, "ff_i."), shift_mlp, scale_mlp, gate_mlp, gate_in_fp32=gate_in_fp32)
+    return O.block_ffn(tokens, _sub(layer, "ff_i."), shift_mlp, scale_mlp, gate_mlp, gate_in_fp32=gate_in_fp32,
+                       routing_out=routing_out)
 
 
 def double_block(layer: Layer, image_tokens: torch.Tensor, text_tokens: torch.Tensor, adaln_input: torch.Tensor,
-                 freqs: torch.Tensor, heads: int, gate_in_fp32: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
+                 freqs: torch.Tensor, heads: int, gate_in_fp32: bool = False,
+                 routing_out=None) -> Tuple[torch.Tensor, torch.Tensor]:
     (shift_msa_i, scale_msa_i, gate_msa_i, shift_mlp_i, scale_mlp_i, gate_mlp_i,
      shift_msa_t, scale_msa_t, gate_msa_t, shift_mlp_t, scale_mlp_t, gate_mlp_t) = _modulation(layer, adaln_input, 12)
     attn_i, attn_t = A.processor(_sub(layer, "attn1."), _norm_mod(image_tokens, shift_msa_i, scale_msa_i),
@@ -58,7 +60,7 @@ def double_block(layer: Layer, image_tokens: torch.Tensor, text_tokens: torch.Te
     image_tokens = gate_msa_i * attn_i + image_tokens
     text_tokens = gate_msa_t * attn_t + text_tokens
     image_tokens = O.block_ffn(image_tokens, _sub(layer, "ff_i."), shift_mlp_i, scale_mlp_i, gate_mlp_i,
-                               gate_in_fp32=gate_in_fp32)
+                               gate_in_fp32=gate_in_fp32, routing_out=routing_out)
     text_tokens = O.block_ffn(text_tokens, layer, shift_mlp_t, scale_mlp_t, gate_mlp_t, dense_prefix="ff_t")
     return image_tokens, text_tokens
 

@@ -168,11 +168,13 @@ def moe_layer(x: torch.Tensor, layer: Layer, mode: str = PLAIN, gate_in_fp32: bo
 
 
 def block_ffn(x: torch.Tensor, layer: Layer, shift: torch.Tensor, scale: torch.Tensor, gate_mlp: torch.Tensor,
-              eps: float = 1e-6, mode: str = PLAIN, dense_prefix: Optional[str] = None, **moe_kw) -> torch.Tensor:
+              eps: float = 1e-6, mode: str = PLAIN, dense_prefix: Optional[str] = None,
+              routing_out: Optional[list] = None, **moe_kw) -> torch.Tensor:
     """Feed-forward half of a HiDream block (model.py:429-433; :515-523 for the double-stream block):
     LayerNorm without affine -> * (1 + scale) + shift -> feed-forward -> gate * (.) + x.
     x [B, S, D]; shift / scale / gate_mlp [B, 1, D].  ``dense_prefix`` selects a plain FeedForwardSwiGLU (the text
-    side, ``ff_t``) instead of the MoE; ``moe_kw`` goes to moe_layer (routing, gate_in_fp32, branch)."""
+    side, ``ff_t``) instead of the MoE; ``moe_kw`` goes to moe_layer (routing, gate_in_fp32, branch); ``routing_out``,
+    a list, receives the (idx, weight) pair the MoE used."""
     wtype = x.dtype
     b, s, d = x.shape
     normed = F.layer_norm(x, (d,), None, None, eps).to(dtype=wtype)
@@ -181,7 +183,9 @@ def block_ffn(x: torch.Tensor, layer: Layer, shift: torch.Tensor, scale: torch.T
     if dense_prefix is not None:
         ff = swiglu_ffn(flat, layer, dense_prefix, mode)
     else:
-        ff, _, _ = moe_layer(flat, layer, mode=mode, **moe_kw)
+        ff, idx, w = moe_layer(flat, layer, mode=mode, **moe_kw)
+        if routing_out is not None:
+            routing_out.append((idx, w))
     return gate_mlp * ff.view(b, s, d) + x
 
 

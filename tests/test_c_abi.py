@@ -73,7 +73,7 @@ def test_argument_validation_needs_no_gpu(lib):
     assert lib.comfy_moe_gate_topk(None, None, 0, 16, 256, 4, 2, None, None, None, None, None, 1e-6, None) == N.EINVAL
     assert lib.comfy_moe_gate_topk(None, None, 0, 0, 256, 4, 2, None, None, None, None, None, 1e-6, None) == N.OK
     assert lib.comfy_moe_combine(None, None, None, None, 8, 256, None, None) == N.EINVAL
-    assert lib.comfy_moe_permute(None, None, None, None, -1, 256, 4, 0, None, None, None, None, None, None) == N.EINVAL
+    assert lib.comfy_moe_permute(None, None, None, None, -1, 256, 4, 0, None, None, None, None, None, None, None) == N.EINVAL
     assert lib.comfy_moe_forward(None, None, None, 8, None, None) == N.EINVAL
     assert lib.comfy_moe_read_status(None, None, None) == N.EINVAL
     for code in range(6):

@@ -19,36 +19,73 @@ def _build(single, dim, heads, head_dim, n_exp, dev, seed):
     return layer, mod
 
 
-def _rows_close(got, want, what):
-    """bf16 tolerance on every row except the few whose MoE routing flipped: the gate sees LayerNorm outputs that
-    differ by an ulp between the GPU and the CPU computation, and a re-routed token differs by O(1)."""
+def _rows_close(got, want, what, flipped=None):
+    """bf16 tolerance on EVERY row whose MoE routing agrees with the oracle's.  The gate sees LayerNorm outputs that
+    differ by an ulp between the GPU and the CPU computation; a token whose two experts changed for that reason
+    differs by O(1) and is excused, but only if its routing really differs (``flipped``, one flag per row; None = no
+    row is excused, e.g. text tokens, whose feed-forward is dense)."""
     got, want = got.float().cpu().reshape(-1, got.shape[-1]), want.float().reshape(-1, want.shape[-1])
     bad = ((got - want).abs() > 2e-2 + 2e-2 * want.abs()).any(dim=1)
-    assert bad.float().mean() < 0.02, f"{what}: {int(bad.sum())} of {bad.numel()} rows outside the tolerance"
-    rel = (got[~bad] - want[~bad]).norm() / want[~bad].norm()
+    if flipped is None:
+        flipped = torch.zeros_like(bad)
+    unexplained = bad & ~flipped
+    assert not bool(unexplained.any()), \
+        f"{what}: {int(unexplained.sum())} of {bad.numel()} rows outside the tolerance with unchanged routing"
+    assert flipped.float().mean() < 0.02, f"{what}: {int(flipped.sum())} of {flipped.numel()} tokens re-routed"
+    keep = ~flipped
+    rel = (got[keep] - want[keep]).norm() / want[keep].norm()
     assert rel < 5e-3, f"{what}: rel-RMS {rel}"
 
 
-@pytest.mark.parametrize("single", [False, True], ids=["double", "single"])
-def test_block_against_oracle(cuda_device, single):
-    dev, heads, head_dim, n_exp, b, hh, ww, n_text = cuda_device, 4, 128, 4, 2, 16, 16, 32
+def _flipped(ff_module, tokens_like, routing_ref):
+    """One flag per token: the kernels' routing of the block's last MoE call differs from the oracle's."""
+    from comfyui_b200 import ops, torch_ops
+
+    n = tokens_like.shape[0] * tokens_like.shape[1]
+    layer = ops._layer_pack(ff_module, tokens_like)
+    assert layer is not None
+    idx = torch_ops._workspace(layer, n).topk_idx.cpu().long()
+    ridx = routing_ref[0][0]
+    return (idx.sort(dim=1).values != ridx.sort(dim=1).values).any(dim=1)
+
+
+def _run_block(cuda_device, single, heads, head_dim, b, hh, ww, n_text, seed):
+    dev, n_exp = cuda_device, 4
     dim = heads * head_dim
-    layer, mod = _build(single, dim, heads, head_dim, n_exp, dev, seed=7)
-    g = torch.Generator().manual_seed(8)
+    layer, mod = _build(single, dim, heads, head_dim, n_exp, dev, seed=seed)
+    g = torch.Generator().manual_seed(seed + 1)
     img = torch.randn((b, hh * ww, dim), generator=g).bfloat16()
     txt = torch.randn((b, n_text, dim), generator=g).bfloat16()
     ada = torch.randn((b, dim), generator=g).bfloat16()
     freqs = A.rope_table(A.make_ids(b, hh, ww, n_text), [64, 32, 32])
+    routing = []
     with torch.no_grad():
         if single:
             seq = torch.cat([img, txt], dim=1)
             got = mod(seq.to(dev), None, None, ada.to(dev), freqs.to(dev))
-            _rows_close(got, B.single_block(layer, seq, ada, freqs, heads, gate_in_fp32=True), "single block")
+            want = B.single_block(layer, seq, ada, freqs, heads, gate_in_fp32=True, routing_out=routing)
+            flips = _flipped(mod.ff_i, got, routing)
+            _rows_close(got, want, "single block", flips)
         else:
             got_i, got_t = mod(img.to(dev), None, txt.to(dev), ada.to(dev), freqs.to(dev))
-            want_i, want_t = B.double_block(layer, img, txt, ada, freqs, heads, gate_in_fp32=True)
-            _rows_close(got_i, want_i, "image tokens")
+            want_i, want_t = B.double_block(layer, img, txt, ada, freqs, heads, gate_in_fp32=True, routing_out=routing)
+            flips = _flipped(mod.ff_i, got_i, routing)
+            _rows_close(got_i, want_i, "image tokens", flips)
             _rows_close(got_t, want_t, "text tokens")
+    print(f"{'single' if single else 'double'} block, {b} x ({hh * ww} + {n_text}) tokens, dim {dim}: "
+          f"{int(flips.sum())} of {flips.numel()} tokens re-routed by a one-ulp difference in the LayerNorm output")
+
+
+@pytest.mark.parametrize("single", [False, True], ids=["double", "single"])
+def test_block_against_oracle(cuda_device, single):
+    _run_block(cuda_device, single, heads=4, head_dim=128, b=2, hh=16, ww=16, n_text=32, seed=7)
+
+
+@pytest.mark.parametrize("single", [False, True], ids=["double", "single"])
+def test_block_at_model_shape(cuda_device, single):
+    """The model's own shape: dim 2560, 20 heads x 128, 64 x 64 image patches + 384 text tokens (one batch element, to
+    keep the CPU oracle within seconds)."""
+    _run_block(cuda_device, single, heads=20, head_dim=128, b=1, hh=64, ww=64, n_text=384, seed=17)
 
 
 def test_every_fused_piece_is_taken(cuda_device, monkeypatch):

@@ -76,6 +76,55 @@ def test_emulated_ranks_on_one_gpu(cuda_device, world, fp8, push):
     assert counts_all.sum(dim=1).tolist() == [2 * t for t in tokens]
 
 
+def test_a_wait_that_runs_out_reports_and_returns(cuda_device):
+    """The bounded wait on its real path: rank 0 of an emulated pair waits for an "arrived" flag that nobody raises,
+    with a budget of about a millisecond.  The kernel gives up, leaves code 7 in the status word and returns; the host
+    turns that into ETIMEOUT; the GPU and the buffers stay usable (a complete step follows on the same buffers)."""
+    import ctypes
+
+    from comfyui_b200 import _native as N
+    from comfyui_b200 import moe_ops as M
+    from comfyui_b200.expert_parallel import PeerBuffers, PeerExpertParallelMoE, Placement
+
+    dev = cuda_device
+    lib = N.load()
+    place = Placement(2, E)
+    bufs = PeerBuffers.emulate(place, 4096, 2048, DIM, torch.bfloat16, dev)
+    status = torch.zeros((N.STATUS_WORDS,), dtype=torch.int32, device=dev)
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    t0 = torch.cuda.Event(enable_timing=True)
+    t1 = torch.cuda.Event(enable_timing=True)
+    t0.record()
+    rc = lib.comfy_moe_ep_wait_budget(bufs[0].plan, N.EP_ARRIVED, 1, 2_000_000, ctypes.c_void_p(status.data_ptr()), stream)
+    t1.record()
+    assert rc == N.OK
+    with pytest.raises(N.MoeError) as err:
+        M.read_status(status)
+    assert err.value.code == N.ETIMEOUT and "status word = 7" in str(err.value)
+    assert 0.2 < t0.elapsed_time(t1) < 100.0            # it waited for its budget (about 1 ms), not for two seconds
+    M.read_status(status)                               # reported once, then clean
+    assert lib.comfy_moe_ep_wait_budget(bufs[0].plan, N.EP_ARRIVED, 1, 0, ctypes.c_void_p(status.data_ptr()),
+                                        stream) == N.EINVAL
+    # the same buffers then carry a normal step
+    module = _module(dev)
+    ranks = [PeerExpertParallelMoE(module, buffers=bufs[r], place=place, rank=r) for r in range(2)]
+    xs = [O.make_input(n, DIM, seed=40 + r).bfloat16().to(dev) for r, n in enumerate((300, 200))]
+    with torch.inference_mode():
+        counts = []
+        for x in xs:
+            _, _, bc, _, _ = M.gate_topk(x, module.gate.weight)
+            counts.append(M.route_plan(bc, x.shape[0], E)[1])
+        counts_all = torch.stack(counts).contiguous()
+        for r in range(2):
+            ranks[r].phase_route(xs[r], counts_all=counts_all)
+        for r in range(2):
+            ranks[r].phase_experts()
+        for r in range(2):
+            out = ranks[r].phase_combine()
+            ranks[r].check()
+            assert torch.equal(out, module(xs[r].view(1, -1, DIM)).view(-1, DIM))
+
+
 def test_two_layers_share_the_buffers(cuda_device):
     """The layers of a model use one set of buffers and one epoch counter, one after the other."""
     from comfyui_b200 import moe_ops as M

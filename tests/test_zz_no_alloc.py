@@ -20,10 +20,12 @@ def _ptr(t):
     return None if t is None else ctypes.c_void_p(t.data_ptr())
 
 
-def _route_static(lib, N, x, w_gate, n_experts):
+def _route_static(lib, N, x, w_gate, n_experts, fp8=False, scale=None):
     n, d = x.shape
     dev = x.device
     rows_cap = 2 * n + n_experts * N.ROW_ALIGN
+    if fp8:
+        return _route_static_fp8(lib, N, x, w_gate, n_experts, scale, rows_cap)
     out = dict(
         idx=torch.empty((n, 2), dtype=torch.int32, device=dev),
         w=torch.empty((n, 2), dtype=torch.float32, device=dev),
@@ -42,13 +44,41 @@ def _route_static(lib, N, x, w_gate, n_experts):
     return out
 
 
-def _route_regular(M, x, w_gate, n_experts):
+def _route_static_fp8(lib, N, x, w_gate, n_experts, scale, rows_cap):
+    """The same call with e4m3 activations: the permuted rows and the shared expert's copy are quantised on the way."""
+    n, d = x.shape
+    dev = x.device
+    out = dict(
+        idx=torch.empty((n, 2), dtype=torch.int32, device=dev),
+        w=torch.empty((n, 2), dtype=torch.float32, device=dev),
+        counts=torch.empty((n_experts,), dtype=torch.int32, device=dev),
+        offsets=torch.empty((n_experts + 1,), dtype=torch.int32, device=dev),
+        x_perm=torch.zeros((rows_cap, d), dtype=torch.uint8, device=dev),
+        x_q=torch.zeros((n, d), dtype=torch.uint8, device=dev),
+        row_map=torch.empty((n, 2), dtype=torch.int32, device=dev),
+        ties=torch.zeros((1,), dtype=torch.int32, device=dev),
+    )
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    rc = lib.comfy_moe_route_static(_ptr(x), _ptr(w_gate), N.BF16, n, d, n_experts, 2, N.FP8_E4M3, _ptr(scale),
+                                    _ptr(out["idx"]), _ptr(out["w"]), _ptr(out["counts"]), _ptr(out["offsets"]),
+                                    _ptr(out["x_perm"]), _ptr(out["x_q"]), _ptr(scale), _ptr(out["row_map"]),
+                                    _ptr(out["ties"]), stream)
+    assert rc == N.OK, lib.comfy_moe_error_string(rc)
+    torch.cuda.synchronize()
+    return out
+
+
+def _route_regular(M, x, w_gate, n_experts, fp8=False, scale=None):
     n = x.shape[0]
     idx, w, block_counts, ties, _ = M.gate_topk(x, w_gate)
     block_offsets, counts, offsets = M.route_plan(block_counts, n, n_experts)
-    x_perm, row_map, _ = M.permute(x, idx, block_offsets, offsets, n_experts, zero_fill=True)
+    x_perm, row_map, x_q = M.permute(x, idx, block_offsets, offsets, n_experts, zero_fill=True, fp8=fp8, want_xq=fp8,
+                                     act_scale=scale, xq_scale=scale)
     torch.cuda.synchronize()
-    return dict(idx=idx, w=w, counts=counts, offsets=offsets, x_perm=x_perm, row_map=row_map, ties=ties)
+    res = dict(idx=idx, w=w, counts=counts, offsets=offsets, x_perm=x_perm, row_map=row_map, ties=ties)
+    if fp8:
+        res["x_perm"], res["x_q"] = x_perm.view(torch.uint8), x_q.view(torch.uint8)
+    return res
 
 
 def test_route_static_matches_regular_entry_points(cuda_device):
@@ -63,6 +93,41 @@ def test_route_static_matches_regular_entry_points(cuda_device):
     for n, d, e in ((4480, 2560, 4), (333, 512, 8)):
         x = torch.randn((n, d), generator=g).bfloat16().to(dev)
         w_gate = (torch.randn((e, d), generator=g) * 0.02).bfloat16().to(dev)
+        got = _route_static(lib, N, x, w_gate, e)
+        ref = _route_regular(M, x, w_gate, e)
+        for key in ("idx", "w", "counts", "offsets", "row_map", "x_perm", "ties"):
+            assert torch.equal(got[key], ref[key]), f"{key} differs at n={n}"
+
+
+def test_route_static_fp8_activations(cuda_device):
+    """The e4m3 variant (rows quantised on the way, with and without a scale_input), again two calls in a row."""
+    from comfyui_b200 import _native as N
+    from comfyui_b200 import moe_ops as M
+
+    lib = N.load()
+    dev = cuda_device
+    g = torch.Generator().manual_seed(12)
+    for n, d, e, s_in in ((1000, 2560, 4, None), (257, 512, 4, 0.75)):
+        x = torch.randn((n, d), generator=g).bfloat16().to(dev)
+        w_gate = (torch.randn((e, d), generator=g) * 0.02).bfloat16().to(dev)
+        scale = None if s_in is None else torch.tensor(s_in, device=dev)
+        got = _route_static(lib, N, x, w_gate, e, fp8=True, scale=scale)
+        ref = _route_regular(M, x, w_gate, e, fp8=True, scale=scale)
+        for key in ("idx", "w", "counts", "offsets", "row_map", "x_perm", "x_q", "ties"):
+            assert torch.equal(got[key], ref[key]), f"{key} differs at n={n}"
+
+
+def test_route_static_at_its_token_limit(cuda_device):
+    """Exactly COMFY_MOE_STATIC_MAX_TOKENS tokens use the whole built-in scratch array; a small call follows it."""
+    from comfyui_b200 import _native as N
+    from comfyui_b200 import moe_ops as M
+
+    lib = N.load()
+    dev = cuda_device
+    g = torch.Generator().manual_seed(13)
+    for n, d, e in ((N.STATIC_MAX_TOKENS, 256, 8), (100, 256, 4)):
+        x = torch.randn((n, d), generator=g).bfloat16().to(dev)
+        w_gate = (torch.randn((e, d), generator=g) * 0.05).bfloat16().to(dev)
         got = _route_static(lib, N, x, w_gate, e)
         ref = _route_regular(M, x, w_gate, e)
         for key in ("idx", "w", "counts", "offsets", "row_map", "x_perm", "ties"):
