@@ -416,6 +416,11 @@ def measure(arm, args, barrier, local_rank, peaks, *, steps: int, warmup: int, e
             arm.step(arm.x)
         ms_total, clocks = time_steps(arm, steps, barrier, local_rank)
         arm.check()
+        st = None
+        if world == 1 and stages:
+            # per-stage timing of the same work through the stage-level C ABI, straight after the headline loop so
+            # that both see the GPU in the same state (the sustained loops further down heat it up)
+            st = time_stages(arm.module, arm.x.view(n, DIM), steps, moe_ops, ops)
         ms_e2e = 0.0
         if e2e:
             # end to end: every step copies its input from pinned host memory and its output back to pinned host
@@ -466,9 +471,7 @@ def measure(arm, args, barrier, local_rank, peaks, *, steps: int, warmup: int, e
                 "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak, "peak_source": label,
                 "frac_of_nominal": achieved / (4500.0 if fp8 else 2250.0), "traffic": None,
             }
-        elif stages:
-            # per-stage timing of the same work through the stage-level C ABI
-            st = time_stages(arm.module, arm.x.view(n, DIM), steps, moe_ops, ops)
+        elif st is not None:
             gemm_ms = st["grouped_gemm_ms"]
             achieved = FLOPS_PER_TOKEN_GEMM * n / (gemm_ms * 1e-3) / 1e12
             peak, label = timed_region_peak(peaks, st["timed_region_ms"], fp8)
@@ -623,9 +626,13 @@ def run_gpu_arm(args) -> None:
     if world == 1 and not args.no_cpu_baseline and rank == 0:
         line["cpu_baseline"] = cpu_baseline_object(args.dtype, reps=10)
 
-    if args.timeline:
+    if args.timeline or args.timeline_dir:
         with torch.inference_mode():
-            if rank == 0:
+            if args.timeline_dir:           # every rank writes its own file
+                os.makedirs(args.timeline_dir, exist_ok=True)
+                tag = f"{arm.world}gpus_{'fp8' if arm.fp8 else 'bf16'}{'_config5' if arm.config5 else ''}"
+                print_timeline(arm.step, arm.x, os.path.join(args.timeline_dir, f"timeline_{tag}_rank{rank}.txt"), rank)
+            elif rank == 0:
                 print_timeline(arm.step, arm.x)
             else:
                 for _ in range(3):          # the other ranks take the same three steps
@@ -748,9 +755,10 @@ def time_stages(module, x2, steps, moe_ops, ops):
     return res
 
 
-def print_timeline(step, x) -> None:
-    """Kernel timeline of one step on this rank (torch.profiler / CUPTI), printed to stderr: start offset, duration,
-    kernel name.  Three steps are profiled and the middle one is shown."""
+def print_timeline(step, x, path=None, rank: int = 0) -> None:
+    """Kernel timeline of one step on this rank (torch.profiler / CUPTI): start offset, duration, stream, kernel name.
+    Three steps are profiled and the middle one is shown, followed by the wall time of each of the three steps on this
+    rank.  Goes to `path` when given (one file per rank), else to stderr."""
     from torch.profiler import ProfilerActivity, profile
 
     with profile(activities=[ProfilerActivity.CUDA]) as prof:
@@ -759,15 +767,27 @@ def print_timeline(step, x) -> None:
         torch.cuda.synchronize()
     evs = [e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA]
     evs.sort(key=lambda e: e.time_range.start)
-    gates = [i for i, e in enumerate(evs) if "gate_topk" in e.name]
-    if len(gates) < 3:
-        print("timeline: no gate kernels found", file=sys.stderr)
-        return
-    lo, hi = gates[1], gates[2]
-    t0 = evs[lo].time_range.start
-    print("timeline of one step (offset us, duration us, kernel):", file=sys.stderr)
-    for e in evs[lo:hi]:
-        print(f"{e.time_range.start - t0:9.1f} {e.time_range.elapsed_us():8.1f}  {e.name[:100]}", file=sys.stderr)
+    out = open(path, "w") if path else sys.stderr
+    try:
+        gates = [i for i, e in enumerate(evs) if "gate_topk" in e.name]
+        if len(gates) < 3:
+            print("timeline: no gate kernels found", file=out)
+            return
+        lo, hi = gates[1], gates[2]
+        # the side stream's first kernels of the step may start before the gate: include what began up to 50 us earlier
+        while lo > 0 and evs[lo - 1].time_range.start > evs[gates[1]].time_range.start - 50:
+            lo -= 1
+        t0 = evs[gates[1]].time_range.start
+        print(f"rank {rank}: timeline of one step (offset us from the gate's start, duration us, stream, kernel)", file=out)
+        for e in evs[lo:hi]:
+            if e.time_range.start < evs[gates[2]].time_range.start - 50 or "gate_topk" in e.name:
+                print(f"{e.time_range.start - t0:9.1f} {e.time_range.elapsed_us():8.1f}  s{getattr(e, 'device_resource_id', '?')}  "
+                      f"{e.name[:110]}", file=out)
+        ends = [evs[gates[i + 1]].time_range.start - evs[gates[i]].time_range.start for i in range(2)]
+        print(f"rank {rank}: gate-to-gate step times under the profiler: {ends[0]:.1f} us, {ends[1]:.1f} us", file=out)
+    finally:
+        if path:
+            out.close()
 
 
 def time_stock_composition(module, x, ops, steps: int = 10):
@@ -976,6 +996,8 @@ def main() -> None:
                     help="bf16 (benchmark configuration 2, the default) or per-tensor scaled fp8 e4m3 expert weights (configuration 3)")
     ap.add_argument("--timeline", action="store_true",
                     help="after the timing, print the kernel timeline of one step on rank 0 to stderr (torch.profiler)")
+    ap.add_argument("--timeline-dir", default=None,
+                    help="like --timeline, but every rank writes its timeline to a file of its own in this directory")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU oracle and the stock-composition timings (profiling runs)")
     ap.add_argument("--headline-only", action="store_true",
                     help="hidream workload: skip the sub-objects (sustained loop, the other dtype, configuration 5, "

@@ -19,20 +19,36 @@ def _build(single, dim, heads, head_dim, n_exp, dev, seed):
     return layer, mod
 
 
-def _rows_close(got, want, what, flipped=None):
-    """bf16 tolerance on EVERY row whose MoE routing agrees with the oracle's.  The gate sees LayerNorm outputs that
-    differ by an ulp between the GPU and the CPU computation; a token whose two experts changed for that reason
-    differs by O(1) and is excused, but only if its routing really differs (``flipped``, one flag per row; None = no
-    row is excused, e.g. text tokens, whose feed-forward is dense)."""
+def _rows_close(got, want, what, flipped=None, elementwise=True):
+    """Every row whose MoE routing agrees with the oracle's has to match; only a row whose routing really differs
+    (``flipped``, one flag per row; None = no row is excused, e.g. text tokens, whose feed-forward is dense) is set
+    aside: the gate sees LayerNorm outputs that differ by an ulp between the GPU and the CPU computation, and a token
+    whose two experts changed for that reason differs by O(1).
+
+    elementwise=True: rtol = atol = 2e-2 on every element of every kept row.
+    elementwise=False (the model's width): a block is a chain of a dozen bf16 operations over 2560-wide rows, and at
+    that depth two correct implementations (PyTorch's own CUDA composition against the same CPU oracle shows the same
+    figures) differ by a few ulps in a few elements per thousand, so the bar is stated per row instead: relative L2
+    error of every kept row below 2e-2 (a re-routed or otherwise wrong row is off by 0.3 or more, a correct one by
+    about 4e-3), at most 2 elements per thousand outside the element tolerance, none by more than 0.25."""
     got, want = got.float().cpu().reshape(-1, got.shape[-1]), want.float().reshape(-1, want.shape[-1])
-    bad = ((got - want).abs() > 2e-2 + 2e-2 * want.abs()).any(dim=1)
     if flipped is None:
-        flipped = torch.zeros_like(bad)
-    unexplained = bad & ~flipped
-    assert not bool(unexplained.any()), \
-        f"{what}: {int(unexplained.sum())} of {bad.numel()} rows outside the tolerance with unchanged routing"
+        flipped = torch.zeros(got.shape[0], dtype=torch.bool)
     assert flipped.float().mean() < 0.02, f"{what}: {int(flipped.sum())} of {flipped.numel()} tokens re-routed"
     keep = ~flipped
+    err = (got - want).abs()
+    out_of_tol = err > 2e-2 + 2e-2 * want.abs()
+    if elementwise:
+        bad = out_of_tol.any(dim=1) & keep
+        assert not bool(bad.any()), \
+            f"{what}: {int(bad.sum())} of {bad.numel()} rows outside the tolerance with unchanged routing"
+    else:
+        row_rel = (got - want).norm(dim=1) / want.norm(dim=1)
+        bad = (row_rel > 2e-2) & keep
+        assert not bool(bad.any()), \
+            f"{what}: {int(bad.sum())} rows with unchanged routing are off by more than 2e-2 (worst {float(row_rel[keep].max()):.3f})"
+        assert float(out_of_tol[keep].float().mean()) < 2e-3, f"{what}: {float(out_of_tol[keep].float().mean()):.2e}"
+        assert float(err[keep].max()) < 0.25, f"{what}: worst element {float(err[keep].max())}"
     rel = (got[keep] - want[keep]).norm() / want[keep].norm()
     assert rel < 5e-3, f"{what}: rel-RMS {rel}"
 
@@ -49,7 +65,7 @@ def _flipped(ff_module, tokens_like, routing_ref):
     return (idx.sort(dim=1).values != ridx.sort(dim=1).values).any(dim=1)
 
 
-def _run_block(cuda_device, single, heads, head_dim, b, hh, ww, n_text, seed):
+def _run_block(cuda_device, single, heads, head_dim, b, hh, ww, n_text, seed, elementwise=True):
     dev, n_exp = cuda_device, 4
     dim = heads * head_dim
     layer, mod = _build(single, dim, heads, head_dim, n_exp, dev, seed=seed)
@@ -65,13 +81,13 @@ def _run_block(cuda_device, single, heads, head_dim, b, hh, ww, n_text, seed):
             got = mod(seq.to(dev), None, None, ada.to(dev), freqs.to(dev))
             want = B.single_block(layer, seq, ada, freqs, heads, gate_in_fp32=True, routing_out=routing)
             flips = _flipped(mod.ff_i, got, routing)
-            _rows_close(got, want, "single block", flips)
+            _rows_close(got, want, "single block", flips, elementwise)
         else:
             got_i, got_t = mod(img.to(dev), None, txt.to(dev), ada.to(dev), freqs.to(dev))
             want_i, want_t = B.double_block(layer, img, txt, ada, freqs, heads, gate_in_fp32=True, routing_out=routing)
             flips = _flipped(mod.ff_i, got_i, routing)
-            _rows_close(got_i, want_i, "image tokens", flips)
-            _rows_close(got_t, want_t, "text tokens")
+            _rows_close(got_i, want_i, "image tokens", flips, elementwise)
+            _rows_close(got_t, want_t, "text tokens", None, elementwise)
     print(f"{'single' if single else 'double'} block, {b} x ({hh * ww} + {n_text}) tokens, dim {dim}: "
           f"{int(flips.sum())} of {flips.numel()} tokens re-routed by a one-ulp difference in the LayerNorm output")
 
@@ -85,7 +101,7 @@ def test_block_against_oracle(cuda_device, single):
 def test_block_at_model_shape(cuda_device, single):
     """The model's own shape: dim 2560, 20 heads x 128, 64 x 64 image patches + 384 text tokens (one batch element, to
     keep the CPU oracle within seconds)."""
-    _run_block(cuda_device, single, heads=20, head_dim=128, b=1, hh=64, ww=64, n_text=384, seed=17)
+    _run_block(cuda_device, single, heads=20, head_dim=128, b=1, hh=64, ww=64, n_text=384, seed=17, elementwise=False)
 
 
 def test_every_fused_piece_is_taken(cuda_device, monkeypatch):
