@@ -42,6 +42,7 @@ EXPORTS = (
     "comfy_moe_forward_gelu_mlp",
     "comfy_moe_ln_modulate",
     "comfy_moe_gate_residual",
+    "comfy_moe_ln_modulate_gate",
     "comfy_moe_combine_block",
     "comfy_moe_ffn_block",
     "comfy_moe_read_status",
@@ -227,6 +228,10 @@ def load(build_if_missing: bool = False) -> ctypes.CDLL:
     lib.comfy_moe_forward.argtypes = [POINTER(Layer), POINTER(Workspace), c_void_p, c_int, c_void_p, c_void_p]
     lib.comfy_moe_ln_modulate.argtypes = [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_float, c_void_p,
                                           c_void_p]
+    lib.comfy_moe_ln_modulate_gate.argtypes = [
+        c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_int, c_int, c_int,
+        c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p,
+    ]
     lib.comfy_moe_gate_residual.argtypes = [c_void_p, c_void_p, c_int64, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]
     lib.comfy_moe_combine_block.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_int,
                                             c_int, c_int, c_void_p, c_void_p]

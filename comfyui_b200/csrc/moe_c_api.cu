@@ -42,7 +42,7 @@ struct BlockEpilogue {
 // MOEFeedForwardSwiGLU.forward (comfy/ldm/hidream/model.py:307-325) as five launches on one stream:
 // gate, routing plan + permutation, two passes of the grouped GEMM, combine.
 static int forward_impl(const ComfyMoeLayer* L, const ComfyMoeWorkspace* ws, const void* x, int n_tokens, void* out,
-                        void* stream, const BlockEpilogue* epi) {
+                        void* stream, const BlockEpilogue* epi, bool gate_done = false) {
   if (!L || !ws || n_tokens < 0) return COMFY_MOE_EINVAL;
   if (n_tokens == 0) return COMFY_MOE_OK;
   if (!x || !out) return COMFY_MOE_EINVAL;
@@ -59,12 +59,13 @@ static int forward_impl(const ComfyMoeLayer* L, const ComfyMoeWorkspace* ws, con
   if (fp8 && !ws->x_q) return COMFY_MOE_EINVAL;
 
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  // only the near-tie counter starts from zero; the status word keeps whatever an earlier call left in it
-  if (cudaMemsetAsync(ws->status + 1, 0, sizeof(int32_t), s) != cudaSuccess) return COMFY_MOE_ECUDA;
-
-  rc = comfy_moe_gate_topk(x, L->w_gate, L->gate_dtype, n_tokens, L->dim, L->n_experts, L->top_k, ws->topk_idx,
-                           ws->topk_weight, ws->block_counts, ws->status + 1, nullptr, 1e-6f, stream);
-  if (rc != COMFY_MOE_OK) return rc;
+  if (!gate_done) {
+    // only the near-tie counter starts from zero; the status word keeps whatever an earlier call left in it
+    if (cudaMemsetAsync(ws->status + 1, 0, sizeof(int32_t), s) != cudaSuccess) return COMFY_MOE_ECUDA;
+    rc = comfy_moe_gate_topk(x, L->w_gate, L->gate_dtype, n_tokens, L->dim, L->n_experts, L->top_k, ws->topk_idx,
+                             ws->topk_weight, ws->block_counts, ws->status + 1, nullptr, 1e-6f, stream);
+    if (rc != COMFY_MOE_OK) return rc;
+  }
   rc = comfy_moe_plan_permute(x, ws->topk_idx, ws->block_counts, n_tokens, L->dim, L->n_experts,
                               fp8 ? COMFY_MOE_FP8_E4M3 : COMFY_MOE_BF16, fp8 ? L->experts[0].scale_in13 : nullptr,
                               ws->block_offsets, ws->expert_counts, ws->expert_offsets, ws->x_perm,
@@ -126,9 +127,15 @@ extern "C" int comfy_moe_ffn_block(const ComfyMoeLayer* L, const ComfyMoeWorkspa
                                    int n_tokens, int tokens_per_batch, float eps, void* out, void* stream) {
   if (!L || !ws || !ws->x_mod) return COMFY_MOE_EINVAL;
   if (n_tokens == 0) return COMFY_MOE_OK;
-  int rc = comfy_moe_ln_modulate(x, shift, scale, mod_batch_stride, n_tokens, tokens_per_batch, L->dim, eps, ws->x_mod,
-                                 stream);
+  if (!ws->topk_idx || !ws->topk_weight || !ws->block_counts || !ws->status) return COMFY_MOE_EINVAL;
+  // The gate rides on the LayerNorm pass: the warp that has just produced a token's modulated row also forms its four
+  // logits, so the row is not read back by a gate kernel of its own (one launch and 5 kB per token less).
+  if (cudaMemsetAsync(ws->status + 1, 0, sizeof(int32_t), static_cast<cudaStream_t>(stream)) != cudaSuccess)
+    return COMFY_MOE_ECUDA;
+  int rc = comfy_moe_ln_modulate_gate(x, shift, scale, mod_batch_stride, n_tokens, tokens_per_batch, L->dim, eps,
+                                      ws->x_mod, L->w_gate, L->gate_dtype, L->n_experts, L->top_k, ws->topk_idx,
+                                      ws->topk_weight, ws->block_counts, ws->status + 1, nullptr, 1e-6f, stream);
   if (rc != COMFY_MOE_OK) return rc;
   const BlockEpilogue epi = {gate, mod_batch_stride, x, tokens_per_batch};
-  return forward_impl(L, ws, ws->x_mod, n_tokens, out, stream, &epi);
+  return forward_impl(L, ws, ws->x_mod, n_tokens, out, stream, &epi, true);
 }

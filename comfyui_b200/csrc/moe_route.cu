@@ -6,6 +6,7 @@
 // A block owns kTokensPerBlock consecutive tokens in both the gate and the permutation; every access is a
 // 16-byte chunk per lane, 512 contiguous bytes per warp, with several rows in flight per thread.
 #include "moe_common.cuh"
+#include "moe_gate.cuh"
 
 namespace comfy_b200 {
 
@@ -66,22 +67,8 @@ gate_topk_kernel(const __nv_bfloat16* __restrict__ x, const void* __restrict__ w
           float f0[8], f1[8];
           unpack_bf16x8(v0[j], f0);
           unpack_bf16x8(v1[j], f1);
-#pragma unroll
-          for (int e = 0; e < E; ++e) {
-            float wv[8];
-            if constexpr (kW32) {
-              const float4 a = reinterpret_cast<const float4*>(w_s)[e * row_vecs + 2 * c];
-              const float4 b = reinterpret_cast<const float4*>(w_s)[e * row_vecs + 2 * c + 1];
-              wv[0] = a.x; wv[1] = a.y; wv[2] = a.z; wv[3] = a.w; wv[4] = b.x; wv[5] = b.y; wv[6] = b.z; wv[7] = b.w;
-            } else {
-              unpack_bf16x8(w_s[e * row_vecs + c], wv);
-            }
-#pragma unroll
-            for (int k = 0; k < 8; ++k) {
-              acc0[e] = fmaf(f0[k], wv[k], acc0[e]);
-              acc1[e] = fmaf(f1[k], wv[k], acc1[e]);
-            }
-          }
+          gate_accumulate<E, kW32>(w_s, row_vecs, c, f0, acc0);
+          gate_accumulate<E, kW32>(w_s, row_vecs, c, f1, acc1);
         }
       }
     }
@@ -97,32 +84,17 @@ gate_topk_kernel(const __nv_bfloat16* __restrict__ x, const void* __restrict__ w
     for (int which = 0; which < 2; ++which) {
       if (which == 1 && !has1) break;
       const int t = t0 + which;
-      float sc[E];
-      float mx = -INFINITY;
-#pragma unroll
-      for (int e = 0; e < E; ++e) { sc[e] = which == 0 ? acc0[e] : acc1[e]; mx = fmaxf(mx, sc[e]); }
-      float sum = 0.f;
-#pragma unroll
-      for (int e = 0; e < E; ++e) { sc[e] = expf(sc[e] - mx); sum += sc[e]; }
-#pragma unroll
-      for (int e = 0; e < E; ++e) sc[e] = sc[e] / sum;
-      int i0 = 0;                                        // strict '>' keeps the lowest index on exact ties
-#pragma unroll
-      for (int e = 1; e < E; ++e) if (sc[e] > sc[i0]) i0 = e;
-      int i1 = (i0 == 0) ? 1 : 0;
-#pragma unroll
-      for (int e = 0; e < E; ++e) if (e != i0 && e != i1 && sc[e] > sc[i1]) i1 = e;
-      float third = -1.f;
-#pragma unroll
-      for (int e = 0; e < E; ++e) if (e != i0 && e != i1) third = fmaxf(third, sc[e]);
+      int i0, i1;
+      float w0, w1;
+      bool tie;
+      gate_select<E>(which == 0 ? acc0 : acc1, neartie_eps, i0, i1, w0, w1, tie);
       if (lane == 0) {
         topk_idx[2 * t] = i0;
         topk_idx[2 * t + 1] = i1;
-        topk_weight[2 * t] = sc[i0];
-        topk_weight[2 * t + 1] = sc[i1];
+        topk_weight[2 * t] = w0;
+        topk_weight[2 * t + 1] = w1;
         atomicAdd(&hist[i0], 1);
         atomicAdd(&hist[i1], 1);
-        const bool tie = (E > 2) && (sc[i1] - third < neartie_eps);
         if (neartie_flags) neartie_flags[t] = tie ? 1 : 0;
         if (tie && neartie_count) atomicAdd(neartie_count, 1);
       }

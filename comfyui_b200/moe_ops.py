@@ -477,6 +477,31 @@ def ln_modulate(x: torch.Tensor, shift: torch.Tensor, scale: torch.Tensor, token
     return out
 
 
+def ln_modulate_gate(x: torch.Tensor, shift: torch.Tensor, scale: torch.Tensor, tokens_per_batch: int,
+                     w_gate: torch.Tensor, eps: float = 1e-6, *, neartie_eps: float = 1e-6, want_flags: bool = False):
+    """ln_modulate and gate_topk of its output in one pass.  Returns (out, topk_idx, topk_weight, block_counts,
+    neartie_count, neartie_flags or None), each bit-identical to what the two separate calls give."""
+    _need_cuda(x, w_gate)
+    n, d = x.shape
+    e = w_gate.shape[0]
+    stride = _modulation(shift, scale)
+    _, n_blocks = plan_sizes(n, e)
+    dev = x.device
+    out = torch.empty_like(x)
+    topk_idx = torch.empty((n, 2), dtype=torch.int32, device=dev)
+    topk_weight = torch.empty((n, 2), dtype=torch.float32, device=dev)
+    block_counts = torch.empty((max(n_blocks, 1), e), dtype=torch.int32, device=dev)
+    count = torch.zeros((1,), dtype=torch.int32, device=dev)
+    flags = torch.zeros((n,), dtype=torch.uint8, device=dev) if want_flags else None
+    w_gate = w_gate.contiguous()
+    rc = N.load().comfy_moe_ln_modulate_gate(_ptr(x), _ptr(shift), _ptr(scale), stride, n, tokens_per_batch, d, float(eps),
+                                             _ptr(out), _ptr(w_gate), _dtype_code(w_gate.dtype), e, 2, _ptr(topk_idx),
+                                             _ptr(topk_weight), _ptr(block_counts), _ptr(count), _ptr(flags),
+                                             float(neartie_eps), _stream())
+    N.check("comfy_moe_ln_modulate_gate", rc)
+    return out, topk_idx, topk_weight, block_counts, count, flags
+
+
 def gate_residual(y: torch.Tensor, gate: torch.Tensor, residual: torch.Tensor, tokens_per_batch: int) -> torch.Tensor:
     """gate * y + residual with PyTorch's bf16 rounding points.  y, residual: bf16 [N, D]; gate: bf16 [B, D] view."""
     _need_cuda(y, residual)

@@ -400,11 +400,21 @@ int comfy_moe_ln_modulate(const void* x, const void* shift, const void* scale, i
                           int tokens_per_batch, int dim, float eps, void* out, void* stream);
 int comfy_moe_gate_residual(const void* y, const void* gate, int64_t gate_batch_stride, const void* residual,
                             int n_tokens, int tokens_per_batch, int dim, void* out, void* stream);
+/* comfy_moe_ln_modulate and, on the row each warp has just produced, comfy_moe_gate_topk (model.py:429-431 followed by
+ * :263-283), in one pass: same `out`, topk_idx, topk_weight, block_counts, neartie outputs, bit for bit, without the
+ * gate's re-read of the modulated tokens and without its launch.  block_counts is zeroed by the call (a memset node on
+ * `stream`) and filled with integer atomics.  w_gate: [n_experts, dim], bf16 or fp32; n_experts 2, 4 or 8; top_k 2. */
+int comfy_moe_ln_modulate_gate(const void* x, const void* shift, const void* scale, int64_t mod_batch_stride,
+                               int n_tokens, int tokens_per_batch, int dim, float eps, void* out, const void* w_gate,
+                               int w_dtype, int n_experts, int top_k, int32_t* topk_idx, float* topk_weight,
+                               int32_t* block_counts, int32_t* neartie_count, uint8_t* neartie_flags, float neartie_eps,
+                               void* stream);
 int comfy_moe_combine_block(const void* y_perm, const int32_t* row_map, const float* topk_weight, const void* y_shared,
                             const void* gate, int64_t gate_batch_stride, const void* residual, int n_tokens,
                             int tokens_per_batch, int dim, void* out, void* stream);
 
-/* ---- feed-forward half of a HiDream block with a MoE (model.py:429-433 / 515-523), six launches ----------
+/* ---- feed-forward half of a HiDream block with a MoE (model.py:429-433 / 515-523), five launches ---------
+ * (LayerNorm + modulation + gate, plan + permutation, two GEMM passes, combine with gate * (.) + residual)
  *   out = gate * MOEFeedForwardSwiGLU(LayerNorm(x) * (1 + scale) + shift) + x
  * x, out: bf16 [n_tokens, dim] (out may alias nothing else); h_ws->x_mod must be set.
  */

@@ -172,6 +172,27 @@ def test_ln_modulate_and_gate_residual(cuda_device, b, s, dim):
     assert torch.equal(got2, ref2)
 
 
+@pytest.mark.parametrize("b,s,dim,e,w32", [(2, 4096, 2560, 4, False), (1, 4480, 2560, 4, False), (2, 300, 512, 4, True),
+                                          (3, 33, 256, 8, False), (1, 1, 256, 2, False), (2, 129, 1024, 4, False)])
+def test_gate_fused_into_the_layernorm_pass(cuda_device, b, s, dim, e, w32):
+    """LayerNorm + modulation + gate in one pass: every output is bit-identical to the two separate kernels."""
+    from comfyui_b200 import moe_ops as M
+
+    dev = cuda_device
+    x = O.make_input(b * s, dim, seed=b + s + 3).bfloat16().to(dev)
+    shift, scale, _ = O.make_modulation(b, dim, seed=6)
+    shift, scale = shift.to(dev)[:, 0], scale.to(dev)[:, 0]
+    g = torch.Generator().manual_seed(e)
+    w_gate = (torch.randn((e, dim), generator=g) * 0.02).to(torch.float32 if w32 else torch.bfloat16).to(dev)
+    x_mod = M.ln_modulate(x, shift, scale, s)
+    idx, w, counts, ties, flags = M.gate_topk(x_mod, w_gate, want_flags=True)
+    f_mod, f_idx, f_w, f_counts, f_ties, f_flags = M.ln_modulate_gate(x, shift, scale, s, w_gate, want_flags=True)
+    assert torch.equal(f_mod, x_mod)
+    assert torch.equal(f_idx, idx) and torch.equal(f_w, w)
+    assert torch.equal(f_counts, counts) and int(f_ties) == int(ties) and torch.equal(f_flags, flags)
+    assert int(f_counts.sum()) == 2 * b * s
+
+
 def test_block_feed_forward_on_kernels(cuda_device, golden):
     """block_feed_forward on the GPU: fused LayerNorm/modulation, MoE, gate/residual epilogue in the combine."""
     from comfyui_b200 import ops
