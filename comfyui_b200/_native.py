@@ -48,7 +48,9 @@ EXPORTS = (
     "comfy_moe_read_status",
     "comfy_moe_quantize_e4m3",
     "comfy_moe_stochastic_round_e4m3",
+    "comfy_moe_quantize_weight_e4m3",
     "comfy_attn_rmsnorm_rope",
+    "comfy_moe_grouped_linear",
     "comfy_moe_ep_dispatch",
     "comfy_moe_ep_signal",
     "comfy_moe_ep_wait",
@@ -118,6 +120,24 @@ class MlpLayer(Structure):
         ("w_gate", c_void_p),
         ("experts", MlpWeights * MAX_EXPERTS),
         ("shared", MlpWeights),
+    ]
+
+
+class LinearGroup(Structure):
+    """struct ComfyMoeLinearGroup"""
+
+    _fields_ = [
+        ("x", c_void_p),
+        ("w", c_void_p),
+        ("bias", c_void_p),
+        ("out", c_void_p),
+        ("ld_x", c_int64),
+        ("ld_w", c_int64),
+        ("ld_out", c_int64),
+        ("rows", c_int32),
+        ("in_features", c_int32),
+        ("out_features", c_int32),
+        ("reserved", c_int32),
     ]
 
 
@@ -249,7 +269,9 @@ def load(build_if_missing: bool = False) -> ctypes.CDLL:
     lib.comfy_moe_quantize_e4m3.argtypes = [c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p]
     lib.comfy_attn_rmsnorm_rope.argtypes = [c_void_p, c_int64, c_void_p, c_float, c_void_p, c_int64, c_int, c_int, c_int,
                                             c_int, c_int, c_int, c_void_p, c_int64, c_int, c_void_p]
+    lib.comfy_moe_grouped_linear.argtypes = [c_int, POINTER(LinearGroup), c_void_p, c_void_p]
     lib.comfy_moe_stochastic_round_e4m3.argtypes = [c_void_p, c_int, c_void_p, c_int64, c_void_p, c_void_p]
+    lib.comfy_moe_quantize_weight_e4m3.argtypes = [c_void_p, c_int, c_int64, c_void_p, c_void_p, c_void_p]
     lib.comfy_moe_ep_signal.argtypes = [POINTER(PeerPlan), c_int, c_uint32, c_void_p]
     lib.comfy_moe_ep_wait.argtypes = [POINTER(PeerPlan), c_int, c_uint32, c_void_p, c_void_p]
     lib.comfy_moe_ep_wait_budget.argtypes = [POINTER(PeerPlan), c_int, c_uint32, c_int64, c_void_p, c_void_p]

@@ -951,3 +951,51 @@ extern "C" int comfy_moe_grouped_gelu_mlp(int n_experts, const ComfyMoeMlpWeight
   if ((rc = launch_gemm<false, false, true>(p1, tiles1[0], tiles1[1], sms, s)) != COMFY_MOE_OK) return rc;
   return launch_gemm<false, false, true>(p2, tiles2[0], tiles2[1], sms, s);
 }
+
+// Several bias Linears in one launch: out_g = x_g . w_g^T + b_g for up to kMaxGroups independent (x, w, b, out) sets,
+// each a plain pass of the kernel above with the bias epilogue.  Replaces the torch.nn.functional.linear calls behind
+// operations.Linear (comfy/ops.py:103-115) where a block runs several of them on the same tokens: the q / k / v
+// projections of HiDreamAttention for image and text tokens (comfy/ldm/hidream/model.py:97-119) are six groups of one
+// launch, the two output projections (:139-144) two groups of another.
+extern "C" int comfy_moe_grouped_linear(int n_groups, const ComfyMoeLinearGroup* h_groups, int32_t* status, void* stream) {
+  if (n_groups < 0 || n_groups > kMaxGroups || !status) return COMFY_MOE_EINVAL;
+  if (n_groups == 0) return COMFY_MOE_OK;
+  if (!h_groups) return COMFY_MOE_EINVAL;
+  constexpr int k_elems = kRowBytes / 2;
+  int sms = 0;
+  int rc = device_sm_count(&sms);
+  if (rc != COMFY_MOE_OK) return rc;
+
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  p.status = status;
+  p.m_fastest = 1;            // K is short: sweep the rows under each weight panel
+  int64_t tiles[2] = {0, 0};
+  int n_maps = 0, g = 0;
+  for (int i = 0; i < n_groups; ++i) {
+    const ComfyMoeLinearGroup& L = h_groups[i];
+    if (L.rows < 0 || L.in_features <= 0 || L.out_features <= 0) return COMFY_MOE_EINVAL;
+    if (L.rows == 0) continue;
+    if (!L.x || !L.w || !L.out) return COMFY_MOE_EINVAL;
+    if (L.bias && !aligned16(L.bias)) return COMFY_MOE_EINVAL;
+    if (L.out_features % kBlockN != 0 || L.in_features % k_elems != 0) return COMFY_MOE_EUNSUPPORTED;
+    if ((rc = make_map(&p.maps[n_maps], L.x, false, L.rows, L.in_features, L.ld_x)) != COMFY_MOE_OK) return rc;
+    if ((rc = make_map(&p.maps[n_maps + 1], L.w, false, L.out_features, L.in_features, L.ld_w)) != COMFY_MOE_OK) return rc;
+    if ((rc = make_map(&p.maps[n_maps + 2], L.out, false, L.rows, L.out_features, L.ld_out)) != COMFY_MOE_OK) return rc;
+    GemmGroup& grp = p.groups[g];
+    grp.a_map = n_maps; grp.b0_map = n_maps + 1; grp.b1_map = n_maps + 1; grp.b1_row_off = 128; grp.out_map = n_maps + 2;
+    grp.k_blocks = L.in_features / k_elems; grp.n_tiles = L.out_features / kBlockN;
+    grp.routed_index = -1; grp.static_rows = L.rows;
+    grp.out = L.out; grp.ld_out = L.ld_out;
+    grp.bias = static_cast<const __nv_bfloat16*>(L.bias); grp.gelu = 0;
+    for (int v = 0; v < 2; ++v) {
+      const int64_t tile_m = kBlockM * (v + 1);
+      tiles[v] += (L.rows + tile_m - 1) / tile_m * grp.n_tiles;
+    }
+    n_maps += 3;
+    ++g;
+  }
+  if (g == 0) return COMFY_MOE_OK;
+  p.num_groups = g;
+  return launch_gemm<false, false, true>(p, tiles[0], tiles[1], sms, static_cast<cudaStream_t>(stream));
+}

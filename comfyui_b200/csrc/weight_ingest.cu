@@ -53,9 +53,79 @@ stochastic_round_e4m3_kernel(const T* __restrict__ x, const __half* __restrict__
     out[i] = stochastic_e4m3(to_half_value<T>(x[i]), __half2float(rand[i]));
 }
 
+// ------------------------------------------------------------------------------------------------
+// Per-tensor scaled e4m3: s = max|w| / 448, wq = (w / s).to(e4m3), the convention of scaled-fp8 checkpoints that
+// scaled_fp8_ops.Linear consumes (comfy/ops.py:379-410: weight e4m3, scale_weight fp32 scalar).  Two passes over the
+// tensor: the maximum (order-independent, so reproducible), then the division in fp32 and the round-to-nearest-even
+// cast; byte-identical to the three torch operations.
+// ------------------------------------------------------------------------------------------------
+template <typename T> __device__ __forceinline__ float to_f32(T v);
+template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <> __device__ __forceinline__ float to_f32<__half>(__half v) { return __half2float(v); }
+
+// amax_bits: the running maximum of |w| as the bit pattern of a non-negative float (integer order = float order);
+// a NaN anywhere makes the result NaN, as torch's max does (its pattern is above +inf's, so it wins the integer max).
+template <typename T>
+__global__ void __launch_bounds__(256)
+absmax_kernel(const T* __restrict__ w, long long n, unsigned int* __restrict__ amax_bits) {
+  unsigned int m = 0;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n; i += stride) {
+    const unsigned int b = __float_as_uint(to_f32<T>(w[i])) & 0x7fffffffu;
+    m = b > m ? b : m;
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) {
+    const unsigned int o = __shfl_xor_sync(0xffffffffu, m, off);
+    m = o > m ? o : m;
+  }
+  if ((threadIdx.x & 31) == 0 && m) atomicMax(amax_bits, m);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+scaled_e4m3_kernel(const T* __restrict__ w, long long n, const unsigned int* __restrict__ amax_bits,
+                   float* __restrict__ scale_out, uint8_t* __restrict__ out) {
+  const float s = __fdiv_rn(__uint_as_float(*amax_bits), 448.0f);
+  if (blockIdx.x == 0 && threadIdx.x == 0) *scale_out = s;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n; i += stride) {
+    // |w / s| <= 448 up to one rounding of the division, far from 464 where the cast would leave the format's range
+    out[i] = static_cast<uint8_t>(__nv_cvt_float_to_fp8(__fdiv_rn(to_f32<T>(w[i]), s), __NV_SATFINITE, __NV_E4M3));
+  }
+}
+
 }  // namespace comfy_b200
 
 using namespace comfy_b200;
+
+extern "C" int comfy_moe_quantize_weight_e4m3(const void* w, int w_dtype, int64_t n_elements, float* scale_out,
+                                              void* out, void* stream) {
+  if (n_elements < 0) return COMFY_MOE_EINVAL;
+  if (!scale_out) return COMFY_MOE_EINVAL;
+  if (n_elements > 0 && (!w || !out)) return COMFY_MOE_EINVAL;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // scale_out doubles as the accumulator of the maximum (the bit pattern of a non-negative float) between the passes
+  unsigned int* amax = reinterpret_cast<unsigned int*>(scale_out);
+  if (cudaMemsetAsync(amax, 0, sizeof(unsigned int), s) != cudaSuccess) return COMFY_MOE_ECUDA;
+  long long blocks = (n_elements + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (blocks < 1) blocks = 1;
+  const int g = static_cast<int>(blocks);
+  uint8_t* o = static_cast<uint8_t*>(out);
+#define COMFY_Q(T) \
+  do { \
+    absmax_kernel<T><<<g, 256, 0, s>>>(static_cast<const T*>(w), n_elements, amax); \
+    scaled_e4m3_kernel<T><<<g, 256, 0, s>>>(static_cast<const T*>(w), n_elements, amax, scale_out, o); \
+  } while (0)
+  if (w_dtype == COMFY_MOE_FP32) COMFY_Q(float);
+  else if (w_dtype == COMFY_MOE_BF16) COMFY_Q(__nv_bfloat16);
+  else if (w_dtype == COMFY_MOE_FP16) COMFY_Q(__half);
+  else return COMFY_MOE_EUNSUPPORTED;
+#undef COMFY_Q
+  return check_launch();
+}
 
 extern "C" int comfy_moe_stochastic_round_e4m3(const void* x, int x_dtype, const void* rand_fp16, int64_t n_elements,
                                            void* out, void* stream) {

@@ -230,8 +230,12 @@ class HiDreamAttnProcessor_flashattn:
 
         hidden = attention(query, key, value, transformer_options=transformer_options)
         if attn.single:
-            return attn.to_out(hidden)
+            fast = b200_ops.grouped_projections([(attn.to_out, hidden)])
+            return fast[0] if fast is not None else attn.to_out(hidden)
         hidden_i, hidden_t = torch.split(hidden, [n_img, hidden.shape[1] - n_img], dim=1)
+        fast = b200_ops.grouped_projections([(attn.to_out, hidden_i), (attn.to_out_t, hidden_t)])
+        if fast is not None:
+            return fast[0], fast[1]
         return attn.to_out(hidden_i), attn.to_out_t(hidden_t)
 
 

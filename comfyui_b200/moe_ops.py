@@ -700,3 +700,48 @@ def stochastic_round_e4m3(x: torch.Tensor, rand: torch.Tensor, out: Optional[tor
     N.check("comfy_moe_stochastic_round_e4m3",
             N.load().comfy_moe_stochastic_round_e4m3(_ptr(x), codes[x.dtype], _ptr(rand), x.numel(), _ptr(out), _stream()))
     return out
+
+
+def quantize_weight_e4m3(w: torch.Tensor):
+    """Per-tensor scaled e4m3 of a weight: returns (wq e4m3 like w, scale fp32 scalar on the device) with
+    scale = max|w| / 448 and wq = (w / scale) rounded to nearest even, the layout scaled-fp8 Linears load."""
+    _need_cuda(w)
+    codes = {torch.float32: N.FP32, torch.bfloat16: N.BF16, torch.float16: N.FP16}
+    if w.dtype not in codes or not w.is_contiguous():
+        raise ValueError("w must be a contiguous fp32 / bf16 / fp16 tensor")
+    out = torch.empty(w.shape, dtype=_FP8, device=w.device)
+    scale = torch.empty((), dtype=torch.float32, device=w.device)
+    N.check("comfy_moe_quantize_weight_e4m3",
+            N.load().comfy_moe_quantize_weight_e4m3(_ptr(w), codes[w.dtype], w.numel(), _ptr(scale), _ptr(out), _stream()))
+    return out, scale
+
+
+def grouped_linear(groups: Sequence[Tuple[torch.Tensor, torch.Tensor, Optional[torch.Tensor]]],
+                   outs: Optional[Sequence[torch.Tensor]] = None, status: Optional[torch.Tensor] = None):
+    """Several ``F.linear(x, w, b)`` in one launch.  groups: (x [rows, in] bf16 with a contiguous last dimension,
+    w [out, in] bf16, bias [out] bf16 or None); returns the list of outputs [rows, out] (``outs`` if given)."""
+    if not groups:
+        return []
+    arr = (N.LinearGroup * len(groups))()
+    res = []
+    dev = groups[0][0].device
+    for i, (x, w, b) in enumerate(groups):
+        _need_cuda(x, w, b)
+        if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or x.dim() != 2 or w.dim() != 2 or \
+                x.stride(1) != 1 or w.stride(1) != 1 or x.shape[1] != w.shape[1]:
+            raise ValueError("grouped_linear: x [rows, in] and w [out, in] must be bf16 with contiguous last dimensions")
+        if b is not None and (b.dtype != torch.bfloat16 or b.shape != (w.shape[0],) or not b.is_contiguous()):
+            raise ValueError("grouped_linear: bias must be a contiguous bf16 vector over the output features")
+        out = outs[i] if outs is not None else torch.empty((x.shape[0], w.shape[0]), dtype=torch.bfloat16, device=dev)
+        if out.shape != (x.shape[0], w.shape[0]) or out.dtype != torch.bfloat16 or out.stride(1) != 1:
+            raise ValueError("grouped_linear: out must be bf16 [rows, out] with a contiguous last dimension")
+        g = arr[i]
+        g.x, g.w, g.out = x.data_ptr(), w.data_ptr(), out.data_ptr()
+        g.bias = None if b is None else b.data_ptr()
+        g.ld_x, g.ld_w, g.ld_out = x.stride(0), w.stride(0), out.stride(0)
+        g.rows, g.in_features, g.out_features = x.shape[0], x.shape[1], w.shape[0]
+        res.append(out)
+    if status is None:
+        status = device_status(dev)
+    N.check("comfy_moe_grouped_linear", N.load().comfy_moe_grouped_linear(len(groups), arr, _ptr(status), _stream()))
+    return res

@@ -548,6 +548,55 @@ def swiglu_ffn_forward(ffn, x: torch.Tensor) -> Optional[torch.Tensor]:
 
 
 # ---- q / k / v glue of the HiDream attention processor ----------------------------------------------------------
+def _bias_linear_state(lin, device, in_features):
+    """(weight, bias or None) if this bf16 Linear can feed the grouped GEMM as it is now, else None."""
+    if lin.weight_function or lin.bias_function:
+        return None
+    w, b = lin.weight, lin.bias
+    if w.device != device or w.dtype != torch.bfloat16 or w.dim() != 2 or w.stride(1) != 1 or w.shape[1] != in_features:
+        return None
+    if w.shape[0] % 256 or w.shape[1] % 64 or w.stride(0) % 8 or w.data_ptr() % 16:
+        return None
+    if b is not None and (b.device != device or b.dtype != torch.bfloat16 or not b.is_contiguous() or b.data_ptr() % 16):
+        return None
+    return (w.detach(), None if b is None else b.detach())
+
+
+def grouped_projections(pairs):
+    """``[lin(x) for lin, x in pairs]`` for bias Linears that share a launch: every (Linear, tokens [.., in]) pair becomes
+    one group of one call of the grouped tcgen05 GEMM (a [B, S, in] slice of a longer sequence, whose batch elements
+    are not adjacent in memory, becomes one group per batch element).  Returns the list of outputs, or None when any
+    pair is not eligible (bf16 weights on the tokens' device, no patch closures, out_features % 256 == 0,
+    in_features % 64 == 0, at most nine groups)."""
+    if not ENABLE_SM100_KERNELS or not pairs:
+        return None
+    from . import moe_ops
+
+    groups, outs, results = [], [], []
+    for lin, x in pairs:
+        if not (x.is_cuda and x.dtype == torch.bfloat16 and x.stride(-1) == 1 and model_management.is_sm100(x.device)):
+            return None
+        state = _bias_linear_state(lin, x.device, x.shape[-1])
+        if state is None or x.data_ptr() % 16:
+            return None
+        w, bias = state
+        out = torch.empty(x.shape[:-1] + (w.shape[0],), dtype=x.dtype, device=x.device)
+        if x.is_contiguous():
+            parts = [(x.reshape(-1, x.shape[-1]), out.view(-1, w.shape[0]))]
+        elif x.dim() == 3 and x.stride(1) == x.shape[2] and (x.stride(0) * 2) % 16 == 0:
+            parts = [(x[i], out[i]) for i in range(x.shape[0])]
+        else:
+            return None
+        for xi, oi in parts:
+            groups.append((xi, w, bias))
+            outs.append(oi)
+        results.append(out)
+    if len(groups) > 9:
+        return None
+    moe_ops.grouped_linear(groups, outs)
+    return results
+
+
 def _norm_weight(norm, device):
     """bf16 weight of an RMSNorm that can feed the kernel as it is now, else None."""
     if getattr(norm, "weight_function", None) or getattr(norm, "bias_function", None) or norm.weight is None:
@@ -592,13 +641,21 @@ def hidream_qkv(attn, image_tokens: torch.Tensor, text_tokens: Optional[torch.Te
         return None
     eps = norms[0].eps if norms[0].eps is not None else torch.finfo(x.dtype).eps
     q, k, v = (torch.empty((b, s_img + s_txt, heads, head_dim), dtype=x.dtype, device=x.device) for _ in range(3))
-    moe_ops.rmsnorm_rope(attn.to_q(x), weights[0], eps, rope, heads, q)
-    moe_ops.rmsnorm_rope(attn.to_k(x), weights[1], eps, rope, heads, k)
-    moe_ops.rmsnorm_rope(attn.to_v(x), None, eps, None, heads, v)
+    # the three (six) projections: one launch of the grouped GEMM when the Linears are plain bf16, else one library
+    # GEMM each, as in the reference
+    pairs = [(attn.to_q, x), (attn.to_k, x), (attn.to_v, x)]
     if joint:
-        moe_ops.rmsnorm_rope(attn.to_q_t(text_tokens), weights[2], eps, rope, heads, q, s_img, s_img)
-        moe_ops.rmsnorm_rope(attn.to_k_t(text_tokens), weights[3], eps, rope, heads, k, s_img, s_img)
-        moe_ops.rmsnorm_rope(attn.to_v_t(text_tokens), None, eps, None, heads, v, s_img, 0)
+        pairs += [(attn.to_q_t, text_tokens), (attn.to_k_t, text_tokens), (attn.to_v_t, text_tokens)]
+    proj = grouped_projections(pairs)
+    if proj is None:
+        proj = [lin(t) for lin, t in pairs]
+    moe_ops.rmsnorm_rope(proj[0], weights[0], eps, rope, heads, q)
+    moe_ops.rmsnorm_rope(proj[1], weights[1], eps, rope, heads, k)
+    moe_ops.rmsnorm_rope(proj[2], None, eps, None, heads, v)
+    if joint:
+        moe_ops.rmsnorm_rope(proj[3], weights[2], eps, rope, heads, q, s_img, s_img)
+        moe_ops.rmsnorm_rope(proj[4], weights[3], eps, rope, heads, k, s_img, s_img)
+        moe_ops.rmsnorm_rope(proj[5], None, eps, None, heads, v, s_img, 0)
     return q, k, v
 
 

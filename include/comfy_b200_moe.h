@@ -291,6 +291,28 @@ typedef struct ComfyMoeMlpLayer {
 int comfy_moe_forward_gelu_mlp(const ComfyMoeMlpLayer* h_layer, const ComfyMoeWorkspace* h_ws, const void* x,
                                int n_tokens, void* out, void* stream);
 
+/* ---- several bias Linears in one launch (operations.Linear, comfy/ops.py:103-115) ----------------------------------
+ * out_g = bf16(x_g . w_g^T + bias_g) (fp32 accumulation, one rounding) for up to COMFY_MOE_MAX_EXPERTS + 1 independent
+ * groups: one launch of the persistent tcgen05 kernel with the bias epilogue.  Serves the q / k / v projections of
+ * HiDreamAttention for image and text tokens (comfy/ldm/hidream/model.py:97-119) as six groups, and its two output
+ * projections (:139-144) as two.  bf16; out_features % 256 == 0, in_features % 64 == 0, leading dimensions in elements
+ * and multiples of 8; rows may be 0 (group skipped).  status: a status block, see comfy_moe_read_status. */
+typedef struct ComfyMoeLinearGroup {
+  const void* x;      /* [rows, in_features], leading dimension ld_x */
+  const void* w;      /* [out_features, in_features], leading dimension ld_w */
+  const void* bias;   /* [out_features] or NULL */
+  void* out;          /* [rows, out_features], leading dimension ld_out */
+  int64_t ld_x;
+  int64_t ld_w;
+  int64_t ld_out;
+  int32_t rows;
+  int32_t in_features;
+  int32_t out_features;
+  int32_t reserved;
+} ComfyMoeLinearGroup;
+
+int comfy_moe_grouped_linear(int n_groups, const ComfyMoeLinearGroup* h_groups, int32_t* status, void* stream);
+
 /* ---- q / k / v glue of the HiDream attention processor (model.py:97-137) ------------------------------------------
  * One pass per projected tensor x [n_tokens, heads * head_dim] (bf16, row stride ld_x):
  *   n   = rms_norm(x, weight, eps) over the whole row as torch.nn.functional.rms_norm computes it for bf16 (fp32
@@ -327,6 +349,15 @@ int comfy_moe_quantize_e4m3(const void* x, const float* scale, int64_t n_element
  */
 int comfy_moe_stochastic_round_e4m3(const void* x, int x_dtype, const void* rand_fp16, int64_t n_elements, void* out,
                                     void* stream);
+
+/* ---- weight ingest: per-tensor scaled e4m3 -------------------------------------------------------------------------
+ * The convention of the scaled-fp8 checkpoints that scaled_fp8_ops.Linear loads (comfy/ops.py:379-410: `weight` in
+ * e4m3, `scale_weight` an fp32 scalar):  *scale_out = max|w| / 448 (fp32),  out = e4m3(w / *scale_out), division in fp32,
+ * round to nearest even.  Byte-identical to `s = w.float().abs().max() / 448; (w.float() / s).to(float8_e4m3fn)`.
+ * w: fp32, bf16 or fp16 (w_dtype), contiguous; scale_out: DEVICE fp32 [1]; out: e4m3 bytes.  Three nodes on `stream`
+ * (a 4-byte memset and two kernels), no host synchronisation. */
+int comfy_moe_quantize_weight_e4m3(const void* w, int w_dtype, int64_t n_elements, float* scale_out, void* out,
+                                   void* stream);
 
 /* ---- expert parallelism over peer memory (one process per GPU, NVLink peer access) ---------------------------
  * No counterpart in the reference (it runs on one GPU).  Tokens stay with their rank; expert e is computed by rank

@@ -52,6 +52,7 @@ def test_struct_layouts_match_header():
     assert ctypes.sizeof(N.MlpLayer) == 4 * 4 + 8 + (N.MAX_EXPERTS + 1) * ctypes.sizeof(N.MlpWeights)
     assert ctypes.sizeof(N.PeerPlan) == 4 * 4 + 2 * 4 * N.MAX_EXPERTS + 8 + 3 * 8 * N.MAX_RANKS
     assert N.FfnWeights.max_sms.offset == 3 * 8 + 2 * 8 + 4
+    assert ctypes.sizeof(N.LinearGroup) == 4 * 8 + 3 * 8 + 4 * 4
 
 
 def test_plan_sizes(lib):

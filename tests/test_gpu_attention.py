@@ -77,9 +77,14 @@ def test_kernel_against_oracle(cuda_device, heads, head_dim, axes, s_img, s_txt,
     mod = _module(layer, dim, heads, False, dev)
     with torch.no_grad():
         fast = ops.hidream_qkv(mod, img.to(dev), txt.to(dev), freqs.to(dev))
-        # the projections as this GPU's library GEMM computes them, so that only the glue is under test
-        proj = {"q": mod.to_q(img.to(dev)), "k": mod.to_k(img.to(dev)), "v": mod.to_v(img.to(dev)),
-                "q_t": mod.to_q_t(txt.to(dev)), "k_t": mod.to_k_t(txt.to(dev)), "v_t": mod.to_v_t(txt.to(dev))}
+        # the projections as the shim itself computes them (one launch of the grouped GEMM), so that only the glue is
+        # under test
+        pairs = [(mod.to_q, img.to(dev)), (mod.to_k, img.to(dev)), (mod.to_v, img.to(dev)),
+                 (mod.to_q_t, txt.to(dev)), (mod.to_k_t, txt.to(dev)), (mod.to_v_t, txt.to(dev))]
+        outs = ops.grouped_projections(pairs)
+        if outs is None:                                   # widths the grouped GEMM does not take: library GEMMs
+            outs = [lin(t) for lin, t in pairs]
+        proj = dict(zip(("q", "k", "v", "q_t", "k_t", "v_t"), outs))
     assert fast is not None
     want = A.norm_cat_rope({k: v.cpu() for k, v in proj.items()}, layer, freqs, heads)
     for got, ref, key in zip(fast, want, ("q", "k", "v")):
@@ -125,3 +130,47 @@ def test_fused_glue_timing_is_reported(cuda_device):
             ops.ENABLE_SM100_KERNELS = True
     print(f"HiDreamAttention forward, 2 x (4096 + 384) tokens: {fast:.3f} ms with the fused q/k/v glue, "
           f"{stock:.3f} ms as PyTorch composes it")
+
+
+@pytest.mark.parametrize("rows,k,n,bias", [(8192, 2560, 2560, True), (768, 2560, 2560, True), (300, 512, 768, False),
+                                           (1, 64, 256, True)])
+def test_grouped_linear_against_torch(cuda_device, rows, k, n, bias):
+    """Several Linears in one launch of the grouped GEMM: each output equals F.linear within the bf16 tolerance (fp32
+    accumulation in another order, one rounding), ragged row counts and strided inputs included."""
+    from comfyui_b200 import moe_ops as M
+
+    dev = cuda_device
+    g = torch.Generator().manual_seed(rows + n)
+    xs = [torch.randn((r, k), generator=g).bfloat16().to(dev) for r in (rows, max(rows // 3, 1), rows)]
+    xs[2] = torch.randn((rows, k + 64), generator=g).bfloat16().to(dev)[:, :k]          # leading dimension > width
+    ws = [(torch.randn((n, k), generator=g) * 0.02).bfloat16().to(dev) for _ in xs]
+    bs = [(torch.randn((n,), generator=g) * 0.1).bfloat16().to(dev) if bias else None for _ in xs]
+    outs = M.grouped_linear(list(zip(xs, ws, bs)))
+    M.read_status(M.device_status(dev))
+    for x, w, b, out in zip(xs, ws, bs, outs):
+        ref = torch.nn.functional.linear(x.float(), w.float(), None if b is None else b.float())
+        torch.testing.assert_close(out.float(), ref, rtol=2e-2, atol=2e-2)
+        assert float((out.float() - ref).norm() / ref.norm()) < 3e-3
+
+
+def test_attention_projections_take_the_grouped_gemm(cuda_device, monkeypatch):
+    """On an eligible call the six q / k / v projections and the two output projections run as two grouped launches."""
+    from comfyui_b200 import moe_ops as M
+
+    dev, heads, head_dim, b, s_img, s_txt = cuda_device, 4, 128, 2, 256, 32
+    dim = heads * head_dim
+    layer = A.make_layer(dim, heads, head_dim, False, seed=5, dtype=torch.bfloat16)
+    mod = _module(layer, dim, heads, False, dev)
+    g = torch.Generator().manual_seed(6)
+    img = torch.randn((b, s_img, dim), generator=g).bfloat16()
+    txt = torch.randn((b, s_txt, dim), generator=g).bfloat16()
+    freqs = A.rope_table(A.make_ids(b, 16, 16, s_txt), [64, 32, 32])
+    calls = []
+    stock = M.grouped_linear
+    monkeypatch.setattr(M, "grouped_linear", lambda groups, outs=None, status=None: calls.append(len(groups)) or stock(groups, outs, status))
+    with torch.no_grad():
+        got_i, got_t = mod(img.to(dev), None, txt.to(dev), rope=freqs.to(dev))
+    assert calls == [6, 4]            # q, k, v of image and text tokens; out projections per batch element
+    want_i, want_t = A.processor(layer, img, txt, freqs, heads)
+    torch.testing.assert_close(got_i.float().cpu(), want_i.float(), rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(got_t.float().cpu(), want_t.float(), rtol=2e-2, atol=2e-2)

@@ -57,3 +57,21 @@ def test_set_weight_on_the_device(cuda_device):
     first = lin.weight.data.clone()
     lin.set_weight(w, seed=5)
     assert torch.equal(first.view(torch.uint8), lin.weight.data.view(torch.uint8))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("shape", [(6912, 2560), (2560, 3584), (3, 5), (1,)])
+def test_scaled_e4m3_weight_quantiser(cuda_device, dtype, shape):
+    """s = max|w| / 448, wq = (w / s).to(e4m3): the kernel against the three torch operations, byte for byte."""
+    from comfyui_b200 import moe_ops as M
+
+    g = torch.Generator().manual_seed(sum(shape))
+    w = (torch.randn(shape, generator=g) * 0.02).to(dtype)
+    wq, scale = M.quantize_weight_e4m3(w.to(cuda_device))
+    # the three operations on the CPU, where `tensor / 448.0` is a true fp32 division (PyTorch's CUDA kernel multiplies by
+    # the reciprocal of a Python scalar instead, which can differ in the last bit)
+    ref_s = w.float().abs().max() / 448.0
+    ref_q = (w.float() / ref_s).to(torch.float8_e4m3fn)
+    assert scale.dtype == torch.float32 and scale.shape == () and torch.equal(scale.cpu(), ref_s)
+    assert torch.equal(wq.cpu().view(torch.uint8), ref_q.view(torch.uint8))
+    assert int(wq.view(torch.uint8).bitwise_and(0x7f).max()) == 0x7e        # the largest element lands on +-448
