@@ -86,15 +86,18 @@ absmax_kernel(const T* __restrict__ w, long long n, unsigned int* __restrict__ a
 template <typename T>
 __global__ void __launch_bounds__(256)
 scaled_e4m3_kernel(const T* __restrict__ w, long long n, const unsigned int* __restrict__ amax_bits,
-                   float* __restrict__ scale_out, uint8_t* __restrict__ out) {
+                   uint8_t* __restrict__ out) {
   const float s = __fdiv_rn(__uint_as_float(*amax_bits), 448.0f);
-  if (blockIdx.x == 0 && threadIdx.x == 0) *scale_out = s;
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n; i += stride) {
     // |w / s| <= 448 up to one rounding of the division, far from 464 where the cast would leave the format's range
     out[i] = static_cast<uint8_t>(__nv_cvt_float_to_fp8(__fdiv_rn(to_f32<T>(w[i]), s), __NV_SATFINITE, __NV_E4M3));
   }
 }
+
+// The word that held the maximum between the passes becomes the scale, once every block of the cast has read it
+// (stream order).
+__global__ void amax_to_scale_kernel(float* __restrict__ scale) { *scale = __fdiv_rn(*scale, 448.0f); }
 
 }  // namespace comfy_b200
 
@@ -117,13 +120,14 @@ extern "C" int comfy_moe_quantize_weight_e4m3(const void* w, int w_dtype, int64_
 #define COMFY_Q(T) \
   do { \
     absmax_kernel<T><<<g, 256, 0, s>>>(static_cast<const T*>(w), n_elements, amax); \
-    scaled_e4m3_kernel<T><<<g, 256, 0, s>>>(static_cast<const T*>(w), n_elements, amax, scale_out, o); \
+    scaled_e4m3_kernel<T><<<g, 256, 0, s>>>(static_cast<const T*>(w), n_elements, amax, o); \
   } while (0)
   if (w_dtype == COMFY_MOE_FP32) COMFY_Q(float);
   else if (w_dtype == COMFY_MOE_BF16) COMFY_Q(__nv_bfloat16);
   else if (w_dtype == COMFY_MOE_FP16) COMFY_Q(__half);
   else return COMFY_MOE_EUNSUPPORTED;
 #undef COMFY_Q
+  amax_to_scale_kernel<<<1, 1, 0, s>>>(scale_out);
   return check_launch();
 }
 

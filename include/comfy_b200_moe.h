@@ -354,8 +354,8 @@ int comfy_moe_stochastic_round_e4m3(const void* x, int x_dtype, const void* rand
  * The convention of the scaled-fp8 checkpoints that scaled_fp8_ops.Linear loads (comfy/ops.py:379-410: `weight` in
  * e4m3, `scale_weight` an fp32 scalar):  *scale_out = max|w| / 448 (fp32),  out = e4m3(w / *scale_out), division in fp32,
  * round to nearest even.  Byte-identical to `s = w.float().abs().max() / 448; (w.float() / s).to(float8_e4m3fn)`.
- * w: fp32, bf16 or fp16 (w_dtype), contiguous; scale_out: DEVICE fp32 [1]; out: e4m3 bytes.  Three nodes on `stream`
- * (a 4-byte memset and two kernels), no host synchronisation. */
+ * w: fp32, bf16 or fp16 (w_dtype), contiguous; scale_out: DEVICE fp32 [1]; out: e4m3 bytes.  Four nodes on `stream`
+ * (a 4-byte memset and three kernels), no host synchronisation. */
 int comfy_moe_quantize_weight_e4m3(const void* w, int w_dtype, int64_t n_elements, float* scale_out, void* out,
                                    void* stream);
 

@@ -249,7 +249,9 @@ def test_unclamped_quantiser_overflow_is_nan_and_counted(M, cuda_device):
     ref_out, _, _ = O.moe_layer(x, layer, mode=O.FP8_MATMUL, routing=(ridx, rw))
     assert torch.equal(torch.isnan(out.float()), torch.isnan(ref_out.float()))
     nan = torch.isnan(out.float())
-    assert bool(nan[1:5].all()) and not bool(nan[0].any()) and not bool(nan[5:].any())
+    # rows 1-4 overflow in the input cast; row 0 (464, which still rounds to 448) overflows later, where
+    # h = silu(w1 x) * (w3 x) is cast for w2, i.e. in the first GEMM pass's epilogue
+    assert bool(nan[:5].all()) and not bool(nan[5:].any())
 
 
 def test_status_word_is_sticky_across_layers(M, cuda_device):
