@@ -623,10 +623,18 @@ def run_gpu_arm(args) -> None:
             line["ep_parity"]["config5"] = expert_parallel_parity(arm5)
         arm = arm5
 
+    if extras and world == 1:
+        del arm
+        torch.cuda.empty_cache()
+        arm = None
+        sub = measure_config4(dev, "bf16", steps=5, local_rank=local_rank)
+        sub.pop("metric"), sub.pop("higher_is_better"), sub.pop("data")
+        line["config4"] = sub
+
     if world == 1 and not args.no_cpu_baseline and rank == 0:
         line["cpu_baseline"] = cpu_baseline_object(args.dtype, reps=10)
 
-    if args.timeline or args.timeline_dir:
+    if (args.timeline or args.timeline_dir) and arm is not None:
         with torch.inference_mode():
             if args.timeline_dir:           # every rank writes its own file
                 os.makedirs(args.timeline_dir, exist_ok=True)
@@ -879,105 +887,104 @@ def run_hunyuan3d(args) -> None:
     }))
 
 
-def run_dit_body(args) -> None:
-    """Side workload (not the headline): the transformer body of benchmark configuration 4, i.e. 16 double-stream and 32
-    single-stream HiDream blocks (dim 2560, 20 heads x 128, MoE feed-forward on the image tokens), random-init bf16,
-    2 x 4096 image tokens + 2 x 384 text tokens (128 T5 + 2 x 128 Llama), one pass = one denoising step without the
-    embedders and the final layer.  Timed with the kernels and, on the same modules, as PyTorch composes it."""
-    from comfyui_b200 import _native, ops
-    from comfyui_b200.ldm.hidream import model as M
+HIDREAM_I1 = dict(patch_size=2, in_channels=16, out_channels=16, num_layers=16, num_single_layers=32,
+                  attention_head_dim=128, num_attention_heads=20, caption_channels=[4096, 4096], text_emb_dim=2048,
+                  num_routed_experts=4, num_activated_experts=2, axes_dims_rope=[64, 32, 32], max_resolution=[128, 128],
+                  llama_layers=list(range(32)) + [31] * 16)
 
-    _native.load()
-    dev = torch.device("cuda", 0)
-    dim, heads, head_dim, b, s_img, s_txt = 2560, 20, 128, 2, 4096, 384
-    n_double, n_single = args.double_blocks, args.single_blocks
-    torch.manual_seed(0)
 
-    fp8 = args.dtype == "fp8"
+def measure_config4(dev, dtype: str, steps: int, n_double: int = 16, n_single: int = 32, local_rank: int = 0):
+    """Benchmark configuration 4: one denoising step of a HiDream-I1-shaped transformer (16 double-stream + 32
+    single-stream blocks, 20 heads x 128, MoE feed-forward on the image tokens), random-init weights, latent
+    [2, 16, 128, 128], T5 states [2, 128, 4096], per-layer Llama states [2, 32, 128, 4096], pooled [2, 2048]; the whole
+    model call (embedders, text projections, blocks, final layer).  Timed with the kernels and, on the same modules
+    and weights, as PyTorch composes it on this GPU."""
+    from comfyui_b200 import ops
+    from comfyui_b200.ldm.hidream.model import HiDreamImageTransformer2DModel
+
+    fp8 = dtype == "fp8"
     operations = ops.disable_weight_init if not fp8 else ops.scaled_fp8_ops(
         fp8_matrix_mult=True, scale_input=False, override_dtype=torch.float8_e4m3fn)
+    cfg = dict(HIDREAM_I1, num_layers=n_double, num_single_layers=n_single)
+    cfg["llama_layers"] = HIDREAM_I1["llama_layers"][:n_double + n_single]
+    torch.manual_seed(0)
+    model = HiDreamImageTransformer2DModel(**cfg, dtype=torch.bfloat16, device=dev, operations=operations).eval()
+    with torch.no_grad():
+        for mod in model.modules():
+            w = getattr(mod, "weight", None)
+            if isinstance(mod, torch.nn.Linear) and w is not None and w.dtype == torch.float8_e4m3fn:
+                # scaled fp8 checkpoint convention: s = max|w| / 448, weight = (w / s) in e4m3, scale_weight = s
+                full = torch.randn(w.shape, device=dev) * 0.02
+                sc = full.abs().max() / 448.0
+                w.copy_((full / sc).to(torch.float8_e4m3fn))
+                mod.scale_weight.fill_(float(sc))
+                if mod.bias is not None:
+                    mod.bias.copy_((torch.randn(mod.bias.shape, device=dev) * 0.02).to(mod.bias.dtype))
+        for name, p in model.named_parameters():
+            if p.dtype == torch.float8_e4m3fn or name.endswith("scale_weight"):
+                continue
+            if "rms_norm" in name:
+                p.fill_(1.0)
+            else:
+                p.normal_(0.0, 0.02)
+    n_params = sum(p.numel() for p in model.parameters())
+    b = 2
+    x = torch.randn((b, 16, 128, 128), device=dev).bfloat16()
+    t = torch.tensor([500.0, 500.0], device=dev)
+    y = torch.randn((b, 2048), device=dev).bfloat16()
+    context = torch.randn((b, 128, 4096), device=dev).bfloat16()
+    llama = torch.randn((b, 32, 128, 4096), device=dev).bfloat16()
 
-    def build(single):
-        cls = M.HiDreamImageSingleTransformerBlock if single else M.HiDreamImageTransformerBlock
-        blk = cls(dim, heads, head_dim, 4, 2, dtype=torch.bfloat16, device=dev, operations=operations).eval()
-        with torch.no_grad():
-            for mod in blk.modules():
-                w = getattr(mod, "weight", None)
-                if isinstance(mod, torch.nn.Linear) and w is not None and w.dtype == torch.float8_e4m3fn:
-                    # scaled fp8 checkpoint convention: s = max|w| / 448, weight = (w / s) in e4m3, scale_weight = s
-                    full = torch.randn(w.shape, device=dev) * 0.02
-                    sc = full.abs().max() / 448.0
-                    w.copy_((full / sc).to(torch.float8_e4m3fn))
-                    mod.scale_weight.fill_(float(sc))
-                    if mod.bias is not None:
-                        mod.bias.copy_((torch.randn(mod.bias.shape, device=dev) * 0.02).to(mod.bias.dtype))
-            for name, p in blk.named_parameters():
-                if p.dtype == torch.float8_e4m3fn or name.endswith("scale_weight"):
-                    continue
-                if "rms_norm" in name:
-                    p.fill_(1.0)
-                else:
-                    p.normal_(0.0, 0.02)
-        return blk
-
-    doubles = [build(False) for _ in range(n_double)]
-    singles = [build(True) for _ in range(n_single)]
-    img = torch.randn((b, s_img, dim), device=dev).bfloat16()
-    txt = torch.randn((b, s_txt, dim), device=dev).bfloat16()
-    ada = torch.randn((b, dim), device=dev).bfloat16()
-    # the model's position ids: (0, row, column) for the 64 x 64 patches, zeros for text tokens
-    ids = torch.zeros((b, s_img + s_txt, 3), device=dev)
-    ids[:, :s_img, 1] = torch.arange(64, device=dev).repeat_interleave(64)
-    ids[:, :s_img, 2] = torch.arange(64, device=dev).repeat(64)
-    omega = [1.0 / (10000 ** torch.linspace(0, (d - 2) / d, steps=d // 2, dtype=torch.float64, device=dev))
-             for d in (64, 32, 32)]
-    ang = torch.cat([ids[..., i, None].float() * omega[i].float() for i in range(3)], dim=-1)
-    rope = torch.stack([ang.cos(), -ang.sin(), ang.sin(), ang.cos()], dim=-1).reshape(b, s_img + s_txt, 1, 64, 2, 2)
-    rope = rope.float().contiguous()
-
-    def step():
-        x, t = img, txt
-        for blk in doubles:
-            x, t = blk(x, None, t, ada, rope)
-        seq = torch.cat([x, t], dim=1)
-        for blk in singles:
-            seq = blk(seq, None, None, ada, rope)
-        return seq
-
-    def timed(steps, warmup):
+    def timed(count, warmup):
         for _ in range(warmup):
-            step()
+            model(x, t, y, context, llama)
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        for _ in range(steps):
-            step()
+        for _ in range(count):
+            out = model(x, t, y, context, llama)
         e1.record()
         torch.cuda.synchronize()
-        return e0.elapsed_time(e1) / steps
+        return e0.elapsed_time(e1) / count, out
 
-    steps = min(args.steps, 10)
     with torch.inference_mode():
-        with ClockSampler(0) as clocks:
-            ms = timed(steps, 3)
+        with ClockSampler(local_rank) as clocks:
+            ms, out = timed(steps, 2)
+        ops.check_device_status()
+        finite = bool(torch.isfinite(out.float()).all())
         ops.ENABLE_SM100_KERNELS = False
         try:
-            ms_stock = timed(max(steps // 2, 2), 2)
+            ms_stock, out_stock = timed(max(steps // 2, 2), 1)
         finally:
             ops.ENABLE_SM100_KERNELS = True
-    print(json.dumps({
-        "metric": "denoising-step body, ms (HiDream-I1 transformer blocks)", "value": ms, "unit": "ms",
-        "n_gpus": 1, "steps": steps, "warmup": 3, "ms_per_step": ms, "higher_is_better": False, "dtype": args.dtype,
-        "data": "synthetic",
-        "config": {"workload": f"benchmark configuration 4 without embedders and final layer: {n_double} double-stream + "
-                               f"{n_single} single-stream blocks, 2 x (4096 image + 384 text) tokens, random-init "
+        rel = float((out.float() - out_stock.float()).norm() / out_stock.float().norm())
+    del model
+    torch.cuda.empty_cache()
+    return {
+        "metric": "one denoising step, ms (HiDream-I1-shaped transformer, whole model call)", "value": ms, "unit": "ms",
+        "steps": steps, "ms_per_step": ms, "higher_is_better": False, "dtype": dtype, "data": "synthetic",
+        "config": {"workload": f"benchmark configuration 4: {n_double} double-stream + {n_single} single-stream blocks, "
+                               "latent [2, 16, 128, 128] (2 x 4096 image tokens), T5 [2, 128, 4096], Llama "
+                               "[2, 32, 128, 4096], pooled [2, 2048], random-init "
                                + ("scaled fp8 e4m3 Linears (fp8 matrix multiplication), bf16 activations" if fp8 else "bf16"),
-                   "dim": dim, "heads": heads, "head_dim": head_dim, "experts": 4, "top_k": 2},
-        "clocks": clocks.summary(),
+                   "parameters": n_params, "dim": 2560, "heads": 20, "head_dim": 128, "experts": 4, "top_k": 2},
+        "clocks": clocks.summary(), "output_finite": finite,
         "gpu_bar": {"what": "same modules and weights, sm_100a kernels off: stock PyTorch composition on this GPU",
                     "ms_per_step": ms_stock},
         "speedup_vs_stock": ms_stock / ms,
-    }))
+        "rel_rms_vs_stock_output": rel,
+    }
+
+
+def run_dit(args) -> None:
+    """Side workload: benchmark configuration 4 on one GPU (see measure_config4)."""
+    from comfyui_b200 import _native
+
+    _native.load()
+    dev = torch.device("cuda", 0)
+    res = measure_config4(dev, args.dtype, min(args.steps, 10), args.double_blocks, args.single_blocks)
+    res.update({"n_gpus": 1, "warmup": 2})
+    print(json.dumps(res))
 
 
 def main() -> None:
@@ -986,12 +993,13 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--double-blocks", type=int, default=16, help="dit_body: number of double-stream blocks")
-    ap.add_argument("--single-blocks", type=int, default=32, help="dit_body: number of single-stream blocks")
-    ap.add_argument("--workload", default="hidream", choices=["hidream", "config5", "hunyuan3d", "dit_body"],
+    ap.add_argument("--double-blocks", type=int, default=16, help="dit: number of double-stream blocks")
+    ap.add_argument("--single-blocks", type=int, default=32, help="dit: number of single-stream blocks")
+    ap.add_argument("--workload", default="hidream", choices=["hidream", "config5", "hunyuan3d", "dit", "dit_body"],
                     help="hidream = the headline layer (8192 tokens per GPU, weak scaling); config5 = 131072 tokens in "
                          "total with a skewed router (strong scaling); hunyuan3d = the sibling GELU-MLP MoE block "
-                         "(one GPU, bf16)")
+                         "(one GPU, bf16); dit = benchmark configuration 4, one denoising step of the whole HiDream-I1-shaped "
+                         "transformer (one GPU; dit_body is an alias)")
     ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp8"],
                     help="bf16 (benchmark configuration 2, the default) or per-tensor scaled fp8 e4m3 expert weights (configuration 3)")
     ap.add_argument("--timeline", action="store_true",
@@ -1007,8 +1015,8 @@ def main() -> None:
         run_reference_arm(args)
     elif args.workload == "hunyuan3d":
         run_hunyuan3d(args)
-    elif args.workload == "dit_body":
-        run_dit_body(args)
+    elif args.workload in ("dit", "dit_body"):
+        run_dit(args)
     else:
         run_gpu_arm(args)
 

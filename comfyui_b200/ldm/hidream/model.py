@@ -386,3 +386,302 @@ class HiDreamImageBlock(nn.Module):
                 transformer_options={}):
         return self.block(image_tokens, image_tokens_masks, text_tokens, adaln_input, rope,
                           transformer_options=transformer_options)
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# The model around the blocks (``comfy/ldm/hidream/model.py:21-72, 349-357, 571-829``): embedders, per-layer text
+# projections, the block loop with its Llama-state concatenations, final layer.  Same constructor, attribute names and
+# state-dict keys as the reference, so a HiDream-I1 checkpoint loads with ``load_state_dict(strict=True)``; the
+# forward is the reference's sequence of steps, and every block inside it takes the kernels where it is eligible.
+# ---------------------------------------------------------------------------------------------------------------
+import math  # noqa: E402
+from typing import List, Tuple  # noqa: E402
+
+
+def rope(pos: torch.Tensor, dim: int, theta: int) -> torch.Tensor:
+    """Rotation matrices of one position axis (``comfy/ldm/flux/math.py:23-36``): [..., n] positions ->
+    [..., n, dim / 2, 2, 2] fp32 with rows (cos, -sin), (sin, cos); the angles are formed in fp64 frequencies times fp32
+    positions, as there."""
+    if dim % 2:
+        raise ValueError("rope: dim must be even")
+    exponent = torch.linspace(0, (dim - 2) / dim, steps=dim // 2, dtype=torch.float64, device=pos.device)
+    omega = 1.0 / (theta ** exponent)
+    angle = torch.einsum("...n,d->...nd", pos.to(dtype=torch.float32), omega)
+    mat = torch.stack([torch.cos(angle), -torch.sin(angle), torch.sin(angle), torch.cos(angle)], dim=-1)
+    return mat.reshape(*mat.shape[:-1], 2, 2).to(dtype=torch.float32)
+
+
+class EmbedND(nn.Module):
+    """Rotary table of multi-axis position ids (``model.py:21-33``): ids [B, S, axes] -> [B, S, 1, sum(axes_dim) / 2, 2, 2]."""
+
+    def __init__(self, theta: int, axes_dim: List[int]):
+        super().__init__()
+        self.theta = theta
+        self.axes_dim = axes_dim
+
+    def forward(self, ids: torch.Tensor) -> torch.Tensor:
+        parts = [rope(ids[..., i], self.axes_dim[i], self.theta) for i in range(ids.shape[-1])]
+        return torch.cat(parts, dim=-3).unsqueeze(2)
+
+
+def _sinusoidal_embedding(timesteps: torch.Tensor, channels: int, flip_sin_to_cos: bool, downscale_freq_shift: float,
+                          scale: float = 1, max_period: int = 10000) -> torch.Tensor:
+    """``comfy/ldm/lightricks/model.py:13-64``: [N] timesteps -> [N, channels] sinusoidal features in fp32."""
+    if timesteps.dim() != 1:
+        raise ValueError("timesteps must be one-dimensional")
+    half = channels // 2
+    exponent = -math.log(max_period) * torch.arange(start=0, end=half, dtype=torch.float32, device=timesteps.device)
+    exponent = exponent / (half - downscale_freq_shift)
+    emb = scale * (timesteps[:, None].float() * torch.exp(exponent)[None, :])
+    emb = torch.cat([torch.sin(emb), torch.cos(emb)], dim=-1)
+    if flip_sin_to_cos:
+        emb = torch.cat([emb[:, half:], emb[:, :half]], dim=-1)
+    if channels % 2 == 1:
+        emb = F.pad(emb, (0, 1, 0, 0))
+    return emb
+
+
+class Timesteps(nn.Module):
+    """``comfy/ldm/lightricks/model.py:116-132``."""
+
+    def __init__(self, num_channels: int, flip_sin_to_cos: bool, downscale_freq_shift: float, scale: int = 1):
+        super().__init__()
+        self.num_channels = num_channels
+        self.flip_sin_to_cos = flip_sin_to_cos
+        self.downscale_freq_shift = downscale_freq_shift
+        self.scale = scale
+
+    def forward(self, timesteps):
+        return _sinusoidal_embedding(timesteps, self.num_channels, self.flip_sin_to_cos, self.downscale_freq_shift,
+                                     self.scale)
+
+
+class TimestepEmbedding(nn.Module):
+    """Linear, SiLU, Linear (``comfy/ldm/lightricks/model.py:67-113``); keys ``linear_1``, ``linear_2`` (``cond_proj``)."""
+
+    def __init__(self, in_channels: int, time_embed_dim: int, act_fn: str = "silu", out_dim: int = None,
+                 post_act_fn: Optional[str] = None, cond_proj_dim=None, sample_proj_bias=True, dtype=None, device=None,
+                 operations=None):
+        super().__init__()
+        self.linear_1 = operations.Linear(in_channels, time_embed_dim, sample_proj_bias, dtype=dtype, device=device)
+        self.cond_proj = None
+        if cond_proj_dim is not None:
+            self.cond_proj = operations.Linear(cond_proj_dim, in_channels, bias=False, dtype=dtype, device=device)
+        self.act = nn.SiLU()
+        self.linear_2 = operations.Linear(time_embed_dim, out_dim if out_dim is not None else time_embed_dim,
+                                          sample_proj_bias, dtype=dtype, device=device)
+        self.post_act = None
+
+    def forward(self, sample, condition=None):
+        if condition is not None:
+            sample = sample + self.cond_proj(condition)
+        return self.linear_2(self.act(self.linear_1(sample)))
+
+
+class PatchEmbed(nn.Module):
+    """``model.py:36-51``: one Linear over flattened patches; key ``proj``."""
+
+    def __init__(self, patch_size=2, in_channels=4, out_channels=1024, dtype=None, device=None, operations=None):
+        super().__init__()
+        self.patch_size = patch_size
+        self.out_channels = out_channels
+        self.proj = operations.Linear(in_channels * patch_size * patch_size, out_channels, bias=True, dtype=dtype,
+                                      device=device)
+
+    def forward(self, latent):
+        return self.proj(latent)
+
+
+class PooledEmbed(nn.Module):
+    """``model.py:54-60``; key ``pooled_embedder``."""
+
+    def __init__(self, text_emb_dim, hidden_size, dtype=None, device=None, operations=None):
+        super().__init__()
+        self.pooled_embedder = TimestepEmbedding(in_channels=text_emb_dim, time_embed_dim=hidden_size, dtype=dtype,
+                                                 device=device, operations=operations)
+
+    def forward(self, pooled_embed):
+        return self.pooled_embedder(pooled_embed)
+
+
+class TimestepEmbed(nn.Module):
+    """``model.py:63-72``; keys ``timestep_embedder.*`` (``time_proj`` has no parameters)."""
+
+    def __init__(self, hidden_size, frequency_embedding_size=256, dtype=None, device=None, operations=None):
+        super().__init__()
+        self.time_proj = Timesteps(num_channels=frequency_embedding_size, flip_sin_to_cos=True, downscale_freq_shift=0)
+        self.timestep_embedder = TimestepEmbedding(in_channels=frequency_embedding_size, time_embed_dim=hidden_size,
+                                                   dtype=dtype, device=device, operations=operations)
+
+    def forward(self, timesteps, wdtype):
+        return self.timestep_embedder(self.time_proj(timesteps).to(dtype=wdtype))
+
+
+class TextProjection(nn.Module):
+    """``model.py:349-357``: bias-free Linear; key ``linear``."""
+
+    def __init__(self, in_features, hidden_size, dtype=None, device=None, operations=None):
+        super().__init__()
+        self.linear = operations.Linear(in_features=in_features, out_features=hidden_size, bias=False, dtype=dtype,
+                                        device=device)
+
+    def forward(self, caption):
+        return self.linear(caption)
+
+
+class LastLayer(nn.Module):
+    """``comfy/ldm/flux/layers.py:264-278``: modulated LayerNorm (``addcmul(shift, norm(x), 1 + scale)``) and the output
+    Linear; keys ``linear``, ``adaLN_modulation.1`` (``norm_final`` has no parameters)."""
+
+    def __init__(self, hidden_size: int, patch_size: int, out_channels: int, dtype=None, device=None, operations=None):
+        super().__init__()
+        self.norm_final = operations.LayerNorm(hidden_size, elementwise_affine=False, eps=1e-6, dtype=dtype, device=device)
+        self.linear = operations.Linear(hidden_size, patch_size * patch_size * out_channels, bias=True, dtype=dtype,
+                                        device=device)
+        self.adaLN_modulation = nn.Sequential(nn.SiLU(), operations.Linear(hidden_size, 2 * hidden_size, bias=True,
+                                                                           dtype=dtype, device=device))
+
+    def forward(self, x, vec, modulation_dims=None):
+        if vec.ndim == 2:
+            vec = vec[:, None, :]
+        shift, scale = self.adaLN_modulation(vec).chunk(2, dim=-1)
+        if modulation_dims is not None:
+            raise NotImplementedError("per-range modulation is not used by HiDream")
+        return self.linear(torch.addcmul(shift, self.norm_final(x), 1 + scale))
+
+
+def pad_to_patch_size(img, patch_size=(2, 2), padding_mode="circular"):
+    """``comfy/ldm/common_dit.py:5-13``: pad the trailing spatial dimensions up to multiples of the patch size."""
+    pad = ()
+    for i in range(img.ndim - 2):
+        pad = (0, (patch_size[i] - img.shape[i + 2] % patch_size[i]) % patch_size[i]) + pad
+    return F.pad(img, pad, mode=padding_mode)
+
+
+class HiDreamImageTransformer2DModel(nn.Module):
+    """The HiDream-I1 diffusion transformer (``model.py:571-829``): one call = one denoising step.
+
+    forward(x [B, C, H, W] latent, t [B] timesteps, y [B, text_emb_dim] pooled embedding, context [B, S_t5, C_t5],
+    encoder_hidden_states_llama3 [B, L, S_llama, C_llama]) -> [B, C_out, H, W]."""
+
+    def __init__(self, patch_size: Optional[int] = None, in_channels: int = 64, out_channels: Optional[int] = None,
+                 num_layers: int = 16, num_single_layers: int = 32, attention_head_dim: int = 128,
+                 num_attention_heads: int = 20, caption_channels: List[int] = None, text_emb_dim: int = 2048,
+                 num_routed_experts: int = 4, num_activated_experts: int = 2, axes_dims_rope: Tuple[int, int] = (32, 32),
+                 max_resolution: Tuple[int, int] = (128, 128), llama_layers: List[int] = None, image_model=None,
+                 dtype=None, device=None, operations=None):
+        super().__init__()
+        self.patch_size = patch_size
+        self.num_attention_heads = num_attention_heads
+        self.attention_head_dim = attention_head_dim
+        self.num_layers = num_layers
+        self.num_single_layers = num_single_layers
+        self.gradient_checkpointing = False
+        self.dtype = dtype
+        self.out_channels = out_channels or in_channels
+        self.inner_dim = num_attention_heads * attention_head_dim
+        self.llama_layers = llama_layers
+        kw = dict(dtype=dtype, device=device, operations=operations)
+
+        self.t_embedder = TimestepEmbed(self.inner_dim, **kw)
+        self.p_embedder = PooledEmbed(text_emb_dim, self.inner_dim, **kw)
+        self.x_embedder = PatchEmbed(patch_size=patch_size, in_channels=in_channels, out_channels=self.inner_dim, **kw)
+        self.pe_embedder = EmbedND(theta=10000, axes_dim=axes_dims_rope)
+
+        def blocks(count, block_type):
+            return nn.ModuleList([
+                HiDreamImageBlock(dim=self.inner_dim, num_attention_heads=num_attention_heads,
+                                  attention_head_dim=attention_head_dim, num_routed_experts=num_routed_experts,
+                                  num_activated_experts=num_activated_experts, block_type=block_type, **kw)
+                for _ in range(count)])
+
+        self.double_stream_blocks = blocks(num_layers, BlockType.TransformerBlock)
+        self.single_stream_blocks = blocks(num_single_layers, BlockType.SingleTransformerBlock)
+        self.final_layer = LastLayer(self.inner_dim, patch_size, self.out_channels, **kw)
+        # one projection per block for that block's Llama layer, and a last one for the T5 states
+        widths = [caption_channels[1]] * (num_layers + num_single_layers) + [caption_channels[0]]
+        self.caption_projection = nn.ModuleList([TextProjection(in_features=w, hidden_size=self.inner_dim, **kw)
+                                                 for w in widths])
+        self.max_seq = max_resolution[0] * max_resolution[1] // (patch_size * patch_size)
+
+    def expand_timesteps(self, timesteps, batch_size, device):
+        if not torch.is_tensor(timesteps):
+            dtype = torch.float64 if isinstance(timesteps, float) else torch.int64
+            timesteps = torch.tensor([timesteps], dtype=dtype, device=device)
+        elif timesteps.dim() == 0:
+            timesteps = timesteps[None].to(device)
+        return timesteps.expand(batch_size)
+
+    def patchify(self, x, max_seq, img_sizes=None):
+        """[B, C, H, W] -> [B, (H / p)(W / p), p p C] (patch pixels outermost, channels innermost), as ``:682-705``."""
+        if not isinstance(x, torch.Tensor) or img_sizes is not None:
+            raise NotImplementedError("only same-size batches given as one tensor are supported")
+        p = self.patch_size
+        b, c, h, w = x.shape
+        ph, pw = h // p, w // p
+        x = x.reshape(b, c, ph, p, pw, p).permute(0, 2, 4, 3, 5, 1).reshape(b, ph * pw, p * p * c)
+        return x, None, [[ph, pw]] * b
+
+    def unpatchify(self, x: torch.Tensor, img_sizes) -> torch.Tensor:
+        p = self.patch_size
+        out = []
+        for i, (ph, pw) in enumerate(img_sizes):
+            tile = x[i, :ph * pw].reshape(1, ph, pw, p, p, -1)
+            out.append(tile.permute(0, 5, 1, 3, 2, 4).reshape(1, -1, ph * p, pw * p))
+        return torch.cat(out, dim=0)
+
+    def forward(self, x, t, y=None, context=None, encoder_hidden_states_llama3=None, image_cond=None, control=None,
+                transformer_options={}):
+        return self._forward(x, t, y, context, encoder_hidden_states_llama3, image_cond, control, transformer_options)
+
+    def _forward(self, x, t, y=None, context=None, encoder_hidden_states_llama3=None, image_cond=None, control=None,
+                 transformer_options={}):
+        bs, c, h, w = x.shape
+        if image_cond is not None:
+            x = torch.cat([x, image_cond], dim=-1)
+        latent = pad_to_patch_size(x, (self.patch_size, self.patch_size))
+        batch, wdtype, dev = latent.shape[0], latent.dtype, latent.device
+
+        # conditioning vector of every block's adaLN: timestep embedding + pooled text embedding
+        adaln_input = self.t_embedder(self.expand_timesteps(t, batch, dev), wdtype) + self.p_embedder(y)
+
+        tokens, masks, img_sizes = self.patchify(latent, self.max_seq)
+        ph, pw = img_sizes[0]
+        img_ids = torch.zeros(ph, pw, 3, device=dev)
+        img_ids[..., 1] += torch.arange(ph, device=dev)[:, None]
+        img_ids[..., 2] += torch.arange(pw, device=dev)[None, :]
+        img_ids = img_ids.reshape(1, ph * pw, 3).expand(batch, -1, -1)
+        tokens = self.x_embedder(tokens)
+
+        # text states: one Llama layer per block (projected by that block's own Linear), then T5 last
+        llama = encoder_hidden_states_llama3.movedim(1, 0)
+        text = [self.caption_projection[i](llama[k]).view(batch, -1, tokens.shape[-1])
+                for i, k in enumerate(self.llama_layers)]
+        text.append(self.caption_projection[-1](context).view(batch, -1, tokens.shape[-1]))
+
+        n_text = text[-1].shape[1] + text[-2].shape[1] + text[0].shape[1]
+        txt_ids = torch.zeros(batch, n_text, 3, device=dev, dtype=img_ids.dtype)
+        rope_table = self.pe_embedder(torch.cat((img_ids, txt_ids), dim=1))
+
+        block_id = 0
+        carried = torch.cat([text[-1], text[-2]], dim=1)          # T5 and the last Llama layer travel through the blocks
+        carried_len = carried.shape[1]
+        for block in self.double_stream_blocks:
+            cur = torch.cat([carried, text[block_id]], dim=1)
+            tokens, carried = block(image_tokens=tokens, image_tokens_masks=masks, text_tokens=cur,
+                                    adaln_input=adaln_input, rope=rope_table, transformer_options=transformer_options)
+            carried = carried[:, :carried_len]
+            block_id += 1
+
+        n_image = tokens.shape[1]
+        tokens = torch.cat([tokens, carried], dim=1)
+        joint_len = tokens.shape[1]
+        for block in self.single_stream_blocks:
+            tokens = torch.cat([tokens, text[block_id]], dim=1)
+            tokens = block(image_tokens=tokens, image_tokens_masks=masks, text_tokens=None, adaln_input=adaln_input,
+                           rope=rope_table, transformer_options=transformer_options)
+            tokens = tokens[:, :joint_len]
+            block_id += 1
+
+        out = self.final_layer(tokens[:, :n_image, ...], adaln_input)
+        return -self.unpatchify(out, img_sizes)[:, :, :h, :w]

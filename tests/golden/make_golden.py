@@ -1,4 +1,5 @@
-"""Generates tests/golden/hidream_moe_small.npz and hunyuan3d_moe_small.npz by running the UNMODIFIED reference.
+"""Generates the files under tests/golden/ (MoE layer, weight rounding, Hunyuan3D MoE, attention, blocks, whole model)
+by running the UNMODIFIED reference.
 
 Usage (in a container that has the reference tree; it is not needed at test time):
 
@@ -296,6 +297,48 @@ def blocks(ref_root: str) -> None:
     print("wrote", path, os.path.getsize(path), "bytes")
 
 
+def model(ref_root: str) -> None:
+    """HiDreamImageTransformer2DModel (comfy/ldm/hidream/model.py:571-829) at reduced depth and width, one denoising
+    step: as shipped in fp32 and bf16, and in bf16 with the MoE gates evaluated on the fp32 copy of their input (the
+    routing convention the kernels follow: indices from the fp32 gate, weights cast back to the activation dtype).
+    The attention variant is the one a CUDA device selects."""
+    import comfy.ldm.hidream.model as RM
+    import comfy.ldm.modules.attention as RA
+    import comfy.ops
+
+    from oracle import hidream_model_recipe as R
+
+    stock_select, stock_gate = RM.optimized_attention, RM.MoEGate.forward
+    RM.optimized_attention = RA.attention_pytorch
+
+    def gate_on_fp32_copy(self, hidden_states):
+        # the reference's own MoEGate.forward, handed x.float(): nothing inside the module is changed
+        idx, w, aux = stock_gate(self, hidden_states.float())
+        return idx, w.to(hidden_states.dtype), aux
+
+    out = {}
+    keys = None
+    for name, dtype, fp32_gate in (("fp32", torch.float32, False), ("bf16", torch.bfloat16, False),
+                                   ("bf16_fp32gate", torch.bfloat16, True)):
+        m = RM.HiDreamImageTransformer2DModel(**R.CONFIG, dtype=dtype, device="cpu",
+                                              operations=comfy.ops.disable_weight_init).eval()
+        shapes = {k: v.shape for k, v in m.state_dict().items()}
+        res = m.load_state_dict(R.make_state(shapes, dtype), strict=True)
+        assert not res.missing_keys and not res.unexpected_keys
+        keys = list(shapes.keys())
+        RM.MoEGate.forward = gate_on_fp32_copy if fp32_gate else stock_gate
+        with torch.no_grad():
+            out[f"{name}/out"] = m(*R.make_inputs(dtype)).detach().float().numpy()
+    RM.MoEGate.forward = stock_gate
+    RM.optimized_attention = stock_select
+    out["keys"] = np.array(keys)
+    out["shapes"] = np.array([",".join(str(d) for d in shapes[k]) for k in keys])
+    out["torch_version"] = np.array([torch.__version__])
+    path = os.path.join(HERE, "hidream_model_small.npz")
+    np.savez_compressed(path, **out)
+    print("wrote", path, os.path.getsize(path), "bytes")
+
+
 def rounding_input(dtype):
     """Seeded tensor with the edge cases of the stochastic rounding in its first row."""
     g = torch.Generator().manual_seed(11)
@@ -330,10 +373,20 @@ def weight_rounding(ref_root: str) -> None:
     print("wrote", path, os.path.getsize(path), "bytes")
 
 
+def _import_reference(ref_root: str) -> None:
+    if ref_root not in sys.path:
+        sys.path.insert(0, ref_root)
+    from comfy.cli_args import args
+    args.cpu = True
+    import comfy.model_management  # noqa: F401
+
+
 if __name__ == "__main__":
+    # python tests/golden/make_golden.py ROOT [part ...]    parts: moe rounding hunyuan3d attention blocks model
     root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("COMFYUI_ROOT", "ComfyUI")
-    main(root)
-    weight_rounding(root)
-    hunyuan3d(root)
-    attention(root)
-    blocks(root)
+    parts = sys.argv[2:] or ["moe", "rounding", "hunyuan3d", "attention", "blocks", "model"]
+    _import_reference(root)
+    table = {"moe": main, "rounding": weight_rounding, "hunyuan3d": hunyuan3d, "attention": attention,
+             "blocks": blocks, "model": model}
+    for part in parts:
+        table[part](root)
