@@ -15,93 +15,65 @@ constexpr int kMaxRowThreads = 512;    // dim / 8 threads per block: dim <= 4096
 __host__ __device__ constexpr int round_up32(int v) { return (v + 31) & ~31; }
 
 // ------------------------------------------------------------------------------------------------
-// Gate.  The gate weight sits in shared memory (as stored: bf16 or fp32); a warp
-// handles two tokens at a time, lane l owning chunks l, l + 32, ... of both rows (up to 20 sixteen-byte
-// loads in flight per lane), so no block barrier separates the rows; the 2 x E dot products are reduced
-// with shuffles and every lane finishes softmax / top-2 redundantly.
+// Gate.  One warp per token: lane l owns the 16-byte chunks l, l + 32, ... of the row and has all of them in flight
+// at once (ten loads per lane at dim 2560); the gate weight (20 KB at dim 2560, bf16) is read through L1, which it
+// never leaves, instead of being staged per block; the E dot products are reduced with shuffles in a fixed order
+// (reproducible) and every lane finishes softmax / top-2 redundantly.  Eight tokens per block, so 8192 tokens are 1024
+// short blocks (several resident per SM) rather than one partly filled wave of 256; the per-32-token expert counts
+// the routing plan needs are accumulated with integer atomics in block_counts, which the launcher zeroes.
 // ------------------------------------------------------------------------------------------------
-constexpr int kGateWarpThreads = 256;
-constexpr int kGateWarpBatch = 10;
+constexpr int kGateWarps = 8;
 
-template <int E, bool kW32>
-__global__ void __launch_bounds__(kGateWarpThreads)
+template <int E, bool kW32, int kChunksPerLane>
+__global__ void __launch_bounds__(kGateWarps * 32)
 gate_topk_kernel(const __nv_bfloat16* __restrict__ x, const void* __restrict__ w_gate, int n_tokens, int dim,
-                      int32_t* __restrict__ topk_idx, float* __restrict__ topk_weight,
-                      int32_t* __restrict__ block_counts, int32_t* __restrict__ neartie_count,
-                      uint8_t* __restrict__ neartie_flags, float neartie_eps) {
-  extern __shared__ uint4 w_s[];                       // E rows of dim elements, 16-byte vectors
-  __shared__ int hist[E];
-  constexpr int kTokPerWarp = kTokensPerBlock / (kGateWarpThreads / 32);   // 4
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+                 int32_t* __restrict__ topk_idx, float* __restrict__ topk_weight, int32_t* __restrict__ block_counts,
+                 int32_t* __restrict__ neartie_count, uint8_t* __restrict__ neartie_flags, float neartie_eps) {
+  const int lane = threadIdx.x & 31;
   const int chunks = dim >> 3;
   const int row_vecs = kW32 ? chunks * 2 : chunks;     // 16-byte vectors per weight row
-  {
-    const uint4* src = static_cast<const uint4*>(w_gate);
-    for (int i = tid; i < E * row_vecs; i += kGateWarpThreads) w_s[i] = src[i];
-  }
-  if (tid < E) hist[tid] = 0;
-  __syncthreads();
-
-  const int block_tok0 = blockIdx.x * kTokensPerBlock;
-#pragma unroll 1
-  for (int pair = 0; pair < kTokPerWarp / 2; ++pair) {
-    const int t0 = block_tok0 + warp * kTokPerWarp + pair * 2;
-    if (t0 >= n_tokens) break;
-    const bool has1 = t0 + 1 < n_tokens;
-    const uint4* r0 = reinterpret_cast<const uint4*>(x + static_cast<size_t>(t0) * dim);
-    const uint4* r1 = reinterpret_cast<const uint4*>(x + static_cast<size_t>(has1 ? t0 + 1 : t0) * dim);
-    float acc0[E], acc1[E];
+  const uint4* w_rows = static_cast<const uint4*>(w_gate);
+  for (int t = blockIdx.x * kGateWarps + (threadIdx.x >> 5); t < n_tokens; t += gridDim.x * kGateWarps) {
+    const uint4* row = reinterpret_cast<const uint4*>(x + static_cast<size_t>(t) * dim);
+    uint4 v[kChunksPerLane];
 #pragma unroll
-    for (int e = 0; e < E; ++e) { acc0[e] = 0.f; acc1[e] = 0.f; }
-    for (int c0 = lane; c0 < chunks; c0 += 32 * kGateWarpBatch) {
-      uint4 v0[kGateWarpBatch], v1[kGateWarpBatch];
+    for (int j = 0; j < kChunksPerLane; ++j) {
+      const int c = lane + 32 * j;
+      if (c < chunks) v[j] = ld_nc_u4(row + c);
+    }
+    float acc[E];
 #pragma unroll
-      for (int j = 0; j < kGateWarpBatch; ++j) {
-        const int c = c0 + 32 * j;
-        if (c < chunks) { v0[j] = ld_nc_u4(r0 + c); v1[j] = ld_nc_u4(r1 + c); }
-      }
+    for (int e = 0; e < E; ++e) acc[e] = 0.f;
 #pragma unroll
-      for (int j = 0; j < kGateWarpBatch; ++j) {
-        const int c = c0 + 32 * j;
-        if (c < chunks) {
-          float f0[8], f1[8];
-          unpack_bf16x8(v0[j], f0);
-          unpack_bf16x8(v1[j], f1);
-          gate_accumulate<E, kW32>(w_s, row_vecs, c, f0, acc0);
-          gate_accumulate<E, kW32>(w_s, row_vecs, c, f1, acc1);
-        }
+    for (int j = 0; j < kChunksPerLane; ++j) {
+      const int c = lane + 32 * j;
+      if (c < chunks) {
+        float f[8];
+        unpack_bf16x8(v[j], f);
+        gate_accumulate<E, kW32>(w_rows, row_vecs, c, f, acc);
       }
     }
 #pragma unroll
     for (int e = 0; e < E; ++e) {
 #pragma unroll
-      for (int off = 16; off > 0; off >>= 1) {
-        acc0[e] += __shfl_xor_sync(0xffffffffu, acc0[e], off);
-        acc1[e] += __shfl_xor_sync(0xffffffffu, acc1[e], off);
-      }
+      for (int off = 16; off > 0; off >>= 1) acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], off);
     }
-#pragma unroll
-    for (int which = 0; which < 2; ++which) {
-      if (which == 1 && !has1) break;
-      const int t = t0 + which;
-      int i0, i1;
-      float w0, w1;
-      bool tie;
-      gate_select<E>(which == 0 ? acc0 : acc1, neartie_eps, i0, i1, w0, w1, tie);
-      if (lane == 0) {
-        topk_idx[2 * t] = i0;
-        topk_idx[2 * t + 1] = i1;
-        topk_weight[2 * t] = w0;
-        topk_weight[2 * t + 1] = w1;
-        atomicAdd(&hist[i0], 1);
-        atomicAdd(&hist[i1], 1);
-        if (neartie_flags) neartie_flags[t] = tie ? 1 : 0;
-        if (tie && neartie_count) atomicAdd(neartie_count, 1);
-      }
+    int i0, i1;
+    float w0, w1;
+    bool tie;
+    gate_select<E>(acc, neartie_eps, i0, i1, w0, w1, tie);
+    if (lane == 0) {
+      topk_idx[2 * t] = i0;
+      topk_idx[2 * t + 1] = i1;
+      topk_weight[2 * t] = w0;
+      topk_weight[2 * t + 1] = w1;
+      int32_t* counts = block_counts + (t / kTokensPerBlock) * E;
+      atomicAdd(counts + i0, 1);                           // integer atomics: the sums do not depend on the order
+      atomicAdd(counts + i1, 1);
+      if (neartie_flags) neartie_flags[t] = tie ? 1 : 0;
+      if (tie && neartie_count) atomicAdd(neartie_count, 1);
     }
   }
-  __syncthreads();
-  if (tid < E) block_counts[blockIdx.x * E + tid] = hist[tid];
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -389,16 +361,27 @@ static int launch_gate(const void* x, const void* w_gate, int w_dtype, int n_tok
                        float* topk_weight, int32_t* block_counts, int32_t* neartie_count, uint8_t* neartie_flags,
                        float neartie_eps, cudaStream_t stream) {
   const int n_blocks = (n_tokens + kTokensPerBlock - 1) / kTokensPerBlock;
-  const bool w32 = w_dtype == COMFY_MOE_FP32;
-  const size_t smem = static_cast<size_t>(E) * dim * (w32 ? 4 : 2);
-  if (smem > 200 * 1024) return COMFY_MOE_EUNSUPPORTED;
-  auto kern = w32 ? gate_topk_kernel<E, true> : gate_topk_kernel<E, false>;
-  if (smem > 48 * 1024 &&
-      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
-    return COMFY_MOE_ECUDA;
-  kern<<<n_blocks, kGateWarpThreads, smem, stream>>>(static_cast<const __nv_bfloat16*>(x), w_gate, n_tokens, dim,
-                                                      topk_idx, topk_weight, block_counts, neartie_count, neartie_flags,
-                                                      neartie_eps);
+  if (cudaMemsetAsync(block_counts, 0, sizeof(int32_t) * n_blocks * E, stream) != cudaSuccess) return COMFY_MOE_ECUDA;
+  int grid = (n_tokens + kGateWarps - 1) / kGateWarps;
+  if (grid > 148 * 16) grid = 148 * 16;
+  const int per_lane = ((dim >> 3) + 31) / 32;     // registers hold the row: the smallest instantiation that fits
+  const __nv_bfloat16* xp = static_cast<const __nv_bfloat16*>(x);
+#define COMFY_GATE_LAUNCH(W32, K) \
+  gate_topk_kernel<E, W32, K><<<grid, kGateWarps * 32, 0, stream>>>(xp, w_gate, n_tokens, dim, topk_idx, topk_weight, \
+                                                                   block_counts, neartie_count, neartie_flags, \
+                                                                   neartie_eps)
+#define COMFY_GATE_PICK(W32) \
+  do { \
+    if (per_lane <= 2) COMFY_GATE_LAUNCH(W32, 2); \
+    else if (per_lane <= 4) COMFY_GATE_LAUNCH(W32, 4); \
+    else if (per_lane <= 8) COMFY_GATE_LAUNCH(W32, 8); \
+    else if (per_lane <= 10) COMFY_GATE_LAUNCH(W32, 10); \
+    else COMFY_GATE_LAUNCH(W32, 16); \
+  } while (0)
+  if (w_dtype == COMFY_MOE_FP32) COMFY_GATE_PICK(true);
+  else COMFY_GATE_PICK(false);
+#undef COMFY_GATE_PICK
+#undef COMFY_GATE_LAUNCH
   return check_launch();
 }
 
