@@ -33,6 +33,7 @@ EXPORTS = (
     "comfy_moe_permute",
     "comfy_moe_plan_permute",
     "comfy_moe_route_static",
+    "comfy_moe_validate_routing",
     "comfy_moe_grouped_swiglu",
     "comfy_moe_grouped_gelu_mlp",
     "comfy_moe_grouped_swiglu_scatter",
@@ -232,6 +233,8 @@ def load(build_if_missing: bool = False) -> ctypes.CDLL:
         c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
         c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
     ]
+    lib.comfy_moe_validate_routing.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int64, c_void_p,
+                                               c_void_p]
     lib.comfy_moe_grouped_swiglu.argtypes = [
         c_int, c_int, POINTER(FfnWeights), POINTER(FfnWeights), c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p,
         c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,

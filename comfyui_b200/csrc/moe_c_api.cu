@@ -28,7 +28,9 @@ extern "C" int comfy_moe_read_status(int32_t* status, void* stream, int32_t* h_s
   if (cudaStreamSynchronize(s) != cudaSuccess) return COMFY_MOE_ECUDA;
   if (*h_status == 0) return COMFY_MOE_OK;
   if (cudaMemsetAsync(status, 0, sizeof(int32_t), s) != cudaSuccess) return COMFY_MOE_ECUDA;
-  return *h_status == 8 ? COMFY_MOE_ETOOLARGE : COMFY_MOE_ETIMEOUT;   // 8: routed rows exceed a peer receive buffer
+  if (*h_status == 8) return COMFY_MOE_ETOOLARGE;    // routed rows exceed a peer receive buffer
+  if (*h_status == 9) return COMFY_MOE_EINVAL;       // the routing check found an inconsistency
+  return COMFY_MOE_ETIMEOUT;
 }
 
 // Block epilogue requested by comfy_moe_ffn_block: gate * (.) + residual folded into the combine.

@@ -496,6 +496,69 @@ extern "C" int comfy_moe_plan_permute(const void* x, const int32_t* topk_idx, co
 }
 
 // ------------------------------------------------------------------------------------------------
+// Debug aid: checks the routing data structures a layer call left behind and reports the first violation
+// through the status word (code 9), instead of letting a bad index become a stray memory access further down.
+// Checked: every expert id is inside the layer or the slot is unmapped (-1); every mapped row lies inside its
+// expert's block [offset[e], offset[e] + count[e]) and below rows_cap; offsets start at 0, are multiples of the row
+// alignment and leave room for each expert's rows; the counts add up to the number of mapped slots.
+// ------------------------------------------------------------------------------------------------
+namespace comfy_b200 {
+constexpr int kStatusRoutingInvalid = 9;
+
+__global__ void __launch_bounds__(256)
+validate_routing_kernel(const int32_t* __restrict__ topk_idx, const int32_t* __restrict__ row_map,
+                        const int32_t* __restrict__ expert_counts, const int32_t* __restrict__ expert_offsets,
+                        int n_tokens, int n_experts, long long rows_cap, int32_t* __restrict__ mapped_slots,
+                        int32_t* __restrict__ status) {
+  bool bad = false;
+  int mapped = 0;
+  const long long slots = 2LL * n_tokens;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < slots;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int e = topk_idx[i], r = row_map[i];
+    if (e < 0 || e >= n_experts) { bad |= (r != -1); continue; }
+    ++mapped;
+    const int lo = expert_offsets[e], cnt = expert_counts[e];
+    bad |= (r < lo) || (r >= lo + cnt) || (r >= rows_cap);
+  }
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    long long row = 0;
+    for (int e = 0; e < n_experts; ++e) {
+      bad |= (expert_offsets[e] != row) || (expert_offsets[e] % kRowAlign != 0) || (expert_counts[e] < 0);
+      row += (static_cast<long long>(expert_counts[e]) + kRowAlign - 1) / kRowAlign * kRowAlign;
+    }
+    bad |= (expert_offsets[n_experts] != row) || (row > rows_cap);
+  }
+  if (mapped) atomicAdd(mapped_slots, mapped);
+  if (bad) atomicCAS(status, 0, kStatusRoutingInvalid);
+}
+
+__global__ void validate_total_kernel(const int32_t* __restrict__ expert_counts, int n_experts,
+                                      const int32_t* __restrict__ mapped_slots, int32_t* __restrict__ status) {
+  long long total = 0;
+  for (int e = 0; e < n_experts; ++e) total += expert_counts[e];
+  if (total != *mapped_slots) atomicCAS(status, 0, kStatusRoutingInvalid);
+}
+}  // namespace comfy_b200
+
+extern "C" int comfy_moe_validate_routing(const int32_t* topk_idx, const int32_t* row_map, const int32_t* expert_counts,
+                                          const int32_t* expert_offsets, int n_tokens, int n_experts, int64_t rows_cap,
+                                          int32_t* status, void* stream) {
+  if (n_tokens < 0 || n_experts < 1 || n_experts > kMaxExperts || rows_cap < 0 || !status) return COMFY_MOE_EINVAL;
+  if (!expert_counts || !expert_offsets || (n_tokens > 0 && (!topk_idx || !row_map))) return COMFY_MOE_EINVAL;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int32_t* mapped = status + 3;                      // the reserved word of the status block serves as the counter
+  if (cudaMemsetAsync(mapped, 0, sizeof(int32_t), s) != cudaSuccess) return COMFY_MOE_ECUDA;
+  long long blocks = (2LL * n_tokens + 255) / 256;
+  if (blocks < 1) blocks = 1;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  validate_routing_kernel<<<static_cast<int>(blocks), 256, 0, s>>>(topk_idx, row_map, expert_counts, expert_offsets,
+                                                                   n_tokens, n_experts, rows_cap, mapped, status);
+  validate_total_kernel<<<1, 1, 0, s>>>(expert_counts, n_experts, mapped, status);
+  return check_launch();
+}
+
+// ------------------------------------------------------------------------------------------------
 // Routing without caller-provided scratch.  The per-block counts and offsets that link the gate, the
 // plan and the permutation live in a fixed device array that is part of the library image, so a
 // caller that cannot allocate device memory passes only inputs and outputs.

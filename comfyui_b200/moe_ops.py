@@ -432,6 +432,16 @@ def read_status(status: torch.Tensor) -> None:
         raise N.MoeError("comfy_moe_read_status", rc, f"device status word = {h.value}")
 
 
+def validate_routing(ws: "Workspace") -> None:
+    """Debug aid: checks the routing the last layer call left in ``ws`` on the device (ids, rows, offsets, counts) and
+    raises if it is inconsistent.  One stream synchronisation."""
+    rc = N.load().comfy_moe_validate_routing(_ptr(ws.topk_idx), _ptr(ws.row_map), _ptr(ws.expert_counts),
+                                             _ptr(ws.expert_offsets), ws.n_tokens, ws.n_experts, ws.rows_cap,
+                                             _ptr(ws.status), _stream())
+    N.check("comfy_moe_validate_routing", rc)
+    read_status(ws.status)
+
+
 def moe_forward(layer: LayerPack, x: torch.Tensor, ws: Optional[Workspace] = None,
                 out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """The whole layer through comfy_moe_forward.  x: bf16 [N, D] contiguous on the device."""

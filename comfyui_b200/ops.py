@@ -18,6 +18,7 @@ from __future__ import annotations
 
 import contextlib
 import logging
+import os
 from typing import Optional
 
 import torch
@@ -343,6 +344,36 @@ def pick_operations(weight_dtype, compute_dtype, load_device=None, disable_fast_
 ENABLE_SM100_KERNELS = True
 # Read the device status word (one stream synchronisation) after every fused call; for debugging.
 CHECK_STATUS_EVERY_CALL = False
+# Debug runs (COMFY_B200_DEBUG=1): after every fused layer call, check the routing it produced on the device (expert
+# ids, rows, offsets, counts) and read the status word.  Stands in for a memory checker at the level of the data
+# structures the kernels index with.
+DEBUG_VALIDATE = os.environ.get("COMFY_B200_DEBUG", "0") not in ("", "0")
+# NVTX ranges around the fused calls (COMFY_B200_NVTX=1), so that a timeline shows the layer as one named span.
+NVTX_RANGES = os.environ.get("COMFY_B200_NVTX", "0") not in ("", "0")
+
+
+class _Range:
+    """``with _Range("name"):`` pushes an NVTX range when NVTX_RANGES is set, and does nothing otherwise."""
+
+    def __init__(self, name: str):
+        self.name = name
+
+    def __enter__(self):
+        if NVTX_RANGES:
+            torch.cuda.nvtx.range_push(self.name)
+
+    def __exit__(self, *exc):
+        if NVTX_RANGES:
+            torch.cuda.nvtx.range_pop()
+
+
+def _after_layer_call(layer, n_tokens: int) -> None:
+    from . import moe_ops
+
+    if DEBUG_VALIDATE:
+        moe_ops.validate_routing(_workspace(layer, n_tokens))
+    elif CHECK_STATUS_EVERY_CALL:
+        moe_ops.read_status(_workspace(layer, n_tokens).status)
 
 
 
@@ -488,9 +519,9 @@ def hidream_moe_forward(moe, x: torch.Tensor) -> Optional[torch.Tensor]:
     from . import moe_ops, torch_ops  # noqa: F401  (importing torch_ops registers the operators)
 
     x2 = x.view(-1, x.shape[-1])
-    out = torch.ops.comfyui_b200.hidream_moe(x2, layer.gate, *_op_args(layer))
-    if CHECK_STATUS_EVERY_CALL:
-        moe_ops.read_status(_workspace(layer, x2.shape[0]).status)
+    with _Range("comfyui_b200::hidream_moe"):
+        out = torch.ops.comfyui_b200.hidream_moe(x2, layer.gate, *_op_args(layer))
+    _after_layer_call(layer, x2.shape[0])
     return out.view(x.shape)
 
 
@@ -734,9 +765,9 @@ def hunyuan3d_moe_forward(moe, x: torch.Tensor) -> Optional[torch.Tensor]:
         args = torch_ops.register(layer)
         layer._op_args = args
     x2 = x.view(-1, x.shape[-1])
-    out = torch.ops.comfyui_b200.hunyuan3d_moe(x2, layer.gate, *args)
-    if CHECK_STATUS_EVERY_CALL:
-        moe_ops.read_status(_workspace(layer, x2.shape[0]).status)
+    with _Range("comfyui_b200::hunyuan3d_moe"):
+        out = torch.ops.comfyui_b200.hunyuan3d_moe(x2, layer.gate, *args)
+    _after_layer_call(layer, x2.shape[0])
     return out.view(x.shape)
 
 
@@ -808,10 +839,10 @@ def hidream_block_ffn(norm, ff, x: torch.Tensor, shift: torch.Tensor, scale: tor
             return None
         from . import torch_ops  # noqa: F401  (registers the operators)
 
-        out = torch.ops.comfyui_b200.hidream_moe_block(x2, shift, scale, gate, s, float(norm.eps), layer.gate,
-                                                       *_op_args(layer))
-        if CHECK_STATUS_EVERY_CALL:
-            moe_ops.read_status(_workspace(layer, x2.shape[0]).status)
+        with _Range("comfyui_b200::hidream_moe_block"):
+            out = torch.ops.comfyui_b200.hidream_moe_block(x2, shift, scale, gate, s, float(norm.eps), layer.gate,
+                                                           *_op_args(layer))
+        _after_layer_call(layer, x2.shape[0])
         return out.view(x.shape)
     if not _input_ok(x, ff.w1.weight.shape[1]):
         return None

@@ -125,6 +125,16 @@ int comfy_moe_plan_permute(const void* x, const int32_t* topk_idx, const int32_t
                            int32_t* expert_counts, int32_t* expert_offsets, void* x_perm, void* x_q,
                            const float* x_q_scale, int32_t* row_map, int32_t* overflow_count, void* stream);
 
+/* ---- debug aid: consistency check of the routing a layer call produced ------------------------------------------
+ * (No counterpart in the reference.)  Verifies on the device that every expert id lies inside the layer or its slot is
+ * unmapped (row -1), every mapped row lies inside its expert's block and below rows_cap, the offsets are aligned,
+ * monotone and leave room for every expert's rows, and the counts add up to the number of mapped slots.  A violation
+ * sets the sticky status word to 9 (comfy_moe_read_status then returns COMFY_MOE_ETIMEOUT's sibling COMFY_MOE_EINVAL).
+ * status: a status block (word 3 is used as scratch).  Two small kernels and a memset node; meant for debug runs. */
+int comfy_moe_validate_routing(const int32_t* topk_idx, const int32_t* row_map, const int32_t* expert_counts,
+                               const int32_t* expert_offsets, int n_tokens, int n_experts, int64_t rows_cap,
+                               int32_t* status, void* stream);
+
 /* ---- gate + routing plan + permutation for callers that cannot allocate device memory -----------------
  * (No counterpart in the reference: it has no allocation-free mode.)
  * Some hosts of this library may not call cudaMalloc or any allocator between set-up and tear-down: real-time
@@ -456,11 +466,12 @@ int comfy_moe_ffn_block(const ComfyMoeLayer* h_layer, const ComfyMoeWorkspace* h
 
 /* The device status word.  Kernels move it from 0 to a code when something went wrong on the device (1-3: a bounded
  * wait of the grouped GEMM's producer / MMA / epilogue role ran out; 7: a peer's flag did not arrive in time; 8: routed
- * rows did not fit a peer receive buffer and were dropped) and never overwrite a code that is already there; no entry
+ * rows did not fit a peer receive buffer and were dropped; 9: the routing check found an inconsistency) and never overwrite a code that is already there; no entry
  * point clears it on the way in.  A caller may therefore share one word among all layers of a model and look at it at
  * a natural synchronisation point (end of a model forward).
  * comfy_moe_read_status synchronises `stream`, copies status[0] to *h_status and returns COMFY_MOE_OK for 0,
- * COMFY_MOE_ETOOLARGE for code 8 and COMFY_MOE_ETIMEOUT for any other code; a non-zero word is cleared once it has
+ * COMFY_MOE_ETOOLARGE for code 8, COMFY_MOE_EINVAL for code 9 (comfy_moe_validate_routing found an inconsistency) and
+ * COMFY_MOE_ETIMEOUT for any other code; a non-zero word is cleared once it has
  * been reported. */
 int comfy_moe_read_status(int32_t* status, void* stream, int32_t* h_status);
 

@@ -499,3 +499,46 @@ def test_config5_skewed_full_size(M, cuda_device):
     w = ws.topk_weight.cpu()[sample].bfloat16()
     ref, _, _ = O.moe_layer(xs, layer, routing=(idx[sample], w))
     torch.testing.assert_close(out[sample].float(), ref.float(), rtol=BF16_RTOL, atol=BF16_ATOL)
+
+
+def test_routing_validation_debug_aid(M, cuda_device):
+    """comfy_moe_validate_routing accepts what a layer call produced and flags a corrupted row map, expert id or count
+    through the status word (the GPU-side stand-in for a memory checker at the level of the routing structures)."""
+    from comfyui_b200 import _native as N
+
+    layer, x, out, ws = _full_layer_case(M, cuda_device, 777, 256, 1024, 4, O.PLAIN)
+    M.validate_routing(ws)                                           # a clean call passes
+    saved = ws.row_map.clone()
+    ws.row_map[5, 1] = ws.rows_cap + 3                               # a row beyond the permuted buffer
+    with pytest.raises(N.MoeError) as err:
+        M.validate_routing(ws)
+    assert err.value.code == N.EINVAL and "status word = 9" in str(err.value)
+    ws.row_map.copy_(saved)
+    M.validate_routing(ws)
+    ws.expert_counts[2] += 1                                         # counts no longer add up to the mapped slots
+    with pytest.raises(N.MoeError):
+        M.validate_routing(ws)
+    ws.expert_counts[2] -= 1
+    ws.topk_idx[9, 0] = 11                                           # an id outside the layer whose slot is still mapped
+    with pytest.raises(N.MoeError):
+        M.validate_routing(ws)
+
+
+def test_debug_mode_validates_every_layer_call(cuda_device, monkeypatch):
+    from comfyui_b200 import ops
+    from comfyui_b200.ldm.hidream.model import MOEFeedForwardSwiGLU
+
+    dev = cuda_device
+    layer = {k: v.bfloat16() for k, v in O.make_layer(256, 1024, 4, seed=0).items()}
+    mod = MOEFeedForwardSwiGLU(256, 1024, 4, 2, dtype=torch.bfloat16, device=dev, operations=ops.disable_weight_init).eval()
+    mod.load_state_dict({k: v.to(dev) for k, v in layer.items()}, strict=True)
+    x = O.make_input(300, 256, seed=2).bfloat16().to(dev).view(1, 300, 256)
+    calls = []
+    from comfyui_b200 import moe_ops
+    stock = moe_ops.validate_routing
+    monkeypatch.setattr(moe_ops, "validate_routing", lambda ws: calls.append(ws.n_tokens) or stock(ws))
+    monkeypatch.setattr(ops, "DEBUG_VALIDATE", True)
+    monkeypatch.setattr(ops, "NVTX_RANGES", True)
+    with torch.inference_mode():
+        out = mod(x)
+    assert calls == [300] and out.shape == x.shape
