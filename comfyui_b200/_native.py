@@ -37,6 +37,7 @@ EXPORTS = (
     "comfy_moe_grouped_swiglu",
     "comfy_moe_grouped_gelu_mlp",
     "comfy_moe_grouped_swiglu_scatter",
+    "comfy_moe_grouped_swiglu_ex",
     "comfy_moe_combine",
     "comfy_moe_combine_partials",
     "comfy_moe_forward",
@@ -139,6 +140,23 @@ class LinearGroup(Structure):
         ("in_features", c_int32),
         ("out_features", c_int32),
         ("reserved", c_int32),
+    ]
+
+
+class GroupedOptions(Structure):
+    """struct ComfyMoeGroupedOptions"""
+
+    _fields_ = [
+        ("passes", c_int32),
+        ("reserved", c_int32),
+        ("y_out", POINTER(c_void_p)),
+        ("y_row_shift", c_void_p),
+        ("y_rows_cap", c_int64),
+        ("arrive_flags", c_void_p),
+        ("group_source", POINTER(c_int32)),
+        ("arrive_epoch", c_uint32),
+        ("reserved2", c_uint32),
+        ("arrive_budget_cycles", c_int64),
     ]
 
 
@@ -268,6 +286,10 @@ def load(build_if_missing: bool = False) -> ctypes.CDLL:
     lib.comfy_moe_grouped_swiglu_scatter.argtypes = [
         c_int, c_int, POINTER(FfnWeights), c_void_p, c_void_p, c_int64, c_int, c_void_p, c_void_p, POINTER(c_void_p),
         c_void_p, c_int64, c_void_p, c_void_p,
+    ]
+    lib.comfy_moe_grouped_swiglu_ex.argtypes = [
+        c_int, c_int, POINTER(FfnWeights), POINTER(FfnWeights), c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p,
+        c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, POINTER(GroupedOptions), c_void_p, c_void_p,
     ]
     lib.comfy_moe_quantize_e4m3.argtypes = [c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p]
     lib.comfy_attn_rmsnorm_rope.argtypes = [c_void_p, c_int64, c_void_p, c_float, c_void_p, c_int64, c_int, c_int, c_int,

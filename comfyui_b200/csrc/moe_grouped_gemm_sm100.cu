@@ -63,6 +63,7 @@ template <int kCtas> struct GemmShape {
 constexpr int kStatusProducerTimeout = 1;
 constexpr int kStatusMmaTimeout = 2;
 constexpr int kStatusEpilogueTimeout = 3;
+constexpr int kStatusArrivalTimeout = 7;          // a source rank's "rows arrived" flag did not come in time
 
 struct GemmGroup {
   int a_map;          // index of the A tensor map
@@ -83,7 +84,7 @@ struct GemmGroup {
   const float* out_scale;      // fp8 pass 1: scale_input of w2 (h is multiplied by bf16(1/s) before the cast)
   const __nv_bfloat16* bias;   // kBiasAct instantiations: bias over the output columns (NULL = none)
   int gelu;                    // kBiasAct instantiations: 1 = exact (erf) GELU on the bf16-rounded sum
-  int reserved2;
+  int wait_source;             // >= 0: the group's rows come from this rank; its "arrived" flag gates the first load
 };
 
 struct alignas(64) GemmParams {
@@ -96,6 +97,14 @@ struct alignas(64) GemmParams {
   int m_fastest;      // plain passes: 1 = row tiles fastest (short K, wide N), 0 = column tiles fastest
   const int32_t* out_shift;   // optional, device, per routed group: output row = input row + out_shift[i] (results that
                               // are written straight into another buffer's layout, e.g. a peer's return buffer)
+  // optional (expert parallelism): arrive_flags[r] reaches arrive_epoch once rank r's rows are in the A operand; a
+  // group with wait_source = r is not loaded before that.  Replaces a wait for ALL ranks in front of the launch: the
+  // rows this GPU routed to itself are there already, and the tiles over them keep the tensor pipe busy while the
+  // other ranks' rows land.
+  const uint32_t* arrive_flags;
+  uint32_t arrive_epoch;
+  int reserved3;
+  long long arrive_budget;    // clock budget of one such wait
 };
 
 // The SwiGLU epilogue works on pairs of neighbouring columns held as bf16x2, so that every rounding the reference
@@ -244,10 +253,20 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
     // ------------------------------------------------------------------ TMA producer (both CTAs of a pair)
     uint32_t it = 0;
     bool ok = true;
+    uint32_t arrived = 0;           // sources whose flag this warp has already seen at the current epoch
     for (int i = 0, t; (t = tile_at(i)) >= 0 && ok; ++i) {
       int g, m_tile, n_tile;
       decode(t, g, m_tile, n_tile);
       const GemmGroup& grp = p.groups[g];
+      if (p.arrive_flags != nullptr && grp.wait_source >= 0 && !((arrived >> grp.wait_source) & 1u)) {
+        ok = flag_wait_warp(p.arrive_flags + grp.wait_source, p.arrive_epoch, p.arrive_budget, abort_ptr);
+        if (!ok) {
+          if (lane == 0) { atomicCAS(p.status, 0, kStatusArrivalTimeout); abort_flag = 1; }
+          break;
+        }
+        arrived |= 1u << grp.wait_source;
+        fence_proxy_async_all();    // the rows were written with ordinary stores; the loads below are tensor-map loads
+      }
       const CUtensorMap* map_a = &p.maps[grp.a_map];
       const int a_row = s_row_base[g] + m_tile * kTileM + static_cast<int>(cta_rank) * kBlockM;
       const int b_row = n_tile * (kSwiglu ? 128 : kBlockN);
@@ -709,8 +728,13 @@ static int grouped_swiglu_impl(int w_dtype, int n_experts, const ComfyMoeFfnWeig
                                const ComfyMoeFfnWeights* h_shared, const int32_t* row_start,
                                const int32_t* row_count, int64_t rows_cap, int n_tokens, int dim, const void* x_perm,
                                void* h_perm, void* y_perm, const void* x_shared, void* h_shared_ws, void* y_shared,
-                               int32_t* status, void* stream, void* const* y_out, const int32_t* y_row_shift,
-                               int64_t y_rows_cap) {
+                               int32_t* status, void* stream, const ComfyMoeGroupedOptions* opt) {
+  void* const* y_out = opt ? opt->y_out : nullptr;
+  const int32_t* y_row_shift = opt ? opt->y_row_shift : nullptr;
+  const int64_t y_rows_cap = opt ? opt->y_rows_cap : 0;
+  const int passes = (opt && opt->passes) ? opt->passes : 3;
+  if (passes < 1 || passes > 3) return COMFY_MOE_EINVAL;
+  if (opt && opt->arrive_flags && !opt->group_source) return COMFY_MOE_EINVAL;
   if (n_experts < 0 || n_experts > kMaxExperts || dim <= 0 || n_tokens < 0 || rows_cap < 0) return COMFY_MOE_EINVAL;
   if (y_out && (!y_row_shift || y_rows_cap <= 0)) return COMFY_MOE_EINVAL;
   if (y_out && !y_perm) y_perm = y_out[0];     // only its non-nullness is checked below
@@ -773,6 +797,12 @@ static int grouped_swiglu_impl(int w_dtype, int n_experts, const ComfyMoeFfnWeig
       g1.k_blocks = dim / k_elems; g1.n_tiles = w.hidden / 128; g1.routed_index = e; g1.static_rows = 0;
       g1.out = h_perm; g1.ld_out = w.hidden; g1.out_map = o1;
       g1.scale_a = w.scale_in13; g1.scale_b0 = w.scale_w1; g1.scale_b1 = w.scale_w3; g1.out_scale = w.scale_in2;
+      g1.wait_source = -1;
+      if (opt && opt->arrive_flags) {
+        const int src = opt->group_source[e];
+        if (src >= 32) return COMFY_MOE_EINVAL;
+        g1.wait_source = src;
+      }
       GemmGroup& g2 = p2.groups[g];
       g2.a_map = a2; g2.b0_map = n_maps2; g2.b1_map = n_maps2; g2.b1_row_off = 128; g2.out_map = o2;
       g2.k_blocks = w.hidden / k_elems; g2.n_tiles = dim / kBlockN; g2.routed_index = e; g2.static_rows = 0;
@@ -807,6 +837,7 @@ static int grouped_swiglu_impl(int w_dtype, int n_experts, const ComfyMoeFfnWeig
     g1.k_blocks = dim / k_elems; g1.n_tiles = w.hidden / 128; g1.routed_index = -1; g1.static_rows = n_tokens;
     g1.out = h_shared_ws; g1.ld_out = w.hidden; g1.out_map = n_maps1 + 3;
     g1.scale_a = w.scale_in13; g1.scale_b0 = w.scale_w1; g1.scale_b1 = w.scale_w3; g1.out_scale = w.scale_in2;
+    g1.wait_source = -1;
     GemmGroup& g2 = p2.groups[g];
     g2.a_map = n_maps2; g2.b0_map = n_maps2 + 1; g2.b1_map = n_maps2 + 1; g2.b1_row_off = 128;
     g2.k_blocks = w.hidden / k_elems; g2.n_tiles = dim / kBlockN; g2.routed_index = -1; g2.static_rows = n_tokens;
@@ -821,14 +852,23 @@ static int grouped_swiglu_impl(int w_dtype, int n_experts, const ComfyMoeFfnWeig
     ++g;
   }
   p1.num_groups = p2.num_groups = g;
+  if (opt && opt->arrive_flags) {
+    p1.arrive_flags = opt->arrive_flags;
+    p1.arrive_epoch = opt->arrive_epoch;
+    p1.arrive_budget = opt->arrive_budget_cycles > 0 ? opt->arrive_budget_cycles : COMFY_MOE_EP_WAIT_CYCLES;
+  }
 
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (fp8) {
-    if ((rc = launch_gemm<true, true>(p1, tiles1[0], tiles1[1], sms, s)) != COMFY_MOE_OK) return rc;
-    return launch_gemm<true, false>(p2, tiles2[0], tiles2[1], sms, s);
+  if (passes & 1) {
+    rc = fp8 ? launch_gemm<true, true>(p1, tiles1[0], tiles1[1], sms, s)
+             : launch_gemm<false, true>(p1, tiles1[0], tiles1[1], sms, s);
+    if (rc != COMFY_MOE_OK) return rc;
   }
-  if ((rc = launch_gemm<false, true>(p1, tiles1[0], tiles1[1], sms, s)) != COMFY_MOE_OK) return rc;
-  return launch_gemm<false, false>(p2, tiles2[0], tiles2[1], sms, s);
+  if (passes & 2) {
+    rc = fp8 ? launch_gemm<true, false>(p2, tiles2[0], tiles2[1], sms, s)
+             : launch_gemm<false, false>(p2, tiles2[0], tiles2[1], sms, s);
+  }
+  return rc;
 }
 
 extern "C" int comfy_moe_grouped_swiglu(int w_dtype, int n_experts, const ComfyMoeFfnWeights* h_experts,
@@ -837,7 +877,17 @@ extern "C" int comfy_moe_grouped_swiglu(int w_dtype, int n_experts, const ComfyM
                                         const void* x_perm, void* h_perm, void* y_perm, const void* x_shared,
                                         void* h_shared_ws, void* y_shared, int32_t* status, void* stream) {
   return grouped_swiglu_impl(w_dtype, n_experts, h_experts, h_shared, row_start, row_count, rows_cap, n_tokens, dim,
-                             x_perm, h_perm, y_perm, x_shared, h_shared_ws, y_shared, status, stream, nullptr, nullptr, 0);
+                             x_perm, h_perm, y_perm, x_shared, h_shared_ws, y_shared, status, stream, nullptr);
+}
+
+extern "C" int comfy_moe_grouped_swiglu_ex(int w_dtype, int n_groups, const ComfyMoeFfnWeights* h_groups,
+                                           const ComfyMoeFfnWeights* h_shared, const int32_t* row_start,
+                                           const int32_t* row_count, int64_t rows_cap, int n_tokens, int dim,
+                                           const void* x_perm, void* h_perm, void* y_perm, const void* x_shared,
+                                           void* h_shared_ws, void* y_shared, const ComfyMoeGroupedOptions* h_options,
+                                           int32_t* status, void* stream) {
+  return grouped_swiglu_impl(w_dtype, n_groups, h_groups, h_shared, row_start, row_count, rows_cap, n_tokens, dim,
+                             x_perm, h_perm, y_perm, x_shared, h_shared_ws, y_shared, status, stream, h_options);
 }
 
 extern "C" int comfy_moe_grouped_swiglu_scatter(int w_dtype, int n_groups, const ComfyMoeFfnWeights* h_groups,
@@ -846,9 +896,13 @@ extern "C" int comfy_moe_grouped_swiglu_scatter(int w_dtype, int n_groups, const
                                                 const int32_t* y_row_shift, int64_t y_rows_cap, int32_t* status,
                                                 void* stream) {
   if (!h_y_out || n_groups <= 0) return COMFY_MOE_EINVAL;
+  ComfyMoeGroupedOptions opt;
+  memset(&opt, 0, sizeof(opt));
+  opt.y_out = h_y_out;
+  opt.y_row_shift = y_row_shift;
+  opt.y_rows_cap = y_rows_cap;
   return grouped_swiglu_impl(w_dtype, n_groups, h_groups, nullptr, row_start, row_count, rows_cap, 0, dim, x_perm,
-                             h_perm, nullptr, nullptr, nullptr, nullptr, status, stream, h_y_out, y_row_shift,
-                             y_rows_cap);
+                             h_perm, nullptr, nullptr, nullptr, nullptr, status, stream, &opt);
 }
 
 // GELU-MLP experts (Linear + bias, exact GELU, Linear + bias): the feed-forward of the Hunyuan3D-2.1 MoE block

@@ -92,9 +92,13 @@ dispatch_kernel(const __grid_constant__ PeerParams p, const __nv_bfloat16* __res
           group_count[j] = fits ? total : 0;
         } else {
           // one row range per (local expert, source): the results of source s go straight into s's return buffer,
-          // at the rows s's own expert-major order gives them
-          for (int src = 0; src < p.world; ++src) {
-            const int g = j * p.world + src;
+          // at the rows s's own expert-major order gives them.  The ranges are listed starting with this rank's own
+          // rows and then rank + 1, rank + 2, ...: the expert GEMM walks them in this order, so it starts on rows
+          // that are certainly there while the peers' rows are still landing, and no two ranks expect the same
+          // peer's rows first.
+          for (int pos = 0; pos < p.world; ++pos) {
+            const int src = (p.rank + pos) % p.world;
+            const int g = j * p.world + pos;
             const int start = recv_row_base(p, counts_all, p.rank, e, src);
             int src_local = 0;
             for (int f = 0; f < e; ++f) src_local += counts_all[src * p.n_experts + f];

@@ -87,6 +87,28 @@ __device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, v
   return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag));
 }
 
+// Orders what this thread has observed through ordinary loads (an acquire of a flag another GPU or CTA released after
+// writing rows) before the tensor-map loads it issues next, which go through the asynchronous proxy.
+__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
+
+// Bounded wait of a converged warp for a 32-bit epoch flag in global memory (possibly written by another GPU) to reach
+// `epoch`; lane 0 polls with acquire semantics at system scope, the result is the same in all lanes.
+__device__ __forceinline__ bool flag_wait_warp(const uint32_t* flag, uint32_t epoch, long long budget_cycles,
+                                               volatile int* abort_flag) {
+  int ok = 1;
+  if ((threadIdx.x & 31) == 0) {
+    const long long t0 = clock64();
+    for (;;) {
+      uint32_t v;
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+      if (static_cast<int32_t>(v - epoch) >= 0) break;
+      if (*abort_flag || clock64() - t0 > budget_cycles) { ok = 0; break; }
+      __nanosleep(100);
+    }
+  }
+  return __shfl_sync(0xffffffffu, ok, 0) != 0;
+}
+
 // ---------------------------------------------------------------- TMA
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* m) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");

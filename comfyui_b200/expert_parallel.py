@@ -452,7 +452,9 @@ class PeerExpertParallelMoE:
         self._h_ws = None
         # gate, plan, dispatch, 2 flags, 2 waits, shared GEMM x2, routed GEMM x2, combine (+ the shared expert's
         # input quantiser for fp8 when it runs beside the routing kernels)
-        self.launches_per_step = 12 + (1 if (self.fp8 and self.front_sms > 0) else 0)
+        # (push: gate, plan, dispatch, flag, shared first pass, routed first pass, common second pass, flag, wait,
+        # combine = 10)
+        self.launches_per_step = (10 if self.push else 12) + (1 if (self.fp8 and self.front_sms > 0) else 0)
 
     def _ensure_buffers(self, n: int, dim: int, device):
         if self.buffers is not None:
@@ -525,8 +527,20 @@ class PeerExpertParallelMoE:
         sc.group_weights = (N.FfnWeights * len(per_group))()
         for i, pack in enumerate(per_group):
             pack.fill(sc.group_weights[i])
-        sc.y_out = (ctypes.c_void_p * len(per_group))(*[int(p) for p in b.peer_ret * len(k.local)]) if self.push else None
         sc.n_groups = len(per_group)
+        sc.y_out = None
+        if self.push:
+            # group j * world + p holds local expert j's rows from source rank (rank + p) % world (own rows first)
+            sources = [(self.rank + pos) % world for _ in k.local for pos in range(world)]
+            sc.y_out = (ctypes.c_void_p * len(per_group))(*[int(b.peer_ret[s]) for s in sources])
+            sc.group_source = (ctypes.c_int32 * len(per_group))(*sources)
+            flags = b.flags.data_ptr() + 4 * N.EP_ARRIVED * N.MAX_RANKS
+            # first pass over the routed groups: every group waits, inside the kernel, for its own source's rows only
+            sc.opt_routed_p1 = N.GroupedOptions(passes=1, arrive_flags=flags, group_source=sc.group_source)
+            # second pass: routed groups (results into the token owners' return buffers) and the shared expert together
+            sc.opt_p2 = N.GroupedOptions(passes=2, y_out=sc.y_out, y_row_shift=sc.p["g_shift"].value,
+                                         y_rows_cap=b.ret_rows)
+            sc.opt_shared_p1 = N.GroupedOptions(passes=1)
         self._scratch_cache[key] = sc
         return sc
 
@@ -578,22 +592,55 @@ class PeerExpertParallelMoE:
         N.check("comfy_moe_ep_signal", lib.comfy_moe_ep_signal(b.plan, N.EP_ARRIVED, b.epoch, S))
         self._state = (sc, x2)
 
-    def phase_experts(self, shared_done: bool = False):
-        """Shared expert on the local tokens (unless the caller already ran it beside the routing kernels), then,
-        after every rank's rows arrived, the local routed experts."""
+    def _shared_first_pass(self, sc, x_in: torch.Tensor, n: int, dim: int, limited: bool):
+        """h_shared = silu(x w1) * (x w3) of the shared expert; its second pass rides in the routed groups' launch."""
+        import ctypes
+
+        N = self.N
+        w = sc.shared_limited if limited else sc.shared
+        N.check("comfy_moe_grouped_swiglu_ex", self.lib.comfy_moe_grouped_swiglu_ex(
+            N.FP8_E4M3 if self.fp8 else N.BF16, 0, None, ctypes.byref(w), None, None, 0, n, dim, None, None, None,
+            ctypes.c_void_p(x_in.data_ptr()), sc.p["h_shared"], sc.p["y_shared"], ctypes.byref(sc.opt_shared_p1),
+            sc.p["status"], self._stream_ptr()))
+
+    def phase_experts(self, shared_done: bool = False, join=None):
+        """Push variant: first pass of the shared expert (unless the caller already ran it beside the routing kernels),
+        first pass of the local routed experts, each group starting as soon as ITS source rank's rows have arrived (the
+        wait sits inside the kernel), then one second pass over routed groups and shared expert together; ``join`` is
+        called between the two passes (the caller's stream join with the shared expert's first pass).
+        Pull variant: shared expert, wait for every rank's rows, routed experts into the local result buffer."""
+        import ctypes
+
         N, lib, b = self.N, self.lib, self.buffers
         sc, x2 = self._state
         p = sc.p
         n, dim = x2.shape
+        act = N.FP8_E4M3 if self.fp8 else N.BF16
+        x_in = sc.x_q if self.fp8 else x2
+        if self.push:
+            if not shared_done and n > 0:
+                self._shared_first_pass(sc, x_in, n, dim, limited=False)
+            S = self._stream_ptr()
+            sc.opt_routed_p1.arrive_epoch = b.epoch
+            N.check("comfy_moe_grouped_swiglu_ex", lib.comfy_moe_grouped_swiglu_ex(
+                act, sc.n_groups, sc.group_weights, None, p["g_start"], p["g_count"], b.cap_rows, 0, dim, p["recv"],
+                p["h_ws"], p["ret0"], None, None, None, ctypes.byref(sc.opt_routed_p1), p["status"], S))
+            if join is not None:
+                join()
+            S = self._stream_ptr()
+            N.check("comfy_moe_grouped_swiglu_ex", lib.comfy_moe_grouped_swiglu_ex(
+                act, sc.n_groups, sc.group_weights, ctypes.byref(sc.shared) if n > 0 else None, p["g_start"],
+                p["g_count"], b.cap_rows, n, dim, p["recv"], p["h_ws"], p["ret0"],
+                ctypes.c_void_p(x_in.data_ptr()) if n > 0 else None, p["h_shared"], p["y_shared"],
+                ctypes.byref(sc.opt_p2), p["status"], S))
+            N.check("comfy_moe_ep_signal", lib.comfy_moe_ep_signal(b.plan, N.EP_DONE, b.epoch, S))
+            return
         if not shared_done and n > 0:
-            self._shared_expert(sc, sc.x_q if self.fp8 else x2, n, dim, limited=False)
+            self._shared_expert(sc, x_in, n, dim, limited=False)
         S = self._stream_ptr()
         N.check("comfy_moe_ep_wait", lib.comfy_moe_ep_wait(b.plan, N.EP_ARRIVED, b.epoch, p["status"], S))
-        act = N.FP8_E4M3 if self.fp8 else N.BF16
-        if self.push:
-            N.check("comfy_moe_grouped_swiglu_scatter", lib.comfy_moe_grouped_swiglu_scatter(
-                act, sc.n_groups, sc.group_weights, p["g_start"], p["g_count"], b.cap_rows, dim, p["recv"], p["h_ws"],
-                sc.y_out, p["g_shift"], b.ret_rows, p["status"], S))
+        if False:
+            pass
         else:
             N.check("comfy_moe_grouped_swiglu", lib.comfy_moe_grouped_swiglu(
                 act, sc.n_groups, sc.group_weights, None, p["g_start"], p["g_count"], b.cap_rows, 0, dim, p["recv"],
@@ -652,10 +699,18 @@ class PeerExpertParallelMoE:
                 self.N.check("comfy_moe_quantize_e4m3", self.lib.comfy_moe_quantize_e4m3(
                     x2.data_ptr(), sc.p["in13_shared"], x2.numel(), sc.p["x_q"],
                     sc.p["overflow"], self._stream_ptr()))
-            self._shared_expert(sc, sc.x_q if self.fp8 else x2, n, dim, limited=True)
+            if self.push:
+                self._shared_first_pass(sc, sc.x_q if self.fp8 else x2, n, dim, limited=True)
+            else:
+                self._shared_expert(sc, sc.x_q if self.fp8 else x2, n, dim, limited=True)
         self.phase_route(x2, want_xq=False)
-        main.wait_stream(side)
-        self.phase_experts(shared_done=True)
+        if self.push:
+            # the routed first pass queues up behind the local dispatch only: it takes SMs as the shared expert's
+            # first pass lets go of them; the streams join before the common second pass
+            self.phase_experts(shared_done=True, join=lambda: main.wait_stream(side))
+        else:
+            main.wait_stream(side)
+            self.phase_experts(shared_done=True)
         return self.phase_combine().view(shape)
 
     def _sm_count(self, device) -> int:

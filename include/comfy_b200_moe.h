@@ -231,6 +231,37 @@ int comfy_moe_grouped_swiglu_scatter(int w_dtype, int n_groups, const ComfyMoeFf
                                      const void* x_perm, void* h_perm, void* const* h_y_out,
                                      const int32_t* y_row_shift, int64_t y_rows_cap, int32_t* status, void* stream);
 
+/* comfy_moe_grouped_swiglu with options (HOST struct; no counterpart in the reference; what the expert-parallel path
+ * is built from):
+ *   passes        1 = first pass only (h_perm / h_shared are written), 2 = second pass only (they are read), 0 or 3 =
+ *                 both.  Lets a caller run the shared expert's first pass beside other kernels and then fold its second
+ *                 pass into the routed groups' launch.
+ *   y_out, y_row_shift, y_rows_cap   as comfy_moe_grouped_swiglu_scatter (NULL: results go to y_perm)
+ *   arrive_flags  DEVICE array of 32-bit epoch flags, one per source rank (NULL: no waiting).  With it, group i is not
+ *                 loaded by the first pass before arrive_flags[group_source[i]] has reached arrive_epoch (acquire at
+ *                 system scope, bounded by arrive_budget_cycles, 0 = COMFY_MOE_EP_WAIT_CYCLES; a wait that runs out
+ *                 leaves code 7 in the status word).  group_source: HOST array [n_groups], -1 = rows already there.
+ *                 So the launch need not be preceded by a wait for every rank: tiles over rows that are there keep
+ *                 the tensor pipe busy while other ranks' rows land. */
+typedef struct ComfyMoeGroupedOptions {
+  int32_t passes;
+  int32_t reserved;
+  void* const* y_out;
+  const int32_t* y_row_shift;
+  int64_t y_rows_cap;
+  const uint32_t* arrive_flags;
+  const int32_t* group_source;
+  uint32_t arrive_epoch;
+  uint32_t reserved2;
+  int64_t arrive_budget_cycles;
+} ComfyMoeGroupedOptions;
+
+int comfy_moe_grouped_swiglu_ex(int w_dtype, int n_groups, const ComfyMoeFfnWeights* h_groups,
+                                const ComfyMoeFfnWeights* h_shared, const int32_t* row_start, const int32_t* row_count,
+                                int64_t rows_cap, int n_tokens, int dim, const void* x_perm, void* h_perm, void* y_perm,
+                                const void* x_shared, void* h_shared_ws, void* y_shared,
+                                const ComfyMoeGroupedOptions* h_options, int32_t* status, void* stream);
+
 /* ---- weighted combine: replaces mul_ + scatter_reduce_ + shared add (model.py:341-345, 324) ---------------
  * out[t] = bf16( bf16( bf16(w0*y[r0]) + bf16(w1*y[r1]) ) + y_shared[t] ), weights rounded to bf16 first.
  * y_shared may be NULL (routed part only, what moe_infer returns).
@@ -389,7 +420,8 @@ int comfy_moe_quantize_weight_e4m3(const void* w, int w_dtype, int64_t n_element
  *   comfy_moe_ep_combine   comfy_moe_combine with every routed row read from its owner's result buffer (two
  *                          partial rows summed, rounded to bf16, with a hidden split).
  * Push variant of the return path (y_row_shift not NULL): the work list has one row range per (local expert, source
- * rank), [local experts * world] entries, and y_row_shift[i] = (first row of that range in the source's own
+ * rank), [local experts * world] entries, entry j * world + p being local expert j's rows from source rank
+ * (rank + p) % world (own rows first), and y_row_shift[i] = (first row of that range in the source's own
  * expert-major order) - (first row of the range here); comfy_moe_grouped_swiglu_scatter then writes the results of
  * range i into the source rank's return buffer (y_out[i], that rank's memory) while it computes, row_map holds rows
  * of the local return buffer, and the plain comfy_moe_combine / comfy_moe_combine_partials finish the step.
