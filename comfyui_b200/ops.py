@@ -383,11 +383,50 @@ def _tensor_key(t: Optional[torch.Tensor]):
     return (t.data_ptr(), t._version, t.dtype, t.device, tuple(t.shape), t.stride(0) if t.dim() else 0)
 
 
+# A Linear that carries weight_function closures (what a model patcher attaches instead of baking a LoRA into the
+# weights, comfy/model_patcher.py:125-149, 670-676) normally evaluates them on every forward.  They are deterministic
+# (a LoRA delta; for fp8 targets a stochastic rounding seeded by the weight's key), so the kernels take the patched
+# weight evaluated ONCE and kept beside the module until the closures or the weight change: the result the stock path
+# computes on every call, at the price of a second copy of the patched weights on the device (which is what the
+# reference itself holds after a full load, comfy/model_patcher.py:594-619).  Set to False to leave patched Linears to
+# the stock composition.
+BAKE_PATCHED_WEIGHTS = True
+
+
+def _patched_weight(lin, device):
+    """``lin.weight`` after its ``weight_function`` closures, evaluated once per (weight, closures) and cached on the
+    module; None when the weight is not on ``device`` or the closures change its dtype or shape."""
+    fns = list(lin.weight_function)
+    w = lin.weight
+    key = (_tensor_key(w), tuple(id(f) for f in fns))
+    cached = lin.__dict__.get("_b200_baked")
+    if cached is not None and cached[0] == key:
+        return cached[2]
+    if w.device != device:
+        return None
+    out = w.detach().clone()              # the closures may work in place; the reference hands them a copy too
+    for fn in fns:
+        out = fn(out)
+    if out.dtype != w.dtype or out.shape != w.shape or out.device != w.device:
+        return None
+    out = out.detach().contiguous()
+    lin.__dict__["_b200_baked"] = (key, fns, out)      # holding the closures keeps their ids from being reused
+    return out
+
+
 def _linear_state(lin, device):
     """(weight, scale_weight, scale_input) if this Linear can feed the kernels as it is now, else None."""
-    if lin.weight_function or lin.bias_function or lin.bias is not None:
+    if lin.bias_function or lin.bias is not None:
         return None
     w = lin.weight
+    if lin.weight_function:
+        if not BAKE_PATCHED_WEIGHTS:
+            return None
+        w = _patched_weight(lin, device)
+        if w is None:
+            return None
+    else:
+        lin.__dict__.pop("_b200_baked", None)
     if w.device != device or w.dim() != 2 or w.stride(1) != 1:
         return None
     if w.dtype == torch.bfloat16:
@@ -508,6 +547,7 @@ def drop_packs(module) -> None:
     for m in module.modules():
         m.__dict__.pop("_b200_pack", None)
         m.__dict__.pop("_b200_layer", None)
+        m.__dict__.pop("_b200_baked", None)
 
 
 def hidream_moe_forward(moe, x: torch.Tensor) -> Optional[torch.Tensor]:

@@ -308,3 +308,51 @@ def test_quantize_e4m3_matches_reference_cast(cuda_device):
     want = (x * inv).to(torch.float8_e4m3fn)        # no clamp in this branch of the reference: overflow becomes NaN
     assert torch.equal(got.view(torch.uint8), want.view(torch.uint8))
     assert int((want.view(torch.uint8) & 0x7f == 0x7f).sum()) >= 4
+
+
+def test_lora_closures_reach_the_kernels(cuda_device):
+    """Experts whose Linears carry weight_function closures (a LoRA attached by a patcher) still take the kernels: the
+    patched weights are evaluated once; the result matches the stock composition, which evaluates them on every call."""
+    from comfyui_b200 import ops
+
+    dev = cuda_device
+    dim, hidden_dim = 512, 2048
+    layer = {k: v.bfloat16() for k, v in O.make_layer(dim, hidden_dim, 4, seed=0).items()}
+    mod = _module(dev, dim, hidden_dim, ops.disable_weight_init, layer)
+    g = torch.Generator().manual_seed(3)
+    count = [0]
+    for ffn in list(mod.experts) + [mod.shared_experts]:
+        for lin in (ffn.w1, ffn.w2, ffn.w3):
+            a = (torch.randn((lin.weight.shape[0], 8), generator=g) * 0.05).bfloat16().to(dev)
+            b = (torch.randn((8, lin.weight.shape[1]), generator=g) * 0.05).bfloat16().to(dev)
+
+            def patch(w, a=a, b=b):
+                count[0] += 1
+                return w + (a @ b)
+
+            lin.weight_function = [patch]
+    x = O.make_input(300, dim, seed=1).bfloat16().to(dev).view(1, 300, dim)
+    with torch.inference_mode():
+        assert ops._layer_pack(mod, x) is not None, "patched experts must stay eligible"
+        evaluated = count[0]
+        assert evaluated == 15
+        fast = mod(x)
+        fast2 = mod(x)
+        assert count[0] == evaluated and torch.equal(fast, fast2)          # no re-evaluation on later calls
+        ops.ENABLE_SM100_KERNELS = False
+        try:
+            stock = mod(x)
+        finally:
+            ops.ENABLE_SM100_KERNELS = True
+    assert count[0] > evaluated                                              # the stock path evaluates per call
+    idx_fast = ops.hidream_gate(mod.gate, x)[0]
+    same = torch.ones(300, dtype=torch.bool)
+    with torch.inference_mode():
+        ops.ENABLE_SM100_KERNELS = False
+        try:
+            idx_stock = mod.gate(x)[0]
+        finally:
+            ops.ENABLE_SM100_KERNELS = True
+    same = (idx_fast.sort(dim=1).values == idx_stock.view(-1, 2).sort(dim=1).values).all(dim=1).cpu()
+    torch.testing.assert_close(fast.view(-1, dim)[same].float().cpu(), stock.view(-1, dim)[same].float().cpu(),
+                               rtol=2e-2, atol=2e-2)

@@ -131,7 +131,12 @@ def test_shim_declines_ineligible_calls(golden):
                                  torch.zeros(256, 1)) is None
     assert ops._linear_state(mod.experts[0].w1, x.device) is not None
     mod.experts[0].w1.weight_function = [lambda t: t]
-    assert ops._linear_state(mod.experts[0].w1, x.device) is None
+    ops.BAKE_PATCHED_WEIGHTS = False            # patched Linears left to the stock composition
+    try:
+        assert ops._linear_state(mod.experts[0].w1, x.device) is None
+    finally:
+        ops.BAKE_PATCHED_WEIGHTS = True
+    assert ops._linear_state(mod.experts[0].w1, x.device) is not None     # default: evaluated once for the kernels
 
 
 def test_stochastic_rounding_is_unbiased_and_exact_on_grid():
@@ -186,3 +191,43 @@ def test_registered_torch_ops_trace_without_a_gpu():
     assert blk.shape == x.shape
     schema = str(torch.ops.comfyui_b200.hidream_moe.default._schema)
     assert "Tensor[] w1" in schema and "-> Tensor" in schema
+
+
+def test_patched_weights_are_evaluated_once_for_the_kernels():
+    """A Linear with weight_function closures (a LoRA attached, not baked): the shim hands the kernels the patched weight
+    evaluated once, re-evaluates when the closures or the weight change, and forgets it when the closures go away."""
+    from comfyui_b200 import ops
+
+    lin = ops.disable_weight_init.Linear(16, 8, bias=False, dtype=torch.bfloat16)
+    with torch.no_grad():
+        lin.weight.copy_(torch.randn(8, 16))
+    calls = []
+    delta = torch.randn(8, 16).bfloat16()
+
+    def lora(w):
+        calls.append(1)
+        return w + delta
+
+    cpu = torch.device("cpu")
+    assert ops._linear_state(lin, cpu)[0] is lin.weight or torch.equal(ops._linear_state(lin, cpu)[0], lin.weight)
+    lin.weight_function = [lora]
+    w1 = ops._linear_state(lin, cpu)[0]
+    w2 = ops._linear_state(lin, cpu)[0]
+    assert len(calls) == 1 and w1 is w2 and torch.equal(w1, lin.weight + delta)
+    assert torch.equal(lin(torch.eye(16).bfloat16()), torch.nn.functional.linear(torch.eye(16).bfloat16(), w1))
+    seen = len(calls)                                       # (the stock forward above evaluated the closure itself)
+    lin.weight_function = [lambda w: lora(w)]               # new closures: evaluated again
+    ops._linear_state(lin, cpu)
+    assert len(calls) == seen + 1
+    with torch.no_grad():
+        lin.weight.add_(1.0)                                # the weight changed in place: evaluated again
+    w3 = ops._linear_state(lin, cpu)[0]
+    assert len(calls) == seen + 2 and torch.equal(w3, lin.weight + delta)
+    lin.weight_function = []
+    assert ops._linear_state(lin, cpu)[0] is lin.weight and "_b200_baked" not in lin.__dict__
+    lin.weight_function = [lora]
+    ops.BAKE_PATCHED_WEIGHTS = False
+    try:
+        assert ops._linear_state(lin, cpu) is None
+    finally:
+        ops.BAKE_PATCHED_WEIGHTS = True
