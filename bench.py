@@ -952,12 +952,26 @@ def measure_config4(dev, dtype: str, steps: int, n_double: int = 16, n_single: i
             ms, out = timed(steps, 2)
         ops.check_device_status()
         finite = bool(torch.isfinite(out.float()).all())
+        from comfyui_b200.ldm.hidream import model as hidream
+
         ops.ENABLE_SM100_KERNELS = False
+        stock_gate = hidream.MoEGate.forward
         try:
             ms_stock, out_stock = timed(max(steps // 2, 2), 1)
+            rel_as_shipped = float((out.float() - out_stock.float()).norm() / out_stock.float().norm())
+
+            # one more stock step with the routing convention of the kernels (MoEGate on the fp32 copy of its input,
+            # weights cast back): what is left is arithmetic, not a different choice of experts
+            def gate_on_fp32_copy(self, hidden_states):
+                idx, w, aux = stock_gate(self, hidden_states.float())
+                return idx, w.to(hidden_states.dtype), aux
+
+            hidream.MoEGate.forward = gate_on_fp32_copy
+            out_same_routing = model(x, t, y, context, llama)
+            rel = float((out.float() - out_same_routing.float()).norm() / out_same_routing.float().norm())
         finally:
+            hidream.MoEGate.forward = stock_gate
             ops.ENABLE_SM100_KERNELS = True
-        rel = float((out.float() - out_stock.float()).norm() / out_stock.float().norm())
     del model
     torch.cuda.empty_cache()
     return {
@@ -972,7 +986,10 @@ def measure_config4(dev, dtype: str, steps: int, n_double: int = 16, n_single: i
         "gpu_bar": {"what": "same modules and weights, sm_100a kernels off: stock PyTorch composition on this GPU",
                     "ms_per_step": ms_stock},
         "speedup_vs_stock": ms_stock / ms,
-        "rel_rms_vs_stock_output": rel,
+        # relative RMS difference of the step output between the kernels and the stock composition: with the gate of
+        # both on the fp32 copy of its input, and against the composition as shipped (bf16 gate: a few tokens per
+        # thousand and layer pick other experts, and 48 layers of random weights spread that over the image)
+        "rel_rms_vs_stock_output": {"same_routing_convention": rel, "as_shipped": rel_as_shipped},
     }
 
 

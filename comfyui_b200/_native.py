@@ -52,6 +52,7 @@ EXPORTS = (
     "comfy_moe_stochastic_round_e4m3",
     "comfy_moe_quantize_weight_e4m3",
     "comfy_attn_rmsnorm_rope",
+    "comfy_attn_forward",
     "comfy_moe_grouped_linear",
     "comfy_moe_ep_dispatch",
     "comfy_moe_ep_signal",
@@ -294,6 +295,8 @@ def load(build_if_missing: bool = False) -> ctypes.CDLL:
     lib.comfy_moe_quantize_e4m3.argtypes = [c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p]
     lib.comfy_attn_rmsnorm_rope.argtypes = [c_void_p, c_int64, c_void_p, c_float, c_void_p, c_int64, c_int, c_int, c_int,
                                             c_int, c_int, c_int, c_void_p, c_int64, c_int, c_void_p]
+    lib.comfy_attn_forward.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p,
+                                       c_void_p, c_void_p]
     lib.comfy_moe_grouped_linear.argtypes = [c_int, POINTER(LinearGroup), c_void_p, c_void_p]
     lib.comfy_moe_stochastic_round_e4m3.argtypes = [c_void_p, c_int, c_void_p, c_int64, c_void_p, c_void_p]
     lib.comfy_moe_quantize_weight_e4m3.argtypes = [c_void_p, c_int, c_int64, c_void_p, c_void_p, c_void_p]

@@ -23,6 +23,7 @@ SOURCES = [
     "moe_grouped_gemm_sm100.cu",
     "moe_peer.cu",
     "attn_glue.cu",
+    "attn_fwd_sm100.cu",
     "weight_ingest.cu",
     "moe_c_api.cu",
 ]

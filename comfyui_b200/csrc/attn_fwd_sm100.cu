@@ -1,0 +1,401 @@
+// Attention forward for the HiDream blocks on sm_100a: softmax(Q K^T / sqrt(d)) V with the two contractions on
+// tcgen05 tensor cores, S and O accumulators in TMEM, K / V tiles fed by TMA.  Replaces the
+// scaled_dot_product_attention call behind comfy/ldm/hidream/model.py:75-76 (attention_pytorch,
+// comfy/ldm/modules/attention.py:475-516) for the block's shape: bf16, head_dim 128, no mask, not causal.
+//
+// One CTA computes 128 query rows of one (batch, head) against all keys, 128 keys at a time:
+//   S_j = Q K_j^T            tcgen05.mma, A = Q (shared memory), B = K_j (shared memory), D = S in TMEM (two buffers)
+//   P_j = exp2(c S_j - m)    128 softmax threads, one query row each: the row's 128 scores come out of TMEM into the
+//                            thread's registers, so maximum and sum need no shuffles; P goes back to TMEM as bf16
+//   O  += P_j V_j            tcgen05.mma, A = P_j (TMEM), B = V_j (shared memory, keys along K), D = O in TMEM
+// The running maximum m is only raised when a row's new maximum exceeds it by more than 8 (in log2 units): P then stays
+// below 2^8, which bf16 and the fp32 accumulators hold without loss, and O (which lives in TMEM and would have to be
+// read, scaled and written back) is rescaled only on those rare tiles; the final division by the row sum makes the
+// result independent of the reference point.
+// Warps: 0-3 softmax and epilogue (TMEM lane quarter = warp index), 4 = MMA issuer and TMEM owner, 5 = TMA producer.
+// Every wait is bounded and reports through the status word like the waits of the grouped GEMM.
+#include <cuda.h>
+
+#include "moe_common.cuh"
+#include "ptx_sm100.cuh"
+
+namespace comfy_b200 {
+
+constexpr int kAttnD = 128;                    // head dimension
+constexpr int kAttnM = 128;                    // query rows per CTA
+constexpr int kAttnN = 128;                    // keys per tile
+constexpr int kAttnStages = 2;                 // K / V stages in flight
+constexpr int kAttnBoxBytes = 128 * 128;       // one TMA box: 128 rows x 64 bf16 (128 bytes, 128-byte swizzle)
+constexpr int kAttnTileBytes = 2 * kAttnBoxBytes;   // a 128 x 128 bf16 tile = two boxes side by side along d
+constexpr int kAttnThreads = 6 * 32;
+constexpr int kAttnTmemCols = 512;             // S0 [0,128) S1 [128,256) O [256,384); P aliases the first 64 columns of S
+constexpr size_t kAttnSmem = kAttnTileBytes * (1 + 2 * kAttnStages) + 1024;
+constexpr int kStatusAttnTimeout = 5;
+constexpr float kAttnRescaleThreshold = 8.0f;  // log2 units
+
+struct AttnParams {
+  CUtensorMap map_q, map_k, map_v;             // [B][S][H * D] bf16, boxes of 128 rows x 64 elements
+  __nv_bfloat16* out;                          // [B, S_q, H * D]
+  int32_t* status;
+  int seq_q, seq_kv, heads;
+  float scale_log2;                            // softmax scale * log2(e)
+};
+
+__device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int x, int y, int z) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      :
+      : "r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z)
+      : "memory");
+}
+
+// Shared-memory descriptor of a B operand whose N dimension is the contiguous one (V: rows = keys = K of the MMA,
+// 64 head-dimension elements per 128-byte row, the other 64 in a second box `box_stride` bytes further), 128-byte
+// swizzle: leading byte offset = distance between the two 64-element column blocks, stride byte offset = distance
+// between groups of eight keys.
+__device__ __forceinline__ uint64_t umma_desc_mn_sw128(uint32_t smem_addr, uint32_t box_stride) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFF) >> 4);
+  d |= static_cast<uint64_t>((box_stride >> 4) & 0x3FFF) << 16;
+  d |= static_cast<uint64_t>(1024 >> 4) << 32;
+  d |= static_cast<uint64_t>(1) << 46;
+  d |= static_cast<uint64_t>(2) << 61;
+  return d;
+}
+
+// D[tmem] (+)= A[tmem] * B[smem]: the A operand (P) is read from tensor memory.
+__device__ __forceinline__ void umma_ts_bf16(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc,
+                                             uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t"
+      "}"
+      :
+      : "r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+__device__ __forceinline__ void tmem_st_32x32b_x32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      :
+      : "r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
+        "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
+        "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__global__ void __launch_bounds__(kAttnThreads, 1)
+attn_fwd_kernel(const __grid_constant__ AttnParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t q_full;
+  __shared__ __align__(8) uint64_t k_full[kAttnStages], k_empty[kAttnStages];
+  __shared__ __align__(8) uint64_t v_full[kAttnStages], v_empty[kAttnStages];
+  __shared__ __align__(8) uint64_t s_full[2];
+  __shared__ __align__(8) uint64_t p_ready[2];
+  __shared__ __align__(8) uint64_t o_done;
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* q_smem = smem;
+  uint8_t* k_smem = smem + kAttnTileBytes;
+  uint8_t* v_smem = k_smem + kAttnStages * kAttnTileBytes;
+
+  const int q_tile = blockIdx.x, head = blockIdx.y, batch = blockIdx.z;
+  const int q_row0 = q_tile * kAttnM;
+  const int n_kv = (p.seq_kv + kAttnN - 1) / kAttnN;
+  const int col0 = head * kAttnD;              // first element of this head inside a token's H * D row
+
+  if (tid == 0) {
+    mbar_init(&q_full, 1);
+    for (int s = 0; s < kAttnStages; ++s) {
+      mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1);
+      mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) { mbar_init(&s_full[b], 1); mbar_init(&p_ready[b], 128); }
+    mbar_init(&o_done, 1);
+    fence_mbar_init();
+    abort_flag = 0;
+  }
+  if (warp == 4) { tmem_alloc(&tmem_slot, kAttnTmemCols); tmem_relinquish(); }
+  __syncwarp();
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = tmem_slot;
+  volatile int* abort_ptr = &abort_flag;
+  auto give_up = [&]() {
+    if (lane == 0) { atomicCAS(p.status, 0, kStatusAttnTimeout); abort_flag = 1; }
+  };
+
+  if (warp == 5) {
+    // ------------------------------------------------------------------ TMA producer
+    if (elect_one()) {
+      mbar_arrive_expect_tx(&q_full, kAttnTileBytes);
+      tma_load_3d(q_smem, &p.map_q, &q_full, col0, q_row0, batch);
+      tma_load_3d(q_smem + kAttnBoxBytes, &p.map_q, &q_full, col0 + 64, q_row0, batch);
+    }
+    __syncwarp();
+    bool ok = true;
+    for (int j = 0; j < n_kv && ok; ++j) {
+      const int s = j % kAttnStages;
+      const uint32_t ph = (j / kAttnStages) & 1u;
+      ok = mbar_wait_warp(&k_empty[s], ph ^ 1u, abort_ptr);
+      if (!ok) { give_up(); break; }
+      if (elect_one()) {
+        mbar_arrive_expect_tx(&k_full[s], kAttnTileBytes);
+        tma_load_3d(k_smem + s * kAttnTileBytes, &p.map_k, &k_full[s], col0, j * kAttnN, batch);
+        tma_load_3d(k_smem + s * kAttnTileBytes + kAttnBoxBytes, &p.map_k, &k_full[s], col0 + 64, j * kAttnN, batch);
+      }
+      __syncwarp();
+      ok = mbar_wait_warp(&v_empty[s], ph ^ 1u, abort_ptr);
+      if (!ok) { give_up(); break; }
+      if (elect_one()) {
+        mbar_arrive_expect_tx(&v_full[s], kAttnTileBytes);
+        tma_load_3d(v_smem + s * kAttnTileBytes, &p.map_v, &v_full[s], col0, j * kAttnN, batch);
+        tma_load_3d(v_smem + s * kAttnTileBytes + kAttnBoxBytes, &p.map_v, &v_full[s], col0 + 64, j * kAttnN, batch);
+      }
+      __syncwarp();
+    }
+  } else if (warp == 4) {
+    // ------------------------------------------------------------------ MMA issuer
+    constexpr uint32_t idesc_qk = umma_idesc<false>(kAttnM, kAttnN);
+    constexpr uint32_t idesc_pv = umma_idesc<false>(kAttnM, kAttnD) | (1u << 16);     // B with N contiguous
+    bool ok = mbar_wait_warp(&q_full, 0, abort_ptr);
+    if (!ok) give_up();
+    const uint32_t q_addr = smem_u32(q_smem);
+    const uint32_t tmem_o = tmem_base + 256;
+    for (int j = 0; j <= n_kv && ok; ++j) {
+      if (j < n_kv) {
+        // S_j = Q K_j^T into S buffer j & 1
+        const int s = j % kAttnStages;
+        ok = mbar_wait_warp(&k_full[s], (j / kAttnStages) & 1u, abort_ptr);
+        if (!ok) { give_up(); break; }
+        tc_fence_after_sync();
+        if (elect_one()) {
+          const uint32_t k_addr = smem_u32(k_smem + s * kAttnTileBytes);
+          const uint32_t d_tmem = tmem_base + (j & 1) * 128;
+#pragma unroll
+          for (int kk = 0; kk < kAttnD / 16; ++kk) {
+            const uint32_t off = (kk >> 2) * kAttnBoxBytes + (kk & 3) * 32;     // box, then 32 bytes per 16 elements
+            umma_ss<false>(d_tmem, umma_desc_k_sw128(q_addr + off), umma_desc_k_sw128(k_addr + off), idesc_qk,
+                           kk != 0 ? 1u : 0u);
+          }
+          umma_commit(&s_full[j & 1]);
+          umma_commit(&k_empty[s]);
+        }
+        __syncwarp();
+      }
+      if (j >= 1) {
+        // O += P_{j-1} V_{j-1}
+        const int t = j - 1, s = t % kAttnStages;
+        ok = mbar_wait_warp(&p_ready[t & 1], (t >> 1) & 1u, abort_ptr);
+        if (ok) ok = mbar_wait_warp(&v_full[s], (t / kAttnStages) & 1u, abort_ptr);
+        if (!ok) { give_up(); break; }
+        tc_fence_after_sync();
+        if (elect_one()) {
+          const uint32_t v_addr = smem_u32(v_smem + s * kAttnTileBytes);
+          const uint32_t p_tmem = tmem_base + (t & 1) * 128;
+#pragma unroll
+          for (int kk = 0; kk < kAttnN / 16; ++kk) {
+            // 16 keys = two groups of eight rows (2048 bytes); 16 bf16 of P = 8 columns of TMEM
+            umma_ts_bf16(tmem_o, p_tmem + kk * 8, umma_desc_mn_sw128(v_addr + kk * 2048, kAttnBoxBytes), idesc_pv,
+                         (t | kk) != 0 ? 1u : 0u);
+          }
+          umma_commit(&v_empty[s]);
+          umma_commit(&o_done);
+        }
+        __syncwarp();
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax + epilogue: one query row per thread
+    const int row = warp * 32 + lane;                    // row inside the tile = TMEM lane
+    const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
+    float m_ref = -INFINITY, l_sum = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_kv && ok; ++j) {
+      const uint32_t s_tmem = lane_base + (j & 1) * 128;
+      ok = mbar_wait_warp(&s_full[j & 1], (j >> 1) & 1u, abort_ptr);
+      if (!ok) { give_up(); break; }
+      tc_fence_after_sync();
+      uint32_t sr[4][32];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld_32x32b_x32(s_tmem + c * 32, sr[c]);
+      tmem_ld_wait();
+      const int valid = p.seq_kv - j * kAttnN;           // keys of this tile that exist
+      float mx = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float v = __uint_as_float(sr[c][i]) * p.scale_log2;
+          if (valid < kAttnN && c * 32 + i >= valid) v = -INFINITY;
+          sr[c][i] = __float_as_uint(v);
+          mx = fmaxf(mx, v);
+        }
+      // raise the reference maximum only when some row of this warp needs it (tcgen05.ld / st are warp-wide)
+      const bool raise = mx > m_ref + kAttnRescaleThreshold;
+      if (__any_sync(0xffffffffu, raise)) {
+        const float m_new = raise ? mx : m_ref;
+        const float factor = (m_ref == -INFINITY) ? 0.f : fast_exp2(m_ref - m_new);
+        if (j > 0) {
+          // O holds the sum over tiles 0 .. j-1 once the last of their MMAs has finished
+          ok = mbar_wait_warp(&o_done, (j - 1) & 1u, abort_ptr);
+          if (!ok) { give_up(); break; }
+          tc_fence_after_sync();
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            uint32_t o[32];
+            tmem_ld_32x32b_x32(lane_base + 256 + c * 32, o);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * factor);
+            tmem_st_32x32b_x32(lane_base + 256 + c * 32, o);
+          }
+          tmem_st_wait();
+        }
+        l_sum *= factor;
+        m_ref = m_new;
+      }
+      // P = exp2(s - m_ref), packed to bf16 pairs; the row sum uses the unrounded values
+      uint32_t pr[2][32];
+      float part = 0.f;
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          const float e0 = fast_exp2(__uint_as_float(sr[c][i]) - m_ref);
+          const float e1 = fast_exp2(__uint_as_float(sr[c][i + 1]) - m_ref);
+          part += e0 + e1;
+          pr[c >> 1][(c & 1) * 16 + (i >> 1)] = pack_bf16x2(e0, e1);
+        }
+      l_sum += part;
+      tmem_st_32x32b_x32(s_tmem, pr[0]);
+      tmem_st_32x32b_x32(s_tmem + 32, pr[1]);
+      tmem_st_wait();
+      tc_fence_before_sync();
+      mbar_arrive(&p_ready[j & 1]);
+    }
+    if (ok) {
+      ok = mbar_wait_warp(&o_done, (n_kv - 1) & 1u, abort_ptr);
+      if (!ok) give_up();
+    }
+    if (ok) {
+      tc_fence_after_sync();
+      const float inv = 1.0f / l_sum;
+      const int q_row = q_row0 + row;
+      __nv_bfloat16* o_row = p.out + (static_cast<size_t>(batch) * p.seq_q + q_row) * (static_cast<size_t>(p.heads) * kAttnD) + col0;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t o[32];
+        tmem_ld_32x32b_x32(lane_base + 256 + c * 32, o);
+        tmem_ld_wait();
+        if (q_row < p.seq_q) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            uint4 q;
+            q.x = pack_bf16x2(__uint_as_float(o[8 * i]) * inv, __uint_as_float(o[8 * i + 1]) * inv);
+            q.y = pack_bf16x2(__uint_as_float(o[8 * i + 2]) * inv, __uint_as_float(o[8 * i + 3]) * inv);
+            q.z = pack_bf16x2(__uint_as_float(o[8 * i + 4]) * inv, __uint_as_float(o[8 * i + 5]) * inv);
+            q.w = pack_bf16x2(__uint_as_float(o[8 * i + 6]) * inv, __uint_as_float(o[8 * i + 7]) * inv);
+            reinterpret_cast<uint4*>(o_row + c * 32)[i] = q;
+          }
+        }
+      }
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  __syncwarp();
+  if (*abort_ptr) {
+    const long long t0 = clock64();
+    while (clock64() - t0 < 2000000LL) __nanosleep(1000);     // copies in flight may still land in shared memory
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 4) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, kAttnTmemCols);
+  }
+}
+
+typedef CUresult (*EncodeTiledFn3)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// [B][S][H * D] bf16, contiguous; boxes of 128 rows x 64 elements, 128-byte swizzle, rows past S read as zero.
+static int make_attn_map(CUtensorMap* map, const void* base, int64_t batch, int64_t seq, int64_t row_elems) {
+  static EncodeTiledFn3 encode = nullptr;
+  if (!encode) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) != cudaSuccess ||
+        qres != cudaDriverEntryPointSuccess)
+      return COMFY_MOE_EDEVICE;
+    encode = reinterpret_cast<EncodeTiledFn3>(ptr);
+  }
+  if (!base || !aligned16(base)) return COMFY_MOE_EINVAL;
+  cuuint64_t dims[3] = {static_cast<cuuint64_t>(row_elems), static_cast<cuuint64_t>(seq), static_cast<cuuint64_t>(batch)};
+  cuuint64_t strides[2] = {static_cast<cuuint64_t>(row_elems) * 2, static_cast<cuuint64_t>(row_elems) * seq * 2};
+  cuuint32_t box[3] = {64u, 128u, 1u};
+  cuuint32_t estr[3] = {1u, 1u, 1u};
+  CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? COMFY_MOE_OK : COMFY_MOE_ECUDA;
+}
+
+}  // namespace comfy_b200
+
+using namespace comfy_b200;
+
+extern "C" int comfy_attn_forward(const void* q, const void* k, const void* v, int batch, int seq_q, int seq_kv,
+                                  int heads, int head_dim, float scale, void* out, int32_t* status, void* stream) {
+  if (batch < 0 || seq_q < 0 || seq_kv < 0 || heads <= 0 || !status) return COMFY_MOE_EINVAL;
+  if (head_dim != kAttnD) return COMFY_MOE_EUNSUPPORTED;
+  if (batch == 0 || seq_q == 0) return COMFY_MOE_OK;
+  if (seq_kv == 0 || !q || !k || !v || !out || !aligned16(out)) return COMFY_MOE_EINVAL;
+  if (batch > 65535 || heads > 65535) return COMFY_MOE_EUNSUPPORTED;
+  int dev = 0, major = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess ||
+      cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess)
+    return COMFY_MOE_ECUDA;
+  if (major != 10) return COMFY_MOE_EDEVICE;
+  AttnParams p;
+  memset(&p, 0, sizeof(p));
+  const int64_t row = static_cast<int64_t>(heads) * kAttnD;
+  int rc;
+  if ((rc = make_attn_map(&p.map_q, q, batch, seq_q, row)) != COMFY_MOE_OK) return rc;
+  if ((rc = make_attn_map(&p.map_k, k, batch, seq_kv, row)) != COMFY_MOE_OK) return rc;
+  if ((rc = make_attn_map(&p.map_v, v, batch, seq_kv, row)) != COMFY_MOE_OK) return rc;
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.status = status;
+  p.seq_q = seq_q; p.seq_kv = seq_kv; p.heads = heads;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  constexpr int kMaxDevices = 64;
+  static bool configured[kMaxDevices] = {false};
+  if (dev < 0 || dev >= kMaxDevices || !configured[dev]) {
+    if (cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kAttnSmem)) !=
+        cudaSuccess)
+      return COMFY_MOE_ECUDA;
+    if (dev >= 0 && dev < kMaxDevices) configured[dev] = true;
+  }
+  dim3 grid((seq_q + kAttnM - 1) / kAttnM, heads, batch);
+  attn_fwd_kernel<<<grid, kAttnThreads, kAttnSmem, static_cast<cudaStream_t>(stream)>>>(p);
+  return check_launch();
+}

@@ -560,9 +560,11 @@ class PeerExpertParallelMoE:
             ctypes.c_void_p(x_in.data_ptr()), sc.p["h_shared"], sc.p["y_shared"], sc.p["status"], self._stream_ptr()))
 
     # -- the three phases of a step ---------------------------------------------------------------
-    def phase_route(self, x2: torch.Tensor, counts_all: Optional[torch.Tensor] = None, want_xq: bool = True):
+    def phase_route(self, x2: torch.Tensor, counts_all: Optional[torch.Tensor] = None, want_xq: bool = True,
+                    after_gate=None):
         """Gate, plan, histogram exchange, dispatch, "arrived" flag.  ``counts_all`` [world, E] replaces the
-        collective in single-GPU emulation."""
+        collective in single-GPU emulation; ``after_gate`` is called once the gate kernel has been launched (the
+        caller's hook for starting work on another stream that should not compete with the gate for SMs)."""
         import ctypes
 
         N, lib = self.N, self.lib
@@ -579,6 +581,8 @@ class PeerExpertParallelMoE:
             N.check("comfy_moe_gate_topk", lib.comfy_moe_gate_topk(px, p["gate_w"], sc.gate_dtype, n, dim, self.n_experts,
                                                                   2, p["idx"], p["w"], p["block_counts"], p["near"], None,
                                                                   1e-6, S))
+        if after_gate is not None:
+            after_gate()
         N.check("comfy_moe_route_plan", lib.comfy_moe_route_plan(p["block_counts"], n, self.n_experts,
                                                                  p["block_offsets"], p["counts"], p["offsets"], S))
         if counts_all is not None:
@@ -683,27 +687,31 @@ class PeerExpertParallelMoE:
             self.phase_route(x2)
             self.phase_experts()
             return self.phase_combine().view(shape)
-        # The shared expert needs only x, so it is launched first, on a side stream and on all but `front_sms` SMs;
-        # the gate, the histogram all-gather and the dispatch kernel (NVLink-bound) run beside it on the SMs left
-        # free, and the routed experts start when both are done.  For fp8 its input is quantised by a kernel of its
-        # own first (the dispatch kernel's quantised copy would come too late).
+        # The shared expert needs only x, so it runs on a side stream, on all but `front_sms` SMs, beside the routing
+        # plan, the histogram all-gather and the dispatch kernel (NVLink-bound), which take the SMs left free; the
+        # routed experts follow.  The gate goes first and alone: it is a memory-bound pass over all tokens that takes
+        # 20 us on the whole GPU and over 100 us on sixteen SMs.  For fp8 the shared expert's input is quantised by a
+        # kernel of its own (the dispatch kernel's quantised copy would come too late).
         self._ensure_buffers(n, dim, x2.device)
         sc = self._scratch(n, dim, x2.device)
         main = torch.cuda.current_stream()
         if self._side is None:
             self._side = torch.cuda.Stream(device=x2.device)
         side = self._side
-        side.wait_stream(main)
-        with torch.cuda.stream(side):
-            if self.fp8:
-                self.N.check("comfy_moe_quantize_e4m3", self.lib.comfy_moe_quantize_e4m3(
-                    x2.data_ptr(), sc.p["in13_shared"], x2.numel(), sc.p["x_q"],
-                    sc.p["overflow"], self._stream_ptr()))
-            if self.push:
-                self._shared_first_pass(sc, sc.x_q if self.fp8 else x2, n, dim, limited=True)
-            else:
-                self._shared_expert(sc, sc.x_q if self.fp8 else x2, n, dim, limited=True)
-        self.phase_route(x2, want_xq=False)
+
+        def start_shared_expert():
+            side.wait_stream(main)              # behind the gate (and whatever produced x)
+            with torch.cuda.stream(side):
+                if self.fp8:
+                    self.N.check("comfy_moe_quantize_e4m3", self.lib.comfy_moe_quantize_e4m3(
+                        x2.data_ptr(), sc.p["in13_shared"], x2.numel(), sc.p["x_q"],
+                        sc.p["overflow"], self._stream_ptr()))
+                if self.push:
+                    self._shared_first_pass(sc, sc.x_q if self.fp8 else x2, n, dim, limited=True)
+                else:
+                    self._shared_expert(sc, sc.x_q if self.fp8 else x2, n, dim, limited=True)
+
+        self.phase_route(x2, want_xq=False, after_gate=start_shared_expert)
         if self.push:
             # the routed first pass queues up behind the local dispatch only: it takes SMs as the shared expert's
             # first pass lets go of them; the streams join before the common second pass

@@ -755,3 +755,23 @@ def grouped_linear(groups: Sequence[Tuple[torch.Tensor, torch.Tensor, Optional[t
         status = device_status(dev)
     N.check("comfy_moe_grouped_linear", N.load().comfy_moe_grouped_linear(len(groups), arr, _ptr(status), _stream()))
     return res
+
+
+def attention_forward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: Optional[float] = None,
+                      status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """softmax(q k^T * scale) v per head.  q [B, Sq, H, 128], k / v [B, Skv, H, 128] bf16 contiguous ->
+    [B, Sq, H * 128]; scale defaults to 1 / sqrt(128)."""
+    _need_cuda(q, k, v)
+    b, sq, h, d = q.shape
+    if k.shape != v.shape or k.shape[0] != b or k.shape[2:] != (h, d):
+        raise ValueError("attention_forward: k and v must be [B, Skv, H, D] matching q's batch, heads and head_dim")
+    for t in (q, k, v):
+        if t.dtype != torch.bfloat16 or not t.is_contiguous():
+            raise ValueError("attention_forward: q, k, v must be contiguous bf16 tensors")
+    out = torch.empty((b, sq, h * d), dtype=torch.bfloat16, device=q.device)
+    if status is None:
+        status = device_status(q.device)
+    rc = N.load().comfy_attn_forward(_ptr(q), _ptr(k), _ptr(v), b, sq, k.shape[1], h, d,
+                                     float(scale if scale is not None else d ** -0.5), _ptr(out), _ptr(status), _stream())
+    N.check("comfy_attn_forward", rc)
+    return out

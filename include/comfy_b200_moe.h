@@ -371,6 +371,15 @@ int comfy_attn_rmsnorm_rope(const void* x, int64_t ld_x, const void* weight, flo
                             int tokens_per_batch, int heads, int head_dim, void* out, int64_t out_batch_stride,
                             int out_row_offset, void* stream);
 
+/* ---- attention forward of the HiDream blocks (model.py:75-76 over attention_pytorch, attention.py:475-516) ---------
+ * out[b, s, h, :] = softmax(q[b, s, h, :] . k[b, :, h, :]^T * scale) . v[b, :, h, :]   (no mask, not causal)
+ * q [batch, seq_q, heads, 128], k / v [batch, seq_kv, heads, 128], out [batch, seq_q, heads * 128]; bf16, contiguous
+ * (the layout comfy_attn_rmsnorm_rope writes and the output projection reads, so nothing is transposed).  Both
+ * contractions run on tcgen05 tensor cores with S and O in tensor memory; scores and probabilities never touch HBM.
+ * head_dim must be 128 (COMFY_MOE_EUNSUPPORTED otherwise).  status: a status block (code 5: a bounded wait ran out). */
+int comfy_attn_forward(const void* q, const void* k, const void* v, int batch, int seq_q, int seq_kv, int heads,
+                       int head_dim, float scale, void* out, int32_t* status, void* stream);
+
 /* ---- activation quantiser on its own (comfy/ops.py:338-343) --------------------------------------------------
  * scale NULL:  out = e4m3(clamp(x, +-448))                 (:339-340; round to nearest even)
  * scale given: out = e4m3(bf16(x * bf16(1 / scale)))       (:342-343; NO clamp: beyond the e4m3 range the result is
@@ -497,7 +506,7 @@ int comfy_moe_ffn_block(const ComfyMoeLayer* h_layer, const ComfyMoeWorkspace* h
                         int tokens_per_batch, float eps, void* out, void* stream);
 
 /* The device status word.  Kernels move it from 0 to a code when something went wrong on the device (1-3: a bounded
- * wait of the grouped GEMM's producer / MMA / epilogue role ran out; 7: a peer's flag did not arrive in time; 8: routed
+ * wait of the grouped GEMM's producer / MMA / epilogue role ran out; 5: one of the attention kernel's; 7: a peer's flag did not arrive in time; 8: routed
  * rows did not fit a peer receive buffer and were dropped; 9: the routing check found an inconsistency) and never overwrite a code that is already there; no entry
  * point clears it on the way in.  A caller may therefore share one word among all layers of a model and look at it at
  * a natural synchronisation point (end of a model forward).
