@@ -3,18 +3,25 @@
 // scaled_dot_product_attention call behind comfy/ldm/hidream/model.py:75-76 (attention_pytorch,
 // comfy/ldm/modules/attention.py:475-516) for the block's shape: bf16, head_dim 128, no mask, not causal.
 //
-// One CTA computes 128 query rows of one (batch, head) against all keys, 128 keys at a time:
-//   S_j = Q K_j^T            tcgen05.mma, A = Q (shared memory), B = K_j (shared memory), D = S in TMEM (two buffers)
-//   P_j = exp2(c S_j - m)    128 softmax threads, one query row each: the row's 128 scores come out of TMEM into the
-//                            thread's registers, so maximum and sum need no shuffles; P goes back to TMEM as bf16
-//   O  += P_j V_j            tcgen05.mma, A = P_j (TMEM), B = V_j (shared memory, keys along K), D = O in TMEM
+// One CTA computes 256 query rows of one (batch, head), as two tiles a and b of 128 rows, against all keys, 128 keys at
+// a time:
+//   S_t = Q_t K_j^T          tcgen05.mma, A = Q_t (shared memory), B = K_j (shared memory), D = S_t in TMEM
+//   P_t = exp2(c S_t - m)    128 softmax threads per tile, one query row each: the row's 128 scores come out of TMEM into
+//                            the thread's registers, so maximum and sum need no shuffles; P goes back to TMEM as bf16,
+//                            over the scores it was made from
+//   O_t += P_t V_j           tcgen05.mma, A = P_t (TMEM), B = V_j (shared memory, keys along K), D = O_t in TMEM
+// The two tiles share every K / V tile in shared memory and take turns on the tensor pipe: while the softmax threads of
+// tile a work on S_a, the pipe computes S_b, then O_a += P_a V and the next S_a, and so on, so that exponentials (the
+// scarce resource: 16 per clock and SM) and MMAs overlap.  TMEM holds S_a, S_b, O_a, O_b: all 512 columns.
 // The running maximum m is only raised when a row's new maximum exceeds it by more than 8 (in log2 units): P then stays
 // below 2^8, which bf16 and the fp32 accumulators hold without loss, and O (which lives in TMEM and would have to be
 // read, scaled and written back) is rescaled only on those rare tiles; the final division by the row sum makes the
 // result independent of the reference point.
-// Warps: 0-3 softmax and epilogue (TMEM lane quarter = warp index), 4 = MMA issuer and TMEM owner, 5 = TMA producer.
-// Every wait is bounded and reports through the status word like the waits of the grouped GEMM.
+// Warps: 0-3 softmax and epilogue of tile a, 4-7 of tile b (TMEM lane quarter = warp index & 3), 8 = MMA issuer and
+// TMEM owner, 9 = TMA producer.  Every wait is bounded and reports through the status word like the waits of the
+// grouped GEMM.
 #include <cuda.h>
+#include <cstdio>
 
 #include "moe_common.cuh"
 #include "ptx_sm100.cuh"
@@ -22,14 +29,16 @@
 namespace comfy_b200 {
 
 constexpr int kAttnD = 128;                    // head dimension
-constexpr int kAttnM = 128;                    // query rows per CTA
+constexpr int kAttnM = 128;                    // query rows per tile
+constexpr int kAttnQTiles = 2;                 // query tiles per CTA
 constexpr int kAttnN = 128;                    // keys per tile
 constexpr int kAttnStages = 2;                 // K / V stages in flight
 constexpr int kAttnBoxBytes = 128 * 128;       // one TMA box: 128 rows x 64 bf16 (128 bytes, 128-byte swizzle)
 constexpr int kAttnTileBytes = 2 * kAttnBoxBytes;   // a 128 x 128 bf16 tile = two boxes side by side along d
-constexpr int kAttnThreads = 6 * 32;
-constexpr int kAttnTmemCols = 512;             // S0 [0,128) S1 [128,256) O [256,384); P aliases the first 64 columns of S
-constexpr size_t kAttnSmem = kAttnTileBytes * (1 + 2 * kAttnStages) + 1024;
+constexpr int kAttnSoftmaxWarps = 4 * kAttnQTiles;
+constexpr int kAttnThreads = (kAttnSoftmaxWarps + 2) * 32;
+constexpr int kAttnTmemCols = 512;             // S_a [0,128) S_b [128,256) O_a [256,384) O_b [384,512); P over S
+constexpr size_t kAttnSmem = kAttnTileBytes * (kAttnQTiles + 2 * kAttnStages) + 1024;
 constexpr int kStatusAttnTimeout = 5;
 constexpr float kAttnRescaleThreshold = 8.0f;  // log2 units
 
@@ -97,26 +106,84 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
+// Row maximum of the 128 raw scores of one query row (TMEM lane of this thread), eight independent chains.  kMasked:
+// the tile holds only `valid` real keys, the rest count as -inf.
+template <bool kMasked>
+__device__ __forceinline__ float attn_row_max(uint32_t s_tmem, int valid) {
+  float mx8[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) mx8[i] = -INFINITY;
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    uint32_t sr[2][32];
+    tmem_ld_32x32b_x32(s_tmem + half * 64, sr[0]);
+    tmem_ld_32x32b_x32(s_tmem + half * 64 + 32, sr[1]);
+    tmem_ld_wait();
+#pragma unroll
+    for (int c = 0; c < 2; ++c)
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        float v = __uint_as_float(sr[c][i]);
+        if constexpr (kMasked) { if (half * 64 + c * 32 + i >= valid) v = -INFINITY; }
+        mx8[i & 7] = fmaxf(mx8[i & 7], v);
+      }
+  }
+  return fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])), fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
+}
+
+// P = exp2(s * scale - m) for the row: one FFMA and one MUFU per element, packed to bf16 pairs and written over the
+// scores (the first 64 columns of the S buffer); returns the row sum of the unrounded values (four chains).
+template <bool kMasked>
+__device__ __forceinline__ float attn_row_exp(uint32_t s_tmem, float scale_log2, float neg_m, int valid) {
+  float part[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    uint32_t sr[2][32];
+    tmem_ld_32x32b_x32(s_tmem + half * 64, sr[0]);
+    tmem_ld_32x32b_x32(s_tmem + half * 64 + 32, sr[1]);
+    tmem_ld_wait();
+    uint32_t pr[32];                                         // 64 probabilities as bf16 pairs = 32 columns of TMEM
+#pragma unroll
+    for (int c = 0; c < 2; ++c)
+#pragma unroll
+      for (int i = 0; i < 32; i += 2) {
+        float e0 = fast_exp2(fmaf(__uint_as_float(sr[c][i]), scale_log2, neg_m));
+        float e1 = fast_exp2(fmaf(__uint_as_float(sr[c][i + 1]), scale_log2, neg_m));
+        if constexpr (kMasked) {
+          if (half * 64 + c * 32 + i >= valid) e0 = 0.f;
+          if (half * 64 + c * 32 + i + 1 >= valid) e1 = 0.f;
+        }
+        part[(i >> 1) & 3] += e0 + e1;
+        pr[c * 16 + (i >> 1)] = pack_bf16x2(e0, e1);
+      }
+    // columns [0, 32) receive probabilities 0 .. 63, whose scores were read above; the second half's scores sit in
+    // columns [64, 128) and are untouched by either store
+    tmem_st_32x32b_x32(s_tmem + half * 32, pr);
+  }
+  return (part[0] + part[1]) + (part[2] + part[3]);
+}
+
+// (10 warps put three on one SM sub-partition, whose 16384 registers then allow 168 per thread)
 __global__ void __launch_bounds__(kAttnThreads, 1)
 attn_fwd_kernel(const __grid_constant__ AttnParams p) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t q_full;
   __shared__ __align__(8) uint64_t k_full[kAttnStages], k_empty[kAttnStages];
   __shared__ __align__(8) uint64_t v_full[kAttnStages], v_empty[kAttnStages];
-  __shared__ __align__(8) uint64_t s_full[2];
-  __shared__ __align__(8) uint64_t p_ready[2];
-  __shared__ __align__(8) uint64_t o_done;
+  __shared__ __align__(8) uint64_t s_full[kAttnQTiles];
+  __shared__ __align__(8) uint64_t p_ready[kAttnQTiles];
+  __shared__ __align__(8) uint64_t o_done[kAttnQTiles];
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* q_smem = smem;
-  uint8_t* k_smem = smem + kAttnTileBytes;
+  uint8_t* k_smem = smem + kAttnQTiles * kAttnTileBytes;
   uint8_t* v_smem = k_smem + kAttnStages * kAttnTileBytes;
 
-  const int q_tile = blockIdx.x, head = blockIdx.y, batch = blockIdx.z;
-  const int q_row0 = q_tile * kAttnM;
+  const int head = blockIdx.y, batch = blockIdx.z;
+  const int q_row0 = blockIdx.x * (kAttnQTiles * kAttnM);
   const int n_kv = (p.seq_kv + kAttnN - 1) / kAttnN;
   const int col0 = head * kAttnD;              // first element of this head inside a token's H * D row
 
@@ -126,12 +193,11 @@ attn_fwd_kernel(const __grid_constant__ AttnParams p) {
       mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1);
       mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1);
     }
-    for (int b = 0; b < 2; ++b) { mbar_init(&s_full[b], 1); mbar_init(&p_ready[b], 128); }
-    mbar_init(&o_done, 1);
+    for (int t = 0; t < kAttnQTiles; ++t) { mbar_init(&s_full[t], 1); mbar_init(&p_ready[t], 128); mbar_init(&o_done[t], 1); }
     fence_mbar_init();
     abort_flag = 0;
   }
-  if (warp == 4) { tmem_alloc(&tmem_slot, kAttnTmemCols); tmem_relinquish(); }
+  if (warp == kAttnSoftmaxWarps) { tmem_alloc(&tmem_slot, kAttnTmemCols); tmem_relinquish(); }
   __syncwarp();
   tc_fence_before_sync();
   __syncthreads();
@@ -142,12 +208,15 @@ attn_fwd_kernel(const __grid_constant__ AttnParams p) {
     if (lane == 0) { atomicCAS(p.status, 0, kStatusAttnTimeout); abort_flag = 1; }
   };
 
-  if (warp == 5) {
+  if (warp == kAttnSoftmaxWarps + 1) {
     // ------------------------------------------------------------------ TMA producer
     if (elect_one()) {
-      mbar_arrive_expect_tx(&q_full, kAttnTileBytes);
-      tma_load_3d(q_smem, &p.map_q, &q_full, col0, q_row0, batch);
-      tma_load_3d(q_smem + kAttnBoxBytes, &p.map_q, &q_full, col0 + 64, q_row0, batch);
+      mbar_arrive_expect_tx(&q_full, kAttnQTiles * kAttnTileBytes);
+#pragma unroll
+      for (int t = 0; t < kAttnQTiles; ++t) {
+        tma_load_3d(q_smem + t * kAttnTileBytes, &p.map_q, &q_full, col0, q_row0 + t * kAttnM, batch);
+        tma_load_3d(q_smem + t * kAttnTileBytes + kAttnBoxBytes, &p.map_q, &q_full, col0 + 64, q_row0 + t * kAttnM, batch);
+      }
     }
     __syncwarp();
     bool ok = true;
@@ -171,83 +240,85 @@ attn_fwd_kernel(const __grid_constant__ AttnParams p) {
       }
       __syncwarp();
     }
-  } else if (warp == 4) {
+  } else if (warp == kAttnSoftmaxWarps) {
     // ------------------------------------------------------------------ MMA issuer
+    // Order on the tensor pipe: S_a(0) S_b(0) | O_a(0) S_a(1) | O_b(0) S_b(1) | O_a(1) S_a(2) | ...
+    // S_t(j+1) overwrites the columns P_t(j) occupies; it is issued after O_t(j), and the pipe executes in order.
     constexpr uint32_t idesc_qk = umma_idesc<false>(kAttnM, kAttnN);
     constexpr uint32_t idesc_pv = umma_idesc<false>(kAttnM, kAttnD) | (1u << 16);     // B with N contiguous
     bool ok = mbar_wait_warp(&q_full, 0, abort_ptr);
     if (!ok) give_up();
     const uint32_t q_addr = smem_u32(q_smem);
-    const uint32_t tmem_o = tmem_base + 256;
-    for (int j = 0; j <= n_kv && ok; ++j) {
-      if (j < n_kv) {
-        // S_j = Q K_j^T into S buffer j & 1
-        const int s = j % kAttnStages;
-        ok = mbar_wait_warp(&k_full[s], (j / kAttnStages) & 1u, abort_ptr);
-        if (!ok) { give_up(); break; }
+
+    auto issue_qk = [&](int t, int j) -> bool {      // S_t = Q_t K_j^T; the last tile to use K_j frees its stage
+      const int s = j % kAttnStages;
+      if (t == 0) {
+        if (!mbar_wait_warp(&k_full[s], (j / kAttnStages) & 1u, abort_ptr)) return false;
         tc_fence_after_sync();
-        if (elect_one()) {
-          const uint32_t k_addr = smem_u32(k_smem + s * kAttnTileBytes);
-          const uint32_t d_tmem = tmem_base + (j & 1) * 128;
-#pragma unroll
-          for (int kk = 0; kk < kAttnD / 16; ++kk) {
-            const uint32_t off = (kk >> 2) * kAttnBoxBytes + (kk & 3) * 32;     // box, then 32 bytes per 16 elements
-            umma_ss<false>(d_tmem, umma_desc_k_sw128(q_addr + off), umma_desc_k_sw128(k_addr + off), idesc_qk,
-                           kk != 0 ? 1u : 0u);
-          }
-          umma_commit(&s_full[j & 1]);
-          umma_commit(&k_empty[s]);
-        }
-        __syncwarp();
       }
-      if (j >= 1) {
-        // O += P_{j-1} V_{j-1}
-        const int t = j - 1, s = t % kAttnStages;
-        ok = mbar_wait_warp(&p_ready[t & 1], (t >> 1) & 1u, abort_ptr);
-        if (ok) ok = mbar_wait_warp(&v_full[s], (t / kAttnStages) & 1u, abort_ptr);
-        if (!ok) { give_up(); break; }
-        tc_fence_after_sync();
-        if (elect_one()) {
-          const uint32_t v_addr = smem_u32(v_smem + s * kAttnTileBytes);
-          const uint32_t p_tmem = tmem_base + (t & 1) * 128;
+      if (elect_one()) {
+        const uint32_t k_addr = smem_u32(k_smem + s * kAttnTileBytes);
+        const uint32_t d_tmem = tmem_base + t * 128;
 #pragma unroll
-          for (int kk = 0; kk < kAttnN / 16; ++kk) {
-            // 16 keys = two groups of eight rows (2048 bytes); 16 bf16 of P = 8 columns of TMEM
-            umma_ts_bf16(tmem_o, p_tmem + kk * 8, umma_desc_mn_sw128(v_addr + kk * 2048, kAttnBoxBytes), idesc_pv,
-                         (t | kk) != 0 ? 1u : 0u);
-          }
-          umma_commit(&v_empty[s]);
-          umma_commit(&o_done);
+        for (int kk = 0; kk < kAttnD / 16; ++kk) {
+          const uint32_t off = (kk >> 2) * kAttnBoxBytes + (kk & 3) * 32;     // box, then 32 bytes per 16 elements
+          umma_ss<false>(d_tmem, umma_desc_k_sw128(q_addr + t * kAttnTileBytes + off), umma_desc_k_sw128(k_addr + off),
+                         idesc_qk, kk != 0 ? 1u : 0u);
         }
-        __syncwarp();
+        umma_commit(&s_full[t]);
+        if (t == kAttnQTiles - 1) umma_commit(&k_empty[s]);
+      }
+      __syncwarp();
+      return true;
+    };
+    auto issue_pv = [&](int t, int j) -> bool {      // O_t += P_t V_j; the last tile to use V_j frees its stage
+      const int s = j % kAttnStages;
+      if (!mbar_wait_warp(&p_ready[t], j & 1u, abort_ptr)) return false;
+      if (t == 0 && !mbar_wait_warp(&v_full[s], (j / kAttnStages) & 1u, abort_ptr)) return false;
+      tc_fence_after_sync();
+      if (elect_one()) {
+        const uint32_t v_addr = smem_u32(v_smem + s * kAttnTileBytes);
+        const uint32_t p_tmem = tmem_base + t * 128;
+        const uint32_t o_tmem = tmem_base + 256 + t * 128;
+#pragma unroll
+        for (int kk = 0; kk < kAttnN / 16; ++kk) {
+          // 16 keys = two groups of eight rows (2048 bytes); 16 bf16 of P = 8 columns of TMEM
+          umma_ts_bf16(o_tmem, p_tmem + kk * 8, umma_desc_mn_sw128(v_addr + kk * 2048, kAttnBoxBytes), idesc_pv,
+                       (j | kk) != 0 ? 1u : 0u);
+        }
+        umma_commit(&o_done[t]);
+        if (t == kAttnQTiles - 1) umma_commit(&v_empty[s]);
+      }
+      __syncwarp();
+      return true;
+    };
+
+    for (int t = 0; t < kAttnQTiles && ok; ++t) ok = issue_qk(t, 0);
+    for (int j = 0; j < n_kv && ok; ++j) {
+      for (int t = 0; t < kAttnQTiles && ok; ++t) {
+        ok = issue_pv(t, j);
+        if (ok && j + 1 < n_kv) ok = issue_qk(t, j + 1);
       }
     }
+    if (!ok) give_up();
   } else {
     // ------------------------------------------------------------------ softmax + epilogue: one query row per thread
-    const int row = warp * 32 + lane;                    // row inside the tile = TMEM lane
-    const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
-    float m_ref = -INFINITY, l_sum = 0.f;
+    const int t = warp >> 2;                                   // query tile of this warp
+    const int row = (warp & 3) * 32 + lane;                    // row inside the tile = TMEM lane
+    const uint32_t lane_base = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16);
+    const uint32_t s_tmem = lane_base + t * 128;
+    const uint32_t o_tmem = lane_base + 256 + t * 128;
+    float m_ref = -INFINITY, l_sum = 0.f;                      // m_ref in units of the raw score times scale_log2
     bool ok = true;
     for (int j = 0; j < n_kv && ok; ++j) {
-      const uint32_t s_tmem = lane_base + (j & 1) * 128;
-      ok = mbar_wait_warp(&s_full[j & 1], (j >> 1) & 1u, abort_ptr);
+      ok = mbar_wait_warp(&s_full[t], j & 1u, abort_ptr);
       if (!ok) { give_up(); break; }
       tc_fence_after_sync();
-      uint32_t sr[4][32];
-#pragma unroll
-      for (int c = 0; c < 4; ++c) tmem_ld_32x32b_x32(s_tmem + c * 32, sr[c]);
-      tmem_ld_wait();
-      const int valid = p.seq_kv - j * kAttnN;           // keys of this tile that exist
-      float mx = -INFINITY;
-#pragma unroll
-      for (int c = 0; c < 4; ++c)
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float v = __uint_as_float(sr[c][i]) * p.scale_log2;
-          if (valid < kAttnN && c * 32 + i >= valid) v = -INFINITY;
-          sr[c][i] = __float_as_uint(v);
-          mx = fmaxf(mx, v);
-        }
+      // first pass over the row: its maximum; the scores are read from TMEM again for the exponentials, 64 at a time,
+      // which costs next to nothing and keeps 128 registers free.  Only the last tile can hold fewer than 128 keys.
+      const int valid = p.seq_kv - j * kAttnN;
+      const bool partial = valid < kAttnN;
+      const float mx = (partial ? attn_row_max<true>(s_tmem, valid) : attn_row_max<false>(s_tmem, valid)) * p.scale_log2;
       // raise the reference maximum only when some row of this warp needs it (tcgen05.ld / st are warp-wide)
       const bool raise = mx > m_ref + kAttnRescaleThreshold;
       if (__any_sync(0xffffffffu, raise)) {
@@ -255,55 +326,42 @@ attn_fwd_kernel(const __grid_constant__ AttnParams p) {
         const float factor = (m_ref == -INFINITY) ? 0.f : fast_exp2(m_ref - m_new);
         if (j > 0) {
           // O holds the sum over tiles 0 .. j-1 once the last of their MMAs has finished
-          ok = mbar_wait_warp(&o_done, (j - 1) & 1u, abort_ptr);
+          ok = mbar_wait_warp(&o_done[t], (j - 1) & 1u, abort_ptr);
           if (!ok) { give_up(); break; }
           tc_fence_after_sync();
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
             uint32_t o[32];
-            tmem_ld_32x32b_x32(lane_base + 256 + c * 32, o);
+            tmem_ld_32x32b_x32(o_tmem + c * 32, o);
             tmem_ld_wait();
 #pragma unroll
             for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * factor);
-            tmem_st_32x32b_x32(lane_base + 256 + c * 32, o);
+            tmem_st_32x32b_x32(o_tmem + c * 32, o);
           }
           tmem_st_wait();
         }
         l_sum *= factor;
         m_ref = m_new;
       }
-      // P = exp2(s - m_ref), packed to bf16 pairs; the row sum uses the unrounded values
-      uint32_t pr[2][32];
-      float part = 0.f;
-#pragma unroll
-      for (int c = 0; c < 4; ++c)
-#pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          const float e0 = fast_exp2(__uint_as_float(sr[c][i]) - m_ref);
-          const float e1 = fast_exp2(__uint_as_float(sr[c][i + 1]) - m_ref);
-          part += e0 + e1;
-          pr[c >> 1][(c & 1) * 16 + (i >> 1)] = pack_bf16x2(e0, e1);
-        }
-      l_sum += part;
-      tmem_st_32x32b_x32(s_tmem, pr[0]);
-      tmem_st_32x32b_x32(s_tmem + 32, pr[1]);
+      l_sum += partial ? attn_row_exp<true>(s_tmem, p.scale_log2, -m_ref, valid)
+                       : attn_row_exp<false>(s_tmem, p.scale_log2, -m_ref, valid);
       tmem_st_wait();
       tc_fence_before_sync();
-      mbar_arrive(&p_ready[j & 1]);
+      mbar_arrive(&p_ready[t]);
     }
     if (ok) {
-      ok = mbar_wait_warp(&o_done, (n_kv - 1) & 1u, abort_ptr);
+      ok = mbar_wait_warp(&o_done[t], (n_kv - 1) & 1u, abort_ptr);
       if (!ok) give_up();
     }
     if (ok) {
       tc_fence_after_sync();
       const float inv = 1.0f / l_sum;
-      const int q_row = q_row0 + row;
+      const int q_row = q_row0 + t * kAttnM + row;
       __nv_bfloat16* o_row = p.out + (static_cast<size_t>(batch) * p.seq_q + q_row) * (static_cast<size_t>(p.heads) * kAttnD) + col0;
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         uint32_t o[32];
-        tmem_ld_32x32b_x32(lane_base + 256 + c * 32, o);
+        tmem_ld_32x32b_x32(o_tmem + c * 32, o);
         tmem_ld_wait();
         if (q_row < p.seq_q) {
 #pragma unroll
@@ -328,7 +386,7 @@ attn_fwd_kernel(const __grid_constant__ AttnParams p) {
   }
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == 4) {
+  if (warp == kAttnSoftmaxWarps) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, kAttnTmemCols);
   }
@@ -390,12 +448,15 @@ extern "C" int comfy_attn_forward(const void* q, const void* k, const void* v, i
   constexpr int kMaxDevices = 64;
   static bool configured[kMaxDevices] = {false};
   if (dev < 0 || dev >= kMaxDevices || !configured[dev]) {
-    if (cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kAttnSmem)) !=
-        cudaSuccess)
-      return COMFY_MOE_ECUDA;
+    cudaError_t e = cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kAttnSmem));
+    if (e != cudaSuccess) { fprintf(stderr, "attn attr: %s\n", cudaGetErrorString(e)); return COMFY_MOE_ECUDA; }
     if (dev >= 0 && dev < kMaxDevices) configured[dev] = true;
   }
-  dim3 grid((seq_q + kAttnM - 1) / kAttnM, heads, batch);
+  dim3 grid((seq_q + kAttnQTiles * kAttnM - 1) / (kAttnQTiles * kAttnM), heads, batch);
   attn_fwd_kernel<<<grid, kAttnThreads, kAttnSmem, static_cast<cudaStream_t>(stream)>>>(p);
-  return check_launch();
+  {
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) { fprintf(stderr, "attn launch: %s\n", cudaGetErrorString(e)); return COMFY_MOE_ECUDA; }
+  }
+  return COMFY_MOE_OK;
 }
