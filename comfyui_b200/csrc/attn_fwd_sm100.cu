@@ -3,20 +3,23 @@
 // scaled_dot_product_attention call behind comfy/ldm/hidream/model.py:75-76 (attention_pytorch,
 // comfy/ldm/modules/attention.py:475-516) for the block's shape: bf16, head_dim 128, no mask, not causal.
 //
-// One CTA computes 256 query rows of one (batch, head), as two tiles a and b of 128 rows, against all keys, 128 keys at
-// a time:
-//   S_t = Q_t K_j^T          tcgen05.mma, A = Q_t (shared memory), B = K_j (shared memory), D = S_t in TMEM
-//   P_t = exp2(c S_t - m)    128 softmax threads per tile, one query row each: the row's 128 scores come out of TMEM into
+// One CTA computes 256 query rows of one (batch, head), as two tiles a and b of 128 rows, against all keys, 64 keys at a
+// time:
+//   S_t = Q_t K_j^T          tcgen05.mma, A = Q_t (shared memory), B = K_j (shared memory), D = S_t in TMEM, two buffers
+//                            per tile, so that S_t(j+1) is computed while the softmax threads still work on S_t(j)
+//   P_t = exp2(c S_t - m)    128 softmax threads per tile, one query row each: the row's 64 scores come out of TMEM into
 //                            the thread's registers, so maximum and sum need no shuffles; P goes back to TMEM as bf16,
 //                            over the scores it was made from
 //   O_t += P_t V_j           tcgen05.mma, A = P_t (TMEM), B = V_j (shared memory, keys along K), D = O_t in TMEM
-// The two tiles share every K / V tile in shared memory and take turns on the tensor pipe: while the softmax threads of
-// tile a work on S_a, the pipe computes S_b, then O_a += P_a V and the next S_a, and so on, so that exponentials (the
-// scarce resource: 16 per clock and SM) and MMAs overlap.  TMEM holds S_a, S_b, O_a, O_b: all 512 columns.
-// The running maximum m is only raised when a row's new maximum exceeds it by more than 8 (in log2 units): P then stays
-// below 2^8, which bf16 and the fp32 accumulators hold without loss, and O (which lives in TMEM and would have to be
-// read, scaled and written back) is rescaled only on those rare tiles; the final division by the row sum makes the
-// result independent of the reference point.
+// The two tiles share every K / V tile in shared memory and alternate on the tensor pipe, so that exponentials (the
+// scarce resource: 16 per clock and SM) and MMAs overlap.  TMEM: S_a0 S_a1 S_b0 S_b1 (64 columns each), O_a, O_b (128
+// each): all 512 columns.
+// The reference maximum m of a row is only raised when a tile's maximum exceeds it by more than 8 (in log2 units): P
+// then stays below 2^8, which bf16 and the fp32 accumulators hold without loss, and O (which lives in TMEM and would
+// have to be read, scaled and written back) is rescaled only on those rare tiles; the final division by the row sum
+// makes the result independent of the reference point.  So the common case is ONE pass over a tile's scores:
+// exponentials against the current m and the tile's maximum side by side; only when the maximum turns out too large
+// (always on the first tile) is the tile redone after raising m.
 // Warps: 0-3 softmax and epilogue of tile a, 4-7 of tile b (TMEM lane quarter = warp index & 3), 8 = MMA issuer and
 // TMEM owner, 9 = TMA producer.  Every wait is bounded and reports through the status word like the waits of the
 // grouped GEMM.
@@ -31,19 +34,24 @@ namespace comfy_b200 {
 constexpr int kAttnD = 128;                    // head dimension
 constexpr int kAttnM = 128;                    // query rows per tile
 constexpr int kAttnQTiles = 2;                 // query tiles per CTA
-constexpr int kAttnN = 128;                    // keys per tile
-constexpr int kAttnStages = 2;                 // K / V stages in flight
-constexpr int kAttnBoxBytes = 128 * 128;       // one TMA box: 128 rows x 64 bf16 (128 bytes, 128-byte swizzle)
-constexpr int kAttnTileBytes = 2 * kAttnBoxBytes;   // a 128 x 128 bf16 tile = two boxes side by side along d
+constexpr int kAttnN = 64;                     // keys per step
+constexpr int kAttnStages = 4;                 // K / V stages in flight
+constexpr int kAttnQBoxBytes = 128 * 128;      // one TMA box of Q: 128 rows x 64 bf16 (128 bytes, 128-byte swizzle)
+constexpr int kAttnQTileBytes = 2 * kAttnQBoxBytes;
+constexpr int kAttnKvBoxBytes = kAttnN * 128;  // one TMA box of K or V: 64 rows x 64 bf16
+constexpr int kAttnKvTileBytes = 2 * kAttnKvBoxBytes;   // 64 keys x 128 head-dimension elements
 constexpr int kAttnSoftmaxWarps = 4 * kAttnQTiles;
 constexpr int kAttnThreads = (kAttnSoftmaxWarps + 2) * 32;
-constexpr int kAttnTmemCols = 512;             // S_a [0,128) S_b [128,256) O_a [256,384) O_b [384,512); P over S
-constexpr size_t kAttnSmem = kAttnTileBytes * (kAttnQTiles + 2 * kAttnStages) + 1024;
+constexpr int kAttnTmemCols = 512;
+constexpr size_t kAttnSmem = kAttnQTiles * kAttnQTileBytes + 2 * kAttnStages * kAttnKvTileBytes + 1024;
 constexpr int kStatusAttnTimeout = 5;
 constexpr float kAttnRescaleThreshold = 8.0f;  // log2 units
 
+__host__ __device__ constexpr uint32_t attn_s_col(int tile, int buffer) { return tile * 128 + buffer * 64; }
+__host__ __device__ constexpr uint32_t attn_o_col(int tile) { return 256 + tile * 128; }
+
 struct AttnParams {
-  CUtensorMap map_q, map_k, map_v;             // [B][S][H * D] bf16, boxes of 128 rows x 64 elements
+  CUtensorMap map_q, map_k, map_v;             // [B][S][H * D] bf16; boxes of 128 (Q) or 64 (K, V) rows x 64 elements
   __nv_bfloat16* out;                          // [B, S_q, H * D]
   int32_t* status;
   int seq_q, seq_kv, heads;
@@ -106,61 +114,36 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
-// Row maximum of the 128 raw scores of one query row (TMEM lane of this thread), eight independent chains.  kMasked:
-// the tile holds only `valid` real keys, the rest count as -inf.
+// One softmax step of one query row (this thread's TMEM lane): the 64 scores of the step against the reference
+// maximum.  p = exp2(s * scale - m): one FFMA and one MUFU per element; the probabilities come back as 32 bf16 pairs,
+// their unrounded sum in `sum`, the largest raw score in `raw_max` (four independent chains each).  kMasked: only the
+// first `valid` keys of the step exist.
 template <bool kMasked>
-__device__ __forceinline__ float attn_row_max(uint32_t s_tmem, int valid) {
-  float mx8[8];
-#pragma unroll
-  for (int i = 0; i < 8; ++i) mx8[i] = -INFINITY;
-#pragma unroll
-  for (int half = 0; half < 2; ++half) {
-    uint32_t sr[2][32];
-    tmem_ld_32x32b_x32(s_tmem + half * 64, sr[0]);
-    tmem_ld_32x32b_x32(s_tmem + half * 64 + 32, sr[1]);
-    tmem_ld_wait();
-#pragma unroll
-    for (int c = 0; c < 2; ++c)
-#pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        float v = __uint_as_float(sr[c][i]);
-        if constexpr (kMasked) { if (half * 64 + c * 32 + i >= valid) v = -INFINITY; }
-        mx8[i & 7] = fmaxf(mx8[i & 7], v);
-      }
-  }
-  return fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])), fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
-}
-
-// P = exp2(s * scale - m) for the row: one FFMA and one MUFU per element, packed to bf16 pairs and written over the
-// scores (the first 64 columns of the S buffer); returns the row sum of the unrounded values (four chains).
-template <bool kMasked>
-__device__ __forceinline__ float attn_row_exp(uint32_t s_tmem, float scale_log2, float neg_m, int valid) {
+__device__ __forceinline__ void attn_softmax_step(uint32_t s_tmem, float scale_log2, float neg_m, int valid,
+                                                  uint32_t (&pr)[32], float& sum, float& raw_max) {
+  uint32_t sr[2][32];
+  tmem_ld_32x32b_x32(s_tmem, sr[0]);
+  tmem_ld_32x32b_x32(s_tmem + 32, sr[1]);
+  tmem_ld_wait();
   float part[4] = {0.f, 0.f, 0.f, 0.f};
+  float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-  for (int half = 0; half < 2; ++half) {
-    uint32_t sr[2][32];
-    tmem_ld_32x32b_x32(s_tmem + half * 64, sr[0]);
-    tmem_ld_32x32b_x32(s_tmem + half * 64 + 32, sr[1]);
-    tmem_ld_wait();
-    uint32_t pr[32];                                         // 64 probabilities as bf16 pairs = 32 columns of TMEM
+  for (int c = 0; c < 2; ++c)
 #pragma unroll
-    for (int c = 0; c < 2; ++c)
-#pragma unroll
-      for (int i = 0; i < 32; i += 2) {
-        float e0 = fast_exp2(fmaf(__uint_as_float(sr[c][i]), scale_log2, neg_m));
-        float e1 = fast_exp2(fmaf(__uint_as_float(sr[c][i + 1]), scale_log2, neg_m));
-        if constexpr (kMasked) {
-          if (half * 64 + c * 32 + i >= valid) e0 = 0.f;
-          if (half * 64 + c * 32 + i + 1 >= valid) e1 = 0.f;
-        }
-        part[(i >> 1) & 3] += e0 + e1;
-        pr[c * 16 + (i >> 1)] = pack_bf16x2(e0, e1);
+    for (int i = 0; i < 32; i += 2) {
+      float s0 = __uint_as_float(sr[c][i]), s1 = __uint_as_float(sr[c][i + 1]);
+      if constexpr (kMasked) {
+        if (c * 32 + i >= valid) s0 = -INFINITY;
+        if (c * 32 + i + 1 >= valid) s1 = -INFINITY;
       }
-    // columns [0, 32) receive probabilities 0 .. 63, whose scores were read above; the second half's scores sit in
-    // columns [64, 128) and are untouched by either store
-    tmem_st_32x32b_x32(s_tmem + half * 32, pr);
-  }
-  return (part[0] + part[1]) + (part[2] + part[3]);
+      mx[(i >> 1) & 3] = fmaxf(mx[(i >> 1) & 3], fmaxf(s0, s1));
+      const float e0 = fast_exp2(fmaf(s0, scale_log2, neg_m));
+      const float e1 = fast_exp2(fmaf(s1, scale_log2, neg_m));
+      part[(i >> 1) & 3] += e0 + e1;
+      pr[c * 16 + (i >> 1)] = pack_bf16x2(e0, e1);
+    }
+  sum = (part[0] + part[1]) + (part[2] + part[3]);
+  raw_max = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
 }
 
 // (10 warps put three on one SM sub-partition, whose 16384 registers then allow 168 per thread)
@@ -170,17 +153,17 @@ attn_fwd_kernel(const __grid_constant__ AttnParams p) {
   __shared__ __align__(8) uint64_t q_full;
   __shared__ __align__(8) uint64_t k_full[kAttnStages], k_empty[kAttnStages];
   __shared__ __align__(8) uint64_t v_full[kAttnStages], v_empty[kAttnStages];
-  __shared__ __align__(8) uint64_t s_full[kAttnQTiles];
-  __shared__ __align__(8) uint64_t p_ready[kAttnQTiles];
-  __shared__ __align__(8) uint64_t o_done[kAttnQTiles];
+  __shared__ __align__(8) uint64_t s_full[kAttnQTiles][2];
+  __shared__ __align__(8) uint64_t p_ready[kAttnQTiles][2];
+  __shared__ __align__(8) uint64_t o_done[kAttnQTiles][2];     // by step parity, like the S buffers
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* q_smem = smem;
-  uint8_t* k_smem = smem + kAttnQTiles * kAttnTileBytes;
-  uint8_t* v_smem = k_smem + kAttnStages * kAttnTileBytes;
+  uint8_t* k_smem = smem + kAttnQTiles * kAttnQTileBytes;
+  uint8_t* v_smem = k_smem + kAttnStages * kAttnKvTileBytes;
 
   const int head = blockIdx.y, batch = blockIdx.z;
   const int q_row0 = blockIdx.x * (kAttnQTiles * kAttnM);
@@ -193,7 +176,9 @@ attn_fwd_kernel(const __grid_constant__ AttnParams p) {
       mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1);
       mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1);
     }
-    for (int t = 0; t < kAttnQTiles; ++t) { mbar_init(&s_full[t], 1); mbar_init(&p_ready[t], 128); mbar_init(&o_done[t], 1); }
+    for (int t = 0; t < kAttnQTiles; ++t) {
+      for (int b = 0; b < 2; ++b) { mbar_init(&s_full[t][b], 1); mbar_init(&p_ready[t][b], 128); mbar_init(&o_done[t][b], 1); }
+    }
     fence_mbar_init();
     abort_flag = 0;
   }
@@ -211,11 +196,11 @@ attn_fwd_kernel(const __grid_constant__ AttnParams p) {
   if (warp == kAttnSoftmaxWarps + 1) {
     // ------------------------------------------------------------------ TMA producer
     if (elect_one()) {
-      mbar_arrive_expect_tx(&q_full, kAttnQTiles * kAttnTileBytes);
+      mbar_arrive_expect_tx(&q_full, kAttnQTiles * kAttnQTileBytes);
 #pragma unroll
       for (int t = 0; t < kAttnQTiles; ++t) {
-        tma_load_3d(q_smem + t * kAttnTileBytes, &p.map_q, &q_full, col0, q_row0 + t * kAttnM, batch);
-        tma_load_3d(q_smem + t * kAttnTileBytes + kAttnBoxBytes, &p.map_q, &q_full, col0 + 64, q_row0 + t * kAttnM, batch);
+        tma_load_3d(q_smem + t * kAttnQTileBytes, &p.map_q, &q_full, col0, q_row0 + t * kAttnM, batch);
+        tma_load_3d(q_smem + t * kAttnQTileBytes + kAttnQBoxBytes, &p.map_q, &q_full, col0 + 64, q_row0 + t * kAttnM, batch);
       }
     }
     __syncwarp();
@@ -226,78 +211,87 @@ attn_fwd_kernel(const __grid_constant__ AttnParams p) {
       ok = mbar_wait_warp(&k_empty[s], ph ^ 1u, abort_ptr);
       if (!ok) { give_up(); break; }
       if (elect_one()) {
-        mbar_arrive_expect_tx(&k_full[s], kAttnTileBytes);
-        tma_load_3d(k_smem + s * kAttnTileBytes, &p.map_k, &k_full[s], col0, j * kAttnN, batch);
-        tma_load_3d(k_smem + s * kAttnTileBytes + kAttnBoxBytes, &p.map_k, &k_full[s], col0 + 64, j * kAttnN, batch);
+        mbar_arrive_expect_tx(&k_full[s], kAttnKvTileBytes);
+        tma_load_3d(k_smem + s * kAttnKvTileBytes, &p.map_k, &k_full[s], col0, j * kAttnN, batch);
+        tma_load_3d(k_smem + s * kAttnKvTileBytes + kAttnKvBoxBytes, &p.map_k, &k_full[s], col0 + 64, j * kAttnN, batch);
       }
       __syncwarp();
       ok = mbar_wait_warp(&v_empty[s], ph ^ 1u, abort_ptr);
       if (!ok) { give_up(); break; }
       if (elect_one()) {
-        mbar_arrive_expect_tx(&v_full[s], kAttnTileBytes);
-        tma_load_3d(v_smem + s * kAttnTileBytes, &p.map_v, &v_full[s], col0, j * kAttnN, batch);
-        tma_load_3d(v_smem + s * kAttnTileBytes + kAttnBoxBytes, &p.map_v, &v_full[s], col0 + 64, j * kAttnN, batch);
+        mbar_arrive_expect_tx(&v_full[s], kAttnKvTileBytes);
+        tma_load_3d(v_smem + s * kAttnKvTileBytes, &p.map_v, &v_full[s], col0, j * kAttnN, batch);
+        tma_load_3d(v_smem + s * kAttnKvTileBytes + kAttnKvBoxBytes, &p.map_v, &v_full[s], col0 + 64, j * kAttnN, batch);
       }
       __syncwarp();
     }
   } else if (warp == kAttnSoftmaxWarps) {
     // ------------------------------------------------------------------ MMA issuer
-    // Order on the tensor pipe: S_a(0) S_b(0) | O_a(0) S_a(1) | O_b(0) S_b(1) | O_a(1) S_a(2) | ...
-    // S_t(j+1) overwrites the columns P_t(j) occupies; it is issued after O_t(j), and the pipe executes in order.
+    // Order on the tensor pipe: S_a(0) S_b(0) S_a(1) S_b(1) | O_a(0) S_a(2) O_b(0) S_b(2) | O_a(1) S_a(3) ...
+    // S_t(j+2) overwrites the buffer whose first columns hold P_t(j); it is issued after O_t(j), and the pipe executes
+    // in order.
     constexpr uint32_t idesc_qk = umma_idesc<false>(kAttnM, kAttnN);
-    constexpr uint32_t idesc_pv = umma_idesc<false>(kAttnM, kAttnD) | (1u << 16);     // B with N contiguous
+    // O_t += P V is issued as two halves of 64 output columns (one V box each), so that every MMA of the kernel has the
+    // same shape 128 x 64 x 16: the tensor pipe keeps MMAs of one shape issued by one thread in order, which the reuse
+    // of the S / P columns relies on
+    constexpr uint32_t idesc_pv = umma_idesc<false>(kAttnM, kAttnD / 2) | (1u << 16);     // B with N contiguous
     bool ok = mbar_wait_warp(&q_full, 0, abort_ptr);
-    if (!ok) give_up();
     const uint32_t q_addr = smem_u32(q_smem);
 
-    auto issue_qk = [&](int t, int j) -> bool {      // S_t = Q_t K_j^T; the last tile to use K_j frees its stage
+    auto issue_qk = [&](int t, int j) -> bool {      // S_t(j) = Q_t K_j^T; the last tile to use K_j frees its stage
       const int s = j % kAttnStages;
       if (t == 0) {
         if (!mbar_wait_warp(&k_full[s], (j / kAttnStages) & 1u, abort_ptr)) return false;
         tc_fence_after_sync();
       }
       if (elect_one()) {
-        const uint32_t k_addr = smem_u32(k_smem + s * kAttnTileBytes);
-        const uint32_t d_tmem = tmem_base + t * 128;
+        const uint32_t k_addr = smem_u32(k_smem + s * kAttnKvTileBytes);
+        const uint32_t d_tmem = tmem_base + attn_s_col(t, j & 1);
 #pragma unroll
         for (int kk = 0; kk < kAttnD / 16; ++kk) {
-          const uint32_t off = (kk >> 2) * kAttnBoxBytes + (kk & 3) * 32;     // box, then 32 bytes per 16 elements
-          umma_ss<false>(d_tmem, umma_desc_k_sw128(q_addr + t * kAttnTileBytes + off), umma_desc_k_sw128(k_addr + off),
-                         idesc_qk, kk != 0 ? 1u : 0u);
+          // 16 elements of the head dimension = 32 bytes inside a box; the second 64 elements live in the second box
+          umma_ss<false>(d_tmem,
+                         umma_desc_k_sw128(q_addr + t * kAttnQTileBytes + (kk >> 2) * kAttnQBoxBytes + (kk & 3) * 32),
+                         umma_desc_k_sw128(k_addr + (kk >> 2) * kAttnKvBoxBytes + (kk & 3) * 32), idesc_qk,
+                         kk != 0 ? 1u : 0u);
         }
-        umma_commit(&s_full[t]);
+        umma_commit(&s_full[t][j & 1]);
         if (t == kAttnQTiles - 1) umma_commit(&k_empty[s]);
       }
       __syncwarp();
       return true;
     };
-    auto issue_pv = [&](int t, int j) -> bool {      // O_t += P_t V_j; the last tile to use V_j frees its stage
+    auto issue_pv = [&](int t, int j) -> bool {      // O_t += P_t(j) V_j; the last tile to use V_j frees its stage
       const int s = j % kAttnStages;
-      if (!mbar_wait_warp(&p_ready[t], j & 1u, abort_ptr)) return false;
+      if (!mbar_wait_warp(&p_ready[t][j & 1], (j >> 1) & 1u, abort_ptr)) return false;
       if (t == 0 && !mbar_wait_warp(&v_full[s], (j / kAttnStages) & 1u, abort_ptr)) return false;
       tc_fence_after_sync();
       if (elect_one()) {
-        const uint32_t v_addr = smem_u32(v_smem + s * kAttnTileBytes);
-        const uint32_t p_tmem = tmem_base + t * 128;
-        const uint32_t o_tmem = tmem_base + 256 + t * 128;
+        const uint32_t v_addr = smem_u32(v_smem + s * kAttnKvTileBytes);
+        const uint32_t p_tmem = tmem_base + attn_s_col(t, j & 1);
+        const uint32_t o_tmem = tmem_base + attn_o_col(t);
 #pragma unroll
         for (int kk = 0; kk < kAttnN / 16; ++kk) {
           // 16 keys = two groups of eight rows (2048 bytes); 16 bf16 of P = 8 columns of TMEM
-          umma_ts_bf16(o_tmem, p_tmem + kk * 8, umma_desc_mn_sw128(v_addr + kk * 2048, kAttnBoxBytes), idesc_pv,
-                       (j | kk) != 0 ? 1u : 0u);
+#pragma unroll
+          for (int half = 0; half < 2; ++half)
+            umma_ts_bf16(o_tmem + half * 64, p_tmem + kk * 8,
+                         umma_desc_mn_sw128(v_addr + half * kAttnKvBoxBytes + kk * 2048, kAttnKvBoxBytes), idesc_pv,
+                         (j | kk) != 0 ? 1u : 0u);
         }
-        umma_commit(&o_done[t]);
+        umma_commit(&o_done[t][j & 1]);
         if (t == kAttnQTiles - 1) umma_commit(&v_empty[s]);
       }
       __syncwarp();
       return true;
     };
 
-    for (int t = 0; t < kAttnQTiles && ok; ++t) ok = issue_qk(t, 0);
+    for (int j = 0; j < 2 && j < n_kv && ok; ++j)
+      for (int t = 0; t < kAttnQTiles && ok; ++t) ok = issue_qk(t, j);
     for (int j = 0; j < n_kv && ok; ++j) {
       for (int t = 0; t < kAttnQTiles && ok; ++t) {
         ok = issue_pv(t, j);
-        if (ok && j + 1 < n_kv) ok = issue_qk(t, j + 1);
+        if (ok && j + 2 < n_kv) ok = issue_qk(t, j + 2);
       }
     }
     if (!ok) give_up();
@@ -306,27 +300,32 @@ attn_fwd_kernel(const __grid_constant__ AttnParams p) {
     const int t = warp >> 2;                                   // query tile of this warp
     const int row = (warp & 3) * 32 + lane;                    // row inside the tile = TMEM lane
     const uint32_t lane_base = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16);
-    const uint32_t s_tmem = lane_base + t * 128;
-    const uint32_t o_tmem = lane_base + 256 + t * 128;
-    float m_ref = -INFINITY, l_sum = 0.f;                      // m_ref in units of the raw score times scale_log2
+    const uint32_t o_tmem = lane_base + attn_o_col(t);
+    float m_ref = -INFINITY, l_sum = 0.f;                      // m_ref in units of score times scale_log2
     bool ok = true;
     for (int j = 0; j < n_kv && ok; ++j) {
-      ok = mbar_wait_warp(&s_full[t], j & 1u, abort_ptr);
+      const uint32_t s_tmem = lane_base + attn_s_col(t, j & 1);
+      ok = mbar_wait_warp(&s_full[t][j & 1], (j >> 1) & 1u, abort_ptr);
       if (!ok) { give_up(); break; }
       tc_fence_after_sync();
-      // first pass over the row: its maximum; the scores are read from TMEM again for the exponentials, 64 at a time,
-      // which costs next to nothing and keeps 128 registers free.  Only the last tile can hold fewer than 128 keys.
-      const int valid = p.seq_kv - j * kAttnN;
+      const int valid = p.seq_kv - j * kAttnN;                 // only the last step can hold fewer than 64 keys
       const bool partial = valid < kAttnN;
-      const float mx = (partial ? attn_row_max<true>(s_tmem, valid) : attn_row_max<false>(s_tmem, valid)) * p.scale_log2;
-      // raise the reference maximum only when some row of this warp needs it (tcgen05.ld / st are warp-wide)
+      uint32_t pr[32];
+      float sum, raw_max;
+      if (partial) attn_softmax_step<true>(s_tmem, p.scale_log2, -m_ref, valid, pr, sum, raw_max);
+      else attn_softmax_step<false>(s_tmem, p.scale_log2, -m_ref, valid, pr, sum, raw_max);
+      // the probabilities above are good unless some row's maximum lies more than the threshold above its reference
+      // (always so on the first step); tcgen05.ld / st are warp-wide, so the warp decides together
+      const float mx = raw_max * p.scale_log2;
       const bool raise = mx > m_ref + kAttnRescaleThreshold;
       if (__any_sync(0xffffffffu, raise)) {
         const float m_new = raise ? mx : m_ref;
         const float factor = (m_ref == -INFINITY) ? 0.f : fast_exp2(m_ref - m_new);
         if (j > 0) {
-          // O holds the sum over tiles 0 .. j-1 once the last of their MMAs has finished
-          ok = mbar_wait_warp(&o_done[t], (j - 1) & 1u, abort_ptr);
+          // O holds the sum over steps 0 .. j-1 once the MMAs of step j-1 have finished.  (One barrier per step parity:
+          // a parity wait is only sound while the waiter is less than two phases behind, and the softmax runs up to two
+          // steps ahead of the O MMAs; step j-3's were finished before S(j-1) was handed over.)
+          ok = mbar_wait_warp(&o_done[t][(j - 1) & 1], ((j - 1) >> 1) & 1u, abort_ptr);
           if (!ok) { give_up(); break; }
           tc_fence_after_sync();
 #pragma unroll
@@ -342,15 +341,18 @@ attn_fwd_kernel(const __grid_constant__ AttnParams p) {
         }
         l_sum *= factor;
         m_ref = m_new;
+        // the scores are still in TMEM: redo the step against the new reference
+        if (partial) attn_softmax_step<true>(s_tmem, p.scale_log2, -m_ref, valid, pr, sum, raw_max);
+        else attn_softmax_step<false>(s_tmem, p.scale_log2, -m_ref, valid, pr, sum, raw_max);
       }
-      l_sum += partial ? attn_row_exp<true>(s_tmem, p.scale_log2, -m_ref, valid)
-                       : attn_row_exp<false>(s_tmem, p.scale_log2, -m_ref, valid);
+      l_sum += sum;
+      tmem_st_32x32b_x32(s_tmem, pr);                          // P over the first 32 columns of the scores it came from
       tmem_st_wait();
       tc_fence_before_sync();
-      mbar_arrive(&p_ready[t]);
+      mbar_arrive(&p_ready[t][j & 1]);
     }
     if (ok) {
-      ok = mbar_wait_warp(&o_done[t], (n_kv - 1) & 1u, abort_ptr);
+      ok = mbar_wait_warp(&o_done[t][(n_kv - 1) & 1], ((n_kv - 1) >> 1) & 1u, abort_ptr);
       if (!ok) give_up();
     }
     if (ok) {
@@ -396,8 +398,8 @@ typedef CUresult (*EncodeTiledFn3)(CUtensorMap*, CUtensorMapDataType, cuuint32_t
                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
-// [B][S][H * D] bf16, contiguous; boxes of 128 rows x 64 elements, 128-byte swizzle, rows past S read as zero.
-static int make_attn_map(CUtensorMap* map, const void* base, int64_t batch, int64_t seq, int64_t row_elems) {
+// [B][S][H * D] bf16, contiguous; boxes of box_rows rows x 64 elements, 128-byte swizzle, rows past S read as zero.
+static int make_attn_map(CUtensorMap* map, const void* base, int64_t batch, int64_t seq, int64_t row_elems, int box_rows) {
   static EncodeTiledFn3 encode = nullptr;
   if (!encode) {
     void* ptr = nullptr;
@@ -410,7 +412,7 @@ static int make_attn_map(CUtensorMap* map, const void* base, int64_t batch, int6
   if (!base || !aligned16(base)) return COMFY_MOE_EINVAL;
   cuuint64_t dims[3] = {static_cast<cuuint64_t>(row_elems), static_cast<cuuint64_t>(seq), static_cast<cuuint64_t>(batch)};
   cuuint64_t strides[2] = {static_cast<cuuint64_t>(row_elems) * 2, static_cast<cuuint64_t>(row_elems) * seq * 2};
-  cuuint32_t box[3] = {64u, 128u, 1u};
+  cuuint32_t box[3] = {64u, static_cast<cuuint32_t>(box_rows), 1u};
   cuuint32_t estr[3] = {1u, 1u, 1u};
   CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -438,9 +440,9 @@ extern "C" int comfy_attn_forward(const void* q, const void* k, const void* v, i
   memset(&p, 0, sizeof(p));
   const int64_t row = static_cast<int64_t>(heads) * kAttnD;
   int rc;
-  if ((rc = make_attn_map(&p.map_q, q, batch, seq_q, row)) != COMFY_MOE_OK) return rc;
-  if ((rc = make_attn_map(&p.map_k, k, batch, seq_kv, row)) != COMFY_MOE_OK) return rc;
-  if ((rc = make_attn_map(&p.map_v, v, batch, seq_kv, row)) != COMFY_MOE_OK) return rc;
+  if ((rc = make_attn_map(&p.map_q, q, batch, seq_q, row, kAttnM)) != COMFY_MOE_OK) return rc;
+  if ((rc = make_attn_map(&p.map_k, k, batch, seq_kv, row, kAttnN)) != COMFY_MOE_OK) return rc;
+  if ((rc = make_attn_map(&p.map_v, v, batch, seq_kv, row, kAttnN)) != COMFY_MOE_OK) return rc;
   p.out = static_cast<__nv_bfloat16*>(out);
   p.status = status;
   p.seq_q = seq_q; p.seq_kv = seq_kv; p.heads = heads;
