@@ -3,23 +3,23 @@
 // scaled_dot_product_attention call behind comfy/ldm/hidream/model.py:75-76 (attention_pytorch,
 // comfy/ldm/modules/attention.py:475-516) for the block's shape: bf16, head_dim 128, no mask, not causal.
 //
-// One CTA computes 256 query rows of one (batch, head), as two tiles a and b of 128 rows, against all keys, 64 keys at a
-// time:
-//   S_t = Q_t K_j^T          tcgen05.mma, A = Q_t (shared memory), B = K_j (shared memory), D = S_t in TMEM, two buffers
-//                            per tile, so that S_t(j+1) is computed while the softmax threads still work on S_t(j)
-//   P_t = exp2(c S_t - m)    128 softmax threads per tile, one query row each: the row's 64 scores come out of TMEM into
+// One CTA computes 256 query rows of one (batch, head), as two tiles a and b of 128 rows, against all keys, 128 keys at
+// a time:
+//   S_t = Q_t K_j^T          tcgen05.mma, A = Q_t (shared memory), B = K_j (shared memory), D = S_t in TMEM
+//   P_t = exp2(c S_t - m)    128 softmax threads per tile, one query row each: the row's scores come out of TMEM into
 //                            the thread's registers, so maximum and sum need no shuffles; P goes back to TMEM as bf16,
 //                            over the scores it was made from
 //   O_t += P_t V_j           tcgen05.mma, A = P_t (TMEM), B = V_j (shared memory, keys along K), D = O_t in TMEM
-// The two tiles share every K / V tile in shared memory and alternate on the tensor pipe, so that exponentials (the
-// scarce resource: 16 per clock and SM) and MMAs overlap.  TMEM: S_a0 S_a1 S_b0 S_b1 (64 columns each), O_a, O_b (128
-// each): all 512 columns.
-// The reference maximum m of a row is only raised when a tile's maximum exceeds it by more than 8 (in log2 units): P
+// The two tiles share every K / V tile in shared memory and alternate on the tensor pipe: while the softmax threads of
+// tile a work on S_a, the pipe runs O_b += P_b V and the next S_b, and the other way round, so that exponentials (the
+// scarce resource: 16 per clock and SM) and MMAs overlap.  TMEM holds S_a, S_b, O_a, O_b: all 512 columns.  (Steps of
+// 64 keys with two S buffers per tile were tried: MMAs with N = 64 ran at half the rate, 0.58 ms against 0.40 ms.)
+// The reference maximum m of a row is only raised when a step's maximum exceeds it by more than 8 (in log2 units): P
 // then stays below 2^8, which bf16 and the fp32 accumulators hold without loss, and O (which lives in TMEM and would
-// have to be read, scaled and written back) is rescaled only on those rare tiles; the final division by the row sum
-// makes the result independent of the reference point.  So the common case is ONE pass over a tile's scores:
-// exponentials against the current m and the tile's maximum side by side; only when the maximum turns out too large
-// (always on the first tile) is the tile redone after raising m.
+// have to be read, scaled and written back) is rescaled only on those rare steps; the final division by the row sum
+// makes the result independent of the reference point.  So the common case is ONE pass over a step's scores, 32 at a
+// time with the next 32 already on their way out of TMEM: exponentials against the current m and the step's maximum
+// side by side; only when the maximum turns out too large (always on the first step) is the step redone after raising m.
 // Warps: 0-3 softmax and epilogue of tile a, 4-7 of tile b (TMEM lane quarter = warp index & 3), 8 = MMA issuer and
 // TMEM owner, 9 = TMA producer.  Every wait is bounded and reports through the status word like the waits of the
 // grouped GEMM.
@@ -34,12 +34,12 @@ namespace comfy_b200 {
 constexpr int kAttnD = 128;                    // head dimension
 constexpr int kAttnM = 128;                    // query rows per tile
 constexpr int kAttnQTiles = 2;                 // query tiles per CTA
-constexpr int kAttnN = 64;                     // keys per step
-constexpr int kAttnStages = 4;                 // K / V stages in flight
+constexpr int kAttnN = 128;                    // keys per step
+constexpr int kAttnStages = 2;                 // K / V stages in flight
 constexpr int kAttnQBoxBytes = 128 * 128;      // one TMA box of Q: 128 rows x 64 bf16 (128 bytes, 128-byte swizzle)
 constexpr int kAttnQTileBytes = 2 * kAttnQBoxBytes;
-constexpr int kAttnKvBoxBytes = kAttnN * 128;  // one TMA box of K or V: 64 rows x 64 bf16
-constexpr int kAttnKvTileBytes = 2 * kAttnKvBoxBytes;   // 64 keys x 128 head-dimension elements
+constexpr int kAttnKvBoxBytes = kAttnN * 128;  // one TMA box of K or V: 128 rows x 64 bf16
+constexpr int kAttnKvTileBytes = 2 * kAttnKvBoxBytes;   // 128 keys x 128 head-dimension elements
 constexpr int kAttnSoftmaxWarps = 4 * kAttnQTiles;
 constexpr int kAttnThreads = (kAttnSoftmaxWarps + 2) * 32;
 constexpr int kAttnTmemCols = 512;
@@ -47,11 +47,11 @@ constexpr size_t kAttnSmem = kAttnQTiles * kAttnQTileBytes + 2 * kAttnStages * k
 constexpr int kStatusAttnTimeout = 5;
 constexpr float kAttnRescaleThreshold = 8.0f;  // log2 units
 
-__host__ __device__ constexpr uint32_t attn_s_col(int tile, int buffer) { return tile * 128 + buffer * 64; }
+__host__ __device__ constexpr uint32_t attn_s_col(int tile) { return tile * 128; }
 __host__ __device__ constexpr uint32_t attn_o_col(int tile) { return 256 + tile * 128; }
 
 struct AttnParams {
-  CUtensorMap map_q, map_k, map_v;             // [B][S][H * D] bf16; boxes of 128 (Q) or 64 (K, V) rows x 64 elements
+  CUtensorMap map_q, map_k, map_v;             // [B][S][H * D] bf16; boxes of 128 rows x 64 elements
   __nv_bfloat16* out;                          // [B, S_q, H * D]
   int32_t* status;
   int seq_q, seq_kv, heads;
@@ -109,29 +109,34 @@ __device__ __forceinline__ void tmem_st_32x32b_x32(uint32_t taddr, const uint32_
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 __device__ __forceinline__ float fast_exp2(float x) {
+#ifdef COMFY_ATTN_EXPERIMENT_NO_MUFU
+  return x * 0.001f + 1.0f;          // timing experiment only: wrong numbers, no special-function unit
+#else
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+#endif
 }
 
-// One softmax step of one query row (this thread's TMEM lane): the 64 scores of the step against the reference
-// maximum.  p = exp2(s * scale - m): one FFMA and one MUFU per element; the probabilities come back as 32 bf16 pairs,
-// their unrounded sum in `sum`, the largest raw score in `raw_max` (four independent chains each).  kMasked: only the
-// first `valid` keys of the step exist.
+// One softmax step of one query row (this thread's TMEM lane): the 128 scores of the step against the reference
+// maximum.  p = exp2(s * scale - m): one FFMA and one MUFU per element.  The scores leave TMEM 32 at a time, the next 32
+// requested before the current ones are worked on; the probabilities come back as 64 bf16 pairs, their unrounded sum
+// in `sum`, the largest raw score in `raw_max` (four independent chains each).  kMasked: only the first `valid` keys
+// of the step exist.
 template <bool kMasked>
 __device__ __forceinline__ void attn_softmax_step(uint32_t s_tmem, float scale_log2, float neg_m, int valid,
-                                                  uint32_t (&pr)[32], float& sum, float& raw_max) {
-  uint32_t sr[2][32];
-  tmem_ld_32x32b_x32(s_tmem, sr[0]);
-  tmem_ld_32x32b_x32(s_tmem + 32, sr[1]);
-  tmem_ld_wait();
+                                                  uint32_t (&pr)[64], float& sum, float& raw_max) {
   float part[4] = {0.f, 0.f, 0.f, 0.f};
   float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+  uint32_t sr[2][32];
+  tmem_ld_32x32b_x32(s_tmem, sr[0]);
 #pragma unroll
-  for (int c = 0; c < 2; ++c)
+  for (int c = 0; c < 4; ++c) {
+    tmem_ld_wait();                                          // chunk c is in sr[c & 1]
+    if (c + 1 < 4) tmem_ld_32x32b_x32(s_tmem + (c + 1) * 32, sr[(c + 1) & 1]);
 #pragma unroll
     for (int i = 0; i < 32; i += 2) {
-      float s0 = __uint_as_float(sr[c][i]), s1 = __uint_as_float(sr[c][i + 1]);
+      float s0 = __uint_as_float(sr[c & 1][i]), s1 = __uint_as_float(sr[c & 1][i + 1]);
       if constexpr (kMasked) {
         if (c * 32 + i >= valid) s0 = -INFINITY;
         if (c * 32 + i + 1 >= valid) s1 = -INFINITY;
@@ -142,6 +147,7 @@ __device__ __forceinline__ void attn_softmax_step(uint32_t s_tmem, float scale_l
       part[(i >> 1) & 3] += e0 + e1;
       pr[c * 16 + (i >> 1)] = pack_bf16x2(e0, e1);
     }
+  }
   sum = (part[0] + part[1]) + (part[2] + part[3]);
   raw_max = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
 }
@@ -153,8 +159,8 @@ attn_fwd_kernel(const __grid_constant__ AttnParams p) {
   __shared__ __align__(8) uint64_t q_full;
   __shared__ __align__(8) uint64_t k_full[kAttnStages], k_empty[kAttnStages];
   __shared__ __align__(8) uint64_t v_full[kAttnStages], v_empty[kAttnStages];
-  __shared__ __align__(8) uint64_t s_full[kAttnQTiles][2];
-  __shared__ __align__(8) uint64_t p_ready[kAttnQTiles][2];
+  __shared__ __align__(8) uint64_t s_full[kAttnQTiles];
+  __shared__ __align__(8) uint64_t p_ready[kAttnQTiles];
   __shared__ __align__(8) uint64_t o_done[kAttnQTiles][2];     // by step parity, like the S buffers
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
@@ -177,7 +183,9 @@ attn_fwd_kernel(const __grid_constant__ AttnParams p) {
       mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1);
     }
     for (int t = 0; t < kAttnQTiles; ++t) {
-      for (int b = 0; b < 2; ++b) { mbar_init(&s_full[t][b], 1); mbar_init(&p_ready[t][b], 128); mbar_init(&o_done[t][b], 1); }
+      mbar_init(&s_full[t], 1);
+      mbar_init(&p_ready[t], 4);            // one arrival per softmax warp
+      for (int b = 0; b < 2; ++b) mbar_init(&o_done[t][b], 1);
     }
     fence_mbar_init();
     abort_flag = 0;
@@ -205,7 +213,12 @@ attn_fwd_kernel(const __grid_constant__ AttnParams p) {
     }
     __syncwarp();
     bool ok = true;
-    for (int j = 0; j < n_kv && ok; ++j) {
+#ifdef COMFY_ATTN_EXPERIMENT_NO_LOADS
+    const int n_loads = n_kv < kAttnStages ? n_kv : kAttnStages;     // timing experiment only: K / V loaded once
+#else
+    const int n_loads = n_kv;
+#endif
+    for (int j = 0; j < n_loads && ok; ++j) {
       const int s = j % kAttnStages;
       const uint32_t ph = (j / kAttnStages) & 1u;
       ok = mbar_wait_warp(&k_empty[s], ph ^ 1u, abort_ptr);
@@ -227,35 +240,38 @@ attn_fwd_kernel(const __grid_constant__ AttnParams p) {
     }
   } else if (warp == kAttnSoftmaxWarps) {
     // ------------------------------------------------------------------ MMA issuer
-    // Order on the tensor pipe: S_a(0) S_b(0) S_a(1) S_b(1) | O_a(0) S_a(2) O_b(0) S_b(2) | O_a(1) S_a(3) ...
-    // S_t(j+2) overwrites the buffer whose first columns hold P_t(j); it is issued after O_t(j), and the pipe executes
-    // in order.
+    // Order on the tensor pipe: S_a(0) S_b(0) | O_a(0) S_a(1) | O_b(0) S_b(1) | O_a(1) S_a(2) | ...
+    // S_t(j+1) overwrites the columns whose first half holds P_t(j); it is issued after O_t(j), and the pipe executes
+    // MMAs of one shape from one thread in order (all MMAs here are 128 x 128 x 16).
     constexpr uint32_t idesc_qk = umma_idesc<false>(kAttnM, kAttnN);
-    // O_t += P V is issued as two halves of 64 output columns (one V box each), so that every MMA of the kernel has the
-    // same shape 128 x 64 x 16: the tensor pipe keeps MMAs of one shape issued by one thread in order, which the reuse
-    // of the S / P columns relies on
-    constexpr uint32_t idesc_pv = umma_idesc<false>(kAttnM, kAttnD / 2) | (1u << 16);     // B with N contiguous
+    constexpr uint32_t idesc_pv = umma_idesc<false>(kAttnM, kAttnD) | (1u << 16);     // B with N contiguous
     bool ok = mbar_wait_warp(&q_full, 0, abort_ptr);
     const uint32_t q_addr = smem_u32(q_smem);
 
     auto issue_qk = [&](int t, int j) -> bool {      // S_t(j) = Q_t K_j^T; the last tile to use K_j frees its stage
       const int s = j % kAttnStages;
+#ifdef COMFY_ATTN_EXPERIMENT_NO_LOADS
+      if (t == 0 && j < kAttnStages) {
+#else
       if (t == 0) {
+#endif
         if (!mbar_wait_warp(&k_full[s], (j / kAttnStages) & 1u, abort_ptr)) return false;
         tc_fence_after_sync();
       }
       if (elect_one()) {
-        const uint32_t k_addr = smem_u32(k_smem + s * kAttnKvTileBytes);
-        const uint32_t d_tmem = tmem_base + attn_s_col(t, j & 1);
+        // The descriptors of the eight MMAs differ from the first one's only in the start address (16-byte units in the
+        // low bits): one 64-bit add with a constant each, so that issuing an MMA costs a handful of instructions (the
+        // MMAs here last 64 cycles; an issue loop that rebuilds descriptors takes about 100 per MMA).
+        const uint64_t q_desc = umma_desc_k_sw128(q_addr + t * kAttnQTileBytes);
+        const uint64_t k_desc = umma_desc_k_sw128(smem_u32(k_smem + s * kAttnKvTileBytes));
+        const uint32_t d_tmem = tmem_base + attn_s_col(t);
 #pragma unroll
         for (int kk = 0; kk < kAttnD / 16; ++kk) {
           // 16 elements of the head dimension = 32 bytes inside a box; the second 64 elements live in the second box
-          umma_ss<false>(d_tmem,
-                         umma_desc_k_sw128(q_addr + t * kAttnQTileBytes + (kk >> 2) * kAttnQBoxBytes + (kk & 3) * 32),
-                         umma_desc_k_sw128(k_addr + (kk >> 2) * kAttnKvBoxBytes + (kk & 3) * 32), idesc_qk,
-                         kk != 0 ? 1u : 0u);
+          umma_ss<false>(d_tmem, q_desc + (((kk >> 2) * kAttnQBoxBytes + (kk & 3) * 32) >> 4),
+                         k_desc + (((kk >> 2) * kAttnKvBoxBytes + (kk & 3) * 32) >> 4), idesc_qk, kk != 0 ? 1u : 0u);
         }
-        umma_commit(&s_full[t][j & 1]);
+        umma_commit(&s_full[t]);
         if (t == kAttnQTiles - 1) umma_commit(&k_empty[s]);
       }
       __syncwarp();
@@ -263,21 +279,24 @@ attn_fwd_kernel(const __grid_constant__ AttnParams p) {
     };
     auto issue_pv = [&](int t, int j) -> bool {      // O_t += P_t(j) V_j; the last tile to use V_j frees its stage
       const int s = j % kAttnStages;
-      if (!mbar_wait_warp(&p_ready[t][j & 1], (j >> 1) & 1u, abort_ptr)) return false;
+#ifndef COMFY_ATTN_EXPERIMENT_NO_PWAIT
+      if (!mbar_wait_warp(&p_ready[t], j & 1u, abort_ptr)) return false;
+#endif
+#ifdef COMFY_ATTN_EXPERIMENT_NO_LOADS
+      if (t == 0 && j < kAttnStages && !mbar_wait_warp(&v_full[s], (j / kAttnStages) & 1u, abort_ptr)) return false;
+#else
       if (t == 0 && !mbar_wait_warp(&v_full[s], (j / kAttnStages) & 1u, abort_ptr)) return false;
+#endif
       tc_fence_after_sync();
       if (elect_one()) {
-        const uint32_t v_addr = smem_u32(v_smem + s * kAttnKvTileBytes);
-        const uint32_t p_tmem = tmem_base + attn_s_col(t, j & 1);
+        const uint64_t v_desc = umma_desc_mn_sw128(smem_u32(v_smem + s * kAttnKvTileBytes), kAttnKvBoxBytes);
+        const uint32_t p_tmem = tmem_base + attn_s_col(t);
         const uint32_t o_tmem = tmem_base + attn_o_col(t);
+        const uint32_t acc0 = j != 0 ? 1u : 0u;
 #pragma unroll
         for (int kk = 0; kk < kAttnN / 16; ++kk) {
           // 16 keys = two groups of eight rows (2048 bytes); 16 bf16 of P = 8 columns of TMEM
-#pragma unroll
-          for (int half = 0; half < 2; ++half)
-            umma_ts_bf16(o_tmem + half * 64, p_tmem + kk * 8,
-                         umma_desc_mn_sw128(v_addr + half * kAttnKvBoxBytes + kk * 2048, kAttnKvBoxBytes), idesc_pv,
-                         (j | kk) != 0 ? 1u : 0u);
+          umma_ts_bf16(o_tmem, p_tmem + kk * 8, v_desc + ((kk * 2048) >> 4), idesc_pv, kk != 0 ? 1u : acc0);
         }
         umma_commit(&o_done[t][j & 1]);
         if (t == kAttnQTiles - 1) umma_commit(&v_empty[s]);
@@ -286,12 +305,11 @@ attn_fwd_kernel(const __grid_constant__ AttnParams p) {
       return true;
     };
 
-    for (int j = 0; j < 2 && j < n_kv && ok; ++j)
-      for (int t = 0; t < kAttnQTiles && ok; ++t) ok = issue_qk(t, j);
+    for (int t = 0; t < kAttnQTiles && ok; ++t) ok = issue_qk(t, 0);
     for (int j = 0; j < n_kv && ok; ++j) {
       for (int t = 0; t < kAttnQTiles && ok; ++t) {
         ok = issue_pv(t, j);
-        if (ok && j + 2 < n_kv) ok = issue_qk(t, j + 2);
+        if (ok && j + 1 < n_kv) ok = issue_qk(t, j + 1);
       }
     }
     if (!ok) give_up();
@@ -304,13 +322,21 @@ attn_fwd_kernel(const __grid_constant__ AttnParams p) {
     float m_ref = -INFINITY, l_sum = 0.f;                      // m_ref in units of score times scale_log2
     bool ok = true;
     for (int j = 0; j < n_kv && ok; ++j) {
-      const uint32_t s_tmem = lane_base + attn_s_col(t, j & 1);
-      ok = mbar_wait_warp(&s_full[t][j & 1], (j >> 1) & 1u, abort_ptr);
+      const uint32_t s_tmem = lane_base + attn_s_col(t);
+      ok = mbar_wait_warp(&s_full[t], j & 1u, abort_ptr);
       if (!ok) { give_up(); break; }
       tc_fence_after_sync();
-      const int valid = p.seq_kv - j * kAttnN;                 // only the last step can hold fewer than 64 keys
+      const int valid = p.seq_kv - j * kAttnN;                 // only the last step can hold fewer than 128 keys
       const bool partial = valid < kAttnN;
-      uint32_t pr[32];
+#ifdef COMFY_ATTN_EXPERIMENT_NO_SOFTMAX
+      if (j >= 0) {                                            // timing experiment only: no softmax work at all
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&p_ready[t]);
+        continue;
+      }
+#endif
+      uint32_t pr[64];
       float sum, raw_max;
       if (partial) attn_softmax_step<true>(s_tmem, p.scale_log2, -m_ref, valid, pr, sum, raw_max);
       else attn_softmax_step<false>(s_tmem, p.scale_log2, -m_ref, valid, pr, sum, raw_max);
@@ -323,8 +349,7 @@ attn_fwd_kernel(const __grid_constant__ AttnParams p) {
         const float factor = (m_ref == -INFINITY) ? 0.f : fast_exp2(m_ref - m_new);
         if (j > 0) {
           // O holds the sum over steps 0 .. j-1 once the MMAs of step j-1 have finished.  (One barrier per step parity:
-          // a parity wait is only sound while the waiter is less than two phases behind, and the softmax runs up to two
-          // steps ahead of the O MMAs; step j-3's were finished before S(j-1) was handed over.)
+          // a parity wait is only sound while the waiter is less than two phases behind.)
           ok = mbar_wait_warp(&o_done[t][(j - 1) & 1], ((j - 1) >> 1) & 1u, abort_ptr);
           if (!ok) { give_up(); break; }
           tc_fence_after_sync();
@@ -346,10 +371,19 @@ attn_fwd_kernel(const __grid_constant__ AttnParams p) {
         else attn_softmax_step<false>(s_tmem, p.scale_log2, -m_ref, valid, pr, sum, raw_max);
       }
       l_sum += sum;
-      tmem_st_32x32b_x32(s_tmem, pr);                          // P over the first 32 columns of the scores it came from
-      tmem_st_wait();
+      {                                                        // P over the first 64 columns of the scores it came from
+        uint32_t half[32];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) half[i] = pr[h * 32 + i];
+          tmem_st_32x32b_x32(s_tmem + h * 32, half);
+        }
+      }
+      tmem_st_wait();                                          // warp-wide: every lane's probabilities are in TMEM
       tc_fence_before_sync();
-      mbar_arrive(&p_ready[t][j & 1]);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_ready[t]);
     }
     if (ok) {
       ok = mbar_wait_warp(&o_done[t][(n_kv - 1) & 1], ((n_kv - 1) >> 1) & 1u, abort_ptr);

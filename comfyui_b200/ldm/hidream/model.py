@@ -188,6 +188,9 @@ def _apply_rope1(x, freqs_cis):
 
 def attention(query, key, value, transformer_options={}):
     """[B, S, H, D] x 3 -> [B, S, H * D] (``model.py:75-76`` over ``attention_pytorch``)."""
+    fast = b200_ops.hidream_attention(query, key, value)
+    if fast is not None:
+        return fast
     b, s, h, d = query.shape
     out = F.scaled_dot_product_attention(query.transpose(1, 2), key.transpose(1, 2), value.transpose(1, 2),
                                          attn_mask=None, dropout_p=0.0, is_causal=False)

@@ -730,6 +730,32 @@ def hidream_qkv(attn, image_tokens: torch.Tensor, text_tokens: Optional[torch.Te
     return q, k, v
 
 
+# Which kernel runs softmax(q k^T) v on the block path: "kernel" = this library's tcgen05 attention, "library" = PyTorch's
+# scaled_dot_product_attention (what the reference calls).  COMFY_B200_ATTENTION overrides.
+ATTENTION_BACKEND = os.environ.get("COMFY_B200_ATTENTION", "kernel")
+
+
+def hidream_attention(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor) -> Optional[torch.Tensor]:
+    """``attention(query, key, value)`` of ``comfy/ldm/hidream/model.py:75-76`` on the tcgen05 attention kernel:
+    [B, S, H, 128] x 3 (bf16, contiguous) -> [B, S, H * 128], or None when the call is not eligible."""
+    if not ENABLE_SM100_KERNELS or ATTENTION_BACKEND != "kernel":
+        return None
+    q = query
+    if not (q.is_cuda and q.dtype == torch.bfloat16 and q.dim() == 4 and q.shape[-1] == 128 and
+            model_management.is_sm100(q.device)):
+        return None
+    for t in (key, value):
+        if t.dtype != q.dtype or t.device != q.device or t.dim() != 4 or t.shape[0] != q.shape[0] or \
+                t.shape[2:] != q.shape[2:] or not t.is_contiguous():
+            return None
+    if key.shape != value.shape or not q.is_contiguous() or q.shape[1] == 0 or key.shape[1] == 0:
+        return None
+    from . import moe_ops
+
+    with _Range("comfyui_b200::attention"):
+        return moe_ops.attention_forward(query, key, value)
+
+
 # ---- Hunyuan3D-2.1 MoE block (GELU feed-forwards with biases) ------------------------------------------------
 def _biased_linear_state(lin, device):
     """(weight, bias or None) if this Linear can feed the GELU-MLP kernels as it is now, else None."""

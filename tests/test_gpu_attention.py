@@ -174,3 +174,83 @@ def test_attention_projections_take_the_grouped_gemm(cuda_device, monkeypatch):
     want_i, want_t = A.processor(layer, img, txt, freqs, heads)
     torch.testing.assert_close(got_i.float().cpu(), want_i.float(), rtol=2e-2, atol=2e-2)
     torch.testing.assert_close(got_t.float().cpu(), want_t.float(), rtol=2e-2, atol=2e-2)
+
+
+ATTN_SHAPES = [(1, 128, 128, 1), (1, 128, 256, 1), (2, 300, 333, 3), (1, 1000, 77, 2), (1, 1024, 1024, 4),
+               (2, 4480, 4480, 20), (1, 4864, 4864, 20)]
+
+
+@pytest.mark.parametrize("b,sq,skv,h", ATTN_SHAPES)
+def test_attention_kernel_against_fp32_softmax(cuda_device, b, sq, skv, h):
+    """softmax(q k^T / sqrt(d)) v on the tcgen05 kernel against the same in fp32: bf16 tolerance, and no further from
+    the fp32 result than PyTorch's own bf16 attention on this GPU is (plus a margin of one bf16 ulp of the output)."""
+    from comfyui_b200 import moe_ops as M
+
+    dev = cuda_device
+    g = torch.Generator().manual_seed(b + sq + skv + h)
+    q = torch.randn((b, sq, h, 128), generator=g).bfloat16().to(dev)
+    k = torch.randn((b, skv, h, 128), generator=g).bfloat16().to(dev)
+    v = torch.randn((b, skv, h, 128), generator=g).bfloat16().to(dev)
+    out = M.attention_forward(q, k, v)
+    M.read_status(M.device_status(dev))
+
+    def sdpa(q, k, v):
+        o = torch.nn.functional.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2))
+        return o.transpose(1, 2).reshape(q.shape[0], q.shape[1], -1)
+
+    want = sdpa(q.float(), k.float(), v.float())
+    lib = sdpa(q, k, v).float()
+    assert out.shape == (b, sq, h * 128) and not torch.isnan(out.float()).any()
+    torch.testing.assert_close(out.float(), want, rtol=BF16_RTOL, atol=BF16_ATOL)
+    err, err_lib = (out.float() - want).abs().max(), (lib - want).abs().max()
+    rel = (out.float() - want).norm() / want.norm()
+    assert rel < 4e-3 and float(err) <= 2 * float(err_lib) + 4e-3, (float(err), float(err_lib), float(rel))
+
+
+def test_attention_kernel_with_peaked_scores(cuda_device):
+    """Scores far apart (one key dominates a row, and the dominant key arrives late in the sequence): the reference
+    maximum has to be raised and the accumulator rescaled on a late step."""
+    from comfyui_b200 import moe_ops as M
+
+    dev = cuda_device
+    g = torch.Generator().manual_seed(3)
+    b, s, h = 1, 640, 2
+    q = torch.randn((b, s, h, 128), generator=g).bfloat16()
+    k = torch.randn((b, s, h, 128), generator=g).bfloat16()
+    v = torch.randn((b, s, h, 128), generator=g).bfloat16()
+    k[:, 600] = q[:, 5] * 3.0                       # query 5 matches key 600 very strongly (score ~ 3 * |q|^2 / sqrt(d))
+    k[:, 300] = q[:, 9] * 1.5
+    q, k, v = q.to(dev), k.to(dev), v.to(dev)
+    out = M.attention_forward(q, k, v).float()
+    M.read_status(M.device_status(dev))
+    o = torch.nn.functional.scaled_dot_product_attention(q.float().transpose(1, 2), k.float().transpose(1, 2),
+                                                         v.float().transpose(1, 2))
+    want = o.transpose(1, 2).reshape(b, s, -1)
+    torch.testing.assert_close(out, want, rtol=BF16_RTOL, atol=BF16_ATOL)
+    torch.testing.assert_close(out[:, 5, :128], v[:, 600, 0].float(), rtol=BF16_RTOL, atol=BF16_ATOL)
+
+
+def test_blocks_use_the_attention_kernel(cuda_device, monkeypatch):
+    """The attention call of a HiDream block goes through the kernel on an eligible call and through PyTorch's attention
+    when switched to the library; both agree within the bf16 tolerance."""
+    from comfyui_b200 import moe_ops as M, ops
+
+    dev, heads, head_dim, b, s_img, s_txt = cuda_device, 4, 128, 2, 256, 32
+    dim = heads * head_dim
+    layer = A.make_layer(dim, heads, head_dim, False, seed=5, dtype=torch.bfloat16)
+    mod = _module(layer, dim, heads, False, dev)
+    g = torch.Generator().manual_seed(6)
+    img = torch.randn((b, s_img, dim), generator=g).bfloat16().to(dev)
+    txt = torch.randn((b, s_txt, dim), generator=g).bfloat16().to(dev)
+    freqs = A.rope_table(A.make_ids(b, 16, 16, s_txt), [64, 32, 32]).to(dev)
+    calls = []
+    stock = M.attention_forward
+    monkeypatch.setattr(M, "attention_forward", lambda *a, **k: calls.append(1) or stock(*a, **k))
+    with torch.no_grad():
+        fast_i, fast_t = mod(img, None, txt, rope=freqs)
+        assert calls == [1]
+        monkeypatch.setattr(ops, "ATTENTION_BACKEND", "library")
+        lib_i, lib_t = mod(img, None, txt, rope=freqs)
+        assert calls == [1]
+    torch.testing.assert_close(fast_i.float(), lib_i.float(), rtol=BF16_RTOL, atol=BF16_ATOL)
+    torch.testing.assert_close(fast_t.float(), lib_t.float(), rtol=BF16_RTOL, atol=BF16_ATOL)
