@@ -71,8 +71,9 @@ def test_weight_replacement_is_picked_up(cuda_device):
     torch.testing.assert_close(second.view(-1, dim).cpu().float(), ref.float(), rtol=2e-2, atol=2e-2)
 
 
-def test_ineligible_calls_run_the_stock_composition(cuda_device):
-    """LoRA closure on a Linear, or fp32 activations: the module still answers, through PyTorch, like the reference."""
+def test_ineligible_calls_run_the_stock_composition(cuda_device, monkeypatch):
+    """A bias closure on a Linear, patched weights with baking switched off, or fp32 activations: the module still
+    answers, through PyTorch, like the reference."""
     from comfyui_b200 import ops
 
     dev = cuda_device
@@ -82,7 +83,10 @@ def test_ineligible_calls_run_the_stock_composition(cuda_device):
     mod = _module(dev, dim, hidden_dim, ops.disable_weight_init, layer)
     xd = x.to(dev).view(1, n, dim)
     mod.experts[0].w1.weight_function = [lambda w: w * 1.0]
-    assert ops._layer_pack(mod, xd) is None
+    assert ops._layer_pack(mod, xd) is not None             # patched weights are evaluated once for the kernels ...
+    monkeypatch.setattr(ops, "BAKE_PATCHED_WEIGHTS", False)
+    assert ops._layer_pack(mod, xd) is None                 # ... unless that is switched off
+    assert ops._layer_pack(mod, xd.float()) is None
     with torch.inference_mode():
         out = mod(xd)
     ref, _, _ = O.moe_layer(x, layer, gate_in_fp32=True)
