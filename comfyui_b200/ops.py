@@ -377,10 +377,16 @@ def _after_layer_call(layer, n_tokens: int) -> None:
 
 
 
+def _version_of(t: torch.Tensor) -> int:
+    """In-place update counter of a tensor; tensors created under torch.inference_mode() keep none (and cannot be
+    updated in place outside it), so their identity is their storage."""
+    return 0 if t.is_inference() else t._version
+
+
 def _tensor_key(t: Optional[torch.Tensor]):
     if t is None:
         return None
-    return (t.data_ptr(), t._version, t.dtype, t.device, tuple(t.shape), t.stride(0) if t.dim() else 0)
+    return (t.data_ptr(), _version_of(t), t.dtype, t.device, tuple(t.shape), t.stride(0) if t.dim() else 0)
 
 
 # A Linear that carries weight_function closures (what a model patcher attaches instead of baking a LoRA into the

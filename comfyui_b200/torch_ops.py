@@ -36,7 +36,8 @@ def _remember(table: OrderedDict, key, value) -> None:
 
 
 def _key(tensors: Sequence[torch.Tensor]):
-    return tuple((t.data_ptr(), t._version, t.dtype, tuple(t.shape), t.stride(0) if t.dim() else 0) for t in tensors)
+    return tuple((t.data_ptr(), 0 if t.is_inference() else t._version, t.dtype, tuple(t.shape),
+                  t.stride(0) if t.dim() else 0) for t in tensors)
 
 
 def _opt(lst: List[torch.Tensor], i: int) -> Optional[torch.Tensor]:

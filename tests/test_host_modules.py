@@ -231,3 +231,19 @@ def test_patched_weights_are_evaluated_once_for_the_kernels():
         assert ops._linear_state(lin, cpu) is None
     finally:
         ops.BAKE_PATCHED_WEIGHTS = True
+
+
+def test_cache_keys_accept_inference_tensors():
+    """ComfyUI runs under torch.inference_mode(): weights loaded or patched there are inference tensors, which keep no
+    version counter; the shim's cache keys must not ask for one."""
+    from comfyui_b200 import ops, torch_ops
+
+    with torch.inference_mode():
+        lin = ops.disable_weight_init.Linear(16, 8, bias=False, dtype=torch.bfloat16)
+        lin.weight = torch.nn.Parameter(torch.randn(8, 16).bfloat16(), requires_grad=False)
+        assert lin.weight.is_inference()
+        state = ops._linear_state(lin, torch.device("cpu"))
+        lin.weight_function = [lambda w: w * 2]
+        baked = ops._linear_state(lin, torch.device("cpu"))
+    assert state is not None and baked is not None and torch.equal(baked[0], lin.weight * 2)
+    assert ops._tensor_key(baked[0])[1] == 0 and torch_ops._key([baked[0]])[0][1] == 0
