@@ -409,11 +409,17 @@ class PeerBuffers:
 class PeerExpertParallelMoE:
     """``out = ep(x)``: the expert-parallel layer with the rows moved by the kernels over peer memory.
 
-    One stream, no host synchronisation: gate -> plan -> all-gather of the 4-bin histograms (NCCL, device to
-    device) -> dispatch kernel (writes rows into the owners' receive buffers) -> flag -> shared expert -> wait ->
-    grouped GEMM on the received rows -> flag -> wait -> combine kernel (reads results from the owners).
-    The three ``phase_*`` methods are the step cut at its two flag waits, so a test can drive several ranks that
-    live on one GPU in lock step."""
+    Two streams, no host synchronisation.  Main: gate -> plan -> all-gather of the 4-bin histograms (NCCL, device to
+    device) -> dispatch kernel (writes rows into the owners' receive buffers) -> "arrived" flag -> routed experts'
+    first pass (every group waits inside the kernel for its own source's flag) -> second pass of routed and shared
+    expert together (results written into the token owners' return buffers) -> "done" flag -> wait -> combine.
+    Side: the shared expert's first pass, started after the gate, joined before the common second pass.
+    The three ``phase_*`` methods are the step cut where ranks depend on one another, so a test can drive several
+    ranks that live on one GPU in lock step.
+
+    Buffer capacity is fixed by the first call: ``max_tokens`` if given, else the largest token count any rank brings to
+    that call (one all-reduce inside the rendezvous that maps the buffers).  A later call with more tokens than that
+    raises here for the caller's own return buffers and reports through the status word for a peer's receive buffer."""
 
     _tensors = {}       # scratch tensors by shape, shared by all layers (see _scratch)
 
@@ -459,7 +465,12 @@ class PeerExpertParallelMoE:
     def _ensure_buffers(self, n: int, dim: int, device):
         if self.buffers is not None:
             return
-        cap_tokens = self.max_tokens if self.max_tokens is not None else n
+        cap_tokens = self.max_tokens
+        if cap_tokens is None:
+            # ranks may bring different token counts: size every rank's buffers for the largest
+            largest = torch.tensor([n], dtype=torch.int64, device=device)
+            dist.all_reduce(largest, op=dist.ReduceOp.MAX, group=self.group)
+            cap_tokens = int(largest.item())
         # a token sends at most one slot to a given expert: world * tokens rows per local expert at most
         cap_rows = self.world * cap_tokens * min(2, self.place.experts_per_rank)
         act = torch.float8_e4m3fn if self.fp8 else torch.bfloat16

@@ -233,7 +233,8 @@ def _worker(rank, world, port, tokens, fp8, push, out_dir):
         module = _module(dev, fp8)
         n = tokens[rank]
         x = O.make_input(n, DIM, seed=100 + rank).bfloat16().to(dev).view(1, n, DIM)
-        ep = PeerExpertParallelMoE(module, max_tokens=max(tokens), push_results=push)
+        # one case leaves the capacity to the constructor's own agreement between the ranks (their counts differ)
+        ep = PeerExpertParallelMoE(module, max_tokens=None if (world == 2 and fp8) else max(tokens), push_results=push)
         with torch.inference_mode():
             outs = [ep(x) for _ in range(3)]
             ep.check()
