@@ -33,6 +33,17 @@
 
 namespace comfy_b200 {
 
+#ifdef COMFY_ATTN_TRACE
+// Development aid, never built into the library: SM-clock stamps of CTA (0, 0, 0), [role][step][event], read back
+// with comfy_attn_trace_read.  Roles: 0 / 1 = first softmax warp of tile a / b, 2 = MMA warp.
+__device__ long long attn_trace[3][64][12];
+#define ATTN_STAMP(role, step, ev) \
+  do { if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0 && (step) >= 0 && (step) < 64) \
+         attn_trace[role][step][ev] = clock64(); } while (0)
+#else
+#define ATTN_STAMP(role, step, ev) do { } while (0)
+#endif
+
 constexpr int kAttnD = 128;                    // head dimension
 constexpr int kAttnM = 128;                    // query rows per tile
 constexpr int kAttnQTiles = 2;                 // query tiles per CTA
@@ -136,6 +147,24 @@ __device__ __forceinline__ void attn_softmax_step(uint32_t s_tmem, float scale_l
   for (int c = 0; c < 4; ++c) {
     tmem_ld_wait();                                          // chunk c is in sr[c & 1]
     if (c + 1 < 4) tmem_ld_32x32b_x32(s_tmem + (c + 1) * 32, sr[(c + 1) & 1]);
+#ifdef COMFY_ATTN_SOFTMAX_PHASED
+    // the chunk's 32 elements go through each stage together, so that no instruction sits next to the one it depends on
+    float xv[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      float sv = __uint_as_float(sr[c & 1][i]);
+      if constexpr (kMasked) { if (c * 32 + i >= valid) sv = -INFINITY; }
+      mx[i & 3] = fmaxf(mx[i & 3], sv);
+      xv[i] = fmaf(sv, scale_log2, neg_m);
+    }
+#pragma unroll
+    for (int i = 0; i < 32; ++i) xv[i] = fast_exp2(xv[i]);
+#pragma unroll
+    for (int i = 0; i < 32; i += 2) {
+      part[(i >> 1) & 3] += xv[i] + xv[i + 1];
+      pr[c * 16 + (i >> 1)] = pack_bf16x2(xv[i], xv[i + 1]);
+    }
+#else
 #pragma unroll
     for (int i = 0; i < 32; i += 2) {
       float s0 = __uint_as_float(sr[c & 1][i]), s1 = __uint_as_float(sr[c & 1][i + 1]);
@@ -149,6 +178,7 @@ __device__ __forceinline__ void attn_softmax_step(uint32_t s_tmem, float scale_l
       part[(i >> 1) & 3] += e0 + e1;
       pr[c * 16 + (i >> 1)] = pack_bf16x2(e0, e1);
     }
+#endif
   }
   sum = (part[0] + part[1]) + (part[2] + part[3]);
   raw_max = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
@@ -260,6 +290,7 @@ attn_fwd_kernel(const __grid_constant__ AttnParams p) {
         if (!mbar_wait_warp(&k_full[s], (j / kAttnStages) & 1u, abort_ptr)) return false;
         tc_fence_after_sync();
       }
+      ATTN_STAMP(2, j - 1, 6 * t + 4);
       if (elect_one()) {
         // The descriptors of the eight MMAs differ from the first one's only in the start address (16-byte units in the
         // low bits): one 64-bit add with a constant each, so that issuing an MMA costs a handful of instructions (the
@@ -284,12 +315,14 @@ attn_fwd_kernel(const __grid_constant__ AttnParams p) {
 #ifndef COMFY_ATTN_EXPERIMENT_NO_PWAIT
       if (!mbar_wait_warp(&p_ready[t], j & 1u, abort_ptr)) return false;
 #endif
+      ATTN_STAMP(2, j, 6 * t + 1);
 #ifdef COMFY_ATTN_EXPERIMENT_NO_LOADS
       if (t == 0 && j < kAttnStages && !mbar_wait_warp(&v_full[s], (j / kAttnStages) & 1u, abort_ptr)) return false;
 #else
       if (t == 0 && !mbar_wait_warp(&v_full[s], (j / kAttnStages) & 1u, abort_ptr)) return false;
 #endif
       tc_fence_after_sync();
+      ATTN_STAMP(2, j, 6 * t + 2);
       if (elect_one()) {
         const uint64_t v_desc = umma_desc_mn_sw128(smem_u32(v_smem + s * kAttnKvTileBytes), kAttnKvBoxBytes);
         const uint32_t p_tmem = tmem_base + attn_s_col(t);
@@ -310,8 +343,11 @@ attn_fwd_kernel(const __grid_constant__ AttnParams p) {
     for (int t = 0; t < kAttnQTiles && ok; ++t) ok = issue_qk(t, 0);
     for (int j = 0; j < n_kv && ok; ++j) {
       for (int t = 0; t < kAttnQTiles && ok; ++t) {
+        ATTN_STAMP(2, j, 6 * t);
         ok = issue_pv(t, j);
+        ATTN_STAMP(2, j, 6 * t + 3);
         if (ok && j + 1 < n_kv) ok = issue_qk(t, j + 1);
+        ATTN_STAMP(2, j, 6 * t + 5);
       }
     }
     if (!ok) give_up();
@@ -325,9 +361,11 @@ attn_fwd_kernel(const __grid_constant__ AttnParams p) {
     bool ok = true;
     for (int j = 0; j < n_kv && ok; ++j) {
       const uint32_t s_tmem = lane_base + attn_s_col(t);
+      if ((warp & 3) == 0) ATTN_STAMP(t, j, 0);
       ok = mbar_wait_warp(&s_full[t], j & 1u, abort_ptr);
       if (!ok) { give_up(); break; }
       tc_fence_after_sync();
+      if ((warp & 3) == 0) ATTN_STAMP(t, j, 1);
       const int valid = p.seq_kv - j * kAttnN;                 // only the last step can hold fewer than 128 keys
       const bool partial = valid < kAttnN;
 #ifdef COMFY_ATTN_EXPERIMENT_NO_SOFTMAX
@@ -373,6 +411,7 @@ attn_fwd_kernel(const __grid_constant__ AttnParams p) {
         else attn_softmax_step<false>(s_tmem, p.scale_log2, -m_ref, valid, pr, sum, raw_max);
       }
       l_sum += sum;
+      if ((warp & 3) == 0) ATTN_STAMP(t, j, 2);
       {                                                        // P over the first 64 columns of the scores it came from
         uint32_t half[32];
 #pragma unroll
@@ -382,10 +421,13 @@ attn_fwd_kernel(const __grid_constant__ AttnParams p) {
           tmem_st_32x32b_x32(s_tmem + h * 32, half);
         }
       }
+      if ((warp & 3) == 0) ATTN_STAMP(t, j, 4);
       tmem_st_wait();                                          // warp-wide: every lane's probabilities are in TMEM
+      if ((warp & 3) == 0) ATTN_STAMP(t, j, 5);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_ready[t]);
+      if ((warp & 3) == 0) ATTN_STAMP(t, j, 3);
     }
     if (ok) {
       ok = mbar_wait_warp(&o_done[t][(n_kv - 1) & 1], ((n_kv - 1) >> 1) & 1u, abort_ptr);
@@ -459,6 +501,12 @@ static int make_attn_map(CUtensorMap* map, const void* base, int64_t batch, int6
 }  // namespace comfy_b200
 
 using namespace comfy_b200;
+
+#ifdef COMFY_ATTN_TRACE
+extern "C" int comfy_attn_trace_read(long long* host) {
+  return cudaMemcpyFromSymbol(host, attn_trace, sizeof(attn_trace)) == cudaSuccess ? COMFY_MOE_OK : COMFY_MOE_ECUDA;
+}
+#endif
 
 extern "C" int comfy_attn_forward(const void* q, const void* k, const void* v, int batch, int seq_q, int seq_kv,
                                   int heads, int head_dim, float scale, void* out, int32_t* status, void* stream) {

@@ -11,6 +11,9 @@
 
 namespace comfy_b200 {
 
+__device__ __forceinline__ __nv_bfloat162 as_bf162(uint32_t w) { return *reinterpret_cast<const __nv_bfloat162*>(&w); }
+__device__ __forceinline__ __nv_bfloat162 kOneBf162() { return as_bf162(0x3f803f80u); }      // (1.0, 1.0)
+
 constexpr int kLnWarps = 8;              // rows per block in flight, one warp each
 constexpr int kLnMaxChunks = 16;         // 16-byte chunks per lane: dim <= 16 * 32 * 8 = 4096
 
@@ -85,18 +88,22 @@ ln_modulate_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
     for (int j = 0; j < kChunksPerLane; ++j) {
       const int c = lane + 32 * j;
       if (c < chunks) {
-        float f[8], sc[8], sh[8], o[8];
+        // n = bf16((x - mean) * rstd) in fp32, two values per conversion; the rest of the line is bf16 arithmetic in the
+        // reference (each operation exact in fp32, rounded once to bf16), which is what the packed bf16x2 instructions
+        // compute: bf16(1 + scale), bf16(n * .), bf16(. + shift); the _rn forms, which may not be contracted into one fma
+        float f[8];
         unpack_bf16x8(v[j], f);
-        unpack_bf16x8(sc_row[c], sc);
-        unpack_bf16x8(sh_row[c], sh);
+        const uint4 scv = sc_row[c], shv = sh_row[c];
+        const uint32_t scw[4] = {scv.x, scv.y, scv.z, scv.w}, shw[4] = {shv.x, shv.y, shv.z, shv.w};
+        uint32_t ow[4];
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          const float n = round_bf16((f[k] - mean) * rstd);        // LayerNorm output, activation dtype
-          const float one_plus = round_bf16(1.0f + sc[k]);         // (1 + scale) is a bf16 tensor in the reference
-          o[k] = round_bf16(n * one_plus) + sh[k];                 // product rounded, sum rounded by the pack
+        for (int k = 0; k < 4; ++k) {
+          const __nv_bfloat162 n = __floats2bfloat162_rn((f[2 * k] - mean) * rstd, (f[2 * k + 1] - mean) * rstd);
+          const __nv_bfloat162 one_plus = __hadd2_rn(kOneBf162(), as_bf162(scw[k]));
+          const __nv_bfloat162 o = __hadd2_rn(__hmul2_rn(n, one_plus), as_bf162(shw[k]));
+          ow[k] = *reinterpret_cast<const uint32_t*>(&o);
         }
-        const uint4 packed = make_uint4(pack_bf16x2(o[0], o[1]), pack_bf16x2(o[2], o[3]), pack_bf16x2(o[4], o[5]),
-                                        pack_bf16x2(o[6], o[7]));
+        const uint4 packed = make_uint4(ow[0], ow[1], ow[2], ow[3]);
         o_row[c] = packed;
         if constexpr (kGateE > 0) {
           float g[8];

@@ -31,6 +31,7 @@
 // Shared memory: kStages x (A 16 KB + B 32/kCtas KB), 128-byte swizzle.  TMEM: 2 x 256 columns, so the
 // epilogue of tile i overlaps the MMAs of tile i+1.
 #include <cuda.h>
+#include <memory>
 
 #include "moe_common.cuh"
 #include "ptx_sm100.cuh"
@@ -634,7 +635,33 @@ static EncodeTiledFn get_encode_fn() {
 }
 
 // [rows, cols] row-major with leading dimension ld (elements); boxes of 128 rows x 128 bytes.
+// An encoded map is a pure function of these arguments (it holds the address and the layout, not the data), so the
+// maps are remembered per calling thread in a small direct-mapped table: the 48 layers of a model with their ~20 maps
+// each are encoded once, not once per call.
+struct MapMemo {
+  const void* base;
+  int64_t rows, cols, ld;
+  int fp8;      // -1 = empty
+  CUtensorMap map;
+};
+constexpr int kMapMemoSlots = 2048;
+
 static int make_map(CUtensorMap* map, const void* base, bool fp8, int64_t rows, int64_t cols, int64_t ld) {
+  static thread_local std::unique_ptr<MapMemo[]> memo;
+  if (!memo) {
+    memo.reset(new MapMemo[kMapMemoSlots]);
+    for (int i = 0; i < kMapMemoSlots; ++i) memo[i].fp8 = -1;
+  }
+  uint64_t hsh = reinterpret_cast<uintptr_t>(base) >> 4;
+  hsh = (hsh ^ static_cast<uint64_t>(rows) * 0x9e3779b97f4a7c15ull ^ static_cast<uint64_t>(cols) * 0xc2b2ae3d27d4eb4full ^
+         static_cast<uint64_t>(ld) * 0x165667b19e3779f9ull ^ (fp8 ? 0x27d4eb2full : 0ull));
+  hsh ^= hsh >> 29;
+  MapMemo& slot = memo[(hsh * 0x9e3779b97f4a7c15ull) >> 53];   // top 11 bits
+  static_assert(kMapMemoSlots == 1 << 11, "slot index takes the top 11 bits of the hash");
+  if (slot.fp8 == static_cast<int>(fp8) && slot.base == base && slot.rows == rows && slot.cols == cols && slot.ld == ld) {
+    *map = slot.map;
+    return COMFY_MOE_OK;
+  }
   EncodeTiledFn encode = get_encode_fn();
   if (!encode) return COMFY_MOE_EDEVICE;
   const int es = fp8 ? 1 : 2;
@@ -647,7 +674,10 @@ static int make_map(CUtensorMap* map, const void* base, bool fp8, int64_t rows, 
                       const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                       CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? COMFY_MOE_OK : COMFY_MOE_ECUDA;
+  if (r != CUDA_SUCCESS) return COMFY_MOE_ECUDA;
+  slot.base = base; slot.rows = rows; slot.cols = cols; slot.ld = ld; slot.fp8 = static_cast<int>(fp8);
+  slot.map = *map;
+  return COMFY_MOE_OK;
 }
 
 static int device_sm_count(int* sms) {

@@ -15,64 +15,138 @@ constexpr int kMaxRowThreads = 512;    // dim / 8 threads per block: dim <= 4096
 __host__ __device__ constexpr int round_up32(int v) { return (v + 31) & ~31; }
 
 // ------------------------------------------------------------------------------------------------
-// Gate.  One warp per token: lane l owns the 16-byte chunks l, l + 32, ... of the row and has all of them in flight
-// at once (ten loads per lane at dim 2560); the gate weight (20 KB at dim 2560, bf16) is read through L1, which it
-// never leaves, instead of being staged per block; the E dot products are reduced with shuffles in a fixed order
-// (reproducible) and every lane finishes softmax / top-2 redundantly.  Eight tokens per block, so 8192 tokens are 1024
-// short blocks (several resident per SM) rather than one partly filled wave of 256; the per-32-token expert counts
-// the routing plan needs are accumulated with integer atomics in block_counts, which the launcher zeroes.
+// Gate.  The kernel is bound by instruction issue, not by HBM: 4 dot products of 2560 per token are 10 240 fp32 FMAs,
+// and unpacking bf16 weights for them costs as much again, while the token itself is only 5 KB.  So the weight is
+// converted to fp32 ONCE per block into shared memory (laid out so that a warp's 16-byte reads are conflict-free), and a
+// warp takes FOUR tokens at a time: every weight value read from shared memory feeds four FMAs.  Lane l owns the
+// 16-byte chunks l, l + 32, ... of each of its rows, three chunk steps (12 loads per lane) in flight ahead of the
+// arithmetic.  Per token the order of operations is the one gate_accumulate uses (chunks ascending, elements
+// ascending, then a butterfly reduction), so the logits equal those of the fused LayerNorm + gate kernel bit for bit.
+// A block of 8 warps owns the 32 consecutive tokens of one counting block, keeps their expert histogram in shared
+// memory and writes it out: no atomics on global memory, nothing to zero beforehand.
 // ------------------------------------------------------------------------------------------------
 constexpr int kGateWarps = 8;
+constexpr int kGateTokensPerWarp = kTokensPerBlock / kGateWarps;   // 4
+constexpr int kGateDepth = 3;                                       // chunk steps in flight
+
+// float4 index of half h (elements 4h .. 4h + 3) of chunk c of expert e's row in the shared-memory copy
+__device__ __forceinline__ int gate_w_slot(int e, int c, int h, int chunks_pad) {
+  return (e * chunks_pad + (c & ~31)) * 2 + h * 32 + (c & 31);
+}
 
 template <int E, bool kW32, int kChunksPerLane>
-__global__ void __launch_bounds__(kGateWarps * 32)
+__global__ void __launch_bounds__(kGateWarps * 32, E > 4 ? 1 : 2)
 gate_topk_kernel(const __nv_bfloat16* __restrict__ x, const void* __restrict__ w_gate, int n_tokens, int dim,
                  int32_t* __restrict__ topk_idx, float* __restrict__ topk_weight, int32_t* __restrict__ block_counts,
                  int32_t* __restrict__ neartie_count, uint8_t* __restrict__ neartie_flags, float neartie_eps) {
-  const int lane = threadIdx.x & 31;
+  extern __shared__ float4 w_s[];                      // E x chunks_pad x 2 float4
+  __shared__ int hist[E];
+  constexpr int T = kGateTokensPerWarp;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int chunks = dim >> 3;
-  const int row_vecs = kW32 ? chunks * 2 : chunks;     // 16-byte vectors per weight row
-  const uint4* w_rows = static_cast<const uint4*>(w_gate);
-  for (int t = blockIdx.x * kGateWarps + (threadIdx.x >> 5); t < n_tokens; t += gridDim.x * kGateWarps) {
-    const uint4* row = reinterpret_cast<const uint4*>(x + static_cast<size_t>(t) * dim);
-    uint4 v[kChunksPerLane];
-#pragma unroll
-    for (int j = 0; j < kChunksPerLane; ++j) {
-      const int c = lane + 32 * j;
-      if (c < chunks) v[j] = ld_nc_u4(row + c);
+  const int chunks_pad = round_up32(chunks);
+  if constexpr (kW32) {
+    const float4* src = static_cast<const float4*>(w_gate);
+    for (int q = tid; q < E * chunks * 2; q += kGateWarps * 32) {
+      const int e = q / (chunks * 2), r = q - e * chunks * 2;
+      w_s[gate_w_slot(e, r >> 1, r & 1, chunks_pad)] = src[q];
     }
-    float acc[E];
+  } else {
+    const uint4* src = static_cast<const uint4*>(w_gate);
+    for (int q = tid; q < E * chunks; q += kGateWarps * 32) {
+      const int e = q / chunks, c = q - e * chunks;
+      float f[8];
+      unpack_bf16x8(src[q], f);
+      w_s[gate_w_slot(e, c, 0, chunks_pad)] = make_float4(f[0], f[1], f[2], f[3]);
+      w_s[gate_w_slot(e, c, 1, chunks_pad)] = make_float4(f[4], f[5], f[6], f[7]);
+    }
+  }
+  const int n_blocks = (n_tokens + kTokensPerBlock - 1) / kTokensPerBlock;
+  for (int tb = blockIdx.x; tb < n_blocks; tb += gridDim.x) {
+    if (tid < E) hist[tid] = 0;
+    __syncthreads();                                   // weights and histogram ready (previous round's counts written)
+    const int t0 = tb * kTokensPerBlock + warp * T;
+    const uint4* rows[T];
 #pragma unroll
-    for (int e = 0; e < E; ++e) acc[e] = 0.f;
+    for (int i = 0; i < T; ++i) {
+      const int t = t0 + i < n_tokens ? t0 + i : n_tokens - 1;      // rows past the end repeat the last one, unused
+      rows[i] = reinterpret_cast<const uint4*>(x + static_cast<size_t>(t) * dim);
+    }
+    uint4 v[kGateDepth][T];
 #pragma unroll
-    for (int j = 0; j < kChunksPerLane; ++j) {
+    for (int j = 0; j < kGateDepth && j < kChunksPerLane; ++j) {
       const int c = lane + 32 * j;
       if (c < chunks) {
-        float f[8];
-        unpack_bf16x8(v[j], f);
-        gate_accumulate<E, kW32>(w_rows, row_vecs, c, f, acc);
+#pragma unroll
+        for (int i = 0; i < T; ++i) v[j][i] = ld_nc_u4(rows[i] + c);
+      }
+    }
+    float acc[T][E];
+#pragma unroll
+    for (int i = 0; i < T; ++i) {
+#pragma unroll
+      for (int e = 0; e < E; ++e) acc[i][e] = 0.f;
+    }
+#pragma unroll
+    for (int j = 0; j < kChunksPerLane; ++j) {
+      const int c = lane + 32 * j;
+      uint4 cur[T];
+#pragma unroll
+      for (int i = 0; i < T; ++i) cur[i] = v[j % kGateDepth][i];
+      if (j + kGateDepth < kChunksPerLane) {
+        const int cn = lane + 32 * (j + kGateDepth);
+        if (cn < chunks) {
+#pragma unroll
+          for (int i = 0; i < T; ++i) v[j % kGateDepth][i] = ld_nc_u4(rows[i] + cn);
+        }
+      }
+      if (c < chunks) {
+        float f[T][8];
+#pragma unroll
+        for (int i = 0; i < T; ++i) unpack_bf16x8(cur[i], f[i]);
+#pragma unroll
+        for (int e = 0; e < E; ++e) {
+          const float4 a = w_s[gate_w_slot(e, c, 0, chunks_pad)];
+          const float4 b = w_s[gate_w_slot(e, c, 1, chunks_pad)];
+          const float wv[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+          for (int i = 0; i < T; ++i) {
+#pragma unroll
+            for (int k = 0; k < 8; ++k) acc[i][e] = fmaf(f[i][k], wv[k], acc[i][e]);
+          }
+        }
       }
     }
 #pragma unroll
-    for (int e = 0; e < E; ++e) {
+    for (int i = 0; i < T; ++i) {
 #pragma unroll
-      for (int off = 16; off > 0; off >>= 1) acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], off);
+      for (int e = 0; e < E; ++e) {
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) acc[i][e] += __shfl_xor_sync(0xffffffffu, acc[i][e], off);
+      }
     }
-    int i0, i1;
-    float w0, w1;
-    bool tie;
-    gate_select<E>(acc, neartie_eps, i0, i1, w0, w1, tie);
-    if (lane == 0) {
-      topk_idx[2 * t] = i0;
-      topk_idx[2 * t + 1] = i1;
-      topk_weight[2 * t] = w0;
-      topk_weight[2 * t + 1] = w1;
-      int32_t* counts = block_counts + (t / kTokensPerBlock) * E;
-      atomicAdd(counts + i0, 1);                           // integer atomics: the sums do not depend on the order
-      atomicAdd(counts + i1, 1);
-      if (neartie_flags) neartie_flags[t] = tie ? 1 : 0;
-      if (tie && neartie_count) atomicAdd(neartie_count, 1);
+#pragma unroll
+    for (int i = 0; i < T; ++i) {
+      const int t = t0 + i;
+      if (t < n_tokens) {                              // warp-uniform
+        int i0, i1;
+        float w0, w1;
+        bool tie;
+        gate_select<E>(acc[i], neartie_eps, i0, i1, w0, w1, tie);
+        if (lane == 0) {
+          topk_idx[2 * t] = i0;
+          topk_idx[2 * t + 1] = i1;
+          topk_weight[2 * t] = w0;
+          topk_weight[2 * t + 1] = w1;
+          atomicAdd(&hist[i0], 1);
+          atomicAdd(&hist[i1], 1);
+          if (neartie_flags) neartie_flags[t] = tie ? 1 : 0;
+          if (tie && neartie_count) atomicAdd(neartie_count, 1);
+        }
+      }
     }
+    __syncthreads();
+    if (tid < E) block_counts[tb * E + tid] = hist[tid];
   }
 }
 
@@ -356,25 +430,34 @@ static int row_threads(int dim) {
   return t < 64 ? 64 : t;     // the permutation ranks 64 slots with the first two warps
 }
 
+template <int E, bool kW32, int K>
+static int launch_gate_as(const __nv_bfloat16* x, const void* w_gate, int n_tokens, int dim, int32_t* topk_idx,
+                          float* topk_weight, int32_t* block_counts, int32_t* neartie_count, uint8_t* neartie_flags,
+                          float neartie_eps, cudaStream_t stream) {
+  const int n_blocks = (n_tokens + kTokensPerBlock - 1) / kTokensPerBlock;
+  const int grid = n_blocks < 148 * 2 ? n_blocks : 148 * 2;          // two blocks per SM, each converts the weight once
+  const size_t smem = static_cast<size_t>(E) * round_up32(dim >> 3) * 2 * sizeof(float4);
+  auto kernel = gate_topk_kernel<E, kW32, K>;
+  if (smem > 48 * 1024 &&
+      cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
+    return COMFY_MOE_ECUDA;
+  kernel<<<grid, kGateWarps * 32, smem, stream>>>(x, w_gate, n_tokens, dim, topk_idx, topk_weight, block_counts,
+                                                  neartie_count, neartie_flags, neartie_eps);
+  return check_launch();
+}
+
 template <int E>
 static int launch_gate(const void* x, const void* w_gate, int w_dtype, int n_tokens, int dim, int32_t* topk_idx,
                        float* topk_weight, int32_t* block_counts, int32_t* neartie_count, uint8_t* neartie_flags,
                        float neartie_eps, cudaStream_t stream) {
-  const int n_blocks = (n_tokens + kTokensPerBlock - 1) / kTokensPerBlock;
-  if (cudaMemsetAsync(block_counts, 0, sizeof(int32_t) * n_blocks * E, stream) != cudaSuccess) return COMFY_MOE_ECUDA;
-  int grid = (n_tokens + kGateWarps - 1) / kGateWarps;
-  if (grid > 148 * 16) grid = 148 * 16;
-  const int per_lane = ((dim >> 3) + 31) / 32;     // registers hold the row: the smallest instantiation that fits
+  const int per_lane = ((dim >> 3) + 31) / 32;     // chunk steps per lane: the smallest instantiation that covers the row
   const __nv_bfloat16* xp = static_cast<const __nv_bfloat16*>(x);
 #define COMFY_GATE_LAUNCH(W32, K) \
-  gate_topk_kernel<E, W32, K><<<grid, kGateWarps * 32, 0, stream>>>(xp, w_gate, n_tokens, dim, topk_idx, topk_weight, \
-                                                                   block_counts, neartie_count, neartie_flags, \
-                                                                   neartie_eps)
+  return launch_gate_as<E, W32, K>(xp, w_gate, n_tokens, dim, topk_idx, topk_weight, block_counts, neartie_count, \
+                                   neartie_flags, neartie_eps, stream)
 #define COMFY_GATE_PICK(W32) \
   do { \
-    if (per_lane <= 2) COMFY_GATE_LAUNCH(W32, 2); \
-    else if (per_lane <= 4) COMFY_GATE_LAUNCH(W32, 4); \
-    else if (per_lane <= 8) COMFY_GATE_LAUNCH(W32, 8); \
+    if (per_lane <= 4) COMFY_GATE_LAUNCH(W32, 4); \
     else if (per_lane <= 10) COMFY_GATE_LAUNCH(W32, 10); \
     else COMFY_GATE_LAUNCH(W32, 16); \
   } while (0)
@@ -382,7 +465,6 @@ static int launch_gate(const void* x, const void* w_gate, int w_dtype, int n_tok
   else COMFY_GATE_PICK(false);
 #undef COMFY_GATE_PICK
 #undef COMFY_GATE_LAUNCH
-  return check_launch();
 }
 
 extern "C" int comfy_moe_gate_topk(const void* x, const void* w_gate, int w_dtype, int n_tokens, int dim,
