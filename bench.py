@@ -395,6 +395,19 @@ def time_steps(arm, steps: int, barrier, local_rank: int):
     return ev0.elapsed_time(ev1), clocks.summary()
 
 
+def clocks_of_all_ranks(clocks: dict, dev, world: int) -> dict:
+    """Adds every rank's median SM clock under load to rank 0's clock record: the step time of a multi-GPU run is set by
+    the slowest GPU, and GPUs under the same power cap do not all settle at the same clock."""
+    import torch.distributed as dist
+
+    if world > 1:
+        mine = torch.tensor([float(clocks.get("sm_mhz") or 0.0)], dtype=torch.float64, device=dev)
+        every = [torch.zeros_like(mine) for _ in range(world)]
+        dist.all_gather(every, mine)
+        clocks = dict(clocks, sm_mhz_per_rank=[float(t.item()) for t in every])
+    return clocks
+
+
 def max_over_ranks(values, dev, world):
     import torch.distributed as dist
 
@@ -415,6 +428,7 @@ def measure(arm, args, barrier, local_rank, peaks, *, steps: int, warmup: int, e
         for _ in range(max(warmup, 3)):
             arm.step(arm.x)
         ms_total, clocks = time_steps(arm, steps, barrier, local_rank)
+        clocks = clocks_of_all_ranks(clocks, dev, world)
         arm.check()
         st = None
         if world == 1 and stages:
@@ -452,6 +466,7 @@ def measure(arm, args, barrier, local_rank, peaks, *, steps: int, warmup: int, e
             # the same loop for at least 1.2 s: the GPU settles at its power-capped clock
             k_long = max(steps, int(1200.0 / ms_step) + 1)
             ms_long, clocks_long = time_steps(arm, k_long, barrier, local_rank)
+            clocks_long = clocks_of_all_ranks(clocks_long, dev, world)
             (ms_long,) = max_over_ranks([ms_long], dev, world)
             ms_l = ms_long / k_long
             res["sustained"] = {
@@ -639,7 +654,13 @@ def run_gpu_arm(args) -> None:
             if args.timeline_dir:           # every rank writes its own file
                 os.makedirs(args.timeline_dir, exist_ok=True)
                 tag = f"{arm.world}gpus_{'fp8' if arm.fp8 else 'bf16'}{'_config5' if arm.config5 else ''}"
-                print_timeline(arm.step, arm.x, os.path.join(args.timeline_dir, f"timeline_{tag}_rank{rank}.txt"), rank)
+                path = os.path.join(args.timeline_dir, f"timeline_{tag}_rank{rank}.txt")
+                print_timeline(arm.step, arm.x, path, rank)
+                counts = getattr(arm.runner, "last_counts_host", None) if arm.world > 1 else None
+                if counts is not None:      # how much work each expert (and so each rank) had in that step
+                    per_expert = [sum(c[e] for c in counts) for e in range(len(counts[0]))]
+                    with open(path, "a") as f:
+                        print(f"rank {rank}: routed rows per expert over all ranks' tokens: {per_expert}", file=f)
             elif rank == 0:
                 print_timeline(arm.step, arm.x)
             else:

@@ -17,9 +17,18 @@
 // The reference maximum m of a row is only raised when a step's maximum exceeds it by more than 8 (in log2 units): P
 // then stays below 2^8, which bf16 and the fp32 accumulators hold without loss, and O (which lives in TMEM and would
 // have to be read, scaled and written back) is rescaled only on those rare steps; the final division by the row sum
-// makes the result independent of the reference point.  So the common case is ONE pass over a step's scores, 32 at a
-// time with the next 32 already on their way out of TMEM: exponentials against the current m and the step's maximum
-// side by side; only when the maximum turns out too large (always on the first step) is the step redone after raising m.
+// makes the result independent of the reference point.  So the common case is ONE pass over a step's scores:
+// exponentials against the current m and the step's maximum side by side; only when the maximum turns out too large
+// (always on the first step) is the step redone after raising m.
+// What bounds it (measured at 2 x 20 heads x 4480 x 128, SM-clock stamps of one CTA): a step of 128 keys for both tiles
+// needs about 2300 cycles of the tensor pipe (the Q K^T MMAs, both operands from shared memory, run at 80 cycles instead
+// of 64: 8 KB of operands per MMA is more than shared memory delivers in 64) and 2048 cycles of the special-function
+// unit (4 exponentials per clock and sub-partition; the softmax warps alone, tensor pipe idle, take 0.28 ms for the
+// whole problem, the MMA stream alone 0.28 ms too).  The kernel takes 3800 per step, 0.40 ms: S_t(j+1) cannot be issued
+// before P_t(j) has been consumed (they share columns; TMEM has no room for a second S per tile), so each tile's chain is
+// softmax (1700 + 230 to store P) -> O_t += P V, S_t = Q K^T (1150) -> barrier latencies (500), and two tiles fill the
+// pipe to 60 %.  Two threads per row (16 softmax warps) lengthened the chain by the exchange between them (0.43 ms);
+// polling with test_wait instead of try_wait, 16-column loads, and one arrival per thread changed nothing or lost.
 // Warps: 0-3 softmax and epilogue of tile a, 4-7 of tile b (TMEM lane quarter = warp index & 3), 8 = MMA issuer and
 // TMEM owner, 9 = TMA producer.  Every wait is bounded and reports through the status word like the waits of the
 // grouped GEMM.
@@ -132,42 +141,25 @@ __device__ __forceinline__ float fast_exp2(float x) {
 }
 
 // One softmax step of one query row (this thread's TMEM lane): the 128 scores of the step against the reference
-// maximum.  p = exp2(s * scale - m): one FFMA and one MUFU per element.  The scores leave TMEM 32 at a time, the next 32
-// requested before the current ones are worked on; the probabilities come back as 64 bf16 pairs, their unrounded sum
-// in `sum`, the largest raw score in `raw_max` (four independent chains each).  kMasked: only the first `valid` keys
-// of the step exist.
+// maximum.  p = exp2(s * scale - m): one FFMA and one MUFU per element.  The probabilities come back as 64 bf16 pairs,
+// their unrounded sum in `sum`, the largest raw score in `raw_max` (four independent chains each).  kMasked: only the
+// first `valid` keys of the step exist.
 template <bool kMasked>
 __device__ __forceinline__ void attn_softmax_step(uint32_t s_tmem, float scale_log2, float neg_m, int valid,
                                                   uint32_t (&pr)[64], float& sum, float& raw_max) {
   float part[4] = {0.f, 0.f, 0.f, 0.f};
   float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-  uint32_t sr[2][32];
-  tmem_ld_32x32b_x32(s_tmem, sr[0]);
+  // All 128 scores are requested at once and waited for once: a TMEM load takes several hundred cycles while the tensor
+  // pipe works on the other tile, and tcgen05.wait::ld waits for every load in flight.
+  uint32_t sr[4][32];
+#pragma unroll
+  for (int c = 0; c < 4; ++c) tmem_ld_32x32b_x32(s_tmem + c * 32, sr[c]);
+  tmem_ld_wait();
 #pragma unroll
   for (int c = 0; c < 4; ++c) {
-    tmem_ld_wait();                                          // chunk c is in sr[c & 1]
-    if (c + 1 < 4) tmem_ld_32x32b_x32(s_tmem + (c + 1) * 32, sr[(c + 1) & 1]);
-#ifdef COMFY_ATTN_SOFTMAX_PHASED
-    // the chunk's 32 elements go through each stage together, so that no instruction sits next to the one it depends on
-    float xv[32];
-#pragma unroll
-    for (int i = 0; i < 32; ++i) {
-      float sv = __uint_as_float(sr[c & 1][i]);
-      if constexpr (kMasked) { if (c * 32 + i >= valid) sv = -INFINITY; }
-      mx[i & 3] = fmaxf(mx[i & 3], sv);
-      xv[i] = fmaf(sv, scale_log2, neg_m);
-    }
-#pragma unroll
-    for (int i = 0; i < 32; ++i) xv[i] = fast_exp2(xv[i]);
 #pragma unroll
     for (int i = 0; i < 32; i += 2) {
-      part[(i >> 1) & 3] += xv[i] + xv[i + 1];
-      pr[c * 16 + (i >> 1)] = pack_bf16x2(xv[i], xv[i + 1]);
-    }
-#else
-#pragma unroll
-    for (int i = 0; i < 32; i += 2) {
-      float s0 = __uint_as_float(sr[c & 1][i]), s1 = __uint_as_float(sr[c & 1][i + 1]);
+      float s0 = __uint_as_float(sr[c][i]), s1 = __uint_as_float(sr[c][i + 1]);
       if constexpr (kMasked) {
         if (c * 32 + i >= valid) s0 = -INFINITY;
         if (c * 32 + i + 1 >= valid) s1 = -INFINITY;
@@ -178,7 +170,6 @@ __device__ __forceinline__ void attn_softmax_step(uint32_t s_tmem, float scale_l
       part[(i >> 1) & 3] += e0 + e1;
       pr[c * 16 + (i >> 1)] = pack_bf16x2(e0, e1);
     }
-#endif
   }
   sum = (part[0] + part[1]) + (part[2] + part[3]);
   raw_max = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
@@ -340,6 +331,9 @@ attn_fwd_kernel(const __grid_constant__ AttnParams p) {
       return true;
     };
 
+#ifdef COMFY_ATTN_EXPERIMENT_SOFTMAX_ONLY
+    ok = false;                                      // timing experiment only: the tensor pipe stays idle
+#endif
     for (int t = 0; t < kAttnQTiles && ok; ++t) ok = issue_qk(t, 0);
     for (int j = 0; j < n_kv && ok; ++j) {
       for (int t = 0; t < kAttnQTiles && ok; ++t) {
@@ -350,7 +344,9 @@ attn_fwd_kernel(const __grid_constant__ AttnParams p) {
         ATTN_STAMP(2, j, 6 * t + 5);
       }
     }
+#ifndef COMFY_ATTN_EXPERIMENT_SOFTMAX_ONLY
     if (!ok) give_up();
+#endif
   } else {
     // ------------------------------------------------------------------ softmax + epilogue: one query row per thread
     const int t = warp >> 2;                                   // query tile of this warp
@@ -362,8 +358,10 @@ attn_fwd_kernel(const __grid_constant__ AttnParams p) {
     for (int j = 0; j < n_kv && ok; ++j) {
       const uint32_t s_tmem = lane_base + attn_s_col(t);
       if ((warp & 3) == 0) ATTN_STAMP(t, j, 0);
+#ifndef COMFY_ATTN_EXPERIMENT_SOFTMAX_ONLY
       ok = mbar_wait_warp(&s_full[t], j & 1u, abort_ptr);
       if (!ok) { give_up(); break; }
+#endif
       tc_fence_after_sync();
       if ((warp & 3) == 0) ATTN_STAMP(t, j, 1);
       const int valid = p.seq_kv - j * kAttnN;                 // only the last step can hold fewer than 128 keys
@@ -383,7 +381,11 @@ attn_fwd_kernel(const __grid_constant__ AttnParams p) {
       // the probabilities above are good unless some row's maximum lies more than the threshold above its reference
       // (always so on the first step); tcgen05.ld / st are warp-wide, so the warp decides together
       const float mx = raw_max * p.scale_log2;
+#ifdef COMFY_ATTN_EXPERIMENT_SOFTMAX_ONLY
+      const bool raise = mx > 1e30f;                           // timing experiment only: the scores are whatever TMEM held
+#else
       const bool raise = mx > m_ref + kAttnRescaleThreshold;
+#endif
       if (__any_sync(0xffffffffu, raise)) {
         const float m_new = raise ? mx : m_ref;
         const float factor = (m_ref == -INFINITY) ? 0.f : fast_exp2(m_ref - m_new);
@@ -429,10 +431,12 @@ attn_fwd_kernel(const __grid_constant__ AttnParams p) {
       if (lane == 0) mbar_arrive(&p_ready[t]);
       if ((warp & 3) == 0) ATTN_STAMP(t, j, 3);
     }
+#ifndef COMFY_ATTN_EXPERIMENT_SOFTMAX_ONLY
     if (ok) {
       ok = mbar_wait_warp(&o_done[t][(n_kv - 1) & 1], ((n_kv - 1) >> 1) & 1u, abort_ptr);
       if (!ok) give_up();
     }
+#endif
     if (ok) {
       tc_fence_after_sync();
       const float inv = 1.0f / l_sum;
