@@ -197,6 +197,62 @@ def test_gate_fused_into_the_layernorm_pass(cuda_device, b, s, dim, e, w32):
     assert int(f_counts.sum()) == 2 * b * s
 
 
+def test_gate_and_layernorm_timings_are_reported(cuda_device):
+    """Device time of the gate, the LayerNorm + modulation pass, the two in a row and the fused pass at the bench size,
+    printed for the record (run with -s) and not asserted: the GPU is shared, a timing is not a pass criterion.  Cold:
+    a 512 MB buffer is zeroed in front of every launch; hot: 50 launches queued behind a long kernel, so that the
+    events see device time and not the host's launch rate."""
+    from comfyui_b200 import moe_ops as M
+
+    dev = cuda_device
+    n, d, e = 8192, 2560, 4
+    x = O.make_input(n, d, seed=1).bfloat16().to(dev)
+    g = torch.Generator().manual_seed(e)
+    w_gate = (torch.randn((e, d), generator=g) * 0.02).bfloat16().to(dev)
+    shift, scale, _ = O.make_modulation(2, d, seed=6)
+    shift, scale = shift.to(dev)[:, 0], scale.to(dev)[:, 0]
+    out = torch.empty_like(x)
+    flush = torch.empty(512 << 20, dtype=torch.uint8, device=dev)
+    big = torch.randn((8192, 8192), device=dev, dtype=torch.bfloat16)
+
+    def cold(fn, reps=20):
+        for _ in range(3):
+            fn()
+        total = 0.0
+        for _ in range(reps):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            total += e0.elapsed_time(e1)
+        return total / reps * 1e3
+
+    def hot(fn, reps=50):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        for _ in range(6):
+            big @ big
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps * 1e3
+
+    cases = {
+        "gate": lambda: M.gate_topk(x, w_gate),
+        "layernorm + modulation": lambda: M.ln_modulate(x, shift, scale, n // 2, out=out),
+        "the two in a row": lambda: (M.ln_modulate(x, shift, scale, n // 2, out=out), M.gate_topk(out, w_gate)),
+        "fused pass": lambda: M.ln_modulate_gate(x, shift, scale, n // 2, w_gate),
+    }
+    for name, fn in cases.items():
+        print(f"{name:24s} cold {cold(fn):6.1f} us   hot {hot(fn):6.1f} us")
+
+
 def test_block_feed_forward_on_kernels(cuda_device, golden):
     """block_feed_forward on the GPU: fused LayerNorm/modulation, MoE, gate/residual epilogue in the combine."""
     from comfyui_b200 import ops
