@@ -19,7 +19,8 @@ ROW_ALIGN = 128
 TOKENS_PER_BLOCK = 32
 MAX_EXPERTS = 8
 STATIC_MAX_TOKENS = 131072
-STATUS_WORDS = 4        # [0] sticky device status, [1] near-ties of the last gate call, [2] e4m3 overflows, [3] reserved
+STATUS_WORDS = 4         # [0] sticky device status, [1] near-ties of the last gate call, [2] e4m3 overflows, [3] reserved
+LINEAR_MAX_MAPS = 22     # COMFY_MOE_LINEAR_MAX_MAPS: distinct operands of one comfy_moe_grouped_linear call
 MAX_RANKS = 8
 EP_ARRIVED, EP_DONE = 0, 1
 

@@ -50,7 +50,8 @@ constexpr int kGemmThreads = 64 + 32 * kEpilogueWarps;
 constexpr int kTmemCols = kAccStages * kBlockN;   // 512
 constexpr int kBandTiles = 32;                    // row tiles per band of a row-fastest pass (8192 rows on SM pairs)
 constexpr int kMaxGroups = kMaxExperts + 1;
-constexpr int kMaxMaps = 4 + 2 * kMaxGroups;
+constexpr int kMaxMaps = COMFY_MOE_LINEAR_MAX_MAPS;
+static_assert(kMaxMaps >= 4 + 2 * kMaxGroups, "the SwiGLU passes use four activation maps and two weight maps per group");
 
 template <int kCtas> struct GemmShape {
   static constexpr int kTileM = kBlockM * kCtas;
@@ -1056,6 +1057,24 @@ extern "C" int comfy_moe_grouped_linear(int n_groups, const ComfyMoeLinearGroup*
   p.m_fastest = 1;            // K is short: sweep the rows under each weight panel
   int64_t tiles[2] = {0, 0};
   int n_maps = 0, g = 0;
+  // Operands that several groups share (the tokens under the q, k and v projections, a weight under the per-batch
+  // groups of a strided output) get ONE tensor map; GemmParams holds COMFY_MOE_LINEAR_MAX_MAPS of them.
+  struct MapKey { const void* base; int64_t rows, cols, ld; };
+  MapKey keys[kMaxMaps];
+  auto map_for = [&](const void* base, int64_t rows, int64_t cols, int64_t ld, int* index) -> int {
+    for (int m = 0; m < n_maps; ++m) {
+      if (keys[m].base == base && keys[m].rows == rows && keys[m].cols == cols && keys[m].ld == ld) {
+        *index = m;
+        return COMFY_MOE_OK;
+      }
+    }
+    if (n_maps >= kMaxMaps) return COMFY_MOE_EUNSUPPORTED;
+    const int made = make_map(&p.maps[n_maps], base, false, rows, cols, ld);
+    if (made != COMFY_MOE_OK) return made;
+    keys[n_maps] = MapKey{base, rows, cols, ld};
+    *index = n_maps++;
+    return COMFY_MOE_OK;
+  };
   for (int i = 0; i < n_groups; ++i) {
     const ComfyMoeLinearGroup& L = h_groups[i];
     if (L.rows < 0 || L.in_features <= 0 || L.out_features <= 0) return COMFY_MOE_EINVAL;
@@ -1063,11 +1082,12 @@ extern "C" int comfy_moe_grouped_linear(int n_groups, const ComfyMoeLinearGroup*
     if (!L.x || !L.w || !L.out) return COMFY_MOE_EINVAL;
     if (L.bias && !aligned16(L.bias)) return COMFY_MOE_EINVAL;
     if (L.out_features % kBlockN != 0 || L.in_features % k_elems != 0) return COMFY_MOE_EUNSUPPORTED;
-    if ((rc = make_map(&p.maps[n_maps], L.x, false, L.rows, L.in_features, L.ld_x)) != COMFY_MOE_OK) return rc;
-    if ((rc = make_map(&p.maps[n_maps + 1], L.w, false, L.out_features, L.in_features, L.ld_w)) != COMFY_MOE_OK) return rc;
-    if ((rc = make_map(&p.maps[n_maps + 2], L.out, false, L.rows, L.out_features, L.ld_out)) != COMFY_MOE_OK) return rc;
+    int a_map = 0, b_map = 0, o_map = 0;
+    if ((rc = map_for(L.x, L.rows, L.in_features, L.ld_x, &a_map)) != COMFY_MOE_OK) return rc;
+    if ((rc = map_for(L.w, L.out_features, L.in_features, L.ld_w, &b_map)) != COMFY_MOE_OK) return rc;
+    if ((rc = map_for(L.out, L.rows, L.out_features, L.ld_out, &o_map)) != COMFY_MOE_OK) return rc;
     GemmGroup& grp = p.groups[g];
-    grp.a_map = n_maps; grp.b0_map = n_maps + 1; grp.b1_map = n_maps + 1; grp.b1_row_off = 128; grp.out_map = n_maps + 2;
+    grp.a_map = a_map; grp.b0_map = b_map; grp.b1_map = b_map; grp.b1_row_off = 128; grp.out_map = o_map;
     grp.k_blocks = L.in_features / k_elems; grp.n_tiles = L.out_features / kBlockN;
     grp.routed_index = -1; grp.static_rows = L.rows;
     grp.out = L.out; grp.ld_out = L.ld_out;
@@ -1076,7 +1096,6 @@ extern "C" int comfy_moe_grouped_linear(int n_groups, const ComfyMoeLinearGroup*
       const int64_t tile_m = kBlockM * (v + 1);
       tiles[v] += (L.rows + tile_m - 1) / tile_m * grp.n_tiles;
     }
-    n_maps += 3;
     ++g;
   }
   if (g == 0) return COMFY_MOE_OK;

@@ -639,36 +639,45 @@ def _bias_linear_state(lin, device, in_features):
     return (w.detach(), None if b is None else b.detach())
 
 
-def grouped_projections(pairs):
+def grouped_projections(pairs, dests=None):
     """``[lin(x) for lin, x in pairs]`` for bias Linears that share a launch: every (Linear, tokens [.., in]) pair becomes
     one group of one call of the grouped tcgen05 GEMM (a [B, S, in] slice of a longer sequence, whose batch elements
-    are not adjacent in memory, becomes one group per batch element).  Returns the list of outputs, or None when any
-    pair is not eligible (bf16 weights on the tokens' device, no patch closures, out_features % 256 == 0,
-    in_features % 64 == 0, at most nine groups)."""
+    are not adjacent in memory, becomes one group per batch element).  ``dests`` may name, per pair, a [B, S, out] view
+    to write into (rows contiguous; batch elements anywhere), e.g. the rows of a longer joint sequence.  Returns the list
+    of outputs, or None when any pair is not eligible (bf16 weights on the tokens' device, no patch closures,
+    out_features % 256 == 0, in_features % 64 == 0, at most nine groups)."""
     if not ENABLE_SM100_KERNELS or not pairs:
         return None
     from . import moe_ops
 
     groups, outs, results = [], [], []
-    for lin, x in pairs:
+    for i, (lin, x) in enumerate(pairs):
         if not (x.is_cuda and x.dtype == torch.bfloat16 and x.stride(-1) == 1 and model_management.is_sm100(x.device)):
             return None
         state = _bias_linear_state(lin, x.device, x.shape[-1])
         if state is None or x.data_ptr() % 16:
             return None
         w, bias = state
-        out = torch.empty(x.shape[:-1] + (w.shape[0],), dtype=x.dtype, device=x.device)
-        if x.is_contiguous():
+        out = dests[i] if dests is not None and dests[i] is not None else None
+        if out is None:
+            out = torch.empty(x.shape[:-1] + (w.shape[0],), dtype=x.dtype, device=x.device)
+        elif not (out.shape == x.shape[:-1] + (w.shape[0],) and out.dtype == x.dtype and out.device == x.device and
+                  out.dim() == 3 and out.stride(2) == 1 and out.stride(1) == out.shape[2] and
+                  out.data_ptr() % 16 == 0 and (out.stride(0) * 2) % 16 == 0):
+            return None
+        if x.is_contiguous() and out.is_contiguous():
             parts = [(x.reshape(-1, x.shape[-1]), out.view(-1, w.shape[0]))]
         elif x.dim() == 3 and x.stride(1) == x.shape[2] and (x.stride(0) * 2) % 16 == 0:
-            parts = [(x[i], out[i]) for i in range(x.shape[0])]
+            parts = [(x[j], out[j]) for j in range(x.shape[0])]
         else:
             return None
         for xi, oi in parts:
             groups.append((xi, w, bias))
             outs.append(oi)
         results.append(out)
-    if len(groups) > 9:
+    operands = {(t.data_ptr(), tuple(t.shape), t.stride(0)) for xi, wi, _ in groups for t in (xi, wi)}
+    operands |= {(o.data_ptr(), tuple(o.shape), o.stride(0)) for o in outs}
+    if len(groups) > 9 or len(operands) > moe_ops.N.LINEAR_MAX_MAPS:     # one tensor map per distinct operand
         return None
     moe_ops.grouped_linear(groups, outs)
     return results
@@ -723,16 +732,24 @@ def hidream_qkv(attn, image_tokens: torch.Tensor, text_tokens: Optional[torch.Te
     pairs = [(attn.to_q, x), (attn.to_k, x), (attn.to_v, x)]
     if joint:
         pairs += [(attn.to_q_t, text_tokens), (attn.to_k_t, text_tokens), (attn.to_v_t, text_tokens)]
-    proj = grouped_projections(pairs)
+    # the value projections need nothing but the concatenation: the GEMM writes them straight into their rows of v
+    v_rows = v.view(b, s_img + s_txt, inner)
+    dests = [None, None, v_rows[:, :s_img]] + ([None, None, v_rows[:, s_img:]] if joint else [])
+    proj = grouped_projections(pairs, dests)
+    v_done = proj is not None
+    if proj is None:
+        proj = grouped_projections(pairs)
     if proj is None:
         proj = [lin(t) for lin, t in pairs]
     moe_ops.rmsnorm_rope(proj[0], weights[0], eps, rope, heads, q)
     moe_ops.rmsnorm_rope(proj[1], weights[1], eps, rope, heads, k)
-    moe_ops.rmsnorm_rope(proj[2], None, eps, None, heads, v)
+    if not v_done:
+        moe_ops.rmsnorm_rope(proj[2], None, eps, None, heads, v)
     if joint:
         moe_ops.rmsnorm_rope(proj[3], weights[2], eps, rope, heads, q, s_img, s_img)
         moe_ops.rmsnorm_rope(proj[4], weights[3], eps, rope, heads, k, s_img, s_img)
-        moe_ops.rmsnorm_rope(proj[5], None, eps, None, heads, v, s_img, 0)
+        if not v_done:
+            moe_ops.rmsnorm_rope(proj[5], None, eps, None, heads, v, s_img, 0)
     return q, k, v
 
 

@@ -338,7 +338,11 @@ int comfy_moe_forward_gelu_mlp(const ComfyMoeMlpLayer* h_layer, const ComfyMoeWo
  * groups: one launch of the persistent tcgen05 kernel with the bias epilogue.  Serves the q / k / v projections of
  * HiDreamAttention for image and text tokens (comfy/ldm/hidream/model.py:97-119) as six groups, and its two output
  * projections (:139-144) as two.  bf16; out_features % 256 == 0, in_features % 64 == 0, leading dimensions in elements
- * and multiples of 8; rows may be 0 (group skipped).  status: a status block, see comfy_moe_read_status. */
+ * and multiples of 8; rows may be 0 (group skipped).  status: a status block, see comfy_moe_read_status.
+ * At most COMFY_MOE_MAX_EXPERTS + 1 groups, and at most COMFY_MOE_LINEAR_MAX_MAPS DISTINCT operands among them (an x,
+ * w or out that several groups name with the same rows, columns and leading dimension counts once); more is
+ * COMFY_MOE_EUNSUPPORTED. */
+#define COMFY_MOE_LINEAR_MAX_MAPS 22
 typedef struct ComfyMoeLinearGroup {
   const void* x;      /* [rows, in_features], leading dimension ld_x */
   const void* w;      /* [out_features, in_features], leading dimension ld_w */

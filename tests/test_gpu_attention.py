@@ -153,6 +153,26 @@ def test_grouped_linear_against_torch(cuda_device, rows, k, n, bias):
         assert float((out.float() - ref).norm() / ref.norm()) < 3e-3
 
 
+def test_grouped_linear_shares_maps_and_refuses_too_many(cuda_device):
+    """Nine groups over one x need 19 tensor maps and run; nine groups with nothing in common would need 27 (the
+    parameter block holds 22) and are refused before anything is launched."""
+    from comfyui_b200 import _native as N, moe_ops as M
+
+    dev = cuda_device
+    g = torch.Generator().manual_seed(9)
+    x = torch.randn((200, 128), generator=g).bfloat16().to(dev)
+    ws = [(torch.randn((256, 128), generator=g) * 0.05).bfloat16().to(dev) for _ in range(9)]
+    outs = M.grouped_linear([(x, w, None) for w in ws])
+    M.read_status(M.device_status(dev))
+    for w, out in zip(ws, outs):
+        torch.testing.assert_close(out.float(), torch.nn.functional.linear(x.float(), w.float()), rtol=2e-2, atol=2e-2)
+    xs = [torch.randn((200, 128), generator=g).bfloat16().to(dev) for _ in range(9)]
+    with pytest.raises(N.MoeError) as err:
+        M.grouped_linear([(xi, w, None) for xi, w in zip(xs, ws)])
+    assert err.value.code == N.EUNSUPPORTED
+    torch.cuda.synchronize()
+
+
 def test_attention_projections_take_the_grouped_gemm(cuda_device, monkeypatch):
     """On an eligible call the six q / k / v projections and the two output projections run as two grouped launches."""
     from comfyui_b200 import moe_ops as M
@@ -170,7 +190,9 @@ def test_attention_projections_take_the_grouped_gemm(cuda_device, monkeypatch):
     monkeypatch.setattr(M, "grouped_linear", lambda groups, outs=None, status=None: calls.append(len(groups)) or stock(groups, outs, status))
     with torch.no_grad():
         got_i, got_t = mod(img.to(dev), None, txt.to(dev), rope=freqs.to(dev))
-    assert calls == [6, 4]            # q, k, v of image and text tokens; out projections per batch element
+    # q and k of image and text tokens, their v per batch element (written straight into the joint v buffer's rows);
+    # out projections per batch element
+    assert calls == [8, 4]
     want_i, want_t = A.processor(layer, img, txt, freqs, heads)
     torch.testing.assert_close(got_i.float().cpu(), want_i.float(), rtol=2e-2, atol=2e-2)
     torch.testing.assert_close(got_t.float().cpu(), want_t.float(), rtol=2e-2, atol=2e-2)
