@@ -10,7 +10,7 @@ copies exactly those, byte for byte, to ``oracle/_ref/`` with their relative pat
 no reference source enters the history; the directory travels to a GPU box like any other build output, where
 ``oracle/ref_runner.py`` imports it to time the reference's own ``MOEFeedForwardSwiGLU`` on the host cores.
 
-    python -m oracle.build_ref [reference_root]        # default reference root: $COMFY_REFERENCE_ROOT or /root/reference
+    python -m oracle.build_ref [reference_root]        # default: $COMFY_REFERENCE_ROOT, else ~/reference
 """
 from __future__ import annotations
 
@@ -41,7 +41,7 @@ print(json.dumps(files))
 
 
 def reference_root(arg: str | None = None) -> str:
-    return arg or os.environ.get("COMFY_REFERENCE_ROOT", "/root/reference")
+    return arg or os.environ.get("COMFY_REFERENCE_ROOT") or os.path.join(os.path.expanduser("~"), "reference")
 
 
 def build(root: str | None = None, quiet: bool = True) -> list[str]:

@@ -74,7 +74,7 @@ def main(ref_root: str) -> None:
             if not gate_in_fp32:
                 fwd = m.forward(x.clone())
                 out[f"{name}/forward"] = f32(fwd.view(n, DIM))
-                # the survey's observation: both branches agree bit for bit when fed the same routing
+                # both branches of the reference agree bit for bit when fed the same routing
                 meta[f"{name}_forward_equals_infer"] = bool(torch.equal(fwd.view(n, DIM), full))
 
     x32 = O.make_input(BATCH * SEQ, DIM, X_SEED).view(BATCH, SEQ, DIM)
