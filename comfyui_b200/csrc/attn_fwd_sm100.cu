@@ -28,7 +28,11 @@
 // before P_t(j) has been consumed (they share columns; TMEM has no room for a second S per tile), so each tile's chain is
 // softmax (1700 + 230 to store P) -> O_t += P V, S_t = Q K^T (1150) -> barrier latencies (500), and two tiles fill the
 // pipe to 60 %.  Two threads per row (16 softmax warps) lengthened the chain by the exchange between them (0.43 ms);
-// polling with test_wait instead of try_wait, 16-column loads, and one arrival per thread changed nothing or lost.
+// handing P to the MMA warp in four pieces, so that O += P V follows the softmax piece by piece, cost more in waits
+// of the MMA warp (about 150 cycles each even when the barrier is already complete, plus MMA issue that blocks at
+// the pipe's rate) than it saved (0.54 ms), and one MMA warp per tile lost the alternation of the two tiles: both
+// softmax phases then run at the same time and both MMA phases after them (0.54 ms); polling with test_wait instead
+// of try_wait, 16-column loads, and one arrival per thread changed nothing or lost.
 // Warps: 0-3 softmax and epilogue of tile a, 4-7 of tile b (TMEM lane quarter = warp index & 3), 8 = MMA issuer and
 // TMEM owner, 9 = TMA producer.  Every wait is bounded and reports through the status word like the waits of the
 // grouped GEMM.
