@@ -10,7 +10,7 @@ from __future__ import annotations
 import ctypes
 import weakref
 from dataclasses import dataclass, field
-from typing import List, Optional, Sequence, Tuple
+from typing import Optional, Sequence, Tuple
 
 import torch
 

@@ -1,5 +1,4 @@
 """Parity of the sm_100a kernels (called through the C ABI) with the CPU oracle.  Needs a B200."""
-import numpy as np
 import pytest
 import torch
 

@@ -1,6 +1,5 @@
 """Host-side mirror of the reference's module and comfy.ops interface, checked on the CPU against
 outputs of the unmodified reference (golden fixtures)."""
-import numpy as np
 import pytest
 import torch
 
