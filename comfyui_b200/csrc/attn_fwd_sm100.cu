@@ -24,7 +24,7 @@
 // needs about 2300 cycles of the tensor pipe (the Q K^T MMAs, both operands from shared memory, run at 80 cycles instead
 // of 64: 8 KB of operands per MMA is more than shared memory delivers in 64) and 2048 cycles of the special-function
 // unit (4 exponentials per clock and sub-partition; the softmax warps alone, tensor pipe idle, take 0.28 ms for the
-// whole problem, the MMA stream alone 0.28 ms too).  The kernel takes 3800 per step, 0.40 ms: S_t(j+1) cannot be issued
+// whole problem, the MMA stream alone 0.28 ms too).  The kernel takes about 3700 per step, 0.39 ms: S_t(j+1) cannot be issued
 // before P_t(j) has been consumed (they share columns; TMEM has no room for a second S per tile), so each tile's chain is
 // softmax (1700 + 230 to store P) -> O_t += P V, S_t = Q K^T (1150) -> barrier latencies (500), and two tiles fill the
 // pipe to 60 %.  Two threads per row (16 softmax warps) lengthened the chain by the exchange between them (0.43 ms);
@@ -275,76 +275,78 @@ attn_fwd_kernel(const __grid_constant__ AttnParams p) {
     bool ok = mbar_wait_warp(&q_full, 0, abort_ptr);
     const uint32_t q_addr = smem_u32(q_smem);
 
-    auto issue_qk = [&](int t, int j) -> bool {      // S_t(j) = Q_t K_j^T; the last tile to use K_j frees its stage
+    // The eight MMAs of one product differ only in the start addresses inside their descriptors (16-byte units in the low
+    // bits): one 64-bit add with a constant each, so that issuing an MMA costs a handful of instructions (the MMAs here
+    // last 64 to 80 cycles; an issue loop that rebuilds descriptors takes about 100 per MMA).
+    auto mma_qk = [&](int t, int j) {                // S_t(j) = Q_t K_j^T; the last tile to use K_j frees its stage
       const int s = j % kAttnStages;
-#ifdef COMFY_ATTN_EXPERIMENT_NO_LOADS
-      if (t == 0 && j < kAttnStages) {
-#else
-      if (t == 0) {
-#endif
-        if (!mbar_wait_warp(&k_full[s], (j / kAttnStages) & 1u, abort_ptr)) return false;
-        tc_fence_after_sync();
-      }
-      ATTN_STAMP(2, j - 1, 6 * t + 4);
-      if (elect_one()) {
-        // The descriptors of the eight MMAs differ from the first one's only in the start address (16-byte units in the
-        // low bits): one 64-bit add with a constant each, so that issuing an MMA costs a handful of instructions (the
-        // MMAs here last 64 cycles; an issue loop that rebuilds descriptors takes about 100 per MMA).
-        const uint64_t q_desc = umma_desc_k_sw128(q_addr + t * kAttnQTileBytes);
-        const uint64_t k_desc = umma_desc_k_sw128(smem_u32(k_smem + s * kAttnKvTileBytes));
-        const uint32_t d_tmem = tmem_base + attn_s_col(t);
+      const uint64_t q_desc = umma_desc_k_sw128(q_addr + t * kAttnQTileBytes);
+      const uint64_t k_desc = umma_desc_k_sw128(smem_u32(k_smem + s * kAttnKvTileBytes));
+      const uint32_t d_tmem = tmem_base + attn_s_col(t);
 #pragma unroll
-        for (int kk = 0; kk < kAttnD / 16; ++kk) {
-          // 16 elements of the head dimension = 32 bytes inside a box; the second 64 elements live in the second box
-          umma_ss<false>(d_tmem, q_desc + (((kk >> 2) * kAttnQBoxBytes + (kk & 3) * 32) >> 4),
-                         k_desc + (((kk >> 2) * kAttnKvBoxBytes + (kk & 3) * 32) >> 4), idesc_qk, kk != 0 ? 1u : 0u);
-        }
-        umma_commit(&s_full[t]);
-        if (t == kAttnQTiles - 1) umma_commit(&k_empty[s]);
+      for (int kk = 0; kk < kAttnD / 16; ++kk) {
+        // 16 elements of the head dimension = 32 bytes inside a box; the second 64 elements live in the second box
+        umma_ss<false>(d_tmem, q_desc + (((kk >> 2) * kAttnQBoxBytes + (kk & 3) * 32) >> 4),
+                       k_desc + (((kk >> 2) * kAttnKvBoxBytes + (kk & 3) * 32) >> 4), idesc_qk, kk != 0 ? 1u : 0u);
       }
-      __syncwarp();
-      return true;
+      umma_commit(&s_full[t]);
+      if (t == kAttnQTiles - 1) umma_commit(&k_empty[s]);
     };
-    auto issue_pv = [&](int t, int j) -> bool {      // O_t += P_t(j) V_j; the last tile to use V_j frees its stage
+    auto mma_pv = [&](int t, int j) {                // O_t += P_t(j) V_j; the last tile to use V_j frees its stage
       const int s = j % kAttnStages;
-#ifndef COMFY_ATTN_EXPERIMENT_NO_PWAIT
-      if (!mbar_wait_warp(&p_ready[t], j & 1u, abort_ptr)) return false;
-#endif
-      ATTN_STAMP(2, j, 6 * t + 1);
-#ifdef COMFY_ATTN_EXPERIMENT_NO_LOADS
-      if (t == 0 && j < kAttnStages && !mbar_wait_warp(&v_full[s], (j / kAttnStages) & 1u, abort_ptr)) return false;
-#else
-      if (t == 0 && !mbar_wait_warp(&v_full[s], (j / kAttnStages) & 1u, abort_ptr)) return false;
-#endif
-      tc_fence_after_sync();
-      ATTN_STAMP(2, j, 6 * t + 2);
-      if (elect_one()) {
-        const uint64_t v_desc = umma_desc_mn_sw128(smem_u32(v_smem + s * kAttnKvTileBytes), kAttnKvBoxBytes);
-        const uint32_t p_tmem = tmem_base + attn_s_col(t);
-        const uint32_t o_tmem = tmem_base + attn_o_col(t);
-        const uint32_t acc0 = j != 0 ? 1u : 0u;
+      const uint64_t v_desc = umma_desc_mn_sw128(smem_u32(v_smem + s * kAttnKvTileBytes), kAttnKvBoxBytes);
+      const uint32_t p_tmem = tmem_base + attn_s_col(t);
+      const uint32_t o_tmem = tmem_base + attn_o_col(t);
+      const uint32_t acc0 = j != 0 ? 1u : 0u;
 #pragma unroll
-        for (int kk = 0; kk < kAttnN / 16; ++kk) {
-          // 16 keys = two groups of eight rows (2048 bytes); 16 bf16 of P = 8 columns of TMEM
-          umma_ts_bf16(o_tmem, p_tmem + kk * 8, v_desc + ((kk * 2048) >> 4), idesc_pv, kk != 0 ? 1u : acc0);
-        }
-        umma_commit(&o_done[t][j & 1]);
-        if (t == kAttnQTiles - 1) umma_commit(&v_empty[s]);
+      for (int kk = 0; kk < kAttnN / 16; ++kk) {
+        // 16 keys = two groups of eight rows (2048 bytes); 16 bf16 of P = 8 columns of TMEM
+        umma_ts_bf16(o_tmem, p_tmem + kk * 8, v_desc + ((kk * 2048) >> 4), idesc_pv, kk != 0 ? 1u : acc0);
       }
-      __syncwarp();
-      return true;
+      umma_commit(&o_done[t][j & 1]);
+      if (t == kAttnQTiles - 1) umma_commit(&v_empty[s]);
+    };
+    // K_j / V_j are in shared memory.  Asked ahead of time (the tiles arrive a whole step before they are needed), so that
+    // these waits, which cost about 150 cycles even on a completed barrier, stay off the chain P ready -> MMAs issued.
+    auto wait_k = [&](int j) -> bool {
+#ifdef COMFY_ATTN_EXPERIMENT_NO_LOADS
+      if (j >= kAttnStages) return true;
+#endif
+      return mbar_wait_warp(&k_full[j % kAttnStages], (j / kAttnStages) & 1u, abort_ptr);
+    };
+    auto wait_v = [&](int j) -> bool {
+#ifdef COMFY_ATTN_EXPERIMENT_NO_LOADS
+      if (j >= kAttnStages) return true;
+#endif
+      return mbar_wait_warp(&v_full[j % kAttnStages], (j / kAttnStages) & 1u, abort_ptr);
     };
 
 #ifdef COMFY_ATTN_EXPERIMENT_SOFTMAX_ONLY
     ok = false;                                      // timing experiment only: the tensor pipe stays idle
 #endif
-    for (int t = 0; t < kAttnQTiles && ok; ++t) ok = issue_qk(t, 0);
+    if (ok) ok = wait_k(0);
+    if (ok) {
+      tc_fence_after_sync();
+      if (elect_one()) {
+        for (int t = 0; t < kAttnQTiles; ++t) mma_qk(t, 0);
+      }
+      __syncwarp();
+    }
     for (int j = 0; j < n_kv && ok; ++j) {
+      ok = wait_v(j) && (j + 1 >= n_kv || wait_k(j + 1));
       for (int t = 0; t < kAttnQTiles && ok; ++t) {
         ATTN_STAMP(2, j, 6 * t);
-        ok = issue_pv(t, j);
-        ATTN_STAMP(2, j, 6 * t + 3);
-        if (ok && j + 1 < n_kv) ok = issue_qk(t, j + 1);
+#ifndef COMFY_ATTN_EXPERIMENT_NO_PWAIT
+        ok = mbar_wait_warp(&p_ready[t], j & 1u, abort_ptr);
+        if (!ok) break;
+#endif
+        tc_fence_after_sync();
+        ATTN_STAMP(2, j, 6 * t + 1);
+        if (elect_one()) {
+          mma_pv(t, j);
+          if (j + 1 < n_kv) mma_qk(t, j + 1);
+        }
+        __syncwarp();
         ATTN_STAMP(2, j, 6 * t + 5);
       }
     }
