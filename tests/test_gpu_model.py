@@ -48,3 +48,33 @@ def test_step_on_kernels_matches_reference(cuda_device, golden_model, monkeypatc
     assert got.shape == want.shape and not torch.isnan(got).any()
     assert rel < 1e-2 and rel < 1.5 * rel_s + 2e-3
     assert frac < 5e-3 + 2 * frac_s
+
+
+def test_step_replays_from_a_cuda_graph(cuda_device):
+    """The whole model call makes no host synchronisation and allocates only through the caching allocator, so it can be
+    captured once and replayed: the replay gives the bytes of the eager call, and a second replay on other inputs
+    (copied into the captured tensors) the bytes of an eager call on those."""
+    dev = cuda_device
+    m, _ = build(torch.bfloat16, dev)
+    inputs = [t.to(dev) for t in R.make_inputs(torch.bfloat16)]
+    with torch.inference_mode():
+        eager = m(*inputs).clone()
+        side = torch.cuda.Stream()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            m(*inputs)                                  # workspaces and packs exist before the capture
+            torch.cuda.synchronize()
+            with torch.cuda.graph(graph, stream=side):
+                captured = m(*inputs)
+        torch.cuda.synchronize()
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(captured, eager)
+        inputs[0].copy_(inputs[0].flip(0))              # other latents in the same tensors
+        graph.replay()
+        torch.cuda.synchronize()
+        again = captured.clone()
+        assert torch.equal(again, m(*inputs))
+    from comfyui_b200 import ops
+
+    ops.check_device_status()
