@@ -71,8 +71,7 @@ int comfy_moe_plan_sizes(int n_tokens, int n_experts, int top_k, int64_t* rows_c
  *   x             bf16 [n_tokens, dim]
  *   w_gate        [n_experts, dim], dtype w_dtype (COMFY_MOE_BF16 or COMFY_MOE_FP32)
  *   topk_idx      int32 [n_tokens, 2]          topk_weight  fp32 [n_tokens, 2]
- *   block_counts  int32 [n_blocks, n_experts]  (fully overwritten: zeroed by a memset node of the call, then
- *                 accumulated with integer atomics)
+ *   block_counts  int32 [n_blocks, n_experts]  (fully overwritten)
  *   neartie_count int32 [1], may be NULL: incremented for every token whose 2nd and 3rd scores differ by
  *                 less than neartie_eps (caller zeroes it);  neartie_flags uint8 [n_tokens], may be NULL.
  */
