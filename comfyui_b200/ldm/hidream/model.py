@@ -8,7 +8,7 @@ HiDream transformer block can build these instead and load the same checkpoint:
     (+ .scale_weight / .scale_input per Linear under scaled-fp8 operations)
 
 Every ``forward`` first offers the call to the dispatch shim in ``comfyui_b200.ops``; when the call is
-eligible (B200, bf16 activations, bf16 or scaled-e4m3 weights resident on the device, no LoRA closures)
+eligible (B200, bf16 activations, bf16 or scaled-e4m3 weights resident on the device; LoRA closures are baked once)
 the whole layer runs as five kernel launches.  Otherwise the module's own PyTorch composition below runs,
 which is what the reference executes everywhere.
 

@@ -11,8 +11,9 @@ What is mirrored (same names, arguments and behaviour, Linear only — the MoE p
 What is new: the dispatch shim at the bottom.  ``hidream_moe_forward`` / ``hidream_moe_infer`` /
 ``hidream_gate`` / ``swiglu_ffn_forward`` check, on every call, whether the module's current weights
 can be handed to the sm_100a kernels (bf16, or e4m3 with per-tensor scales; resident on the input's
-device; no LoRA closures) and if so run the whole layer there.  They return ``None`` when the call is
-not eligible, and the module then runs its stock PyTorch composition, exactly as the reference would.
+device; LoRA closures on a weight are evaluated once and the patched weight kept) and if so run the whole
+layer there.  They return ``None`` when the call is not eligible, and the module then runs its stock PyTorch
+composition, exactly as the reference would.
 """
 from __future__ import annotations
 
@@ -697,8 +698,9 @@ def hidream_qkv(attn, image_tokens: torch.Tensor, text_tokens: Optional[torch.Te
                 image_tokens_masks=None):
     """What ``HiDreamAttnProcessor_flashattn`` does between the six projections and the attention call
     (``comfy/ldm/hidream/model.py:97-137``): q / k RMSNorm, concatenation of image and text tokens, rotary embedding.
-    Returns (query, key, value) as [B, S_img + S_txt, heads, head_dim], or None when the call is not eligible (the
-    projections themselves stay ``operations.Linear`` calls, i.e. library GEMMs, as in the reference)."""
+    Returns (query, key, value) as [B, S_img + S_txt, heads, head_dim], or None when the call is not eligible.  The
+    projections run as one launch of the grouped GEMM when their Linears are eligible, else through the modules' own
+    ``forward`` (library GEMMs, as in the reference)."""
     x = image_tokens
     if image_tokens_masks is not None or not ENABLE_SM100_KERNELS or rope is None:
         return None
