@@ -683,6 +683,9 @@ def near_gpu(index: int):
     afterwards.  A read-only NVML query and a setting of this process only; does nothing where either is unavailable."""
     old = None
     try:
+        # worker threads of the CPU thread pool inherit the CPU set of the thread that first needs them: have the pool
+        # exist before the set is narrowed, so that the CPU baseline later runs on every core
+        torch.ones(1 << 22).sum()
         import pynvml
 
         pynvml.nvmlInit()
