@@ -23,7 +23,6 @@ compares the expert-parallel output of its tokens with the single-GPU layer).
 from __future__ import annotations
 
 import argparse
-import contextlib
 import json
 import os
 import statistics
@@ -441,10 +440,9 @@ def measure(arm, args, barrier, local_rank, peaks, *, steps: int, warmup: int, e
             # end to end: every step copies its input from pinned host memory and its output back to pinned host
             # memory.  The copies run on their own streams with two buffers each, the way a serving loop would feed
             # the layer: step i's upload and step i-1's download overlap step i's compute; nothing is skipped.
-            with near_gpu(local_rank):      # pinned buffers in the memory of the GPU's own NUMA node
-                x_pinned = arm.x_host.pin_memory()
-                out_pinned = torch.empty_like(arm.x_host).pin_memory()
-                ms_e2e = time_end_to_end(arm.step, x_pinned, out_pinned, n, dev, steps, barrier)
+            x_pinned = arm.x_host.pin_memory()
+            out_pinned = torch.empty_like(arm.x_host).pin_memory()
+            ms_e2e = time_end_to_end(arm.step, x_pinned, out_pinned, n, dev, steps, barrier)
         ms_total, ms_e2e = max_over_ranks([ms_total, ms_e2e], dev, world)
         ms_step = ms_total / steps
         res.update({
@@ -683,36 +681,6 @@ def run_gpu_arm(args) -> None:
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
-
-
-@contextlib.contextmanager
-def near_gpu(index: int):
-    """Runs its body on the CPUs NVML names as local to GPU `index` (the NUMA node its PCIe root hangs off), so that the
-    pinned buffers allocated and touched inside it sit in that node's memory; restores the process's CPU set
-    afterwards.  A read-only NVML query and a setting of this process only; does nothing where either is unavailable."""
-    old = None
-    try:
-        # worker threads of the CPU thread pool inherit the CPU set of the thread that first needs them: have the pool
-        # exist before the set is narrowed, so that the CPU baseline later runs on every core
-        torch.ones(1 << 22).sum()
-        import pynvml
-
-        pynvml.nvmlInit()
-        handle = pynvml.nvmlDeviceGetHandleByIndex(index)
-        words = (os.cpu_count() + 63) // 64
-        mask = pynvml.nvmlDeviceGetCpuAffinity(handle, words)
-        cpus = {64 * w + b for w, word in enumerate(mask) for b in range(64) if (word >> b) & 1}
-        allowed = os.sched_getaffinity(0)
-        if cpus & allowed:
-            old = allowed
-            os.sched_setaffinity(0, cpus & allowed)
-    except Exception:
-        old = None
-    try:
-        yield
-    finally:
-        if old is not None:
-            os.sched_setaffinity(0, old)
 
 
 def time_end_to_end(step, x_pinned, out_pinned, n, dev, steps, barrier):
